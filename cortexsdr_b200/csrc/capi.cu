@@ -1,0 +1,398 @@
+// extern "C" face of the CUDA layer: contexts, device images of compressed segments,
+// and the payload-level operations (unpack, fused matmul, decompress, dequantise).
+// Archive-level and decoder entry points live in host/archive.cpp and decoder.cu.
+#include <cstring>
+#include <string>
+
+#include "internal.hpp"
+
+namespace csdr {
+
+namespace {
+thread_local std::string g_last_error;
+}
+
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+
+DeviceBuffer::DeviceBuffer(size_t n, int dev) : bytes(n), device(dev) {
+    CSDR_CUDA(cudaMalloc(&ptr, n ? n : 16));
+}
+DeviceBuffer::~DeviceBuffer() {
+    if (ptr) cudaFree(ptr);
+}
+
+Geometry make_geometry(const csdr_payload_info& v) {
+    Geometry g;
+    g.rows = v.rows;
+    g.cols = v.cols;
+    g.n_tiles = v.n_tiles;
+    g.tile_rows = v.tile_rows;
+    g.tile_cols = v.tile_cols;
+    g.n_atoms = v.n_atoms;
+    g.n_stages = v.n_stages;
+    g.k = v.k_per_stage;
+    g.rows_full = (v.rows / v.tile_rows) * v.tile_rows;
+    g.cols_full = (v.cols / v.tile_cols) * v.tile_cols;
+    g.n_col_tiles = g.cols_full / v.tile_cols;
+    return g;
+}
+
+// Code stream -> its own 16-byte-aligned device buffer, padded so that kernels may
+// finish a 128-bit load past the last code. (Inside a payload the stream starts at
+// 36 + 4*S + 4*K*T, 16-byte aligned only when S = 3 mod 4.)
+DevPtr upload_codes(csdr_context* ctx, const uint8_t* codes, size_t n_codes) {
+    const size_t bytes = ((n_codes * 2 + 15) & ~static_cast<size_t>(15)) + 16;
+    auto buf = std::make_shared<DeviceBuffer>(bytes, ctx->device);
+    CSDR_CUDA(cudaMemsetAsync(buf->ptr, 0, bytes, ctx->stream));
+    CSDR_CUDA(cudaMemcpyAsync(buf->ptr, codes, n_codes * 2, cudaMemcpyHostToDevice, ctx->stream));
+    return buf;
+}
+
+DevPtr upload(csdr_context* ctx, const void* src, size_t bytes) {
+    auto buf = std::make_shared<DeviceBuffer>(bytes, ctx->device);
+    if (bytes) CSDR_CUDA(cudaMemcpyAsync(buf->ptr, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return buf;
+}
+
+void require_ctx(csdr_context* ctx) {
+    if (!ctx) throw Error(CSDR_ERR_INVALID_ARG, "context is null");
+    CSDR_CUDA(cudaSetDevice(ctx->device));
+}
+
+}  // namespace csdr
+
+using namespace csdr;
+
+void* csdr_context::scratch_get(int slot, size_t bytes) {
+    if (!scratch[slot] || scratch[slot]->bytes < bytes) {
+        // Work queued on the stream may still use the old buffer.
+        CSDR_CUDA(cudaStreamSynchronize(stream));
+        scratch[slot].reset();
+        scratch[slot] = std::make_shared<DeviceBuffer>(bytes, device);
+    }
+    return scratch[slot]->ptr;
+}
+
+extern "C" {
+
+const char* csdr_last_error(void) { return g_last_error.c_str(); }
+const char* csdr_version(void) { return "cortexsdr_b200 0.1 (sm_100a)"; }
+
+int csdr_context_create(int device, void* stream, csdr_context** out) {
+    return guard([&] {
+        if (!out) throw Error(CSDR_ERR_INVALID_ARG, "out is null");
+        int n = 0;
+        if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0)
+            throw Error(CSDR_ERR_CUDA, "no CUDA device: this library has no CPU path");
+        if (device < 0) CSDR_CUDA(cudaGetDevice(&device));
+        if (device >= n) throw Error(CSDR_ERR_INVALID_ARG, "device index out of range");
+        CSDR_CUDA(cudaSetDevice(device));
+        cudaDeviceProp prop{};
+        CSDR_CUDA(cudaGetDeviceProperties(&prop, device));
+        if (prop.major != 10)
+            throw Error(CSDR_ERR_CUDA, std::string("built for sm_100a only; device is sm_") +
+                                           std::to_string(prop.major) + std::to_string(prop.minor));
+        auto ctx = std::make_unique<csdr_context>();
+        ctx->device = device;
+        ctx->sm_count = prop.multiProcessorCount;
+        ctx->smem_optin = prop.sharedMemPerBlockOptin;
+        if (stream) {
+            ctx->stream = static_cast<cudaStream_t>(stream);
+        } else {
+            CSDR_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+            ctx->owns_stream = true;
+        }
+        CSDR_CUDA(cudaMalloc(&ctx->status_word, sizeof(int)));
+        CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
+        *out = ctx.release();
+    });
+}
+
+int csdr_context_destroy(csdr_context* ctx) {
+    return guard([&] {
+        if (!ctx) return;
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        for (auto& s : ctx->scratch) s.reset();
+        if (ctx->status_word) cudaFree(ctx->status_word);
+        if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+    });
+}
+
+int csdr_context_synchronize(csdr_context* ctx) {
+    return guard([&] {
+        require_ctx(ctx);
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+void* csdr_context_stream(csdr_context* ctx) { return ctx ? ctx->stream : nullptr; }
+uint64_t csdr_context_launch_count(const csdr_context* ctx) { return ctx ? ctx->launches : 0; }
+
+int csdr_payload_inspect(const void* payload, size_t nbytes, csdr_payload_info* info) {
+    return guard([&] {
+        if (!info) throw Error(CSDR_ERR_INVALID_ARG, "info is null");
+        *info = inspect_payload(static_cast<const uint8_t*>(payload), nbytes, true);
+    });
+}
+
+int csdr_segment_create(csdr_context* ctx, const void* payload, size_t nbytes, csdr_segment** out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!out) throw Error(CSDR_ERR_INVALID_ARG, "out is null");
+        const uint8_t* p = static_cast<const uint8_t*>(payload);
+        const csdr_payload_info v = inspect_payload(p, nbytes, true);
+        if (v.kind != CSDR_KIND_HSDR)
+            throw Error(CSDR_ERR_FORMAT, "HSDR: bad magic - a codes-only stream needs its dictionary");
+        auto seg = std::make_unique<csdr_segment>();
+        seg->ctx = ctx;
+        seg->info = v;
+        seg->g = make_geometry(v);
+        seg->scales_host.resize(v.n_stages);
+        std::memcpy(seg->scales_host.data(), p + v.off_scales, 4u * v.n_stages);
+        seg->scales = upload(ctx, p + v.off_scales, 4u * v.n_stages);
+        seg->atoms = upload(ctx, p + v.off_dict, v.off_codes - v.off_dict);
+        seg->codes = upload_codes(ctx, p + v.off_codes, static_cast<size_t>(v.n_tiles) * v.n_stages * v.k_per_stage);
+        if (v.edge_bytes) seg->edges = upload(ctx, p + v.off_edges, v.edge_bytes);
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));  // payload memory may go away on return
+        *out = seg.release();
+    });
+}
+
+int csdr_dictionary_create(csdr_context* ctx, uint16_t tile_rows, uint16_t tile_cols,
+                           uint16_t n_atoms, uint8_t n_stages, uint8_t k_per_stage,
+                           const float* atoms, const float* scales, csdr_dictionary** out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!out || !atoms || !scales) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (!tile_rows || !tile_cols || !n_atoms || !n_stages || !k_per_stage || n_atoms > 0x7FFF)
+            throw Error(CSDR_ERR_INVALID_ARG, "dictionary config has a zero or out-of-range field");
+        auto d = std::make_unique<csdr_dictionary>();
+        d->ctx = ctx;
+        d->tile_rows = tile_rows;
+        d->tile_cols = tile_cols;
+        d->n_atoms = n_atoms;
+        d->n_stages = n_stages;
+        d->k = k_per_stage;
+        d->scales_host.assign(scales, scales + n_stages);
+        d->scales = upload(ctx, scales, 4u * n_stages);
+        d->atoms = upload(ctx, atoms, 4ull * n_atoms * tile_rows * tile_cols);
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        *out = d.release();
+    });
+}
+
+int csdr_segment_create_shared(csdr_context* ctx, const void* codes, size_t nbytes,
+                               const csdr_dictionary* dict, csdr_segment** out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!out || !dict) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const uint8_t* p = static_cast<const uint8_t*>(codes);
+        const csdr_payload_info v = inspect_payload(p, nbytes, true);
+        if (v.kind != CSDR_KIND_HSDC) throw Error(CSDR_ERR_FORMAT, "HSDR shared: bad codes-stream magic");
+        if (v.tile_rows != dict->tile_rows || v.tile_cols != dict->tile_cols ||
+            v.n_atoms != dict->n_atoms || v.n_stages != dict->n_stages || v.k_per_stage != dict->k)
+            throw Error(CSDR_ERR_GEOMETRY, "HSDR shared: stream geometry doesn't match dictionary config");
+        auto seg = std::make_unique<csdr_segment>();
+        seg->ctx = ctx;
+        seg->info = v;
+        seg->g = make_geometry(v);
+        seg->scales_host = dict->scales_host;
+        seg->scales = dict->scales;
+        seg->atoms = dict->atoms;
+        seg->codes = upload_codes(ctx, p + v.off_codes, static_cast<size_t>(v.n_tiles) * v.n_stages * v.k_per_stage);
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        *out = seg.release();
+    });
+}
+
+int csdr_segment_destroy(csdr_segment* seg) {
+    return guard([&] {
+        if (!seg) return;
+        cudaSetDevice(seg->ctx->device);
+        cudaStreamSynchronize(seg->ctx->stream);
+        delete seg;
+    });
+}
+
+int csdr_dictionary_destroy(csdr_dictionary* dict) {
+    return guard([&] {
+        if (!dict) return;
+        cudaSetDevice(dict->ctx->device);
+        cudaStreamSynchronize(dict->ctx->stream);
+        delete dict;
+    });
+}
+
+int csdr_segment_info(const csdr_segment* seg, csdr_payload_info* info) {
+    return guard([&] {
+        if (!seg || !info) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        *info = seg->info;
+        info->rows = seg->g.rows;
+        info->n_tiles = seg->g.n_tiles;
+    });
+}
+
+int csdr_segment_shard_rows(csdr_context* ctx, const csdr_segment* seg, uint32_t row_begin,
+                            uint32_t row_end, csdr_segment** out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!seg || !out) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const Geometry& g = seg->g;
+        if (row_begin >= row_end || row_end > g.rows_full)
+            throw Error(CSDR_ERR_INVALID_ARG, "row range outside the tiled region");
+        if (row_begin % g.tile_rows || row_end % g.tile_rows)
+            throw Error(CSDR_ERR_GEOMETRY, "row range must fall on tile-row boundaries");
+        auto sh = std::make_unique<csdr_segment>();
+        sh->ctx = ctx;
+        sh->info = seg->info;
+        sh->g = g;
+        sh->g.rows = row_end - row_begin;
+        sh->g.rows_full = sh->g.rows;
+        sh->g.n_tiles = (sh->g.rows / g.tile_rows) * g.n_col_tiles;
+        sh->scales_host = seg->scales_host;
+        sh->scales = seg->scales;
+        sh->atoms = seg->atoms;
+        const size_t slots = g.slots();
+        const size_t first = static_cast<size_t>(row_begin / g.tile_rows) * g.n_col_tiles * slots;
+        const size_t n_codes = static_cast<size_t>(sh->g.n_tiles) * slots;
+        const size_t bytes = ((n_codes * 2 + 15) & ~static_cast<size_t>(15)) + 16;
+        sh->codes = std::make_shared<DeviceBuffer>(bytes, ctx->device);
+        CSDR_CUDA(cudaMemsetAsync(sh->codes->ptr, 0, bytes, ctx->stream));
+        CSDR_CUDA(cudaMemcpyAsync(sh->codes->ptr, seg->codes_ptr() + first, n_codes * 2,
+                                  cudaMemcpyDeviceToDevice, ctx->stream));
+        if (seg->edges && g.cols != g.cols_full) {
+            // top-right strip rows of the shard
+            const size_t w = g.cols - g.cols_full;
+            sh->edges = std::make_shared<DeviceBuffer>(static_cast<size_t>(sh->g.rows) * w * 4, ctx->device);
+            CSDR_CUDA(cudaMemcpyAsync(sh->edges->ptr,
+                                      static_cast<const float*>(seg->edges->ptr) + static_cast<size_t>(row_begin) * w,
+                                      static_cast<size_t>(sh->g.rows) * w * 4, cudaMemcpyDeviceToDevice,
+                                      ctx->stream));
+        }
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        *out = sh.release();
+    });
+}
+
+int csdr_unpack_codes(csdr_context* ctx, const csdr_segment* seg, int32_t* idx_out,
+                      int8_t* sign_out, size_t capacity) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!seg || !idx_out || !sign_out) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const size_t n = static_cast<size_t>(seg->g.n_tiles) * seg->g.slots();
+        if (capacity < n) throw Error(CSDR_ERR_BUFFER, "unpack output buffers too small");
+        const size_t idx_bytes = (n * 4 + 31) & ~static_cast<size_t>(31);
+        unsigned char* buf = static_cast<unsigned char*>(ctx->scratch_get(3, idx_bytes + n + 32));
+        int32_t* idx_dev = reinterpret_cast<int32_t*>(buf);
+        int8_t* sign_dev = reinterpret_cast<int8_t*>(buf + idx_bytes);
+        launch_unpack(ctx, seg->codes_ptr(), n, idx_dev, sign_dev);
+        CSDR_CUDA(cudaMemcpyAsync(idx_out, idx_dev, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaMemcpyAsync(sign_out, sign_dev, n, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+int csdr_matmul_device_async(csdr_context* ctx, const csdr_segment* seg, const void* x_dev,
+                             int x_dtype, int x_layout, size_t batch, float* y_dev, int y_layout,
+                             const float* bias_dev) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!seg || !x_dev || !y_dev) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if ((x_dtype != CSDR_DTYPE_F32 && x_dtype != CSDR_DTYPE_BF16) ||
+            (x_layout != CSDR_LAYOUT_FEATURE_MAJOR && x_layout != CSDR_LAYOUT_TOKEN_MAJOR) ||
+            (y_layout != CSDR_LAYOUT_FEATURE_MAJOR && y_layout != CSDR_LAYOUT_TOKEN_MAJOR))
+            throw Error(CSDR_ERR_INVALID_ARG, "unknown dtype or layout");
+        MatmulArgs a;
+        a.x = x_dev;
+        a.x_dtype = x_dtype;
+        a.x_layout = x_layout;
+        a.batch = batch;
+        a.y = y_dev;
+        a.y_layout = y_layout;
+        a.bias = bias_dev;
+        launch_matmul(ctx, seg, a);
+    });
+}
+
+int csdr_matmul(csdr_context* ctx, const csdr_segment* seg, const float* x, size_t batch, float* y,
+                int allow_2d) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!seg || !x || !y) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const Geometry& g = seg->g;
+        if (!allow_2d) {
+            // matmulRowMajor's own refusals, strategies/HierarchicalSDRStrategy.cpp:1273-1289.
+            if (g.tile_rows != 1)
+                throw Error(CSDR_ERR_GEOMETRY,
+                            "HSDR matmul: fused matmul requires tile_rows == 1; use decompress() + "
+                            "dense matmul for 2D tile encodings");
+            if (g.tile_cols != g.cols)
+                throw Error(CSDR_ERR_GEOMETRY,
+                            "HSDR matmul: 1D row-tile encoding must have tile_cols == original_cols "
+                            "(each tile is exactly one row of W)");
+        }
+        if (batch == 0) return;
+        const size_t xb = static_cast<size_t>(g.cols) * batch * 4, yb = static_cast<size_t>(g.rows) * batch * 4;
+        const size_t xoff = (xb + 255) & ~static_cast<size_t>(255);
+        unsigned char* buf = static_cast<unsigned char*>(ctx->scratch_get(3, xoff + yb));
+        float* xd = reinterpret_cast<float*>(buf);
+        float* yd = reinterpret_cast<float*>(buf + xoff);
+        CSDR_CUDA(cudaMemcpyAsync(xd, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+        MatmulArgs a;
+        a.x = xd;
+        a.batch = batch;
+        a.y = yd;
+        launch_matmul(ctx, seg, a);
+        CSDR_CUDA(cudaMemcpyAsync(y, yd, yb, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+int csdr_decompress_device_async(csdr_context* ctx, const csdr_segment* seg, float* out_dev) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!seg || !out_dev) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        launch_decode_rows(ctx, seg, nullptr, seg->g.rows, out_dev);
+    });
+}
+
+int csdr_decompress(csdr_context* ctx, const csdr_segment* seg, float* out_host,
+                    size_t capacity_floats) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!seg || !out_host) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const size_t n = static_cast<size_t>(seg->g.rows) * seg->g.cols;
+        if (capacity_floats < n) throw Error(CSDR_ERR_BUFFER, "decompress output buffer too small");
+        float* dev = static_cast<float*>(ctx->scratch_get(2, n * 4));
+        launch_decode_rows(ctx, seg, nullptr, seg->g.rows, dev);
+        CSDR_CUDA(cudaMemcpyAsync(out_host, dev, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+int csdr_dequantize(csdr_context* ctx, const char* fmt, const void* data, size_t nbytes,
+                    float scale, float zero_point, float* out_host, size_t capacity_floats,
+                    size_t* n_out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!data || !out_host) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const int id = dequant_format_id(fmt);
+        if (id < 0)
+            throw Error(CSDR_ERR_UNSUPPORTED,
+                        std::string("HSDR dequant: unsupported input dtype '") + (fmt ? fmt : "") +
+                            "'; supported: f32, f16, bf16, i8, q4_0, q8_0, q4_k, q5_k, q6_k");
+        const size_t n = dequant_output_count(id, nbytes);
+        if (n_out) *n_out = n;
+        if (capacity_floats < n) throw Error(CSDR_ERR_BUFFER, "dequantize output buffer too small");
+        const size_t in_off = (n * 4 + 255) & ~static_cast<size_t>(255);
+        unsigned char* buf = static_cast<unsigned char*>(ctx->scratch_get(2, in_off + nbytes + 16));
+        CSDR_CUDA(cudaMemcpyAsync(buf + in_off, data, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+        launch_dequantize(ctx, id, buf + in_off, nbytes, n, scale, zero_point, reinterpret_cast<float*>(buf));
+        CSDR_CUDA(cudaMemcpyAsync(out_host, buf, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+}  // extern "C"

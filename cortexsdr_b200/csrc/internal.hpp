@@ -1,0 +1,144 @@
+// Internal types shared by the CUDA layer and the C++ host classes.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/cortexsdr_b200.h"
+#include "host/format.hpp"
+
+namespace csdr {
+
+void set_last_error(const std::string& msg);
+
+// Runs f, turning any exception into a status code + thread-local message: nothing
+// throws across the C boundary.
+template <typename F>
+int guard(F&& f) {
+    try {
+        f();
+        return CSDR_OK;
+    } catch (const Error& e) {
+        set_last_error(e.what());
+        return e.code;
+    } catch (const std::bad_alloc&) {
+        set_last_error("out of host memory");
+        return CSDR_ERR_INVALID_ARG;
+    } catch (const std::exception& e) {
+        set_last_error(e.what());
+        return CSDR_ERR_INVALID_ARG;
+    } catch (...) {
+        set_last_error("unknown error");
+        return CSDR_ERR_INVALID_ARG;
+    }
+}
+
+#define CSDR_CUDA(expr)                                                                   \
+    do {                                                                                  \
+        cudaError_t _e = (expr);                                                          \
+        if (_e != cudaSuccess)                                                            \
+            throw ::csdr::Error(CSDR_ERR_CUDA, std::string(#expr) + ": " +                \
+                                                   cudaGetErrorString(_e));               \
+    } while (0)
+
+// Device buffer with shared ownership (dictionaries are shared between a segment,
+// its row shards and, in a .hsda, every segment of a role).
+struct DeviceBuffer {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    int device = 0;
+    DeviceBuffer(size_t n, int dev);
+    ~DeviceBuffer();
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+};
+using DevPtr = std::shared_ptr<DeviceBuffer>;
+
+struct Geometry {
+    uint32_t rows = 0, cols = 0;       // logical shape of this image (a shard has fewer rows)
+    uint32_t n_tiles = 0;
+    uint32_t tile_rows = 0, tile_cols = 0;
+    uint32_t n_atoms = 0, n_stages = 0, k = 0;
+    uint32_t rows_full = 0, cols_full = 0;  // tiled region
+    uint32_t n_col_tiles = 0;
+    bool row_tiles() const { return tile_rows == 1 && tile_cols == cols; }
+    uint32_t slots() const { return n_stages * k; }
+    uint64_t tile_dim() const { return static_cast<uint64_t>(tile_rows) * tile_cols; }
+};
+
+}  // namespace csdr
+
+struct csdr_context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    uint64_t launches = 0;
+    // Grow-only scratch (Dx partials, factored 2-D products, host staging).
+    csdr::DevPtr scratch[4];
+    void* scratch_get(int slot, size_t bytes);
+    int* status_word = nullptr;  // device int: kernels record bounded-wait timeouts here
+};
+
+struct csdr_dictionary {
+    csdr_context* ctx = nullptr;
+    uint32_t tile_rows = 0, tile_cols = 0, n_atoms = 0, n_stages = 0, k = 0;
+    csdr::DevPtr atoms;    // fp32 [n_atoms][tile_rows*tile_cols]
+    csdr::DevPtr scales;   // fp32 [n_stages]
+    std::vector<float> scales_host;
+};
+
+struct csdr_segment {
+    csdr_context* ctx = nullptr;
+    csdr_payload_info info{};   // header of the payload this image came from
+    csdr::Geometry g;
+    csdr::DevPtr atoms, scales; // shared with the dictionary / parent
+    csdr::DevPtr codes;         // u16, 16-byte aligned, padded to a multiple of 16 bytes
+    size_t codes_offset = 0;    // element offset of this image's first code within `codes`
+    csdr::DevPtr edges;         // fp32: top-right strip then bottom strip; may be null
+    std::vector<float> scales_host;
+    const uint16_t* codes_ptr() const {
+        return static_cast<const uint16_t*>(codes->ptr) + codes_offset;
+    }
+};
+
+namespace csdr {
+
+Geometry make_geometry(const csdr_payload_info& v);
+DevPtr upload(csdr_context* ctx, const void* src, size_t bytes);
+void require_ctx(csdr_context* ctx);
+
+// ---- kernel launchers (kernels/*.cu). All asynchronous on ctx->stream. ----
+void launch_unpack(csdr_context* ctx, const uint16_t* codes, size_t n, int32_t* idx, int8_t* sign);
+
+struct MatmulArgs {
+    const void* x = nullptr;   // device
+    int x_dtype = CSDR_DTYPE_F32;
+    int x_layout = CSDR_LAYOUT_FEATURE_MAJOR;
+    size_t batch = 0;
+    float* y = nullptr;        // device
+    int y_layout = CSDR_LAYOUT_FEATURE_MAJOR;
+    const float* bias = nullptr;
+};
+void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a);
+
+// rows == nullptr: every row (decompress); else only the listed rows (embedding lookup).
+void launch_decode_rows(csdr_context* ctx, const csdr_segment* seg, const int32_t* rows_dev,
+                        size_t n_rows, float* out_dev);
+
+void launch_dequantize(csdr_context* ctx, int fmt_id, const uint8_t* data_dev, size_t nbytes,
+                       size_t n_out, float scale, float zero_point, float* out_dev);
+int dequant_format_id(const char* fmt);               // -1 when unknown
+size_t dequant_output_count(int fmt_id, size_t nbytes);  // throws on bad size
+
+void launch_dense_matmul(csdr_context* ctx, const float* W_dev, uint32_t R, uint32_t C,
+                         const MatmulArgs& a);
+
+}  // namespace csdr

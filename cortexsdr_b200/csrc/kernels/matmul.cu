@@ -1,0 +1,689 @@
+// Fused HSDR matmul kernels for sm_100a: sparse-code unpack, the 1-D row-tile
+// decode path (dictionary projection Dx = D*x, then a signed gather over Dx), the
+// factored path for 2-D tiles, raw edge strips, and a dense fallback.
+//
+// What each kernel stands in for, in the reference tree (src/ai_compression/):
+//   hsdr_unpack_kernel      unpackIndexSign, strategies/HierarchicalSDRStrategy.cpp:81-84
+//   hsdr_dx_kernel          the Dx loop of matmulRowMajor, :1304-1315 (and :1854-1863)
+//   hsdr_gather_kernel      the gather loop of matmulRowMajor, :1318-1336 (and :1866-1881)
+//   hsdr_tile_project/_tile_gather/_edge kernels
+//                           decompress (:1340-1440) followed by the dense product of
+//                           SDRInferenceEngine::matmulForLayer (SparseInferenceEngine.cpp:1301-1310),
+//                           computed in factored form so the weight never exists in memory
+//   dense_rows_kernel       the same dense product for stored-raw fp32 segments
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "../internal.hpp"
+
+namespace cg = cooperative_groups;
+
+namespace csdr {
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// helpers
+// ---------------------------------------------------------------------------
+
+// Streaming 128-bit load: the dictionary is read once per launch, keep it out of L1.
+__device__ __forceinline__ float4 ldg_stream_f4(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+struct XView {
+    const void* x;
+    int dtype;       // CSDR_DTYPE_*
+    int layout;      // CSDR_LAYOUT_*
+    uint32_t C;      // features
+    uint32_t Mtotal; // tokens in the whole activation matrix
+    uint32_t b0;     // first token of this launch's chunk
+    uint32_t M;      // tokens in this chunk (<= MT)
+};
+
+__device__ __forceinline__ float load_x(const XView& v, uint32_t c, uint32_t b) {
+    const size_t i = v.layout == CSDR_LAYOUT_FEATURE_MAJOR
+                         ? static_cast<size_t>(c) * v.Mtotal + (v.b0 + b)
+                         : static_cast<size_t>(v.b0 + b) * v.C + c;
+    if (v.dtype == CSDR_DTYPE_BF16)
+        return __bfloat162float(static_cast<const __nv_bfloat16*>(v.x)[i]);
+    return static_cast<const float*>(v.x)[i];
+}
+
+struct YView {
+    float* y;
+    int layout;
+    uint32_t R;
+    uint32_t Mtotal;
+    uint32_t b0;
+    uint32_t M;
+    const float* bias;
+};
+
+__device__ __forceinline__ size_t y_index(const YView& v, uint32_t r, uint32_t b) {
+    return v.layout == CSDR_LAYOUT_FEATURE_MAJOR
+               ? static_cast<size_t>(r) * v.Mtotal + (v.b0 + b)
+               : static_cast<size_t>(v.b0 + b) * v.R + r;
+}
+
+// ---------------------------------------------------------------------------
+// K1: unpack. 8 codes per 128-bit load; indices leave as two 128-bit stores, signs
+// as one 64-bit store.
+// ---------------------------------------------------------------------------
+__global__ void hsdr_unpack_kernel(const uint16_t* __restrict__ codes, size_t n,
+                                   int32_t* __restrict__ idx, int8_t* __restrict__ sign) {
+    const size_t n8 = n / 8;
+    const size_t t = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = t; i < n8; i += stride) {
+        const uint4 v = reinterpret_cast<const uint4*>(codes)[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        int32_t id[8];
+        uint32_t sg[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t lo = w[j] & 0xFFFFu, hi = w[j] >> 16;
+            id[2 * j] = static_cast<int32_t>(lo & 0x7FFFu);
+            id[2 * j + 1] = static_cast<int32_t>(hi & 0x7FFFu);
+            const uint32_t s0 = (lo & 0x8000u) ? 0xFFu : 0x01u;
+            const uint32_t s1 = (hi & 0x8000u) ? 0xFFu : 0x01u;
+            const int e = 2 * j;
+            sg[e / 4] |= s0 << (8 * (e % 4));
+            sg[(e + 1) / 4] |= s1 << (8 * ((e + 1) % 4));
+        }
+        reinterpret_cast<int4*>(idx)[2 * i] = make_int4(id[0], id[1], id[2], id[3]);
+        reinterpret_cast<int4*>(idx)[2 * i + 1] = make_int4(id[4], id[5], id[6], id[7]);
+        reinterpret_cast<uint2*>(sign)[i] = make_uint2(sg[0], sg[1]);
+    }
+    for (size_t i = n8 * 8 + t; i < n; i += stride) {
+        const uint16_t c = codes[i];
+        idx[i] = static_cast<int32_t>(c & 0x7FFFu);
+        sign[i] = (c & 0x8000u) ? -1 : 1;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// K2: Dx[a][b] = sum_c D[a][c] * x[c][b] for 1-D row tiles.
+//
+// Grid (nsplit, ceil(K / (8*A))), cluster (nsplit,1,1). A CTA owns 8*A atoms and one
+// column slab; its x slab sits in shared memory token-major; each warp streams A
+// dictionary rows with 128-bit loads, U*A of them in flight per lane, and keeps
+// A*MT accumulators in registers. The column-split partials meet in distributed
+// shared memory and are summed by the cluster's first CTA in a fixed order, so the
+// result does not depend on scheduling.
+// ---------------------------------------------------------------------------
+template <int MT, int A, int U>
+__global__ void __launch_bounds__(256)
+hsdr_dx_kernel(const float* __restrict__ D, uint32_t K, uint32_t C, uint32_t slab, XView xv,
+               float* __restrict__ dx, int nsplit) {
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;                      // [MT][slab]
+    float* part = smem + MT * slab;        // [8*A][MT]
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t c0 = blockIdx.x * slab;
+    const uint32_t cw = c0 < C ? min(slab, C - c0) : 0u;
+
+    for (uint32_t i = tid; i < MT * slab; i += 256) {
+        const uint32_t b = i / slab, c = i - b * slab;
+        xs[i] = (b < xv.M && c < cw) ? load_x(xv, c0 + c, b) : 0.0f;
+    }
+    __syncthreads();
+
+    const uint32_t atom0 = (blockIdx.y * 8u + warp) * A;
+    const uint32_t slab4 = slab >> 2, cw4 = cw >> 2;
+    const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    const float4* drow[A];
+    bool valid[A];
+#pragma unroll
+    for (int a = 0; a < A; ++a) {
+        valid[a] = atom0 + a < K;
+        drow[a] = reinterpret_cast<const float4*>(
+            D + static_cast<size_t>(valid[a] ? atom0 + a : 0u) * C + c0);
+    }
+    float acc[A][MT];
+#pragma unroll
+    for (int a = 0; a < A; ++a)
+#pragma unroll
+        for (int b = 0; b < MT; ++b) acc[a][b] = 0.0f;
+
+    for (uint32_t base = 0; base < cw4; base += 32u * U) {
+        float4 d[U][A];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t c4 = base + u * 32u + lane;
+#pragma unroll
+            for (int a = 0; a < A; ++a)
+                d[u][a] = (c4 < cw4 && valid[a]) ? ldg_stream_f4(drow[a] + c4)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t c4 = base + u * 32u + lane;
+            if (c4 < cw4) {
+#pragma unroll
+                for (int b = 0; b < MT; ++b) {
+                    const float4 x4 = xs4[b * slab4 + c4];
+#pragma unroll
+                    for (int a = 0; a < A; ++a) {
+                        acc[a][b] = fmaf(d[u][a].x, x4.x, acc[a][b]);
+                        acc[a][b] = fmaf(d[u][a].y, x4.y, acc[a][b]);
+                        acc[a][b] = fmaf(d[u][a].z, x4.z, acc[a][b]);
+                        acc[a][b] = fmaf(d[u][a].w, x4.w, acc[a][b]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < A; ++a)
+#pragma unroll
+        for (int b = 0; b < MT; ++b) {
+            float v = acc[a][b];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+            if (lane == 0) part[(warp * A + a) * MT + b] = v;
+        }
+    __syncthreads();
+
+    const uint32_t n_out = 8u * A * MT;
+    if (nsplit == 1) {
+        for (uint32_t t = tid; t < n_out; t += 256) {
+            const uint32_t atom = blockIdx.y * 8u * A + t / MT;
+            if (atom < K) dx[static_cast<size_t>(atom) * MT + t % MT] = part[t];
+        }
+    } else {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (cluster.block_rank() == 0) {
+            for (uint32_t t = tid; t < n_out; t += 256) {
+                float s = 0.0f;
+                for (int r = 0; r < nsplit; ++r) s += cluster.map_shared_rank(part, r)[t];
+                const uint32_t atom = blockIdx.y * 8u * A + t / MT;
+                if (atom < K) dx[static_cast<size_t>(atom) * MT + t % MT] = s;
+            }
+        }
+        cluster.sync();  // peers' shared memory must outlive the reads above
+    }
+}
+
+// ---------------------------------------------------------------------------
+// K3: y[r][b] = sum_l gamma_l * sum_k sign * Dx[idx][b], in the reference's order
+// (stage-major, slot-minor), one multiply and one add per code as its source has it.
+// The CTA's slice of the code stream enters shared memory through 128-bit loads.
+// ---------------------------------------------------------------------------
+constexpr int kGatherThreads = 128;
+
+template <int MT>
+__global__ void __launch_bounds__(kGatherThreads)
+hsdr_gather_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, uint32_t k,
+                   const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
+                   uint32_t rows_per_cta, int dx_in_smem, YView yv) {
+    extern __shared__ __align__(16) unsigned char gsm[];
+    const uint32_t slots = S * k;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t row0 = blockIdx.x * rows_per_cta;
+    if (row0 >= R) return;
+    const uint32_t rows_here = min(rows_per_cta, R - row0);
+
+    // layout: codes (16-byte units) | scales | Dx
+    const size_t code_byte0 = static_cast<size_t>(row0) * slots * 2u;
+    const size_t aligned0 = code_byte0 & ~static_cast<size_t>(15);
+    const uint32_t skip = static_cast<uint32_t>(code_byte0 - aligned0) >> 1;
+    const uint32_t n_codes = rows_here * slots;
+    const uint32_t n16 = (skip * 2u + n_codes * 2u + 15u) >> 4;
+    const uint32_t cap16 = (rows_per_cta * slots * 2u + 15u + 16u) >> 4;
+    uint4* cs16 = reinterpret_cast<uint4*>(gsm);
+    float* sc = reinterpret_cast<float*>(gsm + static_cast<size_t>(cap16) * 16u);
+    float* dxs = sc + ((S + 3u) & ~3u);
+
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(codes) + aligned0);
+    for (uint32_t i = tid; i < n16; i += kGatherThreads) cs16[i] = src[i];
+    for (uint32_t i = tid; i < S; i += kGatherThreads) sc[i] = scales[i];
+    if (dx_in_smem) {
+        const uint32_t n4 = (K * MT) >> 2;
+        const float4* g4 = reinterpret_cast<const float4*>(dx);
+        for (uint32_t i = tid; i < n4; i += kGatherThreads) reinterpret_cast<float4*>(dxs)[i] = g4[i];
+        for (uint32_t i = (n4 << 2) + tid; i < K * MT; i += kGatherThreads) dxs[i] = dx[i];
+    }
+    __syncthreads();
+    const uint16_t* cs = reinterpret_cast<const uint16_t*>(cs16) + skip;
+    const float* dxp = dx_in_smem ? dxs : dx;
+
+    const uint32_t b = tid % MT;
+    constexpr uint32_t RP = kGatherThreads / MT;
+    for (uint32_t rl = tid / MT; rl < rows_here; rl += RP) {
+        const uint16_t* rc = cs + rl * slots;
+        float acc = 0.0f;
+        for (uint32_t l = 0; l < S; ++l) {
+            const float gamma = sc[l];
+            for (uint32_t kk = 0; kk < k; ++kk) {
+                const uint32_t code = rc[l * k + kk];
+                const float scale = (code & 0x8000u) ? -gamma : gamma;
+                acc = __fadd_rn(acc, __fmul_rn(scale, dxp[(code & 0x7FFFu) * MT + b]));
+            }
+        }
+        if (b < yv.M) {
+            const uint32_t r = row0 + rl;
+            if (yv.bias) acc += yv.bias[r];
+            yv.y[y_index(yv, r, b)] = acc;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 2-D tiles, phase 1: P[a][bc][j][b] = sum_i D[a][j][i] * x[bc*Tc + i][b].
+// The dictionary is one matrix of K*Tr "virtual rows" of Tc floats; the CTA stages 64
+// of them in shared memory (row stride Tc+4 keeps 128-bit reads conflict-free), lane =
+// virtual row, each warp walks its column tiles 8 at a time with x broadcast from
+// shared memory. Writes are contiguous in j.
+// ---------------------------------------------------------------------------
+constexpr int kProjRows = 64;
+
+template <int MT>
+__global__ void __launch_bounds__(256)
+hsdr_tile_project_kernel(const float* __restrict__ D, uint32_t VR /* K*Tr */, uint32_t Tr,
+                         uint32_t Tc, uint32_t n_ct, XView xv, float* __restrict__ P) {
+    extern __shared__ __align__(16) float psm[];
+    const uint32_t dstride = Tc + 4u;
+    float* dt = psm;                               // [64][Tc+4]
+    float* xs = psm + kProjRows * dstride;         // [MT][n_ct][Tc]
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t vr0 = blockIdx.x * kProjRows;
+    const uint32_t Tc4 = Tc >> 2;
+
+    for (uint32_t i = tid; i < kProjRows * Tc4; i += 256) {
+        const uint32_t r = i / Tc4, c4 = i - r * Tc4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (vr0 + r < VR)
+            v = ldg_stream_f4(reinterpret_cast<const float4*>(D + static_cast<size_t>(vr0 + r) * Tc) + c4);
+        *reinterpret_cast<float4*>(dt + r * dstride + c4 * 4u) = v;
+    }
+    const uint32_t Cf = n_ct * Tc;
+    for (uint32_t i = tid; i < MT * Cf; i += 256) {
+        const uint32_t b = i / Cf, c = i - b * Cf;
+        xs[i] = b < xv.M ? load_x(xv, c, b) : 0.0f;
+    }
+    __syncthreads();
+
+    const uint32_t rg = warp & 1u;                 // which 32-row group
+    const uint32_t vr = vr0 + rg * 32u + lane;
+    const float* drow = dt + (rg * 32u + lane) * dstride;
+    const uint32_t a = vr / Tr, j = vr - a * Tr;
+    for (uint32_t bc0 = (warp >> 1) * 8u; bc0 < n_ct; bc0 += 32u) {
+        float acc[8][MT];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+#pragma unroll
+            for (int b = 0; b < MT; ++b) acc[q][b] = 0.0f;
+        for (uint32_t i4 = 0; i4 < Tc4; ++i4) {
+            const float4 d4 = *reinterpret_cast<const float4*>(drow + i4 * 4u);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (bc0 + q < n_ct) {
+#pragma unroll
+                    for (int b = 0; b < MT; ++b) {
+                        const float4 x4 = *reinterpret_cast<const float4*>(
+                            xs + (static_cast<size_t>(b) * n_ct + bc0 + q) * Tc + i4 * 4u);
+                        acc[q][b] = fmaf(d4.x, x4.x, acc[q][b]);
+                        acc[q][b] = fmaf(d4.y, x4.y, acc[q][b]);
+                        acc[q][b] = fmaf(d4.z, x4.z, acc[q][b]);
+                        acc[q][b] = fmaf(d4.w, x4.w, acc[q][b]);
+                    }
+                }
+            }
+        }
+        if (vr < VR) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (bc0 + q < n_ct) {
+                    float* dst = P + ((static_cast<size_t>(a) * n_ct + bc0 + q) * Tr + j) * MT;
+#pragma unroll
+                    for (int b = 0; b < MT; ++b) dst[b] = acc[q][b];
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 2-D tiles, phase 2: y[br*Tr + j][b] = sum_bc sum_codes sign*gamma * P[a][bc][j][b].
+// CTA = (32 rows j) x (8 column-tile groups); group partials are summed through
+// shared memory in a fixed order.
+// ---------------------------------------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(256)
+hsdr_tile_gather_kernel(const uint16_t* __restrict__ codes, uint32_t Tr, uint32_t n_ct,
+                        uint32_t n_jchunks, uint32_t S, uint32_t k,
+                        const float* __restrict__ scales, const float* __restrict__ P, YView yv) {
+    extern __shared__ __align__(16) unsigned char tsm[];
+    const uint32_t slots = S * k;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t br = blockIdx.x / n_jchunks, jc = blockIdx.x - br * n_jchunks;
+    const uint32_t n_codes = n_ct * slots;
+
+    const size_t code_byte0 = static_cast<size_t>(br) * n_codes * 2u;
+    const size_t aligned0 = code_byte0 & ~static_cast<size_t>(15);
+    const uint32_t skip = static_cast<uint32_t>(code_byte0 - aligned0) >> 1;
+    const uint32_t n16 = (skip * 2u + n_codes * 2u + 15u) >> 4;
+    const uint32_t cap16 = (n_codes * 2u + 15u + 16u) >> 4;
+    uint4* cs16 = reinterpret_cast<uint4*>(tsm);
+    float* sc = reinterpret_cast<float*>(tsm + static_cast<size_t>(cap16) * 16u);
+    float* red = sc + ((S + 3u) & ~3u);            // [8][32][MT]
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(codes) + aligned0);
+    for (uint32_t i = tid; i < n16; i += 256) cs16[i] = src[i];
+    for (uint32_t i = tid; i < S; i += 256) sc[i] = scales[i];
+    __syncthreads();
+    const uint16_t* cs = reinterpret_cast<const uint16_t*>(cs16) + skip;
+
+    const uint32_t jl = tid & 31u, grp = tid >> 5;
+    const uint32_t j = jc * 32u + jl;
+    float acc[MT];
+#pragma unroll
+    for (int b = 0; b < MT; ++b) acc[b] = 0.0f;
+    if (j < Tr) {
+        for (uint32_t bc = grp; bc < n_ct; bc += 8u) {
+            const uint16_t* tc = cs + bc * slots;
+            for (uint32_t l = 0; l < S; ++l) {
+                const float gamma = sc[l];
+                for (uint32_t kk = 0; kk < k; ++kk) {
+                    const uint32_t code = tc[l * k + kk];
+                    const float scale = (code & 0x8000u) ? -gamma : gamma;
+                    const float* p = P + ((static_cast<size_t>(code & 0x7FFFu) * n_ct + bc) * Tr + j) * MT;
+#pragma unroll
+                    for (int b = 0; b < MT; ++b) acc[b] = fmaf(scale, p[b], acc[b]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < MT; ++b) red[(grp * 32u + jl) * MT + b] = acc[b];
+    __syncthreads();
+    for (uint32_t t = tid; t < 32u * MT; t += 256) {
+        const uint32_t jj = t / MT, b = t - jj * MT;
+        float s = 0.0f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) s += red[(g * 32u + jj) * MT + b];
+        const uint32_t jr = jc * 32u + jj;
+        if (jr < Tr && b < yv.M) {
+            const uint32_t r = br * Tr + jr;
+            if (yv.bias) s += yv.bias[r];
+            yv.y[y_index(yv, r, b)] = s;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Raw edge strips (stored fp32 verbatim): rows < R_full add their top-right strip's
+// contribution to y; rows >= R_full are plain dense rows. One warp per row.
+// ---------------------------------------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(256)
+hsdr_edge_kernel(const float* __restrict__ edges, uint32_t R, uint32_t C, uint32_t Rf,
+                 uint32_t Cf, XView xv, YView yv) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t r = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (r >= R) return;
+    const bool top = r < Rf;
+    const uint32_t wc = top ? C - Cf : C;       // strip width
+    if (wc == 0) return;
+    const float* e = top ? edges + static_cast<size_t>(r) * (C - Cf)
+                         : edges + static_cast<size_t>(Rf) * (C - Cf) + static_cast<size_t>(r - Rf) * C;
+    const uint32_t cbase = top ? Cf : 0u;
+    float acc[MT];
+#pragma unroll
+    for (int b = 0; b < MT; ++b) acc[b] = 0.0f;
+    for (uint32_t c = lane; c < wc; c += 32u) {
+        const float w = e[c];
+#pragma unroll
+        for (int b = 0; b < MT; ++b)
+            if (b < xv.M) acc[b] = fmaf(w, load_x(xv, cbase + c, b), acc[b]);
+    }
+#pragma unroll
+    for (int b = 0; b < MT; ++b) {
+        float v = acc[b];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        if (lane == 0 && b < yv.M) {
+            const size_t yi = y_index(yv, r, b);
+            if (top) yv.y[yi] += v;
+            else yv.y[yi] = v + (yv.bias ? yv.bias[r] : 0.0f);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Dense rows: y[r][b] = sum_c W[r][c] * x[c][b]. One warp per row.
+// ---------------------------------------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(256)
+dense_rows_kernel(const float* __restrict__ W, uint32_t R, uint32_t C, XView xv, YView yv) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t r = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (r >= R) return;
+    const float* w = W + static_cast<size_t>(r) * C;
+    float acc[MT];
+#pragma unroll
+    for (int b = 0; b < MT; ++b) acc[b] = 0.0f;
+    for (uint32_t c = lane; c < C; c += 32u) {
+        const float wv = w[c];
+#pragma unroll
+        for (int b = 0; b < MT; ++b)
+            if (b < xv.M) acc[b] = fmaf(wv, load_x(xv, c, b), acc[b]);
+    }
+#pragma unroll
+    for (int b = 0; b < MT; ++b) {
+        float v = acc[b];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        if (lane == 0 && b < yv.M) yv.y[y_index(yv, r, b)] = v + (yv.bias ? yv.bias[r] : 0.0f);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host-side dispatch
+// ---------------------------------------------------------------------------
+inline void check_launch(csdr_context* ctx, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) throw Error(CSDR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+    ++ctx->launches;
+}
+
+template <typename Kern>
+void ensure_smem(Kern kern, size_t bytes) {
+    if (bytes > 48 * 1024)
+        CSDR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(bytes)));
+}
+
+int pick_mt(size_t m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16; }
+
+template <int MT, int A, int U>
+void launch_dx_t(csdr_context* ctx, const csdr_segment* seg, const XView& xv, float* dx,
+                 uint32_t nsplit, uint32_t slab) {
+    const Geometry& g = seg->g;
+    auto kern = hsdr_dx_kernel<MT, A, U>;
+    const size_t smem = (static_cast<size_t>(MT) * slab + 8u * A * MT) * sizeof(float);
+    ensure_smem(kern, smem);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(nsplit, (g.n_atoms + 8u * A - 1u) / (8u * A), 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nsplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(seg->atoms->ptr), g.n_atoms,
+                                 g.cols, slab, xv, dx, static_cast<int>(nsplit)));
+    check_launch(ctx, "hsdr_dx_kernel");
+}
+
+template <int MT>
+void launch_gather_t(csdr_context* ctx, const csdr_segment* seg, const float* dx, const YView& yv) {
+    const Geometry& g = seg->g;
+    constexpr uint32_t RP = kGatherThreads / MT;
+    uint32_t rows_per_cta = (g.rows + 4u * ctx->sm_count - 1u) / (4u * ctx->sm_count);
+    rows_per_cta = std::max(RP, (rows_per_cta + RP - 1u) / RP * RP);
+    const uint32_t slots = g.slots();
+    const size_t cap16 = (static_cast<size_t>(rows_per_cta) * slots * 2u + 31u) >> 4;
+    const size_t base = cap16 * 16u + ((g.n_stages + 3u) & ~3u) * sizeof(float);
+    const size_t dx_bytes = static_cast<size_t>(g.n_atoms) * MT * sizeof(float);
+    const int dx_in_smem = base + dx_bytes <= 160u * 1024u;
+    const size_t smem = base + (dx_in_smem ? dx_bytes : 0u);
+    auto kern = hsdr_gather_kernel<MT>;
+    ensure_smem(kern, smem);
+    const uint32_t grid = (g.rows + rows_per_cta - 1u) / rows_per_cta;
+    kern<<<grid, kGatherThreads, smem, ctx->stream>>>(
+        seg->codes_ptr(), g.rows, g.n_stages, g.k, static_cast<const float*>(seg->scales->ptr), dx,
+        g.n_atoms, rows_per_cta, dx_in_smem, yv);
+    check_launch(ctx, "hsdr_gather_kernel");
+}
+
+template <int MT>
+void matmul_rowtiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XView& xv,
+                           const YView& yv) {
+    const Geometry& g = seg->g;
+    // Column split: slabs of about 1024 floats, at most 8 CTAs per cluster (the portable
+    // limit), each slab a multiple of 4 floats.
+    uint32_t nsplit = std::min<uint32_t>(8u, std::max<uint32_t>(1u, (g.cols + 1023u) / 1024u));
+    uint32_t slab = ((g.cols + nsplit - 1u) / nsplit + 3u) & ~3u;
+    nsplit = (g.cols + slab - 1u) / slab;
+    float* dx = static_cast<float*>(
+        ctx->scratch_get(0, static_cast<size_t>(g.n_atoms) * 16u * sizeof(float)));
+    if constexpr (MT == 1) launch_dx_t<1, 1, 8>(ctx, seg, xv, dx, nsplit, slab);
+    else if constexpr (MT == 2) launch_dx_t<2, 1, 8>(ctx, seg, xv, dx, nsplit, slab);
+    else if constexpr (MT == 4) launch_dx_t<4, 2, 4>(ctx, seg, xv, dx, nsplit, slab);
+    else if constexpr (MT == 8) launch_dx_t<8, 4, 2>(ctx, seg, xv, dx, nsplit, slab);
+    else launch_dx_t<16, 4, 2>(ctx, seg, xv, dx, nsplit, slab);
+    launch_gather_t<MT>(ctx, seg, dx, yv);
+}
+
+template <int MT>
+void matmul_tiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XView& xv,
+                        const YView& yv) {
+    const Geometry& g = seg->g;
+    const uint32_t VR = g.n_atoms * g.tile_rows;
+    const size_t p_bytes = static_cast<size_t>(VR) * g.n_col_tiles * MT * sizeof(float);
+    float* P = static_cast<float*>(ctx->scratch_get(1, p_bytes));
+    {
+        auto kern = hsdr_tile_project_kernel<MT>;
+        const size_t smem = (static_cast<size_t>(kProjRows) * (g.tile_cols + 4u) +
+                             static_cast<size_t>(MT) * g.cols_full) * sizeof(float);
+        ensure_smem(kern, smem);
+        kern<<<(VR + kProjRows - 1u) / kProjRows, 256, smem, ctx->stream>>>(
+            static_cast<const float*>(seg->atoms->ptr), VR, g.tile_rows, g.tile_cols, g.n_col_tiles,
+            xv, P);
+        check_launch(ctx, "hsdr_tile_project_kernel");
+    }
+    {
+        auto kern = hsdr_tile_gather_kernel<MT>;
+        const uint32_t n_jchunks = (g.tile_rows + 31u) / 32u;
+        const uint32_t n_row_tiles = g.rows_full / g.tile_rows;
+        const size_t cap16 = (static_cast<size_t>(g.n_col_tiles) * g.slots() * 2u + 31u) >> 4;
+        const size_t smem = cap16 * 16u + ((g.n_stages + 3u) & ~3u) * sizeof(float) +
+                            8u * 32u * MT * sizeof(float);
+        ensure_smem(kern, smem);
+        kern<<<n_row_tiles * n_jchunks, 256, smem, ctx->stream>>>(
+            seg->codes_ptr(), g.tile_rows, g.n_col_tiles, n_jchunks, g.n_stages, g.k,
+            static_cast<const float*>(seg->scales->ptr), P, yv);
+        check_launch(ctx, "hsdr_tile_gather_kernel");
+    }
+    if (seg->edges) {
+        hsdr_edge_kernel<MT><<<(g.rows + 7u) / 8u, 256, 0, ctx->stream>>>(
+            static_cast<const float*>(seg->edges->ptr), g.rows, g.cols, g.rows_full, g.cols_full, xv, yv);
+        check_launch(ctx, "hsdr_edge_kernel");
+    }
+}
+
+// Largest token tile (a power of two <= 16) whose shared-memory need fits.
+int fit_mt(int want, size_t fixed_bytes, size_t per_token_bytes, size_t budget) {
+    int mt = want;
+    while (mt > 1 && fixed_bytes + per_token_bytes * mt > budget) mt >>= 1;
+    if (fixed_bytes + per_token_bytes * mt > budget) return 0;
+    return mt;
+}
+
+template <typename F>
+void dispatch_mt(int mt, F&& f) {
+    switch (mt) {
+        case 1: f(std::integral_constant<int, 1>{}); break;
+        case 2: f(std::integral_constant<int, 2>{}); break;
+        case 4: f(std::integral_constant<int, 4>{}); break;
+        case 8: f(std::integral_constant<int, 8>{}); break;
+        default: f(std::integral_constant<int, 16>{}); break;
+    }
+}
+
+}  // namespace
+
+void launch_unpack(csdr_context* ctx, const uint16_t* codes, size_t n, int32_t* idx, int8_t* sign) {
+    if (n == 0) return;
+    const size_t blocks = std::min<size_t>((n / 8 + 255) / 256 + 1, static_cast<size_t>(ctx->sm_count) * 8);
+    hsdr_unpack_kernel<<<static_cast<unsigned>(blocks), 256, 0, ctx->stream>>>(codes, n, idx, sign);
+    check_launch(ctx, "hsdr_unpack_kernel");
+}
+
+void launch_dense_matmul(csdr_context* ctx, const float* W, uint32_t R, uint32_t C,
+                         const MatmulArgs& a) {
+    for (size_t b0 = 0; b0 < a.batch; b0 += 16) {
+        const uint32_t m = static_cast<uint32_t>(std::min<size_t>(16, a.batch - b0));
+        XView xv{a.x, a.x_dtype, a.x_layout, C, static_cast<uint32_t>(a.batch), static_cast<uint32_t>(b0), m};
+        YView yv{a.y, a.y_layout, R, static_cast<uint32_t>(a.batch), static_cast<uint32_t>(b0), m, a.bias};
+        dispatch_mt(pick_mt(m), [&](auto mt) {
+            dense_rows_kernel<decltype(mt)::value><<<(R + 7u) / 8u, 256, 0, ctx->stream>>>(W, R, C, xv, yv);
+            check_launch(ctx, "dense_rows_kernel");
+        });
+    }
+}
+
+void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a) {
+    const Geometry& g = seg->g;
+    if (a.batch == 0) return;
+    if (a.batch > 0xFFFFFFFFull) throw Error(CSDR_ERR_LIMIT, "batch too large");
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 200u * 1024u);
+    const bool fast_rows = g.row_tiles() && (g.cols % 4u == 0);
+    const bool fast_tiles = !fast_rows && (g.tile_cols % 4u == 0);
+    int mt_cap = 0;
+    if (fast_rows) {
+        uint32_t nsplit = std::min<uint32_t>(8u, std::max<uint32_t>(1u, (g.cols + 1023u) / 1024u));
+        const uint32_t slab = ((g.cols + nsplit - 1u) / nsplit + 3u) & ~3u;
+        mt_cap = fit_mt(16, 0, (static_cast<size_t>(slab) + 32u) * sizeof(float), budget);
+    } else if (fast_tiles) {
+        mt_cap = fit_mt(4, static_cast<size_t>(kProjRows) * (g.tile_cols + 4u) * sizeof(float),
+                        static_cast<size_t>(g.cols_full) * sizeof(float), budget);
+        const size_t gather_fixed = ((static_cast<size_t>(g.n_col_tiles) * g.slots() * 2u + 31u) & ~15u) +
+                                    ((g.n_stages + 3u) & ~3u) * sizeof(float);
+        if (gather_fixed + 8u * 32u * 16u * sizeof(float) > budget) mt_cap = 0;
+    }
+    if (mt_cap == 0) {
+        // Odd geometry: materialise W once into scratch, then a dense product — what the
+        // reference does for every 2-D encoding (decompress + dense).
+        float* W = static_cast<float*>(
+            ctx->scratch_get(2, static_cast<size_t>(g.rows) * g.cols * sizeof(float)));
+        launch_decode_rows(ctx, seg, nullptr, g.rows, W);
+        launch_dense_matmul(ctx, W, g.rows, g.cols, a);
+        return;
+    }
+    for (size_t b0 = 0; b0 < a.batch; b0 += mt_cap) {
+        const uint32_t m = static_cast<uint32_t>(std::min<size_t>(mt_cap, a.batch - b0));
+        XView xv{a.x, a.x_dtype, a.x_layout, g.cols, static_cast<uint32_t>(a.batch),
+                 static_cast<uint32_t>(b0), m};
+        YView yv{a.y, a.y_layout, g.rows, static_cast<uint32_t>(a.batch), static_cast<uint32_t>(b0), m, a.bias};
+        dispatch_mt(pick_mt(m), [&](auto mt) {
+            constexpr int MT = decltype(mt)::value;
+            if (fast_rows) matmul_rowtiles_chunk<MT>(ctx, seg, xv, yv);
+            else if constexpr (MT <= 4) matmul_tiles_chunk<MT>(ctx, seg, xv, yv);
+        });
+    }
+}
+
+}  // namespace csdr

@@ -1,0 +1,278 @@
+/*
+ * cortexsdr_b200 — thin extern "C" CUDA layer for the HSDR on-demand inference
+ * matmul on NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only; every function returns an int status (0 = ok,
+ * negative = error, see CSDR_ERR_*); nothing throws across this boundary; there is
+ * no CPU fallback — without a CUDA device every compute entry point fails with
+ * CSDR_ERR_CUDA. A thread-local message for the last failure is available from
+ * csdr_last_error().
+ *
+ * Each entry point names the reference interface it stands in for
+ * (file:line inside the reference tree, under src/ai_compression/).
+ *
+ * Conventions
+ *   - "payload" = the bytes of one compressed segment exactly as they sit in a .sdr
+ *     archive ("HSDR" v2: header, stage scales, dictionary, packed codes, edge
+ *     strips) or in a .hsda container ("HSDC" v1: header, packed codes).
+ *   - Reference activation layout ("feature-major"): x is (C x batch) row-major,
+ *     y is (R x batch) row-major — strategies/HierarchicalSDRStrategy.hpp:164-181.
+ *   - "token-major": x is (batch x C), y is (batch x R) — the layout of
+ *     SDRInferenceEngine::applyLinearLayer (SparseInferenceEngine.cpp:1481).
+ *   - One context = one device + one stream; calls on a context are synchronous on
+ *     return unless the name ends in _async. One thread per context.
+ */
+#ifndef CORTEXSDR_B200_H
+#define CORTEXSDR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CSDR_API __attribute__((visibility("default")))
+#else
+#define CSDR_API
+#endif
+
+enum {
+    CSDR_OK = 0,
+    CSDR_ERR_INVALID_ARG = -1,
+    CSDR_ERR_FORMAT = -2,       /* bad magic / version / truncated stream */
+    CSDR_ERR_GEOMETRY = -3,     /* tile geometry not accepted by this entry point */
+    CSDR_ERR_NOT_FOUND = -4,    /* segment name not in the archive */
+    CSDR_ERR_STRATEGY = -5,     /* segment is not HSDR-encoded */
+    CSDR_ERR_CUDA = -6,         /* CUDA runtime error, or no device */
+    CSDR_ERR_TIMEOUT = -7,      /* a bounded device-side wait ran out */
+    CSDR_ERR_IO = -8,
+    CSDR_ERR_UNSUPPORTED = -9,
+    CSDR_ERR_BUFFER = -10,      /* caller's output buffer too small */
+    CSDR_ERR_CODE_RANGE = -11,  /* a packed code names an atom index >= n_atoms */
+    CSDR_ERR_LIMIT = -12        /* size beyond a documented fixed maximum */
+};
+
+enum { CSDR_DTYPE_F32 = 0, CSDR_DTYPE_BF16 = 1 };
+enum { CSDR_LAYOUT_FEATURE_MAJOR = 0, CSDR_LAYOUT_TOKEN_MAJOR = 1 };
+enum { CSDR_KIND_HSDR = 0, CSDR_KIND_HSDC = 1 };
+
+typedef struct csdr_context csdr_context;
+typedef struct csdr_segment csdr_segment;       /* device image of one compressed weight */
+typedef struct csdr_dictionary csdr_dictionary; /* device image of a shared dictionary */
+typedef struct csdr_archive csdr_archive;       /* an opened .sdr */
+typedef struct csdr_hsda csdr_hsda;             /* an opened .hsda */
+typedef struct csdr_decoder csdr_decoder;       /* device-resident decoder-layer driver */
+
+/* Fields of the payload header (HSDRHeader, strategies/HierarchicalSDRStrategy.cpp:49-66;
+ * HSDRCodesHeader, :675-692) plus the byte offsets of the streams behind it. */
+typedef struct {
+    int32_t kind;               /* CSDR_KIND_* */
+    uint32_t rows, cols, n_tiles;
+    uint16_t tile_rows, tile_cols, n_atoms;
+    uint8_t n_stages, k_per_stage;
+    float stage_decay;
+    uint32_t edge_bytes;
+    uint64_t off_scales, off_dict, off_codes, off_edges;
+    uint64_t payload_bytes;     /* header + all streams */
+} csdr_payload_info;
+
+CSDR_API const char* csdr_last_error(void);
+CSDR_API const char* csdr_version(void);
+
+/* ---- context ---- */
+/* device < 0 selects the current device. stream may be NULL (the context makes its
+ * own non-blocking stream) or a cudaStream_t the caller owns. */
+CSDR_API int csdr_context_create(int device, void* stream, csdr_context** out);
+CSDR_API int csdr_context_destroy(csdr_context* ctx);
+CSDR_API int csdr_context_synchronize(csdr_context* ctx);
+CSDR_API void* csdr_context_stream(csdr_context* ctx);
+/* Number of kernels this library has launched on the context since creation. */
+CSDR_API uint64_t csdr_context_launch_count(const csdr_context* ctx);
+
+/* ---- payload framing (host only) ----
+ * Replaces the header parse + checks at the top of matmulRowMajor / decompress
+ * (strategies/HierarchicalSDRStrategy.cpp:1262-1299, :1345-1389) and parseCodesStream
+ * (:1766-1801). Validates magic, version, stream lengths, and that every packed code
+ * names an atom < n_atoms (the reference does not check the last one; a device kernel
+ * must never be handed an out-of-range index). */
+CSDR_API int csdr_payload_inspect(const void* payload, size_t nbytes, csdr_payload_info* info);
+
+/* ---- device images ---- */
+/* From an "HSDR" payload (dictionary embedded). */
+CSDR_API int csdr_segment_create(csdr_context* ctx, const void* payload, size_t nbytes,
+                                 csdr_segment** out);
+/* SharedDictionary (strategies/HierarchicalSDRStrategy.hpp:194-198): atoms is
+ * (n_atoms x tile_rows*tile_cols) fp32 row-major, scales has n_stages entries. */
+CSDR_API int csdr_dictionary_create(csdr_context* ctx, uint16_t tile_rows, uint16_t tile_cols,
+                                    uint16_t n_atoms, uint8_t n_stages, uint8_t k_per_stage,
+                                    const float* atoms, const float* scales,
+                                    csdr_dictionary** out);
+/* From an "HSDC" codes-only payload + its dictionary; geometry is checked as in
+ * parseCodesStream (:1781-1787). The dictionary must outlive the segment. */
+CSDR_API int csdr_segment_create_shared(csdr_context* ctx, const void* codes, size_t nbytes,
+                                        const csdr_dictionary* dict, csdr_segment** out);
+CSDR_API int csdr_segment_destroy(csdr_segment* seg);
+CSDR_API int csdr_dictionary_destroy(csdr_dictionary* dict);
+CSDR_API int csdr_segment_info(const csdr_segment* seg, csdr_payload_info* info);
+/* Row-shard for tensor parallelism: keep only output rows [row_begin, row_end) of the
+ * code stream (1-D row tiles: any range; 2-D tiles: multiples of tile_rows). The
+ * dictionary is shared with `seg`, which must outlive the shard. */
+CSDR_API int csdr_segment_shard_rows(csdr_context* ctx, const csdr_segment* seg,
+                                     uint32_t row_begin, uint32_t row_end, csdr_segment** out);
+
+/* ---- sparse-code unpack ----
+ * unpackIndexSign (strategies/HierarchicalSDRStrategy.cpp:81-84; loops :1394-1399,
+ * :1795-1799): u16 -> (index = v & 0x7FFF, sign = v >> 15 ? -1 : +1), on the device,
+ * results copied to host arrays of n_tiles*n_stages*k entries. */
+CSDR_API int csdr_unpack_codes(csdr_context* ctx, const csdr_segment* seg, int32_t* idx_out,
+                               int8_t* sign_out, size_t capacity);
+
+/* ---- fused matmul ----
+ * HierarchicalSDRStrategy::matmulRowMajor (strategies/HierarchicalSDRStrategy.cpp:1257)
+ * and ::matmulWithExternalDictionary (:1830): host buffers, reference layout
+ * (x: C x batch, y: R x batch, fp32). As the reference, refuses 2-D tiles
+ * (CSDR_ERR_GEOMETRY) unless allow_2d != 0, in which case the result equals the
+ * reference's decompress() + dense product (SparseInferenceEngine.cpp:1301-1310). */
+CSDR_API int csdr_matmul(csdr_context* ctx, const csdr_segment* seg, const float* x,
+                         size_t batch, float* y, int allow_2d);
+/* Same product with device-resident activations. x_dtype/x_layout/y_layout as the
+ * enums above; y is fp32; bias (R floats, device) may be NULL
+ * (applyLinearLayer adds it, SparseInferenceEngine.cpp:1509-1511). Asynchronous on the
+ * context's stream. */
+CSDR_API int csdr_matmul_device_async(csdr_context* ctx, const csdr_segment* seg,
+                                      const void* x_dev, int x_dtype, int x_layout,
+                                      size_t batch, float* y_dev, int y_layout,
+                                      const float* bias_dev);
+
+/* ---- materialise the weight ----
+ * HierarchicalSDRStrategy::decompress (:1340) / ::decompressWithExternalDictionary
+ * (:1804): fp32 (rows x cols) row-major, edge strips spliced back. */
+CSDR_API int csdr_decompress(csdr_context* ctx, const csdr_segment* seg, float* out_host,
+                             size_t capacity_floats);
+CSDR_API int csdr_decompress_device_async(csdr_context* ctx, const csdr_segment* seg,
+                                          float* out_dev);
+
+/* ---- source-dtype dequantisation ----
+ * HierarchicalSDRStrategy::dequantizeToFP32 (:1017; body :713-989), HSDR's own
+ * element order. fmt: "f32","f16","bf16","i8","q4_0","q8_0","q4_k","q5_k","q6_k".
+ * *n_out receives the element count. Bit-exact against the reference. */
+CSDR_API int csdr_dequantize(csdr_context* ctx, const char* fmt, const void* data,
+                             size_t nbytes, float scale, float zero_point, float* out_host,
+                             size_t capacity_floats, size_t* n_out);
+
+/* ---- .sdr archive: SDRModelLoader / SDRInferenceEngine routing ---- */
+typedef struct {
+    const char* name;           /* owned by the archive */
+    const char* data_format;
+    const char* layer_type;
+    uint8_t original_type;      /* SegmentType, core/ModelSegment.hpp:36-55 */
+    uint8_t strategy_id;        /* 5 = HSDR, 0 = stored raw */
+    uint64_t original_size, compressed_size, data_offset;
+    uint32_t layer_index;
+    uint32_t n_dims;
+    uint32_t dims[8];
+} csdr_segment_header;
+
+/* SDRModelLoader(path) -> loadFromArchive -> AIDecompressor::readArchiveIndex
+ * (SparseInferenceEngine.cpp:725-751, :994; core/AIDecompressor.cpp:78-262). */
+CSDR_API int csdr_archive_open(csdr_context* ctx, const char* path, csdr_archive** out);
+CSDR_API int csdr_archive_close(csdr_archive* ar);
+CSDR_API int csdr_archive_num_segments(const csdr_archive* ar, size_t* n);
+CSDR_API int csdr_archive_header_at(const csdr_archive* ar, size_t i, csdr_segment_header* h);
+/* findSegmentHeader (SparseInferenceEngine.cpp:1066): CSDR_ERR_NOT_FOUND if absent. */
+CSDR_API int csdr_archive_find(const csdr_archive* ar, const char* name, csdr_segment_header* h);
+/* loadCompressedBytesByName (:1055): raw payload bytes. *n gets the needed size. */
+CSDR_API int csdr_archive_read_payload(const csdr_archive* ar, const char* name, void* buf,
+                                       size_t capacity, size_t* n);
+/* loadSegmentByName (:1044): decoded segment bytes (HSDR -> fp32 matrix via the device
+ * decompress kernel; strategy 0 -> stored bytes). Other strategies: CSDR_ERR_UNSUPPORTED. */
+CSDR_API int csdr_archive_load_segment(csdr_archive* ar, const char* name, void* buf,
+                                       size_t capacity, size_t* n);
+/* Device image of a named HSDR segment, uploaded on first use and cached — the step the
+ * reference repeats per call (file open + payload read + two copies). Owned by the archive. */
+CSDR_API int csdr_archive_segment(csdr_archive* ar, const char* name, const csdr_segment** seg);
+/* SDRModelLoader::matmulHSDR (:1074): errors mirror the reference's
+ * ("segment not found" -> CSDR_ERR_NOT_FOUND, "is not HSDR-encoded" -> CSDR_ERR_STRATEGY,
+ * 2-D tiles -> CSDR_ERR_GEOMETRY). y_capacity in floats; *n_out = R*batch. */
+CSDR_API int csdr_archive_matmul_hsdr(csdr_archive* ar, const char* name, const float* x,
+                                      size_t batch, float* y, size_t y_capacity, size_t* n_out);
+/* SDRInferenceEngine::matmulForLayer (:1271): HSDR route for strategy 5 (any tile
+ * geometry; 2-D tiles give the reference's decompress+dense result), dense product on
+ * the device for raw fp32 2-D segments, CSDR_ERR_UNSUPPORTED otherwise. */
+CSDR_API int csdr_archive_matmul_for_layer(csdr_archive* ar, const char* name, const float* x,
+                                           size_t batch, float* y, size_t y_capacity,
+                                           size_t* n_out);
+/* SDRInferenceEngine::applyLinearLayer, HSDR branches (:1487-1521, :1694-1728):
+ * looks up `layer` then `layer + ".weight"`; token-major input (batch x C) and output
+ * (batch x R); optional bias (R floats, host). */
+CSDR_API int csdr_archive_apply_linear(csdr_archive* ar, const char* layer, const float* input,
+                                       size_t input_size, const float* bias, float* output,
+                                       size_t capacity, size_t* n_out);
+
+/* ---- .hsda container: HSDAReader (strategies/HierarchicalSDRStrategy.cpp:2506-2550;
+ * format :1905-1933, reader :2004-2064) ---- */
+CSDR_API int csdr_hsda_open(csdr_context* ctx, const char* path, csdr_hsda** out);
+CSDR_API int csdr_hsda_close(csdr_hsda* h);
+CSDR_API int csdr_hsda_counts(const csdr_hsda* h, size_t* n_dicts, size_t* n_segments);
+CSDR_API int csdr_hsda_has_segment(const csdr_hsda* h, const char* name);
+CSDR_API int csdr_hsda_segment(csdr_hsda* h, const char* name, const csdr_segment** seg);
+/* HSDAReader::matmul (:2536): 1-D row tiles only unless allow_2d. */
+CSDR_API int csdr_hsda_matmul(csdr_hsda* h, const char* name, const float* x, size_t batch,
+                              float* y, size_t y_capacity, size_t* n_out, int allow_2d);
+/* HSDAReader::decompress (:2523). */
+CSDR_API int csdr_hsda_decompress(csdr_hsda* h, const char* name, float* out,
+                                  size_t capacity_floats, size_t* n_out);
+
+/* ---- decoder-layer driver ----
+ * Device-resident restatement of run_transformer_decode (api/cortex_sdk.cpp:1543-1696):
+ * RMSNorm (:1208), RoPE on adjacent pairs (:1363-1423), grouped-query causal attention
+ * (:1453-1478; kernels/attention_kernels.cpp:26-113), SwiGLU (:1245), residual adds,
+ * final norm, logits (SparseInferenceEngine.cpp:2310-2320) — with a KV cache, which the
+ * reference lacks (it recomputes the whole sequence per token). Block tensors are found
+ * by the reference's GGUF-style names (cortex_sdk.cpp:456-524): token_embd.weight,
+ * blk.<n>.{attn_norm,attn_q,attn_k,attn_v,attn_output,ffn_norm,ffn_gate,ffn_up,ffn_down}.weight,
+ * output_norm.weight, output.weight. */
+typedef struct {
+    uint32_t n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab;
+    uint32_t max_seq;       /* KV-cache capacity in positions, per sequence */
+    uint32_t max_batch;     /* sequences decoded together */
+    float rms_eps;          /* reference default 1e-5 (cortex_sdk.cpp:1212) */
+    float rope_theta;       /* reference default 1e6 (cortex_sdk.cpp:1358) */
+    /* tensor parallelism: this rank's index and the number of ranks sharing the model.
+     * tp_size == 1 means no sharding. comm is an ncclComm_t (void*) or NULL. */
+    uint32_t tp_rank, tp_size;
+    void* nccl_comm;
+} csdr_decoder_config;
+
+CSDR_API int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg,
+                                 csdr_decoder** out);
+CSDR_API int csdr_decoder_destroy(csdr_decoder* d);
+CSDR_API int csdr_decoder_reset(csdr_decoder* d);
+/* Run n_tokens new positions of sequence `seq` (prefill when n_tokens > 1). If
+ * logits_out != NULL it receives the vocab logits of the LAST position (host, fp32).
+ * If hidden_out != NULL it receives the final-normed hidden state of every new
+ * position (n_tokens x hidden, host). */
+CSDR_API int csdr_decoder_forward(csdr_decoder* d, uint32_t seq, const int32_t* tokens,
+                                  size_t n_tokens, float* logits_out, float* hidden_out);
+/* One decode step for `batch` sequences at once (sequence b gets tokens[b]); writes the
+ * greedy next token of each to next_out (host). logits_out may be NULL, else
+ * (batch x vocab) host fp32. */
+CSDR_API int csdr_decoder_step(csdr_decoder* d, const int32_t* tokens, size_t batch,
+                               int32_t* next_out, float* logits_out);
+/* Same step, nothing copied to the host: tokens_dev in, next_dev out (device int32). */
+CSDR_API int csdr_decoder_step_device_async(csdr_decoder* d, const int32_t* tokens_dev,
+                                            size_t batch, int32_t* next_dev);
+
+/* ---- NCCL plumbing for tensor parallelism (rank 0 makes the id, the host program
+ * broadcasts it, every rank initialises) ---- */
+CSDR_API int csdr_nccl_unique_id(void* id128);  /* 128-byte buffer */
+CSDR_API int csdr_nccl_comm_create(csdr_context* ctx, const void* id128, int rank, int world,
+                                   void** comm_out);
+CSDR_API int csdr_nccl_comm_destroy(void* comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CORTEXSDR_B200_H */

@@ -1,0 +1,380 @@
+/* TEST INFRASTRUCTURE ONLY — see hsdr_oracle.h. Plain-C restatement of the
+ * reference's HSDR decode side. Each function names the reference lines it follows
+ * (paths inside the reference tree). Loop order and fp32 accumulation order follow
+ * the reference so that differences stay at rounding level. */
+#include "hsdr_oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define HSDR_HDR 36u
+#define HSDC_HDR 32u
+
+static uint32_t rd32(const uint8_t* p) { uint32_t v; memcpy(&v, p, 4); return v; }
+static uint16_t rd16(const uint8_t* p) { uint16_t v; memcpy(&v, p, 2); return v; }
+static float rdf(const uint8_t* p) { float v; memcpy(&v, p, 4); return v; }
+
+/* HSDRHeader / HSDRCodesHeader: strategies/HierarchicalSDRStrategy.cpp:49-66, :675-692;
+ * stream order after the header: scales, dictionary, codes, edges (:1222-1235). */
+int orc_hsdr_parse(const uint8_t* p, size_t n, orc_hsdr_view* v) {
+    memset(v, 0, sizeof(*v));
+    if (n < HSDC_HDR) return -1;
+    if (memcmp(p, "HSDR", 4) == 0) v->kind = 0;
+    else if (memcmp(p, "HSDC", 4) == 0) v->kind = 1;
+    else return -2;
+    const uint32_t ver = rd32(p + 4);
+    if (v->kind == 0 && (n < HSDR_HDR || ver != 2)) return -3;
+    if (v->kind == 1 && ver != 1) return -3;
+    v->rows = rd32(p + 8);
+    v->cols = rd32(p + 12);
+    v->n_tiles = rd32(p + 16);
+    v->tile_rows = rd16(p + 20);
+    v->tile_cols = rd16(p + 22);
+    v->n_atoms = rd16(p + 24);
+    v->n_stages = p[26];
+    v->k = p[27];
+    v->decay = rdf(p + 28);
+    const size_t tile_dim = (size_t)v->tile_rows * v->tile_cols;
+    const size_t n_codes = (size_t)v->n_tiles * v->n_stages * v->k;
+    if (v->kind == 0) {
+        v->edge_bytes = rd32(p + 32);
+        v->off_scales = HSDR_HDR;
+        v->off_dict = v->off_scales + 4u * v->n_stages;
+        v->off_codes = v->off_dict + 4u * (size_t)v->n_atoms * tile_dim;
+        v->off_edges = v->off_codes + 2u * n_codes;
+        if (v->off_edges + v->edge_bytes > n) return -4;
+    } else {
+        v->off_codes = HSDC_HDR;
+        if (v->off_codes + 2u * n_codes > n) return -4;
+    }
+    return 0;
+}
+
+/* unpackIndexSign: :81-84 */
+void orc_unpack_codes(const uint16_t* packed, size_t n, int32_t* idx, int8_t* sign) {
+    for (size_t i = 0; i < n; ++i) {
+        idx[i] = (int32_t)(packed[i] & 0x7FFFu);
+        sign[i] = (packed[i] & 0x8000u) ? -1 : 1;
+    }
+}
+
+/* Shared body of matmulRowMajor (:1301-1337) and matmulWithExternalDictionary
+ * (:1853-1882): Dx = D*x, then per-row signed gather scaled per stage. */
+static int fused_matmul(const float* D, const float* scales, const uint8_t* codes_bytes,
+                        uint32_t R, uint32_t C, uint16_t K, uint8_t S, uint8_t k,
+                        const float* x, size_t batch, float* y) {
+    float* Dx = (float*)calloc((size_t)K * batch, sizeof(float));
+    if (!Dx) return -10;
+    for (uint32_t a = 0; a < K; ++a) {
+        const float* atom = D + (size_t)a * C;
+        float* out_row = Dx + (size_t)a * batch;
+        for (uint32_t c = 0; c < C; ++c) {
+            const float av = atom[c];
+            const float* xrow = x + (size_t)c * batch;
+            for (size_t b = 0; b < batch; ++b) out_row[b] += av * xrow[b];
+        }
+    }
+    const uint32_t slots = (uint32_t)S * k;
+    memset(y, 0, (size_t)R * batch * sizeof(float));
+    for (uint32_t r = 0; r < R; ++r) {
+        float* y_row = y + (size_t)r * batch;
+        for (uint8_t l = 0; l < S; ++l) {
+            const float gamma = scales[l];
+            for (uint8_t kk = 0; kk < k; ++kk) {
+                const uint16_t pk = rd16(codes_bytes + 2u * ((size_t)r * slots + (size_t)l * k + kk));
+                const uint16_t a = pk & 0x7FFFu;
+                const float scale = gamma * ((pk & 0x8000u) ? -1.0f : 1.0f);
+                if (a >= K) { free(Dx); return -11; }
+                const float* dx_row = Dx + (size_t)a * batch;
+                for (size_t b = 0; b < batch; ++b) y_row[b] += scale * dx_row[b];
+            }
+        }
+    }
+    free(Dx);
+    return 0;
+}
+
+/* matmulRowMajor: :1257-1338 (geometry checks :1273-1289). */
+int orc_hsdr_matmul(const uint8_t* p, size_t n, const float* x, size_t batch, float* y) {
+    orc_hsdr_view v;
+    int rc = orc_hsdr_parse(p, n, &v);
+    if (rc) return rc;
+    if (v.kind != 0) return -2;
+    if (v.tile_rows != 1) return -20;           /* "fused matmul requires tile_rows == 1" */
+    if (v.tile_cols != v.cols) return -21;      /* "must have tile_cols == original_cols" */
+    if (v.n_tiles != v.rows) return -22;        /* "tile count must equal row count" */
+    const size_t dict_bytes = 4u * (size_t)v.n_atoms * v.cols;
+    float* D = (float*)malloc(dict_bytes);
+    float scales[256];
+    if (!D) return -10;
+    memcpy(D, p + v.off_dict, dict_bytes);
+    memcpy(scales, p + v.off_scales, 4u * v.n_stages);
+    rc = fused_matmul(D, scales, p + v.off_codes, v.rows, v.cols, v.n_atoms, v.n_stages, v.k,
+                      x, batch, y);
+    free(D);
+    return rc;
+}
+
+static int check_dict_geometry(const orc_hsdr_view* v, uint16_t tr, uint16_t tc, uint16_t K,
+                               uint8_t S, uint8_t k) {
+    /* parseCodesStream: :1781-1787 */
+    return (v->tile_rows == tr && v->tile_cols == tc && v->n_atoms == K && v->n_stages == S &&
+            v->k == k) ? 0 : -30;
+}
+
+/* matmulWithExternalDictionary: :1830-1883 */
+int orc_hsdc_matmul(const uint8_t* p, size_t n, const float* atoms, const float* scales,
+                    uint16_t tr, uint16_t tc, uint16_t K, uint8_t S, uint8_t k,
+                    const float* x, size_t batch, float* y) {
+    orc_hsdr_view v;
+    int rc = orc_hsdr_parse(p, n, &v);
+    if (rc) return rc;
+    if (v.kind != 1) return -2;
+    if ((rc = check_dict_geometry(&v, tr, tc, K, S, k))) return rc;
+    if (v.tile_rows != 1) return -20;
+    if (v.tile_cols != v.cols) return -21;
+    if (v.n_tiles != v.rows) return -22;
+    return fused_matmul(atoms, scales, p + v.off_codes, v.rows, v.cols, K, S, k, x, batch, y);
+}
+
+/* decodeAllTiles (:612-634) followed by reassembleTiles (:119-135) into a matrix with
+ * leading dimension ld (= C for the aligned fast path and for the edge-splice path,
+ * whose intermediate aligned block is copied row by row into the same place, :1416-1424). */
+static int decode_tiles_into(const float* D, const float* scales, const uint8_t* codes_bytes,
+                             uint32_t n_tiles, uint16_t tr, uint16_t tc, uint16_t K, uint8_t S,
+                             uint8_t k, uint32_t n_col_tiles, float* out, size_t ld) {
+    const size_t T = (size_t)tr * tc;
+    const uint32_t slots = (uint32_t)S * k;
+    float* t = (float*)malloc(T * sizeof(float));
+    if (!t) return -10;
+    for (uint32_t i = 0; i < n_tiles; ++i) {
+        for (size_t c = 0; c < T; ++c) t[c] = 0.0f;
+        for (uint8_t l = 0; l < S; ++l) {
+            const float gamma = scales[l];
+            for (uint8_t kk = 0; kk < k; ++kk) {
+                const uint16_t pk = rd16(codes_bytes + 2u * ((size_t)i * slots + (size_t)l * k + kk));
+                const uint16_t a = pk & 0x7FFFu;
+                if (a >= K) { free(t); return -11; }
+                const float scale = gamma * ((pk & 0x8000u) ? -1.0f : 1.0f);
+                const float* atom = D + (size_t)a * T;
+                for (size_t c = 0; c < T; ++c) t[c] += scale * atom[c];
+            }
+        }
+        const uint32_t br = i / n_col_tiles, bc = i % n_col_tiles;
+        for (uint16_t r = 0; r < tr; ++r)
+            memcpy(out + ((size_t)br * tr + r) * ld + (size_t)bc * tc, t + (size_t)r * tc,
+                   sizeof(float) * tc);
+    }
+    free(t);
+    return 0;
+}
+
+/* decompress: :1340-1440 */
+int orc_hsdr_decompress(const uint8_t* p, size_t n, float* out) {
+    orc_hsdr_view v;
+    int rc = orc_hsdr_parse(p, n, &v);
+    if (rc) return rc;
+    if (v.kind != 0) return -2;
+    if (v.tile_rows == 0 || v.tile_cols == 0) return -5;
+    const uint32_t R = v.rows, C = v.cols;
+    const uint32_t R_full = (R / v.tile_rows) * v.tile_rows;
+    const uint32_t C_full = (C / v.tile_cols) * v.tile_cols;
+    const uint32_t n_col_tiles = C_full / v.tile_cols;
+    if (n_col_tiles == 0 || v.n_tiles != (R_full / v.tile_rows) * n_col_tiles) return -6;
+    const size_t T = (size_t)v.tile_rows * v.tile_cols;
+    float* D = (float*)malloc(4u * (size_t)v.n_atoms * T);
+    float scales[256];
+    if (!D) return -10;
+    memcpy(D, p + v.off_dict, 4u * (size_t)v.n_atoms * T);
+    memcpy(scales, p + v.off_scales, 4u * v.n_stages);
+    rc = decode_tiles_into(D, scales, p + v.off_codes, v.n_tiles, v.tile_rows, v.tile_cols,
+                           v.n_atoms, v.n_stages, v.k, n_col_tiles, out, C);
+    free(D);
+    if (rc) return rc;
+    /* edge strips, :1425-1437: top-right rows[0,R_full) x cols[C_full,C), then bottom rows */
+    const size_t need = 4u * ((size_t)R_full * (C - C_full) + (size_t)(R - R_full) * C);
+    if (need != v.edge_bytes) return -7;
+    const uint8_t* e = p + v.off_edges;
+    for (uint32_t r = 0; r < R_full; ++r)
+        for (uint32_t c = C_full; c < C; ++c) { out[(size_t)r * C + c] = rdf(e); e += 4; }
+    for (uint32_t r = R_full; r < R; ++r)
+        for (uint32_t c = 0; c < C; ++c) { out[(size_t)r * C + c] = rdf(e); e += 4; }
+    return 0;
+}
+
+/* decompressWithExternalDictionary: :1804-1828 */
+int orc_hsdc_decompress(const uint8_t* p, size_t n, const float* atoms, const float* scales,
+                        uint16_t tr, uint16_t tc, uint16_t K, uint8_t S, uint8_t k, float* out) {
+    orc_hsdr_view v;
+    int rc = orc_hsdr_parse(p, n, &v);
+    if (rc) return rc;
+    if (v.kind != 1) return -2;
+    if ((rc = check_dict_geometry(&v, tr, tc, K, S, k))) return rc;
+    if (v.rows % tr || v.cols % tc) return -6;
+    const uint32_t n_col_tiles = v.cols / tc;
+    if (v.n_tiles != (v.rows / tr) * n_col_tiles) return -6;
+    return decode_tiles_into(atoms, scales, p + v.off_codes, v.n_tiles, tr, tc, K, S, k,
+                             n_col_tiles, out, v.cols);
+}
+
+/* SDRInferenceEngine::matmulForLayer dense fallback, SparseInferenceEngine.cpp:1301-1310 */
+int orc_dense_matmul(const float* W, size_t R, size_t C, const float* x, size_t batch, float* y) {
+    memset(y, 0, R * batch * sizeof(float));
+    #pragma omp parallel for schedule(static)
+    for (long r = 0; r < (long)R; ++r)
+        for (size_t c = 0; c < C; ++c) {
+            const float w = W[(size_t)r * C + c];
+            for (size_t b = 0; b < batch; ++b) y[(size_t)r * batch + b] += w * x[c * batch + b];
+        }
+    return 0;
+}
+
+/* fp16_to_fp32, utils/fp16_convert.hpp:26-60 (bit-manipulation branch) */
+float orc_fp16_to_fp32(uint16_t h) {
+    const uint32_t sign = (h >> 15) & 1u;
+    uint32_t exponent = (h >> 10) & 0x1Fu;
+    uint32_t mantissa = h & 0x3FFu;
+    uint32_t f;
+    if (exponent == 0) {
+        if (mantissa == 0) {
+            f = sign << 31;
+        } else {
+            int e = 1;
+            while ((mantissa & 0x400u) == 0) { mantissa <<= 1; --e; }
+            mantissa &= 0x3FFu;
+            f = (sign << 31) | ((uint32_t)(e + (127 - 15)) << 23) | (mantissa << 13);
+        }
+    } else if (exponent == 0x1F) {
+        f = (sign << 31) | 0x7F800000u | (mantissa << 13);
+    } else {
+        f = (sign << 31) | ((exponent + (127 - 15)) << 23) | (mantissa << 13);
+    }
+    float out;
+    memcpy(&out, &f, 4);
+    return out;
+}
+
+/* 6-bit scale/min unpack shared by Q4_K and Q5_K: :802-814 */
+static void unpack_k_scales_mins(const uint8_t* s12, uint8_t* sc, uint8_t* mn) {
+    for (int is = 0; is < 4; ++is) {
+        sc[is] = s12[is] & 0x3F;
+        mn[is] = s12[is + 4] & 0x3F;
+    }
+    for (int is = 4; is < 8; ++is) {
+        sc[is] = (uint8_t)((s12[is + 4] & 0x0F) | ((s12[is - 4] >> 6) << 4));
+        mn[is] = (uint8_t)((s12[is + 4] >> 4) | ((s12[is] >> 6) << 4));
+    }
+}
+
+/* dequantizeSegmentToFP32: :713-989 */
+long orc_dequantize(const char* fmt, const uint8_t* p, size_t nbytes, float scale,
+                    float zero_point, float* out, size_t cap) {
+    if (!strcmp(fmt, "f32")) {                                   /* :943-952 */
+        if (nbytes % 4) return -1;
+        if (nbytes / 4 > cap) return -2;
+        memcpy(out, p, nbytes);
+        return (long)(nbytes / 4);
+    }
+    if (!strcmp(fmt, "bf16")) {                                  /* :725-737 */
+        if (nbytes % 2) return -1;
+        const size_t n = nbytes / 2;
+        if (n > cap) return -2;
+        for (size_t i = 0; i < n; ++i) {
+            const uint32_t bits = (uint32_t)rd16(p + 2 * i) << 16;
+            memcpy(&out[i], &bits, 4);
+        }
+        return (long)n;
+    }
+    if (!strcmp(fmt, "f16")) {                                   /* :955-965 */
+        if (nbytes % 2) return -1;
+        const size_t n = nbytes / 2;
+        if (n > cap) return -2;
+        for (size_t i = 0; i < n; ++i) out[i] = orc_fp16_to_fp32(rd16(p + 2 * i));
+        return (long)n;
+    }
+    if (!strcmp(fmt, "i8")) {                                    /* :968-982 */
+        if (nbytes > cap) return -2;
+        for (size_t i = 0; i < nbytes; ++i) out[i] = ((float)(int8_t)p[i] - zero_point) * scale;
+        return (long)nbytes;
+    }
+    if (!strcmp(fmt, "q4_0")) {                                  /* :742-767 */
+        if (nbytes % 18) return -1;
+        const size_t nb = nbytes / 18;
+        if (nb * 32 > cap) return -2;
+        for (size_t b = 0; b < nb; ++b, p += 18) {
+            const float d = orc_fp16_to_fp32(rd16(p));
+            for (size_t j = 0; j < 16; ++j) {
+                const uint8_t byte = p[2 + j];
+                out[b * 32 + 2 * j] = (float)((int)(byte & 0x0F) - 8) * d;
+                out[b * 32 + 2 * j + 1] = (float)((int)(byte >> 4) - 8) * d;
+            }
+        }
+        return (long)(nb * 32);
+    }
+    if (!strcmp(fmt, "q8_0")) {                                  /* :769-790 */
+        if (nbytes % 34) return -1;
+        const size_t nb = nbytes / 34;
+        if (nb * 32 > cap) return -2;
+        for (size_t b = 0; b < nb; ++b, p += 34) {
+            const float d = orc_fp16_to_fp32(rd16(p));
+            for (size_t j = 0; j < 32; ++j) out[b * 32 + j] = (float)(int8_t)p[2 + j] * d;
+        }
+        return (long)(nb * 32);
+    }
+    if (!strcmp(fmt, "q4_k") || !strcmp(fmt, "q5_k")) {          /* :816-849, :851-887 */
+        const int q5 = fmt[1] == '5';
+        const size_t bb = q5 ? 176 : 144;
+        if (nbytes % bb) return -1;
+        const size_t nb = nbytes / bb;
+        if (nb * 256 > cap) return -2;
+        uint8_t sc[8], mn[8];
+        for (size_t b = 0; b < nb; ++b, p += bb) {
+            const float d = orc_fp16_to_fp32(rd16(p));
+            const float dmin = orc_fp16_to_fp32(rd16(p + 2));
+            const uint8_t* qh = p + 16;
+            const uint8_t* qs = q5 ? qh + 32 : p + 16;
+            unpack_k_scales_mins(p + 4, sc, mn);
+            for (int is = 0; is < 8; ++is) {
+                const float ds = d * (float)sc[is];
+                const float dm = dmin * (float)mn[is];
+                for (int j = 0; j < 32; ++j) {
+                    const int idx = is * 32 + j;
+                    const uint8_t byte = qs[idx / 2];
+                    uint8_t q = (idx & 1) ? (uint8_t)(byte >> 4) : (uint8_t)(byte & 0x0F);
+                    if (q5) q |= (uint8_t)(((qh[idx / 8] >> (idx % 8)) & 1) << 4);
+                    out[b * 256 + idx] = (float)q * ds - dm;
+                }
+            }
+        }
+        return (long)(nb * 256);
+    }
+    if (!strcmp(fmt, "q6_k")) {                                  /* :889-940 */
+        if (nbytes % 210) return -1;
+        const size_t nb = nbytes / 210;
+        if (nb * 256 > cap) return -2;
+        for (size_t b = 0; b < nb; ++b, p += 210) {
+            const uint8_t* ql = p;
+            const uint8_t* qh = p + 128;
+            const int8_t* scales = (const int8_t*)(p + 192);
+            const float d = orc_fp16_to_fp32(rd16(p + 208));
+            for (int half = 0; half < 2; ++half) {
+                const uint8_t* ql_h = ql + half * 64;
+                const uint8_t* qh_h = qh + half * 32;
+                for (int sub = 0; sub < 8; ++sub) {
+                    const float ds = d * (float)scales[half * 8 + sub];
+                    for (int j = 0; j < 16; ++j) {
+                        const int e = sub * 16 + j;
+                        const uint8_t lb = ql_h[e / 2];
+                        const uint8_t lo = (e & 1) ? (uint8_t)(lb >> 4) : (uint8_t)(lb & 0x0F);
+                        const uint8_t hi = (uint8_t)((qh_h[e / 4] >> ((e % 4) * 2)) & 3);
+                        const int q = (int)((hi << 4) | lo) - 32;
+                        out[b * 256 + half * 128 + e] = (float)q * ds;
+                    }
+                }
+            }
+        }
+        return (long)(nb * 256);
+    }
+    return -3;
+}

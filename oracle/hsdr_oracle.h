@@ -1,0 +1,116 @@
+/* TEST INFRASTRUCTURE ONLY — a CPU restatement, in plain C, of the reference's
+ * HSDR decode / fused-matmul / dequantisation path and of its decoder-layer
+ * arithmetic. Only tests, the smoke check and the bench's CPU-baseline leg may
+ * call it; the product library never does.
+ *
+ * Parity status: PINNED. tests/test_oracle_golden.py checks every function here
+ * against (a) the known-answer k-quant vectors of the reference's own
+ * src/test_hsdr_kquants.cpp, (b) fixtures under tests/golden/ produced by running
+ * the unmodified reference (oracle/_ref) on the seeds and shapes of its own tests,
+ * and (c), where the reference tree is present, the reference library live.
+ * Exception: the decoder-layer functions (decoder_oracle.c) restate code the
+ * reference never executes with default settings and no reference test covers:
+ * for those parity is UNPINNED beyond primitive-level checks.
+ *
+ * All citations are paths inside the reference tree.
+ */
+#ifndef HSDR_ORACLE_H
+#define HSDR_ORACLE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Parsed view of an "HSDR" (dictionary embedded) or "HSDC" (codes only) payload.
+ * Layouts: strategies/HierarchicalSDRStrategy.cpp:49-66 (HSDR v2, 36 bytes) and
+ * :675-692 (HSDC v1, 32 bytes). */
+typedef struct {
+    int kind;               /* 0 = HSDR, 1 = HSDC */
+    uint32_t rows, cols, n_tiles;
+    uint16_t tile_rows, tile_cols, n_atoms;
+    uint8_t n_stages, k;
+    float decay;
+    uint32_t edge_bytes;
+    size_t off_scales, off_dict, off_codes, off_edges; /* byte offsets; 0 when absent */
+} orc_hsdr_view;
+
+/* Return 0 on success, negative on malformed input (truncated, bad magic/version). */
+int orc_hsdr_parse(const uint8_t* payload, size_t n, orc_hsdr_view* v);
+
+/* unpackIndexSign, strategies/HierarchicalSDRStrategy.cpp:81-84. */
+void orc_unpack_codes(const uint16_t* packed, size_t n, int32_t* idx, int8_t* sign);
+
+/* matmulRowMajor, strategies/HierarchicalSDRStrategy.cpp:1257-1338.
+ * x is (C x batch) row-major, y is (R x batch) row-major. -2 for 2-D tiles etc. */
+int orc_hsdr_matmul(const uint8_t* payload, size_t n, const float* x, size_t batch, float* y);
+
+/* matmulWithExternalDictionary, :1830-1883 (+ parseCodesStream :1766-1801). */
+int orc_hsdc_matmul(const uint8_t* codes, size_t n, const float* atoms, const float* scales,
+                    uint16_t d_tile_rows, uint16_t d_tile_cols, uint16_t d_atoms,
+                    uint8_t d_stages, uint8_t d_k, const float* x, size_t batch, float* y);
+
+/* decompress, :1340-1440 (decodeAllTiles :612-634, reassembleTiles :119-135, edge
+ * strips :1412-1438). out holds rows*cols floats. */
+int orc_hsdr_decompress(const uint8_t* payload, size_t n, float* out);
+
+/* decompressWithExternalDictionary, :1804-1828. */
+int orc_hsdc_decompress(const uint8_t* codes, size_t n, const float* atoms, const float* scales,
+                        uint16_t d_tile_rows, uint16_t d_tile_cols, uint16_t d_atoms,
+                        uint8_t d_stages, uint8_t d_k, float* out);
+
+/* Same arithmetic as decompress+dense in one pass, for any tile geometry:
+ * y (R x batch) = W_reconstructed (R x C) * x (C x batch). Used as the ground truth
+ * for 2-D tile matmuls, which the reference only reaches via decompress() +
+ * SDRInferenceEngine::matmulForLayer's dense loop (SparseInferenceEngine.cpp:1301-1310). */
+int orc_dense_matmul(const float* W, size_t R, size_t C, const float* x, size_t batch, float* y);
+
+/* dequantizeSegmentToFP32, :713-989. fmt is one of
+ * "f32","f16","bf16","i8","q4_0","q8_0","q4_k","q5_k","q6_k".
+ * Returns number of floats written, negative on size errors. */
+long orc_dequantize(const char* fmt, const uint8_t* data, size_t nbytes, float scale,
+                    float zero_point, float* out, size_t out_cap);
+
+float orc_fp16_to_fp32(uint16_t h); /* utils/fp16_convert.hpp:26-60 */
+
+/* ---- decoder-layer arithmetic (decoder_oracle.c) ---- */
+
+/* api/cortex_sdk.cpp:1208-1232 */
+void orc_rms_norm(const float* in, const float* w, size_t tokens, size_t hidden, float eps,
+                  float* out);
+/* api/cortex_sdk.cpp:1363-1423; tensor is (seq, heads, head_dim); position of row t is pos0+t */
+void orc_rope(float* t, size_t seq, size_t heads, size_t head_dim, float theta, size_t pos0);
+/* api/cortex_sdk.cpp:1245-1256 */
+void orc_silu_mul(const float* gate, const float* up, size_t n, float* out);
+/* kernels/attention_kernels.cpp:26-113 + kernels/simd_kernels.cpp:198-217, causal, with
+ * the kv heads shared by q_heads/kv_heads query heads (cortex_sdk.cpp:1453-1478).
+ * q (seq, q_heads, hd); k, v (seq, kv_heads, hd); out (seq, q_heads*hd). */
+void orc_attention(const float* q, const float* k, const float* v, size_t seq, size_t q_heads,
+                   size_t kv_heads, size_t head_dim, float* out);
+
+typedef struct {
+    uint32_t n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab;
+    float eps, theta;
+} orc_decoder_cfg;
+
+/* Dense fp32 weights of one block, all (out x in) row-major, as decompress() yields. */
+typedef struct {
+    const float *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm, *w_gate, *w_up, *w_down;
+} orc_block_weights;
+
+/* run_transformer_decode, api/cortex_sdk.cpp:1543-1696, over the whole `tokens`
+ * sequence (no KV cache, as the reference). hidden_out receives the final-normed
+ * hidden state of EVERY position (seq x hidden); logits_out (may be NULL) the
+ * logits of the LAST position: dot of its hidden with each row of lm_head
+ * (SparseInferenceEngine.cpp:2310-2320). */
+int orc_decoder_forward(const orc_decoder_cfg* cfg, const float* tok_embd,
+                        const orc_block_weights* blocks, const float* out_norm,
+                        const float* lm_head, const int32_t* tokens, size_t seq,
+                        float* hidden_out, float* logits_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
