@@ -1,0 +1,337 @@
+#!/usr/bin/env python
+"""Benchmark of the HSDR compressed-weight matmul on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU code
+
+Workload (N=1): the MLP-projection case — W 11008x4096, HSDR 1-D row tiles (K=512, 3x8),
+decode GEMV at batch 1. One step = one pass over SEGS distinct device-resident copies of
+the compressed weight (SEGS * payload > 2 * L2, so every launch reads HBM, not L2).
+`value` = algorithmic compressed bytes processed per second with inputs resident in HBM;
+`e2e` = the same metric through the host-buffer C-ABI call (H2D of x and D2H of y inside
+the timed region). The M sweep {1, 8, 64, 512} is reported beside it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+R, C, K, S, KPS = 11008, 4096, 512, 3, 8
+SEGS = 32                      # 32 * 8.9 MB = 285 MB  >  2 * 126 MB L2
+CACHE = os.path.join(os.environ.get("TMPDIR", "/tmp"), "cortexsdr_b200_bench")
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def workload_payload():
+    """The 11008x4096 weight, N(0, 0.02) seed 2, encoded by the reference's own encoder
+    (forRow1D, ksvd_iters=0) when oracle/_ref is present, else a synthetic stand-in."""
+    os.makedirs(CACHE, exist_ok=True)
+    path = os.path.join(CACHE, f"w{R}x{C}_k{K}.hsdr")
+    if os.path.exists(path):
+        return open(path, "rb").read(), open(path + ".src").read()
+    from oracle.bindings import SEG_FEED_FORWARD, Reference, Segment, cfg_row1d
+    if Reference.available():
+        W = np.random.default_rng(2).normal(0, 0.02, (R, C)).astype(np.float32)
+        cfg = cfg_row1d(C, K, KPS, ksvd_iters=0)
+        pay = Reference().compress(Segment("blk.0.ffn_gate.weight", W, (R, C), SEG_FEED_FORWARD), cfg, cfg)
+        src = "reference encoder (forRow1D, ksvd_iters=0)"
+    else:
+        from cortexsdr_b200 import synth
+        pay = synth.hsdr_payload(R, C, n_atoms=K, n_stages=S, k=KPS, seed=2)
+        src = "synthetic payload (reference encoder not built here)"
+    with open(path + ".tmp", "wb") as f:
+        f.write(pay)
+    os.replace(path + ".tmp", path)
+    open(path + ".src", "w").write(src)
+    return pay, src
+
+
+def alg_bytes(payload_len: int, m: int, x_bytes: int = 4) -> int:
+    """payload + activations + outputs, the algorithmic traffic of one matmul."""
+    return payload_len + C * m * x_bytes + R * m * 4
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v == "Active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_baseline(pay: bytes, iters: int = 7):
+    """The reference's matmulRowMajor (single-threaded by construction) on the same payload,
+    batch 1, payload bytes already in memory; falls back to the C oracle port."""
+    from oracle.bindings import Oracle, Reference
+    x = np.random.default_rng(3).normal(0, 1, (C, 1)).astype(np.float32)
+    if Reference.available():
+        sec, _ = Reference().matmul_timed(pay, x, 1, R, iters=iters)
+        kind = "reference"
+    else:
+        orc = Oracle()
+        ts = []
+        for _ in range(iters):
+            t0 = time.perf_counter()
+            orc.matmul(pay, x, 1)
+            ts.append(time.perf_counter() - t0)
+        sec, kind = statistics.median(ts), "port"
+    return {"value": alg_bytes(len(pay), 1) / sec / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+            "sample": f"1 of {SEGS} segments, batch 1, median of {iters} calls after 2 warm-ups",
+            "ms_per_matmul": sec * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    pay, src = workload_payload()
+    from oracle.bindings import Reference
+    x = np.random.default_rng(3).normal(0, 1, (C, 1)).astype(np.float32)
+    per_step = 2                      # bounded sample: 2 of the SEGS matmuls per step
+    if Reference.available():
+        ref = Reference()
+        fn, kind = (lambda: ref.matmul_timed(pay, x, 1, R, iters=per_step)[0] * per_step), "reference"
+    else:
+        from oracle.bindings import Oracle
+        orc = Oracle()
+
+        def fn():
+            t0 = time.perf_counter()
+            for _ in range(per_step):
+                orc.matmul(pay, x, 1)
+            return time.perf_counter() - t0
+        kind = "port"
+    for _ in range(args.warmup):
+        fn()
+    secs = [fn() for _ in range(args.steps)]
+    total = sum(secs)
+    val = alg_bytes(len(pay), 1) * per_step * args.steps / total / 1e9
+    line = {"impl": "reference", "metric": "compressed_weight_matmul_GBps", "value": val, "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": f"synthetic N(0,0.02) weight; {src}",
+            "config": {"workload": f"cfg2 MLP projection {R}x{C} HSDR row tiles K={K} {S}x{KPS}, GEMV batch 1"},
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": 1, "kind": kind,
+                             "sample": f"{per_step} of {SEGS} segment matmuls per step (matmulRowMajor is "
+                                       "single-threaded by construction), payload bytes in memory"},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--segs", type=int, default=SEGS)
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    import cortexsdr_b200 as cs
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    hbm_peak, tf_peak, peak_src = peaks()
+
+    if rank == 0:
+        pay, src = workload_payload()
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        pay, src = workload_payload()
+
+    stream = torch.cuda.Stream()
+    ctx = cs.Context(local, stream.cuda_stream)
+    nseg = args.segs
+    segs = [cs.Segment.from_payload(pay, ctx) for _ in range(nseg)]
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    bytes1 = alg_bytes(len(pay), 1)
+
+    def make_io(m, dtype):
+        x = torch.randn((m, C), generator=gen, device="cuda", dtype=torch.float32).to(dtype)
+        y = torch.empty((nseg, m, R), device="cuda", dtype=torch.float32)
+        return x, y
+
+    def step(x, y, m, dt):
+        for i, s in enumerate(segs):
+            s.matmul_device(x.data_ptr(), dt, cs.TOKEN_MAJOR, m, y[i].data_ptr(), cs.TOKEN_MAJOR)
+
+    def timed(fn, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- headline: GEMV, batch 1, fp32 activations resident in HBM ----
+    x1, y1 = make_io(1, torch.float32)
+    launches0 = ctx.launch_count
+    with ClockSampler(local) as clk:
+        ms = timed(lambda: step(x1, y1, 1, cs.DTYPE_F32), args.steps, max(3, args.warmup))
+        # keep the sampler busy long enough to see the clocks under load
+        t_end = time.time() + 1.0
+        while time.time() < t_end:
+            step(x1, y1, 1, cs.DTYPE_F32)
+        ctx.synchronize()
+    launches = None
+    value = bytes1 * nseg * args.steps * world / (ms / 1e3) / 1e9
+    # launch count of exactly the timed region
+    l0 = ctx.launch_count
+    step(x1, y1, 1, cs.DTYPE_F32)
+    ctx.synchronize()
+    launches = (ctx.launch_count - l0) * args.steps
+
+    # ---- per-kernel durations over the same steps (events around every launch) ----
+    ctx.profile(True)
+    with torch.cuda.stream(stream):
+        for _ in range(min(args.steps, 20)):
+            step(x1, y1, 1, cs.DTYPE_F32)
+    prof = ctx.profile_read()
+    ctx.profile(False)
+    n_dx, ms_dx = prof.get("hsdr_dx", (0, 0.0))
+    n_g, ms_g = prof.get("hsdr_gather", (0, 0.0))
+    dict_bytes = 4 * K * C + C * 4 + K * 4          # dictionary + x in, Dx out: the Dx kernel's share
+    dx_us = ms_dx / max(n_dx, 1) * 1e3
+    achieved = dict_bytes / (dx_us * 1e-6) / 1e9 if n_dx else None
+    roofline = {"bound": "hbm", "kernel": "hsdr_dx_kernel", "achieved": achieved, "peak": hbm_peak,
+                "unit": "GB/s", "frac": (achieved / hbm_peak) if achieved else None, "peak_source": peak_src,
+                "traffic": None, "alg_bytes_per_launch": dict_bytes, "us_per_launch": dx_us,
+                "gather_us_per_launch": ms_g / max(n_g, 1) * 1e3,
+                "whole_matmul_frac": value / world / hbm_peak}
+
+    # ---- e2e: host buffers through the C-ABI (csdr_matmul), H2D + D2H inside the timed region ----
+    xh = np.random.default_rng(3).normal(0, 1, (C, 1)).astype(np.float32)
+
+    def e2e_step():
+        for s in segs:
+            s.matmul(xh, 1)
+    for _ in range(2):
+        e2e_step()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    n_e2e = max(3, min(args.steps, 10))
+    for _ in range(n_e2e):
+        e2e_step()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": bytes1 * nseg * n_e2e * world / e2e_s / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": nseg * C * 4, "d2h_bytes_per_step": nseg * R * 4,
+           "api": "csdr_matmul (host x, host y), one call per segment"}
+
+    # ---- M sweep of the same workload (bf16 activations, token-major) ----
+    sweep = {}
+    if not args.no_sweep:
+        for m in (1, 8, 64, 512):
+            xm, ym = make_io(m, torch.bfloat16)
+            st = max(3, args.steps // (4 if m >= 64 else 1))
+            msm = timed(lambda: step(xm, ym, m, cs.DTYPE_BF16), st, 3)
+            per = msm / st / nseg * 1e-3
+            ent = {"us_per_matmul": per * 1e6}
+            if m <= 16:
+                ent["GBps_compressed"] = alg_bytes(len(pay), m, 2) / per / 1e9
+                ent["frac_hbm"] = ent["GBps_compressed"] / hbm_peak
+            ent["TFLOPs_dense_equiv"] = 2.0 * R * C * m / per / 1e12
+            ent["frac_bf16_peak"] = ent["TFLOPs_dense_equiv"] / tf_peak
+            sweep[f"M{m}"] = ent
+            del xm, ym
+
+    line = {"metric": "compressed_weight_matmul_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": f"synthetic N(0,0.02) weight; {src}",
+            "config": {"workload": f"cfg2 MLP projection {R}x{C} HSDR row tiles K={K} {S}x{KPS}, GEMV batch 1",
+                       "segments_per_step": nseg, "payload_bytes": len(pay),
+                       "l2": f"{nseg} distinct device copies = {nseg * len(pay) / 1e6:.0f} MB per step > L2",
+                       "parallelism": f"replicas x{world}"},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
+            "kernel_ms": {k: {"launches": v[0], "us_each": v[1] / v[0] * 1e3} for k, v in prof.items()},
+            "sweep": sweep}
+    if rank == 0:
+        if not args.no_cpu and world == 1:
+            line["cpu_baseline"] = cpu_baseline(pay)
+        elif world > 1:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -97,6 +97,23 @@ class Context:
     def launch_count(self) -> int:
         return int(self._lib.csdr_context_launch_count(self._h))
 
+    def profile(self, enable: bool):
+        """Bracket every kernel launch with CUDA events (benchmarks only)."""
+        _check(self._lib.csdr_context_profile(self._h, 1 if enable else 0))
+
+    def profile_read(self) -> dict:
+        """{kernel class: (launches, total_ms)} since profiling was enabled."""
+        out, cls = {}, 0
+        while True:
+            name = self._lib.csdr_kernel_class_name(cls).decode()
+            if name == "?":
+                return out
+            n, ms = C.c_uint64(), C.c_double()
+            _check(self._lib.csdr_context_profile_read(self._h, cls, C.byref(n), C.byref(ms)))
+            if n.value:
+                out[name] = (int(n.value), float(ms.value))
+            cls += 1
+
     def close(self):
         if getattr(self, "_h", None):
             self._lib.csdr_context_destroy(self._h)

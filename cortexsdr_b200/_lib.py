@@ -67,6 +67,10 @@ SIGNATURES = {
     "csdr_context_synchronize": (C.c_int, [_P]),
     "csdr_context_stream": (_P, [_P]),
     "csdr_context_launch_count": (C.c_uint64, [_P]),
+    "csdr_context_profile": (C.c_int, [_P, C.c_int]),
+    "csdr_context_profile_read": (C.c_int, [_P, C.c_int, C.POINTER(C.c_uint64),
+                                            C.POINTER(C.c_double)]),
+    "csdr_kernel_class_name": (C.c_char_p, [C.c_int]),
     "csdr_payload_inspect": (C.c_int, [_P, _SZ, C.POINTER(PayloadInfo)]),
     "csdr_segment_create": (C.c_int, [_P, _P, _SZ, C.POINTER(_P)]),
     "csdr_dictionary_create": (C.c_int, [_P, C.c_uint16, C.c_uint16, C.c_uint16, C.c_uint8,

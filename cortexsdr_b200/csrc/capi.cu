@@ -54,6 +54,33 @@ DevPtr upload(csdr_context* ctx, const void* src, size_t bytes) {
     return buf;
 }
 
+const char* kernel_class_name(int cls) {
+    static const char* names[KC_COUNT] = {"hsdr_unpack", "hsdr_dx", "hsdr_gather", "hsdr_tile_project",
+                                          "hsdr_tile_gather", "hsdr_edge", "dense_rows", "hsdr_decode_rows",
+                                          "dequant", "hsdr_gemm_tcgen05", "decoder_op"};
+    return (cls >= 0 && cls < KC_COUNT) ? names[cls] : "?";
+}
+
+LaunchScope::LaunchScope(csdr_context* c, int k) : ctx(c), cls(k) {
+    if (ctx->profiling) {
+        CSDR_CUDA(cudaEventCreate(&start));
+        CSDR_CUDA(cudaEventRecord(start, ctx->stream));
+    }
+}
+
+void LaunchScope::done(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) throw Error(CSDR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+    ++ctx->launches;
+    ++ctx->launches_by_class[cls];
+    if (start) {
+        cudaEvent_t stop;
+        CSDR_CUDA(cudaEventCreate(&stop));
+        CSDR_CUDA(cudaEventRecord(stop, ctx->stream));
+        ctx->timed.push_back({cls, start, stop});
+    }
+}
+
 void require_ctx(csdr_context* ctx) {
     if (!ctx) throw Error(CSDR_ERR_INVALID_ARG, "context is null");
     CSDR_CUDA(cudaSetDevice(ctx->device));
@@ -126,6 +153,40 @@ int csdr_context_synchronize(csdr_context* ctx) {
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
     });
 }
+
+int csdr_context_profile(csdr_context* ctx, int enable) {
+    return guard([&] {
+        require_ctx(ctx);
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        for (auto& t : ctx->timed) {
+            cudaEventDestroy(t.start);
+            cudaEventDestroy(t.stop);
+        }
+        ctx->timed.clear();
+        ctx->profiling = enable != 0;
+    });
+}
+
+int csdr_context_profile_read(csdr_context* ctx, int cls, uint64_t* launches, double* total_ms) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (cls < 0 || cls >= KC_COUNT) throw Error(CSDR_ERR_INVALID_ARG, "kernel class out of range");
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        uint64_t n = 0;
+        double ms = 0.0;
+        for (auto& t : ctx->timed) {
+            if (t.cls != cls) continue;
+            float e = 0.f;
+            CSDR_CUDA(cudaEventElapsedTime(&e, t.start, t.stop));
+            ms += e;
+            ++n;
+        }
+        if (launches) *launches = ctx->profiling ? n : ctx->launches_by_class[cls];
+        if (total_ms) *total_ms = ms;
+    });
+}
+
+const char* csdr_kernel_class_name(int cls) { return kernel_class_name(cls); }
 
 void* csdr_context_stream(csdr_context* ctx) { return ctx ? ctx->stream : nullptr; }
 uint64_t csdr_context_launch_count(const csdr_context* ctx) { return ctx ? ctx->launches : 0; }

@@ -74,6 +74,19 @@ struct Geometry {
 
 }  // namespace csdr
 
+namespace csdr {
+// Kernel classes for launch counting and optional per-class device timing.
+enum KernelClass {
+    KC_UNPACK = 0, KC_DX, KC_GATHER, KC_TILE_PROJECT, KC_TILE_GATHER, KC_EDGE, KC_DENSE,
+    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_COUNT
+};
+const char* kernel_class_name(int cls);
+struct TimedLaunch {
+    int cls;
+    cudaEvent_t start, stop;
+};
+}  // namespace csdr
+
 struct csdr_context {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -85,6 +98,10 @@ struct csdr_context {
     csdr::DevPtr scratch[4];
     void* scratch_get(int slot, size_t bytes);
     int* status_word = nullptr;  // device int: kernels record bounded-wait timeouts here
+    uint64_t launches_by_class[csdr::KC_COUNT] = {};
+    // When on, every launch is bracketed by two events on the stream (profile_read resolves them).
+    bool profiling = false;
+    std::vector<csdr::TimedLaunch> timed;
 };
 
 struct csdr_dictionary {
@@ -110,6 +127,16 @@ struct csdr_segment {
 };
 
 namespace csdr {
+
+// Brackets one kernel launch: counts it, checks the launch error, and when the context
+// is profiling records an event on either side.
+struct LaunchScope {
+    csdr_context* ctx;
+    int cls;
+    cudaEvent_t start = nullptr;
+    LaunchScope(csdr_context* c, int k);
+    void done(const char* what);
+};
 
 Geometry make_geometry(const csdr_payload_info& v);
 DevPtr upload(csdr_context* ctx, const void* src, size_t bytes);

@@ -174,12 +174,6 @@ dequant_kquant_kernel(int fmt, const uint8_t* __restrict__ data, size_t n_blocks
     }
 }
 
-inline void count_launch(csdr_context* ctx, const char* what) {
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) throw Error(CSDR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
-    ++ctx->launches;
-}
-
 }  // namespace
 
 void launch_decode_rows(csdr_context* ctx, const csdr_segment* seg, const int32_t* rows_dev,
@@ -192,6 +186,7 @@ void launch_decode_rows(csdr_context* ctx, const csdr_segment* seg, const int32_
     const bool vec = (g.cols % 4u == 0) && (g.tile_cols % 4u == 0);
     const uint32_t per_block = 256u * (vec ? 4u : 1u);
     dim3 grid(static_cast<unsigned>(n_rows), (g.cols + per_block - 1u) / per_block, 1);
+    LaunchScope ls(ctx, KC_DECODE_ROWS);
     if (vec)
         hsdr_decode_rows_kernel<4><<<grid, 256, 0, ctx->stream>>>(
             static_cast<const float*>(seg->atoms->ptr), seg->codes_ptr(),
@@ -200,7 +195,7 @@ void launch_decode_rows(csdr_context* ctx, const csdr_segment* seg, const int32_
         hsdr_decode_rows_kernel<1><<<grid, 256, 0, ctx->stream>>>(
             static_cast<const float*>(seg->atoms->ptr), seg->codes_ptr(),
             static_cast<const float*>(seg->scales->ptr), edges, dg, rows_dev, out_dev);
-    count_launch(ctx, "hsdr_decode_rows_kernel");
+    ls.done("hsdr_decode_rows_kernel");
 }
 
 int dequant_format_id(const char* fmt) {
@@ -227,6 +222,7 @@ size_t dequant_output_count(int fmt, size_t nbytes) {
 void launch_dequantize(csdr_context* ctx, int fmt, const uint8_t* data_dev, size_t nbytes,
                        size_t n_out, float scale, float zero_point, float* out_dev) {
     if (n_out == 0) return;
+    LaunchScope ls(ctx, KC_DEQUANT);
     if (fmt >= Q4_K) {
         const size_t n_blocks = n_out / 256;
         const unsigned grid = static_cast<unsigned>(
@@ -238,7 +234,7 @@ void launch_dequantize(csdr_context* ctx, int fmt, const uint8_t* data_dev, size
         dequant_simple_kernel<<<grid, 256, 0, ctx->stream>>>(fmt, data_dev, n_out, scale, zero_point, out_dev);
     }
     (void)nbytes;
-    count_launch(ctx, "dequant kernel");
+    ls.done("dequant kernel");
 }
 
 }  // namespace csdr

@@ -488,12 +488,6 @@ dense_rows_kernel(const float* __restrict__ W, uint32_t R, uint32_t C, XView xv,
 // ---------------------------------------------------------------------------
 // host-side dispatch
 // ---------------------------------------------------------------------------
-inline void check_launch(csdr_context* ctx, const char* what) {
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) throw Error(CSDR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
-    ++ctx->launches;
-}
-
 template <typename Kern>
 void ensure_smem(Kern kern, size_t bytes) {
     if (bytes > 48 * 1024)
@@ -522,9 +516,10 @@ void launch_dx_t(csdr_context* ctx, const csdr_segment* seg, const XView& xv, fl
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    LaunchScope ls(ctx, KC_DX);
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, static_cast<const float*>(seg->atoms->ptr), g.n_atoms,
                                  g.cols, slab, xv, dx, static_cast<int>(nsplit)));
-    check_launch(ctx, "hsdr_dx_kernel");
+    ls.done("hsdr_dx_kernel");
 }
 
 template <int MT>
@@ -542,10 +537,11 @@ void launch_gather_t(csdr_context* ctx, const csdr_segment* seg, const float* dx
     auto kern = hsdr_gather_kernel<MT>;
     ensure_smem(kern, smem);
     const uint32_t grid = (g.rows + rows_per_cta - 1u) / rows_per_cta;
+    LaunchScope ls(ctx, KC_GATHER);
     kern<<<grid, kGatherThreads, smem, ctx->stream>>>(
         seg->codes_ptr(), g.rows, g.n_stages, g.k, static_cast<const float*>(seg->scales->ptr), dx,
         g.n_atoms, rows_per_cta, dx_in_smem, yv);
-    check_launch(ctx, "hsdr_gather_kernel");
+    ls.done("hsdr_gather_kernel");
 }
 
 template <int MT>
@@ -579,10 +575,11 @@ void matmul_tiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XView&
         const size_t smem = (static_cast<size_t>(kProjRows) * (g.tile_cols + 4u) +
                              static_cast<size_t>(MT) * g.cols_full) * sizeof(float);
         ensure_smem(kern, smem);
+        LaunchScope ls(ctx, KC_TILE_PROJECT);
         kern<<<(VR + kProjRows - 1u) / kProjRows, 256, smem, ctx->stream>>>(
             static_cast<const float*>(seg->atoms->ptr), VR, g.tile_rows, g.tile_cols, g.n_col_tiles,
             xv, P);
-        check_launch(ctx, "hsdr_tile_project_kernel");
+        ls.done("hsdr_tile_project_kernel");
     }
     {
         auto kern = hsdr_tile_gather_kernel<MT>;
@@ -592,15 +589,17 @@ void matmul_tiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XView&
         const size_t smem = cap16 * 16u + ((g.n_stages + 3u) & ~3u) * sizeof(float) +
                             8u * 32u * MT * sizeof(float);
         ensure_smem(kern, smem);
+        LaunchScope ls(ctx, KC_TILE_GATHER);
         kern<<<n_row_tiles * n_jchunks, 256, smem, ctx->stream>>>(
             seg->codes_ptr(), g.tile_rows, g.n_col_tiles, n_jchunks, g.n_stages, g.k,
             static_cast<const float*>(seg->scales->ptr), P, yv);
-        check_launch(ctx, "hsdr_tile_gather_kernel");
+        ls.done("hsdr_tile_gather_kernel");
     }
     if (seg->edges) {
+        LaunchScope ls(ctx, KC_EDGE);
         hsdr_edge_kernel<MT><<<(g.rows + 7u) / 8u, 256, 0, ctx->stream>>>(
             static_cast<const float*>(seg->edges->ptr), g.rows, g.cols, g.rows_full, g.cols_full, xv, yv);
-        check_launch(ctx, "hsdr_edge_kernel");
+        ls.done("hsdr_edge_kernel");
     }
 }
 
@@ -628,8 +627,9 @@ void dispatch_mt(int mt, F&& f) {
 void launch_unpack(csdr_context* ctx, const uint16_t* codes, size_t n, int32_t* idx, int8_t* sign) {
     if (n == 0) return;
     const size_t blocks = std::min<size_t>((n / 8 + 255) / 256 + 1, static_cast<size_t>(ctx->sm_count) * 8);
+    LaunchScope ls(ctx, KC_UNPACK);
     hsdr_unpack_kernel<<<static_cast<unsigned>(blocks), 256, 0, ctx->stream>>>(codes, n, idx, sign);
-    check_launch(ctx, "hsdr_unpack_kernel");
+    ls.done("hsdr_unpack_kernel");
 }
 
 void launch_dense_matmul(csdr_context* ctx, const float* W, uint32_t R, uint32_t C,
@@ -639,8 +639,9 @@ void launch_dense_matmul(csdr_context* ctx, const float* W, uint32_t R, uint32_t
         XView xv{a.x, a.x_dtype, a.x_layout, C, static_cast<uint32_t>(a.batch), static_cast<uint32_t>(b0), m};
         YView yv{a.y, a.y_layout, R, static_cast<uint32_t>(a.batch), static_cast<uint32_t>(b0), m, a.bias};
         dispatch_mt(pick_mt(m), [&](auto mt) {
+            LaunchScope ls(ctx, KC_DENSE);
             dense_rows_kernel<decltype(mt)::value><<<(R + 7u) / 8u, 256, 0, ctx->stream>>>(W, R, C, xv, yv);
-            check_launch(ctx, "dense_rows_kernel");
+            ls.done("dense_rows_kernel");
         });
     }
 }

@@ -1,0 +1,112 @@
+"""Seeded synthetic HSDR payloads and .sdr archives, byte-compatible with the reference
+writer (strategies/HierarchicalSDRStrategy.cpp:1198-1235; core/AICompressor.cpp:233-312).
+
+The reference encoder needs seconds to minutes per tensor; benchmarks, the smoke check and
+large decoder-shaped archives use these stand-ins instead: a Gaussian dictionary and
+uniformly random (atom, sign) codes, scaled so the reconstructed weight has the standard
+deviation asked for. Decoding cost does not depend on which atoms the codes name.
+"""
+from __future__ import annotations
+
+import struct
+
+import numpy as np
+
+SEG_WEIGHTS_FP32, SEG_ATTENTION, SEG_FEED_FORWARD, SEG_EMBEDDING, SEG_LAYER_NORM = 1, 11, 12, 13, 14
+
+
+def hsdr_payload(rows: int, cols: int, *, tile_rows: int = 1, tile_cols: int | None = None,
+                 n_atoms: int = 512, n_stages: int = 3, k: int = 8, decay: float = 0.5,
+                 seed: int = 0, weight_std: float = 0.02) -> bytes:
+    tile_cols = cols if tile_cols is None else tile_cols
+    rng = np.random.default_rng(seed)
+    rf, cf = rows // tile_rows * tile_rows, cols // tile_cols * tile_cols
+    n_tiles = (rf // tile_rows) * (cf // tile_cols)
+    scales = np.array([decay ** l for l in range(n_stages)], np.float32)
+    atom_std = weight_std / np.sqrt(k * float((scales.astype(np.float64) ** 2).sum()))
+    atoms = rng.standard_normal((n_atoms, tile_rows * tile_cols), dtype=np.float32) * np.float32(atom_std)
+    n_codes = n_tiles * n_stages * k
+    codes = (rng.integers(0, n_atoms, n_codes, dtype=np.uint16)
+             | (rng.integers(0, 2, n_codes, dtype=np.uint16) << 15)).astype(np.uint16)
+    n_edge = rf * (cols - cf) + (rows - rf) * cols
+    edges = rng.standard_normal(n_edge, dtype=np.float32) * np.float32(weight_std)
+    hdr = struct.pack("<4sIIIIHHHBBfI", b"HSDR", 2, rows, cols, n_tiles, tile_rows, tile_cols,
+                      n_atoms, n_stages, k, decay, 4 * n_edge)
+    return b"".join((hdr, scales.tobytes(), atoms.tobytes(), codes.tobytes(), edges.tobytes()))
+
+
+def _s(x: str) -> bytes:
+    b = x.encode()
+    return struct.pack("<I", len(b)) + b
+
+
+def write_sdr(path: str, segments) -> None:
+    """segments: iterable of dicts {name, payload(bytes), strategy_id, original_type, dims,
+    original_size, data_format='f32', layer_type='LINEAR', layer_index=0}. Layout of
+    AICompressor::compressModel (archive version 2)."""
+    segments = list(segments)
+    with open(path, "wb") as f:
+        f.write(b"CORTEXSR" + struct.pack("<IQQ", 2, len(segments), 0))
+        offsets = []
+        for s in segments:
+            offsets.append(f.tell())
+            f.write(s["payload"])
+        index_offset = f.tell()
+        for s, off in zip(segments, offsets):
+            dims = tuple(s["dims"])
+            f.write(_s(s["name"]) + _s(s.get("data_format", "f32")) + _s(s.get("layer_type", "LINEAR")))
+            f.write(struct.pack("<BBQQQ", s["original_type"], s["strategy_id"], s["original_size"],
+                                len(s["payload"]), off))
+            f.write(_s(s["name"]) + struct.pack("<I", s.get("layer_index", 0)))
+            f.write(struct.pack("<BB", 1, len(dims)) + struct.pack(f"<{len(dims)}I", *dims))
+            f.write(struct.pack("<fBBB", 0.0, 0, 0, 0))
+            if len(dims) == 2:
+                f.write(struct.pack("<BBII", 1, 2, 1, dims[1]) + struct.pack("<BBII", 1, 2, 1, dims[0]))
+            else:
+                f.write(struct.pack("<BB", 0, 0))
+        f.seek(8 + 4 + 8)
+        f.write(struct.pack("<Q", index_offset))
+
+
+def hsdr_segment(name: str, rows: int, cols: int, seg_type: int = SEG_WEIGHTS_FP32, layer_index: int = 0,
+                 **kw) -> dict:
+    return dict(name=name, payload=hsdr_payload(rows, cols, **kw), strategy_id=5, original_type=seg_type,
+                dims=(rows, cols), original_size=rows * cols * 4, layer_index=layer_index)
+
+
+def raw_segment(name: str, array: np.ndarray, seg_type: int = SEG_LAYER_NORM, layer_index: int = 0) -> dict:
+    a = np.ascontiguousarray(array, dtype=np.float32)
+    return dict(name=name, payload=a.tobytes(), strategy_id=0, original_type=seg_type, dims=a.shape,
+                original_size=a.nbytes, layer_index=layer_index, layer_type="" if a.ndim < 2 else "LINEAR")
+
+
+def decoder_archive(path: str, *, n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab, seed=100,
+                    geometry="row", n_atoms=512, k=8, kv_atoms=None) -> None:
+    """A decoder-shaped .sdr with the reference's GGUF-style tensor names
+    (api/cortex_sdk.cpp:456-524): every linear an HSDR segment, norm vectors stored raw."""
+    segs, sd = [], seed
+    kw = dict(n_atoms=n_atoms, k=k)
+
+    def lin(name, r, c, t, li, atoms=None):
+        nonlocal sd
+        sd += 1
+        a = dict(kw, n_atoms=atoms or n_atoms)
+        if geometry != "row":
+            a.update(tile_rows=geometry[0], tile_cols=geometry[1])
+        segs.append(hsdr_segment(name, r, c, t, li, seed=sd, **a))
+
+    lin("token_embd.weight", vocab, hidden, SEG_EMBEDDING, 0)
+    for i in range(n_layers):
+        p = f"blk.{i}."
+        segs.append(raw_segment(p + "attn_norm.weight", np.ones(hidden, np.float32), layer_index=i))
+        lin(p + "attn_q.weight", q_heads * head_dim, hidden, SEG_ATTENTION, i)
+        lin(p + "attn_k.weight", kv_heads * head_dim, hidden, SEG_ATTENTION, i, kv_atoms)
+        lin(p + "attn_v.weight", kv_heads * head_dim, hidden, SEG_ATTENTION, i, kv_atoms)
+        lin(p + "attn_output.weight", hidden, q_heads * head_dim, SEG_ATTENTION, i)
+        segs.append(raw_segment(p + "ffn_norm.weight", np.ones(hidden, np.float32), layer_index=i))
+        lin(p + "ffn_gate.weight", inter, hidden, SEG_FEED_FORWARD, i)
+        lin(p + "ffn_up.weight", inter, hidden, SEG_FEED_FORWARD, i)
+        lin(p + "ffn_down.weight", hidden, inter, SEG_FEED_FORWARD, i)
+    segs.append(raw_segment("output_norm.weight", np.ones(hidden, np.float32)))
+    lin("output.weight", vocab, hidden, SEG_EMBEDDING, 0)
+    write_sdr(path, segs)

@@ -91,6 +91,17 @@ CSDR_API void* csdr_context_stream(csdr_context* ctx);
 /* Number of kernels this library has launched on the context since creation. */
 CSDR_API uint64_t csdr_context_launch_count(const csdr_context* ctx);
 
+/* Per-kernel device timing for benchmarks. While enabled, every kernel this library
+ * launches on the context is bracketed by two CUDA events on the context's stream;
+ * csdr_context_profile_read then gives, for one kernel class (0 <= cls < the count
+ * csdr_kernel_class_name knows), the launches bracketed since enabling and the sum of
+ * their event-to-event durations. Enabling or disabling clears the record. With
+ * profiling off, *launches is the class's lifetime launch count and *total_ms is 0. */
+CSDR_API int csdr_context_profile(csdr_context* ctx, int enable);
+CSDR_API int csdr_context_profile_read(csdr_context* ctx, int cls, uint64_t* launches,
+                                       double* total_ms);
+CSDR_API const char* csdr_kernel_class_name(int cls); /* "?" past the last class */
+
 /* ---- payload framing (host only) ----
  * Replaces the header parse + checks at the top of matmulRowMajor / decompress
  * (strategies/HierarchicalSDRStrategy.cpp:1262-1299, :1345-1389) and parseCodesStream

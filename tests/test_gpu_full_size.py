@@ -1,0 +1,117 @@
+"""BASELINE-sized cases on the GPU: config 1 (4096x4096, batch 1, both tile geometries) and
+config 2 (11008x4096, M in {1, 8, 64, 512}, bf16 activations), encoded by the reference's
+own encoder where oracle/_ref is present (ksvd_iters=0: the legal fast mode; parity is
+against the reference decoding the SAME archive), else by the synthetic writer. Checked
+against the oracle and through size-independent properties."""
+import os
+import zlib
+
+import numpy as np
+import pytest
+
+import cortexsdr_b200 as cs
+from cortexsdr_b200 import synth
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+CACHE = os.path.join(os.environ.get("TMPDIR", "/tmp"), "cortexsdr_b200_tests")
+
+
+def _payload(tag, R, C, seed, geometry, seg_type):
+    """geometry: 'row' = forRow1D(C) (K=512, 3x8); 'tile' = the reference's default 2-D config
+    (128x128; K=256 k=5, or forMLP K=512 k=8 for FEED_FORWARD segments)."""
+    os.makedirs(CACHE, exist_ok=True)
+    path = os.path.join(CACHE, f"{tag}.hsdr")
+    if os.path.exists(path):
+        return open(path, "rb").read()
+    from oracle.bindings import SEG_FEED_FORWARD, Reference, Segment, cfg_default, cfg_mlp, cfg_row1d
+    mlp = seg_type == SEG_FEED_FORWARD
+    if Reference.available():
+        W = np.random.default_rng(seed).normal(0, 0.02, (R, C)).astype(np.float32)
+        if geometry == "row":
+            a = m = cfg_row1d(C, ksvd_iters=0)
+        else:
+            a, m = cfg_default(ksvd_iters=0), cfg_mlp(ksvd_iters=0)
+        pay = Reference().compress(Segment(tag + ".weight", W, (R, C), seg_type), a, m)
+    elif geometry == "row":
+        pay = synth.hsdr_payload(R, C, seed=seed)
+    else:
+        pay = synth.hsdr_payload(R, C, tile_rows=128, tile_cols=128, n_atoms=512 if mlp else 256,
+                                 k=8 if mlp else 5, seed=seed)
+    open(path, "wb").write(pay)
+    return pay
+
+
+def test_config1_row_tiles(ctx, oracle):
+    from oracle.bindings import SEG_WEIGHTS_FP32
+    pay = _payload("cfg1_row", 4096, 4096, 0, "row", SEG_WEIGHTS_FP32)
+    info = cs.inspect_payload(pay)
+    assert (info.n_atoms, info.n_stages, info.k_per_stage, info.tile_rows) == (512, 3, 8, 1)
+    assert len(pay) == 8585264                       # 36 + 12 + 4*512*4096 + 2*4096*24
+    seg = cs.Segment.from_payload(pay, ctx)
+    idx, sign = seg.unpack()
+    _, oidx, osign, _ = oracle.codes(pay)
+    assert np.array_equal(idx, oidx) and np.array_equal(sign, osign)
+    x = np.random.default_rng(1).normal(0, 1, (4096, 1)).astype(np.float32)
+    y = seg.matmul(x, 1)
+    e = rel_err(y, oracle.matmul(pay, x, 1))
+    assert e[0] < TOL and e[1] < TOL, e
+    # the decompress + dense route of the reference agrees with the fused one
+    W = seg.decompress()
+    assert zlib.crc32(W.tobytes()) == zlib.crc32(oracle.decompress(pay).tobytes())
+    e = rel_err(y, oracle.dense_matmul(W, x, 1))
+    assert e[0] < TOL and e[1] < TOL, e
+    # linearity of the whole path
+    x2 = np.random.default_rng(2).normal(0, 1, (4096, 1)).astype(np.float32)
+    lin = seg.matmul(x + 2 * x2, 1) - (y + 2 * seg.matmul(x2, 1))
+    assert np.abs(lin).max() < 1e-4 * np.abs(y).max()
+
+
+def test_config1_default_2d_tiles(ctx, oracle):
+    from oracle.bindings import SEG_WEIGHTS_FP32
+    pay = _payload("cfg1_tile", 4096, 4096, 0, "tile", SEG_WEIGHTS_FP32)
+    info = cs.inspect_payload(pay)
+    assert (info.tile_rows, info.tile_cols, info.n_atoms, info.k_per_stage) == (128, 128, 256, 5)
+    assert len(pay) == 16807984
+    seg = cs.Segment.from_payload(pay, ctx)
+    W = seg.decompress()
+    Wo = oracle.decompress(pay)
+    assert np.array_equal(W, Wo)
+    x = np.random.default_rng(1).normal(0, 1, (4096, 1)).astype(np.float32)
+    with pytest.raises(cs.CompressionError):
+        seg.matmul(x, 1)                             # the reference refuses 2-D tiles here
+    e = rel_err(seg.matmul(x, 1, allow_2d=True), oracle.dense_matmul(Wo, x, 1))
+    assert e[0] < TOL and e[1] < TOL, e
+
+
+@pytest.mark.parametrize("M", [1, 8, 64, 512])
+def test_config2_mlp_projection_sweep(ctx, oracle, M):
+    import torch
+    from oracle.bindings import SEG_FEED_FORWARD
+    pay = _payload("cfg2_row", 11008, 4096, 2, "row", SEG_FEED_FORWARD)
+    seg = cs.Segment.from_payload(pay, ctx)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    xb = torch.randn((M, 4096), generator=g, device="cuda").to(torch.bfloat16)
+    y = torch.empty((M, 11008), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    seg.matmul_device(xb.data_ptr(), cs.DTYPE_BF16, cs.TOKEN_MAJOR, M, y.data_ptr(), cs.TOKEN_MAJOR)
+    ctx.synchronize()
+    x32 = xb.float().cpu().numpy()                   # the bf16-rounded values, widened
+    want = oracle.matmul(pay, np.ascontiguousarray(x32.T), M).T
+    e = rel_err(y.cpu().numpy(), want)
+    assert e[0] < TOL and e[1] < TOL, (M, e)
+
+
+def test_config2_default_2d_tiles_mlp(ctx, oracle):
+    from oracle.bindings import SEG_FEED_FORWARD
+    pay = _payload("cfg2_tile", 11008, 4096, 2, "tile", SEG_FEED_FORWARD)
+    info = cs.inspect_payload(pay)
+    assert (info.n_atoms, info.k_per_stage, info.n_tiles) == (512, 8, 86 * 32)
+    seg = cs.Segment.from_payload(pay, ctx)
+    Wo = oracle.decompress(pay)
+    assert np.array_equal(seg.decompress(), Wo)
+    for M in (1, 4):
+        x = np.random.default_rng(M).normal(0, 1, (4096, M)).astype(np.float32)
+        e = rel_err(seg.matmul(x, M, allow_2d=True), oracle.dense_matmul(Wo, x, M))
+        assert e[0] < TOL and e[1] < TOL, (M, e)
