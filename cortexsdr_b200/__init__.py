@@ -542,6 +542,9 @@ class Decoder:
     def reset(self):
         _check(self.ctx._lib.csdr_decoder_reset(self._h))
 
+    def seek(self, seq: int, position: int):
+        _check(self.ctx._lib.csdr_decoder_seek(self._h, seq, position))
+
     def forward(self, tokens, seq: int = 0, want_logits=True, want_hidden=False):
         t = np.ascontiguousarray(tokens, dtype=np.int32)
         logits = np.empty(self.cfg.vocab, np.float32) if want_logits else None

@@ -1,14 +1,484 @@
-// placeholder until the decoder driver lands
+// Device-resident decoder-layer driver: the block loop of run_transformer_decode
+// (api/cortex_sdk.cpp:1543-1696) with every linear going through the compressed matmul,
+// activations kept on the device, and a KV cache in place of the reference's
+// whole-sequence recompute. Tensor parallelism row-shards every compressed weight
+// (dictionaries replicated) and rejoins with NCCL all-gathers at the four points per
+// block where a full vector is next consumed.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+#include <string>
+#include <vector>
+
 #include "internal.hpp"
+#include "kernels/decoder_ops.hpp"
+
 using namespace csdr;
-extern "C" {
-int csdr_decoder_create(csdr_archive*, const csdr_decoder_config*, csdr_decoder**) { set_last_error("decoder not built yet"); return CSDR_ERR_UNSUPPORTED; }
-int csdr_decoder_destroy(csdr_decoder*) { return CSDR_OK; }
-int csdr_decoder_reset(csdr_decoder*) { return CSDR_ERR_UNSUPPORTED; }
-int csdr_decoder_forward(csdr_decoder*, uint32_t, const int32_t*, size_t, float*, float*) { return CSDR_ERR_UNSUPPORTED; }
-int csdr_decoder_step(csdr_decoder*, const int32_t*, size_t, int32_t*, float*) { return CSDR_ERR_UNSUPPORTED; }
-int csdr_decoder_step_device_async(csdr_decoder*, const int32_t*, size_t, int32_t*) { return CSDR_ERR_UNSUPPORTED; }
-int csdr_nccl_unique_id(void*) { return CSDR_ERR_UNSUPPORTED; }
-int csdr_nccl_comm_create(csdr_context*, const void*, int, int, void**) { return CSDR_ERR_UNSUPPORTED; }
-int csdr_nccl_comm_destroy(void*) { return CSDR_ERR_UNSUPPORTED; }
+
+namespace {
+
+// ---- NCCL, bound at run time so the library loads (and the single-GPU path runs)
+// without it. If a process already holds libnccl.so.2 (PyTorch's), that copy is used. ----
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+NcclApi& nccl() {
+    static NcclApi api;
+    if (api.handle) return api;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) throw Error(CSDR_ERR_UNSUPPORTED, std::string("NCCL not available: ") + dlerror());
+    auto sym = [&](const char* n) {
+        void* p = dlsym(h, n);
+        if (!p) throw Error(CSDR_ERR_UNSUPPORTED, std::string("NCCL symbol missing: ") + n);
+        return p;
+    };
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+    api.handle = h;
+    return api;
 }
+
+void nccl_check(ncclResult_t r, const char* what) {
+    if (r != ncclSuccess)
+        throw Error(CSDR_ERR_CUDA, std::string(what) + ": " + nccl().GetErrorString(r));
+}
+
+void rethrow_last(int rc) {
+    if (rc != CSDR_OK) throw Error(rc, csdr_last_error());
+}
+
+// One linear layer of the model: an HSDR image (whole or this rank's row shard) or a
+// stored-raw fp32 matrix.
+struct Linear {
+    const csdr_segment* seg = nullptr;  // owned by the archive
+    csdr_segment* shard = nullptr;      // owned here
+    DevPtr raw;                         // fp32 (rows_local x cols), rows already sliced
+    uint32_t rows = 0, cols = 0, rows_local = 0;
+    const csdr_segment* use() const { return shard ? shard : seg; }
+};
+
+struct Layer {
+    DevPtr attn_norm, ffn_norm;
+    Linear q, k, v, o, gate, up, down;
+};
+
+}  // namespace
+
+struct csdr_decoder {
+    csdr_archive* ar = nullptr;
+    csdr_context* ctx = nullptr;
+    csdr_decoder_config cfg{};
+    uint32_t P = 1, rank = 0;
+    uint32_t QH_l = 0, KVH_l = 0, QD_l = 0, KVD_l = 0, I_l = 0, H_l = 0, V_l = 0;
+    uint32_t T_max = 0;
+    ncclComm_t comm = nullptr;
+    Linear emb, lm_head;
+    DevPtr out_norm;
+    std::vector<Layer> layers;
+    DevPtr kcache, vcache;  // [layer][seq][pos][kv head (local)][head_dim]
+    size_t cache_layer_stride = 0;
+    std::vector<int32_t> pos_host;
+    DevPtr pos_dev, tokens_dev, seq_of, pos_of, next_dev;
+    DevPtr hidden, normed, q, k, v, att, att_full, proj, gate, up, act_full, staged, logits, logits_l;
+    ~csdr_decoder() {
+        auto drop = [](Linear& l) {
+            if (l.shard) csdr_segment_destroy(l.shard);
+        };
+        drop(emb);
+        drop(lm_head);
+        for (auto& L : layers) {
+            drop(L.q); drop(L.k); drop(L.v); drop(L.o); drop(L.gate); drop(L.up); drop(L.down);
+        }
+    }
+};
+
+namespace {
+
+DevPtr dev_alloc(csdr_context* ctx, size_t bytes) { return std::make_shared<DeviceBuffer>(bytes, ctx->device); }
+float* F(const DevPtr& p) { return static_cast<float*>(p->ptr); }
+int32_t* I32(const DevPtr& p) { return static_cast<int32_t*>(p->ptr); }
+
+std::vector<float> load_raw(csdr_archive* ar, const std::string& name, size_t want_floats) {
+    size_t n = 0;
+    int rc = csdr_archive_load_segment(ar, name.c_str(), nullptr, 0, &n);
+    if (rc != CSDR_OK && rc != CSDR_ERR_BUFFER) rethrow_last(rc);
+    std::vector<float> v((n + 3) / 4);
+    rethrow_last(csdr_archive_load_segment(ar, name.c_str(), v.data(), v.size() * 4, &n));
+    if (want_floats && v.size() < want_floats)
+        throw Error(CSDR_ERR_GEOMETRY, "tensor '" + name + "' is smaller than the decoder config needs");
+    return v;
+}
+
+DevPtr load_vector(csdr_decoder* d, const std::string& name, uint32_t n) {
+    std::vector<float> v = load_raw(d->ar, name, n);
+    DevPtr p = upload(d->ctx, v.data(), static_cast<size_t>(n) * 4);
+    CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    return p;
+}
+
+// Resolve a linear by name; shard its output rows [rank*R/P, (rank+1)*R/P) when sharded.
+Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint32_t cols, bool sharded) {
+    csdr_segment_header h{};
+    int rc = csdr_archive_find(d->ar, name.c_str(), &h);
+    if (rc == CSDR_ERR_NOT_FOUND) throw Error(CSDR_ERR_NOT_FOUND, "decoder: tensor not in archive: " + name);
+    rethrow_last(rc);
+    Linear l;
+    l.rows = rows;
+    l.cols = cols;
+    const uint32_t P = sharded ? d->P : 1u;
+    if (rows % P) throw Error(CSDR_ERR_GEOMETRY, "decoder: rows of '" + name + "' do not divide by the tensor-parallel size");
+    l.rows_local = rows / P;
+    const uint32_t r0 = (sharded ? d->rank : 0u) * l.rows_local;
+    if (h.strategy_id == kHSDRStrategyId) {
+        rethrow_last(csdr_archive_segment(d->ar, name.c_str(), &l.seg));
+        if (l.seg->g.rows != rows || l.seg->g.cols != cols)
+            throw Error(CSDR_ERR_GEOMETRY, "decoder: shape of '" + name + "' does not match the config");
+        if (P > 1) rethrow_last(csdr_segment_shard_rows(d->ctx, l.seg, r0, r0 + l.rows_local, &l.shard));
+    } else if (h.strategy_id == 0) {
+        std::vector<float> w = load_raw(d->ar, name, static_cast<size_t>(rows) * cols);
+        l.raw = upload(d->ctx, w.data() + static_cast<size_t>(r0) * cols, static_cast<size_t>(l.rows_local) * cols * 4);
+        CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    } else {
+        throw Error(CSDR_ERR_UNSUPPORTED, "decoder: tensor '" + name + "' uses a strategy this library does not decode");
+    }
+    return l;
+}
+
+// y (T x rows_local) = x (T x cols) * W^T, token-major both sides.
+void linear(csdr_decoder* d, const Linear& l, const float* x, uint32_t T, float* y) {
+    if (l.raw) {
+        MatmulArgs a;
+        a.x = x;
+        a.x_layout = CSDR_LAYOUT_TOKEN_MAJOR;
+        a.batch = T;
+        a.y = y;
+        a.y_layout = CSDR_LAYOUT_TOKEN_MAJOR;
+        launch_dense_matmul(d->ctx, F(l.raw), l.rows_local, l.cols, a);
+    } else {
+        rethrow_last(csdr_matmul_device_async(d->ctx, l.use(), x, CSDR_DTYPE_F32, CSDR_LAYOUT_TOKEN_MAJOR, T, y,
+                                              CSDR_LAYOUT_TOKEN_MAJOR, nullptr));
+    }
+}
+
+// Rejoin row shards: local (T x W) on every rank -> full (T x P*W), replicated.
+void rejoin(csdr_decoder* d, const float* local, uint32_t T, uint32_t W, float* full, bool add) {
+    nccl_check(nccl().AllGather(local, F(d->staged), static_cast<size_t>(T) * W, ncclFloat, d->comm, d->ctx->stream),
+               "ncclAllGather");
+    op_unshard(d->ctx, F(d->staged), d->P, T, W, full, add);
+}
+
+void embed(csdr_decoder* d, uint32_t T) {
+    if (d->emb.raw) op_gather_rows(d->ctx, F(d->emb.raw), d->cfg.vocab, d->cfg.hidden, I32(d->tokens_dev), T, F(d->hidden));
+    else launch_decode_rows(d->ctx, d->emb.seg, I32(d->tokens_dev), T, F(d->hidden));
+}
+
+// All blocks over T tokens whose (sequence, position) pairs sit in seq_of/pos_of; leaves the
+// final-normed hidden states in d->normed.
+void run_blocks(csdr_decoder* d, uint32_t T) {
+    const csdr_decoder_config& c = d->cfg;
+    csdr_context* ctx = d->ctx;
+    const uint32_t H = c.hidden, HD = c.head_dim;
+    const bool tp = d->P > 1;
+    op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, F(d->normed));
+    for (uint32_t li = 0; li < c.n_layers; ++li) {
+        Layer& L = d->layers[li];
+        linear(d, L.q, F(d->normed), T, F(d->q));
+        linear(d, L.k, F(d->normed), T, F(d->k));
+        linear(d, L.v, F(d->normed), T, F(d->v));
+        float* kc = F(d->kcache) + li * d->cache_layer_stride;
+        float* vc = F(d->vcache) + li * d->cache_layer_stride;
+        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
+                      c.max_seq, c.rope_theta);
+        op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        const float* att = F(d->att);
+        if (tp) {
+            rejoin(d, F(d->att), T, d->QD_l, F(d->att_full), false);
+            att = F(d->att_full);
+        }
+        linear(d, L.o, att, T, F(d->proj));
+        if (tp) {
+            rejoin(d, F(d->proj), T, d->H_l, F(d->hidden), true);
+            op_rmsnorm(ctx, F(d->hidden), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
+        } else {
+            op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
+        }
+        linear(d, L.gate, F(d->normed), T, F(d->gate));
+        linear(d, L.up, F(d->normed), T, F(d->up));
+        op_silu_mul(ctx, F(d->gate), F(d->up), static_cast<size_t>(T) * d->I_l, F(d->gate));
+        const float* act = F(d->gate);
+        if (tp) {
+            rejoin(d, F(d->gate), T, d->I_l, F(d->act_full), false);
+            act = F(d->act_full);
+        }
+        linear(d, L.down, act, T, F(d->proj));
+        const float* next_norm = li + 1 < c.n_layers ? F(d->layers[li + 1].attn_norm) : F(d->out_norm);
+        if (tp) {
+            rejoin(d, F(d->proj), T, d->H_l, F(d->hidden), true);
+            op_rmsnorm(ctx, F(d->hidden), next_norm, T, H, c.rms_eps, F(d->normed));
+        } else {
+            op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), next_norm, T, H, c.rms_eps, F(d->normed));
+        }
+    }
+}
+
+// logits (T x vocab) of the given final-normed hidden rows.
+void run_logits(csdr_decoder* d, const float* hidden_rows, uint32_t T) {
+    if (d->P > 1) {
+        linear(d, d->lm_head, hidden_rows, T, F(d->logits_l));
+        rejoin(d, F(d->logits_l), T, d->V_l, F(d->logits), false);
+    } else {
+        linear(d, d->lm_head, hidden_rows, T, F(d->logits));
+    }
+}
+
+void need(csdr_decoder* d) {
+    if (!d) throw Error(CSDR_ERR_INVALID_ARG, "decoder is null");
+    require_ctx(d->ctx);
+}
+
+}  // namespace
+
+extern "C" {
+
+int csdr_nccl_unique_id(void* id128) {
+    return guard([&] {
+        if (!id128) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+        ncclUniqueId id;
+        nccl_check(nccl().GetUniqueId(&id), "ncclGetUniqueId");
+        std::memcpy(id128, &id, sizeof(id));
+    });
+}
+
+int csdr_nccl_comm_create(csdr_context* ctx, const void* id128, int rank, int world, void** comm_out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!id128 || !comm_out || world < 1 || rank < 0 || rank >= world)
+            throw Error(CSDR_ERR_INVALID_ARG, "bad communicator arguments");
+        ncclUniqueId id;
+        std::memcpy(&id, id128, sizeof(id));
+        ncclComm_t comm = nullptr;
+        nccl_check(nccl().CommInitRank(&comm, world, id, rank), "ncclCommInitRank");
+        *comm_out = comm;
+    });
+}
+
+int csdr_nccl_comm_destroy(void* comm) {
+    return guard([&] {
+        if (comm) nccl_check(nccl().CommDestroy(static_cast<ncclComm_t>(comm)), "ncclCommDestroy");
+    });
+}
+
+int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_decoder** out) {
+    return guard([&] {
+        if (!ar || !cfg || !out) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const csdr_segment* probe = nullptr;  // also proves the archive has a device context
+        auto d = std::make_unique<csdr_decoder>();
+        d->ar = ar;
+        d->cfg = *cfg;
+        const csdr_decoder_config& c = d->cfg;
+        if (!c.n_layers || !c.hidden || !c.q_heads || !c.kv_heads || !c.head_dim || !c.inter || !c.vocab ||
+            !c.max_seq || !c.max_batch || c.q_heads % c.kv_heads)
+            throw Error(CSDR_ERR_INVALID_ARG, "decoder config has a zero or inconsistent field");
+        d->P = c.tp_size ? c.tp_size : 1;
+        d->rank = c.tp_rank;
+        if (d->rank >= d->P) throw Error(CSDR_ERR_INVALID_ARG, "tp_rank out of range");
+        if (d->P > 1 && !c.nccl_comm) throw Error(CSDR_ERR_INVALID_ARG, "tensor parallelism needs an NCCL communicator");
+        if (c.q_heads % d->P || c.kv_heads % d->P || c.hidden % d->P || c.inter % d->P || c.vocab % d->P)
+            throw Error(CSDR_ERR_GEOMETRY, "heads, hidden, intermediate and vocab sizes must divide by the tensor-parallel size");
+        d->comm = static_cast<ncclComm_t>(c.nccl_comm);
+        // the context comes with the first HSDR image
+        int rc = csdr_archive_segment(ar, "token_embd.weight", &probe);
+        if (rc == CSDR_OK) d->ctx = probe->ctx;
+        else if (rc == CSDR_ERR_STRATEGY) {
+            rethrow_last(csdr_archive_segment(ar, "blk.0.attn_q.weight", &probe));
+            d->ctx = probe->ctx;
+        } else rethrow_last(rc);
+        require_ctx(d->ctx);
+        const uint32_t H = c.hidden, HD = c.head_dim, QD = c.q_heads * HD, KVD = c.kv_heads * HD;
+        d->QH_l = c.q_heads / d->P;
+        d->KVH_l = c.kv_heads / d->P;
+        d->QD_l = QD / d->P;
+        d->KVD_l = KVD / d->P;
+        d->I_l = c.inter / d->P;
+        d->H_l = H / d->P;
+        d->V_l = c.vocab / d->P;
+        d->emb = load_linear(d.get(), "token_embd.weight", c.vocab, H, false);
+        {
+            csdr_segment_header h{};
+            const char* head = csdr_archive_find(ar, "output.weight", &h) == CSDR_OK ? "output.weight"
+                               : csdr_archive_find(ar, "lm_head.weight", &h) == CSDR_OK ? "lm_head.weight"
+                                                                                        : "token_embd.weight";
+            d->lm_head = load_linear(d.get(), head, c.vocab, H, true);
+        }
+        d->out_norm = load_vector(d.get(), "output_norm.weight", H);
+        d->layers.resize(c.n_layers);
+        for (uint32_t i = 0; i < c.n_layers; ++i) {
+            const std::string p = "blk." + std::to_string(i) + ".";
+            Layer& L = d->layers[i];
+            L.attn_norm = load_vector(d.get(), p + "attn_norm.weight", H);
+            L.ffn_norm = load_vector(d.get(), p + "ffn_norm.weight", H);
+            L.q = load_linear(d.get(), p + "attn_q.weight", QD, H, true);
+            L.k = load_linear(d.get(), p + "attn_k.weight", KVD, H, true);
+            L.v = load_linear(d.get(), p + "attn_v.weight", KVD, H, true);
+            L.o = load_linear(d.get(), p + "attn_output.weight", H, QD, true);
+            L.gate = load_linear(d.get(), p + "ffn_gate.weight", c.inter, H, true);
+            L.up = load_linear(d.get(), p + "ffn_up.weight", c.inter, H, true);
+            L.down = load_linear(d.get(), p + "ffn_down.weight", H, c.inter, true);
+        }
+        csdr_context* ctx = d->ctx;
+        d->T_max = std::max(c.max_seq, c.max_batch);
+        const size_t T = d->T_max;
+        d->cache_layer_stride = static_cast<size_t>(c.max_batch) * c.max_seq * d->KVD_l;
+        d->kcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * 4);
+        d->vcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * 4);
+        d->pos_host.assign(c.max_batch, 0);
+        d->pos_dev = dev_alloc(ctx, c.max_batch * 4);
+        d->tokens_dev = dev_alloc(ctx, T * 4);
+        d->seq_of = dev_alloc(ctx, T * 4);
+        d->pos_of = dev_alloc(ctx, T * 4);
+        d->next_dev = dev_alloc(ctx, c.max_batch * 4);
+        d->hidden = dev_alloc(ctx, T * H * 4);
+        d->normed = dev_alloc(ctx, T * H * 4);
+        d->q = dev_alloc(ctx, T * d->QD_l * 4);
+        d->k = dev_alloc(ctx, T * d->KVD_l * 4);
+        d->v = dev_alloc(ctx, T * d->KVD_l * 4);
+        d->att = dev_alloc(ctx, T * d->QD_l * 4);
+        d->proj = dev_alloc(ctx, T * d->H_l * 4);
+        d->gate = dev_alloc(ctx, T * d->I_l * 4);
+        d->up = dev_alloc(ctx, T * d->I_l * 4);
+        d->logits = dev_alloc(ctx, static_cast<size_t>(c.max_batch) * c.vocab * 4);
+        if (d->P > 1) {
+            d->att_full = dev_alloc(ctx, T * QD * 4);
+            d->act_full = dev_alloc(ctx, T * c.inter * 4);
+            d->logits_l = dev_alloc(ctx, static_cast<size_t>(c.max_batch) * d->V_l * 4);
+            const size_t widest = std::max<size_t>(std::max<size_t>(T * QD, T * c.inter),
+                                                   std::max<size_t>(T * H, static_cast<size_t>(c.max_batch) * c.vocab));
+            d->staged = dev_alloc(ctx, widest * 4);
+        }
+        CSDR_CUDA(cudaMemsetAsync(d->kcache->ptr, 0, d->kcache->bytes, ctx->stream));
+        CSDR_CUDA(cudaMemsetAsync(d->vcache->ptr, 0, d->vcache->bytes, ctx->stream));
+        CSDR_CUDA(cudaMemsetAsync(d->pos_dev->ptr, 0, d->pos_dev->bytes, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        *out = d.release();
+    });
+}
+
+int csdr_decoder_destroy(csdr_decoder* d) {
+    return guard([&] {
+        if (!d) return;
+        cudaSetDevice(d->ctx->device);
+        cudaStreamSynchronize(d->ctx->stream);
+        delete d;
+    });
+}
+
+int csdr_decoder_reset(csdr_decoder* d) {
+    return guard([&] {
+        need(d);
+        std::fill(d->pos_host.begin(), d->pos_host.end(), 0);
+        CSDR_CUDA(cudaMemsetAsync(d->pos_dev->ptr, 0, d->pos_dev->bytes, d->ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    });
+}
+
+int csdr_decoder_seek(csdr_decoder* d, uint32_t seq, uint32_t position) {
+    return guard([&] {
+        need(d);
+        if (seq >= d->cfg.max_batch || position > d->cfg.max_seq)
+            throw Error(CSDR_ERR_INVALID_ARG, "sequence or position out of range");
+        d->pos_host[seq] = static_cast<int32_t>(position);
+        CSDR_CUDA(cudaMemcpyAsync(I32(d->pos_dev) + seq, &d->pos_host[seq], 4, cudaMemcpyHostToDevice, d->ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    });
+}
+
+int csdr_decoder_forward(csdr_decoder* d, uint32_t seq, const int32_t* tokens, size_t n_tokens,
+                         float* logits_out, float* hidden_out) {
+    return guard([&] {
+        need(d);
+        const csdr_decoder_config& c = d->cfg;
+        if (!tokens || n_tokens == 0) throw Error(CSDR_ERR_INVALID_ARG, "no tokens");
+        if (seq >= c.max_batch) throw Error(CSDR_ERR_INVALID_ARG, "sequence index out of range");
+        const int32_t p0 = d->pos_host[seq];
+        if (n_tokens > d->T_max || p0 + n_tokens > c.max_seq)
+            throw Error(CSDR_ERR_LIMIT, "sequence would exceed the KV-cache capacity (max_seq)");
+        for (size_t i = 0; i < n_tokens; ++i)
+            if (tokens[i] < 0 || static_cast<uint32_t>(tokens[i]) >= c.vocab)
+                throw Error(CSDR_ERR_INVALID_ARG, "token id outside the vocabulary");
+        csdr_context* ctx = d->ctx;
+        const uint32_t T = static_cast<uint32_t>(n_tokens);
+        std::vector<int32_t> so(T, static_cast<int32_t>(seq)), po(T);
+        for (uint32_t t = 0; t < T; ++t) po[t] = p0 + static_cast<int32_t>(t);
+        CSDR_CUDA(cudaMemcpyAsync(d->tokens_dev->ptr, tokens, T * 4, cudaMemcpyHostToDevice, ctx->stream));
+        CSDR_CUDA(cudaMemcpyAsync(d->seq_of->ptr, so.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
+        CSDR_CUDA(cudaMemcpyAsync(d->pos_of->ptr, po.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
+        embed(d, T);
+        run_blocks(d, T);
+        if (hidden_out)
+            CSDR_CUDA(cudaMemcpyAsync(hidden_out, d->normed->ptr, static_cast<size_t>(T) * c.hidden * 4,
+                                      cudaMemcpyDeviceToHost, ctx->stream));
+        if (logits_out) {
+            run_logits(d, F(d->normed) + static_cast<size_t>(T - 1) * c.hidden, 1);
+            CSDR_CUDA(cudaMemcpyAsync(logits_out, d->logits->ptr, static_cast<size_t>(c.vocab) * 4,
+                                      cudaMemcpyDeviceToHost, ctx->stream));
+        }
+        d->pos_host[seq] = p0 + static_cast<int32_t>(T);
+        CSDR_CUDA(cudaMemcpyAsync(I32(d->pos_dev) + seq, &d->pos_host[seq], 4, cudaMemcpyHostToDevice, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+int csdr_decoder_step_device_async(csdr_decoder* d, const int32_t* tokens_dev, size_t batch, int32_t* next_dev) {
+    return guard([&] {
+        need(d);
+        const csdr_decoder_config& c = d->cfg;
+        if (!tokens_dev || !next_dev || batch == 0 || batch > c.max_batch)
+            throw Error(CSDR_ERR_INVALID_ARG, "bad batch or null buffers");
+        for (size_t b = 0; b < batch; ++b)
+            if (d->pos_host[b] >= static_cast<int32_t>(c.max_seq))
+                throw Error(CSDR_ERR_LIMIT, "sequence would exceed the KV-cache capacity (max_seq)");
+        csdr_context* ctx = d->ctx;
+        const uint32_t B = static_cast<uint32_t>(batch);
+        if (tokens_dev != I32(d->tokens_dev))
+            CSDR_CUDA(cudaMemcpyAsync(d->tokens_dev->ptr, tokens_dev, B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        op_step_positions(ctx, I32(d->pos_dev), B, I32(d->seq_of), I32(d->pos_of));
+        embed(d, B);
+        run_blocks(d, B);
+        run_logits(d, F(d->normed), B);
+        op_argmax(ctx, F(d->logits), B, c.vocab, next_dev);
+        for (size_t b = 0; b < batch; ++b) ++d->pos_host[b];
+    });
+}
+
+int csdr_decoder_step(csdr_decoder* d, const int32_t* tokens, size_t batch, int32_t* next_out, float* logits_out) {
+    return guard([&] {
+        need(d);
+        if (!tokens || !next_out || batch == 0 || batch > d->cfg.max_batch)
+            throw Error(CSDR_ERR_INVALID_ARG, "bad batch or null buffers");
+        for (size_t b = 0; b < batch; ++b)
+            if (tokens[b] < 0 || static_cast<uint32_t>(tokens[b]) >= d->cfg.vocab)
+                throw Error(CSDR_ERR_INVALID_ARG, "token id outside the vocabulary");
+        csdr_context* ctx = d->ctx;
+        CSDR_CUDA(cudaMemcpyAsync(d->tokens_dev->ptr, tokens, batch * 4, cudaMemcpyHostToDevice, ctx->stream));
+        rethrow_last(csdr_decoder_step_device_async(d, I32(d->tokens_dev), batch, I32(d->next_dev)));
+        CSDR_CUDA(cudaMemcpyAsync(next_out, d->next_dev->ptr, batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        if (logits_out)
+            CSDR_CUDA(cudaMemcpyAsync(logits_out, d->logits->ptr, batch * d->cfg.vocab * 4, cudaMemcpyDeviceToHost,
+                                      ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,380 @@
+// Device kernels for the decoder-layer glue around the compressed matmul. Activations are
+// fp32, token-major (tokens x features), as in the reference's driver
+// (api/cortex_sdk.cpp:1543-1696). What each kernel restates:
+//   rmsnorm_kernel        rms_norm, api/cortex_sdk.cpp:1208-1232
+//   rope_cache_kernel     get_rope_cache + apply_rope_inplace, :1363-1423 (adjacent pairs
+//                         (2i, 2i+1), freq = theta^(-2i/head_dim)), then the K/V cache write
+//   attention_kernel      repeat_kv_heads :1453-1478 + multi_head_attention(causal)
+//                         kernels/attention_kernels.cpp:26-113 + softmax simd_kernels.cpp:198-217
+//   silu_mul_kernel       silu_mul, :1245-1256
+//   add_kernel            add_vectors, :1234-1243
+//   argmax_kernel         greedy pick over the logits row
+#include <cfloat>
+
+#include "../internal.hpp"
+#include "decoder_ops.hpp"
+
+namespace csdr {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    return v;
+}
+
+// One CTA per token.
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_t H, float eps,
+               float* __restrict__ out) {
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const float* src = x + static_cast<size_t>(blockIdx.x) * H;
+    float* dst = out + static_cast<size_t>(blockIdx.x) * H;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < H; i += 256) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += red[i];
+        inv_s = 1.0f / sqrtf(t / static_cast<float>(H) + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (uint32_t i = threadIdx.x; i < H; i += 256) dst[i] = src[i] * inv * w[i];
+}
+
+// hidden += delta, then out = rmsnorm(hidden) — the residual add and the next norm in one pass.
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
+                   const float* __restrict__ w, uint32_t H, float eps, float* __restrict__ out) {
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    float* h = hidden + static_cast<size_t>(blockIdx.x) * H;
+    const float* d = delta + static_cast<size_t>(blockIdx.x) * H;
+    float* dst = out + static_cast<size_t>(blockIdx.x) * H;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < H; i += 256) {
+        const float v = h[i] + d[i];
+        h[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += red[i];
+        inv_s = 1.0f / sqrtf(t / static_cast<float>(H) + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (uint32_t i = threadIdx.x; i < H; i += 256) dst[i] = h[i] * inv * w[i];
+}
+
+// grid (tokens); rotates q in place, writes rotated k and plain v into the cache slot
+// (seq_of[t], pos_of[t]). q (T, QH, HD); k, v (T, KVH, HD); caches (B, max_seq, KVH, HD).
+__global__ void __launch_bounds__(256)
+rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                  float* __restrict__ kc, float* __restrict__ vc, const int32_t* __restrict__ seq_of,
+                  const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t HD,
+                  uint32_t max_seq, float theta) {
+    const uint32_t t = blockIdx.x;
+    const int32_t pos = pos_of[t], sq = seq_of[t];
+    const uint32_t rotary = HD - (HD & 1u), half = rotary >> 1;
+    float* qt = q + static_cast<size_t>(t) * QH * HD;
+    const float* kt = k + static_cast<size_t>(t) * KVH * HD;
+    const float* vt = v + static_cast<size_t>(t) * KVH * HD;
+    const size_t slot = (static_cast<size_t>(sq) * max_seq + static_cast<size_t>(pos)) * KVH * HD;
+    const bool in_cache = pos >= 0 && static_cast<uint32_t>(pos) < max_seq && sq >= 0;
+    for (uint32_t e = threadIdx.x; e < (QH + KVH) * half; e += 256) {
+        const uint32_t head = e / half, i = (e - head * half) * 2u;
+        const float exponent = static_cast<float>(i) / static_cast<float>(HD);
+        const float freq = powf(theta, -exponent);
+        const float angle = static_cast<float>(pos) * freq;
+        const float c = cosf(angle), s = sinf(angle);
+        if (head < QH) {
+            float* b = qt + head * HD + i;
+            const float x0 = b[0], x1 = b[1];
+            b[0] = x0 * c - x1 * s;
+            b[1] = x0 * s + x1 * c;
+        } else if (in_cache) {
+            const uint32_t kh = head - QH;
+            const float* b = kt + kh * HD + i;
+            const float x0 = b[0], x1 = b[1];
+            kc[slot + kh * HD + i] = x0 * c - x1 * s;
+            kc[slot + kh * HD + i + 1] = x0 * s + x1 * c;
+        }
+    }
+    if (in_cache) {
+        if (HD & 1u)
+            for (uint32_t kh = threadIdx.x; kh < KVH; kh += 256)
+                kc[slot + kh * HD + HD - 1] = kt[kh * HD + HD - 1];
+        for (uint32_t e = threadIdx.x; e < KVH * HD; e += 256) vc[slot + e] = vt[e];
+    }
+}
+
+// One CTA (4 warps) per (token, query head). Each warp walks every 4th key with the head
+// dimension spread over its lanes (VPL floats per lane), keeping a running max / sum /
+// weighted V (the softmax of simd_kernels.cpp:198-217 evaluated in one pass); the four
+// partial states are merged through shared memory. Causality: token t sees cache positions
+// 0..pos_of[t] of its own sequence, all of which are written before this kernel runs.
+constexpr int kAttnWarps = 4;
+
+template <int VPL>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
+                 const float* __restrict__ vc, const int32_t* __restrict__ seq_of,
+                 const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t max_seq,
+                 float scale, float* __restrict__ out) {
+    constexpr uint32_t HD = VPL * 32u;
+    __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
+    __shared__ float sm_acc[kAttnWarps][HD];
+    const uint32_t t = blockIdx.x, h = blockIdx.y;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t kvh = h / (QH / KVH);
+    const int32_t n_keys = min(pos_of[t] + 1, static_cast<int32_t>(max_seq));
+    const size_t row = static_cast<size_t>(KVH) * HD;
+    const size_t base = static_cast<size_t>(seq_of[t]) * max_seq * row + kvh * HD + lane * VPL;
+    const float* qp = q + (static_cast<size_t>(t) * QH + h) * HD + lane * VPL;
+    float qv[VPL], acc[VPL];
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) {
+        qv[e] = qp[e];
+        acc[e] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    for (int32_t j = warp; j < n_keys; j += kAttnWarps) {
+        const float* kp = kc + base + static_cast<size_t>(j) * row;
+        const float* vp = vc + base + static_cast<size_t>(j) * row;
+        float kv[VPL], vv[VPL];
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) {
+            kv[e] = kp[e];
+            vv[e] = vp[e];
+        }
+        float s = 0.0f;
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) s = fmaf(qv[e], kv[e], s);
+        s = warp_sum(s) * scale;
+        const float m_new = fmaxf(m, s);
+        const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first key
+        const float p = expf(s - m_new);
+        l = l * corr + p;
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) acc[e] = fmaf(p, vv[e], acc[e] * corr);
+        m = m_new;
+    }
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) sm_acc[warp][lane * VPL + e] = acc[e];
+    __syncthreads();
+    if (warp == 0) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w]);
+        float L = 0.0f, o[VPL];
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) o[e] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float f = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
+            L = fmaf(sm_l[w], f, L);
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) o[e] = fmaf(sm_acc[w][lane * VPL + e], f, o[e]);
+        }
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+        float* op = out + (static_cast<size_t>(t) * QH + h) * HD + lane * VPL;
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) op[e] = o[e] * inv;
+    }
+}
+
+__global__ void silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                size_t n, float* __restrict__ out) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+        const float x = gate[i];
+        const float sig = 1.0f / (1.0f + expf(-x));
+        out[i] = (x * sig) * up[i];
+    }
+}
+
+__global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, size_t n) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride)
+        a[i] = a[i] + b[i];
+}
+
+// Rank-major gathered shards (P, T, W) -> token-major (T, P*W); add != 0 accumulates.
+__global__ void unshard_kernel(const float* __restrict__ staged, uint32_t P, uint32_t T, uint32_t W,
+                               float* __restrict__ out, int add) {
+    const size_t n = static_cast<size_t>(P) * T * W;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+        const uint32_t w = static_cast<uint32_t>(i % W);
+        const uint32_t t = static_cast<uint32_t>((i / W) % T);
+        const uint32_t p = static_cast<uint32_t>(i / (static_cast<size_t>(W) * T));
+        const size_t o = static_cast<size_t>(t) * P * W + static_cast<size_t>(p) * W + w;
+        out[o] = add ? out[o] + staged[i] : staged[i];
+    }
+}
+
+__global__ void gather_rows_kernel(const float* __restrict__ table, uint32_t n_rows, uint32_t H,
+                                   const int32_t* __restrict__ ids, float* __restrict__ out) {
+    const int32_t r = ids[blockIdx.x];
+    float* dst = out + static_cast<size_t>(blockIdx.x) * H;
+    const bool ok = r >= 0 && static_cast<uint32_t>(r) < n_rows;
+    const float* src = table + static_cast<size_t>(ok ? r : 0) * H;
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? src[i] : 0.0f;
+}
+
+// One CTA per logits row; first maximum wins.
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, uint32_t V, int32_t* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int32_t bi[32];
+    const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
+    float best = -INFINITY;
+    int32_t idx = 0x7FFFFFFF;
+    for (uint32_t i = threadIdx.x; i < V; i += 1024) {
+        const float v = row[i];
+        if (v > best || (v == best && static_cast<int32_t>(i) < idx)) {
+            best = v;
+            idx = static_cast<int32_t>(i);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+        const int32_t oi = __shfl_xor_sync(0xFFFFFFFFu, idx, off);
+        if (ov > best || (ov == best && oi < idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    if ((threadIdx.x & 31u) == 0) {
+        bv[threadIdx.x >> 5] = best;
+        bi[threadIdx.x >> 5] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = bv[threadIdx.x];
+        idx = bi[threadIdx.x];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+            const int32_t oi = __shfl_xor_sync(0xFFFFFFFFu, idx, off);
+            if (ov > best || (ov == best && oi < idx)) {
+                best = ov;
+                idx = oi;
+            }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7FFFFFFF ? 0 : idx;
+    }
+}
+
+// positions: pos_of[t] = pos[b] for a batched step, then pos[b] += 1 (all on the device, so a
+// captured step replays without host involvement).
+__global__ void step_positions_kernel(int32_t* __restrict__ pos, uint32_t B, int32_t* __restrict__ seq_of,
+                                      int32_t* __restrict__ pos_of) {
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) {
+        seq_of[b] = static_cast<int32_t>(b);
+        pos_of[b] = pos[b];
+        pos[b] = pos[b] + 1;
+    }
+}
+
+unsigned grid_for(size_t n, csdr_context* ctx) {
+    return static_cast<unsigned>(std::min<size_t>((n + 255) / 256, static_cast<size_t>(ctx->sm_count) * 8));
+}
+
+}  // namespace
+
+void op_rmsnorm(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps,
+                float* out) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(x, w, H, eps, out);
+    ls.done("rmsnorm_kernel");
+}
+
+void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const float* w, uint32_t T,
+                    uint32_t H, float eps, float* out) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    add_rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(hidden, delta, w, H, eps, out);
+    ls.done("add_rmsnorm_kernel");
+}
+
+void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, float* kc, float* vc,
+                   const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
+                   uint32_t HD, uint32_t max_seq, float theta) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    rope_cache_kernel<<<T, 256, 0, ctx->stream>>>(q, k, v, kc, vc, seq_of, pos_of, QH, KVH, HD, max_seq, theta);
+    ls.done("rope_cache_kernel");
+}
+
+void op_attention(csdr_context* ctx, const float* q, const float* kc, const float* vc,
+                  const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
+                  uint32_t HD, uint32_t max_seq, float* out) {
+    if (HD % 32u || HD > 256u || HD == 96u || HD == 160u || HD == 192u || HD == 224u)
+        throw Error(CSDR_ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 128 or 256");
+    const float scale = 1.0f / sqrtf(static_cast<float>(HD));
+    dim3 grid(T, QH);
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    switch (HD / 32u) {
+        case 1: attention_kernel<1><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
+        case 2: attention_kernel<2><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
+        case 4: attention_kernel<4><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
+        default: attention_kernel<8><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
+    }
+    ls.done("attention_kernel");
+}
+
+void op_silu_mul(csdr_context* ctx, const float* gate, const float* up, size_t n, float* out) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    silu_mul_kernel<<<grid_for(n, ctx), 256, 0, ctx->stream>>>(gate, up, n, out);
+    ls.done("silu_mul_kernel");
+}
+
+void op_add(csdr_context* ctx, float* a, const float* b, size_t n) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    add_kernel<<<grid_for(n, ctx), 256, 0, ctx->stream>>>(a, b, n);
+    ls.done("add_kernel");
+}
+
+void op_unshard(csdr_context* ctx, const float* staged, uint32_t P, uint32_t T, uint32_t W, float* out,
+                bool add) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    unshard_kernel<<<grid_for(static_cast<size_t>(P) * T * W, ctx), 256, 0, ctx->stream>>>(staged, P, T, W, out, add ? 1 : 0);
+    ls.done("unshard_kernel");
+}
+
+void op_gather_rows(csdr_context* ctx, const float* table, uint32_t n_rows, uint32_t H,
+                    const int32_t* ids, uint32_t T, float* out) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    gather_rows_kernel<<<T, 256, 0, ctx->stream>>>(table, n_rows, H, ids, out);
+    ls.done("gather_rows_kernel");
+}
+
+void op_argmax(csdr_context* ctx, const float* logits, uint32_t rows, uint32_t V, int32_t* out) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    argmax_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, V, out);
+    ls.done("argmax_kernel");
+}
+
+void op_step_positions(csdr_context* ctx, int32_t* pos, uint32_t B, int32_t* seq_of, int32_t* pos_of) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    step_positions_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(pos, B, seq_of, pos_of);
+    ls.done("step_positions_kernel");
+}
+
+}  // namespace csdr

@@ -1,0 +1,29 @@
+// Launchers of the decoder-layer glue kernels (decoder_ops.cu). All asynchronous on the
+// context's stream; activations fp32, token-major.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+struct csdr_context;
+
+namespace csdr {
+
+void op_rmsnorm(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps, float* out);
+void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const float* w, uint32_t T,
+                    uint32_t H, float eps, float* out);
+void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, float* kc, float* vc,
+                   const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
+                   uint32_t HD, uint32_t max_seq, float theta);
+void op_attention(csdr_context* ctx, const float* q, const float* kc, const float* vc, const int32_t* seq_of,
+                  const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH, uint32_t HD, uint32_t max_seq,
+                  float* out);
+void op_silu_mul(csdr_context* ctx, const float* gate, const float* up, size_t n, float* out);
+void op_add(csdr_context* ctx, float* a, const float* b, size_t n);
+void op_unshard(csdr_context* ctx, const float* staged, uint32_t P, uint32_t T, uint32_t W, float* out, bool add);
+void op_gather_rows(csdr_context* ctx, const float* table, uint32_t n_rows, uint32_t H, const int32_t* ids,
+                    uint32_t T, float* out);
+void op_argmax(csdr_context* ctx, const float* logits, uint32_t rows, uint32_t V, int32_t* out);
+void op_step_positions(csdr_context* ctx, int32_t* pos, uint32_t B, int32_t* seq_of, int32_t* pos_of);
+
+}  // namespace csdr

@@ -261,6 +261,10 @@ CSDR_API int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cf
                                  csdr_decoder** out);
 CSDR_API int csdr_decoder_destroy(csdr_decoder* d);
 CSDR_API int csdr_decoder_reset(csdr_decoder* d);
+/* Set sequence `seq` to `position` without computing anything: the cache rows below it
+ * keep whatever they hold (zeros after creation). For throughput measurements at a given
+ * context length. */
+CSDR_API int csdr_decoder_seek(csdr_decoder* d, uint32_t seq, uint32_t position);
 /* Run n_tokens new positions of sequence `seq` (prefill when n_tokens > 1). If
  * logits_out != NULL it receives the vocab logits of the LAST position (host, fp32).
  * If hidden_out != NULL it receives the final-normed hidden state of every new

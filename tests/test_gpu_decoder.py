@@ -1,0 +1,108 @@
+"""Decoder-layer driver on the GPU against the CPU restatement of the reference's
+run_transformer_decode (oracle/decoder_oracle.c), with every linear decoded by the oracle
+from the same archive. Tolerance on logits: 2e-2 max-abs, as the task states (observed
+differences are orders of magnitude smaller). No reference test covers this code, so
+parity here is against the restatement only."""
+import os
+
+import numpy as np
+import pytest
+
+import cortexsdr_b200 as cs
+from cortexsdr_b200 import synth
+
+pytestmark = pytest.mark.gpu
+LOGIT_TOL = 2e-2
+
+CFG = dict(n_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=32, inter=256, vocab=300)
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory, oracle):
+    path = str(tmp_path_factory.mktemp("dec") / "tiny.sdr")
+    synth.decoder_archive(path, **CFG, n_atoms=32, k=3, kv_atoms=16, seed=7)
+    ld = cs.SDRModelLoader(path, index_only=True)
+    dense = lambda n: oracle.decompress(ld.loadCompressedBytesByName(n))
+    raw = lambda n: ld.loadSegmentByName(n).view(np.float32)
+    blocks = []
+    for i in range(CFG["n_layers"]):
+        p = f"blk.{i}."
+        blocks.append(dict(attn_norm=raw(p + "attn_norm.weight"), wq=dense(p + "attn_q.weight"),
+                           wk=dense(p + "attn_k.weight"), wv=dense(p + "attn_v.weight"),
+                           wo=dense(p + "attn_output.weight"), ffn_norm=raw(p + "ffn_norm.weight"),
+                           w_gate=dense(p + "ffn_gate.weight"), w_up=dense(p + "ffn_up.weight"),
+                           w_down=dense(p + "ffn_down.weight")))
+    weights = dict(tok=dense("token_embd.weight"), blocks=blocks, out_norm=raw("output_norm.weight"),
+                   head=dense("output.weight"))
+    return path, weights
+
+
+def oracle_forward(oracle, weights, tokens, eps=1e-6, theta=1e6):
+    cfg = dict(CFG, eps=eps, theta=theta)
+    return oracle.decoder_forward(cfg, weights["tok"], weights["blocks"], weights["out_norm"], weights["head"], tokens)
+
+
+def make_decoder(path, ctx, **kw):
+    ld = cs.SDRModelLoader(path, ctx)
+    return cs.Decoder(ld, **CFG, max_seq=64, rms_eps=1e-6, rope_theta=1e6, **kw)
+
+
+def test_prefill_matches_oracle(ctx, oracle, model):
+    path, weights = model
+    tokens = np.random.default_rng(0).integers(0, CFG["vocab"], 12)
+    hid, logits = oracle_forward(oracle, weights, tokens)
+    dec = make_decoder(path, ctx)
+    g_logits, g_hid = dec.forward(tokens, want_hidden=True)
+    assert np.abs(g_hid - hid).max() < 1e-3
+    assert np.abs(g_logits - logits).max() < LOGIT_TOL
+    assert int(g_logits.argmax()) == int(logits.argmax())
+
+
+def test_kv_cache_equals_recompute(ctx, oracle, model):
+    path, weights = model
+    tokens = np.random.default_rng(1).integers(0, CFG["vocab"], 12)
+    dec = make_decoder(path, ctx)
+    one_shot, _ = dec.forward(tokens)
+    dec.reset()
+    dec.forward(tokens[:8], want_logits=False)
+    chunked, _ = dec.forward(tokens[8:])
+    assert np.abs(one_shot - chunked).max() < 1e-4
+    # greedy decode three tokens; the oracle recomputes the whole sequence each step, as the reference does
+    seq = list(tokens)
+    nxt = int(chunked.argmax())
+    for _ in range(3):
+        seq.append(nxt)
+        _, want = oracle_forward(oracle, weights, np.array(seq))
+        got_next, got = dec.step([nxt], want_logits=True)
+        assert np.abs(got[0] - want).max() < LOGIT_TOL
+        assert int(got_next[0]) == int(want.argmax())
+        nxt = int(got_next[0])
+
+
+def test_batched_step_sequences_are_independent(ctx, oracle, model):
+    path, weights = model
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, CFG["vocab"], n) for n in (5, 9, 3)]
+    dec = make_decoder(path, ctx, max_batch=3)
+    for s, p in enumerate(prompts):
+        dec.forward(p, seq=s, want_logits=False)
+    new = rng.integers(0, CFG["vocab"], 3)
+    nxt, logits = dec.step(new, want_logits=True)
+    for s, p in enumerate(prompts):
+        _, want = oracle_forward(oracle, weights, np.append(p, new[s]))
+        assert np.abs(logits[s] - want).max() < LOGIT_TOL
+        assert int(nxt[s]) == int(want.argmax())
+
+
+def test_decoder_limits_and_errors(ctx, model):
+    path, _ = model
+    dec = make_decoder(path, ctx)
+    with pytest.raises(ValueError, match="vocabulary"):
+        dec.forward([CFG["vocab"]])
+    with pytest.raises(ValueError, match="capacity"):
+        dec.forward(np.zeros(65, np.int32))
+    ld = cs.SDRModelLoader(path, ctx)
+    with pytest.raises(cs.CompressionError, match="does not match the config"):
+        cs.Decoder(ld, **dict(CFG, hidden=64), max_seq=8)
+    with pytest.raises(RuntimeError, match="not in archive"):
+        cs.Decoder(ld, **dict(CFG, n_layers=3), max_seq=8)
