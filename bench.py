@@ -176,6 +176,7 @@ def main():
     ap.add_argument("--segs", type=int, default=SEGS)
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -237,14 +238,27 @@ def main():
 
     # ---- headline: GEMV, batch 1, fp32 activations resident in HBM ----
     x1, y1 = make_io(1, torch.float32)
-    launches0 = ctx.launch_count
+    eager_ms = timed(lambda: step(x1, y1, 1, cs.DTYPE_F32), args.steps, max(3, args.warmup))
+    # The step is launch-bound from Python (one ctypes call per matmul): capture it once in a
+    # CUDA graph and time the replay; the eager figure is reported beside it.
+    run_step, launch_mode = (lambda: step(x1, y1, 1, cs.DTYPE_F32)), "eager (one C-ABI call per matmul)"
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step(x1, y1, 1, cs.DTYPE_F32)
+            run_step, launch_mode = graph.replay, f"CUDA graph replay of the step ({nseg} matmuls)"
+        except Exception as e:  # capture not possible: keep the eager loop
+            launch_mode += f"; graph capture failed: {type(e).__name__}"
+            torch.cuda.synchronize()
     with ClockSampler(local) as clk:
-        ms = timed(lambda: step(x1, y1, 1, cs.DTYPE_F32), args.steps, max(3, args.warmup))
+        ms = timed(run_step, args.steps, max(3, args.warmup))
         # keep the sampler busy long enough to see the clocks under load
         t_end = time.time() + 1.0
         while time.time() < t_end:
-            step(x1, y1, 1, cs.DTYPE_F32)
-        ctx.synchronize()
+            with torch.cuda.stream(stream):
+                run_step()
+            ctx.synchronize()
     launches = None
     value = bytes1 * nseg * args.steps * world / (ms / 1e3) / 1e9
     # launch count of exactly the timed region
@@ -260,16 +274,57 @@ def main():
             step(x1, y1, 1, cs.DTYPE_F32)
     prof = ctx.profile_read()
     ctx.profile(False)
-    n_dx, ms_dx = prof.get("hsdr_dx", (0, 0.0))
-    n_g, ms_g = prof.get("hsdr_gather", (0, 0.0))
-    dict_bytes = 4 * K * C + C * 4 + K * 4          # dictionary + x in, Dx out: the Dx kernel's share
-    dx_us = ms_dx / max(n_dx, 1) * 1e3
-    achieved = dict_bytes / (dx_us * 1e-6) / 1e9 if n_dx else None
-    roofline = {"bound": "hbm", "kernel": "hsdr_dx_kernel", "achieved": achieved, "peak": hbm_peak,
-                "unit": "GB/s", "frac": (achieved / hbm_peak) if achieved else None, "peak_source": peak_src,
-                "traffic": None, "alg_bytes_per_launch": dict_bytes, "us_per_launch": dx_us,
-                "gather_us_per_launch": ms_g / max(n_g, 1) * 1e3,
-                "whole_matmul_frac": value / world / hbm_peak}
+    if "hsdr_gemv_fused" in prof:
+        # one kernel per matmul: its launches overlap (programmatic dependent launch), so the
+        # per-launch duration is the timed region divided by the launches in it
+        us_launch = ms / args.steps / nseg * 1e3
+        achieved = bytes1 / (us_launch * 1e-6) / 1e9
+        n_f, ms_f = prof["hsdr_gemv_fused"]
+        roofline = {"bound": "hbm", "kernel": "hsdr_gemv_fused_kernel", "achieved": achieved, "peak": hbm_peak,
+                    "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
+                    "alg_bytes_per_launch": bytes1, "us_per_launch": us_launch,
+                    "us_per_launch_isolated": ms_f / max(n_f, 1) * 1e3,
+                    "note": "us_per_launch = timed region / launches (launches overlap); isolated = one "
+                            "launch bracketed by events, nothing overlapping it"}
+    else:
+        n_dx, ms_dx = prof.get("hsdr_dx", (0, 0.0))
+        n_g, ms_g = prof.get("hsdr_gather", (0, 0.0))
+        dict_bytes = 4 * K * C + C * 4 + K * 4      # dictionary + x in, Dx out: the Dx kernel's share
+        dx_us = ms_dx / max(n_dx, 1) * 1e3
+        achieved = dict_bytes / (dx_us * 1e-6) / 1e9 if n_dx else None
+        roofline = {"bound": "hbm", "kernel": "hsdr_dx_kernel", "achieved": achieved, "peak": hbm_peak,
+                    "unit": "GB/s", "frac": (achieved / hbm_peak) if achieved else None, "peak_source": peak_src,
+                    "traffic": None, "alg_bytes_per_launch": dict_bytes, "us_per_launch": dx_us,
+                    "gather_us_per_launch": ms_g / max(n_g, 1) * 1e3,
+                    "whole_matmul_frac": value / world / hbm_peak}
+
+    # ---- segments that share x (gate|up, q|k|v) in one launch ----
+    grouped = {}
+    for gsz in (2, 4):
+        if nseg % gsz:
+            continue
+        ptrs = [[y1[i + j].data_ptr() for j in range(gsz)] for i in range(0, nseg, gsz)]
+
+        def gstep():
+            for gi, i in enumerate(range(0, nseg, gsz)):
+                cs.Segment.matmul_group_device(segs[i:i + gsz], x1.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 1,
+                                               ptrs[gi], cs.TOKEN_MAJOR)
+        try:
+            gstep()
+            ctx.synchronize()
+            fn = gstep
+            if not args.no_graph:
+                gg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gg, stream=stream):
+                    gstep()
+                fn = gg.replay
+            gms = timed(fn, args.steps, 3)
+            gb = bytes1 * nseg * args.steps / (gms / 1e3) / 1e9
+            grouped[f"x{gsz}"] = {"GBps_compressed": gb, "frac_hbm": gb / hbm_peak,
+                                  "us_per_launch": gms / args.steps / (nseg // gsz) * 1e3}
+        except Exception as e:
+            grouped[f"x{gsz}"] = {"error": f"{type(e).__name__}: {e}"[:200]}
+            torch.cuda.synchronize()
 
     # ---- e2e: host buffers through the C-ABI (csdr_matmul), H2D + D2H inside the timed region ----
     xh = np.random.default_rng(3).normal(0, 1, (C, 1)).astype(np.float32)
@@ -318,10 +373,11 @@ def main():
             "config": {"workload": f"cfg2 MLP projection {R}x{C} HSDR row tiles K={K} {S}x{KPS}, GEMV batch 1",
                        "segments_per_step": nseg, "payload_bytes": len(pay),
                        "l2": f"{nseg} distinct device copies = {nseg * len(pay) / 1e6:.0f} MB per step > L2",
+                       "launch": launch_mode, "eager_ms_per_step": eager_ms / args.steps,
                        "parallelism": f"replicas x{world}"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
             "kernel_ms": {k: {"launches": v[0], "us_each": v[1] / v[0] * 1e3} for k, v in prof.items()},
-            "sweep": sweep}
+            "grouped_same_x": grouped, "sweep": sweep}
     if rank == 0:
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(pay)

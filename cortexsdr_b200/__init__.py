@@ -114,6 +114,15 @@ class Context:
                 out[name] = (int(n.value), float(ms.value))
             cls += 1
 
+    def gemv_trace(self, enable: bool = True):
+        """Phase stamps (ns) of the last fused-GEMV launch as an (n_ctas, 8) array, then set tracing."""
+        buf = np.zeros(16 * 2048, np.uint64)
+        n = C.c_size_t()
+        _check(self._lib.csdr_context_gemv_trace(self._h, 1 if enable else 0,
+                                                 buf.ctypes.data_as(C.POINTER(C.c_uint64)), buf.size,
+                                                 C.byref(n)))
+        return buf[:n.value].reshape(-1, 16)
+
     def close(self):
         if getattr(self, "_h", None):
             self._lib.csdr_context_destroy(self._h)
@@ -236,6 +245,17 @@ class Segment:
         _check(self.ctx._lib.csdr_matmul_device_async(
             self.ctx._h, self._h, C.c_void_p(x_ptr), x_dtype, x_layout, batch, C.c_void_p(y_ptr),
             y_layout, C.c_void_p(bias_ptr) if bias_ptr else None))
+
+    @staticmethod
+    def matmul_group_device(segs, x_ptr: int, x_dtype: int, x_layout: int, batch: int, y_ptrs,
+                            y_layout: int):
+        """Segments sharing one activation (q|k|v, gate|up) in as few launches as possible."""
+        ctx = segs[0].ctx
+        n = len(segs)
+        hs = (C.c_void_p * n)(*[s._h for s in segs])
+        ys = (C.c_void_p * n)(*[C.c_void_p(p) for p in y_ptrs])
+        _check(ctx._lib.csdr_matmul_group_device_async(ctx._h, hs, n, C.c_void_p(x_ptr), x_dtype,
+                                                       x_layout, batch, ys, y_layout))
 
     def decompress(self) -> np.ndarray:
         out = np.empty((self.rows, self.cols), np.float32)

@@ -71,6 +71,7 @@ SIGNATURES = {
     "csdr_context_profile_read": (C.c_int, [_P, C.c_int, C.POINTER(C.c_uint64),
                                             C.POINTER(C.c_double)]),
     "csdr_kernel_class_name": (C.c_char_p, [C.c_int]),
+    "csdr_context_gemv_trace": (C.c_int, [_P, C.c_int, C.POINTER(C.c_uint64), _SZ, C.POINTER(_SZ)]),
     "csdr_payload_inspect": (C.c_int, [_P, _SZ, C.POINTER(PayloadInfo)]),
     "csdr_segment_create": (C.c_int, [_P, _P, _SZ, C.POINTER(_P)]),
     "csdr_dictionary_create": (C.c_int, [_P, C.c_uint16, C.c_uint16, C.c_uint16, C.c_uint8,
@@ -83,6 +84,8 @@ SIGNATURES = {
     "csdr_unpack_codes": (C.c_int, [_P, _P, C.POINTER(C.c_int32), C.POINTER(C.c_int8), _SZ]),
     "csdr_matmul": (C.c_int, [_P, _P, _F, _SZ, _F, C.c_int]),
     "csdr_matmul_device_async": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _SZ, _P, C.c_int, _P]),
+    "csdr_matmul_group_device_async": (C.c_int, [_P, C.POINTER(_P), _SZ, _P, C.c_int, C.c_int, _SZ,
+                                                 C.POINTER(_P), C.c_int]),
     "csdr_decompress": (C.c_int, [_P, _P, _F, _SZ]),
     "csdr_decompress_device_async": (C.c_int, [_P, _P, _P]),
     "csdr_dequantize": (C.c_int, [_P, C.c_char_p, _P, _SZ, C.c_float, C.c_float, _F, _SZ,

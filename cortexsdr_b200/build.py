@@ -13,6 +13,7 @@ SOURCES = [
     "capi.cu",
     "kernels/matmul.cu",
     "kernels/decode.cu",
+    "kernels/gemv_fused.cu",
     "kernels/decoder_ops.cu",
     "kernels/gemm_tcgen05.cu",
     "decoder.cu",

@@ -1,10 +1,13 @@
 // extern "C" face of the CUDA layer: contexts, device images of compressed segments,
 // and the payload-level operations (unpack, fused matmul, decompress, dequantise).
 // Archive-level and decoder entry points live in host/archive.cpp and decoder.cu.
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
 #include "internal.hpp"
+#include "kernels/gemv_fused.hpp"
 
 namespace csdr {
 
@@ -57,7 +60,7 @@ DevPtr upload(csdr_context* ctx, const void* src, size_t bytes) {
 const char* kernel_class_name(int cls) {
     static const char* names[KC_COUNT] = {"hsdr_unpack", "hsdr_dx", "hsdr_gather", "hsdr_tile_project",
                                           "hsdr_tile_gather", "hsdr_edge", "dense_rows", "hsdr_decode_rows",
-                                          "dequant", "hsdr_gemm_tcgen05", "decoder_op"};
+                                          "dequant", "hsdr_gemm_tcgen05", "decoder_op", "hsdr_gemv_fused"};
     return (cls >= 0 && cls < KC_COUNT) ? names[cls] : "?";
 }
 
@@ -96,6 +99,8 @@ void* csdr_context::scratch_get(int slot, size_t bytes) {
         CSDR_CUDA(cudaStreamSynchronize(stream));
         scratch[slot].reset();
         scratch[slot] = std::make_shared<DeviceBuffer>(bytes, device);
+        // Fresh scratch starts at zero: the fused GEMV reads epoch tags from it, and 0 is never a tag.
+        CSDR_CUDA(cudaMemsetAsync(scratch[slot]->ptr, 0, bytes, stream));
     }
     return scratch[slot]->ptr;
 }
@@ -131,6 +136,9 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         }
         CSDR_CUDA(cudaMalloc(&ctx->status_word, sizeof(int)));
         CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
+        if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
         *out = ctx.release();
     });
 }
@@ -150,7 +158,17 @@ int csdr_context_destroy(csdr_context* ctx) {
 int csdr_context_synchronize(csdr_context* ctx) {
     return guard([&] {
         require_ctx(ctx);
+        int status = 0;
+        CSDR_CUDA(cudaMemcpyAsync(&status, ctx->status_word, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (status != 0) {
+            CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
+            CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+            throw Error(CSDR_ERR_TIMEOUT,
+                        "a device-side wait ran out (fused GEMV hand-over): results of the calls since "
+                        "the last synchronize are invalid; set CSDR_FUSED_GEMV=0 if the GPU is shared "
+                        "with long-running kernels");
+        }
     });
 }
 
@@ -187,6 +205,27 @@ int csdr_context_profile_read(csdr_context* ctx, int cls, uint64_t* launches, do
 }
 
 const char* csdr_kernel_class_name(int cls) { return kernel_class_name(cls); }
+
+int csdr_context_gemv_trace(csdr_context* ctx, int enable, uint64_t* out, size_t capacity, size_t* n_out) {
+    return guard([&] {
+        require_ctx(ctx);
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        const size_t words = static_cast<size_t>(ctx->sm_count) * 2u * 16u;
+        if (out && ctx->gemv_trace) {
+            const size_t n = std::min(capacity, words);
+            CSDR_CUDA(cudaMemcpy(out, ctx->gemv_trace->ptr, n * 8u, cudaMemcpyDeviceToHost));
+            if (n_out) *n_out = n;
+        } else if (n_out) {
+            *n_out = 0;
+        }
+        if (enable && !ctx->gemv_trace) {
+            ctx->gemv_trace = std::make_shared<DeviceBuffer>(words * 8u, ctx->device);
+            CSDR_CUDA(cudaMemset(ctx->gemv_trace->ptr, 0, words * 8u));
+        } else if (!enable) {
+            ctx->gemv_trace.reset();
+        }
+    });
+}
 
 void* csdr_context_stream(csdr_context* ctx) { return ctx ? ctx->stream : nullptr; }
 uint64_t csdr_context_launch_count(const csdr_context* ctx) { return ctx ? ctx->launches : 0; }
@@ -374,6 +413,51 @@ int csdr_matmul_device_async(csdr_context* ctx, const csdr_segment* seg, const v
         a.y_layout = y_layout;
         a.bias = bias_dev;
         launch_matmul(ctx, seg, a);
+    });
+}
+
+int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const* segs, size_t n_segs,
+                                   const void* x_dev, int x_dtype, int x_layout, size_t batch,
+                                   float* const* ys_dev, int y_layout) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!segs || !ys_dev || !x_dev || n_segs == 0) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (batch > 0xFFFFFFFFull) throw Error(CSDR_ERR_LIMIT, "batch too large");
+        for (size_t i = 0; i < n_segs; ++i) {
+            if (!segs[i] || !ys_dev[i]) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+            if (segs[i]->g.cols != segs[0]->g.cols)
+                throw Error(CSDR_ERR_GEOMETRY, "grouped matmul: every segment must consume the same activation width");
+        }
+        size_t done = 0;
+        while (done < n_segs) {
+            const uint32_t n = static_cast<uint32_t>(std::min<size_t>(kMaxFusedGroup, n_segs - done));
+            bool fused = true;
+            for (size_t b0 = 0; b0 < batch && fused; b0 += 16) {
+                const uint32_t m = static_cast<uint32_t>(std::min<size_t>(16, batch - b0));
+                const int mt = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16;
+                fused = gemv_fused_supported(ctx, segs + done, n, mt);
+            }
+            if (fused) {
+                for (size_t b0 = 0; b0 < batch; b0 += 16) {
+                    const uint32_t m = static_cast<uint32_t>(std::min<size_t>(16, batch - b0));
+                    const int mt = m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16;
+                    launch_gemv_fused(ctx, segs + done, n, x_dev, x_dtype, x_layout, static_cast<uint32_t>(batch),
+                                      static_cast<uint32_t>(b0), m, ys_dev + done, y_layout, nullptr, mt);
+                }
+            } else {
+                for (uint32_t i = 0; i < n; ++i) {
+                    MatmulArgs a;
+                    a.x = x_dev;
+                    a.x_dtype = x_dtype;
+                    a.x_layout = x_layout;
+                    a.batch = batch;
+                    a.y = ys_dev[done + i];
+                    a.y_layout = y_layout;
+                    launch_matmul(ctx, segs[done + i], a);
+                }
+            }
+            done += n;
+        }
     });
 }
 

@@ -8,6 +8,7 @@
 #include <nccl.h>
 
 #include <cstring>
+#include <initializer_list>
 #include <string>
 #include <vector>
 
@@ -171,6 +172,28 @@ void linear(csdr_decoder* d, const Linear& l, const float* x, uint32_t T, float*
     }
 }
 
+// Several linears over the same x in as few launches as the matmul layer allows.
+void linear_group(csdr_decoder* d, std::initializer_list<const Linear*> ls, const float* x, uint32_t T,
+                  std::initializer_list<float*> ys) {
+    bool all_hsdr = true;
+    for (const Linear* l : ls) all_hsdr = all_hsdr && !l->raw;
+    if (!all_hsdr) {
+        auto y = ys.begin();
+        for (const Linear* l : ls) linear(d, *l, x, T, *y++);
+        return;
+    }
+    const csdr_segment* segs[8];
+    float* outs[8];
+    size_t n = 0;
+    auto y = ys.begin();
+    for (const Linear* l : ls) {
+        segs[n] = l->use();
+        outs[n++] = *y++;
+    }
+    rethrow_last(csdr_matmul_group_device_async(d->ctx, segs, n, x, CSDR_DTYPE_F32, CSDR_LAYOUT_TOKEN_MAJOR, T, outs,
+                                                CSDR_LAYOUT_TOKEN_MAJOR));
+}
+
 // Rejoin row shards: local (T x W) on every rank -> full (T x P*W), replicated.
 void rejoin(csdr_decoder* d, const float* local, uint32_t T, uint32_t W, float* full, bool add) {
     nccl_check(nccl().AllGather(local, F(d->staged), static_cast<size_t>(T) * W, ncclFloat, d->comm, d->ctx->stream),
@@ -193,9 +216,7 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
     op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, F(d->normed));
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         Layer& L = d->layers[li];
-        linear(d, L.q, F(d->normed), T, F(d->q));
-        linear(d, L.k, F(d->normed), T, F(d->k));
-        linear(d, L.v, F(d->normed), T, F(d->v));
+        linear_group(d, {&L.q, &L.k, &L.v}, F(d->normed), T, {F(d->q), F(d->k), F(d->v)});
         float* kc = F(d->kcache) + li * d->cache_layer_stride;
         float* vc = F(d->vcache) + li * d->cache_layer_stride;
         op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
@@ -213,8 +234,7 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
         } else {
             op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
         }
-        linear(d, L.gate, F(d->normed), T, F(d->gate));
-        linear(d, L.up, F(d->normed), T, F(d->up));
+        linear_group(d, {&L.gate, &L.up}, F(d->normed), T, {F(d->gate), F(d->up)});
         op_silu_mul(ctx, F(d->gate), F(d->up), static_cast<size_t>(T) * d->I_l, F(d->gate));
         const float* act = F(d->gate);
         if (tp) {

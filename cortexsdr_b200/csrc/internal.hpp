@@ -78,7 +78,7 @@ namespace csdr {
 // Kernel classes for launch counting and optional per-class device timing.
 enum KernelClass {
     KC_UNPACK = 0, KC_DX, KC_GATHER, KC_TILE_PROJECT, KC_TILE_GATHER, KC_EDGE, KC_DENSE,
-    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_COUNT
+    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_GEMV_FUSED, KC_COUNT
 };
 const char* kernel_class_name(int cls);
 struct TimedLaunch {
@@ -95,9 +95,14 @@ struct csdr_context {
     size_t smem_optin = 0;
     uint64_t launches = 0;
     // Grow-only scratch (Dx partials, factored 2-D products, host staging).
-    csdr::DevPtr scratch[4];
+    csdr::DevPtr scratch[6];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials
     void* scratch_get(int slot, size_t bytes);
     int* status_word = nullptr;  // device int: kernels record bounded-wait timeouts here
+    // Fused GEMV: every launch tags its partial results with a fresh non-zero epoch.
+    uint32_t gemv_epoch = 0;
+    csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
+    bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
+    bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
     uint64_t launches_by_class[csdr::KC_COUNT] = {};
     // When on, every launch is bracketed by two events on the stream (profile_read resolves them).
     bool profiling = false;

@@ -17,6 +17,8 @@
 #include <algorithm>
 
 #include "../internal.hpp"
+#include "gemv_fused.hpp"
+#include "views.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -27,50 +29,6 @@ namespace {
 // ---------------------------------------------------------------------------
 // helpers
 // ---------------------------------------------------------------------------
-
-// Streaming 128-bit load: the dictionary is read once per launch, keep it out of L1.
-__device__ __forceinline__ float4 ldg_stream_f4(const float4* p) {
-    float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(p));
-    return v;
-}
-
-struct XView {
-    const void* x;
-    int dtype;       // CSDR_DTYPE_*
-    int layout;      // CSDR_LAYOUT_*
-    uint32_t C;      // features
-    uint32_t Mtotal; // tokens in the whole activation matrix
-    uint32_t b0;     // first token of this launch's chunk
-    uint32_t M;      // tokens in this chunk (<= MT)
-};
-
-__device__ __forceinline__ float load_x(const XView& v, uint32_t c, uint32_t b) {
-    const size_t i = v.layout == CSDR_LAYOUT_FEATURE_MAJOR
-                         ? static_cast<size_t>(c) * v.Mtotal + (v.b0 + b)
-                         : static_cast<size_t>(v.b0 + b) * v.C + c;
-    if (v.dtype == CSDR_DTYPE_BF16)
-        return __bfloat162float(static_cast<const __nv_bfloat16*>(v.x)[i]);
-    return static_cast<const float*>(v.x)[i];
-}
-
-struct YView {
-    float* y;
-    int layout;
-    uint32_t R;
-    uint32_t Mtotal;
-    uint32_t b0;
-    uint32_t M;
-    const float* bias;
-};
-
-__device__ __forceinline__ size_t y_index(const YView& v, uint32_t r, uint32_t b) {
-    return v.layout == CSDR_LAYOUT_FEATURE_MAJOR
-               ? static_cast<size_t>(r) * v.Mtotal + (v.b0 + b)
-               : static_cast<size_t>(v.b0 + b) * v.R + r;
-}
 
 // ---------------------------------------------------------------------------
 // K1: unpack. 8 codes per 128-bit load; indices leave as two 128-bit stores, signs
@@ -681,7 +639,12 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
         YView yv{a.y, a.y_layout, g.rows, static_cast<uint32_t>(a.batch), static_cast<uint32_t>(b0), m, a.bias};
         dispatch_mt(pick_mt(m), [&](auto mt) {
             constexpr int MT = decltype(mt)::value;
-            if (fast_rows) matmul_rowtiles_chunk<MT>(ctx, seg, xv, yv);
+            if (fast_rows && gemv_fused_supported(ctx, &seg, 1, MT)) {
+                float* yp = a.y;
+                const float* bp = a.bias;
+                launch_gemv_fused(ctx, &seg, 1, a.x, a.x_dtype, a.x_layout, static_cast<uint32_t>(a.batch),
+                                  static_cast<uint32_t>(b0), m, &yp, a.y_layout, a.bias ? &bp : nullptr, MT);
+            } else if (fast_rows) matmul_rowtiles_chunk<MT>(ctx, seg, xv, yv);
             else if constexpr (MT <= 4) matmul_tiles_chunk<MT>(ctx, seg, xv, yv);
         });
     }

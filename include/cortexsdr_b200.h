@@ -101,6 +101,14 @@ CSDR_API int csdr_context_profile(csdr_context* ctx, int enable);
 CSDR_API int csdr_context_profile_read(csdr_context* ctx, int cls, uint64_t* launches,
                                        double* total_ms);
 CSDR_API const char* csdr_kernel_class_name(int cls); /* "?" past the last class */
+/* Phase timeline of the fused decode GEMV, for tuning. While enabled, thread 0 of every CTA
+ * of each fused-GEMV launch stores global-timer stamps (ns) in 16 slots: 0 start, 1 weights
+ * requested, 2 dependency wait over, 3 activations staged, 4 projection published, 5 hand-over
+ * seen, 6 first gather done, 7 end, 8 products done, 9 partials stored, 10 CTA joined; the rest
+ * unused. The call first copies the stamps of the LAST launch to `out` (16 words per CTA, may
+ * be NULL), then applies `enable`. */
+CSDR_API int csdr_context_gemv_trace(csdr_context* ctx, int enable, uint64_t* out, size_t capacity,
+                                     size_t* n_out);
 
 /* ---- payload framing (host only) ----
  * Replaces the header parse + checks at the top of matmulRowMajor / decompress
@@ -156,6 +164,16 @@ CSDR_API int csdr_matmul_device_async(csdr_context* ctx, const csdr_segment* seg
                                       const void* x_dev, int x_dtype, int x_layout,
                                       size_t batch, float* y_dev, int y_layout,
                                       const float* bias_dev);
+
+/* Several compressed weights that consume the SAME activations (q|k|v, gate|up) in as few
+ * launches as possible: 1-D row-tile segments of equal column count share one kernel,
+ * anything else is issued segment by segment. ys_dev[i] receives segment i's product.
+ * The reference issues these as separate matmulHSDR calls
+ * (api/cortex_sdk.cpp:1578-1583, :1653-1656). */
+CSDR_API int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const* segs,
+                                            size_t n_segs, const void* x_dev, int x_dtype,
+                                            int x_layout, size_t batch, float* const* ys_dev,
+                                            int y_layout);
 
 /* ---- materialise the weight ----
  * HierarchicalSDRStrategy::decompress (:1340) / ::decompressWithExternalDictionary

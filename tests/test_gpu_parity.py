@@ -225,3 +225,62 @@ def test_row_shards_concatenate_to_whole(ctx, oracle, golden):
     assert np.array_equal(np.concatenate(parts2, 0), whole2)
     with pytest.raises(cs.CompressionError, match="tile-row boundaries"):
         seg2.shard_rows(0, 40)
+
+
+def test_grouped_matmul_matches_single_calls(ctx, oracle, golden):
+    import torch
+    from cortexsdr_b200 import synth
+    pays = [synth.hsdr_payload(r, 512, n_atoms=k, k=4, seed=40 + i) for i, (r, k) in enumerate(((256, 64), (96, 32), (130, 64)))]
+    segs = [cs.Segment.from_payload(p, ctx) for p in pays]
+    rng = np.random.default_rng(9)
+    for batch in (1, 5, 16, 21):
+        x = torch.from_numpy(rng.normal(0, 1, (batch, 512)).astype(np.float32)).cuda()
+        ys = [torch.zeros((batch, s.rows), device="cuda") for s in segs]
+        torch.cuda.synchronize()
+        cs.Segment.matmul_group_device(segs, x.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, batch,
+                                       [y.data_ptr() for y in ys], cs.TOKEN_MAJOR)
+        ctx.synchronize()
+        for p, y in zip(pays, ys):
+            want = oracle.matmul(p, np.ascontiguousarray(x.cpu().numpy().T), batch).T
+            e = rel_err(y.cpu().numpy(), want)
+            assert e[0] < TOL and e[1] < TOL, (batch, e)
+
+
+def test_fused_and_two_kernel_paths_agree(lib, oracle, golden, monkeypatch):
+    g = golden("fused_rowtile.npz")
+    x = np.random.default_rng(5).normal(0, 1, (512, 9)).astype(np.float32)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("CSDR_FUSED_GEMV", flag)
+        c = cs.Context(0)
+        seg = cs.Segment.from_payload(g["payload"], c)
+        outs.append(seg.matmul(x, 9))
+        seg.close()
+        c.close()
+    want = oracle.matmul(g["payload"], x, 9)
+    for y in outs:
+        e = rel_err(y, want)
+        assert e[0] < TOL and e[1] < TOL
+    assert np.abs(outs[0] - outs[1]).max() < 1e-5
+
+
+def test_chained_launches_are_ordered(ctx, oracle, golden):
+    # y of one launch feeds the next as x: the dependent launch must see the finished result
+    import torch
+    from cortexsdr_b200 import synth
+    p1 = synth.hsdr_payload(512, 512, n_atoms=64, k=4, seed=70)
+    p2 = synth.hsdr_payload(512, 512, n_atoms=64, k=4, seed=71)
+    s1, s2 = cs.Segment.from_payload(p1, ctx), cs.Segment.from_payload(p2, ctx)
+    x0 = np.random.default_rng(6).normal(0, 1, (1, 512)).astype(np.float32)
+    a = torch.from_numpy(x0).cuda()
+    b = torch.empty_like(a)
+    torch.cuda.synchronize()
+    for _ in range(6):
+        s1.matmul_device(a.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 1, b.data_ptr(), cs.TOKEN_MAJOR)
+        s2.matmul_device(b.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 1, a.data_ptr(), cs.TOKEN_MAJOR)
+    ctx.synchronize()
+    v = x0.T.copy()
+    for _ in range(6):
+        v = oracle.matmul(p2, oracle.matmul(p1, v, 1), 1)
+    e = rel_err(a.cpu().numpy().T, v)
+    assert e[0] < 1e-3, e
