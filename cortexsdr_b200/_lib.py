@@ -86,6 +86,8 @@ SIGNATURES = {
     "csdr_matmul_device_async": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _SZ, _P, C.c_int, _P]),
     "csdr_matmul_group_device_async": (C.c_int, [_P, C.POINTER(_P), _SZ, _P, C.c_int, C.c_int, _SZ,
                                                  C.POINTER(_P), C.c_int]),
+    "csdr_matmul_rowtiles_noalloc": (C.c_int, [_P, _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                               C.c_uint32, _P, C.c_int, C.c_int, _SZ, _P, C.c_int, _P]),
     "csdr_decompress": (C.c_int, [_P, _P, _F, _SZ]),
     "csdr_decompress_device_async": (C.c_int, [_P, _P, _P]),
     "csdr_dequantize": (C.c_int, [_P, C.c_char_p, _P, _SZ, C.c_float, C.c_float, _F, _SZ,

@@ -651,3 +651,153 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
 }
 
 }  // namespace csdr
+
+// ---------------------------------------------------------------------------
+// Allocation-free entry point.
+//
+// Some hosts of this library may not call cudaMalloc at all once they are running: a
+// real-time or safety-certified process that fixes its device memory map at start-up, a
+// plug-in living inside another runtime's memory pool, or code running while a stream is
+// being captured, where an allocation is an error. csdr_matmul_rowtiles_noalloc serves them:
+// the row-tile product through the two-kernel path (projection, then gather), with the one
+// piece of scratch that path needs - Dx, n_atoms x 16 floats - in a fixed array that lives
+// in the library's device image instead of coming from the allocator.
+// ---------------------------------------------------------------------------
+namespace csdr {
+namespace {
+
+constexpr uint32_t kNoAllocMaxAtoms = 4096;  // 4096 atoms x 16 tokens x 4 B = 256 KiB per GPU
+constexpr uint32_t kNoAllocTokens = 16;
+constexpr int kNoAllocMaxDevices = 64;
+
+// Held by every GPU that loads the library, until the process exits. Host code may name
+// this array only to ask for its address: the symbol itself is not a device pointer.
+static __device__ __align__(256) float g_noalloc_dx[kNoAllocMaxAtoms * kNoAllocTokens];
+
+// Device address of the array on `device`, which must be current. Looked up once per device.
+float* noalloc_scratch(int device) {
+    static float* addr[kNoAllocMaxDevices] = {};
+    static std::mutex mu;
+    if (device < 0 || device >= kNoAllocMaxDevices) throw Error(CSDR_ERR_LIMIT, "device index beyond 63");
+    std::lock_guard<std::mutex> lk(mu);
+    if (!addr[device]) {
+        float* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dx);
+        if (e != cudaSuccess || !p)
+            throw Error(CSDR_ERR_CUDA, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(e));
+        addr[device] = p;
+    }
+    return addr[device];
+}
+
+template <typename Kern>
+void noalloc_smem(Kern kern, size_t bytes) {
+    if (bytes > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(bytes));
+        if (e != cudaSuccess) throw Error(CSDR_ERR_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+    }
+}
+
+void noalloc_check(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) throw Error(CSDR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+template <int MT, int A, int U>
+void noalloc_chunk(const float* D, const uint16_t* codes, const float* scales, uint32_t R, uint32_t C,
+                   uint32_t K, uint32_t S, uint32_t k, const XView& xv, const YView& yv, float* dx,
+                   int sm_count, cudaStream_t stream) {
+    uint32_t nsplit = std::min<uint32_t>(8u, std::max<uint32_t>(1u, (C + 1023u) / 1024u));
+    const uint32_t slab = ((C + nsplit - 1u) / nsplit + 3u) & ~3u;
+    nsplit = (C + slab - 1u) / slab;
+    {
+        auto kern = hsdr_dx_kernel<MT, A, U>;
+        const size_t smem = (static_cast<size_t>(MT) * slab + 8u * A * MT) * sizeof(float);
+        noalloc_smem(kern, smem);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(nsplit, (K + 8u * A - 1u) / (8u * A), 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = nsplit;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, D, K, C, slab, xv, dx, static_cast<int>(nsplit));
+        if (e != cudaSuccess) throw Error(CSDR_ERR_CUDA, std::string("hsdr_dx_kernel: ") + cudaGetErrorString(e));
+    }
+    {
+        constexpr uint32_t RP = kGatherThreads / MT;
+        uint32_t rows_per_cta = (R + 4u * sm_count - 1u) / (4u * sm_count);
+        rows_per_cta = std::max(RP, (rows_per_cta + RP - 1u) / RP * RP);
+        const uint32_t slots = S * k;
+        const size_t cap16 = (static_cast<size_t>(rows_per_cta) * slots * 2u + 31u) >> 4;
+        const size_t base = cap16 * 16u + ((S + 3u) & ~3u) * sizeof(float);
+        const size_t dx_bytes = static_cast<size_t>(K) * MT * sizeof(float);
+        const int dx_in_smem = base + dx_bytes <= 160u * 1024u;
+        const size_t smem = base + (dx_in_smem ? dx_bytes : 0u);
+        auto kern = hsdr_gather_kernel<MT>;
+        noalloc_smem(kern, smem);
+        kern<<<(R + rows_per_cta - 1u) / rows_per_cta, kGatherThreads, smem, stream>>>(
+            codes, R, S, k, scales, dx, K, rows_per_cta, dx_in_smem, yv);
+        noalloc_check("hsdr_gather_kernel");
+    }
+}
+
+}  // namespace
+}  // namespace csdr
+
+extern "C" int csdr_matmul_rowtiles_noalloc(const float* dict_dev, const uint16_t* codes_dev,
+                                            const float* scales_dev, uint32_t rows, uint32_t cols,
+                                            uint32_t n_atoms, uint32_t n_stages, uint32_t k_per_stage,
+                                            const void* x_dev, int x_dtype, int x_layout, size_t batch,
+                                            float* y_dev, int y_layout, void* stream) {
+    using namespace csdr;
+    return guard([&] {
+        if (!dict_dev || !codes_dev || !scales_dev || !x_dev || !y_dev)
+            throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (!rows || !cols || !n_atoms || !n_stages || !k_per_stage)
+            throw Error(CSDR_ERR_INVALID_ARG, "zero-sized geometry field");
+        if (n_atoms > kNoAllocMaxAtoms)
+            throw Error(CSDR_ERR_LIMIT, "csdr_matmul_rowtiles_noalloc: n_atoms " + std::to_string(n_atoms) +
+                                            " exceeds the fixed scratch of " + std::to_string(kNoAllocMaxAtoms) +
+                                            " atoms; use csdr_matmul_device_async");
+        if (n_atoms > 0x7FFFu || cols > 0xFFFFu || (cols & 3u))
+            throw Error(CSDR_ERR_LIMIT, "csdr_matmul_rowtiles_noalloc: cols must be a multiple of 4 and at most 65535");
+        if (batch > 0xFFFFFFFFull) throw Error(CSDR_ERR_LIMIT, "batch too large");
+        if ((reinterpret_cast<uintptr_t>(dict_dev) | reinterpret_cast<uintptr_t>(codes_dev)) & 15u)
+            throw Error(CSDR_ERR_INVALID_ARG, "dictionary and code stream must be 16-byte aligned");
+        if ((x_dtype != CSDR_DTYPE_F32 && x_dtype != CSDR_DTYPE_BF16) ||
+            (x_layout != CSDR_LAYOUT_FEATURE_MAJOR && x_layout != CSDR_LAYOUT_TOKEN_MAJOR) ||
+            (y_layout != CSDR_LAYOUT_FEATURE_MAJOR && y_layout != CSDR_LAYOUT_TOKEN_MAJOR))
+            throw Error(CSDR_ERR_INVALID_ARG, "unknown dtype or layout");
+        if (batch == 0) return;
+        int device = 0, sm_count = 0;
+        CSDR_CUDA(cudaGetDevice(&device));
+        CSDR_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+        float* dx = noalloc_scratch(device);  // first call on a device looks the address up
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        // token tile: the widest power of two <= 16 whose x slab fits in 200 KiB of shared memory
+        uint32_t nsplit = std::min<uint32_t>(8u, std::max<uint32_t>(1u, (cols + 1023u) / 1024u));
+        const uint32_t slab = ((cols + nsplit - 1u) / nsplit + 3u) & ~3u;
+        const int mt_cap = fit_mt(16, 0, (static_cast<size_t>(slab) + 32u) * sizeof(float), 200u * 1024u);
+        if (mt_cap == 0) throw Error(CSDR_ERR_LIMIT, "csdr_matmul_rowtiles_noalloc: row too wide for shared memory");
+        for (size_t b0 = 0; b0 < batch; b0 += mt_cap) {
+            const uint32_t m = static_cast<uint32_t>(std::min<size_t>(mt_cap, batch - b0));
+            XView xv{x_dev, x_dtype, x_layout, cols, static_cast<uint32_t>(batch), static_cast<uint32_t>(b0), m};
+            YView yv{y_dev, y_layout, rows, static_cast<uint32_t>(batch), static_cast<uint32_t>(b0), m, nullptr};
+            switch (pick_mt(m)) {
+                case 1: noalloc_chunk<1, 1, 8>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
+                case 2: noalloc_chunk<2, 1, 8>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
+                case 4: noalloc_chunk<4, 2, 4>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
+                case 8: noalloc_chunk<8, 4, 2>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
+                default: noalloc_chunk<16, 4, 2>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
+            }
+        }
+    });
+}
+

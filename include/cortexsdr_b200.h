@@ -175,6 +175,36 @@ CSDR_API int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segmen
                                             int x_layout, size_t batch, float* const* ys_dev,
                                             int y_layout);
 
+/* The same row-tile product for callers that must not allocate. No counterpart in the
+ * reference: it exists for hosts that cannot call cudaMalloc while they run - a process
+ * whose device memory map is frozen after start-up (real-time or certified systems), a
+ * plug-in that lives inside another runtime's memory pool, or code inside a stream capture,
+ * where allocating is an error. This call allocates nothing, on the host or the device: no
+ * cudaMalloc, no cudaFree, no library routine that allocates. Every buffer is the caller's,
+ * as raw device pointers taken straight from a payload's streams:
+ *   dict_dev    n_atoms x cols fp32 (the "HSDR" dictionary stream), 16-byte aligned
+ *   codes_dev   rows x n_stages x k_per_stage packed u16 codes, 16-byte aligned, in an
+ *               allocation whose length is rounded up to 16 bytes (kernels read it in
+ *               128-bit units); every code must name an atom < n_atoms (csdr_payload_inspect
+ *               checks that on the host)
+ *   scales_dev  n_stages fp32
+ *   x_dev/y_dev activations and fp32 output, dtype and layouts as for csdr_matmul_device_async
+ * The one piece of scratch the two-kernel path needs (Dx, n_atoms x 16 floats) sits in a
+ * fixed array inside the library's device image: 256 KiB, held by every GPU that loads the
+ * library until the process exits. Hence the limit: n_atoms <= 4096 (CSDR_ERR_LIMIT beyond
+ * it), 1-D row tiles only, cols a multiple of 4. The first call on a device looks up the
+ * array's device address (that device must be current, as for every call); make that first
+ * call before starting any stream capture. All calls share the array, and it keeps the last
+ * call's contents (nothing in it needs clearing: each call overwrites what it reads): calls
+ * that overlap on the GPU - different streams, or captured graphs replayed side by side -
+ * race on it; calls on one stream are ordered and safe. Asynchronous on `stream`
+ * (a cudaStream_t; NULL is the default stream). */
+CSDR_API int csdr_matmul_rowtiles_noalloc(const float* dict_dev, const uint16_t* codes_dev,
+                                          const float* scales_dev, uint32_t rows, uint32_t cols,
+                                          uint32_t n_atoms, uint32_t n_stages, uint32_t k_per_stage,
+                                          const void* x_dev, int x_dtype, int x_layout, size_t batch,
+                                          float* y_dev, int y_layout, void* stream);
+
 /* ---- materialise the weight ----
  * HierarchicalSDRStrategy::decompress (:1340) / ::decompressWithExternalDictionary
  * (:1804): fp32 (rows x cols) row-major, edge strips spliced back. */
