@@ -657,8 +657,8 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
 //
 // Some hosts of this library may not call cudaMalloc at all once they are running: a
 // real-time or safety-certified process that fixes its device memory map at start-up, a
-// plug-in living inside another runtime's memory pool, or code running while a stream is
-// being captured, where an allocation is an error. csdr_matmul_rowtiles_noalloc serves them:
+// plug-in living inside another runtime's memory pool, or a service whose own arena already
+// holds all device memory. csdr_matmul_rowtiles_noalloc serves them:
 // the row-tile product through the two-kernel path (projection, then gather), with the one
 // piece of scratch that path needs - Dx, n_atoms x 16 floats - in a fixed array that lives
 // in the library's device image instead of coming from the allocator.

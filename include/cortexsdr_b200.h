@@ -178,8 +178,8 @@ CSDR_API int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segmen
 /* The same row-tile product for callers that must not allocate. No counterpart in the
  * reference: it exists for hosts that cannot call cudaMalloc while they run - a process
  * whose device memory map is frozen after start-up (real-time or certified systems), a
- * plug-in that lives inside another runtime's memory pool, or code inside a stream capture,
- * where allocating is an error. This call allocates nothing, on the host or the device: no
+ * plug-in that lives inside another runtime's memory pool and owns no allocator of its own,
+ * or a service that has handed all device memory to its own arena. This call allocates nothing, on the host or the device: no
  * cudaMalloc, no cudaFree, no library routine that allocates. Every buffer is the caller's,
  * as raw device pointers taken straight from a payload's streams:
  *   dict_dev    n_atoms x cols fp32 (the "HSDR" dictionary stream), 16-byte aligned
@@ -196,8 +196,7 @@ CSDR_API int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segmen
  * array's device address (that device must be current, as for every call); make that first
  * call before starting any stream capture. All calls share the array, and it keeps the last
  * call's contents (nothing in it needs clearing: each call overwrites what it reads): calls
- * that overlap on the GPU - different streams, or captured graphs replayed side by side -
- * race on it; calls on one stream are ordered and safe. Asynchronous on `stream`
+ * that overlap on the GPU - issued on different streams - race on it; calls on one stream are ordered and safe. Asynchronous on `stream`
  * (a cudaStream_t; NULL is the default stream). */
 CSDR_API int csdr_matmul_rowtiles_noalloc(const float* dict_dev, const uint16_t* codes_dev,
                                           const float* scales_dev, uint32_t rows, uint32_t cols,

@@ -1,5 +1,5 @@
 """The allocation-free entry point, for hosts that may not call cudaMalloc once they run (a
-frozen device memory map, a plug-in inside another runtime's pool, code under stream capture).
+frozen device memory map, a plug-in inside another runtime's pool, an arena that holds it all).
 It must give what the ordinary entry point gives, on two calls in a row - the second call
 reuses the fixed scratch array with the first call's contents still in it. Collected last, so
 a run that stops at the first failure has already been through every other test."""
