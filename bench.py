@@ -129,6 +129,89 @@ def cpu_baseline(pay: bytes, iters: int = 7):
             "ms_per_matmul": sec * 1e3}
 
 
+DECODERS = {
+    # config 3: Qwen2-0.5B shape, batch 1, 512-token prompt then 128 greedy steps
+    "qwen0.5b": dict(cfg=dict(n_layers=24, hidden=896, q_heads=14, kv_heads=2, head_dim=64, inter=4864,
+                              vocab=151936), kv_atoms=128, batch=1, context=512, steps=128, eps=1e-6, prefill=True),
+    # config 4: Llama-7B shape, batch 16 at context 1024
+    "llama7b": dict(cfg=dict(n_layers=32, hidden=4096, q_heads=32, kv_heads=32, head_dim=128, inter=11008,
+                             vocab=32000), kv_atoms=None, batch=16, context=1024, steps=32, eps=1e-5, prefill=False),
+}
+
+
+def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True):
+    """Decode tokens/s of a decoder-shaped synthetic archive (every linear an HSDR row-tile segment
+    with its own dictionary, K=512 3x8; random-init stand-in for the config's weights)."""
+    from cortexsdr_b200 import synth
+    spec = DECODERS[name]
+    cfg = spec["cfg"]
+    os.makedirs(CACHE, exist_ok=True)
+    path = os.path.join(CACHE, f"{name}.sdr")
+    if rank == 0 and not os.path.exists(path):
+        synth.decoder_archive(path + ".tmp", **cfg, kv_atoms=spec["kv_atoms"], seed=100)
+        os.replace(path + ".tmp", path)
+    if world > 1:
+        dist.barrier()
+    B, ctxlen, steps = spec["batch"], spec["context"], spec["steps"]
+    ld = cs.SDRModelLoader(path, ctx)
+    dec = cs.Decoder(ld, **cfg, max_seq=ctxlen + steps + 8, max_batch=B, rms_eps=spec["eps"], comm=comm)
+    rng = np.random.default_rng(7)
+    out = {"batch": B, "context": ctxlen, "steps": steps, "tp": world}
+    with torch.cuda.stream(stream):
+        if spec["prefill"]:
+            prompt = rng.integers(0, cfg["vocab"], ctxlen)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            logits, _ = dec.forward(prompt, seq=0)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            out["prefill_ms"] = e0.elapsed_time(e1)
+            first = np.array([int(logits.argmax())], np.int32)
+        else:
+            for b in range(B):          # context without prefill: the cache rows below hold zeros;
+                dec.seek(b, ctxlen)     # decode cost does not depend on their content
+            first = rng.integers(0, cfg["vocab"], B).astype(np.int32)
+            out["note"] = "KV cache positioned at the context length without a prefill pass"
+        tok = torch.from_numpy(first).cuda()
+        torch.cuda.synchronize()
+
+        def one():
+            dec.step_device(tok.data_ptr(), B, tok.data_ptr())   # greedy token fed straight back
+        for _ in range(3):
+            one()
+        ctx.synchronize()
+        mode, run = "eager", one
+        if use_graph:
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    one()
+                mode, run = "cuda graph", g.replay
+            except Exception as e:
+                mode = f"eager (graph capture failed: {type(e).__name__})"
+                torch.cuda.synchronize()
+        run()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = steps - 5
+        e0.record(stream)
+        for _ in range(n):
+            run()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    out.update(launch=mode, ms_per_step=ms / n, tokens_per_s=B * n / (ms / 1e3))
+    dec.close()
+    ld.close()
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -177,6 +260,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--decoder", default="qwen0.5b,llama7b", help="comma list of decoder shapes to time, or none")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -366,6 +450,28 @@ def main():
             sweep[f"M{m}"] = ent
             del xm, ym
 
+    # ---- decoder-shaped decode tokens/s (tensor-parallel over the ranks when world > 1) ----
+    decode = {}
+    for s_ in segs:
+        s_.close()
+    segs.clear()
+    del y1
+    torch.cuda.empty_cache()
+    comm = None
+    if world > 1:
+        ids = [cs.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = cs.NcclComm(ctx, ids[0], rank, world)
+    for name in [n for n in args.decoder.split(",") if n and n != "none"]:
+        try:
+            if DECODERS[name]["cfg"]["kv_heads"] % world:
+                decode[name] = {"skipped": f"{DECODERS[name]['cfg']['kv_heads']} kv heads do not divide over {world} ranks"}
+                continue
+            decode[name] = decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, not args.no_graph)
+        except Exception as e:
+            decode[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            torch.cuda.synchronize()
+
     line = {"metric": "compressed_weight_matmul_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -377,7 +483,7 @@ def main():
                        "parallelism": f"replicas x{world}"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
             "kernel_ms": {k: {"launches": v[0], "us_each": v[1] / v[0] * 1e3} for k, v in prof.items()},
-            "grouped_same_x": grouped, "sweep": sweep}
+            "grouped_same_x": grouped, "sweep": sweep, "decode_tokens_per_s": decode}
     if rank == 0:
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(pay)

@@ -20,6 +20,7 @@ All arithmetic runs on the GPU; nothing here falls back to the CPU.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from dataclasses import dataclass
 
 import numpy as np
@@ -30,7 +31,7 @@ from ._lib import (DTYPE_BF16, DTYPE_F32, FEATURE_MAJOR, TOKEN_MAJOR, DecoderCon
 
 __all__ = ["CompressionError", "Context", "Segment", "Dictionary", "HierarchicalSDRStrategy",
            "SDRModelLoader", "SDRInferenceEngine", "HSDAReader", "Decoder", "default_context",
-           "HSDR_STRATEGY_ID"]
+           "HSDR_STRATEGY_ID", "NcclComm", "nccl_unique_id"]
 
 HSDR_STRATEGY_ID = 5
 
@@ -85,6 +86,12 @@ class Context:
         _check(self._lib.csdr_context_create(device, C.c_void_p(stream) if stream else None,
                                              C.byref(h)))
         self._h = h
+        # Everything created on this context; closed before the context itself, whatever order
+        # the interpreter finalises objects in (at shutdown the cyclic collector picks any).
+        self._children = weakref.WeakSet()
+
+    def _adopt(self, child):
+        self._children.add(child)
 
     def synchronize(self):
         _check(self._lib.csdr_context_synchronize(self._h))
@@ -125,6 +132,11 @@ class Context:
 
     def close(self):
         if getattr(self, "_h", None):
+            for child in sorted(list(self._children), key=lambda c: getattr(c, "_close_rank", 1)):
+                try:
+                    child.close()
+                except Exception:
+                    pass
             self._lib.csdr_context_destroy(self._h)
             self._h = None
 
@@ -141,6 +153,9 @@ class _NoDevice:
     def __init__(self):
         self._lib = _lib.load()
         self._h = None
+
+    def _adopt(self, child):
+        pass
 
 
 _default_ctx: Context | None = None
@@ -173,11 +188,12 @@ class Dictionary:
         _check(ctx._lib.csdr_dictionary_create(ctx._h, tile_rows, tile_cols, n_atoms, n_stages, k,
                                                _fp(atoms), _fp(scales), C.byref(h)))
         self._h = h
+        ctx._adopt(self)
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and self.ctx._h:
             self.ctx._lib.csdr_dictionary_destroy(self._h)
-            self._h = None
+        self._h = None
 
     def __del__(self):
         try:
@@ -191,6 +207,8 @@ class Segment:
 
     def __init__(self, ctx: Context, handle, owned=True, keep=None):
         self.ctx, self._h, self._owned, self._keep = ctx, handle, owned, keep
+        self._close_rank = 0          # segments and shards go first
+        ctx._adopt(self)
         info = PayloadInfo()
         _check(ctx._lib.csdr_segment_info(handle, C.byref(info)))
         self.info = info
@@ -266,7 +284,7 @@ class Segment:
         _check(self.ctx._lib.csdr_decompress_device_async(self.ctx._h, self._h, C.c_void_p(out_ptr)))
 
     def close(self):
-        if getattr(self, "_h", None) and self._owned:
+        if getattr(self, "_h", None) and self._owned and self.ctx._h:
             self.ctx._lib.csdr_segment_destroy(self._h)
         self._h = None
 
@@ -384,6 +402,9 @@ class SDRModelLoader:
         h = C.c_void_p()
         _check(self.ctx._lib.csdr_archive_open(self.ctx._h, archive_path.encode(), C.byref(h)))
         self._h = h
+        self._index_only = index_only
+        self._close_rank = 2          # after the decoders that borrow its device images
+        self.ctx._adopt(self)
         self.archive_path = archive_path
 
     def getSegmentHeaders(self):
@@ -446,9 +467,9 @@ class SDRModelLoader:
         return self._mm(self.ctx._lib.csdr_archive_matmul_hsdr, segment_name, x, batch)
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and (self._index_only or self.ctx._h):
             self.ctx._lib.csdr_archive_close(self._h)
-            self._h = None
+        self._h = None
 
     def __del__(self):
         try:
@@ -488,6 +509,9 @@ class SDRInferenceEngine:
 class HSDAReader:
     def __init__(self, handle, ctx: Context, path: str):
         self._h, self.ctx, self.path = handle, ctx, path
+        self._index_only = isinstance(ctx, _NoDevice)
+        self._close_rank = 2
+        ctx._adopt(self)
 
     @classmethod
     def fromFile(cls, path: str, ctx: Context | None = None, index_only: bool = False) -> "HSDAReader":
@@ -533,9 +557,39 @@ class HSDAReader:
         return y
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and (self._index_only or self.ctx._h):
             self.ctx._lib.csdr_hsda_close(self._h)
-            self._h = None
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def nccl_unique_id() -> bytes:
+    """128-byte NCCL id made on one rank; broadcast it to the others by any host-side means."""
+    buf = C.create_string_buffer(128)
+    _check(_lib.load().csdr_nccl_unique_id(buf))
+    return buf.raw
+
+
+class NcclComm:
+    """One rank's communicator for the tensor-parallel decoder."""
+
+    def __init__(self, ctx: Context, unique_id: bytes, rank: int, world: int):
+        self.ctx = ctx
+        h = C.c_void_p()
+        _check(ctx._lib.csdr_nccl_comm_create(ctx._h, unique_id, rank, world, C.byref(h)))
+        self._h, self.rank, self.world = h, rank, world
+        self._close_rank = 3
+        ctx._adopt(self)
+
+    def close(self):
+        if getattr(self, "_h", None) and self.ctx._h:
+            self.ctx._lib.csdr_nccl_comm_destroy(self._h)
+        self._h = None
 
     def __del__(self):
         try:
@@ -549,15 +603,16 @@ class Decoder:
     api/cortex_sdk.cpp:1543-1696, with a KV cache)."""
 
     def __init__(self, loader: SDRModelLoader, *, n_layers, hidden, q_heads, kv_heads, head_dim,
-                 inter, vocab, max_seq, max_batch=1, rms_eps=1e-5, rope_theta=1e6, tp_rank=0,
-                 tp_size=1, nccl_comm=None):
-        self.loader, self.ctx = loader, loader.ctx
+                 inter, vocab, max_seq, max_batch=1, rms_eps=1e-5, rope_theta=1e6, comm: "NcclComm | None" = None):
+        self.loader, self.ctx, self.comm = loader, loader.ctx, comm
         self.cfg = DecoderConfig(n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab,
-                                 max_seq, max_batch, rms_eps, rope_theta, tp_rank, tp_size,
-                                 C.c_void_p(nccl_comm) if nccl_comm else None)
+                                 max_seq, max_batch, rms_eps, rope_theta, comm.rank if comm else 0,
+                                 comm.world if comm else 1, comm._h if comm else None)
         h = C.c_void_p()
         _check(self.ctx._lib.csdr_decoder_create(loader._h, C.byref(self.cfg), C.byref(h)))
         self._h = h
+        self._close_rank = 1
+        self.ctx._adopt(self)
 
     def reset(self):
         _check(self.ctx._lib.csdr_decoder_reset(self._h))
@@ -588,9 +643,9 @@ class Decoder:
                                                             C.c_void_p(next_ptr)))
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and self.ctx._h and self.loader._h:
             self.ctx._lib.csdr_decoder_destroy(self._h)
-            self._h = None
+        self._h = None
 
     def __del__(self):
         try:

@@ -7,6 +7,7 @@
 #include <string>
 
 #include "internal.hpp"
+#include "kernels/gemm_tcgen05.hpp"
 #include "kernels/gemv_fused.hpp"
 
 namespace csdr {
@@ -60,7 +61,7 @@ DevPtr upload(csdr_context* ctx, const void* src, size_t bytes) {
 const char* kernel_class_name(int cls) {
     static const char* names[KC_COUNT] = {"hsdr_unpack", "hsdr_dx", "hsdr_gather", "hsdr_tile_project",
                                           "hsdr_tile_gather", "hsdr_edge", "dense_rows", "hsdr_decode_rows",
-                                          "dequant", "hsdr_gemm_tcgen05", "decoder_op", "hsdr_gemv_fused"};
+                                          "dequant", "hsdr_gemm_tcgen05", "decoder_op", "hsdr_gemv_fused", "attention"};
     return (cls >= 0 && cls < KC_COUNT) ? names[cls] : "?";
 }
 
@@ -138,6 +139,8 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
         if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_TENSOR_CORES")) ctx->tensor_cores = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_TC_MIN_BATCH")) ctx->tc_min_batch = static_cast<size_t>(std::max(1, std::atoi(e)));
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
         *out = ctx.release();
     });
@@ -427,6 +430,21 @@ int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const*
             if (!segs[i] || !ys_dev[i]) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
             if (segs[i]->g.cols != segs[0]->g.cols)
                 throw Error(CSDR_ERR_GEOMETRY, "grouped matmul: every segment must consume the same activation width");
+        }
+        bool all_tc = true;
+        for (size_t i = 0; i < n_segs; ++i) all_tc = all_tc && tcgen05_supported(ctx, segs[i], batch);
+        if (all_tc) {  // wide batch: each projection goes to the tensor cores on its own
+            for (size_t i = 0; i < n_segs; ++i) {
+                MatmulArgs a;
+                a.x = x_dev;
+                a.x_dtype = x_dtype;
+                a.x_layout = x_layout;
+                a.batch = batch;
+                a.y = ys_dev[i];
+                a.y_layout = y_layout;
+                launch_matmul_tcgen05(ctx, segs[i], a);
+            }
+            return;
         }
         size_t done = 0;
         while (done < n_segs) {

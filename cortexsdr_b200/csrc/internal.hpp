@@ -78,7 +78,7 @@ namespace csdr {
 // Kernel classes for launch counting and optional per-class device timing.
 enum KernelClass {
     KC_UNPACK = 0, KC_DX, KC_GATHER, KC_TILE_PROJECT, KC_TILE_GATHER, KC_EDGE, KC_DENSE,
-    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_GEMV_FUSED, KC_COUNT
+    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_GEMV_FUSED, KC_ATTENTION, KC_COUNT
 };
 const char* kernel_class_name(int cls);
 struct TimedLaunch {
@@ -103,6 +103,8 @@ struct csdr_context {
     csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
+    bool tensor_cores = true;   // CSDR_TENSOR_CORES=0 keeps wide batches on the CUDA-core kernels
+    size_t tc_min_batch = 16;   // CSDR_TC_MIN_BATCH: smallest batch sent to the tcgen05 path
     uint64_t launches_by_class[csdr::KC_COUNT] = {};
     // When on, every launch is bracketed by two events on the stream (profile_read resolves them).
     bool profiling = false;
@@ -169,6 +171,10 @@ void launch_dequantize(csdr_context* ctx, int fmt_id, const uint8_t* data_dev, s
                        size_t n_out, float scale, float zero_point, float* out_dev);
 int dequant_format_id(const char* fmt);               // -1 when unknown
 size_t dequant_output_count(int fmt_id, size_t nbytes);  // throws on bad size
+
+// Gather phase alone for a 16-token tile: dx is [n_atoms][16] fp32 (two-kernel layout).
+void launch_gather_tile16(csdr_context* ctx, const csdr_segment* seg, const float* dx, float* y, int y_layout,
+                          uint32_t m_total, uint32_t b0, uint32_t m, const float* bias);
 
 void launch_dense_matmul(csdr_context* ctx, const float* W_dev, uint32_t R, uint32_t C,
                          const MatmulArgs& a);

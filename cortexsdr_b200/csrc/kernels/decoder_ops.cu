@@ -119,12 +119,35 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
     }
 }
 
-// One CTA (4 warps) per (token, query head). Each warp walks every 4th key with the head
-// dimension spread over its lanes (VPL floats per lane), keeping a running max / sum /
-// weighted V (the softmax of simd_kernels.cpp:198-217 evaluated in one pass); the four
-// partial states are merged through shared memory. Causality: token t sees cache positions
-// 0..pos_of[t] of its own sequence, all of which are written before this kernel runs.
+// One CTA (4 warps) per (token, query head). Each warp walks the keys four at a time with the
+// head dimension spread over its lanes (VPL floats per lane, 128-bit loads): the eight K and V
+// rows of a step are requested before any is used, so a warp keeps 4 KB of cache rows in
+// flight. It keeps a running max / sum / weighted V (the softmax of simd_kernels.cpp:198-217
+// evaluated in one pass); the four warps' partial states are merged through shared memory.
+// Causality: token t sees cache positions 0..pos_of[t] of its own sequence, all of which are
+// written before this kernel runs.
 constexpr int kAttnWarps = 4;
+constexpr int kAttnKeys = 4;   // keys per warp per step
+
+template <int VPL>
+__device__ __forceinline__ void load_row(const float* p, float (&v)[VPL]) {
+    if constexpr (VPL == 1) {
+        v[0] = __ldg(p);
+    } else if constexpr (VPL == 2) {
+        const float2 t = __ldg(reinterpret_cast<const float2*>(p));
+        v[0] = t.x;
+        v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPL / 4; ++i) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(p) + i);
+            v[4 * i] = t.x;
+            v[4 * i + 1] = t.y;
+            v[4 * i + 2] = t.z;
+            v[4 * i + 3] = t.w;
+        }
+    }
+}
 
 template <int VPL>
 __global__ void __launch_bounds__(kAttnWarps * 32)
@@ -141,34 +164,44 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
     const int32_t n_keys = min(pos_of[t] + 1, static_cast<int32_t>(max_seq));
     const size_t row = static_cast<size_t>(KVH) * HD;
     const size_t base = static_cast<size_t>(seq_of[t]) * max_seq * row + kvh * HD + lane * VPL;
-    const float* qp = q + (static_cast<size_t>(t) * QH + h) * HD + lane * VPL;
     float qv[VPL], acc[VPL];
+    load_row<VPL>(q + (static_cast<size_t>(t) * QH + h) * HD + lane * VPL, qv);
 #pragma unroll
-    for (int e = 0; e < VPL; ++e) {
-        qv[e] = qp[e];
-        acc[e] = 0.0f;
-    }
+    for (int e = 0; e < VPL; ++e) acc[e] = 0.0f;
     float m = -INFINITY, l = 0.0f;
-    for (int32_t j = warp; j < n_keys; j += kAttnWarps) {
-        const float* kp = kc + base + static_cast<size_t>(j) * row;
-        const float* vp = vc + base + static_cast<size_t>(j) * row;
-        float kv[VPL], vv[VPL];
+    for (int32_t j0 = warp * kAttnKeys; j0 < n_keys; j0 += kAttnWarps * kAttnKeys) {
+        float kv[kAttnKeys][VPL], vv[kAttnKeys][VPL];
 #pragma unroll
-        for (int e = 0; e < VPL; ++e) {
-            kv[e] = kp[e];
-            vv[e] = vp[e];
+        for (int u = 0; u < kAttnKeys; ++u) {
+            const int32_t j = min(j0 + u, n_keys - 1);   // clamp: the tail re-reads the last row, unused
+            load_row<VPL>(kc + base + static_cast<size_t>(j) * row, kv[u]);
+            load_row<VPL>(vc + base + static_cast<size_t>(j) * row, vv[u]);
         }
-        float s = 0.0f;
+        float s[kAttnKeys];
 #pragma unroll
-        for (int e = 0; e < VPL; ++e) s = fmaf(qv[e], kv[e], s);
-        s = warp_sum(s) * scale;
-        const float m_new = fmaxf(m, s);
-        const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first key
-        const float p = expf(s - m_new);
-        l = l * corr + p;
+        for (int u = 0; u < kAttnKeys; ++u) {
+            float d = 0.0f;
 #pragma unroll
-        for (int e = 0; e < VPL; ++e) acc[e] = fmaf(p, vv[e], acc[e] * corr);
-        m = m_new;
+            for (int e = 0; e < VPL; ++e) d = fmaf(qv[e], kv[u][e], d);
+            s[u] = d;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+            for (int u = 0; u < kAttnKeys; ++u) s[u] += __shfl_xor_sync(0xFFFFFFFFu, s[u], off);
+#pragma unroll
+        for (int u = 0; u < kAttnKeys; ++u) {
+            if (j0 + u < n_keys) {
+                const float sc = s[u] * scale;
+                const float m_new = fmaxf(m, sc);
+                const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first key
+                const float p = expf(sc - m_new);
+                l = l * corr + p;
+#pragma unroll
+                for (int e = 0; e < VPL; ++e) acc[e] = fmaf(p, vv[u][e], acc[e] * corr);
+                m = m_new;
+            }
+        }
     }
     if (lane == 0) {
         sm_m[warp] = m;
@@ -329,7 +362,7 @@ void op_attention(csdr_context* ctx, const float* q, const float* kc, const floa
         throw Error(CSDR_ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 128 or 256");
     const float scale = 1.0f / sqrtf(static_cast<float>(HD));
     dim3 grid(T, QH);
-    LaunchScope ls(ctx, KC_DECODER_OP);
+    LaunchScope ls(ctx, KC_ATTENTION);
     switch (HD / 32u) {
         case 1: attention_kernel<1><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
         case 2: attention_kernel<2><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;

@@ -1,0 +1,458 @@
+// Tensor-core path for wide token tiles (batched decode at M >= 16, prefill) of 1-D row-tile
+// HSDR segments on sm_100a: the dictionary projection Dx = D * X^T runs on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in tensor memory), the signed gather over Dx stays
+// on the CUDA cores.
+//
+// Reference arithmetic: the Dx loop and the gather loop of matmulRowMajor
+// (strategies/HierarchicalSDRStrategy.cpp:1304-1336), which the reference runs in fp32.
+//
+// Precision. The dictionary is fp32 in the archive and the tolerance is 1e-3 relative with
+// fp32 accumulation; one bf16 (or tf32) rounding of D would sit right at that limit. So the
+// weights are rebuilt in shared memory as TWO bf16 tiles, hi = bf16(d) and lo = bf16(d - hi),
+// and likewise fp32 activations; the product is hi*hi + hi*lo + lo*hi on the tensor cores with
+// fp32 accumulation in TMEM (error ~2^-16 per term). bf16 activations need only hi*hi + lo*hi.
+//
+// One CTA = one (128-atom tile, token tile of N <= 256, column range). Per 64-column block:
+// all eight warps pull the fp32 block with 128-bit loads, split it, and write the bf16 tiles
+// in the K-major 128-byte-swizzle layout the MMA's shared-memory descriptors name; a
+// generic->async proxy fence and a CTA barrier later, one thread issues the MMAs and commits
+// them to the stage's mbarrier; two stages, so the next block's loads overlap the MMAs. The
+// epilogue reads TMEM with tcgen05.ld (warp w owns lanes 32*(w%4)..+31 = atoms) and writes
+// Dx, or one column-split partial of it. Every wait on an mbarrier is bounded.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "../internal.hpp"
+#include "gemm_tcgen05.hpp"
+#include "views.cuh"
+
+namespace csdr {
+
+namespace {
+
+constexpr int kTcThreads = 256;
+constexpr uint32_t kBlockK = 64;          // bf16 elements per row of a tile = 128 bytes = one swizzle span
+constexpr uint32_t kTileM = 128;          // atoms per CTA = MMA M
+constexpr uint32_t kATileBytes = kTileM * 128u;   // 16 KB
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, eight
+// rows (1024 bytes) per swizzle atom, atoms stacked along M/N with a 1024-byte stride.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+    d |= static_cast<uint64_t>(1) << 16;                             // leading byte offset (unused for swizzled K-major)
+    d |= static_cast<uint64_t>(1024u >> 4) << 32;                    // stride byte offset: 8 rows * 128 B
+    d |= static_cast<uint64_t>(1) << 46;                             // descriptor version for sm_100
+    d |= static_cast<uint64_t>(2) << 61;                             // layout: 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
+    uint32_t d = 0;
+    d |= 1u << 4;              // D format: f32
+    d |= 1u << 7;              // A format: bf16
+    d |= 1u << 10;             // B format: bf16
+    d |= (n >> 3) << 17;       // N / 8
+    d |= (kTileM >> 4) << 24;  // M / 16
+    return d;
+}
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Bounded wait on an mbarrier phase; false when it ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// byte offset of (row, 16-byte chunk) inside a K-major 128-byte-swizzle tile
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) {
+    return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+
+__device__ __forceinline__ void split4(const float4 v, uint2& hi, uint2& lo) {
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
+    const __nv_bfloat16 h2 = __float2bfloat16_rn(v.z), h3 = __float2bfloat16_rn(v.w);
+    const __nv_bfloat16 l0 = __float2bfloat16_rn(v.x - __bfloat162float(h0));
+    const __nv_bfloat16 l1 = __float2bfloat16_rn(v.y - __bfloat162float(h1));
+    const __nv_bfloat16 l2 = __float2bfloat16_rn(v.z - __bfloat162float(h2));
+    const __nv_bfloat16 l3 = __float2bfloat16_rn(v.w - __bfloat162float(h3));
+    hi.x = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
+    hi.y = static_cast<uint32_t>(__bfloat16_as_ushort(h2)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h3)) << 16);
+    lo.x = static_cast<uint32_t>(__bfloat16_as_ushort(l0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l1)) << 16);
+    lo.y = static_cast<uint32_t>(__bfloat16_as_ushort(l2)) | (static_cast<uint32_t>(__bfloat16_as_ushort(l3)) << 16);
+}
+
+struct TcParams {
+    const float* D;       // [K][C]
+    uint32_t K, C;
+    XView x;              // tokens b0..b0+M of the activation matrix
+    uint32_t n_tile;      // MMA N: 16, 32, 64, 128 or 256
+    uint32_t tmem_cols;   // power of two >= max(32, n_tile)
+    uint32_t kb_per_split;
+    uint32_t n_kb;        // C / 64
+    uint32_t n_split;
+    float* out;           // [n_split][K][M] (n_split == 1: Dx itself)
+    int* status;
+    int x_has_lo;         // 0 when the activations are bf16 already
+};
+
+// grid (K/128, token tiles, column splits)
+__global__ void __launch_bounds__(kTcThreads)
+hsdr_dx_tcgen05_kernel(const __grid_constant__ TcParams p) {
+    extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
+    __shared__ __align__(8) unsigned long long mbar[3];   // stage 0, stage 1, final
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int failed_s;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023));
+    const uint32_t N = p.n_tile;
+    const uint32_t b_tile_bytes = N * 128u;
+    const uint32_t stage_bytes = 2u * kATileBytes + 2u * b_tile_bytes;   // A_hi, A_lo, B_hi, B_lo
+    const uint32_t atom0 = blockIdx.x * kTileM;
+    const uint32_t tok0 = blockIdx.y * N;
+    const uint32_t kb_begin = blockIdx.z * p.kb_per_split;
+    const uint32_t kb_end = min(p.n_kb, kb_begin + p.kb_per_split);
+    constexpr uint32_t kSpin = 4000000u;   // a fraction of a second of polling, then give up
+
+    if (tid == 0) {
+        for (int i = 0; i < 3; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar[i])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        failed_s = 0;
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                     "r"(p.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    const uint32_t idesc = make_idesc(N);
+    // x fast paths (whole launch): token-major rows that can be read 128 / 64 bits at a time
+    const bool tm_f32 = p.x.dtype == CSDR_DTYPE_F32 && p.x.layout == CSDR_LAYOUT_TOKEN_MAJOR &&
+                        ((reinterpret_cast<uintptr_t>(p.x.x) | (static_cast<uintptr_t>(p.x.C) * 4u)) & 15u) == 0;
+    const bool tm_bf16 = p.x.dtype == CSDR_DTYPE_BF16 && p.x.layout == CSDR_LAYOUT_TOKEN_MAJOR &&
+                         ((reinterpret_cast<uintptr_t>(p.x.x) | (static_cast<uintptr_t>(p.x.C) * 2u)) & 7u) == 0;
+    // This thread's share of a weight block: 8 units of (row, four columns); requested one
+    // block ahead so the HBM latency hides behind the previous block's conversion and MMAs.
+    constexpr uint32_t kAUnits = kTileM * 16u / kTcThreads;   // 8
+    float4 dreg[kAUnits];
+    auto request_weights = [&](uint32_t kb) {
+        const uint32_t c0 = kb * kBlockK;
+#pragma unroll
+        for (uint32_t i = 0; i < kAUnits; ++i) {
+            const uint32_t u = tid + i * kTcThreads, r = u >> 4, c4 = u & 15u;
+            dreg[i] = atom0 + r < p.K
+                          ? ldg_stream_f4(reinterpret_cast<const float4*>(p.D + static_cast<size_t>(atom0 + r) * p.C + c0) + c4)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    if (kb_begin < kb_end) request_weights(kb_begin);
+
+    uint32_t it = 0;
+    for (uint32_t kb = kb_begin; kb < kb_end; ++kb, ++it) {
+        const uint32_t s = it & 1u;
+        unsigned char* st = smem + s * stage_bytes;
+        unsigned char* a_hi = st;
+        unsigned char* a_lo = st + kATileBytes;
+        unsigned char* b_hi = st + 2u * kATileBytes;
+        unsigned char* b_lo = b_hi + b_tile_bytes;
+        // the MMAs that read this stage two blocks ago must be done before it is overwritten
+        if (it >= 2u && !mbar_wait(smem_u32(&mbar[s]), ((it >> 1) - 1u) & 1u, kSpin)) failed_s = 1;
+        const uint32_t c0 = kb * kBlockK;
+        // ---- weights: 128 atoms x 64 columns fp32 -> bf16 hi / lo tiles ----
+#pragma unroll
+        for (uint32_t i = 0; i < kAUnits; ++i) {
+            const uint32_t u = tid + i * kTcThreads, r = u >> 4, c4 = u & 15u;
+            uint2 hi, lo;
+            split4(dreg[i], hi, lo);
+            const uint32_t off = swz(r, c4 >> 1) + (c4 & 1u) * 8u;
+            *reinterpret_cast<uint2*>(a_hi + off) = hi;
+            *reinterpret_cast<uint2*>(a_lo + off) = lo;
+        }
+        if (kb + 1u < kb_end) request_weights(kb + 1u);
+        // ---- activations: N tokens x 64 columns -> bf16 hi / lo tiles ----
+        for (uint32_t u = tid; u < N * 16u; u += kTcThreads) {
+            const uint32_t r = u >> 4, c4 = u & 15u;
+            const uint32_t tok = tok0 + r;
+            uint2 hi = make_uint2(0u, 0u), lo = make_uint2(0u, 0u);
+            if (tok < p.x.M) {
+                if (tm_f32) {
+                    const float4 v = *(reinterpret_cast<const float4*>(static_cast<const float*>(p.x.x) +
+                                                                       static_cast<size_t>(p.x.b0 + tok) * p.x.C + c0) + c4);
+                    split4(v, hi, lo);
+                } else if (tm_bf16) {
+                    hi = *(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.x.x) +
+                                                          static_cast<size_t>(p.x.b0 + tok) * p.x.C + c0) + c4);
+                } else {
+                    const float4 v = make_float4(load_x(p.x, c0 + c4 * 4u, tok), load_x(p.x, c0 + c4 * 4u + 1u, tok),
+                                                 load_x(p.x, c0 + c4 * 4u + 2u, tok), load_x(p.x, c0 + c4 * 4u + 3u, tok));
+                    split4(v, hi, lo);
+                }
+            }
+            const uint32_t off = swz(r, c4 >> 1) + (c4 & 1u) * 8u;
+            *reinterpret_cast<uint2*>(b_hi + off) = hi;
+            if (p.x_has_lo) *reinterpret_cast<uint2*>(b_lo + off) = lo;
+        }
+        // generic-proxy writes -> visible to the tensor core's async proxy, then everyone is done
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (failed_s) break;   // a wait ran out somewhere in the CTA: stop issuing work
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi_addr = smem_u32(a_hi), a_lo_addr = smem_u32(a_lo);
+            const uint32_t b_hi_addr = smem_u32(b_hi), b_lo_addr = smem_u32(b_lo);
+#pragma unroll
+            for (uint32_t k = 0; k < kBlockK / 16u; ++k) {          // four K = 16 steps, 32 bytes apart
+                const uint64_t ah = make_desc(a_hi_addr + k * 32u), al = make_desc(a_lo_addr + k * 32u);
+                const uint64_t bh = make_desc(b_hi_addr + k * 32u), bl = make_desc(b_lo_addr + k * 32u);
+                mma_bf16(tmem_base, ah, bh, idesc, (it | k) != 0u);
+                mma_bf16(tmem_base, al, bh, idesc, 1u);
+                if (p.x_has_lo) mma_bf16(tmem_base, ah, bl, idesc, 1u);
+            }
+            // arrive on this stage's barrier when every MMA issued so far has finished
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_u32(&mbar[s]))
+                         : "memory");
+        }
+    }
+    // ---- all MMAs done? ----
+    if (tid == 0) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                         smem_u32(&mbar[2]))
+                     : "memory");
+    }
+    if (!mbar_wait(smem_u32(&mbar[2]), 0u, kSpin)) failed_s = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    const bool good = failed_s == 0 && it > 0u;
+
+    // ---- epilogue: TMEM -> registers -> global. Warp w reads lanes 32*(w%4)..+31; warps 4-7
+    // take the upper half of the token columns. ----
+    if (good) {
+        const uint32_t lane_grp = warp & 3u;
+        const uint32_t atom = atom0 + lane_grp * 32u + lane;
+        const uint32_t half = warp >> 2;
+        const uint32_t chunks = N / 16u;                       // 16-column chunks
+        const uint32_t ch_begin = half * ((chunks + 1u) / 2u);
+        const uint32_t ch_end = half ? chunks : (chunks + 1u) / 2u;
+        float* orow = p.out + (static_cast<size_t>(blockIdx.z) * p.K + atom) * p.x.M;
+        for (uint32_t ch = ch_begin; ch < ch_end; ++ch) {
+            uint32_t r[16];
+            const uint32_t taddr = tmem_base + ((lane_grp * 32u) << 16) + ch * 16u;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(taddr)
+                : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (atom < p.K) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint32_t tok = tok0 + ch * 16u + j;
+                    if (tok < p.x.M) orow[tok] = __uint_as_float(r[j]);
+                }
+            }
+        }
+    } else if (tid == 0 && failed_s) {
+        atomicExch(p.status, 1);   // a bounded wait ran out: the host reports it
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+    }
+}
+
+// Dx[i] = sum over column splits, in split order.
+__global__ void dx_reduce_kernel(const float* __restrict__ part, uint32_t n, uint32_t n_split,
+                                 float* __restrict__ dx) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = 0.0f;
+    for (uint32_t s0 = 0; s0 < n_split; s0 += 8u) {
+        float a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = s0 + j < n_split ? __ldcg(part + static_cast<size_t>(s0 + j) * n + i) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v += a[j];
+    }
+    dx[i] = v;
+}
+
+// Gather for wide token tiles: CTA = (256 rows, 64-token slice); Dx slice [K][64] in shared
+// memory; one thread per output row walks the slice four tokens at a time (128-bit lookups),
+// adding in the reference's order (stage-major, slot-minor), one multiply + one add per code.
+constexpr uint32_t kWideTokens = 64;
+
+__global__ void __launch_bounds__(256)
+hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, uint32_t k,
+                        const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
+                        uint32_t M /* tokens in dx rows */, YView yv) {
+    extern __shared__ __align__(16) float wsm[];
+    float* dxs = wsm;                        // [K][64]
+    float* sc = wsm + static_cast<size_t>(K) * kWideTokens;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t t0 = blockIdx.y * kWideTokens;
+    const uint32_t tw = min(kWideTokens, M - t0);
+    for (uint32_t i = tid; i < K * (kWideTokens / 4u); i += 256) {
+        const uint32_t a = i / (kWideTokens / 4u), q = i - a * (kWideTokens / 4u);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* src = dx + static_cast<size_t>(a) * M + t0 + q * 4u;
+        if (q * 4u + 3u < tw && (M & 3u) == 0) v = __ldcg(reinterpret_cast<const float4*>(src));
+        else {
+            if (q * 4u + 0u < tw) v.x = __ldcg(src + 0);
+            if (q * 4u + 1u < tw) v.y = __ldcg(src + 1);
+            if (q * 4u + 2u < tw) v.z = __ldcg(src + 2);
+            if (q * 4u + 3u < tw) v.w = __ldcg(src + 3);
+        }
+        reinterpret_cast<float4*>(dxs)[i] = v;
+    }
+    for (uint32_t i = tid; i < S; i += 256) sc[i] = scales[i];
+    __syncthreads();
+    const uint32_t r = blockIdx.x * 256u + tid;
+    if (r >= R) return;
+    const uint32_t slots = S * k;
+    const uint16_t* rc = codes + static_cast<size_t>(r) * slots;
+    const float bias = yv.bias ? yv.bias[r] : 0.0f;
+    for (uint32_t q = 0; q * 4u < tw; ++q) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t l = 0; l < S; ++l) {
+            const float gamma = sc[l];
+            for (uint32_t kk = 0; kk < k; ++kk) {
+                const uint32_t code = rc[l * k + kk];
+                const float scale = (code & 0x8000u) ? -gamma : gamma;
+                const float4 v = reinterpret_cast<const float4*>(dxs)[(code & 0x7FFFu) * (kWideTokens / 4u) + q];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(scale, v.x));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(scale, v.y));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(scale, v.z));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(scale, v.w));
+            }
+        }
+        const float o[4] = {acc.x + bias, acc.y + bias, acc.z + bias, acc.w + bias};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t tok = t0 + q * 4u + j;
+            if (q * 4u + j < tw && tok < yv.M) yv.y[y_index(yv, r, tok)] = o[j];
+        }
+    }
+}
+
+}  // namespace
+
+bool tcgen05_supported(const csdr_context* ctx, const csdr_segment* seg, size_t batch) {
+    const Geometry& g = seg->g;
+    if (!ctx->tensor_cores || batch < ctx->tc_min_batch) return false;
+    if (!g.row_tiles() || g.n_atoms % kTileM || g.cols % kBlockK) return false;
+    const size_t gather_smem = (static_cast<size_t>(g.n_atoms) * kWideTokens + ((g.n_stages + 3u) & ~3u)) * 4u;
+    return gather_smem <= ctx->smem_optin;
+}
+
+void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a) {
+    const Geometry& g = seg->g;
+    const uint32_t M = static_cast<uint32_t>(a.batch);
+    // token tile: the smallest supported MMA N that covers the batch, capped at 128 so that two
+    // stages of operands (2 x (32 KB + 2 x N x 128 B)) stay well inside shared memory
+    uint32_t N = 16;
+    while (N < 128u && N < M) N <<= 1;
+    const uint32_t tok_tiles = (M + N - 1u) / N;
+    const uint32_t atom_tiles = g.n_atoms / kTileM;
+    const uint32_t n_kb = g.cols / kBlockK;
+    // Enough CTAs to have every SM streaming (two per SM while the tiles are few).
+    uint32_t n_split = std::max<uint32_t>(1u, 2u * static_cast<uint32_t>(ctx->sm_count) / std::max(1u, atom_tiles * tok_tiles));
+    n_split = std::min(n_split, n_kb);
+    const uint32_t kb_per_split = (n_kb + n_split - 1u) / n_split;
+    n_split = (n_kb + kb_per_split - 1u) / kb_per_split;
+
+    TcParams p{};
+    p.D = static_cast<const float*>(seg->atoms->ptr);
+    p.K = g.n_atoms;
+    p.C = g.cols;
+    p.x = XView{a.x, a.x_dtype, a.x_layout, g.cols, M, 0u, M};
+    p.n_tile = N;
+    p.tmem_cols = std::max(32u, N);
+    p.kb_per_split = kb_per_split;
+    p.n_kb = n_kb;
+    p.n_split = n_split;
+    p.status = ctx->status_word;
+    p.x_has_lo = a.x_dtype == CSDR_DTYPE_F32 ? 1 : 0;
+    const size_t dx_floats = static_cast<size_t>(g.n_atoms) * M;
+    float* dx = static_cast<float*>(ctx->scratch_get(0, std::max<size_t>(dx_floats * 4u, static_cast<size_t>(g.n_atoms) * 64u)));
+    float* part = n_split > 1 ? static_cast<float*>(ctx->scratch_get(1, dx_floats * n_split * 4u)) : dx;
+    p.out = part;
+    {
+        const size_t smem = 2u * (2u * kATileBytes + 2u * static_cast<size_t>(N) * 128u) + 1024u;
+        static size_t smem_set = 0;
+        if (smem > smem_set) {
+            CSDR_CUDA(cudaFuncSetAttribute(hsdr_dx_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)));
+            smem_set = smem;
+        }
+        LaunchScope ls(ctx, KC_GEMM);
+        hsdr_dx_tcgen05_kernel<<<dim3(atom_tiles, tok_tiles, n_split), kTcThreads, smem, ctx->stream>>>(p);
+        ls.done("hsdr_dx_tcgen05_kernel");
+    }
+    if (n_split > 1) {
+        LaunchScope ls(ctx, KC_DECODER_OP);
+        dx_reduce_kernel<<<static_cast<unsigned>((dx_floats + 255) / 256), 256, 0, ctx->stream>>>(
+            part, static_cast<uint32_t>(dx_floats), n_split, dx);
+        ls.done("dx_reduce_kernel");
+    }
+    if (M == 16u) {
+        // one 16-token tile: Dx is exactly the [n_atoms][16] block the compact gather expects
+        launch_gather_tile16(ctx, seg, dx, a.y, a.y_layout, M, 0u, M, a.bias);
+        return;
+    }
+    {
+        const size_t smem = (static_cast<size_t>(g.n_atoms) * kWideTokens + ((g.n_stages + 3u) & ~3u)) * 4u;
+        static size_t smem_set = 0;
+        if (smem > 48u * 1024u && smem > smem_set) {
+            CSDR_CUDA(cudaFuncSetAttribute(hsdr_gather_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)));
+            smem_set = smem;
+        }
+        YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
+        LaunchScope ls(ctx, KC_GATHER);
+        hsdr_gather_wide_kernel<<<dim3((g.rows + 255u) / 256u, (M + kWideTokens - 1u) / kWideTokens), 256, smem,
+                                  ctx->stream>>>(seg->codes_ptr(), g.rows, g.n_stages, g.k,
+                                                 static_cast<const float*>(seg->scales->ptr), dx, g.n_atoms, M, yv);
+        ls.done("hsdr_gather_wide_kernel");
+    }
+}
+
+}  // namespace csdr

@@ -17,6 +17,7 @@
 #include <algorithm>
 
 #include "../internal.hpp"
+#include "gemm_tcgen05.hpp"
 #include "gemv_fused.hpp"
 #include "views.cuh"
 
@@ -484,7 +485,10 @@ template <int MT>
 void launch_gather_t(csdr_context* ctx, const csdr_segment* seg, const float* dx, const YView& yv) {
     const Geometry& g = seg->g;
     constexpr uint32_t RP = kGatherThreads / MT;
-    uint32_t rows_per_cta = (g.rows + 4u * ctx->sm_count - 1u) / (4u * ctx->sm_count);
+    // Every CTA stages the whole Dx block (n_atoms x MT floats): with wide tiles fewer, larger
+    // CTAs keep that staging a small share of the traffic.
+    const uint32_t ctas = (MT >= 8 ? 1u : 4u) * static_cast<uint32_t>(ctx->sm_count);
+    uint32_t rows_per_cta = (g.rows + ctas - 1u) / ctas;
     rows_per_cta = std::max(RP, (rows_per_cta + RP - 1u) / RP * RP);
     const uint32_t slots = g.slots();
     const size_t cap16 = (static_cast<size_t>(rows_per_cta) * slots * 2u + 31u) >> 4;
@@ -582,6 +586,12 @@ void dispatch_mt(int mt, F&& f) {
 
 }  // namespace
 
+void launch_gather_tile16(csdr_context* ctx, const csdr_segment* seg, const float* dx, float* y, int y_layout,
+                          uint32_t m_total, uint32_t b0, uint32_t m, const float* bias) {
+    YView yv{y, y_layout, seg->g.rows, m_total, b0, m, bias};
+    launch_gather_t<16>(ctx, seg, dx, yv);
+}
+
 void launch_unpack(csdr_context* ctx, const uint16_t* codes, size_t n, int32_t* idx, int8_t* sign) {
     if (n == 0) return;
     const size_t blocks = std::min<size_t>((n / 8 + 255) / 256 + 1, static_cast<size_t>(ctx->sm_count) * 8);
@@ -608,6 +618,10 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
     const Geometry& g = seg->g;
     if (a.batch == 0) return;
     if (a.batch > 0xFFFFFFFFull) throw Error(CSDR_ERR_LIMIT, "batch too large");
+    if (tcgen05_supported(ctx, seg, a.batch)) {
+        launch_matmul_tcgen05(ctx, seg, a);
+        return;
+    }
     const size_t budget = std::min<size_t>(ctx->smem_optin, 200u * 1024u);
     const bool fast_rows = g.row_tiles() && (g.cols % 4u == 0);
     const bool fast_tiles = !fast_rows && (g.tile_cols % 4u == 0);

@@ -1,0 +1,68 @@
+"""Tensor-parallel decoder on two GPUs: every compressed weight row-sharded, NCCL all-gather at
+the rejoin points, logits equal to the single-GPU decoder's. Needs two B200s; skipped otherwise.
+Ranks run as child processes, one per GPU, with in-switch reduction off (NCCL_NVLS_ENABLE=0)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CFG = dict(n_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=32, inter=256, vocab=300)
+
+
+def _rank(rank, world, port, path, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    import cortexsdr_b200 as cs
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)   # host-side plumbing only
+    try:
+        ctx = cs.Context(rank)
+        ids = [cs.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = cs.NcclComm(ctx, ids[0], rank, world)
+        ld = cs.SDRModelLoader(path, ctx)
+        dec = cs.Decoder(ld, **CFG, max_seq=64, max_batch=2, rms_eps=1e-6, comm=comm)
+        tokens = np.random.default_rng(0).integers(0, CFG["vocab"], 12)
+        logits, hidden = dec.forward(tokens, want_hidden=True)
+        nxt, step_logits = dec.step([int(logits.argmax())], want_logits=True)
+        out = dict(logits=logits, hidden=hidden, step=step_logits[0], nxt=int(nxt[0]))
+        if rank == 0:
+            single = cs.Decoder(ld, **CFG, max_seq=64, max_batch=2, rms_eps=1e-6)
+            l1, h1 = single.forward(tokens, want_hidden=True)
+            n1, s1 = single.step([int(l1.argmax())], want_logits=True)
+            out.update(l1=l1, h1=h1, s1=s1[0], n1=int(n1[0]))
+        dist.barrier()
+        comm.close()
+        q.put((rank, out))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_decoder_matches_single_gpu(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from cortexsdr_b200 import synth
+    path = str(tmp_path / "tp.sdr")
+    synth.decoder_archive(path, **CFG, n_atoms=32, k=3, kv_atoms=16, seed=7)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29600 + os.getpid() % 1000
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, path, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    r0, r1 = res[0], res[1]
+    assert np.abs(r0["logits"] - r0["l1"]).max() < 1e-4
+    assert np.abs(r0["hidden"] - r0["h1"]).max() < 1e-4
+    assert np.abs(r0["step"] - r0["s1"]).max() < 1e-4 and r0["nxt"] == r0["n1"]
+    assert np.array_equal(r0["logits"], r1["logits"])      # replicated result on every rank
