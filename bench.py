@@ -447,6 +447,13 @@ def main():
                 ent["frac_hbm"] = ent["GBps_compressed"] / hbm_peak
             ent["TFLOPs_dense_equiv"] = 2.0 * R * C * m / per / 1e12
             ent["frac_bf16_peak"] = ent["TFLOPs_dense_equiv"] / tf_peak
+            if m >= 64:
+                # events around every launch: where the time of one wide matmul goes
+                ctx.profile(True)
+                with torch.cuda.stream(stream):
+                    step(xm, ym, m, cs.DTYPE_BF16)
+                ent["kernel_us"] = {k: round(v[1] / v[0] * 1e3, 2) for k, v in ctx.profile_read().items()}
+                ctx.profile(False)
             sweep[f"M{m}"] = ent
             del xm, ym
 

@@ -315,22 +315,64 @@ __global__ void dx_reduce_kernel(const float* __restrict__ part, uint32_t n, uin
     dx[i] = v;
 }
 
-// Gather for wide token tiles: CTA = (256 rows, 64-token slice); Dx slice [K][64] in shared
-// memory; one thread per output row walks the slice four tokens at a time (128-bit lookups),
-// adding in the reference's order (stage-major, slot-minor), one multiply + one add per code.
+// Gather for wide token tiles. CTA = (a run of rows, one 64-token slice); the Dx slice [K][64]
+// sits in shared memory. A half-warp owns one output row at a time: each lane carries four
+// tokens, so one 128-bit shared-memory read per code serves the whole row and the two halves of
+// a warp read two different atoms without a bank conflict. Rows are taken in blocks of eight
+// whose codes are prefetched into registers one block ahead and parked in shared memory; the
+// eight results stay in registers so that either output layout leaves in 16/32-byte pieces.
+// Sums run in the order of the stream (stage-major, slot-minor).
 constexpr uint32_t kWideTokens = 64;
+constexpr uint32_t kWideThreads = 512;
+constexpr uint32_t kWideHalfWarps = kWideThreads / 16u;
+constexpr uint32_t kWideRows = 8;        // rows per block of a half-warp
+constexpr uint32_t kWideMaxSlots = 64;   // S*k the code parking area is sized for
+constexpr uint32_t kWideCodeWords = (kWideRows * kWideMaxSlots + 2u) / 2u;   // per half-warp, u32
+constexpr uint32_t kWideWordsPerLane = (kWideCodeWords + 15u) / 16u;
 
-__global__ void __launch_bounds__(256)
+inline size_t gather_wide_smem(uint32_t K) {
+    return (static_cast<size_t>(K) * kWideTokens + kWideMaxSlots) * 4u +
+           static_cast<size_t>(kWideHalfWarps) * kWideCodeWords * 4u;
+}
+
+__global__ void __launch_bounds__(kWideThreads, 1)
 hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, uint32_t k,
                         const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
-                        uint32_t M /* tokens in dx rows */, YView yv) {
+                        uint32_t M /* tokens in dx rows */, uint32_t rows_per_cta, YView yv) {
     extern __shared__ __align__(16) float wsm[];
-    float* dxs = wsm;                        // [K][64]
-    float* sc = wsm + static_cast<size_t>(K) * kWideTokens;
+    float* dxs = wsm;                                           // [K][64]
+    float* gs = wsm + static_cast<size_t>(K) * kWideTokens;     // stage scales, [<= 64]
+    uint32_t* csm = reinterpret_cast<uint32_t*>(gs + kWideMaxSlots);   // [half-warp][kWideCodeWords]
     const uint32_t tid = threadIdx.x;
+    const uint32_t hw = tid >> 4, l16 = tid & 15u;
     const uint32_t t0 = blockIdx.y * kWideTokens;
     const uint32_t tw = min(kWideTokens, M - t0);
-    for (uint32_t i = tid; i < K * (kWideTokens / 4u); i += 256) {
+    const uint32_t slots = S * k;
+    const uint32_t row_lo = blockIdx.x * rows_per_cta;          // multiple of kWideRows
+    const uint32_t row_hi = min(R, row_lo + rows_per_cta);
+    const uint32_t n_blocks = row_lo < row_hi ? (row_hi - row_lo + kWideRows - 1u) / kWideRows : 0u;
+    const uint32_t iters = (n_blocks + kWideHalfWarps - 1u) / kWideHalfWarps;
+
+    // Codes of a block start on an even u16 offset from the stream's base (eight rows), so the
+    // parity of the base decides whether 32-bit loads must start one code early.
+    uint32_t nx[kWideWordsPerLane];
+    auto fetch = [&](uint32_t blk) {
+#pragma unroll
+        for (uint32_t i = 0; i < kWideWordsPerLane; ++i) nx[i] = 0u;
+        if (blk >= n_blocks) return;
+        const uint32_t r0 = row_lo + blk * kWideRows;
+        const uint16_t* bp = codes + static_cast<size_t>(r0) * slots;
+        const uint32_t off = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(bp) >> 1) & 1u;
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(bp - off);
+        const uint32_t nwords = (min(kWideRows, row_hi - r0) * slots + off + 1u) / 2u;
+#pragma unroll
+        for (uint32_t i = 0; i < kWideWordsPerLane; ++i)
+            if (i * 16u + l16 < nwords) nx[i] = __ldg(wp + i * 16u + l16);
+    };
+    fetch(hw);
+
+    // stage the Dx slice (zero beyond the last token)
+    for (uint32_t i = tid; i < K * (kWideTokens / 4u); i += kWideThreads) {
         const uint32_t a = i / (kWideTokens / 4u), q = i - a * (kWideTokens / 4u);
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* src = dx + static_cast<size_t>(a) * M + t0 + q * 4u;
@@ -343,32 +385,83 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
         }
         reinterpret_cast<float4*>(dxs)[i] = v;
     }
-    for (uint32_t i = tid; i < S; i += 256) sc[i] = scales[i];
+    if (tid < kWideMaxSlots) gs[tid] = tid < S ? scales[tid] : 0.0f;
     __syncthreads();
-    const uint32_t r = blockIdx.x * 256u + tid;
-    if (r >= R) return;
-    const uint32_t slots = S * k;
-    const uint16_t* rc = codes + static_cast<size_t>(r) * slots;
-    const float bias = yv.bias ? yv.bias[r] : 0.0f;
-    for (uint32_t q = 0; q * 4u < tw; ++q) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t l = 0; l < S; ++l) {
-            const float gamma = sc[l];
-            for (uint32_t kk = 0; kk < k; ++kk) {
-                const uint32_t code = rc[l * k + kk];
-                const float scale = (code & 0x8000u) ? -gamma : gamma;
-                const float4 v = reinterpret_cast<const float4*>(dxs)[(code & 0x7FFFu) * (kWideTokens / 4u) + q];
-                acc.x = __fadd_rn(acc.x, __fmul_rn(scale, v.x));
-                acc.y = __fadd_rn(acc.y, __fmul_rn(scale, v.y));
-                acc.z = __fadd_rn(acc.z, __fmul_rn(scale, v.z));
-                acc.w = __fadd_rn(acc.w, __fmul_rn(scale, v.w));
-            }
-        }
-        const float o[4] = {acc.x + bias, acc.y + bias, acc.z + bias, acc.w + bias};
+
+    const float4* dxs4 = reinterpret_cast<const float4*>(dxs) + l16;
+    uint32_t* my_csm = csm + hw * kWideCodeWords;
+    const bool y_vec = (reinterpret_cast<uintptr_t>(yv.y) & 15u) == 0;
+    for (uint32_t it = 0; it < iters; ++it) {
+        const uint32_t blk = hw + it * kWideHalfWarps;
+        __syncwarp();                       // the previous block's code reads are over
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t tok = t0 + q * 4u + j;
-            if (q * 4u + j < tw && tok < yv.M) yv.y[y_index(yv, r, tok)] = o[j];
+        for (uint32_t i = 0; i < kWideWordsPerLane; ++i)
+            if (i * 16u + l16 < kWideCodeWords) my_csm[i * 16u + l16] = nx[i];
+        __syncwarp();
+        fetch(blk + kWideHalfWarps);
+        if (blk >= n_blocks) continue;
+        const uint32_t r0 = row_lo + blk * kWideRows;
+        const uint32_t nrows = min(kWideRows, row_hi - r0);
+        const uint32_t off =
+            static_cast<uint32_t>(reinterpret_cast<uintptr_t>(codes + static_cast<size_t>(r0) * slots) >> 1) & 1u;
+        const uint16_t* crow = reinterpret_cast<const uint16_t*>(my_csm) + off;
+        float out[kWideRows][4];
+#pragma unroll
+        for (uint32_t rb = 0; rb < kWideRows; ++rb) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (rb < nrows) {
+                const uint16_t* cr = crow + rb * slots;
+                for (uint32_t st = 0; st < S; ++st) {
+                    const uint32_t gbits = __float_as_uint(gs[st]);
+#pragma unroll 4
+                    for (uint32_t j = 0; j < k; ++j) {
+                        const uint32_t code = cr[st * k + j];
+                        const float scale = __uint_as_float(gbits ^ ((code & 0x8000u) << 16));
+                        const float4 v = dxs4[(code & 0x7FFFu) * (kWideTokens / 4u)];
+                        acc.x = fmaf(scale, v.x, acc.x);
+                        acc.y = fmaf(scale, v.y, acc.y);
+                        acc.z = fmaf(scale, v.z, acc.z);
+                        acc.w = fmaf(scale, v.w, acc.w);
+                    }
+                }
+                const float bias = yv.bias ? yv.bias[r0 + rb] : 0.0f;
+                acc.x += bias; acc.y += bias; acc.z += bias; acc.w += bias;
+            }
+            out[rb][0] = acc.x; out[rb][1] = acc.y; out[rb][2] = acc.z; out[rb][3] = acc.w;
+        }
+        const uint32_t tl = 4u * l16;               // first token of this lane inside the slice
+        if (tl >= tw) continue;
+        if (yv.layout == CSDR_LAYOUT_FEATURE_MAJOR) {
+            // y[r][token]: a row's 64 tokens are contiguous
+            const size_t col = static_cast<size_t>(yv.b0) + t0 + tl;
+            const bool vec = y_vec && (yv.Mtotal & 3u) == 0 && (col & 3u) == 0 && tl + 3u < tw;
+#pragma unroll
+            for (uint32_t rb = 0; rb < kWideRows; ++rb) {
+                if (rb >= nrows) break;
+                float* dst = yv.y + static_cast<size_t>(r0 + rb) * yv.Mtotal + col;
+                if (vec) *reinterpret_cast<float4*>(dst) = make_float4(out[rb][0], out[rb][1], out[rb][2], out[rb][3]);
+                else {
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j)
+                        if (tl + j < tw) dst[j] = out[rb][j];
+                }
+            }
+        } else {
+            // y[token][r]: eight consecutive rows of one token are contiguous
+            const bool vec = y_vec && (yv.R & 3u) == 0 && nrows == kWideRows;
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                if (tl + j >= tw) break;
+                float* dst = yv.y + (static_cast<size_t>(yv.b0) + t0 + tl + j) * yv.R + r0;
+                if (vec) {
+                    reinterpret_cast<float4*>(dst)[0] = make_float4(out[0][j], out[1][j], out[2][j], out[3][j]);
+                    reinterpret_cast<float4*>(dst)[1] = make_float4(out[4][j], out[5][j], out[6][j], out[7][j]);
+                } else {
+#pragma unroll
+                    for (uint32_t rb = 0; rb < kWideRows; ++rb)
+                        if (rb < nrows) dst[rb] = out[rb][j];
+                }
+            }
         }
     }
 }
@@ -379,8 +472,8 @@ bool tcgen05_supported(const csdr_context* ctx, const csdr_segment* seg, size_t 
     const Geometry& g = seg->g;
     if (!ctx->tensor_cores || batch < ctx->tc_min_batch) return false;
     if (!g.row_tiles() || g.n_atoms % kTileM || g.cols % kBlockK) return false;
-    const size_t gather_smem = (static_cast<size_t>(g.n_atoms) * kWideTokens + ((g.n_stages + 3u) & ~3u)) * 4u;
-    return gather_smem <= ctx->smem_optin;
+    if (g.slots() > kWideMaxSlots) return false;
+    return gather_wide_smem(g.n_atoms) <= ctx->smem_optin;
 }
 
 void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a) {
@@ -439,7 +532,7 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
         return;
     }
     {
-        const size_t smem = (static_cast<size_t>(g.n_atoms) * kWideTokens + ((g.n_stages + 3u) & ~3u)) * 4u;
+        const size_t smem = gather_wide_smem(g.n_atoms);
         static size_t smem_set = 0;
         if (smem > 48u * 1024u && smem > smem_set) {
             CSDR_CUDA(cudaFuncSetAttribute(hsdr_gather_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -447,10 +540,17 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
             smem_set = smem;
         }
         YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
+        // one CTA per SM (the slice fills most of its shared memory): split the rows so that
+        // slices x row runs covers the GPU once, in runs that are multiples of eight rows
+        const uint32_t slices = (M + kWideTokens - 1u) / kWideTokens;
+        const uint32_t want = std::max(1u, static_cast<uint32_t>(ctx->sm_count) / slices);
+        uint32_t rows_per_cta = (g.rows + want - 1u) / want;
+        rows_per_cta = (rows_per_cta + kWideRows - 1u) / kWideRows * kWideRows;
+        const uint32_t runs = (g.rows + rows_per_cta - 1u) / rows_per_cta;
         LaunchScope ls(ctx, KC_GATHER);
-        hsdr_gather_wide_kernel<<<dim3((g.rows + 255u) / 256u, (M + kWideTokens - 1u) / kWideTokens), 256, smem,
-                                  ctx->stream>>>(seg->codes_ptr(), g.rows, g.n_stages, g.k,
-                                                 static_cast<const float*>(seg->scales->ptr), dx, g.n_atoms, M, yv);
+        hsdr_gather_wide_kernel<<<dim3(runs, slices), kWideThreads, smem, ctx->stream>>>(
+            seg->codes_ptr(), g.rows, g.n_stages, g.k, static_cast<const float*>(seg->scales->ptr), dx,
+            g.n_atoms, M, rows_per_cta, yv);
         ls.done("hsdr_gather_wide_kernel");
     }
 }
