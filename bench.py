@@ -413,9 +413,11 @@ def main():
     # ---- e2e: host buffers through the C-ABI (csdr_matmul), H2D + D2H inside the timed region ----
     xh = np.random.default_rng(3).normal(0, 1, (C, 1)).astype(np.float32)
 
+    yh = np.empty((R, 1), np.float32)
+
     def e2e_step():
         for s in segs:
-            s.matmul(xh, 1)
+            s.matmul(xh, 1, out=yh)
     for _ in range(2):
         e2e_step()
     if world > 1:

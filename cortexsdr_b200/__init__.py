@@ -247,15 +247,21 @@ class Segment:
                                                sign.ctypes.data_as(C.POINTER(C.c_int8)), n))
         return idx, sign
 
-    def matmul(self, x, batch: int, allow_2d: bool = False) -> np.ndarray:
-        """x (C, batch) row-major fp32 -> y (R, batch), host arrays."""
-        x = _f32(x)
+    def matmul(self, x, batch: int, allow_2d: bool = False, out: np.ndarray | None = None) -> np.ndarray:
+        """x (C, batch) row-major fp32 -> y (R, batch), host arrays. `out` (fp32, C-contiguous,
+        rows*batch elements) receives the result when given, so that a caller in a loop does
+        not pay for an allocation per call."""
+        if not (type(x) is np.ndarray and x.dtype == np.float32 and x.flags.c_contiguous):
+            x = _f32(x)
         if x.size != self.cols * batch:
             raise ValueError("x must hold cols*batch floats")
-        y = np.empty((self.rows, batch), np.float32)
-        _check(self.ctx._lib.csdr_matmul(self.ctx._h, self._h, _fp(x), batch, _fp(y),
-                                         1 if allow_2d else 0))
-        return y
+        if out is None:
+            out = np.empty((self.rows, batch), np.float32)
+        elif not (out.dtype == np.float32 and out.flags.c_contiguous and out.size == self.rows * batch):
+            raise ValueError("out must be a C-contiguous fp32 array of rows*batch elements")
+        _check(self.ctx._lib.csdr_matmul(self.ctx._h, self._h, x.__array_interface__["data"][0], batch,
+                                         out.__array_interface__["data"][0], 1 if allow_2d else 0))
+        return out
 
     def matmul_device(self, x_ptr: int, x_dtype: int, x_layout: int, batch: int, y_ptr: int,
                       y_layout: int, bias_ptr: int = 0):

@@ -15,7 +15,7 @@ SOURCES = [
     "kernels/decode.cu",
     "kernels/gemv_fused.cu",
     "kernels/decoder_ops.cu",
-    "kernels/gemm_tcgen05.cu",
+    "kernels/gemm_tcgen05.cu", "kernels/gemm_tma.cu",
     "decoder.cu",
     "host/format.cpp",
     "host/archive.cpp",

@@ -3,6 +3,7 @@
 // Archive-level and decoder entry points live in host/archive.cpp and decoder.cu.
 #include <algorithm>
 #include <cstdlib>
+#include <chrono>
 #include <cstring>
 #include <string>
 
@@ -106,6 +107,52 @@ void* csdr_context::scratch_get(int slot, size_t bytes) {
     return scratch[slot]->ptr;
 }
 
+namespace csdr_hostio {
+
+// Host-buffer calls on small operands avoid the copy engines and the driver's stream wait:
+// one CTA pulls x out of mapped page-locked memory (every element crosses the bus once), the
+// product writes y straight into mapped memory, and a one-thread kernel behind it (launched
+// early, released when the product's grid has completed and flushed) stores a sequence number
+// that the host polls.
+__global__ void __launch_bounds__(1024) host_x_pull_kernel(const float4* __restrict__ src, float4* __restrict__ dst,
+                                                           uint32_t n4) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+__global__ void host_notify_kernel(volatile uint32_t* word, uint32_t seq) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    *word = seq;
+    __threadfence_system();
+}
+
+// Polls the completion word for a bounded time; false means "not seen, use the stream wait".
+bool wait_host_word(const volatile uint32_t* word, uint32_t seq) {
+    const auto t0 = std::chrono::steady_clock::now();
+    for (uint32_t spin = 0;; ++spin) {
+        if (*word == seq) return true;
+        if ((spin & 255u) == 255u &&
+            std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(500))
+            return false;
+    }
+}
+
+}  // namespace csdr_hostio
+using namespace csdr_hostio;
+
+void* csdr_context::pinned_get(size_t bytes) {
+    if (pinned_bytes < bytes) {
+        CSDR_CUDA(cudaStreamSynchronize(stream));
+        if (pinned) cudaFreeHost(pinned);
+        pinned = nullptr;
+        pinned_bytes = 0;
+        const size_t want = std::max<size_t>(bytes, 1u << 20);
+        CSDR_CUDA(cudaHostAlloc(&pinned, want, cudaHostAllocMapped));
+        pinned_bytes = want;
+    }
+    return pinned;
+}
+
 extern "C" {
 
 const char* csdr_last_error(void) { return g_last_error.c_str(); }
@@ -140,6 +187,7 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TENSOR_CORES")) ctx->tensor_cores = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_TMA")) ctx->tma = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TC_MIN_BATCH")) ctx->tc_min_batch = static_cast<size_t>(std::max(1, std::atoi(e)));
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
         *out = ctx.release();
@@ -153,6 +201,7 @@ int csdr_context_destroy(csdr_context* ctx) {
         cudaStreamSynchronize(ctx->stream);
         for (auto& s : ctx->scratch) s.reset();
         if (ctx->status_word) cudaFree(ctx->status_word);
+        if (ctx->pinned) cudaFreeHost(ctx->pinned);
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
     });
@@ -498,18 +547,60 @@ int csdr_matmul(csdr_context* ctx, const csdr_segment* seg, const float* x, size
         }
         if (batch == 0) return;
         const size_t xb = static_cast<size_t>(g.cols) * batch * 4, yb = static_cast<size_t>(g.rows) * batch * 4;
+        const size_t head = 256;                                   // completion word lives here
         const size_t xoff = (xb + 255) & ~static_cast<size_t>(255);
-        unsigned char* buf = static_cast<unsigned char*>(ctx->scratch_get(3, xoff + yb));
-        float* xd = reinterpret_cast<float*>(buf);
-        float* yd = reinterpret_cast<float*>(buf + xoff);
-        CSDR_CUDA(cudaMemcpyAsync(xd, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+        // Small operands: x pulled by a kernel, y written by the product into mapped memory,
+        // completion through a polled word. Large ones: plain DMAs from/to page-locked staging.
+        const bool small = xb <= (256u << 10) && yb <= (256u << 10) && (xb & 15u) == 0;
+        unsigned char* hbuf = static_cast<unsigned char*>(ctx->pinned_get(head + xoff + yb));
+        unsigned char* dbuf = static_cast<unsigned char*>(ctx->scratch_get(3, xoff + (small ? 0 : yb)));
+        volatile uint32_t* word = reinterpret_cast<volatile uint32_t*>(hbuf);
+        unsigned char* xh = hbuf + head;
+        float* yh = reinterpret_cast<float*>(hbuf + head + xoff);
+        std::memcpy(xh, x, xb);
+        float* xd = reinterpret_cast<float*>(dbuf);
+        float* yd = reinterpret_cast<float*>(dbuf + xoff);
         MatmulArgs a;
         a.x = xd;
         a.batch = batch;
-        a.y = yd;
-        launch_matmul(ctx, seg, a);
-        CSDR_CUDA(cudaMemcpyAsync(y, yd, yb, cudaMemcpyDeviceToHost, ctx->stream));
-        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (small) {
+            void* mapped = nullptr;
+            CSDR_CUDA(cudaHostGetDevicePointer(&mapped, hbuf, 0));
+            unsigned char* mb = static_cast<unsigned char*>(mapped);
+            const uint32_t n4 = static_cast<uint32_t>(xb / 16u);
+            {
+                LaunchScope ls(ctx, KC_DECODER_OP);
+                host_x_pull_kernel<<<std::min<uint32_t>(8u, (n4 + 1023u) / 1024u), 1024, 0, ctx->stream>>>(
+                    reinterpret_cast<const float4*>(mb + head), reinterpret_cast<float4*>(xd), n4);
+                ls.done("host_x_pull_kernel");
+            }
+            a.y = reinterpret_cast<float*>(mb + head + xoff);
+            launch_matmul(ctx, seg, a);
+            if (++ctx->notify_seq == 0) ++ctx->notify_seq;
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(1, 1, 1);
+            cfg.blockDim = dim3(1, 1, 1);
+            cfg.stream = ctx->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            {
+                LaunchScope ls(ctx, KC_DECODER_OP);
+                CSDR_CUDA(cudaLaunchKernelEx(&cfg, host_notify_kernel,
+                                             reinterpret_cast<volatile uint32_t*>(mb), ctx->notify_seq));
+                ls.done("host_notify_kernel");
+            }
+            if (!wait_host_word(word, ctx->notify_seq)) CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        } else {
+            CSDR_CUDA(cudaMemcpyAsync(xd, xh, xb, cudaMemcpyHostToDevice, ctx->stream));
+            a.y = yd;
+            launch_matmul(ctx, seg, a);
+            CSDR_CUDA(cudaMemcpyAsync(yh, yd, yb, cudaMemcpyDeviceToHost, ctx->stream));
+            CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        }
+        std::memcpy(y, yh, yb);
     });
 }
 

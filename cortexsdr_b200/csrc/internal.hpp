@@ -53,6 +53,8 @@ struct DeviceBuffer {
     void* ptr = nullptr;
     size_t bytes = 0;
     int device = 0;
+    // Derived data cached beside the buffer and freed with it (a dictionary's bf16 planes).
+    std::shared_ptr<void> aux;
     DeviceBuffer(size_t n, int dev);
     ~DeviceBuffer();
     DeviceBuffer(const DeviceBuffer&) = delete;
@@ -98,12 +100,18 @@ struct csdr_context {
     csdr::DevPtr scratch[6];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials
     void* scratch_get(int slot, size_t bytes);
     int* status_word = nullptr;  // device int: kernels record bounded-wait timeouts here
+    // Page-locked, device-mapped host staging for the host-buffer entry points (grow-only).
+    void* pinned = nullptr;
+    size_t pinned_bytes = 0;
+    void* pinned_get(size_t bytes);
+    uint32_t notify_seq = 0;     // value of the last completion word written into `pinned`
     // Fused GEMV: every launch tags its partial results with a fresh non-zero epoch.
     uint32_t gemv_epoch = 0;
     csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
     bool tensor_cores = true;   // CSDR_TENSOR_CORES=0 keeps wide batches on the CUDA-core kernels
+    bool tma = true;            // CSDR_TMA=0 keeps the register-fed tensor-core kernel
     size_t tc_min_batch = 16;   // CSDR_TC_MIN_BATCH: smallest batch sent to the tcgen05 path
     uint64_t launches_by_class[csdr::KC_COUNT] = {};
     // When on, every launch is bracketed by two events on the stream (profile_read resolves them).

@@ -492,6 +492,11 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
     const uint32_t kb_per_split = (n_kb + n_split - 1u) / n_split;
     n_split = (n_kb + kb_per_split - 1u) / kb_per_split;
 
+    const size_t dx_floats = static_cast<size_t>(g.n_atoms) * M;
+    float* dx = static_cast<float*>(ctx->scratch_get(0, std::max<size_t>(dx_floats * 4u, static_cast<size_t>(g.n_atoms) * 64u)));
+    const bool use_tma = dx_tma_supported(ctx, seg, a.batch);
+    if (use_tma) launch_dx_tma(ctx, seg, a, dx);
+
     TcParams p{};
     p.D = static_cast<const float*>(seg->atoms->ptr);
     p.K = g.n_atoms;
@@ -504,11 +509,9 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
     p.n_split = n_split;
     p.status = ctx->status_word;
     p.x_has_lo = a.x_dtype == CSDR_DTYPE_F32 ? 1 : 0;
-    const size_t dx_floats = static_cast<size_t>(g.n_atoms) * M;
-    float* dx = static_cast<float*>(ctx->scratch_get(0, std::max<size_t>(dx_floats * 4u, static_cast<size_t>(g.n_atoms) * 64u)));
-    float* part = n_split > 1 ? static_cast<float*>(ctx->scratch_get(1, dx_floats * n_split * 4u)) : dx;
+    float* part = (n_split > 1 && !use_tma) ? static_cast<float*>(ctx->scratch_get(1, dx_floats * n_split * 4u)) : dx;
     p.out = part;
-    {
+    if (!use_tma) {
         const size_t smem = 2u * (2u * kATileBytes + 2u * static_cast<size_t>(N) * 128u) + 1024u;
         static size_t smem_set = 0;
         if (smem > smem_set) {
@@ -520,7 +523,7 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
         hsdr_dx_tcgen05_kernel<<<dim3(atom_tiles, tok_tiles, n_split), kTcThreads, smem, ctx->stream>>>(p);
         ls.done("hsdr_dx_tcgen05_kernel");
     }
-    if (n_split > 1) {
+    if (n_split > 1 && !use_tma) {
         LaunchScope ls(ctx, KC_DECODER_OP);
         dx_reduce_kernel<<<static_cast<unsigned>((dx_floats + 255) / 256), 256, 0, ctx->stream>>>(
             part, static_cast<uint32_t>(dx_floats), n_split, dx);

@@ -1,0 +1,481 @@
+// TMA-fed tensor-core projection Dx = D * X^T for wide token tiles of 1-D row-tile HSDR segments
+// on sm_100a. Same arithmetic as the register-fed kernel in gemm_tcgen05.cu (bf16 hi/lo split of
+// the fp32 dictionary and activations, fp32 accumulation in tensor memory; reference loop:
+// strategies/HierarchicalSDRStrategy.cpp:1304-1318), but the split happens once per dictionary
+// instead of once per CTA, and nothing passes through registers on the way to the MMA:
+//
+//   * the dictionary is kept as two bf16 planes hi = bf16(d), lo = bf16(d - hi), built on the
+//     first wide call and cached beside the fp32 atoms (shared by every segment and row shard
+//     that uses the dictionary);
+//   * activations that are already bf16, token-major and 16-byte aligned are read in place;
+//     anything else is split into planes by a small kernel first;
+//   * one CTA owns (128 atoms) x (N tokens) x (a range of 64-column blocks). Warp 0 issues
+//     cp.async.bulk.tensor loads (128-byte swizzle, the layout the MMA descriptors name) into a
+//     ring of stages and arms each stage's mbarrier with the expected byte count; warp 1 waits
+//     for a stage, issues tcgen05.mma (hi*hi + lo*hi [+ hi*lo]) and commits the stage back to the
+//     loader; warps 2-5 read the accumulators out of tensor memory at the end;
+//   * the column ranges of one output tile form a thread-block cluster: every CTA parks its
+//     partial tile in its own shared memory, and after a cluster barrier each CTA sums a slice
+//     of the rows over all peers (distributed shared memory, fixed rank order, so the result
+//     does not depend on timing) and writes that slice of Dx. No partials in global memory and
+//     no separate reduction kernel.
+//
+// Every mbarrier wait is a bounded try_wait loop; a wait that runs out sets the context's status
+// word, the roles stop issuing work, and the CTA still meets its cluster barriers and frees its
+// tensor memory. No load here uses cluster multicast.
+#include <cooperative_groups.h>
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "../internal.hpp"
+#include "gemm_tcgen05.hpp"
+#include "views.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace csdr {
+
+namespace tma_detail {
+
+constexpr uint32_t kThreads = 192;       // loader warp, MMA warp, four epilogue warps
+constexpr uint32_t kBlockK = 64;         // bf16 per tile row = 128 bytes = one swizzle span
+constexpr uint32_t kTileM = 128;         // atoms per CTA = MMA M
+constexpr uint32_t kATile = kTileM * 128u;
+constexpr uint32_t kMaxStages = 4;
+constexpr uint32_t kSpin = 4000000u;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// K-major operand, 128-byte swizzle: 8 rows x 128 B per swizzle atom, atoms 1024 B apart.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024u >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// kind::f16: D fp32, A and B bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((kTileM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpin; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+struct Params {
+    uint32_t K, M;          // atoms, tokens
+    uint32_t n_tile;        // MMA N: 16, 32, 64 or 128
+    uint32_t tmem_cols;     // power of two >= max(32, n_tile)
+    uint32_t n_kb;          // C / 64
+    uint32_t kb_per_cta;
+    uint32_t stages;
+    uint32_t x_has_lo;
+    float* dx;              // [K][M]
+    int* status;
+};
+
+// grid (K/128, token tiles, column ranges); cluster (1, 1, column ranges)
+__global__ void __launch_bounds__(kThreads, 1)
+hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+                   const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
+                   const __grid_constant__ Params p) {
+    extern __shared__ __align__(1024) unsigned char tma_smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[kMaxStages];
+    __shared__ __align__(8) unsigned long long empty_bar[kMaxStages];
+    __shared__ __align__(8) unsigned long long accum_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int failed_s;
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t n_ranks = cluster.num_blocks();
+    const uint32_t rank = cluster.block_rank();
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tma_smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023));
+    const uint32_t N = p.n_tile;
+    const uint32_t b_tile = N * 128u;
+    const uint32_t stage_bytes = 2u * kATile + (p.x_has_lo ? 2u : 1u) * b_tile;
+    const uint32_t atom0 = blockIdx.x * kTileM;
+    const uint32_t tok0 = blockIdx.y * N;
+    const uint32_t kb_begin = min(p.n_kb, rank * p.kb_per_cta);
+    const uint32_t kb_end = min(p.n_kb, kb_begin + p.kb_per_cta);
+    const uint32_t n_it = kb_end - kb_begin;
+
+    if (tid == 0) {
+        for (uint32_t i = 0; i < kMaxStages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[i])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&empty_bar[i])));
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&accum_bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        failed_s = 0;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                     "r"(p.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        // ---- loader ----
+        if (lane == 0) {
+            for (uint32_t it = 0; it < n_it; ++it) {
+                const uint32_t s = it % p.stages, use = it / p.stages;
+                if (use > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (use - 1u) & 1u)) {
+                    failed_s = 1;
+                    break;
+                }
+                if (failed_s) break;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_bytes)
+                             : "memory");
+                const uint32_t dst = smem_u32(smem + s * stage_bytes);
+                const uint32_t c0 = (kb_begin + it) * kBlockK;
+                tma_load_2d(dst, &map_ahi, c0, atom0, bar);
+                tma_load_2d(dst + kATile, &map_alo, c0, atom0, bar);
+                tma_load_2d(dst + 2u * kATile, &map_xhi, c0, tok0, bar);
+                if (p.x_has_lo) tma_load_2d(dst + 2u * kATile + b_tile, &map_xlo, c0, tok0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(N);
+            for (uint32_t it = 0; it < n_it; ++it) {
+                const uint32_t s = it % p.stages, use = it / p.stages;
+                if (!mbar_wait(smem_u32(&full_bar[s]), use & 1u)) {
+                    failed_s = 1;
+                    break;
+                }
+                if (failed_s) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_hi = smem_u32(smem + s * stage_bytes), a_lo = a_hi + kATile;
+                const uint32_t b_hi = a_hi + 2u * kATile, b_lo = b_hi + b_tile;
+#pragma unroll
+                for (uint32_t k = 0; k < kBlockK / 16u; ++k) {     // four K = 16 steps, 32 bytes apart
+                    const uint64_t ah = make_desc(a_hi + k * 32u), al = make_desc(a_lo + k * 32u);
+                    const uint64_t bh = make_desc(b_hi + k * 32u);
+                    mma_bf16(tmem_base, ah, bh, idesc, (it | k) != 0u);
+                    mma_bf16(tmem_base, al, bh, idesc, 1u);
+                    if (p.x_has_lo) mma_bf16(tmem_base, ah, make_desc(b_lo + k * 32u), idesc, 1u);
+                }
+                // the stage is free again once every MMA issued so far has read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 smem_u32(&empty_bar[s]))
+                             : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_u32(&accum_bar))
+                         : "memory");
+        }
+    }
+    // ---- accumulators -> this CTA's partial tile in shared memory (stage memory is free now) ----
+    const uint32_t pstride = N + 4u;                      // floats; keeps 128-bit row writes conflict-free
+    float* ptile = reinterpret_cast<float*>(smem);
+    if (warp >= 2) {
+        const bool done = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&accum_bar), 0u));   // warp-uniform
+        if (!done) failed_s = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t quad = warp & 3u;                  // TMEM lanes 32*quad .. +31
+        float* prow = ptile + static_cast<size_t>(quad * 32u + lane) * pstride;
+        for (uint32_t ch = 0; ch < N / 16u; ++ch) {
+            uint32_t r[16];
+            if (done && n_it > 0u) {
+                const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + ch * 16u;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+                      "=r"(r[15])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;   // an empty column range adds nothing
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<uint4*>(prow + ch * 16u + j * 4) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0 && failed_s) atomicExch(p.status, 1);    // a bounded wait ran out: the host reports it
+    cluster.sync();                                       // every partial tile is in place
+
+    // ---- each CTA sums its slice of the rows over the cluster, in rank order ----
+    if (warp >= 2) {
+        const uint32_t t = tid - 64u;
+        const uint32_t rows_mine = kTileM / n_ranks;
+        const uint32_t row_begin = rank * rows_mine;
+        const uint32_t n4 = N / 4u;
+        const bool vec = (p.M & 3u) == 0;
+        for (uint32_t i = t; i < rows_mine * n4; i += 128u) {
+            const uint32_t row = row_begin + i / n4, c4 = i % n4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t r = 0; r < n_ranks; ++r) {
+                const float* peer = cluster.map_shared_rank(ptile, r);
+                const float4 v = *reinterpret_cast<const float4*>(peer + static_cast<size_t>(row) * pstride + c4 * 4u);
+                acc.x += v.x;
+                acc.y += v.y;
+                acc.z += v.z;
+                acc.w += v.w;
+            }
+            const uint32_t atom = atom0 + row, tok = tok0 + c4 * 4u;
+            if (atom < p.K && tok < p.M) {
+                float* dst = p.dx + static_cast<size_t>(atom) * p.M + tok;
+                if (vec) *reinterpret_cast<float4*>(dst) = acc;     // tok and M are multiples of four
+                else {
+                    dst[0] = acc.x;
+                    if (tok + 1u < p.M) dst[1] = acc.y;
+                    if (tok + 2u < p.M) dst[2] = acc.z;
+                    if (tok + 3u < p.M) dst[3] = acc.w;
+                }
+            }
+        }
+    }
+    cluster.sync();                                       // nobody leaves while a peer still reads its tile
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+    }
+}
+
+// fp32 -> bf16 hi / lo planes, element order unchanged (the dictionary: [K][C]).
+__global__ void split_planes_kernel(const float4* __restrict__ src, uint2* __restrict__ hi, uint2* __restrict__ lo,
+                                    size_t n4) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float4 v = src[i];
+        const __nv_bfloat162 h01 = __floats2bfloat162_rn(v.x, v.y), h23 = __floats2bfloat162_rn(v.z, v.w);
+        const __nv_bfloat162 l01 = __floats2bfloat162_rn(v.x - __low2float(h01), v.y - __high2float(h01));
+        const __nv_bfloat162 l23 = __floats2bfloat162_rn(v.z - __low2float(h23), v.w - __high2float(h23));
+        hi[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+        lo[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+    }
+}
+
+// Activations of any supported dtype/layout -> token-major bf16 planes [M][C].
+__global__ void x_planes_kernel(XView xv, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    const size_t n = static_cast<size_t>(xv.M) * xv.C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint32_t b = static_cast<uint32_t>(i / xv.C), c = static_cast<uint32_t>(i - static_cast<size_t>(b) * xv.C);
+        const float v = load_x(xv, c, b);
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        hi[i] = h;
+        if (lo) lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q{};
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// bf16 matrix [rows][cols] row-major; box = 64 columns x box_rows rows, 128-byte swizzle.
+// Rows past the end read as zero.
+CUtensorMap make_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    CUtensorMap m{};
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2u};
+    const cuuint32_t box[2] = {kBlockK, box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    EncodeFn fn = encode_fn();
+    if (!fn) throw Error(CSDR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) throw Error(CSDR_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string(rc) + ")");
+    return m;
+}
+
+// bf16 planes of one dictionary, cached on the fp32 atom buffer.
+struct Planes {
+    DevPtr buf;           // hi plane then lo plane
+    CUtensorMap map_hi, map_lo;
+};
+
+std::shared_ptr<Planes> planes_for(csdr_context* ctx, const csdr_segment* seg) {
+    DeviceBuffer* atoms = seg->atoms.get();
+    if (atoms->aux) return std::static_pointer_cast<Planes>(atoms->aux);
+    const Geometry& g = seg->g;
+    const size_t n = static_cast<size_t>(g.n_atoms) * g.cols;
+    auto pl = std::make_shared<Planes>();
+    pl->buf = std::make_shared<DeviceBuffer>(n * 4u, ctx->device);
+    __nv_bfloat16* hi = static_cast<__nv_bfloat16*>(pl->buf->ptr);
+    __nv_bfloat16* lo = hi + n;
+    {
+        LaunchScope ls(ctx, KC_DECODER_OP);
+        split_planes_kernel<<<static_cast<unsigned>(std::min<size_t>((n / 4u + 255u) / 256u, 4096u)), 256, 0, ctx->stream>>>(
+            static_cast<const float4*>(atoms->ptr), reinterpret_cast<uint2*>(hi), reinterpret_cast<uint2*>(lo), n / 4u);
+        ls.done("split_planes_kernel");
+    }
+    pl->map_hi = make_map(hi, g.n_atoms, g.cols, kTileM);
+    pl->map_lo = make_map(lo, g.n_atoms, g.cols, kTileM);
+    atoms->aux = pl;
+    return pl;
+}
+
+}  // namespace tma_detail
+
+bool dx_tma_supported(const csdr_context* ctx, const csdr_segment* seg, size_t batch) {
+    using namespace tma_detail;
+    const Geometry& g = seg->g;
+    (void)batch;
+    return ctx->tma && g.row_tiles() && g.n_atoms % kTileM == 0 && g.cols % kBlockK == 0 && encode_fn() != nullptr;
+}
+
+void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx) {
+    using namespace tma_detail;
+    const Geometry& g = seg->g;
+    const uint32_t M = static_cast<uint32_t>(a.batch);
+    auto planes = planes_for(ctx, seg);
+
+    // activations: in place when they already are what the loader wants
+    const bool in_place = a.x_dtype == CSDR_DTYPE_BF16 && a.x_layout == CSDR_LAYOUT_TOKEN_MAJOR &&
+                          (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (g.cols & 7u) == 0;
+    const bool has_lo = a.x_dtype == CSDR_DTYPE_F32;
+    const __nv_bfloat16* xhi = static_cast<const __nv_bfloat16*>(a.x);
+    const __nv_bfloat16* xlo = nullptr;
+    if (!in_place) {
+        const size_t n = static_cast<size_t>(M) * g.cols;
+        __nv_bfloat16* buf = static_cast<__nv_bfloat16*>(ctx->scratch_get(5, n * (has_lo ? 4u : 2u)));
+        XView xv{a.x, a.x_dtype, a.x_layout, g.cols, M, 0u, M};
+        LaunchScope ls(ctx, KC_DECODER_OP);
+        x_planes_kernel<<<static_cast<unsigned>(std::min<size_t>((n + 255u) / 256u, 2048u)), 256, 0, ctx->stream>>>(
+            xv, buf, has_lo ? buf + n : nullptr);
+        ls.done("x_planes_kernel");
+        xhi = buf;
+        xlo = has_lo ? buf + n : nullptr;
+    }
+    uint32_t N = 16;
+    while (N < 128u && N < M) N <<= 1;
+    const CUtensorMap map_xhi = make_map(xhi, M, g.cols, N);
+    const CUtensorMap map_xlo = has_lo ? make_map(xlo, M, g.cols, N) : map_xhi;
+
+    const uint32_t tok_tiles = (M + N - 1u) / N;
+    const uint32_t atom_tiles = g.n_atoms / kTileM;
+    const uint32_t n_kb = g.cols / kBlockK;
+    const uint32_t stage_bytes = 2u * kATile + (has_lo ? 2u : 1u) * N * 128u;
+    const uint32_t ptile_bytes = kTileM * (N + 4u) * 4u;
+
+    static bool attrs_set = false;
+    static int max_cluster = 8;
+    const size_t smem_max = ctx->smem_optin - 2048u;   // static barriers and alignment slack
+    if (!attrs_set) {
+        CSDR_CUDA(cudaFuncSetAttribute(hsdr_dx_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem_max)));
+        if (cudaFuncSetAttribute(hsdr_dx_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess)
+            max_cluster = 16;
+        else
+            (void)cudaGetLastError();
+        attrs_set = true;
+    }
+    // column ranges per tile: fill the GPU once, as a power of two that divides the 128 rows
+    uint32_t ranks = 1;
+    while (ranks * 2u <= static_cast<uint32_t>(max_cluster) && ranks * 2u <= n_kb &&
+           atom_tiles * tok_tiles * ranks * 2u <= static_cast<uint32_t>(ctx->sm_count))
+        ranks *= 2u;
+    const uint32_t kb_per_cta = (n_kb + ranks - 1u) / ranks;
+    uint32_t stages = std::min<uint32_t>(kMaxStages, static_cast<uint32_t>((smem_max - 1024u) / stage_bytes));
+    stages = std::max(1u, std::min(stages, kb_per_cta));
+    const size_t smem = std::max<size_t>(static_cast<size_t>(stages) * stage_bytes, ptile_bytes) + 1024u;
+
+    Params p{};
+    p.K = g.n_atoms;
+    p.M = M;
+    p.n_tile = N;
+    p.tmem_cols = std::max(32u, N);
+    p.n_kb = n_kb;
+    p.kb_per_cta = kb_per_cta;
+    p.stages = stages;
+    p.x_has_lo = has_lo ? 1u : 0u;
+    p.dx = dx;
+    p.status = ctx->status_word;
+
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(atom_tiles, tok_tiles, ranks);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = ranks;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (ranks > 8u) {
+        // a cluster of 16 must fit inside one GPC; fall back to 8 where it cannot be placed
+        int n_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&n_clusters, hsdr_dx_tma_kernel, &cfg) != cudaSuccess || n_clusters < 1) {
+            (void)cudaGetLastError();
+            max_cluster = 8;
+            launch_dx_tma(ctx, seg, a, dx);
+            return;
+        }
+    }
+    LaunchScope ls(ctx, KC_GEMM);
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_dx_tma_kernel, planes->map_hi, planes->map_lo, map_xhi, map_xlo, p));
+    ls.done("hsdr_dx_tma_kernel");
+}
+
+}  // namespace csdr
