@@ -371,21 +371,29 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
     };
     fetch(hw);
 
-    // stage the Dx slice (zero beyond the last token)
-    for (uint32_t i = tid; i < K * (kWideTokens / 4u); i += kWideThreads) {
-        const uint32_t a = i / (kWideTokens / 4u), q = i - a * (kWideTokens / 4u);
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float* src = dx + static_cast<size_t>(a) * M + t0 + q * 4u;
-        if (q * 4u + 3u < tw && (M & 3u) == 0) v = __ldcg(reinterpret_cast<const float4*>(src));
-        else {
-            if (q * 4u + 0u < tw) v.x = __ldcg(src + 0);
-            if (q * 4u + 1u < tw) v.y = __ldcg(src + 1);
-            if (q * 4u + 2u < tw) v.z = __ldcg(src + 2);
-            if (q * 4u + 3u < tw) v.w = __ldcg(src + 3);
-        }
-        reinterpret_cast<float4*>(dxs)[i] = v;
-    }
     if (tid < kWideMaxSlots) gs[tid] = tid < S ? scales[tid] : 0.0f;
+    // Dx is the output of the kernel before this one on the stream
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // stage the Dx slice (zero beyond the last token): asynchronous 16-byte copies, all of a
+    // thread's requests in flight at once
+    if ((M & 3u) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15u) == 0) {
+        for (uint32_t i = tid; i < K * (kWideTokens / 4u); i += kWideThreads) {
+            const uint32_t a = i / (kWideTokens / 4u), q = i - a * (kWideTokens / 4u);
+            const float* src = dx + static_cast<size_t>(a) * M + t0 + q * 4u;
+            const uint32_t valid = q * 4u < tw ? min(16u, (tw - q * 4u) * 4u) : 0u;   // bytes; the rest reads as zero
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                             static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
+                         "l"(valid ? src : dx), "r"(valid)
+                         : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        for (uint32_t i = tid; i < K * kWideTokens; i += kWideThreads) {
+            const uint32_t a = i / kWideTokens, t = i - a * kWideTokens;
+            dxs[i] = t < tw ? __ldcg(dx + static_cast<size_t>(a) * M + t0 + t) : 0.0f;
+        }
+    }
     __syncthreads();
 
     const float4* dxs4 = reinterpret_cast<const float4*>(dxs) + l16;
@@ -405,29 +413,45 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
         const uint32_t off =
             static_cast<uint32_t>(reinterpret_cast<uintptr_t>(codes + static_cast<size_t>(r0) * slots) >> 1) & 1u;
         const uint16_t* crow = reinterpret_cast<const uint16_t*>(my_csm) + off;
+        // Four rows advance together: their lookups are independent, which keeps enough
+        // shared-memory reads in flight per warp. Rows past the end of the run read codes that
+        // are real (an earlier block's) or zero, so their lookups stay inside the slice; their
+        // results are never stored.
         float out[kWideRows][4];
 #pragma unroll
-        for (uint32_t rb = 0; rb < kWideRows; ++rb) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (rb < nrows) {
-                const uint16_t* cr = crow + rb * slots;
-                for (uint32_t st = 0; st < S; ++st) {
-                    const uint32_t gbits = __float_as_uint(gs[st]);
-#pragma unroll 4
-                    for (uint32_t j = 0; j < k; ++j) {
-                        const uint32_t code = cr[st * k + j];
-                        const float scale = __uint_as_float(gbits ^ ((code & 0x8000u) << 16));
-                        const float4 v = dxs4[(code & 0x7FFFu) * (kWideTokens / 4u)];
-                        acc.x = fmaf(scale, v.x, acc.x);
-                        acc.y = fmaf(scale, v.y, acc.y);
-                        acc.z = fmaf(scale, v.z, acc.z);
-                        acc.w = fmaf(scale, v.w, acc.w);
+        for (uint32_t rq = 0; rq < kWideRows; rq += 4u) {
+            float4 acc[4];
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            const uint16_t* cr = crow + rq * slots;
+            for (uint32_t st = 0; st < S; ++st) {
+                const uint32_t gbits = __float_as_uint(gs[st]);
+#pragma unroll 2
+                for (uint32_t j = 0; j < k; ++j) {
+                    uint32_t code[4];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4u; ++i) code[i] = cr[i * slots + st * k + j];
+                    float4 v[4];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4u; ++i) v[i] = dxs4[(code[i] & 0x7FFFu) * (kWideTokens / 4u)];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4u; ++i) {
+                        const float scale = __uint_as_float(gbits ^ ((code[i] & 0x8000u) << 16));
+                        acc[i].x = fmaf(scale, v[i].x, acc[i].x);
+                        acc[i].y = fmaf(scale, v[i].y, acc[i].y);
+                        acc[i].z = fmaf(scale, v[i].z, acc[i].z);
+                        acc[i].w = fmaf(scale, v[i].w, acc[i].w);
                     }
                 }
-                const float bias = yv.bias ? yv.bias[r0 + rb] : 0.0f;
-                acc.x += bias; acc.y += bias; acc.z += bias; acc.w += bias;
             }
-            out[rb][0] = acc.x; out[rb][1] = acc.y; out[rb][2] = acc.z; out[rb][3] = acc.w;
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i) {
+                const float bias = (yv.bias && rq + i < nrows) ? yv.bias[r0 + rq + i] : 0.0f;
+                out[rq + i][0] = acc[i].x + bias;
+                out[rq + i][1] = acc[i].y + bias;
+                out[rq + i][2] = acc[i].z + bias;
+                out[rq + i][3] = acc[i].w + bias;
+            }
         }
         const uint32_t tl = 4u * l16;               // first token of this lane inside the slice
         if (tl >= tw) continue;
@@ -551,9 +575,19 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
         rows_per_cta = (rows_per_cta + kWideRows - 1u) / kWideRows * kWideRows;
         const uint32_t runs = (g.rows + rows_per_cta - 1u) / rows_per_cta;
         LaunchScope ls(ctx, KC_GATHER);
-        hsdr_gather_wide_kernel<<<dim3(runs, slices), kWideThreads, smem, ctx->stream>>>(
-            seg->codes_ptr(), g.rows, g.n_stages, g.k, static_cast<const float*>(seg->scales->ptr), dx,
-            g.n_atoms, M, rows_per_cta, yv);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(runs, slices, 1);
+        cfg.blockDim = dim3(kWideThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_gather_wide_kernel, seg->codes_ptr(), g.rows, g.n_stages, g.k,
+                                     static_cast<const float*>(seg->scales->ptr), static_cast<const float*>(dx),
+                                     g.n_atoms, M, rows_per_cta, yv));
         ls.done("hsdr_gather_wide_kernel");
     }
 }

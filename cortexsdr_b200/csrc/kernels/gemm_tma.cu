@@ -14,11 +14,11 @@
 //     ring of stages and arms each stage's mbarrier with the expected byte count; warp 1 waits
 //     for a stage, issues tcgen05.mma (hi*hi + lo*hi [+ hi*lo]) and commits the stage back to the
 //     loader; warps 2-5 read the accumulators out of tensor memory at the end;
-//   * the column ranges of one output tile form a thread-block cluster: every CTA parks its
-//     partial tile in its own shared memory, and after a cluster barrier each CTA sums a slice
-//     of the rows over all peers (distributed shared memory, fixed rank order, so the result
-//     does not depend on timing) and writes that slice of Dx. No partials in global memory and
-//     no separate reduction kernel.
+//   * the column ranges of one output tile form a thread-block cluster (co-scheduled by the
+//     hardware): every CTA writes its accumulator tile to a partial buffer (L2-resident), the
+//     cluster meets at its barrier, and each CTA sums its share of the rows over the ranks in
+//     rank order (so the result does not depend on timing) and writes those rows of Dx. No
+//     separate reduction kernel, no spin-waits between CTAs.
 //
 // Every mbarrier wait is a bounded try_wait loop; a wait that runs out sets the context's status
 // word, the roles stop issuing work, and the CTA still meets its cluster barriers and frees its
@@ -112,8 +112,23 @@ struct Params {
     uint32_t stages;
     uint32_t x_has_lo;
     float* dx;              // [K][M]
+    float* part;            // [tile][rank][128][N] accumulator tiles of the column ranges
     int* status;
+    unsigned long long* trace;   // optional: 16 global-timer stamps per CTA (phase boundaries)
+    uint32_t trace_ctas;
 };
+
+// One thread of a role records when that role passed a phase boundary.
+__device__ __forceinline__ void stamp(const Params& p, int slot) {
+    if (p.trace) {
+        const uint32_t cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        if (cta < p.trace_ctas) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            p.trace[cta * 16u + slot] = t;
+        }
+    }
+}
 
 // grid (K/128, token tiles, column ranges); cluster (1, 1, column ranges)
 __global__ void __launch_bounds__(kThreads, 1)
@@ -121,6 +136,9 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
                    const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                    const __grid_constant__ Params p) {
     extern __shared__ __align__(1024) unsigned char tma_smem_raw[];
+    // the gather behind this kernel may start its prologue (code prefetch) right away; it waits
+    // for this grid's completion before it touches Dx
+    asm volatile("griddepcontrol.launch_dependents;");
     __shared__ __align__(8) unsigned long long full_bar[kMaxStages];
     __shared__ __align__(8) unsigned long long empty_bar[kMaxStages];
     __shared__ __align__(8) unsigned long long accum_bar;
@@ -142,6 +160,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
     const uint32_t n_it = kb_end - kb_begin;
 
     if (tid == 0) {
+        stamp(p, 0);
         for (uint32_t i = 0; i < kMaxStages; ++i) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[i])));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&empty_bar[i])));
@@ -160,6 +179,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    if (tid == 0) stamp(p, 1);
 
     if (warp == 0) {
         // ---- loader ----
@@ -193,6 +213,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
                     break;
                 }
                 if (failed_s) break;
+                if (it == 0) stamp(p, 2);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_hi = smem_u32(smem + s * stage_bytes), a_lo = a_hi + kATile;
                 const uint32_t b_hi = a_hi + 2u * kATile, b_lo = b_hi + b_tile;
@@ -212,17 +233,30 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                              smem_u32(&accum_bar))
                          : "memory");
+            stamp(p, 3);
         }
     }
-    // ---- accumulators -> this CTA's partial tile in shared memory (stage memory is free now) ----
-    const uint32_t pstride = N + 4u;                      // floats; keeps 128-bit row writes conflict-free
+    // ---- column-range reduction through L2. Every CTA writes its accumulator tile to the
+    // launch's partial buffer, the cluster meets at its barrier (release/acquire at cluster scope
+    // covers those global writes), and each CTA then sums its share of the tile's rows over the
+    // ranks, in rank order, into Dx. (Remote shared memory was measured at ~20 GB/s per SM on
+    // this part, several times slower than the same exchange through L2.) ----
+    const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+    float* part = p.part + static_cast<size_t>(tile) * n_ranks * kTileM * N;
+    const uint32_t pstride = N + 4u;
     float* ptile = reinterpret_cast<float*>(smem);
+    bool done = true;
     if (warp >= 2) {
-        const bool done = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&accum_bar), 0u));   // warp-uniform
+        done = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&accum_bar), 0u));   // warp-uniform
         if (!done) failed_s = 1;
+        if (tid == 64) stamp(p, 4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t quad = warp & 3u;                  // TMEM lanes 32*quad .. +31
-        float* prow = ptile + static_cast<size_t>(quad * 32u + lane) * pstride;
+        const uint32_t row = quad * 32u + lane;
+        // rows of the accumulator tile go to shared memory first (stage memory is free: this
+        // CTA's MMAs are done and nobody else touches it), padded so that 128-bit row writes do
+        // not collide; the copy to global memory below is then fully coalesced
+        float* prow = ptile + static_cast<size_t>(row) * pstride;
         for (uint32_t ch = 0; ch < N / 16u; ++ch) {
             uint32_t r[16];
             if (done && n_it > 0u) {
@@ -246,41 +280,80 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    {
+        // one rank and an aligned token count: the tile is Dx itself; otherwise this rank's slab
+        const bool direct = n_ranks == 1u && (p.M & 3u) == 0;
+        const uint32_t n4 = N / 4u;
+        for (uint32_t i = tid; i < kTileM * n4; i += kThreads) {
+            const uint32_t row = i / n4, c4 = i - row * n4;
+            const float4 v = *reinterpret_cast<const float4*>(ptile + static_cast<size_t>(row) * pstride + c4 * 4u);
+            if (direct) {
+                if (tok0 + c4 * 4u < p.M)
+                    *reinterpret_cast<float4*>(p.dx + static_cast<size_t>(atom0 + row) * p.M + tok0 + c4 * 4u) = v;
+            } else {
+                *reinterpret_cast<float4*>(part + (static_cast<size_t>(rank) * kTileM + row) * N + c4 * 4u) = v;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
     if (tid == 0 && failed_s) atomicExch(p.status, 1);    // a bounded wait ran out: the host reports it
-    cluster.sync();                                       // every partial tile is in place
-
-    // ---- each CTA sums its slice of the rows over the cluster, in rank order ----
-    if (warp >= 2) {
-        const uint32_t t = tid - 64u;
-        const uint32_t rows_mine = kTileM / n_ranks;
-        const uint32_t row_begin = rank * rows_mine;
+    if (tid == 0) stamp(p, 5);
+    cluster.sync();                                       // every rank's tile is in the partial buffer
+    if (tid == 0) stamp(p, 6);
+    if (!(n_ranks == 1u && (p.M & 3u) == 0)) {
+        const uint32_t rows_each = (kTileM + n_ranks - 1u) / n_ranks;
+        const uint32_t row_begin = min(kTileM, rank * rows_each);
+        const uint32_t rows_mine = min(kTileM, row_begin + rows_each) - row_begin;
         const uint32_t n4 = N / 4u;
         const bool vec = (p.M & 3u) == 0;
-        for (uint32_t i = t; i < rows_mine * n4; i += 128u) {
-            const uint32_t row = row_begin + i / n4, c4 = i % n4;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t r = 0; r < n_ranks; ++r) {
-                const float* peer = cluster.map_shared_rank(ptile, r);
-                const float4 v = *reinterpret_cast<const float4*>(peer + static_cast<size_t>(row) * pstride + c4 * 4u);
-                acc.x += v.x;
-                acc.y += v.y;
-                acc.z += v.z;
-                acc.w += v.w;
+        const float* tile_part = p.part + static_cast<size_t>(tile) * n_ranks * kTileM * N;
+        // two items per pass, every rank's piece of both requested before the first add: the
+        // loads are L2 round trips and must overlap
+        for (uint32_t i0 = tid; i0 < rows_mine * n4; i0 += 2u * kThreads) {
+            float4 v[2][16];
+#pragma unroll
+            for (uint32_t h = 0; h < 2u; ++h) {
+                const uint32_t i = i0 + h * kThreads;
+                if (i < rows_mine * n4) {
+                    const uint32_t row = row_begin + i / n4, c4 = i % n4;
+                    const float* src = tile_part + static_cast<size_t>(row) * N + c4 * 4u;
+#pragma unroll
+                    for (uint32_t r = 0; r < 16u; ++r)
+                        if (r < n_ranks)
+                            v[h][r] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(r) * kTileM * N));
+                }
             }
-            const uint32_t atom = atom0 + row, tok = tok0 + c4 * 4u;
-            if (atom < p.K && tok < p.M) {
-                float* dst = p.dx + static_cast<size_t>(atom) * p.M + tok;
-                if (vec) *reinterpret_cast<float4*>(dst) = acc;     // tok and M are multiples of four
-                else {
-                    dst[0] = acc.x;
-                    if (tok + 1u < p.M) dst[1] = acc.y;
-                    if (tok + 2u < p.M) dst[2] = acc.z;
-                    if (tok + 3u < p.M) dst[3] = acc.w;
+#pragma unroll
+            for (uint32_t h = 0; h < 2u; ++h) {
+                const uint32_t i = i0 + h * kThreads;
+                if (i >= rows_mine * n4) break;
+                const uint32_t row = row_begin + i / n4, c4 = i % n4;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (uint32_t r = 0; r < 16u; ++r)
+                    if (r < n_ranks) {
+                        acc.x += v[h][r].x;
+                        acc.y += v[h][r].y;
+                        acc.z += v[h][r].z;
+                        acc.w += v[h][r].w;
+                    }
+                const uint32_t atom = atom0 + row, tok = tok0 + c4 * 4u;
+                if (atom < p.K && tok < p.M) {
+                    float* dst = p.dx + static_cast<size_t>(atom) * p.M + tok;
+                    if (vec) *reinterpret_cast<float4*>(dst) = acc;     // tok and M are multiples of four
+                    else {
+                        dst[0] = acc.x;
+                        if (tok + 1u < p.M) dst[1] = acc.y;
+                        if (tok + 2u < p.M) dst[2] = acc.z;
+                        if (tok + 3u < p.M) dst[3] = acc.w;
+                    }
                 }
             }
         }
     }
-    cluster.sync();                                       // nobody leaves while a peer still reads its tile
+    if (tid == 0) stamp(p, 7);
+    __syncthreads();
     if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
@@ -415,7 +488,6 @@ void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
     const uint32_t atom_tiles = g.n_atoms / kTileM;
     const uint32_t n_kb = g.cols / kBlockK;
     const uint32_t stage_bytes = 2u * kATile + (has_lo ? 2u : 1u) * N * 128u;
-    const uint32_t ptile_bytes = kTileM * (N + 4u) * 4u;
 
     static bool attrs_set = false;
     static int max_cluster = 8;
@@ -429,15 +501,51 @@ void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
             (void)cudaGetLastError();
         attrs_set = true;
     }
-    // column ranges per tile: fill the GPU once, as a power of two that divides the 128 rows
-    uint32_t ranks = 1;
-    while (ranks * 2u <= static_cast<uint32_t>(max_cluster) && ranks * 2u <= n_kb &&
-           atom_tiles * tok_tiles * ranks * 2u <= static_cast<uint32_t>(ctx->sm_count))
-        ranks *= 2u;
-    const uint32_t kb_per_cta = (n_kb + ranks - 1u) / ranks;
     uint32_t stages = std::min<uint32_t>(kMaxStages, static_cast<uint32_t>((smem_max - 1024u) / stage_bytes));
-    stages = std::max(1u, std::min(stages, kb_per_cta));
-    const size_t smem = std::max<size_t>(static_cast<size_t>(stages) * stage_bytes, ptile_bytes) + 1024u;
+    stages = std::max(1u, stages);
+    const size_t smem = std::max<size_t>(static_cast<size_t>(stages) * stage_bytes,
+                                         static_cast<size_t>(kTileM) * (N + 4u) * 4u) + 1024u;
+
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+
+    // Column ranges per tile = cluster size: the largest one for which every cluster of the
+    // launch is resident at once (the hardware places a cluster inside one GPC, so the answer
+    // depends on the cluster size; asked once per (size, shared memory) and remembered).
+    const uint32_t tiles = atom_tiles * tok_tiles;
+    static std::unordered_map<uint64_t, int> fit;      // (ranks, smem) -> clusters resident at once
+    uint32_t ranks = 1;
+    for (uint32_t r = std::min<uint32_t>({static_cast<uint32_t>(max_cluster), n_kb,
+                                          std::max(1u, static_cast<uint32_t>(ctx->sm_count) / tiles)});
+         r > 1u; --r) {
+        const uint64_t key = (static_cast<uint64_t>(r) << 32) | static_cast<uint64_t>(smem);
+        auto itf = fit.find(key);
+        if (itf == fit.end()) {
+            cfg.gridDim = dim3(atom_tiles, tok_tiles, r);
+            attr[0].val.clusterDim.z = r;
+            int n_clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&n_clusters, hsdr_dx_tma_kernel, &cfg) != cudaSuccess) {
+                (void)cudaGetLastError();
+                n_clusters = 0;
+            }
+            itf = fit.emplace(key, n_clusters).first;
+        }
+        if (itf->second >= static_cast<int>(tiles)) {
+            ranks = r;
+            break;
+        }
+    }
+    const uint32_t kb_per_cta = (n_kb + ranks - 1u) / ranks;
+    cfg.gridDim = dim3(atom_tiles, tok_tiles, ranks);
+    attr[0].val.clusterDim.z = ranks;
 
     Params p{};
     p.K = g.n_atoms;
@@ -449,29 +557,18 @@ void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
     p.stages = stages;
     p.x_has_lo = has_lo ? 1u : 0u;
     p.dx = dx;
+    p.part = ranks > 1u || (M & 3u) ? static_cast<float*>(ctx->scratch_get(
+                                           1, static_cast<size_t>(tiles) * ranks * kTileM * N * 4u))
+                                    : nullptr;
     p.status = ctx->status_word;
+    p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
+    p.trace_ctas = static_cast<uint32_t>(ctx->sm_count) * 2u;
 
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(atom_tiles, tok_tiles, ranks);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = ranks;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (ranks > 8u) {
-        // a cluster of 16 must fit inside one GPC; fall back to 8 where it cannot be placed
-        int n_clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&n_clusters, hsdr_dx_tma_kernel, &cfg) != cudaSuccess || n_clusters < 1) {
-            (void)cudaGetLastError();
-            max_cluster = 8;
-            launch_dx_tma(ctx, seg, a, dx);
-            return;
-        }
+    if (std::getenv("CSDR_DEBUG_TMA")) {
+        int n_clusters = -1;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, hsdr_dx_tma_kernel, &cfg);
+        fprintf(stderr, "dx_tma: M=%u N=%u tiles=%u ranks=%u stages=%u smem=%zu maxActiveClusters=%d (%s)\n", M, N,
+                tiles, ranks, stages, smem, n_clusters, cudaGetErrorString(e));
     }
     LaunchScope ls(ctx, KC_GEMM);
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_dx_tma_kernel, planes->map_hi, planes->map_lo, map_xhi, map_xlo, p));
