@@ -112,7 +112,7 @@ struct csdr_context {
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
     bool tensor_cores = true;   // CSDR_TENSOR_CORES=0 keeps wide batches on the CUDA-core kernels
     bool tma = true;            // CSDR_TMA=0 keeps the register-fed tensor-core kernel
-    size_t tc_min_batch = 16;   // CSDR_TC_MIN_BATCH: smallest batch sent to the tcgen05 path
+    size_t tc_min_batch = 8;    // CSDR_TC_MIN_BATCH: smallest batch sent to the tcgen05 path
     uint64_t launches_by_class[csdr::KC_COUNT] = {};
     // When on, every launch is bracketed by two events on the stream (profile_read resolves them).
     bool profiling = false;
@@ -180,9 +180,10 @@ void launch_dequantize(csdr_context* ctx, int fmt_id, const uint8_t* data_dev, s
 int dequant_format_id(const char* fmt);               // -1 when unknown
 size_t dequant_output_count(int fmt_id, size_t nbytes);  // throws on bad size
 
-// Gather phase alone for a 16-token tile: dx is [n_atoms][16] fp32 (two-kernel layout).
-void launch_gather_tile16(csdr_context* ctx, const csdr_segment* seg, const float* dx, float* y, int y_layout,
-                          uint32_t m_total, uint32_t b0, uint32_t m, const float* bias);
+// Gather phase alone for one token tile: dx is [n_atoms][mt] fp32 (two-kernel layout),
+// mt one of 1, 2, 4, 8, 16 and at least m.
+void launch_gather_tile(csdr_context* ctx, const csdr_segment* seg, const float* dx, int mt, float* y, int y_layout,
+                        uint32_t m_total, uint32_t b0, uint32_t m, const float* bias);
 
 void launch_dense_matmul(csdr_context* ctx, const float* W_dev, uint32_t R, uint32_t C,
                          const MatmulArgs& a);

@@ -519,7 +519,14 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
     const size_t dx_floats = static_cast<size_t>(g.n_atoms) * M;
     float* dx = static_cast<float*>(ctx->scratch_get(0, std::max<size_t>(dx_floats * 4u, static_cast<size_t>(g.n_atoms) * 64u)));
     const bool use_tma = dx_tma_supported(ctx, seg, a.batch);
-    if (use_tma) launch_dx_tma(ctx, seg, a, dx);
+    // up to 16 tokens: Dx rows padded to the compact gather's tile width (the register-fed
+    // kernel writes rows of exactly M, so there only M == 16 qualifies)
+    uint32_t tile_mt = 0;
+    if (M <= 16u && (use_tma || M == 16u)) {
+        tile_mt = 1;
+        while (tile_mt < M) tile_mt <<= 1;
+    }
+    if (use_tma) launch_dx_tma(ctx, seg, a, dx, tile_mt ? tile_mt : M);
 
     TcParams p{};
     p.D = static_cast<const float*>(seg->atoms->ptr);
@@ -553,9 +560,9 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
             part, static_cast<uint32_t>(dx_floats), n_split, dx);
         ls.done("dx_reduce_kernel");
     }
-    if (M == 16u) {
-        // one 16-token tile: Dx is exactly the [n_atoms][16] block the compact gather expects
-        launch_gather_tile16(ctx, seg, dx, a.y, a.y_layout, M, 0u, M, a.bias);
+    if (tile_mt) {
+        // one token tile: Dx is exactly the [n_atoms][mt] block the compact gather expects
+        launch_gather_tile(ctx, seg, dx, static_cast<int>(tile_mt), a.y, a.y_layout, M, 0u, M, a.bias);
         return;
     }
     {

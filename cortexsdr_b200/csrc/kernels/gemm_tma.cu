@@ -105,6 +105,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 
 struct Params {
     uint32_t K, M;          // atoms, tokens
+    uint32_t dx_stride;     // floats between Dx rows (>= M)
     uint32_t n_tile;        // MMA N: 16, 32, 64 or 128
     uint32_t tmem_cols;     // power of two >= max(32, n_tile)
     uint32_t n_kb;          // C / 64
@@ -282,14 +283,14 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
     __syncthreads();
     {
         // one rank and an aligned token count: the tile is Dx itself; otherwise this rank's slab
-        const bool direct = n_ranks == 1u && (p.M & 3u) == 0;
+        const bool direct = n_ranks == 1u && ((p.M | p.dx_stride) & 3u) == 0;
         const uint32_t n4 = N / 4u;
         for (uint32_t i = tid; i < kTileM * n4; i += kThreads) {
             const uint32_t row = i / n4, c4 = i - row * n4;
             const float4 v = *reinterpret_cast<const float4*>(ptile + static_cast<size_t>(row) * pstride + c4 * 4u);
             if (direct) {
                 if (tok0 + c4 * 4u < p.M)
-                    *reinterpret_cast<float4*>(p.dx + static_cast<size_t>(atom0 + row) * p.M + tok0 + c4 * 4u) = v;
+                    *reinterpret_cast<float4*>(p.dx + static_cast<size_t>(atom0 + row) * p.dx_stride + tok0 + c4 * 4u) = v;
             } else {
                 *reinterpret_cast<float4*>(part + (static_cast<size_t>(rank) * kTileM + row) * N + c4 * 4u) = v;
             }
@@ -301,12 +302,12 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
     if (tid == 0) stamp(p, 5);
     cluster.sync();                                       // every rank's tile is in the partial buffer
     if (tid == 0) stamp(p, 6);
-    if (!(n_ranks == 1u && (p.M & 3u) == 0)) {
+    if (!(n_ranks == 1u && ((p.M | p.dx_stride) & 3u) == 0)) {
         const uint32_t rows_each = (kTileM + n_ranks - 1u) / n_ranks;
         const uint32_t row_begin = min(kTileM, rank * rows_each);
         const uint32_t rows_mine = min(kTileM, row_begin + rows_each) - row_begin;
         const uint32_t n4 = N / 4u;
-        const bool vec = (p.M & 3u) == 0;
+        const bool vec = ((p.M | p.dx_stride) & 3u) == 0;
         const float* tile_part = p.part + static_cast<size_t>(tile) * n_ranks * kTileM * N;
         // two items per pass, every rank's piece of both requested before the first add: the
         // loads are L2 round trips and must overlap
@@ -340,7 +341,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
                     }
                 const uint32_t atom = atom0 + row, tok = tok0 + c4 * 4u;
                 if (atom < p.K && tok < p.M) {
-                    float* dst = p.dx + static_cast<size_t>(atom) * p.M + tok;
+                    float* dst = p.dx + static_cast<size_t>(atom) * p.dx_stride + tok;
                     if (vec) *reinterpret_cast<float4*>(dst) = acc;     // tok and M are multiples of four
                     else {
                         dst[0] = acc.x;
@@ -456,7 +457,7 @@ bool dx_tma_supported(const csdr_context* ctx, const csdr_segment* seg, size_t b
     return ctx->tma && g.row_tiles() && g.n_atoms % kTileM == 0 && g.cols % kBlockK == 0 && encode_fn() != nullptr;
 }
 
-void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx) {
+void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride) {
     using namespace tma_detail;
     const Geometry& g = seg->g;
     const uint32_t M = static_cast<uint32_t>(a.batch);
@@ -550,6 +551,7 @@ void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
     Params p{};
     p.K = g.n_atoms;
     p.M = M;
+    p.dx_stride = dx_stride;
     p.n_tile = N;
     p.tmem_cols = std::max(32u, N);
     p.n_kb = n_kb;
@@ -557,7 +559,7 @@ void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
     p.stages = stages;
     p.x_has_lo = has_lo ? 1u : 0u;
     p.dx = dx;
-    p.part = ranks > 1u || (M & 3u) ? static_cast<float*>(ctx->scratch_get(
+    p.part = ranks > 1u || ((M | dx_stride) & 3u) ? static_cast<float*>(ctx->scratch_get(
                                            1, static_cast<size_t>(tiles) * ranks * kTileM * N * 4u))
                                     : nullptr;
     p.status = ctx->status_word;

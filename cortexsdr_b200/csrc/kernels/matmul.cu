@@ -586,10 +586,10 @@ void dispatch_mt(int mt, F&& f) {
 
 }  // namespace
 
-void launch_gather_tile16(csdr_context* ctx, const csdr_segment* seg, const float* dx, float* y, int y_layout,
-                          uint32_t m_total, uint32_t b0, uint32_t m, const float* bias) {
+void launch_gather_tile(csdr_context* ctx, const csdr_segment* seg, const float* dx, int mt, float* y, int y_layout,
+                        uint32_t m_total, uint32_t b0, uint32_t m, const float* bias) {
     YView yv{y, y_layout, seg->g.rows, m_total, b0, m, bias};
-    launch_gather_t<16>(ctx, seg, dx, yv);
+    dispatch_mt(mt, [&](auto mtc) { launch_gather_t<decltype(mtc)::value>(ctx, seg, dx, yv); });
 }
 
 void launch_unpack(csdr_context* ctx, const uint16_t* codes, size_t n, int32_t* idx, int8_t* sign) {
