@@ -482,7 +482,22 @@ int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const*
         }
         bool all_tc = true;
         for (size_t i = 0; i < n_segs; ++i) all_tc = all_tc && tcgen05_supported(ctx, segs[i], batch);
-        if (all_tc) {  // wide batch: each projection goes to the tensor cores on its own
+        if (all_tc) {
+            // wide batch: the activations become bf16 planes once; groups of up to four
+            // segments share one projection launch (and, up to 16 tokens, one gather launch)
+            bool grouped = true;
+            for (size_t i0 = 0; i0 < n_segs && grouped; i0 += 4)
+                grouped = wide_group_supported(ctx, segs + i0, static_cast<uint32_t>(std::min<size_t>(4, n_segs - i0)), batch);
+            if (grouped) {
+                const XPlanesView xp = make_x_planes(ctx, x_dev, x_dtype, x_layout, static_cast<uint32_t>(batch), segs[0]->g.cols);
+                for (size_t i0 = 0; i0 < n_segs; i0 += 4) {
+                    const uint32_t n = static_cast<uint32_t>(std::min<size_t>(4, n_segs - i0));
+                    WideOut outs[4];
+                    for (uint32_t i = 0; i < n; ++i) outs[i] = WideOut{ys_dev[i0 + i], nullptr, nullptr};
+                    launch_matmul_wide_group(ctx, segs + i0, n, xp, static_cast<uint32_t>(batch), outs, y_layout);
+                }
+                return;
+            }
             for (size_t i = 0; i < n_segs; ++i) {
                 MatmulArgs a;
                 a.x = x_dev;

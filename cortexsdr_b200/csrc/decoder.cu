@@ -14,6 +14,7 @@
 
 #include "internal.hpp"
 #include "kernels/decoder_ops.hpp"
+#include "kernels/gemm_tcgen05.hpp"
 
 using namespace csdr;
 
@@ -92,6 +93,10 @@ struct csdr_decoder {
     std::vector<int32_t> pos_host;
     DevPtr pos_dev, tokens_dev, seq_of, pos_of, next_dev;
     DevPtr hidden, normed, q, k, v, att, att_full, proj, gate, up, act_full, staged, logits, logits_l;
+    // bf16 hi/lo planes of the three activation widths the projections consume (hidden,
+    // attention output, SwiGLU product) for steps that run on the tensor cores
+    DevPtr xp_h, xp_att, xp_act;
+    bool planes_capable = false;
     ~csdr_decoder() {
         auto drop = [](Linear& l) {
             if (l.shard) csdr_segment_destroy(l.shard);
@@ -206,6 +211,61 @@ void embed(csdr_decoder* d, uint32_t T) {
     else launch_decode_rows(d->ctx, d->emb.seg, I32(d->tokens_dev), T, F(d->hidden));
 }
 
+__nv_bfloat16* BF(const DevPtr& p) { return static_cast<__nv_bfloat16*>(p->ptr); }
+
+// One group of linears over activation planes: a projection launch plus a gather launch.
+void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const DevPtr& planes, uint32_t T, uint32_t width,
+          std::initializer_list<WideOut> outs) {
+    const csdr_segment* segs[4];
+    WideOut o[4];
+    uint32_t n = 0;
+    auto it = outs.begin();
+    for (const Linear* l : ls) {
+        segs[n] = l->use();
+        o[n++] = *it++;
+    }
+    const XPlanesView xp{BF(planes), BF(planes) + static_cast<size_t>(T) * width};
+    launch_matmul_wide_group(d->ctx, segs, n, xp, T, o, CSDR_LAYOUT_TOKEN_MAJOR);
+}
+
+// The block loop for steps of at least the tensor-core threshold on one GPU: every glue kernel
+// hands its result to the next projection as bf16 planes, q|k|v and gate|up share a projection
+// launch and a gather launch, and the two residual additions ride on the gathers of the output
+// and down projections. Same arithmetic as run_blocks otherwise.
+void run_blocks_planes(csdr_decoder* d, uint32_t T) {
+    const csdr_decoder_config& c = d->cfg;
+    csdr_context* ctx = d->ctx;
+    const uint32_t H = c.hidden, HD = c.head_dim;
+    __nv_bfloat16* h_hi = BF(d->xp_h);
+    __nv_bfloat16* h_lo = h_hi + static_cast<size_t>(T) * H;
+    __nv_bfloat16* a_hi = BF(d->xp_att);
+    __nv_bfloat16* a_lo = a_hi + static_cast<size_t>(T) * d->QD_l;
+    __nv_bfloat16* i_hi = BF(d->xp_act);
+    __nv_bfloat16* i_lo = i_hi + static_cast<size_t>(T) * d->I_l;
+    op_rmsnorm_planes(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, h_hi, h_lo);
+    for (uint32_t li = 0; li < c.n_layers; ++li) {
+        Layer& L = d->layers[li];
+        wide(d, {&L.q, &L.k, &L.v}, d->xp_h, T, H,
+             {WideOut{F(d->q), nullptr, nullptr}, WideOut{F(d->k), nullptr, nullptr}, WideOut{F(d->v), nullptr, nullptr}});
+        float* kc = F(d->kcache) + li * d->cache_layer_stride;
+        float* vc = F(d->vcache) + li * d->cache_layer_stride;
+        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
+                      c.max_seq, c.rope_theta);
+        op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, nullptr,
+                     a_hi, a_lo);
+        wide(d, {&L.o}, d->xp_att, T, d->QD_l, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
+        op_rmsnorm_planes(ctx, F(d->hidden), F(L.ffn_norm), T, H, c.rms_eps, h_hi, h_lo);
+        wide(d, {&L.gate, &L.up}, d->xp_h, T, H,
+             {WideOut{F(d->gate), nullptr, nullptr}, WideOut{F(d->up), nullptr, nullptr}});
+        op_silu_mul_planes(ctx, F(d->gate), F(d->up), static_cast<size_t>(T) * d->I_l, i_hi, i_lo);
+        wide(d, {&L.down}, d->xp_act, T, d->I_l, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
+        if (li + 1 < c.n_layers)
+            op_rmsnorm_planes(ctx, F(d->hidden), F(d->layers[li + 1].attn_norm), T, H, c.rms_eps, h_hi, h_lo);
+        else
+            op_rmsnorm(ctx, F(d->hidden), F(d->out_norm), T, H, c.rms_eps, F(d->normed));
+    }
+}
+
 // All blocks over T tokens whose (sequence, position) pairs sit in seq_of/pos_of; leaves the
 // final-normed hidden states in d->normed.
 void run_blocks(csdr_decoder* d, uint32_t T) {
@@ -213,6 +273,10 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
     csdr_context* ctx = d->ctx;
     const uint32_t H = c.hidden, HD = c.head_dim;
     const bool tp = d->P > 1;
+    if (d->planes_capable && ctx->tensor_cores && ctx->tma && T >= ctx->tc_min_batch) {
+        run_blocks_planes(d, T);
+        return;
+    }
     op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, F(d->normed));
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         Layer& L = d->layers[li];
@@ -379,6 +443,28 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         d->gate = dev_alloc(ctx, T * d->I_l * 4);
         d->up = dev_alloc(ctx, T * d->I_l * 4);
         d->logits = dev_alloc(ctx, static_cast<size_t>(c.max_batch) * c.vocab * 4);
+        if (d->P == 1) {
+            // the planes pipeline needs every block linear to be an HSDR image the grouped
+            // tensor-core path takes
+            bool ok = true;
+            for (const Layer& L : d->layers) {
+                const Linear* all[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
+                for (const Linear* l : all) {
+                    if (l->raw || !l->use()) {
+                        ok = false;
+                        continue;
+                    }
+                    const csdr_segment* sgp = l->use();
+                    ok = ok && wide_group_supported(ctx, &sgp, 1, ctx->tc_min_batch);
+                }
+            }
+            d->planes_capable = ok;
+            if (ok) {
+                d->xp_h = dev_alloc(ctx, T * H * 4);           // two bf16 planes
+                d->xp_att = dev_alloc(ctx, T * d->QD_l * 4);
+                d->xp_act = dev_alloc(ctx, T * d->I_l * 4);
+            }
+        }
         if (d->P > 1) {
             d->att_full = dev_alloc(ctx, T * QD * 4);
             d->act_full = dev_alloc(ctx, T * c.inter * 4);

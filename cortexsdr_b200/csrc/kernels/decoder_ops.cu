@@ -9,6 +9,8 @@
 //   silu_mul_kernel       silu_mul, :1245-1256
 //   add_kernel            add_vectors, :1234-1243
 //   argmax_kernel         greedy pick over the logits row
+#include <cuda_bf16.h>
+
 #include <cfloat>
 
 #include "../internal.hpp"
@@ -17,6 +19,13 @@
 namespace csdr {
 
 namespace {
+
+// bf16 planes of an fp32 value for the tensor-core projection: hi = bf16(v), lo = bf16(v - hi).
+__device__ __forceinline__ void store_planes(__nv_bfloat16* hi, __nv_bfloat16* lo, size_t i, float v) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -27,7 +36,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // One CTA per token.
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_t H, float eps,
-               float* __restrict__ out) {
+               float* __restrict__ out, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
     __shared__ float red[8];
     __shared__ float inv_s;
     const float* src = x + static_cast<size_t>(blockIdx.x) * H;
@@ -45,7 +54,12 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_
     }
     __syncthreads();
     const float inv = inv_s;
-    for (uint32_t i = threadIdx.x; i < H; i += 256) dst[i] = src[i] * inv * w[i];
+    if (hi) {
+        const size_t o = static_cast<size_t>(blockIdx.x) * H;
+        for (uint32_t i = threadIdx.x; i < H; i += 256) store_planes(hi, lo, o + i, src[i] * inv * w[i]);
+    } else {
+        for (uint32_t i = threadIdx.x; i < H; i += 256) dst[i] = src[i] * inv * w[i];
+    }
 }
 
 // hidden += delta, then out = rmsnorm(hidden) — the residual add and the next norm in one pass.
@@ -154,7 +168,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
                  const float* __restrict__ vc, const int32_t* __restrict__ seq_of,
                  const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t max_seq,
-                 float scale, float* __restrict__ out) {
+                 float scale, float* __restrict__ out, __nv_bfloat16* __restrict__ hi,
+                 __nv_bfloat16* __restrict__ lo) {
     constexpr uint32_t HD = VPL * 32u;
     __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
     __shared__ float sm_acc[kAttnWarps][HD];
@@ -225,19 +240,25 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
             for (int e = 0; e < VPL; ++e) o[e] = fmaf(sm_acc[w][lane * VPL + e], f, o[e]);
         }
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-        float* op = out + (static_cast<size_t>(t) * QH + h) * HD + lane * VPL;
+        const size_t o0 = (static_cast<size_t>(t) * QH + h) * HD + lane * VPL;
 #pragma unroll
-        for (int e = 0; e < VPL; ++e) op[e] = o[e] * inv;
+        for (int e = 0; e < VPL; ++e) {
+            if (hi) store_planes(hi, lo, o0 + e, o[e] * inv);
+            else out[o0 + e] = o[e] * inv;
+        }
     }
 }
 
 __global__ void silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up,
-                                size_t n, float* __restrict__ out) {
+                                size_t n, float* __restrict__ out, __nv_bfloat16* __restrict__ hi,
+                                __nv_bfloat16* __restrict__ lo) {
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
         const float x = gate[i];
         const float sig = 1.0f / (1.0f + expf(-x));
-        out[i] = (x * sig) * up[i];
+        const float v = (x * sig) * up[i];
+        if (hi) store_planes(hi, lo, i, v);
+        else out[i] = v;
     }
 }
 
@@ -336,7 +357,14 @@ unsigned grid_for(size_t n, csdr_context* ctx) {
 void op_rmsnorm(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps,
                 float* out) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(x, w, H, eps, out);
+    rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(x, w, H, eps, out, nullptr, nullptr);
+    ls.done("rmsnorm_kernel");
+}
+
+void op_rmsnorm_planes(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps,
+                       __nv_bfloat16* hi, __nv_bfloat16* lo) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(x, w, H, eps, nullptr, hi, lo);
     ls.done("rmsnorm_kernel");
 }
 
@@ -357,24 +385,31 @@ void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, 
 
 void op_attention(csdr_context* ctx, const float* q, const float* kc, const float* vc,
                   const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
-                  uint32_t HD, uint32_t max_seq, float* out) {
+                  uint32_t HD, uint32_t max_seq, float* out, __nv_bfloat16* hi, __nv_bfloat16* lo) {
     if (HD % 32u || HD > 256u || HD == 96u || HD == 160u || HD == 192u || HD == 224u)
         throw Error(CSDR_ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 128 or 256");
     const float scale = 1.0f / sqrtf(static_cast<float>(HD));
     dim3 grid(T, QH);
     LaunchScope ls(ctx, KC_ATTENTION);
     switch (HD / 32u) {
-        case 1: attention_kernel<1><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
-        case 2: attention_kernel<2><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
-        case 4: attention_kernel<4><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
-        default: attention_kernel<8><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out); break;
+        case 1: attention_kernel<1><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
+        case 2: attention_kernel<2><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
+        case 4: attention_kernel<4><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
+        default: attention_kernel<8><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
     }
     ls.done("attention_kernel");
 }
 
 void op_silu_mul(csdr_context* ctx, const float* gate, const float* up, size_t n, float* out) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    silu_mul_kernel<<<grid_for(n, ctx), 256, 0, ctx->stream>>>(gate, up, n, out);
+    silu_mul_kernel<<<grid_for(n, ctx), 256, 0, ctx->stream>>>(gate, up, n, out, nullptr, nullptr);
+    ls.done("silu_mul_kernel");
+}
+
+void op_silu_mul_planes(csdr_context* ctx, const float* gate, const float* up, size_t n, __nv_bfloat16* hi,
+                        __nv_bfloat16* lo) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    silu_mul_kernel<<<grid_for(n, ctx), 256, 0, ctx->stream>>>(gate, up, n, nullptr, hi, lo);
     ls.done("silu_mul_kernel");
 }
 

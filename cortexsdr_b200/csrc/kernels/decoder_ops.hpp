@@ -1,6 +1,10 @@
 // Launchers of the decoder-layer glue kernels (decoder_ops.cu). All asynchronous on the
-// context's stream; activations fp32, token-major.
+// context's stream; activations fp32, token-major. The *_planes forms (and attention with hi/lo
+// given) write their result as the two bf16 planes the tensor-core projection reads, instead of
+// fp32: hi = bf16(v), lo = bf16(v - hi), same element order.
 #pragma once
+
+#include <cuda_bf16.h>
 
 #include <cstddef>
 #include <cstdint>
@@ -10,6 +14,8 @@ struct csdr_context;
 namespace csdr {
 
 void op_rmsnorm(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps, float* out);
+void op_rmsnorm_planes(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps,
+                       __nv_bfloat16* hi, __nv_bfloat16* lo);
 void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const float* w, uint32_t T,
                     uint32_t H, float eps, float* out);
 void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, float* kc, float* vc,
@@ -17,8 +23,10 @@ void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, 
                    uint32_t HD, uint32_t max_seq, float theta);
 void op_attention(csdr_context* ctx, const float* q, const float* kc, const float* vc, const int32_t* seq_of,
                   const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH, uint32_t HD, uint32_t max_seq,
-                  float* out);
+                  float* out, __nv_bfloat16* hi = nullptr, __nv_bfloat16* lo = nullptr);
 void op_silu_mul(csdr_context* ctx, const float* gate, const float* up, size_t n, float* out);
+void op_silu_mul_planes(csdr_context* ctx, const float* gate, const float* up, size_t n, __nv_bfloat16* hi,
+                        __nv_bfloat16* lo);
 void op_add(csdr_context* ctx, float* a, const float* b, size_t n);
 void op_unshard(csdr_context* ctx, const float* staged, uint32_t P, uint32_t T, uint32_t W, float* out, bool add);
 void op_gather_rows(csdr_context* ctx, const float* table, uint32_t n_rows, uint32_t H, const int32_t* ids,

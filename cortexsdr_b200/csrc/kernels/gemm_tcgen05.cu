@@ -462,7 +462,13 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
 #pragma unroll
             for (uint32_t rb = 0; rb < kWideRows; ++rb) {
                 if (rb >= nrows) break;
-                float* dst = yv.y + static_cast<size_t>(r0 + rb) * yv.Mtotal + col;
+                const size_t o = static_cast<size_t>(r0 + rb) * yv.Mtotal + col;
+                float* dst = yv.y + o;
+                if (yv.residual) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j)
+                        if (tl + j < tw) out[rb][j] += yv.residual[o + j];
+                }
                 if (vec) *reinterpret_cast<float4*>(dst) = make_float4(out[rb][0], out[rb][1], out[rb][2], out[rb][3]);
                 else {
 #pragma unroll
@@ -476,7 +482,13 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j) {
                 if (tl + j >= tw) break;
-                float* dst = yv.y + (static_cast<size_t>(yv.b0) + t0 + tl + j) * yv.R + r0;
+                const size_t o = (static_cast<size_t>(yv.b0) + t0 + tl + j) * yv.R + r0;
+                float* dst = yv.y + o;
+                if (yv.residual) {
+#pragma unroll
+                    for (uint32_t rb = 0; rb < kWideRows; ++rb)
+                        if (rb < nrows) out[rb][j] += yv.residual[o + rb];
+                }
                 if (vec) {
                     reinterpret_cast<float4*>(dst)[0] = make_float4(out[0][j], out[1][j], out[2][j], out[3][j]);
                     reinterpret_cast<float4*>(dst)[1] = make_float4(out[4][j], out[5][j], out[6][j], out[7][j]);
@@ -490,7 +502,228 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
     }
 }
 
+// Compact gather for one token tile (M <= 16) over a group of segments that were projected
+// together: CTA -> (member, run of rows). Same arithmetic as hsdr_gather_kernel (matmul.cu): the
+// member's Dx [K][MT] and the CTA's code rows sit in shared memory, thread = (row, token), sums in
+// stream order with one multiply and one add per code. Codes and scales are fetched before the
+// dependency wait; Dx only after it.
+constexpr uint32_t kGroupThreads = 256;
+constexpr uint32_t kGatherGroupMax = 4;
+
+struct GatherMember {
+    const uint16_t* codes;
+    const float* scales;
+    const float* dx;        // [K][MT]
+    float* y;
+    const float* bias;
+    const float* residual;
+    uint32_t R, S, k, K;
+    uint32_t cta_begin, rows_per_cta;
+};
+
+struct GatherGroupParams {
+    GatherMember m[kGatherGroupMax];
+    uint32_t n_seg, M, m_total, code_cap16;
+    int y_layout;
+};
+
+template <int MT>
+__global__ void __launch_bounds__(kGroupThreads)
+hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
+    extern __shared__ __align__(16) unsigned char ggsm[];
+    uint32_t mi = 0;
+#pragma unroll
+    for (uint32_t i = 1; i < kGatherGroupMax; ++i)
+        if (i < g.n_seg && blockIdx.x >= g.m[i].cta_begin) mi = i;
+    const GatherMember& m = g.m[mi];
+    const uint32_t slots = m.S * m.k;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t row0 = (blockIdx.x - m.cta_begin) * m.rows_per_cta;
+    const bool active = row0 < m.R;
+    const uint32_t rows_here = active ? min(m.rows_per_cta, m.R - row0) : 0u;
+
+    // layout: codes (16-byte units) | scales | Dx
+    const size_t code_byte0 = static_cast<size_t>(row0) * slots * 2u;
+    const size_t aligned0 = code_byte0 & ~static_cast<size_t>(15);
+    const uint32_t skip = static_cast<uint32_t>(code_byte0 - aligned0) >> 1;
+    const uint32_t n16 = active ? (skip * 2u + rows_here * slots * 2u + 15u) >> 4 : 0u;
+    uint4* cs16 = reinterpret_cast<uint4*>(ggsm);
+    float* sc = reinterpret_cast<float*>(ggsm + static_cast<size_t>(g.code_cap16) * 16u);
+    float* dxs = sc + 64;
+    {
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(m.codes) + aligned0;
+        for (uint32_t i = tid; i < n16; i += kGroupThreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                             static_cast<uint32_t>(__cvta_generic_to_shared(cs16 + i))),
+                         "l"(src + static_cast<size_t>(i) * 16u)
+                         : "memory");
+        for (uint32_t i = tid; i < m.S; i += kGroupThreads) sc[i] = m.scales[i];
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (active) {
+        const uint32_t n4 = (m.K * MT) >> 2;
+        for (uint32_t i = tid; i < n4; i += kGroupThreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                             static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
+                         "l"(m.dx + static_cast<size_t>(i) * 4u)
+                         : "memory");
+        for (uint32_t i = (n4 << 2) + tid; i < m.K * MT; i += kGroupThreads) dxs[i] = m.dx[i];
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (!active) return;
+    const uint16_t* cs = reinterpret_cast<const uint16_t*>(cs16) + skip;
+    const uint32_t b = tid % MT;
+    constexpr uint32_t RP = kGroupThreads / MT;
+    for (uint32_t rl = tid / MT; rl < rows_here; rl += RP) {
+        const uint16_t* rc = cs + rl * slots;
+        float acc = 0.0f;
+        for (uint32_t l = 0; l < m.S; ++l) {
+            const float gamma = sc[l];
+#pragma unroll 4
+            for (uint32_t kk = 0; kk < m.k; ++kk) {
+                const uint32_t code = rc[l * m.k + kk];
+                const float scale = (code & 0x8000u) ? -gamma : gamma;
+                acc = __fadd_rn(acc, __fmul_rn(scale, dxs[(code & 0x7FFFu) * MT + b]));
+            }
+        }
+        if (b < g.M) {
+            const uint32_t r = row0 + rl;
+            const size_t o = g.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * g.m_total + b
+                                                                      : static_cast<size_t>(b) * m.R + r;
+            if (m.bias) acc += m.bias[r];
+            if (m.residual) acc += m.residual[o];
+            m.y[o] = acc;
+        }
+    }
+}
+
+template <int MT>
+void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t total_rows, uint32_t max_k, uint32_t max_slots) {
+    // about two CTAs per SM over the whole group
+    const uint32_t want = 2u * static_cast<uint32_t>(ctx->sm_count);
+    const uint32_t rows_per_cta = std::max(kGroupThreads / MT, (total_rows + want - 1u) / want);
+    uint32_t ctas = 0;
+    for (uint32_t i = 0; i < g.n_seg; ++i) {
+        g.m[i].cta_begin = ctas;
+        g.m[i].rows_per_cta = rows_per_cta;
+        ctas += (g.m[i].R + rows_per_cta - 1u) / rows_per_cta;
+    }
+    g.code_cap16 = (rows_per_cta * max_slots * 2u + 15u + 16u) >> 4;
+    const size_t smem = static_cast<size_t>(g.code_cap16) * 16u + 64u * 4u + static_cast<size_t>(max_k) * MT * 4u;
+    auto kern = hsdr_gather_group_kernel<MT>;
+    static size_t smem_set = 0;
+    if (smem > 48u * 1024u && smem > smem_set) {
+        CSDR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        smem_set = smem;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas, 1, 1);
+    cfg.blockDim = dim3(kGroupThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LaunchScope ls(ctx, KC_GATHER);
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, g));
+    ls.done("hsdr_gather_group_kernel");
+}
+
+void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float* dx, uint32_t M, const YView& yv) {
+    const Geometry& g = seg->g;
+    const size_t smem = gather_wide_smem(g.n_atoms);
+    static size_t smem_set = 0;
+    if (smem > 48u * 1024u && smem > smem_set) {
+        CSDR_CUDA(cudaFuncSetAttribute(hsdr_gather_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+        smem_set = smem;
+    }
+    // one CTA per SM (the slice fills most of its shared memory): split the rows so that
+    // slices x row runs covers the GPU once, in runs that are multiples of eight rows
+    const uint32_t slices = (M + kWideTokens - 1u) / kWideTokens;
+    const uint32_t want = std::max(1u, static_cast<uint32_t>(ctx->sm_count) / slices);
+    uint32_t rows_per_cta = (g.rows + want - 1u) / want;
+    rows_per_cta = (rows_per_cta + kWideRows - 1u) / kWideRows * kWideRows;
+    const uint32_t runs = (g.rows + rows_per_cta - 1u) / rows_per_cta;
+    LaunchScope ls(ctx, KC_GATHER);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(runs, slices, 1);
+    cfg.blockDim = dim3(kWideThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_gather_wide_kernel, seg->codes_ptr(), g.rows, g.n_stages, g.k,
+                                 static_cast<const float*>(seg->scales->ptr), dx, g.n_atoms, M, rows_per_cta, yv));
+    ls.done("hsdr_gather_wide_kernel");
+}
+
 }  // namespace
+
+bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, size_t batch) {
+    if (n == 0 || n > kGatherGroupMax) return false;
+    for (uint32_t i = 0; i < n; ++i) {
+        if (!tcgen05_supported(ctx, segs[i], batch) || !dx_tma_supported(ctx, segs[i], batch)) return false;
+        if (segs[i]->g.cols != segs[0]->g.cols || segs[i]->g.n_stages > 64u) return false;
+    }
+    return true;
+}
+
+void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
+                              uint32_t M, const WideOut* outs, int y_layout) {
+    if (n == 0 || n > kGatherGroupMax) throw Error(CSDR_ERR_LIMIT, "matmul group holds 1 to 4 segments");
+    uint32_t tile_mt = 0;
+    if (M <= 16u) {
+        tile_mt = 1;
+        while (tile_mt < M) tile_mt <<= 1;
+    }
+    const uint32_t stride = tile_mt ? tile_mt : M;
+    size_t total_atoms = 0;
+    for (uint32_t i = 0; i < n; ++i) total_atoms += segs[i]->g.n_atoms;
+    float* dx0 = static_cast<float*>(ctx->scratch_get(0, total_atoms * std::max<size_t>(stride, 16u) * 4u));
+    float* dx[kGatherGroupMax];
+    size_t off = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        dx[i] = dx0 + off;
+        off += static_cast<size_t>(segs[i]->g.n_atoms) * stride;
+    }
+    launch_dx_tma_group(ctx, segs, n, x, M, dx, stride);
+    if (tile_mt) {
+        GatherGroupParams g{};
+        g.n_seg = n;
+        g.M = M;
+        g.m_total = M;
+        g.y_layout = y_layout;
+        uint32_t total_rows = 0, max_k = 0, max_slots = 0;
+        for (uint32_t i = 0; i < n; ++i) {
+            const Geometry& sg = segs[i]->g;
+            g.m[i] = GatherMember{segs[i]->codes_ptr(), static_cast<const float*>(segs[i]->scales->ptr), dx[i], outs[i].y,
+                                  outs[i].bias, outs[i].residual, sg.rows, sg.n_stages, sg.k, sg.n_atoms, 0u, 0u};
+            total_rows += sg.rows;
+            max_k = std::max(max_k, sg.n_atoms);
+            max_slots = std::max(max_slots, sg.slots());
+        }
+        switch (tile_mt) {
+            case 1: launch_gather_group_t<1>(ctx, g, total_rows, max_k, max_slots); break;
+            case 2: launch_gather_group_t<2>(ctx, g, total_rows, max_k, max_slots); break;
+            case 4: launch_gather_group_t<4>(ctx, g, total_rows, max_k, max_slots); break;
+            case 8: launch_gather_group_t<8>(ctx, g, total_rows, max_k, max_slots); break;
+            default: launch_gather_group_t<16>(ctx, g, total_rows, max_k, max_slots); break;
+        }
+        return;
+    }
+    for (uint32_t i = 0; i < n; ++i) {
+        YView yv{outs[i].y, y_layout, segs[i]->g.rows, M, 0u, M, outs[i].bias, outs[i].residual};
+        launch_gather_wide(ctx, segs[i], dx[i], M, yv);
+    }
+}
 
 bool tcgen05_supported(const csdr_context* ctx, const csdr_segment* seg, size_t batch) {
     const Geometry& g = seg->g;
@@ -565,38 +798,8 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
         launch_gather_tile(ctx, seg, dx, static_cast<int>(tile_mt), a.y, a.y_layout, M, 0u, M, a.bias);
         return;
     }
-    {
-        const size_t smem = gather_wide_smem(g.n_atoms);
-        static size_t smem_set = 0;
-        if (smem > 48u * 1024u && smem > smem_set) {
-            CSDR_CUDA(cudaFuncSetAttribute(hsdr_gather_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem)));
-            smem_set = smem;
-        }
-        YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
-        // one CTA per SM (the slice fills most of its shared memory): split the rows so that
-        // slices x row runs covers the GPU once, in runs that are multiples of eight rows
-        const uint32_t slices = (M + kWideTokens - 1u) / kWideTokens;
-        const uint32_t want = std::max(1u, static_cast<uint32_t>(ctx->sm_count) / slices);
-        uint32_t rows_per_cta = (g.rows + want - 1u) / want;
-        rows_per_cta = (rows_per_cta + kWideRows - 1u) / kWideRows * kWideRows;
-        const uint32_t runs = (g.rows + rows_per_cta - 1u) / rows_per_cta;
-        LaunchScope ls(ctx, KC_GATHER);
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3(runs, slices, 1);
-        cfg.blockDim = dim3(kWideThreads, 1, 1);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = ctx->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_gather_wide_kernel, seg->codes_ptr(), g.rows, g.n_stages, g.k,
-                                     static_cast<const float*>(seg->scales->ptr), static_cast<const float*>(dx),
-                                     g.n_atoms, M, rows_per_cta, yv));
-        ls.done("hsdr_gather_wide_kernel");
-    }
+    YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
+    launch_gather_wide(ctx, seg, dx, M, yv);
 }
 
 }  // namespace csdr

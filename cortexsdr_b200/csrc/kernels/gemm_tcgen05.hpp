@@ -1,7 +1,10 @@
 // Tensor-core (tcgen05 / TMEM) path for wide token tiles of 1-D row-tile HSDR segments.
 #pragma once
 
+#include <cuda_bf16.h>
+
 #include <cstddef>
+#include <cstdint>
 
 struct csdr_context;
 struct csdr_segment;
@@ -22,5 +25,31 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
 // dictionary.
 bool dx_tma_supported(const csdr_context* ctx, const csdr_segment* seg, size_t batch);
 void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride);
+
+
+// Activations as token-major bf16 planes [tokens][cols]: hi = bf16(x), lo = bf16(x - hi); lo is
+// null when the source was bf16 already.
+struct XPlanesView {
+    const __nv_bfloat16* hi;
+    const __nv_bfloat16* lo;
+};
+// Planes of a caller's activation matrix: the matrix itself when it is bf16, token-major and
+// 16-byte aligned, else a conversion into context scratch (valid until the next conversion).
+XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_layout, uint32_t M, uint32_t cols);
+// One projection launch for up to four dictionaries over the same activations (q|k|v, gate|up).
+void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
+                         float* const* dx, uint32_t dx_stride);
+
+// Up to four row-tile segments over the same activation planes: one projection launch and, for
+// a single token tile (M <= 16), one gather launch for the whole group. y = W x (+ bias)
+// (+ residual, which may be y itself).
+struct WideOut {
+    float* y;
+    const float* bias;
+    const float* residual;
+};
+bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, size_t batch);
+void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
+                              uint32_t M, const WideOut* outs, int y_layout);
 
 }  // namespace csdr

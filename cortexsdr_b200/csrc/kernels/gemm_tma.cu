@@ -103,8 +103,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+constexpr uint32_t kMaxGroup = 4;       // dictionaries that may share one launch (q|k|v, gate|up)
+
+// Tensor maps of the dictionaries' bf16 planes, one pair per group member.
+struct GroupMaps {
+    CUtensorMap hi[kMaxGroup], lo[kMaxGroup];
+};
+
 struct Params {
-    uint32_t K, M;          // atoms, tokens
+    uint32_t n_seg;
+    uint32_t tile_begin[kMaxGroup + 1];   // first atom tile (blockIdx.x) of each member
+    float* dx_of[kMaxGroup];              // each member's Dx, [K_s][dx_stride]
+    uint32_t M;             // tokens
     uint32_t dx_stride;     // floats between Dx rows (>= M)
     uint32_t n_tile;        // MMA N: 16, 32, 64 or 128
     uint32_t tmem_cols;     // power of two >= max(32, n_tile)
@@ -112,7 +122,6 @@ struct Params {
     uint32_t kb_per_cta;
     uint32_t stages;
     uint32_t x_has_lo;
-    float* dx;              // [K][M]
     float* part;            // [tile][rank][128][N] accumulator tiles of the column ranges
     int* status;
     unsigned long long* trace;   // optional: 16 global-timer stamps per CTA (phase boundaries)
@@ -131,11 +140,10 @@ __device__ __forceinline__ void stamp(const Params& p, int slot) {
     }
 }
 
-// grid (K/128, token tiles, column ranges); cluster (1, 1, column ranges)
+// grid (atom tiles of every member, token tiles, column ranges); cluster (1, 1, column ranges)
 __global__ void __launch_bounds__(kThreads, 1)
-hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
-                   const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
-                   const __grid_constant__ Params p) {
+hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant__ CUtensorMap map_xhi,
+                   const __grid_constant__ CUtensorMap map_xlo, const __grid_constant__ Params p) {
     extern __shared__ __align__(1024) unsigned char tma_smem_raw[];
     // the gather behind this kernel may start its prologue (code prefetch) right away; it waits
     // for this grid's completion before it touches Dx
@@ -154,7 +162,14 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
     const uint32_t N = p.n_tile;
     const uint32_t b_tile = N * 128u;
     const uint32_t stage_bytes = 2u * kATile + (p.x_has_lo ? 2u : 1u) * b_tile;
-    const uint32_t atom0 = blockIdx.x * kTileM;
+    uint32_t seg = 0;
+#pragma unroll
+    for (uint32_t i = 1; i < kMaxGroup; ++i)
+        if (i < p.n_seg && blockIdx.x >= p.tile_begin[i]) seg = i;
+    const uint32_t atom0 = (blockIdx.x - p.tile_begin[seg]) * kTileM;
+    float* const dx = p.dx_of[seg];
+    const CUtensorMap* map_ahi = &maps.hi[seg];
+    const CUtensorMap* map_alo = &maps.lo[seg];
     const uint32_t tok0 = blockIdx.y * N;
     const uint32_t kb_begin = min(p.n_kb, rank * p.kb_per_cta);
     const uint32_t kb_end = min(p.n_kb, kb_begin + p.kb_per_cta);
@@ -197,8 +212,8 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
                              : "memory");
                 const uint32_t dst = smem_u32(smem + s * stage_bytes);
                 const uint32_t c0 = (kb_begin + it) * kBlockK;
-                tma_load_2d(dst, &map_ahi, c0, atom0, bar);
-                tma_load_2d(dst + kATile, &map_alo, c0, atom0, bar);
+                tma_load_2d(dst, map_ahi, c0, atom0, bar);
+                tma_load_2d(dst + kATile, map_alo, c0, atom0, bar);
                 tma_load_2d(dst + 2u * kATile, &map_xhi, c0, tok0, bar);
                 if (p.x_has_lo) tma_load_2d(dst + 2u * kATile + b_tile, &map_xlo, c0, tok0, bar);
             }
@@ -290,7 +305,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
             const float4 v = *reinterpret_cast<const float4*>(ptile + static_cast<size_t>(row) * pstride + c4 * 4u);
             if (direct) {
                 if (tok0 + c4 * 4u < p.M)
-                    *reinterpret_cast<float4*>(p.dx + static_cast<size_t>(atom0 + row) * p.dx_stride + tok0 + c4 * 4u) = v;
+                    *reinterpret_cast<float4*>(dx + static_cast<size_t>(atom0 + row) * p.dx_stride + tok0 + c4 * 4u) = v;
             } else {
                 *reinterpret_cast<float4*>(part + (static_cast<size_t>(rank) * kTileM + row) * N + c4 * 4u) = v;
             }
@@ -340,8 +355,8 @@ hsdr_dx_tma_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_con
                         acc.w += v[h][r].w;
                     }
                 const uint32_t atom = atom0 + row, tok = tok0 + c4 * 4u;
-                if (atom < p.K && tok < p.M) {
-                    float* dst = p.dx + static_cast<size_t>(atom) * p.dx_stride + tok;
+                if (tok < p.M) {
+                    float* dst = dx + static_cast<size_t>(atom) * p.dx_stride + tok;
                     if (vec) *reinterpret_cast<float4*>(dst) = acc;     // tok and M are multiples of four
                     else {
                         dst[0] = acc.x;
@@ -457,37 +472,51 @@ bool dx_tma_supported(const csdr_context* ctx, const csdr_segment* seg, size_t b
     return ctx->tma && g.row_tiles() && g.n_atoms % kTileM == 0 && g.cols % kBlockK == 0 && encode_fn() != nullptr;
 }
 
-void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride) {
+XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_layout, uint32_t M, uint32_t cols) {
     using namespace tma_detail;
-    const Geometry& g = seg->g;
-    const uint32_t M = static_cast<uint32_t>(a.batch);
-    auto planes = planes_for(ctx, seg);
+    // in place when the activations already are what the loader wants
+    if (x_dtype == CSDR_DTYPE_BF16 && x_layout == CSDR_LAYOUT_TOKEN_MAJOR && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+        (cols & 7u) == 0)
+        return XPlanesView{static_cast<const __nv_bfloat16*>(x), nullptr};
+    const bool has_lo = x_dtype == CSDR_DTYPE_F32;
+    const size_t n = static_cast<size_t>(M) * cols;
+    __nv_bfloat16* buf = static_cast<__nv_bfloat16*>(ctx->scratch_get(5, n * (has_lo ? 4u : 2u)));
+    XView xv{x, x_dtype, x_layout, cols, M, 0u, M};
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    x_planes_kernel<<<static_cast<unsigned>(std::min<size_t>((n + 255u) / 256u, 2048u)), 256, 0, ctx->stream>>>(
+        xv, buf, has_lo ? buf + n : nullptr);
+    ls.done("x_planes_kernel");
+    return XPlanesView{buf, has_lo ? buf + n : nullptr};
+}
 
-    // activations: in place when they already are what the loader wants
-    const bool in_place = a.x_dtype == CSDR_DTYPE_BF16 && a.x_layout == CSDR_LAYOUT_TOKEN_MAJOR &&
-                          (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (g.cols & 7u) == 0;
-    const bool has_lo = a.x_dtype == CSDR_DTYPE_F32;
-    const __nv_bfloat16* xhi = static_cast<const __nv_bfloat16*>(a.x);
-    const __nv_bfloat16* xlo = nullptr;
-    if (!in_place) {
-        const size_t n = static_cast<size_t>(M) * g.cols;
-        __nv_bfloat16* buf = static_cast<__nv_bfloat16*>(ctx->scratch_get(5, n * (has_lo ? 4u : 2u)));
-        XView xv{a.x, a.x_dtype, a.x_layout, g.cols, M, 0u, M};
-        LaunchScope ls(ctx, KC_DECODER_OP);
-        x_planes_kernel<<<static_cast<unsigned>(std::min<size_t>((n + 255u) / 256u, 2048u)), 256, 0, ctx->stream>>>(
-            xv, buf, has_lo ? buf + n : nullptr);
-        ls.done("x_planes_kernel");
-        xhi = buf;
-        xlo = has_lo ? buf + n : nullptr;
-    }
+void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
+                         float* const* dx, uint32_t dx_stride) {
+    using namespace tma_detail;
+    if (n_seg == 0 || n_seg > kMaxGroup) throw Error(CSDR_ERR_LIMIT, "projection group holds 1 to 4 dictionaries");
+    const uint32_t cols = segs[0]->g.cols;
+    const bool has_lo = x.lo != nullptr;
     uint32_t N = 16;
     while (N < 128u && N < M) N <<= 1;
-    const CUtensorMap map_xhi = make_map(xhi, M, g.cols, N);
-    const CUtensorMap map_xlo = has_lo ? make_map(xlo, M, g.cols, N) : map_xhi;
+    const CUtensorMap map_xhi = make_map(x.hi, M, cols, N);
+    const CUtensorMap map_xlo = has_lo ? make_map(x.lo, M, cols, N) : map_xhi;
+
+    GroupMaps maps{};
+    Params p{};
+    p.n_seg = n_seg;
+    uint32_t atom_tiles = 0;
+    for (uint32_t i = 0; i < n_seg; ++i) {
+        if (segs[i]->g.cols != cols) throw Error(CSDR_ERR_GEOMETRY, "projection group: members differ in columns");
+        auto planes = planes_for(ctx, segs[i]);
+        maps.hi[i] = planes->map_hi;
+        maps.lo[i] = planes->map_lo;
+        p.tile_begin[i] = atom_tiles;
+        p.dx_of[i] = dx[i];
+        atom_tiles += segs[i]->g.n_atoms / kTileM;
+    }
+    for (uint32_t i = n_seg; i <= kMaxGroup; ++i) p.tile_begin[i] = atom_tiles;
 
     const uint32_t tok_tiles = (M + N - 1u) / N;
-    const uint32_t atom_tiles = g.n_atoms / kTileM;
-    const uint32_t n_kb = g.cols / kBlockK;
+    const uint32_t n_kb = cols / kBlockK;
     const uint32_t stage_bytes = 2u * kATile + (has_lo ? 2u : 1u) * N * 128u;
 
     static bool attrs_set = false;
@@ -544,37 +573,33 @@ void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
             break;
         }
     }
-    const uint32_t kb_per_cta = (n_kb + ranks - 1u) / ranks;
     cfg.gridDim = dim3(atom_tiles, tok_tiles, ranks);
     attr[0].val.clusterDim.z = ranks;
 
-    Params p{};
-    p.K = g.n_atoms;
     p.M = M;
     p.dx_stride = dx_stride;
     p.n_tile = N;
     p.tmem_cols = std::max(32u, N);
     p.n_kb = n_kb;
-    p.kb_per_cta = kb_per_cta;
+    p.kb_per_cta = (n_kb + ranks - 1u) / ranks;
     p.stages = stages;
     p.x_has_lo = has_lo ? 1u : 0u;
-    p.dx = dx;
     p.part = ranks > 1u || ((M | dx_stride) & 3u) ? static_cast<float*>(ctx->scratch_get(
-                                           1, static_cast<size_t>(tiles) * ranks * kTileM * N * 4u))
-                                    : nullptr;
+                                                         1, static_cast<size_t>(tiles) * ranks * kTileM * N * 4u))
+                                                   : nullptr;
     p.status = ctx->status_word;
     p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
     p.trace_ctas = static_cast<uint32_t>(ctx->sm_count) * 2u;
 
-    if (std::getenv("CSDR_DEBUG_TMA")) {
-        int n_clusters = -1;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, hsdr_dx_tma_kernel, &cfg);
-        fprintf(stderr, "dx_tma: M=%u N=%u tiles=%u ranks=%u stages=%u smem=%zu maxActiveClusters=%d (%s)\n", M, N,
-                tiles, ranks, stages, smem, n_clusters, cudaGetErrorString(e));
-    }
     LaunchScope ls(ctx, KC_GEMM);
-    CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_dx_tma_kernel, planes->map_hi, planes->map_lo, map_xhi, map_xlo, p));
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_dx_tma_kernel, maps, map_xhi, map_xlo, p));
     ls.done("hsdr_dx_tma_kernel");
+}
+
+void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride) {
+    const uint32_t M = static_cast<uint32_t>(a.batch);
+    const XPlanesView x = make_x_planes(ctx, a.x, a.x_dtype, a.x_layout, M, seg->g.cols);
+    launch_dx_tma_group(ctx, &seg, 1, x, M, &dx, dx_stride);
 }
 
 }  // namespace csdr

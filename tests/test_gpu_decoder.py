@@ -17,10 +17,9 @@ LOGIT_TOL = 2e-2
 CFG = dict(n_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=32, inter=256, vocab=300)
 
 
-@pytest.fixture(scope="module")
-def model(tmp_path_factory, oracle):
-    path = str(tmp_path_factory.mktemp("dec") / "tiny.sdr")
-    synth.decoder_archive(path, **CFG, n_atoms=32, k=3, kv_atoms=16, seed=7)
+def _build_model(tmp_path_factory, oracle, tag, **atoms):
+    path = str(tmp_path_factory.mktemp("dec") / f"{tag}.sdr")
+    synth.decoder_archive(path, **CFG, k=3, seed=7, **atoms)
     ld = cs.SDRModelLoader(path, index_only=True)
     dense = lambda n: oracle.decompress(ld.loadCompressedBytesByName(n))
     raw = lambda n: ld.loadSegmentByName(n).view(np.float32)
@@ -35,6 +34,18 @@ def model(tmp_path_factory, oracle):
     weights = dict(tok=dense("token_embd.weight"), blocks=blocks, out_norm=raw("output_norm.weight"),
                    head=dense("output.weight"))
     return path, weights
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory, oracle):
+    return _build_model(tmp_path_factory, oracle, "tiny", n_atoms=32, kv_atoms=16)
+
+
+@pytest.fixture(scope="module")
+def model_tc(tmp_path_factory, oracle):
+    """Dictionaries of 128 atoms: steps of eight tokens or more take the tensor-core projection
+    and the block loop that hands activations on as bf16 planes."""
+    return _build_model(tmp_path_factory, oracle, "tc", n_atoms=128, kv_atoms=128)
 
 
 def oracle_forward(oracle, weights, tokens, eps=1e-6, theta=1e6):
@@ -92,6 +103,29 @@ def test_batched_step_sequences_are_independent(ctx, oracle, model):
         _, want = oracle_forward(oracle, weights, np.append(p, new[s]))
         assert np.abs(logits[s] - want).max() < LOGIT_TOL
         assert int(nxt[s]) == int(want.argmax())
+
+
+def test_tensor_core_block_loop_matches_oracle(ctx, oracle, model_tc):
+    path, weights = model_tc
+    rng = np.random.default_rng(3)
+    tokens = rng.integers(0, CFG["vocab"], 21)
+    hid, logits = oracle_forward(oracle, weights, tokens)
+    dec = make_decoder(path, ctx, max_batch=9)
+    g_logits, g_hid = dec.forward(tokens, want_hidden=True)          # 21 tokens: wide gather
+    assert np.abs(g_hid - hid).max() < 1e-3
+    assert np.abs(g_logits - logits).max() < LOGIT_TOL
+    assert int(g_logits.argmax()) == int(logits.argmax())
+    # nine sequences stepping together: one token tile, grouped gather, residual on the gather
+    dec.reset()
+    prompts = [rng.integers(0, CFG["vocab"], n) for n in (5, 9, 3, 1, 7, 2, 11, 4, 6)]
+    for s_, p_ in enumerate(prompts):
+        dec.forward(p_, seq=s_, want_logits=False)
+    new = rng.integers(0, CFG["vocab"], 9)
+    nxt, lg = dec.step(new, want_logits=True)
+    for s_, p_ in enumerate(prompts):
+        _, want = oracle_forward(oracle, weights, np.append(p_, new[s_]))
+        assert np.abs(lg[s_] - want).max() < LOGIT_TOL
+        assert int(nxt[s_]) == int(want.argmax())
 
 
 def test_decoder_limits_and_errors(ctx, model):

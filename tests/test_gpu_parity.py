@@ -246,6 +246,35 @@ def test_grouped_matmul_matches_single_calls(ctx, oracle, golden):
             assert e[0] < TOL and e[1] < TOL, (batch, e)
 
 
+def test_grouped_tensor_core_projection_matches_oracle(ctx, oracle):
+    """Members with different atom counts and row counts over one activation matrix: one
+    projection launch for the group (bf16 planes built once), one gather launch up to 16 tokens."""
+    import torch
+    from cortexsdr_b200 import synth
+    shapes = ((264, 128), (96, 256), (130, 128))
+    pays = [synth.hsdr_payload(r, 512, n_atoms=k, k=4, seed=60 + i) for i, (r, k) in enumerate(shapes)]
+    segs = [cs.Segment.from_payload(p, ctx) for p in pays]
+    rng = np.random.default_rng(11)
+    for batch, dtype in ((8, "f32"), (13, "f32"), (16, "bf16"), (21, "f32"), (64, "bf16"), (130, "f32")):
+        xf = rng.normal(0, 1, (batch, 512)).astype(np.float32)
+        if dtype == "bf16":
+            x = torch.from_numpy(xf).cuda().to(torch.bfloat16)
+            xf = x.float().cpu().numpy()
+            code = cs.DTYPE_BF16
+        else:
+            x = torch.from_numpy(xf).cuda()
+            code = cs.DTYPE_F32
+        ys = [torch.zeros((batch, s.rows), device="cuda") for s in segs]
+        torch.cuda.synchronize()
+        cs.Segment.matmul_group_device(segs, x.data_ptr(), code, cs.TOKEN_MAJOR, batch,
+                                       [y.data_ptr() for y in ys], cs.TOKEN_MAJOR)
+        ctx.synchronize()
+        for p, y in zip(pays, ys):
+            want = oracle.matmul(p, np.ascontiguousarray(xf.T), batch).T
+            e = rel_err(y.cpu().numpy(), want)
+            assert e[0] < TOL and e[1] < TOL, (batch, dtype, e)
+
+
 def test_fused_and_two_kernel_paths_agree(lib, oracle, golden, monkeypatch):
     g = golden("fused_rowtile.npz")
     x = np.random.default_rng(5).normal(0, 1, (512, 9)).astype(np.float32)
