@@ -27,6 +27,30 @@ __device__ __forceinline__ void store_planes(__nv_bfloat16* hi, __nv_bfloat16* l
     lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
 }
 
+// Every glue kernel lets the kernel behind it on the stream start its own prologue at once and
+// then waits until everything before it on the stream has completed and is visible; no global
+// memory is touched before that wait.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Launch with programmatic stream serialization allowed (the kernel must begin with pdl_enter()).
+template <typename... KArgs, typename... Args>
+void launch_pdl(csdr_context* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
@@ -37,6 +61,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_t H, float eps,
                float* __restrict__ out, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo) {
+    pdl_enter();
     __shared__ float red[8];
     __shared__ float inv_s;
     const float* src = x + static_cast<size_t>(blockIdx.x) * H;
@@ -66,6 +91,7 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
                    const float* __restrict__ w, uint32_t H, float eps, float* __restrict__ out) {
+    pdl_enter();
     __shared__ float red[8];
     __shared__ float inv_s;
     float* h = hidden + static_cast<size_t>(blockIdx.x) * H;
@@ -98,6 +124,7 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
                   float* __restrict__ kc, float* __restrict__ vc, const int32_t* __restrict__ seq_of,
                   const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t HD,
                   uint32_t max_seq, float theta) {
+    pdl_enter();
     const uint32_t t = blockIdx.x;
     const int32_t pos = pos_of[t], sq = seq_of[t];
     const uint32_t rotary = HD - (HD & 1u), half = rotary >> 1;
@@ -140,7 +167,6 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
 // evaluated in one pass); the four warps' partial states are merged through shared memory.
 // Causality: token t sees cache positions 0..pos_of[t] of its own sequence, all of which are
 // written before this kernel runs.
-constexpr int kAttnWarps = 4;
 constexpr int kAttnKeys = 4;   // keys per warp per step
 
 template <int VPL>
@@ -163,13 +189,16 @@ __device__ __forceinline__ void load_row(const float* p, float (&v)[VPL]) {
     }
 }
 
-template <int VPL>
+// WARPS warps split the keys of one (token, head); few (token, head) pairs (batched decode
+// against a long context) take more warps each so that enough K/V rows are in flight per SM.
+template <int VPL, int kAttnWarps>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
                  const float* __restrict__ vc, const int32_t* __restrict__ seq_of,
                  const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t max_seq,
                  float scale, float* __restrict__ out, __nv_bfloat16* __restrict__ hi,
                  __nv_bfloat16* __restrict__ lo) {
+    pdl_enter();
     constexpr uint32_t HD = VPL * 32u;
     __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
     __shared__ float sm_acc[kAttnWarps][HD];
@@ -252,6 +281,7 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
 __global__ void silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                 size_t n, float* __restrict__ out, __nv_bfloat16* __restrict__ hi,
                                 __nv_bfloat16* __restrict__ lo) {
+    pdl_enter();
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride) {
         const float x = gate[i];
@@ -357,21 +387,21 @@ unsigned grid_for(size_t n, csdr_context* ctx) {
 void op_rmsnorm(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps,
                 float* out) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(x, w, H, eps, out, nullptr, nullptr);
+    launch_pdl(ctx, rmsnorm_kernel, dim3(T), dim3(256), x, w, H, eps, out, nullptr, nullptr);
     ls.done("rmsnorm_kernel");
 }
 
 void op_rmsnorm_planes(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps,
                        __nv_bfloat16* hi, __nv_bfloat16* lo) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(x, w, H, eps, nullptr, hi, lo);
+    launch_pdl(ctx, rmsnorm_kernel, dim3(T), dim3(256), x, w, H, eps, nullptr, hi, lo);
     ls.done("rmsnorm_kernel");
 }
 
 void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const float* w, uint32_t T,
                     uint32_t H, float eps, float* out) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    add_rmsnorm_kernel<<<T, 256, 0, ctx->stream>>>(hidden, delta, w, H, eps, out);
+    launch_pdl(ctx, add_rmsnorm_kernel, dim3(T), dim3(256), hidden, delta, w, H, eps, out);
     ls.done("add_rmsnorm_kernel");
 }
 
@@ -379,7 +409,7 @@ void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, 
                    const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
                    uint32_t HD, uint32_t max_seq, float theta) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    rope_cache_kernel<<<T, 256, 0, ctx->stream>>>(q, k, v, kc, vc, seq_of, pos_of, QH, KVH, HD, max_seq, theta);
+    launch_pdl(ctx, rope_cache_kernel, dim3(T), dim3(256), q, k, v, kc, vc, seq_of, pos_of, QH, KVH, HD, max_seq, theta);
     ls.done("rope_cache_kernel");
 }
 
@@ -391,25 +421,39 @@ void op_attention(csdr_context* ctx, const float* q, const float* kc, const floa
     const float scale = 1.0f / sqrtf(static_cast<float>(HD));
     dim3 grid(T, QH);
     LaunchScope ls(ctx, KC_ATTENTION);
+    const uint32_t pairs = T * QH;
+    const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
+    const int warps = pairs >= sms * 8u ? 4 : pairs >= sms * 4u ? 8 : 16;
+#define CSDR_ATTN(V, W)                                                                                         \
+    launch_pdl(ctx, attention_kernel<V, W>, grid, dim3(W * 32), q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, \
+               out, hi, lo)
+#define CSDR_ATTN_W(V)                     \
+    do {                                   \
+        if (warps == 4) CSDR_ATTN(V, 4);   \
+        else if (warps == 8) CSDR_ATTN(V, 8); \
+        else CSDR_ATTN(V, 16);             \
+    } while (0)
     switch (HD / 32u) {
-        case 1: attention_kernel<1><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
-        case 2: attention_kernel<2><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
-        case 4: attention_kernel<4><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
-        default: attention_kernel<8><<<grid, kAttnWarps * 32, 0, ctx->stream>>>(q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo); break;
+        case 1: CSDR_ATTN_W(1); break;
+        case 2: CSDR_ATTN_W(2); break;
+        case 4: CSDR_ATTN_W(4); break;
+        default: CSDR_ATTN_W(8); break;
     }
+#undef CSDR_ATTN_W
+#undef CSDR_ATTN
     ls.done("attention_kernel");
 }
 
 void op_silu_mul(csdr_context* ctx, const float* gate, const float* up, size_t n, float* out) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    silu_mul_kernel<<<grid_for(n, ctx), 256, 0, ctx->stream>>>(gate, up, n, out, nullptr, nullptr);
+    launch_pdl(ctx, silu_mul_kernel, dim3(grid_for(n, ctx)), dim3(256), gate, up, n, out, nullptr, nullptr);
     ls.done("silu_mul_kernel");
 }
 
 void op_silu_mul_planes(csdr_context* ctx, const float* gate, const float* up, size_t n, __nv_bfloat16* hi,
                         __nv_bfloat16* lo) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    silu_mul_kernel<<<grid_for(n, ctx), 256, 0, ctx->stream>>>(gate, up, n, nullptr, hi, lo);
+    launch_pdl(ctx, silu_mul_kernel, dim3(grid_for(n, ctx)), dim3(256), gate, up, n, nullptr, hi, lo);
     ls.done("silu_mul_kernel");
 }
 

@@ -340,6 +340,7 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
                         const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
                         uint32_t M /* tokens in dx rows */, uint32_t rows_per_cta, YView yv) {
     extern __shared__ __align__(16) float wsm[];
+    asm volatile("griddepcontrol.launch_dependents;");
     float* dxs = wsm;                                           // [K][64]
     float* gs = wsm + static_cast<size_t>(K) * kWideTokens;     // stage scales, [<= 64]
     uint32_t* csm = reinterpret_cast<uint32_t*>(gs + kWideMaxSlots);   // [half-warp][kWideCodeWords]
@@ -531,6 +532,7 @@ template <int MT>
 __global__ void __launch_bounds__(kGroupThreads)
 hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     extern __shared__ __align__(16) unsigned char ggsm[];
+    asm volatile("griddepcontrol.launch_dependents;");
     uint32_t mi = 0;
 #pragma unroll
     for (uint32_t i = 1; i < kGatherGroupMax; ++i)

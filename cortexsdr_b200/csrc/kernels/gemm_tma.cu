@@ -199,10 +199,30 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
 
     if (warp == 0) {
         // ---- loader ----
+        // The dictionary planes do not depend on earlier work on the stream: the first round of
+        // stages gets its weight tiles before the dependency wait, the activation tiles after.
         if (lane == 0) {
-            for (uint32_t it = 0; it < n_it; ++it) {
+            const uint32_t pre = min(p.stages, n_it);
+            for (uint32_t it = 0; it < pre; ++it) {
+                const uint32_t bar = smem_u32(&full_bar[it]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_bytes)
+                             : "memory");
+                const uint32_t dst = smem_u32(smem + it * stage_bytes);
+                const uint32_t c0 = (kb_begin + it) * kBlockK;
+                tma_load_2d(dst, map_ahi, c0, atom0, bar);
+                tma_load_2d(dst + kATile, map_alo, c0, atom0, bar);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (uint32_t it = 0; it < pre; ++it) {
+                const uint32_t bar = smem_u32(&full_bar[it]);
+                const uint32_t dst = smem_u32(smem + it * stage_bytes);
+                const uint32_t c0 = (kb_begin + it) * kBlockK;
+                tma_load_2d(dst + 2u * kATile, &map_xhi, c0, tok0, bar);
+                if (p.x_has_lo) tma_load_2d(dst + 2u * kATile + b_tile, &map_xlo, c0, tok0, bar);
+            }
+            for (uint32_t it = pre; it < n_it; ++it) {
                 const uint32_t s = it % p.stages, use = it / p.stages;
-                if (use > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (use - 1u) & 1u)) {
+                if (!mbar_wait(smem_u32(&empty_bar[s]), (use - 1u) & 1u)) {
                     failed_s = 1;
                     break;
                 }
@@ -540,12 +560,14 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
 
     // Column ranges per tile = cluster size: the largest one for which every cluster of the
     // launch is resident at once (the hardware places a cluster inside one GPC, so the answer
