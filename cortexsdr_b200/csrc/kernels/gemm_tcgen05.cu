@@ -338,7 +338,8 @@ inline size_t gather_wide_smem(uint32_t K) {
 __global__ void __launch_bounds__(kWideThreads, 1)
 hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, uint32_t k,
                         const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
-                        uint32_t M /* tokens in dx rows */, uint32_t rows_per_cta, YView yv) {
+                        uint32_t M /* tokens in dx rows */, uint32_t rows_per_cta, YView yv,
+                        const float* residual /* laid out like y, added on the way out; may be y itself */) {
     extern __shared__ __align__(16) float wsm[];
     asm volatile("griddepcontrol.launch_dependents;");
     float* dxs = wsm;                                           // [K][64]
@@ -465,10 +466,10 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
                 if (rb >= nrows) break;
                 const size_t o = static_cast<size_t>(r0 + rb) * yv.Mtotal + col;
                 float* dst = yv.y + o;
-                if (yv.residual) {
+                if (residual) {
 #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j)
-                        if (tl + j < tw) out[rb][j] += yv.residual[o + j];
+                        if (tl + j < tw) out[rb][j] += residual[o + j];
                 }
                 if (vec) *reinterpret_cast<float4*>(dst) = make_float4(out[rb][0], out[rb][1], out[rb][2], out[rb][3]);
                 else {
@@ -485,10 +486,10 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
                 if (tl + j >= tw) break;
                 const size_t o = (static_cast<size_t>(yv.b0) + t0 + tl + j) * yv.R + r0;
                 float* dst = yv.y + o;
-                if (yv.residual) {
+                if (residual) {
 #pragma unroll
                     for (uint32_t rb = 0; rb < kWideRows; ++rb)
-                        if (rb < nrows) out[rb][j] += yv.residual[o + rb];
+                        if (rb < nrows) out[rb][j] += residual[o + rb];
                 }
                 if (vec) {
                     reinterpret_cast<float4*>(dst)[0] = make_float4(out[0][j], out[1][j], out[2][j], out[3][j]);
@@ -635,7 +636,8 @@ void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t tot
     ls.done("hsdr_gather_group_kernel");
 }
 
-void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float* dx, uint32_t M, const YView& yv) {
+void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float* dx, uint32_t M, const YView& yv,
+                        const float* residual) {
     const Geometry& g = seg->g;
     const size_t smem = gather_wide_smem(g.n_atoms);
     static size_t smem_set = 0;
@@ -663,7 +665,8 @@ void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float*
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_gather_wide_kernel, seg->codes_ptr(), g.rows, g.n_stages, g.k,
-                                 static_cast<const float*>(seg->scales->ptr), dx, g.n_atoms, M, rows_per_cta, yv));
+                                 static_cast<const float*>(seg->scales->ptr), dx, g.n_atoms, M, rows_per_cta, yv,
+                                 residual));
     ls.done("hsdr_gather_wide_kernel");
 }
 
@@ -722,8 +725,8 @@ void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs
         return;
     }
     for (uint32_t i = 0; i < n; ++i) {
-        YView yv{outs[i].y, y_layout, segs[i]->g.rows, M, 0u, M, outs[i].bias, outs[i].residual};
-        launch_gather_wide(ctx, segs[i], dx[i], M, yv);
+        YView yv{outs[i].y, y_layout, segs[i]->g.rows, M, 0u, M, outs[i].bias};
+        launch_gather_wide(ctx, segs[i], dx[i], M, yv, outs[i].residual);
     }
 }
 
@@ -801,7 +804,7 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
         return;
     }
     YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
-    launch_gather_wide(ctx, seg, dx, M, yv);
+    launch_gather_wide(ctx, seg, dx, M, yv, nullptr);
 }
 
 }  // namespace csdr

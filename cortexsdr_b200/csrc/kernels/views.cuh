@@ -45,7 +45,6 @@ struct YView {
     uint32_t b0;
     uint32_t M;
     const float* bias;
-    const float* residual = nullptr;   // same layout as y; added on the way out (may alias y)
 };
 
 __device__ __forceinline__ size_t y_index(const YView& v, uint32_t r, uint32_t b) {
