@@ -238,6 +238,13 @@ class Segment:
         _check(self.ctx._lib.csdr_segment_shard_rows(self.ctx._h, self._h, begin, end, C.byref(h)))
         return Segment(self.ctx, h, True, self)
 
+    def shard_cols(self, begin: int, end: int) -> "Segment":
+        """Input columns [begin, end) of a row-tile segment: its product with x[begin:end] is that
+        slice's share of W x."""
+        h = C.c_void_p()
+        _check(self.ctx._lib.csdr_segment_shard_cols(self.ctx._h, self._h, begin, end, C.byref(h)))
+        return Segment(self.ctx, h, True, self)
+
     def unpack(self):
         """(int32 indices, int8 signs), produced by the device unpack kernel."""
         n = self.n_codes

@@ -81,6 +81,7 @@ SIGNATURES = {
     "csdr_dictionary_destroy": (C.c_int, [_P]),
     "csdr_segment_info": (C.c_int, [_P, C.POINTER(PayloadInfo)]),
     "csdr_segment_shard_rows": (C.c_int, [_P, _P, C.c_uint32, C.c_uint32, C.POINTER(_P)]),
+    "csdr_segment_shard_cols": (C.c_int, [_P, _P, C.c_uint32, C.c_uint32, C.POINTER(_P)]),
     "csdr_unpack_codes": (C.c_int, [_P, _P, C.POINTER(C.c_int32), C.POINTER(C.c_int8), _SZ]),
     "csdr_matmul": (C.c_int, [_P, _P, _P, _SZ, _P, C.c_int]),   # float* passed as raw addresses
     "csdr_matmul_device_async": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _SZ, _P, C.c_int, _P]),

@@ -382,7 +382,42 @@ int csdr_segment_info(const csdr_segment* seg, csdr_payload_info* info) {
         if (!seg || !info) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
         *info = seg->info;
         info->rows = seg->g.rows;
+        info->cols = seg->g.cols;
+        info->tile_cols = static_cast<uint16_t>(seg->g.tile_cols);
         info->n_tiles = seg->g.n_tiles;
+    });
+}
+
+int csdr_segment_shard_cols(csdr_context* ctx, const csdr_segment* seg, uint32_t col_begin,
+                            uint32_t col_end, csdr_segment** out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!seg || !out) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const Geometry& g = seg->g;
+        if (!g.row_tiles()) throw Error(CSDR_ERR_GEOMETRY, "column shards exist for 1-D row tiles only");
+        if (col_begin >= col_end || col_end > g.cols)
+            throw Error(CSDR_ERR_INVALID_ARG, "column range outside the matrix");
+        if ((col_begin | col_end) & 3u)
+            throw Error(CSDR_ERR_GEOMETRY, "column range must fall on multiples of four");
+        if (col_end - col_begin > 0xFFFFu) throw Error(CSDR_ERR_LIMIT, "column shard wider than 65535");
+        auto sh = std::make_unique<csdr_segment>();
+        sh->ctx = ctx;
+        sh->info = seg->info;
+        sh->g = g;
+        const uint32_t w = col_end - col_begin;
+        sh->g.cols = sh->g.cols_full = sh->g.tile_cols = w;
+        sh->scales_host = seg->scales_host;
+        sh->scales = seg->scales;
+        sh->codes = seg->codes;
+        sh->codes_offset = seg->codes_offset;
+        // the shard's own dictionary: columns [col_begin, col_end) of every atom, contiguous
+        sh->atoms = std::make_shared<DeviceBuffer>(static_cast<size_t>(g.n_atoms) * w * 4, ctx->device);
+        CSDR_CUDA(cudaMemcpy2DAsync(sh->atoms->ptr, static_cast<size_t>(w) * 4,
+                                    static_cast<const float*>(seg->atoms->ptr) + col_begin,
+                                    static_cast<size_t>(g.cols) * 4, static_cast<size_t>(w) * 4, g.n_atoms,
+                                    cudaMemcpyDeviceToDevice, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        *out = sh.release();
     });
 }
 

@@ -7,6 +7,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <cstring>
 #include <initializer_list>
 #include <string>
@@ -28,6 +29,7 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -46,6 +48,7 @@ NcclApi& nccl() {
     api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
     api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
     api.handle = h;
     return api;
@@ -66,7 +69,7 @@ struct Linear {
     const csdr_segment* seg = nullptr;  // owned by the archive
     csdr_segment* shard = nullptr;      // owned here
     DevPtr raw;                         // fp32 (rows_local x cols), rows already sliced
-    uint32_t rows = 0, cols = 0, rows_local = 0;
+    uint32_t rows = 0, cols = 0, rows_local = 0, cols_local = 0;
     const csdr_segment* use() const { return shard ? shard : seg; }
 };
 
@@ -92,7 +95,11 @@ struct csdr_decoder {
     size_t cache_layer_stride = 0;
     std::vector<int32_t> pos_host;
     DevPtr pos_dev, tokens_dev, seq_of, pos_of, next_dev;
-    DevPtr hidden, normed, q, k, v, att, att_full, proj, gate, up, act_full, staged, logits, logits_l;
+    DevPtr hidden, normed, normed_l, q, k, v, att, proj, gate, up, staged, logits, logits_l;
+    // projections of a group between its two launches, behind a block of per-token sums of
+    // squares: [sum_pad floats][Dx of every member]; tensor-parallel ranks add theirs up in place
+    DevPtr dxbuf;
+    uint32_t sum_pad = 0;
     // bf16 hi/lo planes of the three activation widths the projections consume (hidden,
     // attention output, SwiGLU product) for steps that run on the tensor cores
     DevPtr xp_h, xp_att, xp_act;
@@ -126,15 +133,21 @@ std::vector<float> load_raw(csdr_archive* ar, const std::string& name, size_t wa
     return v;
 }
 
+// A norm weight vector; tensor-parallel ranks keep their slice of it.
 DevPtr load_vector(csdr_decoder* d, const std::string& name, uint32_t n) {
     std::vector<float> v = load_raw(d->ar, name, n);
-    DevPtr p = upload(d->ctx, v.data(), static_cast<size_t>(n) * 4);
+    const uint32_t nl = n / d->P;
+    DevPtr p = upload(d->ctx, v.data() + static_cast<size_t>(d->rank) * nl, static_cast<size_t>(nl) * 4);
     CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
     return p;
 }
 
-// Resolve a linear by name; shard its output rows [rank*R/P, (rank+1)*R/P) when sharded.
-Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint32_t cols, bool sharded) {
+// Resolve a linear by name. Tensor-parallel ranks keep output rows [rank*R/P, (rank+1)*R/P) of
+// the code stream (row_shard) and input columns [rank*C/P, (rank+1)*C/P) of the dictionary
+// (col_shard): each rank then reads 1/P of every dictionary, projects its slice of the
+// activations, and the ranks' partial projections are summed before the gather.
+Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint32_t cols, bool row_shard,
+                   bool col_shard) {
     csdr_segment_header h{};
     int rc = csdr_archive_find(d->ar, name.c_str(), &h);
     if (rc == CSDR_ERR_NOT_FOUND) throw Error(CSDR_ERR_NOT_FOUND, "decoder: tensor not in archive: " + name);
@@ -142,18 +155,32 @@ Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint
     Linear l;
     l.rows = rows;
     l.cols = cols;
-    const uint32_t P = sharded ? d->P : 1u;
-    if (rows % P) throw Error(CSDR_ERR_GEOMETRY, "decoder: rows of '" + name + "' do not divide by the tensor-parallel size");
-    l.rows_local = rows / P;
-    const uint32_t r0 = (sharded ? d->rank : 0u) * l.rows_local;
+    const uint32_t PR = row_shard ? d->P : 1u, PC = col_shard ? d->P : 1u;
+    if (rows % PR || cols % PC)
+        throw Error(CSDR_ERR_GEOMETRY, "decoder: shape of '" + name + "' does not divide by the tensor-parallel size");
+    l.rows_local = rows / PR;
+    l.cols_local = cols / PC;
+    const uint32_t r0 = (row_shard ? d->rank : 0u) * l.rows_local;
+    const uint32_t c0 = (col_shard ? d->rank : 0u) * l.cols_local;
     if (h.strategy_id == kHSDRStrategyId) {
         rethrow_last(csdr_archive_segment(d->ar, name.c_str(), &l.seg));
         if (l.seg->g.rows != rows || l.seg->g.cols != cols)
             throw Error(CSDR_ERR_GEOMETRY, "decoder: shape of '" + name + "' does not match the config");
-        if (P > 1) rethrow_last(csdr_segment_shard_rows(d->ctx, l.seg, r0, r0 + l.rows_local, &l.shard));
+        csdr_segment* by_cols = nullptr;
+        if (PC > 1) rethrow_last(csdr_segment_shard_cols(d->ctx, l.seg, c0, c0 + l.cols_local, &by_cols));
+        if (PR > 1) {
+            rc = csdr_segment_shard_rows(d->ctx, by_cols ? by_cols : l.seg, r0, r0 + l.rows_local, &l.shard);
+            if (by_cols) csdr_segment_destroy(by_cols);   // the row shard shares its dictionary
+            rethrow_last(rc);
+        } else {
+            l.shard = by_cols;
+        }
     } else if (h.strategy_id == 0) {
+        if (d->P > 1)
+            throw Error(CSDR_ERR_UNSUPPORTED, "decoder: tensor-parallel decoding needs HSDR-encoded linears ('" + name +
+                                                  "' is stored raw)");
         std::vector<float> w = load_raw(d->ar, name, static_cast<size_t>(rows) * cols);
-        l.raw = upload(d->ctx, w.data() + static_cast<size_t>(r0) * cols, static_cast<size_t>(l.rows_local) * cols * 4);
+        l.raw = upload(d->ctx, w.data(), static_cast<size_t>(rows) * cols * 4);
         CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
     } else {
         throw Error(CSDR_ERR_UNSUPPORTED, "decoder: tensor '" + name + "' uses a strategy this library does not decode");
@@ -199,23 +226,24 @@ void linear_group(csdr_decoder* d, std::initializer_list<const Linear*> ls, cons
                                                 CSDR_LAYOUT_TOKEN_MAJOR));
 }
 
-// Rejoin row shards: local (T x W) on every rank -> full (T x P*W), replicated.
-void rejoin(csdr_decoder* d, const float* local, uint32_t T, uint32_t W, float* full, bool add) {
-    nccl_check(nccl().AllGather(local, F(d->staged), static_cast<size_t>(T) * W, ncclFloat, d->comm, d->ctx->stream),
-               "ncclAllGather");
-    op_unshard(d->ctx, F(d->staged), d->P, T, W, full, add);
-}
-
 void embed(csdr_decoder* d, uint32_t T) {
     if (d->emb.raw) op_gather_rows(d->ctx, F(d->emb.raw), d->cfg.vocab, d->cfg.hidden, I32(d->tokens_dev), T, F(d->hidden));
-    else launch_decode_rows(d->ctx, d->emb.seg, I32(d->tokens_dev), T, F(d->hidden));
+    else launch_decode_rows(d->ctx, d->emb.use(), I32(d->tokens_dev), T, F(d->hidden));
 }
 
 __nv_bfloat16* BF(const DevPtr& p) { return static_cast<__nv_bfloat16*>(p->ptr); }
 
-// One group of linears over activation planes: a projection launch plus a gather launch.
-void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const DevPtr& planes, uint32_t T, uint32_t width,
-          std::initializer_list<WideOut> outs) {
+// Sum the ranks' partial projections (and, when asked, the block of per-token sums of squares
+// in front of them) in place. One collective per group of linears.
+void sum_over_ranks(csdr_decoder* d, float* from, size_t floats) {
+    if (d->P == 1) return;
+    nccl_check(nccl().AllReduce(from, from, floats, ncclFloat, ncclSum, d->comm, d->ctx->stream), "ncclAllReduce");
+}
+
+// One group of linears over activation planes: projection launch, rank sum, gather launch.
+// `normed`: the planes hold w*h and the gather applies 1/rms from the sums of squares.
+void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_bfloat16* planes, size_t plane_elems,
+          uint32_t T, bool normed, const float* sums, std::initializer_list<WideOut> outs) {
     const csdr_segment* segs[4];
     WideOut o[4];
     uint32_t n = 0;
@@ -224,56 +252,72 @@ void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const DevPtr
         segs[n] = l->use();
         o[n++] = *it++;
     }
-    const XPlanesView xp{BF(planes), BF(planes) + static_cast<size_t>(T) * width};
-    launch_matmul_wide_group(d->ctx, segs, n, xp, T, o, CSDR_LAYOUT_TOKEN_MAJOR);
+    const XPlanesView xp{planes, planes + plane_elems};
+    float* base = F(d->dxbuf);
+    const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
+    // the sums sit right in front of the projections: one collective covers both
+    if (normed && sums == base) sum_over_ranks(d, base, d->sum_pad + w.floats);
+    else sum_over_ranks(d, w.base, w.floats);
+    TokenScale ts{};
+    if (normed) ts = TokenScale{sums, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
+    launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts);
 }
 
-// The block loop for steps of at least the tensor-core threshold on one GPU: every glue kernel
-// hands its result to the next projection as bf16 planes, q|k|v and gate|up share a projection
-// launch and a gather launch, and the two residual additions ride on the gathers of the output
-// and down projections. Same arithmetic as run_blocks otherwise.
+// The block loop on the tensor cores (steps of at least the tensor-core threshold on one GPU;
+// every step under tensor parallelism). Every glue kernel hands its result to the next
+// projection as bf16 planes; q|k|v and gate|up share a projection launch and a gather launch;
+// the residual additions ride on the gathers of the output and down projections; RMS
+// normalisation is split into "planes of w*h + sums of squares" before the projection and
+// "times 1/rms" in the gather. With P ranks everything is sliced P ways - hidden width, heads,
+// KV cache, intermediate width, dictionary columns, code rows - and the only exchange is the sum
+// of the ranks' partial projections (K x T floats per dictionary), four per block.
+// Leaves the final hidden states in d->hidden (this rank's slice) and the final norm's planes
+// and sums in xp_h / dxbuf.
 void run_blocks_planes(csdr_decoder* d, uint32_t T) {
     const csdr_decoder_config& c = d->cfg;
     csdr_context* ctx = d->ctx;
-    const uint32_t H = c.hidden, HD = c.head_dim;
+    const uint32_t HD = c.head_dim, Hl = d->H_l;
+    float* sums = F(d->dxbuf);
     __nv_bfloat16* h_hi = BF(d->xp_h);
-    __nv_bfloat16* h_lo = h_hi + static_cast<size_t>(T) * H;
     __nv_bfloat16* a_hi = BF(d->xp_att);
-    __nv_bfloat16* a_lo = a_hi + static_cast<size_t>(T) * d->QD_l;
     __nv_bfloat16* i_hi = BF(d->xp_act);
-    __nv_bfloat16* i_lo = i_hi + static_cast<size_t>(T) * d->I_l;
-    op_rmsnorm_planes(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, h_hi, h_lo);
+    const size_t h_n = static_cast<size_t>(T) * Hl, a_n = static_cast<size_t>(T) * d->QD_l, i_n = static_cast<size_t>(T) * d->I_l;
+    op_scale_sumsq_planes(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, Hl, h_hi, h_hi + h_n, sums);
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         Layer& L = d->layers[li];
-        wide(d, {&L.q, &L.k, &L.v}, d->xp_h, T, H,
+        wide(d, {&L.q, &L.k, &L.v}, h_hi, h_n, T, true, sums,
              {WideOut{F(d->q), nullptr, nullptr}, WideOut{F(d->k), nullptr, nullptr}, WideOut{F(d->v), nullptr, nullptr}});
         float* kc = F(d->kcache) + li * d->cache_layer_stride;
         float* vc = F(d->vcache) + li * d->cache_layer_stride;
         op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
                       c.max_seq, c.rope_theta);
         op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, nullptr,
-                     a_hi, a_lo);
-        wide(d, {&L.o}, d->xp_att, T, d->QD_l, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
-        op_rmsnorm_planes(ctx, F(d->hidden), F(L.ffn_norm), T, H, c.rms_eps, h_hi, h_lo);
-        wide(d, {&L.gate, &L.up}, d->xp_h, T, H,
+                     a_hi, a_hi + a_n);
+        wide(d, {&L.o}, a_hi, a_n, T, false, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
+        op_scale_sumsq_planes(ctx, F(d->hidden), F(L.ffn_norm), T, Hl, h_hi, h_hi + h_n, sums);
+        wide(d, {&L.gate, &L.up}, h_hi, h_n, T, true, sums,
              {WideOut{F(d->gate), nullptr, nullptr}, WideOut{F(d->up), nullptr, nullptr}});
-        op_silu_mul_planes(ctx, F(d->gate), F(d->up), static_cast<size_t>(T) * d->I_l, i_hi, i_lo);
-        wide(d, {&L.down}, d->xp_act, T, d->I_l, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
-        if (li + 1 < c.n_layers)
-            op_rmsnorm_planes(ctx, F(d->hidden), F(d->layers[li + 1].attn_norm), T, H, c.rms_eps, h_hi, h_lo);
-        else
-            op_rmsnorm(ctx, F(d->hidden), F(d->out_norm), T, H, c.rms_eps, F(d->normed));
+        op_silu_mul_planes(ctx, F(d->gate), F(d->up), i_n, i_hi, i_hi + i_n);
+        wide(d, {&L.down}, i_hi, i_n, T, false, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
+        const float* next_norm = li + 1 < c.n_layers ? F(d->layers[li + 1].attn_norm) : F(d->out_norm);
+        op_scale_sumsq_planes(ctx, F(d->hidden), next_norm, T, Hl, h_hi, h_hi + h_n, sums);
     }
 }
 
-// All blocks over T tokens whose (sequence, position) pairs sit in seq_of/pos_of; leaves the
-// final-normed hidden states in d->normed.
+bool use_planes(const csdr_decoder* d, uint32_t T) {
+    if (d->P > 1) return true;
+    const csdr_context* ctx = d->ctx;
+    return d->planes_capable && ctx->tensor_cores && ctx->tma && T >= ctx->tc_min_batch;
+}
+
+// All blocks over T tokens whose (sequence, position) pairs sit in seq_of/pos_of. On return
+// either d->normed holds the final-normed hidden states (fp32 path), or the planes path's state
+// described above does.
 void run_blocks(csdr_decoder* d, uint32_t T) {
     const csdr_decoder_config& c = d->cfg;
     csdr_context* ctx = d->ctx;
     const uint32_t H = c.hidden, HD = c.head_dim;
-    const bool tp = d->P > 1;
-    if (d->planes_capable && ctx->tensor_cores && ctx->tma && T >= ctx->tc_min_batch) {
+    if (use_planes(d, T)) {
         run_blocks_planes(d, T);
         return;
     }
@@ -286,43 +330,59 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
         op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
                       c.max_seq, c.rope_theta);
         op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
-        const float* att = F(d->att);
-        if (tp) {
-            rejoin(d, F(d->att), T, d->QD_l, F(d->att_full), false);
-            att = F(d->att_full);
-        }
-        linear(d, L.o, att, T, F(d->proj));
-        if (tp) {
-            rejoin(d, F(d->proj), T, d->H_l, F(d->hidden), true);
-            op_rmsnorm(ctx, F(d->hidden), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
-        } else {
-            op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
-        }
+        linear(d, L.o, F(d->att), T, F(d->proj));
+        op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
         linear_group(d, {&L.gate, &L.up}, F(d->normed), T, {F(d->gate), F(d->up)});
         op_silu_mul(ctx, F(d->gate), F(d->up), static_cast<size_t>(T) * d->I_l, F(d->gate));
-        const float* act = F(d->gate);
-        if (tp) {
-            rejoin(d, F(d->gate), T, d->I_l, F(d->act_full), false);
-            act = F(d->act_full);
-        }
-        linear(d, L.down, act, T, F(d->proj));
+        linear(d, L.down, F(d->gate), T, F(d->proj));
         const float* next_norm = li + 1 < c.n_layers ? F(d->layers[li + 1].attn_norm) : F(d->out_norm);
-        if (tp) {
-            rejoin(d, F(d->proj), T, d->H_l, F(d->hidden), true);
-            op_rmsnorm(ctx, F(d->hidden), next_norm, T, H, c.rms_eps, F(d->normed));
-        } else {
-            op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), next_norm, T, H, c.rms_eps, F(d->normed));
-        }
+        op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), next_norm, T, H, c.rms_eps, F(d->normed));
     }
 }
 
-// logits (T x vocab) of the given final-normed hidden rows.
-void run_logits(csdr_decoder* d, const float* hidden_rows, uint32_t T) {
+// Final-normed hidden states of all T tokens, whole width, into d->normed (what forward() hands
+// back); only the planes path has work to do here.
+void materialise_normed(csdr_decoder* d, uint32_t T) {
+    if (!use_planes(d, T)) return;
+    float* sums = F(d->dxbuf);
+    sum_over_ranks(d, sums, T);
+    if (d->P == 1) {
+        op_norm_from_sumsq(d->ctx, F(d->hidden), F(d->out_norm), sums, T, d->H_l, d->cfg.hidden, d->cfg.rms_eps, F(d->normed));
+        return;
+    }
+    op_norm_from_sumsq(d->ctx, F(d->hidden), F(d->out_norm), sums, T, d->H_l, d->cfg.hidden, d->cfg.rms_eps, F(d->normed_l));
+    nccl_check(nccl().AllGather(F(d->normed_l), F(d->staged), static_cast<size_t>(T) * d->H_l, ncclFloat, d->comm,
+                                d->ctx->stream),
+               "ncclAllGather");
+    op_unshard(d->ctx, F(d->staged), d->P, T, d->H_l, F(d->normed), false);
+}
+
+// logits (n x vocab) of tokens [t0, t0 + n) of the T that run_blocks just processed. `summed`:
+// materialise_normed already added the ranks' sums of squares up.
+void run_logits(csdr_decoder* d, uint32_t T, uint32_t t0, uint32_t n, bool summed) {
+    if (!use_planes(d, T)) {
+        linear(d, d->lm_head, F(d->normed) + static_cast<size_t>(t0) * d->cfg.hidden, n, F(d->logits));
+        return;
+    }
+    // the final norm's planes and sums are in place; rows t0.. of them feed the head
+    float* base = F(d->dxbuf);
+    const size_t h_n = static_cast<size_t>(T) * d->H_l;
+    const __nv_bfloat16* hi = BF(d->xp_h) + static_cast<size_t>(t0) * d->H_l;
+    const csdr_segment* seg = d->lm_head.use();
+    const XPlanesView xp{hi, hi + h_n};
+    const WideDx w = launch_wide_project(d->ctx, &seg, 1, xp, n, base + d->sum_pad);
     if (d->P > 1) {
-        linear(d, d->lm_head, hidden_rows, T, F(d->logits_l));
-        rejoin(d, F(d->logits_l), T, d->V_l, F(d->logits), false);
-    } else {
-        linear(d, d->lm_head, hidden_rows, T, F(d->logits));
+        if (!summed) sum_over_ranks(d, base, T);
+        sum_over_ranks(d, w.base, w.floats);
+    }
+    const TokenScale ts{base + t0, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
+    const WideOut out{d->P > 1 ? F(d->logits_l) : F(d->logits), nullptr, nullptr};
+    launch_wide_gather(d->ctx, &seg, 1, w, n, &out, CSDR_LAYOUT_TOKEN_MAJOR, ts);
+    if (d->P > 1) {
+        nccl_check(nccl().AllGather(F(d->logits_l), F(d->staged), static_cast<size_t>(n) * d->V_l, ncclFloat, d->comm,
+                                    d->ctx->stream),
+                   "ncclAllGather");
+        op_unshard(d->ctx, F(d->staged), d->P, n, d->V_l, F(d->logits), false);
     }
 }
 
@@ -398,13 +458,13 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         d->I_l = c.inter / d->P;
         d->H_l = H / d->P;
         d->V_l = c.vocab / d->P;
-        d->emb = load_linear(d.get(), "token_embd.weight", c.vocab, H, false);
+        d->emb = load_linear(d.get(), "token_embd.weight", c.vocab, H, false, true);
         {
             csdr_segment_header h{};
             const char* head = csdr_archive_find(ar, "output.weight", &h) == CSDR_OK ? "output.weight"
                                : csdr_archive_find(ar, "lm_head.weight", &h) == CSDR_OK ? "lm_head.weight"
                                                                                         : "token_embd.weight";
-            d->lm_head = load_linear(d.get(), head, c.vocab, H, true);
+            d->lm_head = load_linear(d.get(), head, c.vocab, H, true, true);
         }
         d->out_norm = load_vector(d.get(), "output_norm.weight", H);
         d->layers.resize(c.n_layers);
@@ -413,13 +473,13 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
             Layer& L = d->layers[i];
             L.attn_norm = load_vector(d.get(), p + "attn_norm.weight", H);
             L.ffn_norm = load_vector(d.get(), p + "ffn_norm.weight", H);
-            L.q = load_linear(d.get(), p + "attn_q.weight", QD, H, true);
-            L.k = load_linear(d.get(), p + "attn_k.weight", KVD, H, true);
-            L.v = load_linear(d.get(), p + "attn_v.weight", KVD, H, true);
-            L.o = load_linear(d.get(), p + "attn_output.weight", H, QD, true);
-            L.gate = load_linear(d.get(), p + "ffn_gate.weight", c.inter, H, true);
-            L.up = load_linear(d.get(), p + "ffn_up.weight", c.inter, H, true);
-            L.down = load_linear(d.get(), p + "ffn_down.weight", H, c.inter, true);
+            L.q = load_linear(d.get(), p + "attn_q.weight", QD, H, true, true);
+            L.k = load_linear(d.get(), p + "attn_k.weight", KVD, H, true, true);
+            L.v = load_linear(d.get(), p + "attn_v.weight", KVD, H, true, true);
+            L.o = load_linear(d.get(), p + "attn_output.weight", H, QD, true, true);
+            L.gate = load_linear(d.get(), p + "ffn_gate.weight", c.inter, H, true, true);
+            L.up = load_linear(d.get(), p + "ffn_up.weight", c.inter, H, true, true);
+            L.down = load_linear(d.get(), p + "ffn_down.weight", H, c.inter, true, true);
         }
         csdr_context* ctx = d->ctx;
         d->T_max = std::max(c.max_seq, c.max_batch);
@@ -433,7 +493,7 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         d->seq_of = dev_alloc(ctx, T * 4);
         d->pos_of = dev_alloc(ctx, T * 4);
         d->next_dev = dev_alloc(ctx, c.max_batch * 4);
-        d->hidden = dev_alloc(ctx, T * H * 4);
+        d->hidden = dev_alloc(ctx, T * d->H_l * 4);
         d->normed = dev_alloc(ctx, T * H * 4);
         d->q = dev_alloc(ctx, T * d->QD_l * 4);
         d->k = dev_alloc(ctx, T * d->KVD_l * 4);
@@ -443,10 +503,12 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         d->gate = dev_alloc(ctx, T * d->I_l * 4);
         d->up = dev_alloc(ctx, T * d->I_l * 4);
         d->logits = dev_alloc(ctx, static_cast<size_t>(c.max_batch) * c.vocab * 4);
-        if (d->P == 1) {
-            // the planes pipeline needs every block linear to be an HSDR image the grouped
-            // tensor-core path takes
-            bool ok = true;
+        {
+            // the planes path needs every block linear (and the head) to be an HSDR image the
+            // grouped tensor-core path takes
+            bool ok = !d->lm_head.raw;
+            uint32_t widest = 0;   // atoms of the largest group
+            auto atoms = [](const Linear& l) { return l.use() ? l.use()->g.n_atoms : 0u; };
             for (const Layer& L : d->layers) {
                 const Linear* all[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
                 for (const Linear* l : all) {
@@ -457,21 +519,32 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
                     const csdr_segment* sgp = l->use();
                     ok = ok && wide_group_supported(ctx, &sgp, 1, ctx->tc_min_batch);
                 }
+                widest = std::max({widest, atoms(L.q) + atoms(L.k) + atoms(L.v), atoms(L.gate) + atoms(L.up), atoms(L.o),
+                                   atoms(L.down)});
+            }
+            if (ok) {
+                const csdr_segment* sgp = d->lm_head.use();
+                ok = wide_group_supported(ctx, &sgp, 1, ctx->tc_min_batch);
+                widest = std::max(widest, atoms(d->lm_head));
             }
             d->planes_capable = ok;
+            if (d->P > 1 && !ok)
+                throw Error(CSDR_ERR_UNSUPPORTED,
+                            "decoder: tensor parallelism needs every linear as HSDR row tiles with a multiple of 128 "
+                            "atoms and per-rank input widths that are multiples of 64");
             if (ok) {
-                d->xp_h = dev_alloc(ctx, T * H * 4);           // two bf16 planes
+                d->xp_h = dev_alloc(ctx, T * d->H_l * 4);          // two bf16 planes each
                 d->xp_att = dev_alloc(ctx, T * d->QD_l * 4);
                 d->xp_act = dev_alloc(ctx, T * d->I_l * 4);
+                d->sum_pad = static_cast<uint32_t>((T + 63) / 64 * 64);
+                d->dxbuf = dev_alloc(ctx, (d->sum_pad + static_cast<size_t>(widest) * std::max<size_t>(T, 16)) * 4);
+                CSDR_CUDA(cudaMemsetAsync(d->dxbuf->ptr, 0, d->dxbuf->bytes, ctx->stream));
             }
         }
         if (d->P > 1) {
-            d->att_full = dev_alloc(ctx, T * QD * 4);
-            d->act_full = dev_alloc(ctx, T * c.inter * 4);
+            d->normed_l = dev_alloc(ctx, T * d->H_l * 4);
             d->logits_l = dev_alloc(ctx, static_cast<size_t>(c.max_batch) * d->V_l * 4);
-            const size_t widest = std::max<size_t>(std::max<size_t>(T * QD, T * c.inter),
-                                                   std::max<size_t>(T * H, static_cast<size_t>(c.max_batch) * c.vocab));
-            d->staged = dev_alloc(ctx, widest * 4);
+            d->staged = dev_alloc(ctx, std::max<size_t>(T * H, static_cast<size_t>(c.max_batch) * c.vocab) * 4);
         }
         CSDR_CUDA(cudaMemsetAsync(d->kcache->ptr, 0, d->kcache->bytes, ctx->stream));
         CSDR_CUDA(cudaMemsetAsync(d->vcache->ptr, 0, d->vcache->bytes, ctx->stream));
@@ -532,11 +605,13 @@ int csdr_decoder_forward(csdr_decoder* d, uint32_t seq, const int32_t* tokens, s
         CSDR_CUDA(cudaMemcpyAsync(d->pos_of->ptr, po.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
         embed(d, T);
         run_blocks(d, T);
-        if (hidden_out)
+        if (hidden_out) {
+            materialise_normed(d, T);
             CSDR_CUDA(cudaMemcpyAsync(hidden_out, d->normed->ptr, static_cast<size_t>(T) * c.hidden * 4,
                                       cudaMemcpyDeviceToHost, ctx->stream));
+        }
         if (logits_out) {
-            run_logits(d, F(d->normed) + static_cast<size_t>(T - 1) * c.hidden, 1);
+            run_logits(d, T, T - 1, 1, hidden_out != nullptr);
             CSDR_CUDA(cudaMemcpyAsync(logits_out, d->logits->ptr, static_cast<size_t>(c.vocab) * 4,
                                       cudaMemcpyDeviceToHost, ctx->stream));
         }
@@ -562,7 +637,7 @@ int csdr_decoder_step_device_async(csdr_decoder* d, const int32_t* tokens_dev, s
         op_step_positions(ctx, I32(d->pos_dev), B, I32(d->seq_of), I32(d->pos_of));
         embed(d, B);
         run_blocks(d, B);
-        run_logits(d, F(d->normed), B);
+        run_logits(d, B, 0, B, false);
         op_argmax(ctx, F(d->logits), B, c.vocab, next_dev);
         for (size_t b = 0; b < batch; ++b) ++d->pos_host[b];
     });

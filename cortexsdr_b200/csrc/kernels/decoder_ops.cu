@@ -88,6 +88,44 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_
 }
 
 // hidden += delta, then out = rmsnorm(hidden) — the residual add and the next norm in one pass.
+// Planes of w * x (not normalised) plus each token's sum of squares over this slice of the
+// hidden width: the normalisation itself is applied behind the projection, where a
+// tensor-parallel rank has the sums of all slices (rms_norm, api/cortex_sdk.cpp:1208-1232, split
+// in two).
+__global__ void __launch_bounds__(256)
+scale_sumsq_planes_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_t H,
+                          __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                          float* __restrict__ sumsq) {
+    pdl_enter();
+    __shared__ float red[8];
+    const size_t o = static_cast<size_t>(blockIdx.x) * H;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < H; i += 256) {
+        const float v = x[o + i];
+        ss = fmaf(v, v, ss);
+        store_planes(hi, lo, o + i, v * w[i]);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t += red[i];
+        sumsq[blockIdx.x] = t;
+    }
+}
+
+// out = x * w / rms, with the sum of squares of the whole hidden width given.
+__global__ void __launch_bounds__(256)
+norm_from_sumsq_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ sumsq,
+                       uint32_t H, float inv_width, float eps, float* __restrict__ out) {
+    pdl_enter();
+    const size_t o = static_cast<size_t>(blockIdx.x) * H;
+    const float inv = rsqrtf(sumsq[blockIdx.x] * inv_width + eps);
+    for (uint32_t i = threadIdx.x; i < H; i += 256) out[o + i] = x[o + i] * inv * w[i];
+}
+
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
                    const float* __restrict__ w, uint32_t H, float eps, float* __restrict__ out) {
@@ -396,6 +434,21 @@ void op_rmsnorm_planes(csdr_context* ctx, const float* x, const float* w, uint32
     LaunchScope ls(ctx, KC_DECODER_OP);
     launch_pdl(ctx, rmsnorm_kernel, dim3(T), dim3(256), x, w, H, eps, nullptr, hi, lo);
     ls.done("rmsnorm_kernel");
+}
+
+void op_scale_sumsq_planes(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H,
+                           __nv_bfloat16* hi, __nv_bfloat16* lo, float* sumsq) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    launch_pdl(ctx, scale_sumsq_planes_kernel, dim3(T), dim3(256), x, w, H, hi, lo, sumsq);
+    ls.done("scale_sumsq_planes_kernel");
+}
+
+void op_norm_from_sumsq(csdr_context* ctx, const float* x, const float* w, const float* sumsq, uint32_t T,
+                        uint32_t H, uint32_t full_width, float eps, float* out) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    launch_pdl(ctx, norm_from_sumsq_kernel, dim3(T), dim3(256), x, w, sumsq, H, 1.0f / static_cast<float>(full_width),
+               eps, out);
+    ls.done("norm_from_sumsq_kernel");
 }
 
 void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const float* w, uint32_t T,

@@ -16,6 +16,13 @@ namespace csdr {
 void op_rmsnorm(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps, float* out);
 void op_rmsnorm_planes(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H, float eps,
                        __nv_bfloat16* hi, __nv_bfloat16* lo);
+// RMS normalisation in two halves for hidden states split over tensor-parallel ranks (H = this
+// rank's slice): planes of w*x plus per-token sums of squares; and the normalised values once
+// the sums over the whole width are known.
+void op_scale_sumsq_planes(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H,
+                           __nv_bfloat16* hi, __nv_bfloat16* lo, float* sumsq);
+void op_norm_from_sumsq(csdr_context* ctx, const float* x, const float* w, const float* sumsq, uint32_t T,
+                        uint32_t H, uint32_t full_width, float eps, float* out);
 void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const float* w, uint32_t T,
                     uint32_t H, float eps, float* out);
 void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, float* kc, float* vc,

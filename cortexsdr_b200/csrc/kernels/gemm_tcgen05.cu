@@ -339,7 +339,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, uint32_t k,
                         const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
                         uint32_t M /* tokens in dx rows */, uint32_t rows_per_cta, YView yv,
-                        const float* residual /* laid out like y, added on the way out; may be y itself */) {
+                        const float* residual /* laid out like y, added on the way out; may be y itself */,
+                        TokenScale ts) {
     extern __shared__ __align__(16) float wsm[];
     asm volatile("griddepcontrol.launch_dependents;");
     float* dxs = wsm;                                           // [K][64]
@@ -448,15 +449,31 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
             }
 #pragma unroll
             for (uint32_t i = 0; i < 4u; ++i) {
-                const float bias = (yv.bias && rq + i < nrows) ? yv.bias[r0 + rq + i] : 0.0f;
-                out[rq + i][0] = acc[i].x + bias;
-                out[rq + i][1] = acc[i].y + bias;
-                out[rq + i][2] = acc[i].z + bias;
-                out[rq + i][3] = acc[i].w + bias;
+                out[rq + i][0] = acc[i].x;
+                out[rq + i][1] = acc[i].y;
+                out[rq + i][2] = acc[i].z;
+                out[rq + i][3] = acc[i].w;
             }
         }
         const uint32_t tl = 4u * l16;               // first token of this lane inside the slice
         if (tl >= tw) continue;
+        if (ts.sumsq) {
+            // RMS normalisation folded behind the product: y = (W (w*h)) / rms(h), per token
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                const float inv = tl + j < tw ? rsqrtf(ts.sumsq[t0 + tl + j] * ts.inv_width + ts.eps) : 0.0f;
+#pragma unroll
+                for (uint32_t rb = 0; rb < kWideRows; ++rb) out[rb][j] *= inv;
+            }
+        }
+        if (yv.bias) {
+#pragma unroll
+            for (uint32_t rb = 0; rb < kWideRows; ++rb) {
+                const float bias = rb < nrows ? yv.bias[r0 + rb] : 0.0f;
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) out[rb][j] += bias;
+            }
+        }
         if (yv.layout == CSDR_LAYOUT_FEATURE_MAJOR) {
             // y[r][token]: a row's 64 tokens are contiguous
             const size_t col = static_cast<size_t>(yv.b0) + t0 + tl;
@@ -527,6 +544,7 @@ struct GatherGroupParams {
     GatherMember m[kGatherGroupMax];
     uint32_t n_seg, M, m_total, code_cap16;
     int y_layout;
+    TokenScale ts;
 };
 
 template <int MT>
@@ -595,6 +613,7 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
             const uint32_t r = row0 + rl;
             const size_t o = g.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * g.m_total + b
                                                                       : static_cast<size_t>(b) * m.R + r;
+            if (g.ts.sumsq) acc *= rsqrtf(g.ts.sumsq[b] * g.ts.inv_width + g.ts.eps);
             if (m.bias) acc += m.bias[r];
             if (m.residual) acc += m.residual[o];
             m.y[o] = acc;
@@ -637,7 +656,7 @@ void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t tot
 }
 
 void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float* dx, uint32_t M, const YView& yv,
-                        const float* residual) {
+                        const float* residual, const TokenScale& ts) {
     const Geometry& g = seg->g;
     const size_t smem = gather_wide_smem(g.n_atoms);
     static size_t smem_set = 0;
@@ -666,7 +685,7 @@ void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float*
     cfg.numAttrs = 1;
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_gather_wide_kernel, seg->codes_ptr(), g.rows, g.n_stages, g.k,
                                  static_cast<const float*>(seg->scales->ptr), dx, g.n_atoms, M, rows_per_cta, yv,
-                                 residual));
+                                 residual, ts));
     ls.done("hsdr_gather_wide_kernel");
 }
 
@@ -681,41 +700,48 @@ bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* se
     return true;
 }
 
-void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
-                              uint32_t M, const WideOut* outs, int y_layout) {
+WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x, uint32_t M,
+                           float* dx_base) {
     if (n == 0 || n > kGatherGroupMax) throw Error(CSDR_ERR_LIMIT, "matmul group holds 1 to 4 segments");
-    uint32_t tile_mt = 0;
+    WideDx w{};
     if (M <= 16u) {
-        tile_mt = 1;
-        while (tile_mt < M) tile_mt <<= 1;
+        w.tile_mt = 1;
+        while (w.tile_mt < M) w.tile_mt <<= 1;
     }
-    const uint32_t stride = tile_mt ? tile_mt : M;
+    w.stride = w.tile_mt ? w.tile_mt : M;
     size_t total_atoms = 0;
     for (uint32_t i = 0; i < n; ++i) total_atoms += segs[i]->g.n_atoms;
-    float* dx0 = static_cast<float*>(ctx->scratch_get(0, total_atoms * std::max<size_t>(stride, 16u) * 4u));
-    float* dx[kGatherGroupMax];
+    w.floats = total_atoms * w.stride;
+    w.base = dx_base ? dx_base
+                     : static_cast<float*>(ctx->scratch_get(0, total_atoms * std::max<size_t>(w.stride, 16u) * 4u));
     size_t off = 0;
     for (uint32_t i = 0; i < n; ++i) {
-        dx[i] = dx0 + off;
-        off += static_cast<size_t>(segs[i]->g.n_atoms) * stride;
+        w.dx[i] = w.base + off;
+        off += static_cast<size_t>(segs[i]->g.n_atoms) * w.stride;
     }
-    launch_dx_tma_group(ctx, segs, n, x, M, dx, stride);
-    if (tile_mt) {
+    launch_dx_tma_group(ctx, segs, n, x, M, w.dx, w.stride);
+    return w;
+}
+
+void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
+                        const WideOut* outs, int y_layout, const TokenScale& ts) {
+    if (w.tile_mt) {
         GatherGroupParams g{};
         g.n_seg = n;
         g.M = M;
         g.m_total = M;
         g.y_layout = y_layout;
+        g.ts = ts;
         uint32_t total_rows = 0, max_k = 0, max_slots = 0;
         for (uint32_t i = 0; i < n; ++i) {
             const Geometry& sg = segs[i]->g;
-            g.m[i] = GatherMember{segs[i]->codes_ptr(), static_cast<const float*>(segs[i]->scales->ptr), dx[i], outs[i].y,
+            g.m[i] = GatherMember{segs[i]->codes_ptr(), static_cast<const float*>(segs[i]->scales->ptr), w.dx[i], outs[i].y,
                                   outs[i].bias, outs[i].residual, sg.rows, sg.n_stages, sg.k, sg.n_atoms, 0u, 0u};
             total_rows += sg.rows;
             max_k = std::max(max_k, sg.n_atoms);
             max_slots = std::max(max_slots, sg.slots());
         }
-        switch (tile_mt) {
+        switch (w.tile_mt) {
             case 1: launch_gather_group_t<1>(ctx, g, total_rows, max_k, max_slots); break;
             case 2: launch_gather_group_t<2>(ctx, g, total_rows, max_k, max_slots); break;
             case 4: launch_gather_group_t<4>(ctx, g, total_rows, max_k, max_slots); break;
@@ -726,8 +752,14 @@ void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs
     }
     for (uint32_t i = 0; i < n; ++i) {
         YView yv{outs[i].y, y_layout, segs[i]->g.rows, M, 0u, M, outs[i].bias};
-        launch_gather_wide(ctx, segs[i], dx[i], M, yv, outs[i].residual);
+        launch_gather_wide(ctx, segs[i], w.dx[i], M, yv, outs[i].residual, ts);
     }
+}
+
+void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
+                              uint32_t M, const WideOut* outs, int y_layout) {
+    const WideDx w = launch_wide_project(ctx, segs, n, x, M, nullptr);
+    launch_wide_gather(ctx, segs, n, w, M, outs, y_layout, TokenScale{});
 }
 
 bool tcgen05_supported(const csdr_context* ctx, const csdr_segment* seg, size_t batch) {
@@ -804,7 +836,7 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
         return;
     }
     YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
-    launch_gather_wide(ctx, seg, dx, M, yv, nullptr);
+    launch_gather_wide(ctx, seg, dx, M, yv, nullptr, TokenScale{});
 }
 
 }  // namespace csdr

@@ -48,6 +48,28 @@ struct WideOut {
     const float* bias;
     const float* residual;
 };
+// Per-token factor applied by the gather before bias and residual: 1 / sqrt(sumsq[t] * inv_width
+// + eps). With activations w*h (not yet normalised) this is the RMS normalisation of h moved
+// behind the product; sumsq == nullptr means no factor.
+struct TokenScale {
+    const float* sumsq = nullptr;
+    float inv_width = 0.0f;
+    float eps = 0.0f;
+};
+// Where a group's projections live between the two launches: member i at dx[i], rows `stride`
+// floats apart, `floats` in all from `base` (one contiguous block, so that tensor-parallel
+// ranks can sum their partial projections with one collective over it).
+struct WideDx {
+    float* base;
+    float* dx[4];
+    size_t floats;
+    uint32_t stride, tile_mt;
+};
+// The two halves of launch_matmul_wide_group. dx_base == nullptr: context scratch.
+WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x, uint32_t M,
+                           float* dx_base);
+void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
+                        const WideOut* outs, int y_layout, const TokenScale& ts);
 bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, size_t batch);
 void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
                               uint32_t M, const WideOut* outs, int y_layout);

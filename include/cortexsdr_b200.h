@@ -140,6 +140,13 @@ CSDR_API int csdr_segment_info(const csdr_segment* seg, csdr_payload_info* info)
  * dictionary is shared with `seg`, which must outlive the shard. */
 CSDR_API int csdr_segment_shard_rows(csdr_context* ctx, const csdr_segment* seg,
                                      uint32_t row_begin, uint32_t row_end, csdr_segment** out);
+/* Column-shard for tensor parallelism (1-D row tiles): keep input columns [col_begin, col_end),
+ * multiples of four, of every dictionary atom, copied into a dictionary of the shard's own;
+ * the code stream is shared with `seg`, which must outlive the shard. A column shard times
+ * the matching slice of x is that slice's share of W x: the shares of all slices add up to
+ * the product (no counterpart in the reference, whose matmul is not distributed). */
+CSDR_API int csdr_segment_shard_cols(csdr_context* ctx, const csdr_segment* seg,
+                                     uint32_t col_begin, uint32_t col_end, csdr_segment** out);
 
 /* ---- sparse-code unpack ----
  * unpackIndexSign (strategies/HierarchicalSDRStrategy.cpp:81-84; loops :1394-1399,

@@ -227,6 +227,30 @@ def test_row_shards_concatenate_to_whole(ctx, oracle, golden):
         seg2.shard_rows(0, 40)
 
 
+def test_column_shards_add_up_to_the_whole_product(ctx, oracle):
+    """Input-column shards (tensor parallelism): each shard times its slice of x is that slice's
+    share of W x; shares add up to the oracle's product, on the GEMV path and the tensor-core path."""
+    from cortexsdr_b200 import synth
+    pay = synth.hsdr_payload(200, 512, n_atoms=128, k=4, seed=71)
+    seg = cs.Segment.from_payload(pay, ctx)
+    shards = [seg.shard_cols(b, e) for b, e in ((0, 128), (128, 320), (320, 512))]
+    assert [s.cols for s in shards] == [128, 192, 192] and all(s.rows == 200 for s in shards)
+    rng = np.random.default_rng(12)
+    for batch in (1, 16):
+        x = rng.normal(0, 1, (512, batch)).astype(np.float32)
+        want = oracle.matmul(pay, x, batch)
+        got = sum(s.matmul(np.ascontiguousarray(x[b:e]), batch)
+                  for s, (b, e) in zip(shards, ((0, 128), (128, 320), (320, 512))))
+        e = rel_err(got, want)
+        assert e[0] < TOL and e[1] < TOL, (batch, e)
+    # a row shard of a column shard keeps the column shard's dictionary
+    both = shards[1].shard_rows(40, 120)
+    x = rng.normal(0, 1, (192, 3)).astype(np.float32)
+    assert np.array_equal(both.matmul(x, 3), shards[1].matmul(x, 3)[40:120])
+    with pytest.raises(cs.CompressionError, match="multiples of four"):
+        seg.shard_cols(2, 130)
+
+
 def test_grouped_matmul_matches_single_calls(ctx, oracle, golden):
     import torch
     from cortexsdr_b200 import synth

@@ -1,6 +1,8 @@
-"""Tensor-parallel decoder on two GPUs: every compressed weight row-sharded, NCCL all-gather at
-the rejoin points, logits equal to the single-GPU decoder's. Needs two B200s; skipped otherwise.
-Ranks run as child processes, one per GPU, with in-switch reduction off (NCCL_NVLS_ENABLE=0)."""
+"""Tensor-parallel decoder on two GPUs: every compressed weight sharded by output rows (codes)
+and input columns (dictionary), the ranks' partial projections summed with one NCCL all-reduce
+per group of linears, logits equal to the single-GPU decoder's within the matmul tolerance.
+Needs two B200s; skipped otherwise. Ranks run as child processes, one per GPU, with in-switch
+reduction off (NCCL_NVLS_ENABLE=0)."""
 import os
 import sys
 
@@ -50,7 +52,7 @@ def test_two_rank_decoder_matches_single_gpu(tmp_path):
         pytest.skip("needs two GPUs")
     from cortexsdr_b200 import synth
     path = str(tmp_path / "tp.sdr")
-    synth.decoder_archive(path, **CFG, n_atoms=32, k=3, kv_atoms=16, seed=7)
+    synth.decoder_archive(path, **CFG, n_atoms=128, k=3, kv_atoms=128, seed=7)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29600 + os.getpid() % 1000
@@ -62,7 +64,7 @@ def test_two_rank_decoder_matches_single_gpu(tmp_path):
         p.join(timeout=60)
         assert p.exitcode == 0
     r0, r1 = res[0], res[1]
-    assert np.abs(r0["logits"] - r0["l1"]).max() < 1e-4
-    assert np.abs(r0["hidden"] - r0["h1"]).max() < 1e-4
-    assert np.abs(r0["step"] - r0["s1"]).max() < 1e-4 and r0["nxt"] == r0["n1"]
+    assert np.abs(r0["logits"] - r0["l1"]).max() < 1e-3
+    assert np.abs(r0["hidden"] - r0["h1"]).max() < 1e-3
+    assert np.abs(r0["step"] - r0["s1"]).max() < 1e-3 and r0["nxt"] == r0["n1"]
     assert np.array_equal(r0["logits"], r1["logits"])      # replicated result on every rank
