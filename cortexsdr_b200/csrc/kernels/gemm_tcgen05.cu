@@ -765,7 +765,10 @@ void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs
 bool tcgen05_supported(const csdr_context* ctx, const csdr_segment* seg, size_t batch) {
     const Geometry& g = seg->g;
     if (!ctx->tensor_cores || batch < ctx->tc_min_batch) return false;
-    if (!g.row_tiles() || g.n_atoms % kTileM || g.cols % kBlockK) return false;
+    if (!g.row_tiles() || g.n_atoms % kTileM) return false;
+    // the TMA-fed projection takes any multiple of eight columns, the register-fed one whole
+    // 64-column blocks
+    if (g.cols % kBlockK && !dx_tma_supported(ctx, seg, batch)) return false;
     if (g.slots() > kWideMaxSlots) return false;
     return gather_wide_smem(g.n_atoms) <= ctx->smem_optin;
 }

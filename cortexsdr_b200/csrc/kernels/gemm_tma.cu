@@ -489,7 +489,9 @@ bool dx_tma_supported(const csdr_context* ctx, const csdr_segment* seg, size_t b
     using namespace tma_detail;
     const Geometry& g = seg->g;
     (void)batch;
-    return ctx->tma && g.row_tiles() && g.n_atoms % kTileM == 0 && g.cols % kBlockK == 0 && encode_fn() != nullptr;
+    // rows of the bf16 planes must be 16-byte multiples for the tensor maps; a last 64-column
+    // block that sticks out past the row end reads as zero on both operands
+    return ctx->tma && g.row_tiles() && g.n_atoms % kTileM == 0 && g.cols % 8u == 0 && encode_fn() != nullptr;
 }
 
 XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_layout, uint32_t M, uint32_t cols) {
@@ -536,7 +538,7 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     for (uint32_t i = n_seg; i <= kMaxGroup; ++i) p.tile_begin[i] = atom_tiles;
 
     const uint32_t tok_tiles = (M + N - 1u) / N;
-    const uint32_t n_kb = cols / kBlockK;
+    const uint32_t n_kb = (cols + kBlockK - 1u) / kBlockK;
     const uint32_t stage_bytes = 2u * kATile + (has_lo ? 2u : 1u) * N * 128u;
 
     static bool attrs_set = false;

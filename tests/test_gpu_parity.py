@@ -276,11 +276,12 @@ def test_grouped_tensor_core_projection_matches_oracle(ctx, oracle):
     import torch
     from cortexsdr_b200 import synth
     shapes = ((264, 128), (96, 256), (130, 128))
-    pays = [synth.hsdr_payload(r, 512, n_atoms=k, k=4, seed=60 + i) for i, (r, k) in enumerate(shapes)]
+    # 472 columns: seven 64-column blocks and a ragged eighth
+    pays = [synth.hsdr_payload(r, 472, n_atoms=k, k=4, seed=60 + i) for i, (r, k) in enumerate(shapes)]
     segs = [cs.Segment.from_payload(p, ctx) for p in pays]
     rng = np.random.default_rng(11)
     for batch, dtype in ((8, "f32"), (13, "f32"), (16, "bf16"), (21, "f32"), (64, "bf16"), (130, "f32")):
-        xf = rng.normal(0, 1, (batch, 512)).astype(np.float32)
+        xf = rng.normal(0, 1, (batch, 472)).astype(np.float32)
         if dtype == "bf16":
             x = torch.from_numpy(xf).cuda().to(torch.bfloat16)
             xf = x.float().cpu().numpy()
