@@ -154,9 +154,18 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
         dist.barrier()
     B, ctxlen, steps = spec["batch"], spec["context"], spec["steps"]
     ld = cs.SDRModelLoader(path, ctx)
-    dec = cs.Decoder(ld, **cfg, max_seq=ctxlen + steps + 8, max_batch=B, rms_eps=spec["eps"], comm=comm)
+    ag = None
+    if world > 1:
+        def ag(b):
+            got = [None] * world
+            dist.all_gather_object(got, b)
+            return got
+    dec = cs.Decoder(ld, **cfg, max_seq=ctxlen + steps + 8, max_batch=B, rms_eps=spec["eps"], comm=comm,
+                     all_gather=None if os.environ.get("CSDR_BENCH_NCCL_ONLY") else ag)
     rng = np.random.default_rng(7)
     out = {"batch": B, "context": ctxlen, "steps": steps, "tp": world}
+    if world > 1:
+        out["partial_sums"] = "ncclAllReduce" if os.environ.get("CSDR_BENCH_NCCL_ONLY") or world > 8 else "peer memory (in-kernel)"
     with torch.cuda.stream(stream):
         if spec["prefill"]:
             prompt = rng.integers(0, cfg["vocab"], ctxlen)

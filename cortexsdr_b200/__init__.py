@@ -616,7 +616,12 @@ class Decoder:
     api/cortex_sdk.cpp:1543-1696, with a KV cache)."""
 
     def __init__(self, loader: SDRModelLoader, *, n_layers, hidden, q_heads, kv_heads, head_dim,
-                 inter, vocab, max_seq, max_batch=1, rms_eps=1e-5, rope_theta=1e6, comm: "NcclComm | None" = None):
+                 inter, vocab, max_seq, max_batch=1, rms_eps=1e-5, rope_theta=1e6, comm: "NcclComm | None" = None,
+                 all_gather=None):
+        """all_gather: a callable bytes -> list[bytes] (one entry per rank, rank order) supplied by
+        the host program, e.g. built on torch.distributed.all_gather_object. When given with a
+        communicator of 2 to 8 ranks, the ranks exchange CUDA IPC handles through it and sum their
+        partial projections through peer memory for steps of at most 16 tokens."""
         self.loader, self.ctx, self.comm = loader, loader.ctx, comm
         self.cfg = DecoderConfig(n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab,
                                  max_seq, max_batch, rms_eps, rope_theta, comm.rank if comm else 0,
@@ -626,6 +631,13 @@ class Decoder:
         self._h = h
         self._close_rank = 1
         self.ctx._adopt(self)
+        if comm is not None and all_gather is not None and 2 <= comm.world <= 8:
+            mine = C.create_string_buffer(64)
+            _check(self.ctx._lib.csdr_decoder_exchange_export(self._h, mine))
+            handles = all_gather(mine.raw)
+            if len(handles) != comm.world or any(len(b) != 64 for b in handles):
+                raise ValueError("all_gather must return one 64-byte handle per rank")
+            _check(self.ctx._lib.csdr_decoder_exchange_import(self._h, b"".join(handles), comm.world))
 
     def reset(self):
         _check(self.ctx._lib.csdr_decoder_reset(self._h))

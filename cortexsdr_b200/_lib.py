@@ -114,6 +114,8 @@ SIGNATURES = {
     "csdr_decoder_create": (C.c_int, [_P, C.POINTER(DecoderConfig), C.POINTER(_P)]),
     "csdr_decoder_destroy": (C.c_int, [_P]),
     "csdr_decoder_reset": (C.c_int, [_P]),
+    "csdr_decoder_exchange_export": (C.c_int, [_P, _P]),
+    "csdr_decoder_exchange_import": (C.c_int, [_P, _P, _SZ]),
     "csdr_decoder_seek": (C.c_int, [_P, C.c_uint32, C.c_uint32]),
     "csdr_decoder_forward": (C.c_int, [_P, C.c_uint32, C.POINTER(C.c_int32), _SZ, _F, _F]),
     "csdr_decoder_step": (C.c_int, [_P, C.POINTER(C.c_int32), _SZ, C.POINTER(C.c_int32), _F]),

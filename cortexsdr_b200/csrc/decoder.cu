@@ -100,11 +100,19 @@ struct csdr_decoder {
     // squares: [sum_pad floats][Dx of every member]; tensor-parallel ranks add theirs up in place
     DevPtr dxbuf;
     uint32_t sum_pad = 0;
+    // peer-memory exchange of partial projections between tensor-parallel ranks (steps of at
+    // most 16 tokens); until the host program has passed the peers' handles in, NCCL sums them
+    DevPtr xch_region;
+    Exchange xch;                  // ranks == 0 until imported
+    uint32_t xch_blk = 0;
+    std::vector<void*> xch_maps;   // peers' regions as mapped here (closed on destroy)
     // bf16 hi/lo planes of the three activation widths the projections consume (hidden,
     // attention output, SwiGLU product) for steps that run on the tensor cores
     DevPtr xp_h, xp_att, xp_act;
     bool planes_capable = false;
     ~csdr_decoder() {
+        for (void* m : xch_maps)
+            if (m) cudaIpcCloseMemHandle(m);
         auto drop = [](Linear& l) {
             if (l.shard) csdr_segment_destroy(l.shard);
         };
@@ -255,11 +263,18 @@ void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
     const XPlanesView xp{planes, planes + plane_elems};
     float* base = F(d->dxbuf);
     const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
+    TokenScale ts{};
+    if (normed) ts = TokenScale{sums, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
+    if (d->xch.ranks > 1u && w.tile_mt && d->sum_pad + w.floats <= d->xch_blk) {
+        // every rank pushes its block to every rank; the gather sums the slots while staging
+        if (normed) launch_push_partials(d->ctx, d->xch, base, 0u, d->sum_pad + w.floats);
+        else launch_push_partials(d->ctx, d->xch, w.base, d->sum_pad, w.floats);
+        launch_wide_gather_exchanged(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts, d->xch, base);
+        return;
+    }
     // the sums sit right in front of the projections: one collective covers both
     if (normed && sums == base) sum_over_ranks(d, base, d->sum_pad + w.floats);
     else sum_over_ranks(d, w.base, w.floats);
-    TokenScale ts{};
-    if (normed) ts = TokenScale{sums, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
     launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts);
 }
 
@@ -541,6 +556,19 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
                 CSDR_CUDA(cudaMemsetAsync(d->dxbuf->ptr, 0, d->dxbuf->bytes, ctx->stream));
             }
         }
+        if (d->P > 1 && d->P <= kMaxExchangeRanks) {
+            // exchange region: [2][P] slots of a decode-sized block, then flag words, then this
+            // rank's two counters; zeroed (sequence numbers start at 1)
+            uint32_t widest = 0;
+            auto atoms = [](const Linear& l) { return l.use() ? l.use()->g.n_atoms : 0u; };
+            for (const Layer& L : d->layers)
+                widest = std::max({widest, atoms(L.q) + atoms(L.k) + atoms(L.v), atoms(L.gate) + atoms(L.up), atoms(L.o),
+                                   atoms(L.down)});
+            d->xch_blk = d->sum_pad + widest * 16u;
+            const size_t slot_bytes = static_cast<size_t>(2) * d->P * d->xch_blk * 4;
+            d->xch_region = dev_alloc(ctx, slot_bytes + 1024);
+            CSDR_CUDA(cudaMemsetAsync(d->xch_region->ptr, 0, d->xch_region->bytes, ctx->stream));
+        }
         if (d->P > 1) {
             d->normed_l = dev_alloc(ctx, T * d->H_l * 4);
             d->logits_l = dev_alloc(ctx, static_cast<size_t>(c.max_batch) * d->V_l * 4);
@@ -551,6 +579,49 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         CSDR_CUDA(cudaMemsetAsync(d->pos_dev->ptr, 0, d->pos_dev->bytes, ctx->stream));
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
         *out = d.release();
+    });
+}
+
+int csdr_decoder_exchange_export(csdr_decoder* d, void* handle64) {
+    return guard([&] {
+        need(d);
+        if (!handle64) throw Error(CSDR_ERR_INVALID_ARG, "handle buffer is null");
+        if (!d->xch_region) throw Error(CSDR_ERR_UNSUPPORTED, "this decoder has no exchange region (one rank, or more than 8)");
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+        cudaIpcMemHandle_t h;
+        CSDR_CUDA(cudaIpcGetMemHandle(&h, d->xch_region->ptr));
+        std::memcpy(handle64, &h, 64);
+    });
+}
+
+int csdr_decoder_exchange_import(csdr_decoder* d, const void* handles, size_t n_ranks) {
+    return guard([&] {
+        need(d);
+        if (!handles || n_ranks != d->P) throw Error(CSDR_ERR_INVALID_ARG, "one 64-byte handle per rank, rank-major");
+        if (!d->xch_region) throw Error(CSDR_ERR_UNSUPPORTED, "this decoder has no exchange region (one rank, or more than 8)");
+        if (d->xch.ranks) throw Error(CSDR_ERR_INVALID_ARG, "exchange handles were imported already");
+        const size_t slot_bytes = static_cast<size_t>(2) * d->P * d->xch_blk * 4;
+        Exchange x{};
+        d->xch_maps.assign(d->P, nullptr);
+        for (uint32_t r = 0; r < d->P; ++r) {
+            void* base = d->xch_region->ptr;
+            if (r != d->rank) {
+                cudaIpcMemHandle_t h;
+                std::memcpy(&h, static_cast<const unsigned char*>(handles) + 64u * r, 64);
+                CSDR_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+                d->xch_maps[r] = base;
+            }
+            x.slots[r] = static_cast<float*>(base);
+            x.flags[r] = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(base) + slot_bytes);
+        }
+        unsigned char* mine = static_cast<unsigned char*>(d->xch_region->ptr) + slot_bytes;
+        x.seq = reinterpret_cast<uint32_t*>(mine + 512);
+        x.done = reinterpret_cast<uint32_t*>(mine + 768);
+        x.rank = d->rank;
+        x.blk_floats = d->xch_blk;
+        x.status = d->ctx->status_word;
+        x.ranks = d->P;
+        d->xch = x;
     });
 }
 

@@ -540,12 +540,66 @@ struct GatherMember {
     uint32_t cta_begin, rows_per_cta;
 };
 
+// What the gather needs of an exchange: this rank's own slots and flags.
+struct GatherExchange {
+    const float* slots;       // [2][ranks][blk_floats]
+    const uint32_t* flags;    // [2][ranks]
+    const uint32_t* seq;
+    uint32_t ranks, blk_floats;
+    uint32_t dx_off[kGatherGroupMax];   // offset of each member's Dx inside a block
+    int* status;
+};
+
 struct GatherGroupParams {
     GatherMember m[kGatherGroupMax];
     uint32_t n_seg, M, m_total, code_cap16;
     int y_layout;
     TokenScale ts;
+    GatherExchange xch;       // ranks <= 1: Dx is read from m[i].dx
 };
+
+constexpr uint32_t kExchangeSpin = 8000000u;   // polls of a flag word before giving up (several seconds)
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct PushParams {
+    const float* src;
+    uint32_t off_floats, count4;
+    uint32_t ranks, rank, blk_floats;
+    float* slots[kMaxExchangeRanks];
+    uint32_t* flags[kMaxExchangeRanks];
+    uint32_t* seq;
+    uint32_t* done;
+};
+
+// grid (chunks, ranks): CTA (c, p) copies chunk c of the block into rank p's slot for this rank.
+__global__ void __launch_bounds__(256) push_partials_kernel(const __grid_constant__ PushParams p) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;   // advanced by the last CTA below
+    const uint32_t par = seq & 1u;
+    const uint32_t peer = blockIdx.y;
+    float4* dst = reinterpret_cast<float4*>(p.slots[peer] + (static_cast<size_t>(par) * p.ranks + p.rank) * p.blk_floats +
+                                            p.off_floats);
+    const float4* src = reinterpret_cast<const float4*>(p.src);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < p.count4; i += gridDim.x * blockDim.x) dst[i] = __ldcg(src + i);
+    __threadfence_system();           // this thread's peer stores are visible system-wide ...
+    __syncthreads();                  // ... for every thread of the CTA, before the CTA is counted
+    if (threadIdx.x == 0) {
+        const uint32_t prev = atomicAdd(p.done, 1u);
+        if (prev == gridDim.x * gridDim.y - 1u) {
+            *p.done = 0u;
+            __threadfence_system();
+            for (uint32_t r = 0; r < p.ranks; ++r)
+                *reinterpret_cast<volatile uint32_t*>(p.flags[r] + par * p.ranks + p.rank) = seq;
+            *reinterpret_cast<volatile uint32_t*>(p.seq) = seq;
+        }
+    }
+}
 
 template <int MT>
 __global__ void __launch_bounds__(kGroupThreads)
@@ -581,14 +635,64 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
         for (uint32_t i = tid; i < m.S; i += kGroupThreads) sc[i] = m.scales[i];
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (active) {
-        const uint32_t n4 = (m.K * MT) >> 2;
-        for (uint32_t i = tid; i < n4; i += kGroupThreads)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                             static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
-                         "l"(m.dx + static_cast<size_t>(i) * 4u)
-                         : "memory");
-        for (uint32_t i = (n4 << 2) + tid; i < m.K * MT; i += kGroupThreads) dxs[i] = m.dx[i];
+    __shared__ float inv_rms_s[16];
+    __shared__ int late_s;
+    if (g.xch.ranks > 1u) {
+        // ---- partial projections of all ranks arrive through peer memory ----
+        const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(g.xch.seq);   // the push before this kernel set it
+        const uint32_t par = seq & 1u;
+        if (tid == 0) late_s = 0;
+        __syncthreads();
+        if (tid < g.xch.ranks) {
+            const uint32_t* f = g.xch.flags + par * g.xch.ranks + tid;
+            uint32_t spins = 0;
+            while (ld_acquire_sys(f) != seq) {
+                if (++spins > kExchangeSpin) {   // gave up: the host will see it
+                    late_s = 1;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        const float* slot0 = g.xch.slots + static_cast<size_t>(par) * g.xch.ranks * g.xch.blk_floats;
+        if (active) {
+            const uint32_t n4 = (m.K * MT) >> 2;
+            const float* mine = slot0 + g.xch.dx_off[mi];
+            for (uint32_t i = tid; i < n4; i += kGroupThreads) {
+                float4 v[kMaxExchangeRanks];               // all ranks' pieces in flight, then the adds
+#pragma unroll
+                for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)
+                    if (r < g.xch.ranks)
+                        v[r] = __ldcg(reinterpret_cast<const float4*>(mine + static_cast<size_t>(r) * g.xch.blk_floats) + i);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)   // rank order: every rank gets the same sum
+                    if (r < g.xch.ranks) {
+                        acc.x += v[r].x;
+                        acc.y += v[r].y;
+                        acc.z += v[r].z;
+                        acc.w += v[r].w;
+                    }
+                reinterpret_cast<float4*>(dxs)[i] = acc;
+            }
+        }
+        if (g.ts.sumsq && tid < MT) {
+            float t = 0.0f;
+            for (uint32_t r = 0; r < g.xch.ranks; ++r) t += __ldcg(slot0 + static_cast<size_t>(r) * g.xch.blk_floats + tid);
+            inv_rms_s[tid] = rsqrtf(t * g.ts.inv_width + g.ts.eps);
+        }
+        if (tid == 0 && late_s && blockIdx.x == 0) atomicExch(g.xch.status, 1);
+    } else {
+        if (active) {
+            const uint32_t n4 = (m.K * MT) >> 2;
+            for (uint32_t i = tid; i < n4; i += kGroupThreads)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                                 static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
+                             "l"(m.dx + static_cast<size_t>(i) * 4u)
+                             : "memory");
+            for (uint32_t i = (n4 << 2) + tid; i < m.K * MT; i += kGroupThreads) dxs[i] = m.dx[i];
+        }
+        if (g.ts.sumsq && tid < MT) inv_rms_s[tid] = rsqrtf(g.ts.sumsq[tid < g.M ? tid : 0] * g.ts.inv_width + g.ts.eps);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -613,7 +717,7 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
             const uint32_t r = row0 + rl;
             const size_t o = g.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * g.m_total + b
                                                                       : static_cast<size_t>(b) * m.R + r;
-            if (g.ts.sumsq) acc *= rsqrtf(g.ts.sumsq[b] * g.ts.inv_width + g.ts.eps);
+            if (g.ts.sumsq) acc *= inv_rms_s[b];
             if (m.bias) acc += m.bias[r];
             if (m.residual) acc += m.residual[o];
             m.y[o] = acc;
@@ -654,6 +758,42 @@ void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t tot
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, g));
     ls.done("hsdr_gather_group_kernel");
 }
+
+}  // namespace
+
+void launch_push_partials(csdr_context* ctx, const Exchange& x, const float* src, uint32_t off_floats, size_t floats) {
+    if (x.ranks < 2u) return;
+    if ((off_floats & 3u) || (floats & 3u) || off_floats + floats > x.blk_floats)
+        throw Error(CSDR_ERR_INVALID_ARG, "exchange: block range must be whole float4s inside a slot");
+    PushParams p{};
+    p.src = src;
+    p.off_floats = off_floats;
+    p.count4 = static_cast<uint32_t>(floats / 4u);
+    p.ranks = x.ranks;
+    p.rank = x.rank;
+    p.blk_floats = x.blk_floats;
+    for (uint32_t r = 0; r < x.ranks; ++r) {
+        p.slots[r] = x.slots[r];
+        p.flags[r] = x.flags[r];
+    }
+    p.seq = x.seq;
+    p.done = x.done;
+    const uint32_t chunks = std::max(1u, std::min(8u, (p.count4 + 1023u) / 1024u));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(chunks, x.ranks, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, push_partials_kernel, p));
+    ls.done("push_partials_kernel");
+}
+
+namespace {
 
 void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float* dx, uint32_t M, const YView& yv,
                         const float* residual, const TokenScale& ts) {
@@ -723,37 +863,60 @@ WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, u
     return w;
 }
 
+namespace {
+void gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
+                       const WideOut* outs, int y_layout, const TokenScale& ts, const Exchange* x, const float* blk_base) {
+    GatherGroupParams g{};
+    g.n_seg = n;
+    g.M = M;
+    g.m_total = M;
+    g.y_layout = y_layout;
+    g.ts = ts;
+    if (x && x->ranks > 1u) {
+        g.xch.slots = x->slots[x->rank];
+        g.xch.flags = x->flags[x->rank];
+        g.xch.seq = x->seq;
+        g.xch.ranks = x->ranks;
+        g.xch.blk_floats = x->blk_floats;
+        g.xch.status = x->status;
+        for (uint32_t i = 0; i < n; ++i) g.xch.dx_off[i] = static_cast<uint32_t>(w.dx[i] - blk_base);
+    }
+    uint32_t total_rows = 0, max_k = 0, max_slots = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        const Geometry& sg = segs[i]->g;
+        g.m[i] = GatherMember{segs[i]->codes_ptr(), static_cast<const float*>(segs[i]->scales->ptr), w.dx[i], outs[i].y,
+                              outs[i].bias, outs[i].residual, sg.rows, sg.n_stages, sg.k, sg.n_atoms, 0u, 0u};
+        total_rows += sg.rows;
+        max_k = std::max(max_k, sg.n_atoms);
+        max_slots = std::max(max_slots, sg.slots());
+    }
+    switch (w.tile_mt) {
+        case 1: launch_gather_group_t<1>(ctx, g, total_rows, max_k, max_slots); break;
+        case 2: launch_gather_group_t<2>(ctx, g, total_rows, max_k, max_slots); break;
+        case 4: launch_gather_group_t<4>(ctx, g, total_rows, max_k, max_slots); break;
+        case 8: launch_gather_group_t<8>(ctx, g, total_rows, max_k, max_slots); break;
+        default: launch_gather_group_t<16>(ctx, g, total_rows, max_k, max_slots); break;
+    }
+}
+}  // namespace
+
 void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
                         const WideOut* outs, int y_layout, const TokenScale& ts) {
     if (w.tile_mt) {
-        GatherGroupParams g{};
-        g.n_seg = n;
-        g.M = M;
-        g.m_total = M;
-        g.y_layout = y_layout;
-        g.ts = ts;
-        uint32_t total_rows = 0, max_k = 0, max_slots = 0;
-        for (uint32_t i = 0; i < n; ++i) {
-            const Geometry& sg = segs[i]->g;
-            g.m[i] = GatherMember{segs[i]->codes_ptr(), static_cast<const float*>(segs[i]->scales->ptr), w.dx[i], outs[i].y,
-                                  outs[i].bias, outs[i].residual, sg.rows, sg.n_stages, sg.k, sg.n_atoms, 0u, 0u};
-            total_rows += sg.rows;
-            max_k = std::max(max_k, sg.n_atoms);
-            max_slots = std::max(max_slots, sg.slots());
-        }
-        switch (w.tile_mt) {
-            case 1: launch_gather_group_t<1>(ctx, g, total_rows, max_k, max_slots); break;
-            case 2: launch_gather_group_t<2>(ctx, g, total_rows, max_k, max_slots); break;
-            case 4: launch_gather_group_t<4>(ctx, g, total_rows, max_k, max_slots); break;
-            case 8: launch_gather_group_t<8>(ctx, g, total_rows, max_k, max_slots); break;
-            default: launch_gather_group_t<16>(ctx, g, total_rows, max_k, max_slots); break;
-        }
+        gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts, nullptr, nullptr);
         return;
     }
     for (uint32_t i = 0; i < n; ++i) {
         YView yv{outs[i].y, y_layout, segs[i]->g.rows, M, 0u, M, outs[i].bias};
         launch_gather_wide(ctx, segs[i], w.dx[i], M, yv, outs[i].residual, ts);
     }
+}
+
+void launch_wide_gather_exchanged(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w,
+                                  uint32_t M, const WideOut* outs, int y_layout, const TokenScale& ts,
+                                  const Exchange& x, const float* blk_base) {
+    if (!w.tile_mt) throw Error(CSDR_ERR_LIMIT, "the peer-memory exchange carries single token tiles (at most 16 tokens)");
+    gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts, &x, blk_base);
 }
 
 void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,

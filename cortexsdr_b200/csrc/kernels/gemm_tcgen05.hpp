@@ -65,11 +65,41 @@ struct WideDx {
     size_t floats;
     uint32_t stride, tile_mt;
 };
+// Exchange of partial projections between tensor-parallel ranks through peer memory (one
+// process per GPU, regions mapped into each other with CUDA IPC). Every rank owns a region of
+// 2 (parity) x ranks slots of `blk_floats` floats plus 2 x ranks flag words. A rank pushes its
+// block into slot [parity][its rank] of EVERY rank's region (plain peer stores), then stores the
+// exchange's sequence number into the matching flag word of every region. The gather on each
+// rank waits (bounded) for all flags of the parity to show the number and sums the slots in rank
+// order while it stages Dx. Two parities: a rank can run at most one exchange ahead of a peer,
+// because its next gather needs that peer's next push. The sequence number lives in device
+// memory and is advanced by the push kernel, so a captured CUDA graph replays correctly.
+constexpr uint32_t kMaxExchangeRanks = 8;
+struct Exchange {
+    uint32_t ranks = 0;            // 0 or 1: no exchange
+    uint32_t rank = 0;
+    uint32_t blk_floats = 0;
+    float* slots[kMaxExchangeRanks] = {};       // every rank's slot area (index = owner), [2][ranks][blk_floats]
+    uint32_t* flags[kMaxExchangeRanks] = {};    // every rank's flag words, [2][ranks]
+    uint32_t* seq = nullptr;       // this rank's sequence counter (device)
+    uint32_t* done = nullptr;      // this rank's CTA-completion counter of the push kernel (device)
+    int* status = nullptr;         // context status word: a wait that ran out is recorded here
+};
+// Push `floats` floats starting `off_floats` into this rank's projection block (at local address
+// `src`) to every rank, then raise the flags.
+void launch_push_partials(csdr_context* ctx, const Exchange& x, const float* src, uint32_t off_floats, size_t floats);
+
 // The two halves of launch_matmul_wide_group. dx_base == nullptr: context scratch.
 WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x, uint32_t M,
                            float* dx_base);
 void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
                         const WideOut* outs, int y_layout, const TokenScale& ts);
+// Gather of a single token tile (M <= 16) whose projections (and sums of squares, when ts.sumsq
+// is set: then they sit at the start of the block) arrive through the exchange: `blk_base` is the
+// local address that corresponds to offset 0 of a block.
+void launch_wide_gather_exchanged(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w,
+                                  uint32_t M, const WideOut* outs, int y_layout, const TokenScale& ts,
+                                  const Exchange& x, const float* blk_base);
 bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, size_t batch);
 void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
                               uint32_t M, const WideOut* outs, int y_layout);

@@ -315,6 +315,14 @@ CSDR_API int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cf
                                  csdr_decoder** out);
 CSDR_API int csdr_decoder_destroy(csdr_decoder* d);
 CSDR_API int csdr_decoder_reset(csdr_decoder* d);
+/* Tensor-parallel ranks (2 to 8, one process per GPU) can sum their partial projections through
+ * peer memory instead of NCCL for steps of at most 16 tokens: every rank exports a 64-byte CUDA
+ * IPC handle of its exchange region, the host program gathers the handles of all ranks
+ * (rank-major) and every rank imports them. All ranks must do so, or none (no counterpart in
+ * the reference). Waits on peers are bounded; one that runs out surfaces as CSDR_ERR_TIMEOUT
+ * from csdr_context_synchronize. */
+CSDR_API int csdr_decoder_exchange_export(csdr_decoder* d, void* handle64);
+CSDR_API int csdr_decoder_exchange_import(csdr_decoder* d, const void* handles, size_t n_ranks);
 /* Set sequence `seq` to `position` without computing anything: the cache rows below it
  * keep whatever they hold (zeros after creation). For throughput measurements at a given
  * context length. */

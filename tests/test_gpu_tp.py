@@ -28,16 +28,32 @@ def _rank(rank, world, port, path, q):
         dist.broadcast_object_list(ids, src=0)
         comm = cs.NcclComm(ctx, ids[0], rank, world)
         ld = cs.SDRModelLoader(path, ctx)
-        dec = cs.Decoder(ld, **CFG, max_seq=64, max_batch=2, rms_eps=1e-6, comm=comm)
+        def all_gather(b):
+            out = [None] * world
+            dist.all_gather_object(out, b)
+            return out
+
+        out = {}
         tokens = np.random.default_rng(0).integers(0, CFG["vocab"], 12)
-        logits, hidden = dec.forward(tokens, want_hidden=True)
-        nxt, step_logits = dec.step([int(logits.argmax())], want_logits=True)
-        out = dict(logits=logits, hidden=hidden, step=step_logits[0], nxt=int(nxt[0]))
+        long_tokens = np.random.default_rng(1).integers(0, CFG["vocab"], 21)
+        # "nccl": partial projections summed by ncclAllReduce; "peer": pushed into peer memory and
+        # summed by the gather (steps of at most 16 tokens; the 21-token pass still takes NCCL)
+        for tag, kw in (("nccl", {}), ("peer", dict(all_gather=all_gather))):
+            dec = cs.Decoder(ld, **CFG, max_seq=64, max_batch=2, rms_eps=1e-6, comm=comm, **kw)
+            logits, hidden = dec.forward(tokens, want_hidden=True)
+            nxt, step_logits = dec.step([int(logits.argmax())], want_logits=True)
+            dec.reset()
+            wide_logits, _ = dec.forward(long_tokens)
+            ctx.synchronize()
+            out[tag] = dict(logits=logits, hidden=hidden, step=step_logits[0], nxt=int(nxt[0]), wide=wide_logits)
+            dec.close()
         if rank == 0:
             single = cs.Decoder(ld, **CFG, max_seq=64, max_batch=2, rms_eps=1e-6)
             l1, h1 = single.forward(tokens, want_hidden=True)
             n1, s1 = single.step([int(l1.argmax())], want_logits=True)
-            out.update(l1=l1, h1=h1, s1=s1[0], n1=int(n1[0]))
+            single.reset()
+            w1, _ = single.forward(long_tokens)
+            out["single"] = dict(logits=l1, hidden=h1, step=s1[0], nxt=int(n1[0]), wide=w1)
         dist.barrier()
         comm.close()
         q.put((rank, out))
@@ -64,7 +80,12 @@ def test_two_rank_decoder_matches_single_gpu(tmp_path):
         p.join(timeout=60)
         assert p.exitcode == 0
     r0, r1 = res[0], res[1]
-    assert np.abs(r0["logits"] - r0["l1"]).max() < 1e-3
-    assert np.abs(r0["hidden"] - r0["h1"]).max() < 1e-3
-    assert np.abs(r0["step"] - r0["s1"]).max() < 1e-3 and r0["nxt"] == r0["n1"]
-    assert np.array_equal(r0["logits"], r1["logits"])      # replicated result on every rank
+    one = r0["single"]
+    for tag in ("nccl", "peer"):
+        got = r0[tag]
+        assert np.abs(got["logits"] - one["logits"]).max() < 1e-3, tag
+        assert np.abs(got["hidden"] - one["hidden"]).max() < 1e-3, tag
+        assert np.abs(got["step"] - one["step"]).max() < 1e-3 and got["nxt"] == one["nxt"], tag
+        assert np.abs(got["wide"] - one["wide"]).max() < 1e-3, tag
+        assert np.array_equal(got["logits"], r1[tag]["logits"]), tag      # same result on every rank
+        assert np.array_equal(got["step"], r1[tag]["step"]), tag
