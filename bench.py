@@ -139,6 +139,9 @@ DECODERS = {
 }
 
 
+FUSED_GEMV_DRAM_BYTES_NCU = 8996000   # per launch, cfg2 shape, batch 1 (8.996 MB read, 0 written)
+
+
 def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True):
     """Decode tokens/s of a decoder-shaped synthetic archive (every linear an HSDR row-tile segment
     with its own dictionary, K=512 3x8; random-init stand-in for the config's weights)."""
@@ -377,7 +380,10 @@ def main():
         achieved = bytes1 / (us_launch * 1e-6) / 1e9
         n_f, ms_f = prof["hsdr_gemv_fused"]
         roofline = {"bound": "hbm", "kernel": "hsdr_gemv_fused_kernel", "achieved": achieved, "peak": hbm_peak,
-                    "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
+                    "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
+                    # workload, from the ncu capture summarised in profiles/gemv_fused_cfg2_m1.md
+                    "traffic": FUSED_GEMV_DRAM_BYTES_NCU if (R, C) == (11008, 4096) else None,
                     "alg_bytes_per_launch": bytes1, "us_per_launch": us_launch,
                     "us_per_launch_isolated": ms_f / max(n_f, 1) * 1e3,
                     "note": "us_per_launch = timed region / launches (launches overlap); isolated = one "

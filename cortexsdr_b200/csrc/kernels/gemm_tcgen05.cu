@@ -327,7 +327,7 @@ constexpr uint32_t kWideThreads = 512;
 constexpr uint32_t kWideHalfWarps = kWideThreads / 16u;
 constexpr uint32_t kWideRows = 8;        // rows per block of a half-warp
 constexpr uint32_t kWideMaxSlots = 64;   // S*k the code parking area is sized for
-constexpr uint32_t kWideCodeWords = (kWideRows * kWideMaxSlots + 2u) / 2u;   // per half-warp, u32
+constexpr uint32_t kWideCodeWords = ((kWideRows * kWideMaxSlots + 2u) / 2u + 1u) & ~1u;   // per half-warp, u32; even: 64-bit code reads
 constexpr uint32_t kWideWordsPerLane = (kWideCodeWords + 15u) / 16u;
 
 inline size_t gather_wide_smem(uint32_t K) {
@@ -416,43 +416,51 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
         const uint32_t off =
             static_cast<uint32_t>(reinterpret_cast<uintptr_t>(codes + static_cast<size_t>(r0) * slots) >> 1) & 1u;
         const uint16_t* crow = reinterpret_cast<const uint16_t*>(my_csm) + off;
-        // Four rows advance together: their lookups are independent, which keeps enough
-        // shared-memory reads in flight per warp. Rows past the end of the run read codes that
-        // are real (an earlier block's) or zero, so their lookups stay inside the slice; their
-        // results are never stored.
+        // All eight rows of the block advance together: their lookups are independent, which
+        // keeps enough shared-memory reads in flight per warp, and the accumulators are the
+        // block's results. Rows past the end of the run read codes that are real (an earlier
+        // block's) or zero, so their lookups stay inside the slice; their results are never
+        // stored. Codes come four slots at a time (one 64-bit read per row) when the stream's
+        // layout allows it.
         float out[kWideRows][4];
 #pragma unroll
-        for (uint32_t rq = 0; rq < kWideRows; rq += 4u) {
-            float4 acc[4];
-#pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            const uint16_t* cr = crow + rq * slots;
+        for (uint32_t i = 0; i < kWideRows; ++i) out[i][0] = out[i][1] = out[i][2] = out[i][3] = 0.0f;
+        auto step = [&](uint32_t i, uint32_t code, uint32_t gbits) {
+            const float4 v = dxs4[(code & 0x7FFFu) * (kWideTokens / 4u)];
+            const float scale = __uint_as_float(gbits ^ ((code & 0x8000u) << 16));
+            out[i][0] = fmaf(scale, v.x, out[i][0]);
+            out[i][1] = fmaf(scale, v.y, out[i][1]);
+            out[i][2] = fmaf(scale, v.z, out[i][2]);
+            out[i][3] = fmaf(scale, v.w, out[i][3]);
+        };
+        if (off == 0u && (k & 3u) == 0u) {
             for (uint32_t st = 0; st < S; ++st) {
                 const uint32_t gbits = __float_as_uint(gs[st]);
-#pragma unroll 2
-                for (uint32_t j = 0; j < k; ++j) {
-                    uint32_t code[4];
+                for (uint32_t j0 = 0; j0 < k; j0 += 4u) {
+                    uint2 c4[kWideRows];     // rows are slots*2 bytes apart, slots a multiple of four here
 #pragma unroll
-                    for (uint32_t i = 0; i < 4u; ++i) code[i] = cr[i * slots + st * k + j];
-                    float4 v[4];
+                    for (uint32_t i = 0; i < kWideRows; ++i)
+                        c4[i] = *reinterpret_cast<const uint2*>(crow + i * slots + st * k + j0);
 #pragma unroll
-                    for (uint32_t i = 0; i < 4u; ++i) v[i] = dxs4[(code[i] & 0x7FFFu) * (kWideTokens / 4u)];
+                    for (uint32_t i = 0; i < kWideRows; ++i) step(i, c4[i].x & 0xFFFFu, gbits);
 #pragma unroll
-                    for (uint32_t i = 0; i < 4u; ++i) {
-                        const float scale = __uint_as_float(gbits ^ ((code[i] & 0x8000u) << 16));
-                        acc[i].x = fmaf(scale, v[i].x, acc[i].x);
-                        acc[i].y = fmaf(scale, v[i].y, acc[i].y);
-                        acc[i].z = fmaf(scale, v[i].z, acc[i].z);
-                        acc[i].w = fmaf(scale, v[i].w, acc[i].w);
-                    }
+                    for (uint32_t i = 0; i < kWideRows; ++i) step(i, c4[i].x >> 16, gbits);
+#pragma unroll
+                    for (uint32_t i = 0; i < kWideRows; ++i) step(i, c4[i].y & 0xFFFFu, gbits);
+#pragma unroll
+                    for (uint32_t i = 0; i < kWideRows; ++i) step(i, c4[i].y >> 16, gbits);
                 }
             }
+        } else {
+            for (uint32_t st = 0; st < S; ++st) {
+                const uint32_t gbits = __float_as_uint(gs[st]);
+                for (uint32_t j = 0; j < k; ++j) {
+                    uint32_t code[kWideRows];
 #pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) {
-                out[rq + i][0] = acc[i].x;
-                out[rq + i][1] = acc[i].y;
-                out[rq + i][2] = acc[i].z;
-                out[rq + i][3] = acc[i].w;
+                    for (uint32_t i = 0; i < kWideRows; ++i) code[i] = crow[i * slots + st * k + j];
+#pragma unroll
+                    for (uint32_t i = 0; i < kWideRows; ++i) step(i, code[i], gbits);
+                }
             }
         }
         const uint32_t tl = 4u * l16;               // first token of this lane inside the slice
