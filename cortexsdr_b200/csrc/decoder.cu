@@ -262,16 +262,19 @@ void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
     }
     const XPlanesView xp{planes, planes + plane_elems};
     float* base = F(d->dxbuf);
-    const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
     TokenScale ts{};
     if (normed) ts = TokenScale{sums, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
-    if (d->xch.ranks > 1u && w.tile_mt && d->sum_pad + w.floats <= d->xch_blk) {
-        // every rank pushes its block to every rank; the gather sums the slots while staging
-        if (normed) launch_push_partials(d->ctx, d->xch, base, 0u, d->sum_pad + w.floats);
-        else launch_push_partials(d->ctx, d->xch, w.base, d->sum_pad, w.floats);
+    uint32_t total_atoms = 0;
+    for (uint32_t i = 0; i < n; ++i) total_atoms += segs[i]->g.n_atoms;
+    if (d->xch.ranks > 1u && T <= 16u && d->sum_pad + static_cast<size_t>(total_atoms) * 16u <= d->xch_blk) {
+        // the projection kernel stores its finished rows (and this rank's sums of squares) into
+        // every rank's exchange slot and raises the flags; the gather sums the slots while staging
+        const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, &d->xch, base,
+                                             normed ? sums : nullptr);
         launch_wide_gather_exchanged(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts, d->xch, base);
         return;
     }
+    const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
     // the sums sit right in front of the projections: one collective covers both
     if (normed && sums == base) sum_over_ranks(d, base, d->sum_pad + w.floats);
     else sum_over_ranks(d, w.base, w.floats);

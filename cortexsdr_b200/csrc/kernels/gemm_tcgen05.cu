@@ -574,41 +574,6 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
-struct PushParams {
-    const float* src;
-    uint32_t off_floats, count4;
-    uint32_t ranks, rank, blk_floats;
-    float* slots[kMaxExchangeRanks];
-    uint32_t* flags[kMaxExchangeRanks];
-    uint32_t* seq;
-    uint32_t* done;
-};
-
-// grid (chunks, ranks): CTA (c, p) copies chunk c of the block into rank p's slot for this rank.
-__global__ void __launch_bounds__(256) push_partials_kernel(const __grid_constant__ PushParams p) {
-    asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;   // advanced by the last CTA below
-    const uint32_t par = seq & 1u;
-    const uint32_t peer = blockIdx.y;
-    float4* dst = reinterpret_cast<float4*>(p.slots[peer] + (static_cast<size_t>(par) * p.ranks + p.rank) * p.blk_floats +
-                                            p.off_floats);
-    const float4* src = reinterpret_cast<const float4*>(p.src);
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < p.count4; i += gridDim.x * blockDim.x) dst[i] = __ldcg(src + i);
-    __threadfence_system();           // this thread's peer stores are visible system-wide ...
-    __syncthreads();                  // ... for every thread of the CTA, before the CTA is counted
-    if (threadIdx.x == 0) {
-        const uint32_t prev = atomicAdd(p.done, 1u);
-        if (prev == gridDim.x * gridDim.y - 1u) {
-            *p.done = 0u;
-            __threadfence_system();
-            for (uint32_t r = 0; r < p.ranks; ++r)
-                *reinterpret_cast<volatile uint32_t*>(p.flags[r] + par * p.ranks + p.rank) = seq;
-            *reinterpret_cast<volatile uint32_t*>(p.seq) = seq;
-        }
-    }
-}
-
 template <int MT>
 __global__ void __launch_bounds__(kGroupThreads)
 hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
@@ -767,42 +732,6 @@ void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t tot
     ls.done("hsdr_gather_group_kernel");
 }
 
-}  // namespace
-
-void launch_push_partials(csdr_context* ctx, const Exchange& x, const float* src, uint32_t off_floats, size_t floats) {
-    if (x.ranks < 2u) return;
-    if ((off_floats & 3u) || (floats & 3u) || off_floats + floats > x.blk_floats)
-        throw Error(CSDR_ERR_INVALID_ARG, "exchange: block range must be whole float4s inside a slot");
-    PushParams p{};
-    p.src = src;
-    p.off_floats = off_floats;
-    p.count4 = static_cast<uint32_t>(floats / 4u);
-    p.ranks = x.ranks;
-    p.rank = x.rank;
-    p.blk_floats = x.blk_floats;
-    for (uint32_t r = 0; r < x.ranks; ++r) {
-        p.slots[r] = x.slots[r];
-        p.flags[r] = x.flags[r];
-    }
-    p.seq = x.seq;
-    p.done = x.done;
-    const uint32_t chunks = std::max(1u, std::min(8u, (p.count4 + 1023u) / 1024u));
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(chunks, x.ranks, 1);
-    cfg.blockDim = dim3(256, 1, 1);
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    LaunchScope ls(ctx, KC_DECODER_OP);
-    CSDR_CUDA(cudaLaunchKernelEx(&cfg, push_partials_kernel, p));
-    ls.done("push_partials_kernel");
-}
-
-namespace {
-
 void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float* dx, uint32_t M, const YView& yv,
                         const float* residual, const TokenScale& ts) {
     const Geometry& g = seg->g;
@@ -849,7 +778,7 @@ bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* se
 }
 
 WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x, uint32_t M,
-                           float* dx_base) {
+                           float* dx_base, const Exchange* xch, const float* blk_base, const float* sums) {
     if (n == 0 || n > kGatherGroupMax) throw Error(CSDR_ERR_LIMIT, "matmul group holds 1 to 4 segments");
     WideDx w{};
     if (M <= 16u) {
@@ -867,7 +796,7 @@ WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, u
         w.dx[i] = w.base + off;
         off += static_cast<size_t>(segs[i]->g.n_atoms) * w.stride;
     }
-    launch_dx_tma_group(ctx, segs, n, x, M, w.dx, w.stride);
+    launch_dx_tma_group(ctx, segs, n, x, M, w.dx, w.stride, xch, blk_base, sums);
     return w;
 }
 

@@ -36,9 +36,15 @@ struct XPlanesView {
 // Planes of a caller's activation matrix: the matrix itself when it is bf16, token-major and
 // 16-byte aligned, else a conversion into context scratch (valid until the next conversion).
 XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_layout, uint32_t M, uint32_t cols);
+struct Exchange;
 // One projection launch for up to four dictionaries over the same activations (q|k|v, gate|up).
+// With an exchange (tensor parallelism, at most 16 tokens) the finished rows go into every
+// rank's slot for this rank, at the offsets dx[i] - blk_base, `sums` (this rank's per-token sums
+// of squares, or null) ride along at offset 0, and the launch's last CTA raises the flags: the
+// projection and its share of the collective are one kernel.
 void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
-                         float* const* dx, uint32_t dx_stride);
+                         float* const* dx, uint32_t dx_stride, const Exchange* xch, const float* blk_base,
+                         const float* sums);
 
 // Up to four row-tile segments over the same activation planes: one projection launch and, for
 // a single token tile (M <= 16), one gather launch for the whole group. y = W x (+ bias)
@@ -67,13 +73,14 @@ struct WideDx {
 };
 // Exchange of partial projections between tensor-parallel ranks through peer memory (one
 // process per GPU, regions mapped into each other with CUDA IPC). Every rank owns a region of
-// 2 (parity) x ranks slots of `blk_floats` floats plus 2 x ranks flag words. A rank pushes its
-// block into slot [parity][its rank] of EVERY rank's region (plain peer stores), then stores the
-// exchange's sequence number into the matching flag word of every region. The gather on each
+// 2 (parity) x ranks slots of `blk_floats` floats plus 2 x ranks flag words. A rank's projection
+// kernel stores its finished rows into slot [parity][its rank] of EVERY rank's region (plain peer
+// stores), and its last CTA stores the exchange's sequence number into the matching flag word of
+// every region. The gather on each
 // rank waits (bounded) for all flags of the parity to show the number and sums the slots in rank
 // order while it stages Dx. Two parities: a rank can run at most one exchange ahead of a peer,
 // because its next gather needs that peer's next push. The sequence number lives in device
-// memory and is advanced by the push kernel, so a captured CUDA graph replays correctly.
+// memory and is advanced by the projection kernel, so a captured CUDA graph replays correctly.
 constexpr uint32_t kMaxExchangeRanks = 8;
 struct Exchange {
     uint32_t ranks = 0;            // 0 or 1: no exchange
@@ -82,16 +89,13 @@ struct Exchange {
     float* slots[kMaxExchangeRanks] = {};       // every rank's slot area (index = owner), [2][ranks][blk_floats]
     uint32_t* flags[kMaxExchangeRanks] = {};    // every rank's flag words, [2][ranks]
     uint32_t* seq = nullptr;       // this rank's sequence counter (device)
-    uint32_t* done = nullptr;      // this rank's CTA-completion counter of the push kernel (device)
+    uint32_t* done = nullptr;      // this rank's count of finished CTAs of the projection kernel (device)
     int* status = nullptr;         // context status word: a wait that ran out is recorded here
 };
-// Push `floats` floats starting `off_floats` into this rank's projection block (at local address
-// `src`) to every rank, then raise the flags.
-void launch_push_partials(csdr_context* ctx, const Exchange& x, const float* src, uint32_t off_floats, size_t floats);
-
 // The two halves of launch_matmul_wide_group. dx_base == nullptr: context scratch.
 WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x, uint32_t M,
-                           float* dx_base);
+                           float* dx_base, const Exchange* xch = nullptr, const float* blk_base = nullptr,
+                           const float* sums = nullptr);
 void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
                         const WideOut* outs, int y_layout, const TokenScale& ts);
 // Gather of a single token tile (M <= 16) whose projections (and sums of squares, when ts.sumsq

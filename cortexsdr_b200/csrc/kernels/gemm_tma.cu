@@ -123,6 +123,17 @@ struct Params {
     uint32_t stages;
     uint32_t x_has_lo;
     float* part;            // [tile][rank][128][N] accumulator tiles of the column ranges
+    // Tensor-parallel exchange (xch_ranks > 1): the finished rows of this rank's partial
+    // projection go straight into every rank's slot for this rank instead of dx_of[]; see
+    // struct Exchange. xch_off[i]: member i's offset inside a block; xch_sums: this rank's
+    // per-token sums of squares to push along (block offset 0), or null.
+    uint32_t xch_ranks, xch_rank, xch_blk;
+    uint32_t xch_off[kMaxGroup];
+    float* xch_slots[kMaxExchangeRanks];
+    uint32_t* xch_flags[kMaxExchangeRanks];
+    uint32_t* xch_seq;
+    uint32_t* xch_done;
+    const float* xch_sums;
     int* status;
     unsigned long long* trace;   // optional: 16 global-timer stamps per CTA (phase boundaries)
     uint32_t trace_ctas;
@@ -196,7 +207,6 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
     if (tid == 0) stamp(p, 1);
-
     if (warp == 0) {
         // ---- loader ----
         // The dictionary planes do not depend on earlier work on the stream: the first round of
@@ -316,6 +326,42 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    // exchange: the sequence number this launch will publish. Read here, behind the accumulator
+    // wait (so behind the loader's dependency wait: every earlier launch, the previous
+    // exchange's included, has completed), and before this CTA is counted out below (the
+    // launch's last CTA advances the counter only after every CTA has been counted)
+    const uint32_t xseq = p.xch_ranks > 1u ? *reinterpret_cast<volatile uint32_t*>(p.xch_seq) + 1u : 0u;
+    const size_t xslot = (static_cast<size_t>(xseq & 1u) * p.xch_ranks + p.xch_rank) * p.xch_blk;
+    // a finished piece of Dx: four tokens of one atom, to the local buffer or to every rank
+    auto emit = [&](uint32_t atom, uint32_t tok, const float4& v, bool vec) {
+        const size_t o = static_cast<size_t>(atom) * p.dx_stride + tok;
+        if (p.xch_ranks > 1u) {
+            const size_t xo = xslot + p.xch_off[seg] + o;
+#pragma unroll
+            for (uint32_t r = 0; r < kMaxExchangeRanks; ++r) {
+                if (r < p.xch_ranks) {
+                    float* dst = p.xch_slots[r] + xo;
+                    if (vec) *reinterpret_cast<float4*>(dst) = v;
+                    else {
+                        dst[0] = v.x;
+                        if (tok + 1u < p.M) dst[1] = v.y;
+                        if (tok + 2u < p.M) dst[2] = v.z;
+                        if (tok + 3u < p.M) dst[3] = v.w;
+                    }
+                }
+            }
+        } else {
+            float* dst = dx + o;
+            if (vec) *reinterpret_cast<float4*>(dst) = v;
+            else {
+                dst[0] = v.x;
+                if (tok + 1u < p.M) dst[1] = v.y;
+                if (tok + 2u < p.M) dst[2] = v.z;
+                if (tok + 3u < p.M) dst[3] = v.w;
+            }
+        }
+    };
+
     {
         // one rank and an aligned token count: the tile is Dx itself; otherwise this rank's slab
         const bool direct = n_ranks == 1u && ((p.M | p.dx_stride) & 3u) == 0;
@@ -324,8 +370,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
             const uint32_t row = i / n4, c4 = i - row * n4;
             const float4 v = *reinterpret_cast<const float4*>(ptile + static_cast<size_t>(row) * pstride + c4 * 4u);
             if (direct) {
-                if (tok0 + c4 * 4u < p.M)
-                    *reinterpret_cast<float4*>(dx + static_cast<size_t>(atom0 + row) * p.dx_stride + tok0 + c4 * 4u) = v;
+                if (tok0 + c4 * 4u < p.M) emit(atom0 + row, tok0 + c4 * 4u, v, true);
             } else {
                 *reinterpret_cast<float4*>(part + (static_cast<size_t>(rank) * kTileM + row) * N + c4 * 4u) = v;
             }
@@ -375,20 +420,31 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
                         acc.w += v[h][r].w;
                     }
                 const uint32_t atom = atom0 + row, tok = tok0 + c4 * 4u;
-                if (tok < p.M) {
-                    float* dst = dx + static_cast<size_t>(atom) * p.dx_stride + tok;
-                    if (vec) *reinterpret_cast<float4*>(dst) = acc;     // tok and M are multiples of four
-                    else {
-                        dst[0] = acc.x;
-                        if (tok + 1u < p.M) dst[1] = acc.y;
-                        if (tok + 2u < p.M) dst[2] = acc.z;
-                        if (tok + 3u < p.M) dst[3] = acc.w;
-                    }
-                }
+                if (tok < p.M) emit(atom, tok, acc, vec);   // vec: tok and M are multiples of four
             }
         }
     }
     if (tid == 0) stamp(p, 7);
+    if (p.xch_ranks > 1u) {
+        // this rank's sums of squares ride along (one CTA pushes them), then the launch is
+        // counted out: the last CTA raises this rank's flag in every rank's region
+        if (p.xch_sums && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid < p.M) {
+            const float v = __ldcg(p.xch_sums + tid);
+            for (uint32_t r = 0; r < p.xch_ranks; ++r) p.xch_slots[r][xslot + tid] = v;
+        }
+        __threadfence_system();           // this thread's peer stores are visible system-wide ...
+        __syncthreads();                  // ... for all threads of the CTA before it is counted
+        if (tid == 0) {
+            const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+            if (atomicAdd(p.xch_done, 1u) == total - 1u) {
+                *p.xch_done = 0u;
+                __threadfence_system();
+                for (uint32_t r = 0; r < p.xch_ranks; ++r)
+                    *reinterpret_cast<volatile uint32_t*>(p.xch_flags[r] + (xseq & 1u) * p.xch_ranks + p.xch_rank) = xseq;
+                *reinterpret_cast<volatile uint32_t*>(p.xch_seq) = xseq;
+            }
+        }
+    }
     __syncthreads();
     if (warp == 1) {
         __syncwarp();
@@ -512,7 +568,8 @@ XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_l
 }
 
 void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
-                         float* const* dx, uint32_t dx_stride) {
+                         float* const* dx, uint32_t dx_stride, const Exchange* xch, const float* blk_base,
+                         const float* sums) {
     using namespace tma_detail;
     if (n_seg == 0 || n_seg > kMaxGroup) throw Error(CSDR_ERR_LIMIT, "projection group holds 1 to 4 dictionaries");
     const uint32_t cols = segs[0]->g.cols;
@@ -614,6 +671,24 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     p.status = ctx->status_word;
     p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
     p.trace_ctas = static_cast<uint32_t>(ctx->sm_count) * 2u;
+    if (xch && xch->ranks > 1u) {
+        if (M > 16u) throw Error(CSDR_ERR_LIMIT, "the peer-memory exchange carries single token tiles (at most 16 tokens)");
+        p.xch_ranks = xch->ranks;
+        p.xch_rank = xch->rank;
+        p.xch_blk = xch->blk_floats;
+        for (uint32_t i = 0; i < n_seg; ++i) {
+            p.xch_off[i] = static_cast<uint32_t>(dx[i] - blk_base);
+            if (p.xch_off[i] + static_cast<size_t>(segs[i]->g.n_atoms) * dx_stride > xch->blk_floats)
+                throw Error(CSDR_ERR_LIMIT, "projection group does not fit an exchange slot");
+        }
+        for (uint32_t r = 0; r < xch->ranks; ++r) {
+            p.xch_slots[r] = xch->slots[r];
+            p.xch_flags[r] = xch->flags[r];
+        }
+        p.xch_seq = xch->seq;
+        p.xch_done = xch->done;
+        p.xch_sums = sums;
+    }
 
     LaunchScope ls(ctx, KC_GEMM);
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_dx_tma_kernel, maps, map_xhi, map_xlo, p));
@@ -623,7 +698,7 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
 void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride) {
     const uint32_t M = static_cast<uint32_t>(a.batch);
     const XPlanesView x = make_x_planes(ctx, a.x, a.x_dtype, a.x_layout, M, seg->g.cols);
-    launch_dx_tma_group(ctx, &seg, 1, x, M, &dx, dx_stride);
+    launch_dx_tma_group(ctx, &seg, 1, x, M, &dx, dx_stride, nullptr, nullptr, nullptr);
 }
 
 }  // namespace csdr
