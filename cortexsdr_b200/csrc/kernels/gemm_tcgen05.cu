@@ -566,7 +566,7 @@ struct GatherGroupParams {
     GatherExchange xch;       // ranks <= 1: Dx is read from m[i].dx
 };
 
-constexpr uint32_t kExchangeSpin = 8000000u;   // polls of a flag word before giving up (several seconds)
+constexpr uint32_t kExchangeSpin = 2000000u;   // polls of a flag word before giving up (a few seconds)
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -618,9 +618,12 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
         __syncthreads();
         if (tid < g.xch.ranks) {
             const uint32_t* f = g.xch.flags + par * g.xch.ranks + tid;
+            // once a wait has run out on this context nothing after it waits again: the step is
+            // lost anyway, and the host must get its error quickly
+            const bool already_failed = *reinterpret_cast<const volatile int*>(g.xch.status) != 0;
             uint32_t spins = 0;
             while (ld_acquire_sys(f) != seq) {
-                if (++spins > kExchangeSpin) {   // gave up: the host will see it
+                if (already_failed || ++spins > kExchangeSpin) {   // gave up: the host will see it
                     late_s = 1;
                     break;
                 }

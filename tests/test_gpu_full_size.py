@@ -1,5 +1,6 @@
-"""BASELINE-sized cases on the GPU: config 1 (4096x4096, batch 1, both tile geometries) and
-config 2 (11008x4096, M in {1, 8, 64, 512}, bf16 activations), encoded by the reference's
+"""BASELINE-sized cases on the GPU: config 1 (4096x4096, batch 1, both tile geometries),
+config 2 (11008x4096, M in {1, 8, 64, 512}, bf16 activations) and config 5 (a q4_K source
+tensor pair 14336x4096 / 4096x14336 behind one shared dictionary, M in {1, 128}), encoded by the reference's
 own encoder where oracle/_ref is present (ksvd_iters=0: the legal fast mode; parity is
 against the reference decoding the SAME archive), else by the synthetic writer. Checked
 against the oracle and through size-independent properties."""
@@ -115,3 +116,51 @@ def test_config2_default_2d_tiles_mlp(ctx, oracle):
         x = np.random.default_rng(M).normal(0, 1, (4096, M)).astype(np.float32)
         e = rel_err(seg.matmul(x, M, allow_2d=True), oracle.dense_matmul(Wo, x, M))
         assert e[0] < TOL and e[1] < TOL, (M, e)
+
+
+def test_config5_kquant_source_shared_dictionary(ctx, oracle, tmp_path):
+    """Two k-quant (q4_K) source tensors, 14336x4096 and 4096x14336: dequantised on the device
+    bit for bit like the oracle, then - as the reference does for quantised GGUF tensors, whose
+    blocks are source dtypes, not coefficient packing - HSDR-encoded from the fp32 values by the
+    reference encoder into an .hsda whose FEED_FORWARD role shares one 128x128-tile dictionary.
+    The sparsity setting of the config is inert for HSDR, so one archive stands for all three."""
+    import torch
+    from oracle.bindings import SEG_FEED_FORWARD, Reference, Segment, cfg_default, cfg_mlp
+    if not Reference.available():
+        pytest.skip("needs the compiled reference (oracle/_ref) to write the shared-dictionary archive")
+    ref = Reference()
+    st = cs.HierarchicalSDRStrategy(ctx)
+    rng = np.random.default_rng(55)
+    shapes = ((14336, 4096), (4096, 14336))
+    segs = []
+    for i, (R, C) in enumerate(shapes):
+        nblk = R * C // 256
+        raw = rng.integers(0, 256, size=(nblk, 144), dtype=np.uint8)
+        # fp16 super-scale d and super-min dmin of every block: small, finite
+        raw[:, 0:4] = rng.normal(0, 0.002, size=(nblk, 2)).astype(np.float16).view(np.uint8).reshape(nblk, 4)
+        raw = raw.reshape(-1)
+        w = st.dequantizeToFP32(raw, "q4_k")
+        assert w.size == R * C
+        want = oracle.dequantize("q4_k", raw)
+        assert zlib.crc32(w.tobytes()) == zlib.crc32(want.tobytes())          # bit-exact at full size
+        segs.append(Segment(f"blk.{i}.ffn.weight", w.reshape(R, C), (R, C), SEG_FEED_FORWARD, layer_index=i))
+    path = str(tmp_path / "cfg5.hsda")
+    n_dicts = ref.hsda_write(segs, path, cfg_default(ksvd_iters=0), cfg_mlp(ksvd_iters=0))
+    assert n_dicts == 1                                                       # one dictionary for both tensors
+    r = cs.HSDAReader.fromFile(path, ctx)
+    assert r.numDictionaries() == 1
+    for i, (R, C) in enumerate(shapes):
+        name = f"blk.{i}.ffn.weight"
+        W = r.decompress(name)
+        assert zlib.crc32(W.tobytes()) == zlib.crc32(ref.hsda_decompress(path, name, R, C).tobytes())
+        Wd = torch.from_numpy(W).cuda()
+        for M in (1, 128):
+            xb = torch.randn((C, M), generator=torch.Generator().manual_seed(M + i)).to(torch.bfloat16).float()
+            x = np.ascontiguousarray(xb.numpy())
+            with pytest.raises(cs.CompressionError):
+                r.matmul(name, x, M)                                          # the reference refuses 2-D tiles here
+            y = r.matmul(name, x, M, allow_2d=True)
+            want = (Wd.double() @ xb.cuda().double()).float().cpu().numpy()  # dense product of the decoded weights
+            e = rel_err(y, want)
+            assert e[0] < TOL and e[1] < TOL, (name, M, e)
+        del Wd
