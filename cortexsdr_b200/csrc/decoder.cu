@@ -250,8 +250,11 @@ void sum_over_ranks(csdr_decoder* d, float* from, size_t floats) {
 
 // One group of linears over activation planes: projection launch, rank sum, gather launch.
 // `normed`: the planes hold w*h and the gather applies 1/rms from the sums of squares.
-void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_bfloat16* planes, size_t plane_elems,
-          uint32_t T, bool normed, const float* sums, std::initializer_list<WideOut> outs) {
+// `act_hi`: the group is (gate, up) and, when the step is a single token tile, the gather writes
+// silu(gate) * up into these planes and returns true; else the caller applies SiLU itself.
+bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_bfloat16* planes, size_t plane_elems,
+          uint32_t T, bool normed, const float* sums, std::initializer_list<WideOut> outs,
+          __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr) {
     const csdr_segment* segs[4];
     WideOut o[4];
     uint32_t n = 0;
@@ -271,14 +274,23 @@ void wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
         // every rank's exchange slot and raises the flags; the gather sums the slots while staging
         const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, &d->xch, base,
                                              normed ? sums : nullptr);
+        if (act_hi) {
+            launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo, &d->xch, base);
+            return true;
+        }
         launch_wide_gather_exchanged(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts, d->xch, base);
-        return;
+        return false;
     }
     const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
     // the sums sit right in front of the projections: one collective covers both
     if (normed && sums == base) sum_over_ranks(d, base, d->sum_pad + w.floats);
     else sum_over_ranks(d, w.base, w.floats);
+    if (act_hi && w.tile_mt) {
+        launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo, nullptr, nullptr);
+        return true;
+    }
     launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts);
+    return false;
 }
 
 // The block loop on the tensor cores (steps of at least the tensor-core threshold on one GPU;
@@ -313,9 +325,9 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
                      a_hi, a_hi + a_n);
         wide(d, {&L.o}, a_hi, a_n, T, false, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
         op_scale_sumsq_planes(ctx, F(d->hidden), F(L.ffn_norm), T, Hl, h_hi, h_hi + h_n, sums);
-        wide(d, {&L.gate, &L.up}, h_hi, h_n, T, true, sums,
-             {WideOut{F(d->gate), nullptr, nullptr}, WideOut{F(d->up), nullptr, nullptr}});
-        op_silu_mul_planes(ctx, F(d->gate), F(d->up), i_n, i_hi, i_hi + i_n);
+        if (!wide(d, {&L.gate, &L.up}, h_hi, h_n, T, true, sums,
+                  {WideOut{F(d->gate), nullptr, nullptr}, WideOut{F(d->up), nullptr, nullptr}}, i_hi, i_hi + i_n))
+            op_silu_mul_planes(ctx, F(d->gate), F(d->up), i_n, i_hi, i_hi + i_n);
         wide(d, {&L.down}, i_hi, i_n, T, false, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
         const float* next_norm = li + 1 < c.n_layers ? F(d->layers[li + 1].attn_norm) : F(d->out_norm);
         op_scale_sumsq_planes(ctx, F(d->hidden), next_norm, T, Hl, h_hi, h_hi + h_n, sums);

@@ -561,9 +561,12 @@ struct GatherExchange {
 struct GatherGroupParams {
     GatherMember m[kGatherGroupMax];
     uint32_t n_seg, M, m_total, code_cap16;
+    uint32_t region_bytes;    // shared memory of one member: codes | scales | Dx
     int y_layout;
     TokenScale ts;
     GatherExchange xch;       // ranks <= 1: Dx is read from m[i].dx
+    __nv_bfloat16* act_hi;    // SwiGLU pair: planes of silu(member 0) * member 1, laid out like y
+    __nv_bfloat16* act_lo;
 };
 
 constexpr uint32_t kExchangeSpin = 2000000u;   // polls of a flag word before giving up (a few seconds)
@@ -574,31 +577,40 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
-template <int MT>
+// PAIR: the group is (gate, up) of a SwiGLU block with equal row counts; a CTA gathers the same
+// rows of both and writes silu(gate) * up as bf16 planes (silu_mul, api/cortex_sdk.cpp:1245-1256,
+// folded in), so the two fp32 intermediates never exist.
+template <int MT, bool PAIR>
 __global__ void __launch_bounds__(kGroupThreads)
 hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     extern __shared__ __align__(16) unsigned char ggsm[];
     asm volatile("griddepcontrol.launch_dependents;");
-    uint32_t mi = 0;
+    constexpr uint32_t NM = PAIR ? 2u : 1u;      // members this CTA works on
+    uint32_t mi0 = 0;
+    if (!PAIR) {
 #pragma unroll
-    for (uint32_t i = 1; i < kGatherGroupMax; ++i)
-        if (i < g.n_seg && blockIdx.x >= g.m[i].cta_begin) mi = i;
-    const GatherMember& m = g.m[mi];
-    const uint32_t slots = m.S * m.k;
+        for (uint32_t i = 1; i < kGatherGroupMax; ++i)
+            if (i < g.n_seg && blockIdx.x >= g.m[i].cta_begin) mi0 = i;
+    }
+    const GatherMember& m0 = g.m[mi0];
     const uint32_t tid = threadIdx.x;
-    const uint32_t row0 = (blockIdx.x - m.cta_begin) * m.rows_per_cta;
-    const bool active = row0 < m.R;
-    const uint32_t rows_here = active ? min(m.rows_per_cta, m.R - row0) : 0u;
+    const uint32_t row0 = (blockIdx.x - m0.cta_begin) * m0.rows_per_cta;
+    const bool active = row0 < m0.R;
+    const uint32_t rows_here = active ? min(m0.rows_per_cta, m0.R - row0) : 0u;
 
-    // layout: codes (16-byte units) | scales | Dx
-    const size_t code_byte0 = static_cast<size_t>(row0) * slots * 2u;
-    const size_t aligned0 = code_byte0 & ~static_cast<size_t>(15);
-    const uint32_t skip = static_cast<uint32_t>(code_byte0 - aligned0) >> 1;
-    const uint32_t n16 = active ? (skip * 2u + rows_here * slots * 2u + 15u) >> 4 : 0u;
-    uint4* cs16 = reinterpret_cast<uint4*>(ggsm);
-    float* sc = reinterpret_cast<float*>(ggsm + static_cast<size_t>(g.code_cap16) * 16u);
-    float* dxs = sc + 64;
-    {
+    // per member: codes (16-byte units) | scales | Dx
+    const uint32_t region = g.region_bytes;
+    uint32_t skip[NM];
+#pragma unroll
+    for (uint32_t q = 0; q < NM; ++q) {
+        const GatherMember& m = g.m[mi0 + q];
+        const uint32_t slots = m.S * m.k;
+        const size_t code_byte0 = static_cast<size_t>(row0) * slots * 2u;
+        const size_t aligned0 = code_byte0 & ~static_cast<size_t>(15);
+        skip[q] = static_cast<uint32_t>(code_byte0 - aligned0) >> 1;
+        const uint32_t n16 = active ? (skip[q] * 2u + rows_here * slots * 2u + 15u) >> 4 : 0u;
+        uint4* cs16 = reinterpret_cast<uint4*>(ggsm + q * region);
+        float* sc = reinterpret_cast<float*>(ggsm + q * region + static_cast<size_t>(g.code_cap16) * 16u);
         const unsigned char* src = reinterpret_cast<const unsigned char*>(m.codes) + aligned0;
         for (uint32_t i = tid; i < n16; i += kGroupThreads)
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
@@ -612,7 +624,7 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     __shared__ int late_s;
     if (g.xch.ranks > 1u) {
         // ---- partial projections of all ranks arrive through peer memory ----
-        const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(g.xch.seq);   // the push before this kernel set it
+        const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(g.xch.seq);   // the projection before this kernel set it
         const uint32_t par = seq & 1u;
         if (tid == 0) late_s = 0;
         __syncthreads();
@@ -632,24 +644,29 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
         __syncthreads();
         const float* slot0 = g.xch.slots + static_cast<size_t>(par) * g.xch.ranks * g.xch.blk_floats;
         if (active) {
-            const uint32_t n4 = (m.K * MT) >> 2;
-            const float* mine = slot0 + g.xch.dx_off[mi];
-            for (uint32_t i = tid; i < n4; i += kGroupThreads) {
-                float4 v[kMaxExchangeRanks];               // all ranks' pieces in flight, then the adds
 #pragma unroll
-                for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)
-                    if (r < g.xch.ranks)
-                        v[r] = __ldcg(reinterpret_cast<const float4*>(mine + static_cast<size_t>(r) * g.xch.blk_floats) + i);
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t q = 0; q < NM; ++q) {
+                const GatherMember& m = g.m[mi0 + q];
+                float* dxs = reinterpret_cast<float*>(ggsm + q * region + static_cast<size_t>(g.code_cap16) * 16u) + 64;
+                const uint32_t n4 = (m.K * MT) >> 2;
+                const float* mine = slot0 + g.xch.dx_off[mi0 + q];
+                for (uint32_t i = tid; i < n4; i += kGroupThreads) {
+                    float4 v[kMaxExchangeRanks];               // all ranks' pieces in flight, then the adds
 #pragma unroll
-                for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)   // rank order: every rank gets the same sum
-                    if (r < g.xch.ranks) {
-                        acc.x += v[r].x;
-                        acc.y += v[r].y;
-                        acc.z += v[r].z;
-                        acc.w += v[r].w;
-                    }
-                reinterpret_cast<float4*>(dxs)[i] = acc;
+                    for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)
+                        if (r < g.xch.ranks)
+                            v[r] = __ldcg(reinterpret_cast<const float4*>(mine + static_cast<size_t>(r) * g.xch.blk_floats) + i);
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)   // rank order: every rank gets the same sum
+                        if (r < g.xch.ranks) {
+                            acc.x += v[r].x;
+                            acc.y += v[r].y;
+                            acc.z += v[r].z;
+                            acc.w += v[r].w;
+                        }
+                    reinterpret_cast<float4*>(dxs)[i] = acc;
+                }
             }
         }
         if (g.ts.sumsq && tid < MT) {
@@ -660,13 +677,18 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
         if (tid == 0 && late_s && blockIdx.x == 0) atomicExch(g.xch.status, 1);
     } else {
         if (active) {
-            const uint32_t n4 = (m.K * MT) >> 2;
-            for (uint32_t i = tid; i < n4; i += kGroupThreads)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                                 static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
-                             "l"(m.dx + static_cast<size_t>(i) * 4u)
-                             : "memory");
-            for (uint32_t i = (n4 << 2) + tid; i < m.K * MT; i += kGroupThreads) dxs[i] = m.dx[i];
+#pragma unroll
+            for (uint32_t q = 0; q < NM; ++q) {
+                const GatherMember& m = g.m[mi0 + q];
+                float* dxs = reinterpret_cast<float*>(ggsm + q * region + static_cast<size_t>(g.code_cap16) * 16u) + 64;
+                const uint32_t n4 = (m.K * MT) >> 2;
+                for (uint32_t i = tid; i < n4; i += kGroupThreads)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                                     static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
+                                 "l"(m.dx + static_cast<size_t>(i) * 4u)
+                                 : "memory");
+                for (uint32_t i = (n4 << 2) + tid; i < m.K * MT; i += kGroupThreads) dxs[i] = m.dx[i];
+            }
         }
         if (g.ts.sumsq && tid < MT) inv_rms_s[tid] = rsqrtf(g.ts.sumsq[tid < g.M ? tid : 0] * g.ts.inv_width + g.ts.eps);
     }
@@ -674,51 +696,73 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     if (!active) return;
-    const uint16_t* cs = reinterpret_cast<const uint16_t*>(cs16) + skip;
     const uint32_t b = tid % MT;
     constexpr uint32_t RP = kGroupThreads / MT;
     for (uint32_t rl = tid / MT; rl < rows_here; rl += RP) {
-        const uint16_t* rc = cs + rl * slots;
-        float acc = 0.0f;
-        for (uint32_t l = 0; l < m.S; ++l) {
-            const float gamma = sc[l];
+        float res[NM];
+#pragma unroll
+        for (uint32_t q = 0; q < NM; ++q) {
+            const GatherMember& m = g.m[mi0 + q];
+            const unsigned char* base = ggsm + q * region;
+            const uint16_t* cs = reinterpret_cast<const uint16_t*>(base) + skip[q];
+            const float* sc = reinterpret_cast<const float*>(base + static_cast<size_t>(g.code_cap16) * 16u);
+            const float* dxs = sc + 64;
+            const uint16_t* rc = cs + rl * (m.S * m.k);
+            float acc = 0.0f;
+            for (uint32_t l = 0; l < m.S; ++l) {
+                const float gamma = sc[l];
 #pragma unroll 4
-            for (uint32_t kk = 0; kk < m.k; ++kk) {
-                const uint32_t code = rc[l * m.k + kk];
-                const float scale = (code & 0x8000u) ? -gamma : gamma;
-                acc = __fadd_rn(acc, __fmul_rn(scale, dxs[(code & 0x7FFFu) * MT + b]));
+                for (uint32_t kk = 0; kk < m.k; ++kk) {
+                    const uint32_t code = rc[l * m.k + kk];
+                    const float scale = (code & 0x8000u) ? -gamma : gamma;
+                    acc = __fadd_rn(acc, __fmul_rn(scale, dxs[(code & 0x7FFFu) * MT + b]));
+                }
             }
+            if (g.ts.sumsq) acc *= inv_rms_s[b];
+            if (m.bias) acc += m.bias[row0 + rl];
+            res[q] = acc;
         }
         if (b < g.M) {
             const uint32_t r = row0 + rl;
             const size_t o = g.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * g.m_total + b
-                                                                      : static_cast<size_t>(b) * m.R + r;
-            if (g.ts.sumsq) acc *= inv_rms_s[b];
-            if (m.bias) acc += m.bias[r];
-            if (m.residual) acc += m.residual[o];
-            m.y[o] = acc;
+                                                                      : static_cast<size_t>(b) * m0.R + r;
+            if (PAIR) {
+                const float x = res[0];
+                const float sig = 1.0f / (1.0f + expf(-x));
+                const float v = (x * sig) * res[NM - 1];
+                const __nv_bfloat16 h = __float2bfloat16_rn(v);
+                g.act_hi[o] = h;
+                g.act_lo[o] = __float2bfloat16_rn(v - __bfloat162float(h));
+            } else {
+                float acc = res[0];
+                if (m0.residual) acc += m0.residual[o];
+                m0.y[o] = acc;
+            }
         }
     }
 }
 
 template <int MT>
 void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t total_rows, uint32_t max_k, uint32_t max_slots) {
-    // about two CTAs per SM over the whole group
+    const bool pair = g.act_hi != nullptr;
+    // about two CTAs per SM over the whole group (a pair walks the rows of one member)
     const uint32_t want = 2u * static_cast<uint32_t>(ctx->sm_count);
-    const uint32_t rows_per_cta = std::max(kGroupThreads / MT, (total_rows + want - 1u) / want);
+    const uint32_t rows_all = pair ? g.m[0].R : total_rows;
+    const uint32_t rows_per_cta = std::max(kGroupThreads / MT, (rows_all + want - 1u) / want);
     uint32_t ctas = 0;
     for (uint32_t i = 0; i < g.n_seg; ++i) {
-        g.m[i].cta_begin = ctas;
+        g.m[i].cta_begin = pair ? 0u : ctas;
         g.m[i].rows_per_cta = rows_per_cta;
-        ctas += (g.m[i].R + rows_per_cta - 1u) / rows_per_cta;
+        if (!pair || i == 0) ctas += (g.m[i].R + rows_per_cta - 1u) / rows_per_cta;
     }
     g.code_cap16 = (rows_per_cta * max_slots * 2u + 15u + 16u) >> 4;
-    const size_t smem = static_cast<size_t>(g.code_cap16) * 16u + 64u * 4u + static_cast<size_t>(max_k) * MT * 4u;
-    auto kern = hsdr_gather_group_kernel<MT>;
-    static size_t smem_set = 0;
-    if (smem > 48u * 1024u && smem > smem_set) {
+    g.region_bytes = static_cast<uint32_t>(static_cast<size_t>(g.code_cap16) * 16u + 64u * 4u + static_cast<size_t>(max_k) * MT * 4u);
+    const size_t smem = static_cast<size_t>(g.region_bytes) * (pair ? 2u : 1u);
+    auto kern = pair ? hsdr_gather_group_kernel<MT, true> : hsdr_gather_group_kernel<MT, false>;
+    static size_t smem_set[2] = {0, 0};
+    if (smem > 48u * 1024u && smem > smem_set[pair]) {
         CSDR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        smem_set = smem;
+        smem_set[pair] = smem;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(ctas, 1, 1);
@@ -805,8 +849,15 @@ WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, u
 
 namespace {
 void gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
-                       const WideOut* outs, int y_layout, const TokenScale& ts, const Exchange* x, const float* blk_base) {
+                       const WideOut* outs, int y_layout, const TokenScale& ts, const Exchange* x, const float* blk_base,
+                       __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr) {
     GatherGroupParams g{};
+    if (act_hi) {
+        if (n != 2 || segs[0]->g.rows != segs[1]->g.rows || !act_lo)
+            throw Error(CSDR_ERR_INVALID_ARG, "a SwiGLU pair is two segments with the same number of rows");
+        g.act_hi = act_hi;
+        g.act_lo = act_lo;
+    }
     g.n_seg = n;
     g.M = M;
     g.m_total = M;
@@ -857,6 +908,14 @@ void launch_wide_gather_exchanged(csdr_context* ctx, const csdr_segment* const* 
                                   const Exchange& x, const float* blk_base) {
     if (!w.tile_mt) throw Error(CSDR_ERR_LIMIT, "the peer-memory exchange carries single token tiles (at most 16 tokens)");
     gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts, &x, blk_base);
+}
+
+void launch_wide_gather_swiglu(csdr_context* ctx, const csdr_segment* const* gate_up, const WideDx& w, uint32_t M,
+                               const TokenScale& ts, __nv_bfloat16* act_hi, __nv_bfloat16* act_lo, const Exchange* x,
+                               const float* blk_base) {
+    if (!w.tile_mt) throw Error(CSDR_ERR_LIMIT, "the fused SwiGLU gather takes single token tiles (at most 16 tokens)");
+    const WideOut none[2] = {WideOut{nullptr, nullptr, nullptr}, WideOut{nullptr, nullptr, nullptr}};
+    gather_tile_group(ctx, gate_up, 2, w, M, none, CSDR_LAYOUT_TOKEN_MAJOR, ts, x, blk_base, act_hi, act_lo);
 }
 
 void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,

@@ -104,6 +104,12 @@ void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint
 void launch_wide_gather_exchanged(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w,
                                   uint32_t M, const WideOut* outs, int y_layout, const TokenScale& ts,
                                   const Exchange& x, const float* blk_base);
+// (gate, up) of a SwiGLU block over at most 16 tokens: one gather launch that writes
+// silu(gate) * up, token-major, as bf16 planes for the down projection. `x` (with blk_base) when
+// the projections arrive through the tensor-parallel exchange, else null.
+void launch_wide_gather_swiglu(csdr_context* ctx, const csdr_segment* const* gate_up, const WideDx& w, uint32_t M,
+                               const TokenScale& ts, __nv_bfloat16* act_hi, __nv_bfloat16* act_lo, const Exchange* x,
+                               const float* blk_base);
 bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, size_t batch);
 void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
                               uint32_t M, const WideOut* outs, int y_layout);
