@@ -11,6 +11,7 @@
 //   argmax_kernel         greedy pick over the logits row
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cfloat>
 
 #include "../internal.hpp"
@@ -163,6 +164,9 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
                   const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t HD,
                   uint32_t max_seq, float theta) {
     pdl_enter();
+    // grid (token, slice of the heads): the few tokens of a decode step still fill a good part of
+    // the GPU. A thread keeps one rotary pair index whenever the block size is a multiple of the
+    // pairs per head, so the angle's cosine and sine are computed once per thread.
     const uint32_t t = blockIdx.x;
     const int32_t pos = pos_of[t], sq = seq_of[t];
     const uint32_t rotary = HD - (HD & 1u), half = rotary >> 1;
@@ -171,12 +175,10 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
     const float* vt = v + static_cast<size_t>(t) * KVH * HD;
     const size_t slot = (static_cast<size_t>(sq) * max_seq + static_cast<size_t>(pos)) * KVH * HD;
     const bool in_cache = pos >= 0 && static_cast<uint32_t>(pos) < max_seq && sq >= 0;
-    for (uint32_t e = threadIdx.x; e < (QH + KVH) * half; e += 256) {
-        const uint32_t head = e / half, i = (e - head * half) * 2u;
-        const float exponent = static_cast<float>(i) / static_cast<float>(HD);
-        const float freq = powf(theta, -exponent);
-        const float angle = static_cast<float>(pos) * freq;
-        const float c = cosf(angle), s = sinf(angle);
+    const uint32_t heads = QH + KVH;
+    const uint32_t per = (heads + gridDim.y - 1u) / gridDim.y;
+    const uint32_t h0 = blockIdx.y * per, h1 = min(heads, h0 + per);
+    auto rotate = [&](uint32_t head, uint32_t i, float c, float s) {
         if (head < QH) {
             float* b = qt + head * HD + i;
             const float x0 = b[0], x1 = b[1];
@@ -189,12 +191,34 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
             kc[slot + kh * HD + i] = x0 * c - x1 * s;
             kc[slot + kh * HD + i + 1] = x0 * s + x1 * c;
         }
+    };
+    auto angle_of = [&](uint32_t i, float& c, float& s) {
+        const float exponent = static_cast<float>(i) / static_cast<float>(HD);
+        const float freq = powf(theta, -exponent);
+        const float angle = static_cast<float>(pos) * freq;
+        c = cosf(angle);
+        s = sinf(angle);
+    };
+    if (half > 0 && half <= 256u && 256u % half == 0) {
+        const uint32_t i = (threadIdx.x % half) * 2u;
+        float c, s;
+        angle_of(i, c, s);
+        for (uint32_t head = h0 + threadIdx.x / half; head < h1; head += 256u / half) rotate(head, i, c, s);
+    } else {
+        for (uint32_t e = threadIdx.x; e < (h1 - h0) * half; e += 256) {
+            const uint32_t head = h0 + e / half, i = (e % half) * 2u;
+            float c, s;
+            angle_of(i, c, s);
+            rotate(head, i, c, s);
+        }
     }
     if (in_cache) {
+        // this slice's share of the K tail (odd head_dim) and of V: the kv heads it covers
+        const uint32_t kv0 = h0 > QH ? h0 - QH : 0u, kv1 = h1 > QH ? h1 - QH : 0u;
         if (HD & 1u)
-            for (uint32_t kh = threadIdx.x; kh < KVH; kh += 256)
+            for (uint32_t kh = kv0 + threadIdx.x; kh < kv1; kh += 256)
                 kc[slot + kh * HD + HD - 1] = kt[kh * HD + HD - 1];
-        for (uint32_t e = threadIdx.x; e < KVH * HD; e += 256) vc[slot + e] = vt[e];
+        for (uint32_t e = kv0 * HD + threadIdx.x; e < kv1 * HD; e += 256) vc[slot + e] = vt[e];
     }
 }
 
@@ -462,7 +486,10 @@ void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, 
                    const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
                    uint32_t HD, uint32_t max_seq, float theta) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    launch_pdl(ctx, rope_cache_kernel, dim3(T), dim3(256), q, k, v, kc, vc, seq_of, pos_of, QH, KVH, HD, max_seq, theta);
+    // slices of the heads per token: enough CTAs for a decode step, one for a long prefill
+    const uint32_t slices = T >= 256u ? 1u : std::min<uint32_t>(QH + KVH, std::max(1u, 256u / std::max(T, 1u)));
+    launch_pdl(ctx, rope_cache_kernel, dim3(T, std::min(slices, 16u)), dim3(256), q, k, v, kc, vc, seq_of, pos_of, QH, KVH, HD,
+               max_seq, theta);
     ls.done("rope_cache_kernel");
 }
 
