@@ -8,6 +8,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <initializer_list>
 #include <string>
@@ -95,7 +96,7 @@ struct csdr_decoder {
     size_t cache_layer_stride = 0;
     std::vector<int32_t> pos_host;
     DevPtr pos_dev, tokens_dev, seq_of, pos_of, next_dev;
-    DevPtr hidden, normed, normed_l, q, k, v, att, proj, gate, up, staged, logits, logits_l;
+    DevPtr hidden, normed, q, k, v, att, proj, gate, up, staged, logits, logits_l;
     // projections of a group between its two launches, behind a block of per-token sums of
     // squares: [sum_pad floats][Dx of every member]; tensor-parallel ranks add theirs up in place
     DevPtr dxbuf;
@@ -104,6 +105,7 @@ struct csdr_decoder {
     // most 16 tokens); until the host program has passed the peers' handles in, NCCL sums them
     DevPtr xch_region;
     Exchange xch;                  // ranks == 0 until imported
+    bool xch_use = false;          // imported AND chosen: CSDR_TP_EXCHANGE=peer|nccl, default peer from 3 ranks up
     uint32_t xch_blk = 0;
     std::vector<void*> xch_maps;   // peers' regions as mapped here (closed on destroy)
     // bf16 hi/lo planes of the three activation widths the projections consume (hidden,
@@ -141,19 +143,19 @@ std::vector<float> load_raw(csdr_archive* ar, const std::string& name, size_t wa
     return v;
 }
 
-// A norm weight vector; tensor-parallel ranks keep their slice of it.
 DevPtr load_vector(csdr_decoder* d, const std::string& name, uint32_t n) {
     std::vector<float> v = load_raw(d->ar, name, n);
-    const uint32_t nl = n / d->P;
-    DevPtr p = upload(d->ctx, v.data() + static_cast<size_t>(d->rank) * nl, static_cast<size_t>(nl) * 4);
+    DevPtr p = upload(d->ctx, v.data(), static_cast<size_t>(n) * 4);
     CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
     return p;
 }
 
-// Resolve a linear by name. Tensor-parallel ranks keep output rows [rank*R/P, (rank+1)*R/P) of
-// the code stream (row_shard) and input columns [rank*C/P, (rank+1)*C/P) of the dictionary
-// (col_shard): each rank then reads 1/P of every dictionary, projects its slice of the
-// activations, and the ranks' partial projections are summed before the gather.
+// Resolve a linear by name. A tensor-parallel rank keeps output rows [rank*R/P, (rank+1)*R/P) of
+// the code stream (row_shard: q, k, v, gate, up, the head - their input is the replicated
+// hidden state, their output stays on the rank) or input columns [rank*C/P, (rank+1)*C/P) of the
+// dictionary (col_shard: the output and down projections - their input is the rank's slice of
+// the heads / intermediate width; every rank projects its slice, the partial projections are
+// summed over the ranks, and every rank gathers all rows into its copy of the hidden state).
 Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint32_t cols, bool row_shard,
                    bool col_shard) {
     csdr_segment_header h{};
@@ -252,8 +254,10 @@ void sum_over_ranks(csdr_decoder* d, float* from, size_t floats) {
 // `normed`: the planes hold w*h and the gather applies 1/rms from the sums of squares.
 // `act_hi`: the group is (gate, up) and, when the step is a single token tile, the gather writes
 // silu(gate) * up into these planes and returns true; else the caller applies SiLU itself.
+// `partial`: every rank holds a column slice of the dictionaries, so the projections must be
+// summed over the ranks before the gather.
 bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_bfloat16* planes, size_t plane_elems,
-          uint32_t T, bool normed, const float* sums, std::initializer_list<WideOut> outs,
+          uint32_t T, bool normed, bool partial, const float* sums, std::initializer_list<WideOut> outs,
           __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr) {
     const csdr_segment* segs[4];
     WideOut o[4];
@@ -269,11 +273,10 @@ bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
     if (normed) ts = TokenScale{sums, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
     uint32_t total_atoms = 0;
     for (uint32_t i = 0; i < n; ++i) total_atoms += segs[i]->g.n_atoms;
-    if (d->xch.ranks > 1u && T <= 16u && d->sum_pad + static_cast<size_t>(total_atoms) * 16u <= d->xch_blk) {
-        // the projection kernel stores its finished rows (and this rank's sums of squares) into
-        // every rank's exchange slot and raises the flags; the gather sums the slots while staging
-        const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, &d->xch, base,
-                                             normed ? sums : nullptr);
+    if (partial && d->xch_use && T <= 16u && d->sum_pad + static_cast<size_t>(total_atoms) * 16u <= d->xch_blk) {
+        // the projection kernel stores its finished rows into every rank's exchange slot and
+        // raises the flags; the gather sums the slots while staging
+        const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, &d->xch, base, nullptr);
         if (act_hi) {
             launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo, &d->xch, base);
             return true;
@@ -282,9 +285,7 @@ bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
         return false;
     }
     const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
-    // the sums sit right in front of the projections: one collective covers both
-    if (normed && sums == base) sum_over_ranks(d, base, d->sum_pad + w.floats);
-    else sum_over_ranks(d, w.base, w.floats);
+    if (partial) sum_over_ranks(d, w.base, w.floats);
     if (act_hi && w.tile_mt) {
         launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo, nullptr, nullptr);
         return true;
@@ -298,11 +299,13 @@ bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
 // projection as bf16 planes; q|k|v and gate|up share a projection launch and a gather launch;
 // the residual additions ride on the gathers of the output and down projections; RMS
 // normalisation is split into "planes of w*h + sums of squares" before the projection and
-// "times 1/rms" in the gather. With P ranks everything is sliced P ways - hidden width, heads,
-// KV cache, intermediate width, dictionary columns, code rows - and the only exchange is the sum
-// of the ranks' partial projections (K x T floats per dictionary), four per block.
-// Leaves the final hidden states in d->hidden (this rank's slice) and the final norm's planes
-// and sums in xp_h / dxbuf.
+// "times 1/rms" in the gather; SwiGLU is folded into the gate|up gather for single token tiles.
+// With P ranks the hidden state is replicated; heads, KV cache and intermediate width are sliced
+// P ways, q|k|v|gate|up by code rows, and the output and down projections by dictionary columns,
+// so that the only exchanges are the sums of those two projections' partial results (K x T
+// floats each): two per block, each of them a barrier across the ranks.
+// Leaves the final hidden states in d->hidden and the final norm's planes and sums in
+// xp_h / dxbuf.
 void run_blocks_planes(csdr_decoder* d, uint32_t T) {
     const csdr_decoder_config& c = d->cfg;
     csdr_context* ctx = d->ctx;
@@ -315,7 +318,7 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
     op_scale_sumsq_planes(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, Hl, h_hi, h_hi + h_n, sums);
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         Layer& L = d->layers[li];
-        wide(d, {&L.q, &L.k, &L.v}, h_hi, h_n, T, true, sums,
+        wide(d, {&L.q, &L.k, &L.v}, h_hi, h_n, T, true, false, sums,
              {WideOut{F(d->q), nullptr, nullptr}, WideOut{F(d->k), nullptr, nullptr}, WideOut{F(d->v), nullptr, nullptr}});
         float* kc = F(d->kcache) + li * d->cache_layer_stride;
         float* vc = F(d->vcache) + li * d->cache_layer_stride;
@@ -323,12 +326,12 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
                       c.max_seq, c.rope_theta);
         op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, nullptr,
                      a_hi, a_hi + a_n);
-        wide(d, {&L.o}, a_hi, a_n, T, false, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
+        wide(d, {&L.o}, a_hi, a_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
         op_scale_sumsq_planes(ctx, F(d->hidden), F(L.ffn_norm), T, Hl, h_hi, h_hi + h_n, sums);
-        if (!wide(d, {&L.gate, &L.up}, h_hi, h_n, T, true, sums,
+        if (!wide(d, {&L.gate, &L.up}, h_hi, h_n, T, true, false, sums,
                   {WideOut{F(d->gate), nullptr, nullptr}, WideOut{F(d->up), nullptr, nullptr}}, i_hi, i_hi + i_n))
             op_silu_mul_planes(ctx, F(d->gate), F(d->up), i_n, i_hi, i_hi + i_n);
-        wide(d, {&L.down}, i_hi, i_n, T, false, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
+        wide(d, {&L.down}, i_hi, i_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
         const float* next_norm = li + 1 < c.n_layers ? F(d->layers[li + 1].attn_norm) : F(d->out_norm);
         op_scale_sumsq_planes(ctx, F(d->hidden), next_norm, T, Hl, h_hi, h_hi + h_n, sums);
     }
@@ -370,41 +373,29 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
     }
 }
 
-// Final-normed hidden states of all T tokens, whole width, into d->normed (what forward() hands
-// back); only the planes path has work to do here.
+// Final-normed hidden states of all T tokens into d->normed (what forward() hands back); only
+// the planes path has work to do here.
 void materialise_normed(csdr_decoder* d, uint32_t T) {
     if (!use_planes(d, T)) return;
-    float* sums = F(d->dxbuf);
-    sum_over_ranks(d, sums, T);
-    if (d->P == 1) {
-        op_norm_from_sumsq(d->ctx, F(d->hidden), F(d->out_norm), sums, T, d->H_l, d->cfg.hidden, d->cfg.rms_eps, F(d->normed));
-        return;
-    }
-    op_norm_from_sumsq(d->ctx, F(d->hidden), F(d->out_norm), sums, T, d->H_l, d->cfg.hidden, d->cfg.rms_eps, F(d->normed_l));
-    nccl_check(nccl().AllGather(F(d->normed_l), F(d->staged), static_cast<size_t>(T) * d->H_l, ncclFloat, d->comm,
-                                d->ctx->stream),
-               "ncclAllGather");
-    op_unshard(d->ctx, F(d->staged), d->P, T, d->H_l, F(d->normed), false);
+    op_norm_from_sumsq(d->ctx, F(d->hidden), F(d->out_norm), F(d->dxbuf), T, d->cfg.hidden, d->cfg.hidden, d->cfg.rms_eps,
+                       F(d->normed));
 }
 
-// logits (n x vocab) of tokens [t0, t0 + n) of the T that run_blocks just processed. `summed`:
-// materialise_normed already added the ranks' sums of squares up.
-void run_logits(csdr_decoder* d, uint32_t T, uint32_t t0, uint32_t n, bool summed) {
+// logits (n x vocab) of tokens [t0, t0 + n) of the T that run_blocks just processed. Ranks hold
+// row shards of the head (whole dictionary, replicated hidden state): the logits are
+// all-gathered.
+void run_logits(csdr_decoder* d, uint32_t T, uint32_t t0, uint32_t n) {
     if (!use_planes(d, T)) {
         linear(d, d->lm_head, F(d->normed) + static_cast<size_t>(t0) * d->cfg.hidden, n, F(d->logits));
         return;
     }
     // the final norm's planes and sums are in place; rows t0.. of them feed the head
     float* base = F(d->dxbuf);
-    const size_t h_n = static_cast<size_t>(T) * d->H_l;
-    const __nv_bfloat16* hi = BF(d->xp_h) + static_cast<size_t>(t0) * d->H_l;
+    const size_t h_n = static_cast<size_t>(T) * d->cfg.hidden;
+    const __nv_bfloat16* hi = BF(d->xp_h) + static_cast<size_t>(t0) * d->cfg.hidden;
     const csdr_segment* seg = d->lm_head.use();
     const XPlanesView xp{hi, hi + h_n};
     const WideDx w = launch_wide_project(d->ctx, &seg, 1, xp, n, base + d->sum_pad);
-    if (d->P > 1) {
-        if (!summed) sum_over_ranks(d, base, T);
-        sum_over_ranks(d, w.base, w.floats);
-    }
     const TokenScale ts{base + t0, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
     const WideOut out{d->P > 1 ? F(d->logits_l) : F(d->logits), nullptr, nullptr};
     launch_wide_gather(d->ctx, &seg, 1, w, n, &out, CSDR_LAYOUT_TOKEN_MAJOR, ts);
@@ -486,15 +477,15 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         d->QD_l = QD / d->P;
         d->KVD_l = KVD / d->P;
         d->I_l = c.inter / d->P;
-        d->H_l = H / d->P;
+        d->H_l = H;   // the residual stream is replicated on every rank
         d->V_l = c.vocab / d->P;
-        d->emb = load_linear(d.get(), "token_embd.weight", c.vocab, H, false, true);
+        d->emb = load_linear(d.get(), "token_embd.weight", c.vocab, H, false, false);
         {
             csdr_segment_header h{};
             const char* head = csdr_archive_find(ar, "output.weight", &h) == CSDR_OK ? "output.weight"
                                : csdr_archive_find(ar, "lm_head.weight", &h) == CSDR_OK ? "lm_head.weight"
                                                                                         : "token_embd.weight";
-            d->lm_head = load_linear(d.get(), head, c.vocab, H, true, true);
+            d->lm_head = load_linear(d.get(), head, c.vocab, H, true, false);
         }
         d->out_norm = load_vector(d.get(), "output_norm.weight", H);
         d->layers.resize(c.n_layers);
@@ -503,13 +494,13 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
             Layer& L = d->layers[i];
             L.attn_norm = load_vector(d.get(), p + "attn_norm.weight", H);
             L.ffn_norm = load_vector(d.get(), p + "ffn_norm.weight", H);
-            L.q = load_linear(d.get(), p + "attn_q.weight", QD, H, true, true);
-            L.k = load_linear(d.get(), p + "attn_k.weight", KVD, H, true, true);
-            L.v = load_linear(d.get(), p + "attn_v.weight", KVD, H, true, true);
-            L.o = load_linear(d.get(), p + "attn_output.weight", H, QD, true, true);
-            L.gate = load_linear(d.get(), p + "ffn_gate.weight", c.inter, H, true, true);
-            L.up = load_linear(d.get(), p + "ffn_up.weight", c.inter, H, true, true);
-            L.down = load_linear(d.get(), p + "ffn_down.weight", H, c.inter, true, true);
+            L.q = load_linear(d.get(), p + "attn_q.weight", QD, H, true, false);
+            L.k = load_linear(d.get(), p + "attn_k.weight", KVD, H, true, false);
+            L.v = load_linear(d.get(), p + "attn_v.weight", KVD, H, true, false);
+            L.o = load_linear(d.get(), p + "attn_output.weight", H, QD, false, true);
+            L.gate = load_linear(d.get(), p + "ffn_gate.weight", c.inter, H, true, false);
+            L.up = load_linear(d.get(), p + "ffn_up.weight", c.inter, H, true, false);
+            L.down = load_linear(d.get(), p + "ffn_down.weight", H, c.inter, false, true);
         }
         csdr_context* ctx = d->ctx;
         d->T_max = std::max(c.max_seq, c.max_batch);
@@ -585,7 +576,6 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
             CSDR_CUDA(cudaMemsetAsync(d->xch_region->ptr, 0, d->xch_region->bytes, ctx->stream));
         }
         if (d->P > 1) {
-            d->normed_l = dev_alloc(ctx, T * d->H_l * 4);
             d->logits_l = dev_alloc(ctx, static_cast<size_t>(c.max_batch) * d->V_l * 4);
             d->staged = dev_alloc(ctx, std::max<size_t>(T * H, static_cast<size_t>(c.max_batch) * c.vocab) * 4);
         }
@@ -637,6 +627,14 @@ int csdr_decoder_exchange_import(csdr_decoder* d, const void* handles, size_t n_
         x.status = d->ctx->status_word;
         x.ranks = d->P;
         d->xch = x;
+        // measured on B200s: at 2 ranks ncclAllReduce of a 32 KB block is ~4 us quicker than the
+        // fused exchange (4.40 vs 4.64 ms per step), at 8 ranks the fused exchange wins by a
+        // third; the environment overrides the default
+        d->xch_use = d->P > 2;
+        if (const char* e = std::getenv("CSDR_TP_EXCHANGE")) {
+            if (std::string(e) == "peer") d->xch_use = true;
+            else if (std::string(e) == "nccl") d->xch_use = false;
+        }
     });
 }
 
@@ -697,7 +695,7 @@ int csdr_decoder_forward(csdr_decoder* d, uint32_t seq, const int32_t* tokens, s
                                       cudaMemcpyDeviceToHost, ctx->stream));
         }
         if (logits_out) {
-            run_logits(d, T, T - 1, 1, hidden_out != nullptr);
+            run_logits(d, T, T - 1, 1);
             CSDR_CUDA(cudaMemcpyAsync(logits_out, d->logits->ptr, static_cast<size_t>(c.vocab) * 4,
                                       cudaMemcpyDeviceToHost, ctx->stream));
         }
@@ -723,7 +721,7 @@ int csdr_decoder_step_device_async(csdr_decoder* d, const int32_t* tokens_dev, s
         op_step_positions(ctx, I32(d->pos_dev), B, I32(d->seq_of), I32(d->pos_of));
         embed(d, B);
         run_blocks(d, B);
-        run_logits(d, B, 0, B, false);
+        run_logits(d, B, 0, B);
         op_argmax(ctx, F(d->logits), B, c.vocab, next_dev);
         for (size_t b = 0; b < batch; ++b) ++d->pos_host[b];
     });

@@ -432,9 +432,11 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
             const float v = __ldcg(p.xch_sums + tid);
             for (uint32_t r = 0; r < p.xch_ranks; ++r) p.xch_slots[r][xslot + tid] = v;
         }
-        __threadfence_system();           // this thread's peer stores are visible system-wide ...
-        __syncthreads();                  // ... for all threads of the CTA before it is counted
+        // one system-scope fence per CTA: the barrier orders every thread's peer stores before
+        // thread 0's fence (fences are cumulative), and the fence before the count
+        __syncthreads();
         if (tid == 0) {
+            __threadfence_system();
             const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
             if (atomicAdd(p.xch_done, 1u) == total - 1u) {
                 *p.xch_done = 0u;
