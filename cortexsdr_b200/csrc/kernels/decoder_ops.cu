@@ -93,26 +93,48 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_
 // hidden width: the normalisation itself is applied behind the projection, where a
 // tensor-parallel rank has the sums of all slices (rms_norm, api/cortex_sdk.cpp:1208-1232, split
 // in two).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 scale_sumsq_planes_kernel(const float* __restrict__ x, const float* __restrict__ w, uint32_t H,
                           __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
                           float* __restrict__ sumsq) {
     pdl_enter();
-    __shared__ float red[8];
+    __shared__ float red[32];
     const size_t o = static_cast<size_t>(blockIdx.x) * H;
     float ss = 0.0f;
-    for (uint32_t i = threadIdx.x; i < H; i += 256) {
-        const float v = x[o + i];
-        ss = fmaf(v, v, ss);
-        store_planes(hi, lo, o + i, v * w[i]);
+    if ((H & 3u) == 0) {
+        // four elements per thread and pass: 128-bit loads, 64-bit plane stores
+        const float4* x4 = reinterpret_cast<const float4*>(x + o);
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        uint2* hi2 = reinterpret_cast<uint2*>(hi + o);
+        uint2* lo2 = reinterpret_cast<uint2*>(lo + o);
+        for (uint32_t i = threadIdx.x; i < H / 4u; i += blockDim.x) {
+            const float4 v = x4[i], ww = w4[i];
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            const float p[4] = {v.x * ww.x, v.y * ww.y, v.z * ww.z, v.w * ww.w};
+            __nv_bfloat16 h[4], l[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                h[j] = __float2bfloat16_rn(p[j]);
+                l[j] = __float2bfloat16_rn(p[j] - __bfloat162float(h[j]));
+            }
+            hi2[i] = make_uint2(static_cast<uint32_t>(__bfloat16_as_ushort(h[0])) | (static_cast<uint32_t>(__bfloat16_as_ushort(h[1])) << 16),
+                                static_cast<uint32_t>(__bfloat16_as_ushort(h[2])) | (static_cast<uint32_t>(__bfloat16_as_ushort(h[3])) << 16));
+            lo2[i] = make_uint2(static_cast<uint32_t>(__bfloat16_as_ushort(l[0])) | (static_cast<uint32_t>(__bfloat16_as_ushort(l[1])) << 16),
+                                static_cast<uint32_t>(__bfloat16_as_ushort(l[2])) | (static_cast<uint32_t>(__bfloat16_as_ushort(l[3])) << 16));
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = x[o + i];
+            ss = fmaf(v, v, ss);
+            store_planes(hi, lo, o + i, v * w[i]);
+        }
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     if (threadIdx.x == 0) {
         float t = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) t += red[i];
+        for (uint32_t i = 0; i < (blockDim.x + 31u) / 32u; ++i) t += red[i];
         sumsq[blockIdx.x] = t;
     }
 }
@@ -463,7 +485,8 @@ void op_rmsnorm_planes(csdr_context* ctx, const float* x, const float* w, uint32
 void op_scale_sumsq_planes(csdr_context* ctx, const float* x, const float* w, uint32_t T, uint32_t H,
                            __nv_bfloat16* hi, __nv_bfloat16* lo, float* sumsq) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    launch_pdl(ctx, scale_sumsq_planes_kernel, dim3(T), dim3(256), x, w, H, hi, lo, sumsq);
+    // few tokens: a wide block per token keeps the pass short; many tokens: the grid already fills the GPU
+    launch_pdl(ctx, scale_sumsq_planes_kernel, dim3(T), dim3(T <= 64u ? 1024u : 256u), x, w, H, hi, lo, sumsq);
     ls.done("scale_sumsq_planes_kernel");
 }
 

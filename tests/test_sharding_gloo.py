@@ -2,9 +2,10 @@
 the code stream of a compressed weight, runs the oracle on it, and the rank-major
 all-gather followed by the shard-interleave reproduces the unsharded result. This is the
 index arithmetic csdr_segment_shard_rows and the decoder's logits rejoin rely on. A second case
-covers the decoder's tensor-parallel block arithmetic: dictionary columns and hidden width
-sliced per rank, partial projections and per-token sums of squares added up with one all-reduce,
-RMS normalisation applied behind the projection, each rank gathering its own output rows."""
+covers the column-sharded projection (csdr_segment_shard_cols; the decoder's output and down
+projections) in its most general form: dictionary columns and input width sliced per rank,
+partial projections and per-token sums of squares added up with one all-reduce, RMS
+normalisation applied behind the projection, each rank gathering its own output rows."""
 import os
 import struct
 import sys
