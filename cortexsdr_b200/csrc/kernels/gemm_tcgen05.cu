@@ -22,6 +22,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "../internal.hpp"
 #include "gemm_tcgen05.hpp"
@@ -745,8 +746,8 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
 template <int MT>
 void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t total_rows, uint32_t max_k, uint32_t max_slots) {
     const bool pair = g.act_hi != nullptr;
-    // about two CTAs per SM over the whole group (a pair walks the rows of one member)
-    const uint32_t want = 2u * static_cast<uint32_t>(ctx->sm_count);
+    // about three CTAs per SM over the whole group (a pair walks the rows of one member)
+    const uint32_t want = 3u * static_cast<uint32_t>(ctx->sm_count);   // measured best of 1..4 on the 7B-shaped decode
     const uint32_t rows_all = pair ? g.m[0].R : total_rows;
     const uint32_t rows_per_cta = std::max(kGroupThreads / MT, (rows_all + want - 1u) / want);
     uint32_t ctas = 0;
