@@ -140,6 +140,15 @@ bool wait_host_word(const volatile uint32_t* word, uint32_t seq) {
 }  // namespace csdr_hostio
 using namespace csdr_hostio;
 
+void csdr_context::opt_in_smem(const void* kernel, size_t bytes) {
+    if (bytes <= 48u * 1024u) return;
+    size_t& have = smem_optins[kernel];
+    if (bytes > have) {
+        CSDR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+        have = bytes;
+    }
+}
+
 void* csdr_context::pinned_get(size_t bytes) {
     if (pinned_bytes < bytes) {
         CSDR_CUDA(cudaStreamSynchronize(stream));

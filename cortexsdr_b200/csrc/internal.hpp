@@ -113,6 +113,14 @@ struct csdr_context {
     bool tensor_cores = true;   // CSDR_TENSOR_CORES=0 keeps wide batches on the CUDA-core kernels
     bool tma = true;            // CSDR_TMA=0 keeps the register-fed tensor-core kernel
     size_t tc_min_batch = 8;    // CSDR_TC_MIN_BATCH: smallest batch sent to the tcgen05 path
+    // Per-device launch facts, remembered per context (function attributes and occupancy belong
+    // to a device; a process may hold contexts on several).
+    std::unordered_map<const void*, size_t> smem_optins;              // kernel -> dynamic smem opted into
+    void opt_in_smem(const void* kernel, size_t bytes);               // raises the opt-in when bytes needs it
+    std::unordered_map<const void*, std::pair<size_t, int>> occupancy; // kernel -> (smem asked, CTAs per SM)
+    bool tma_attrs_set = false;
+    int tma_max_cluster = 8;
+    std::unordered_map<uint64_t, int> cluster_fit;                    // (cluster size, smem) -> clusters resident
     uint64_t launches_by_class[csdr::KC_COUNT] = {};
     // When on, every launch is bracketed by two events on the stream (profile_read resolves them).
     bool profiling = false;

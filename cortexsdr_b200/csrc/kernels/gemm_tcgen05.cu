@@ -760,11 +760,7 @@ void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t tot
     g.region_bytes = static_cast<uint32_t>(static_cast<size_t>(g.code_cap16) * 16u + 64u * 4u + static_cast<size_t>(max_k) * MT * 4u);
     const size_t smem = static_cast<size_t>(g.region_bytes) * (pair ? 2u : 1u);
     auto kern = pair ? hsdr_gather_group_kernel<MT, true> : hsdr_gather_group_kernel<MT, false>;
-    static size_t smem_set[2] = {0, 0};
-    if (smem > 48u * 1024u && smem > smem_set[pair]) {
-        CSDR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        smem_set[pair] = smem;
-    }
+    ctx->opt_in_smem(reinterpret_cast<const void*>(kern), smem);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(ctas, 1, 1);
     cfg.blockDim = dim3(kGroupThreads, 1, 1);
@@ -784,12 +780,7 @@ void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float*
                         const float* residual, const TokenScale& ts) {
     const Geometry& g = seg->g;
     const size_t smem = gather_wide_smem(g.n_atoms);
-    static size_t smem_set = 0;
-    if (smem > 48u * 1024u && smem > smem_set) {
-        CSDR_CUDA(cudaFuncSetAttribute(hsdr_gather_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem)));
-        smem_set = smem;
-    }
+    ctx->opt_in_smem(reinterpret_cast<const void*>(hsdr_gather_wide_kernel), smem);
     // one CTA per SM (the slice fills most of its shared memory): split the rows so that
     // slices x row runs covers the GPU once, in runs that are multiples of eight rows
     const uint32_t slices = (M + kWideTokens - 1u) / kWideTokens;
@@ -980,12 +971,7 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
     p.out = part;
     if (!use_tma) {
         const size_t smem = 2u * (2u * kATileBytes + 2u * static_cast<size_t>(N) * 128u) + 1024u;
-        static size_t smem_set = 0;
-        if (smem > smem_set) {
-            CSDR_CUDA(cudaFuncSetAttribute(hsdr_dx_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem)));
-            smem_set = smem;
-        }
+        ctx->opt_in_smem(reinterpret_cast<const void*>(hsdr_dx_tcgen05_kernel), smem);
         LaunchScope ls(ctx, KC_GEMM);
         hsdr_dx_tcgen05_kernel<<<dim3(atom_tiles, tok_tiles, n_split), kTcThreads, smem, ctx->stream>>>(p);
         ls.done("hsdr_dx_tcgen05_kernel");

@@ -600,18 +600,16 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     const uint32_t n_kb = (cols + kBlockK - 1u) / kBlockK;
     const uint32_t stage_bytes = 2u * kATile + (has_lo ? 2u : 1u) * N * 128u;
 
-    static bool attrs_set = false;
-    static int max_cluster = 8;
     const size_t smem_max = ctx->smem_optin - 2048u;   // static barriers and alignment slack
-    if (!attrs_set) {
-        CSDR_CUDA(cudaFuncSetAttribute(hsdr_dx_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem_max)));
+    if (!ctx->tma_attrs_set) {
+        ctx->opt_in_smem(reinterpret_cast<const void*>(hsdr_dx_tma_kernel), smem_max);
         if (cudaFuncSetAttribute(hsdr_dx_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess)
-            max_cluster = 16;
+            ctx->tma_max_cluster = 16;
         else
             (void)cudaGetLastError();
-        attrs_set = true;
+        ctx->tma_attrs_set = true;
     }
+    const int max_cluster = ctx->tma_max_cluster;
     uint32_t stages = std::min<uint32_t>(kMaxStages, static_cast<uint32_t>((smem_max - 1024u) / stage_bytes));
     stages = std::max(1u, stages);
     const size_t smem = std::max<size_t>(static_cast<size_t>(stages) * stage_bytes,
@@ -634,7 +632,7 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     // launch is resident at once (the hardware places a cluster inside one GPC, so the answer
     // depends on the cluster size; asked once per (size, shared memory) and remembered).
     const uint32_t tiles = atom_tiles * tok_tiles;
-    static std::unordered_map<uint64_t, int> fit;      // (ranks, smem) -> clusters resident at once
+    std::unordered_map<uint64_t, int>& fit = ctx->cluster_fit;   // (ranks, smem) -> clusters resident at once
     uint32_t ranks = 1;
     for (uint32_t r = std::min<uint32_t>({static_cast<uint32_t>(max_cluster), n_kb,
                                           std::max(1u, static_cast<uint32_t>(ctx->sm_count) / tiles)});

@@ -405,17 +405,13 @@ void launch_t(csdr_context* ctx, FusedParams& p, uint32_t max_k, bool pdl) {
     const uint32_t want_gather = p.gather_ctas;
     const size_t smem = plan_for(std::min<uint32_t>(want_gather, static_cast<uint32_t>(ctx->sm_count)));
     if (smem > ctx->smem_optin) throw Error(CSDR_ERR_LIMIT, "fused GEMV: shared memory need exceeds the device limit");
-    static size_t smem_set = 0;
-    static int occ_cached = 0;
-    static size_t occ_smem = ~static_cast<size_t>(0);
-    if (smem > 48 * 1024 && smem > smem_set) {
-        CSDR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        smem_set = smem;
+    ctx->opt_in_smem(reinterpret_cast<const void*>(kern), smem);
+    std::pair<size_t, int>& occ = ctx->occupancy[reinterpret_cast<const void*>(kern)];
+    if (occ.second == 0 || occ.first != smem) {
+        CSDR_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ.second, kern, kThreads, smem));
+        occ.first = smem;
     }
-    if (occ_smem != smem) {
-        CSDR_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_cached, kern, kThreads, smem));
-        occ_smem = smem;
-    }
+    const int occ_cached = occ.second;
     if (occ_cached < 1) throw Error(CSDR_ERR_LIMIT, "fused GEMV does not fit on an SM");
     // Every CTA must be resident for the barrier: at most what one otherwise idle GPU holds.
     const uint32_t grid = static_cast<uint32_t>(ctx->sm_count) * static_cast<uint32_t>(std::min(occ_cached, 2));
