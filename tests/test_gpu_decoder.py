@@ -140,3 +140,17 @@ def test_decoder_limits_and_errors(ctx, model):
         cs.Decoder(ld, **dict(CFG, hidden=64), max_seq=8)
     with pytest.raises(RuntimeError, match="not found|not in archive"):
         cs.Decoder(ld, **dict(CFG, n_layers=3), max_seq=8)
+
+
+def test_exchange_needs_tensor_parallel_ranks(ctx, model):
+    """A single-rank decoder has no exchange region: export and import say so instead of
+    handing out a handle nobody could use."""
+    import ctypes as C
+    path, _ = model
+    dec = make_decoder(path, ctx)
+    buf = C.create_string_buffer(64)
+    lib = ctx._lib
+    assert lib.csdr_decoder_exchange_export(dec._h, buf) == cs._lib.ERR_UNSUPPORTED
+    assert lib.csdr_decoder_exchange_import(dec._h, buf.raw, 1) == cs._lib.ERR_UNSUPPORTED
+    assert lib.csdr_decoder_exchange_import(dec._h, buf.raw, 2) == cs._lib.ERR_INVALID_ARG
+    assert b"exchange" in lib.csdr_last_error() or b"handle" in lib.csdr_last_error()
