@@ -126,6 +126,12 @@ def test_tensor_core_block_loop_matches_oracle(ctx, oracle, model_tc):
         _, want = oracle_forward(oracle, weights, np.append(p_, new[s_]))
         assert np.abs(lg[s_] - want).max() < LOGIT_TOL
         assert int(nxt[s_]) == int(want.argmax())
+    # a second step reads the cache rows the first one filed
+    nxt2, lg2 = dec.step(nxt, want_logits=True)
+    for s_, p_ in enumerate(prompts):
+        _, want = oracle_forward(oracle, weights, np.concatenate([p_, [new[s_]], [nxt[s_]]]))
+        assert np.abs(lg2[s_] - want).max() < LOGIT_TOL
+        assert int(nxt2[s_]) == int(want.argmax())
 
 
 def test_decoder_limits_and_errors(ctx, model):
