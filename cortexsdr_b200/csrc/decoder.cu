@@ -8,6 +8,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <cctype>
 #include <cstdlib>
 #include <cstring>
 #include <initializer_list>
@@ -189,8 +190,34 @@ Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint
         if (d->P > 1)
             throw Error(CSDR_ERR_UNSUPPORTED, "decoder: tensor-parallel decoding needs HSDR-encoded linears ('" + name +
                                                   "' is stored raw)");
-        std::vector<float> w = load_raw(d->ar, name, static_cast<size_t>(rows) * cols);
-        l.raw = upload(d->ctx, w.data(), static_cast<size_t>(rows) * cols * 4);
+        // stored as it came from the model file: fp32, or a source dtype (f16, bf16, q4_0, q8_0,
+        // q4_k, q5_k, q6_k) that is widened to fp32 on the device once, with the kernels of
+        // dequantizeSegmentToFP32 (strategies/HierarchicalSDRStrategy.cpp:713-989)
+        std::string fmt = h.data_format ? h.data_format : "";
+        for (char& ch : fmt) ch = static_cast<char>(std::tolower(static_cast<unsigned char>(ch)));
+        const size_t want = static_cast<size_t>(rows) * cols;
+        if (fmt.empty() || fmt == "f32" || fmt == "fp32" || fmt == "float32") {
+            std::vector<float> w = load_raw(d->ar, name, want);
+            l.raw = upload(d->ctx, w.data(), want * 4);
+        } else {
+            const int id = dequant_format_id(fmt == "fp16" || fmt == "float16" || fmt == "half" ? "f16"
+                                             : fmt == "bfloat16"                                ? "bf16"
+                                                                                                : fmt.c_str());
+            if (id < 0)
+                throw Error(CSDR_ERR_UNSUPPORTED, "decoder: tensor '" + name + "' is stored as '" + fmt +
+                                                      "', which this library does not widen");
+            size_t nbytes = 0;
+            int rc2 = csdr_archive_load_segment(d->ar, name.c_str(), nullptr, 0, &nbytes);
+            if (rc2 != CSDR_OK && rc2 != CSDR_ERR_BUFFER) rethrow_last(rc2);
+            std::vector<uint8_t> bytes(nbytes);
+            rethrow_last(csdr_archive_load_segment(d->ar, name.c_str(), bytes.data(), bytes.size(), &nbytes));
+            if (dequant_output_count(id, nbytes) < want)
+                throw Error(CSDR_ERR_GEOMETRY, "tensor '" + name + "' is smaller than the decoder config needs");
+            DevPtr packed = upload(d->ctx, bytes.data(), nbytes);
+            l.raw = dev_alloc(d->ctx, dequant_output_count(id, nbytes) * 4);
+            launch_dequantize(d->ctx, id, static_cast<const uint8_t*>(packed->ptr), nbytes, dequant_output_count(id, nbytes),
+                              1.0f, 0.0f, F(l.raw));
+        }
         CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
     } else {
         throw Error(CSDR_ERR_UNSUPPORTED, "decoder: tensor '" + name + "' uses a strategy this library does not decode");

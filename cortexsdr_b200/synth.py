@@ -74,22 +74,62 @@ def hsdr_segment(name: str, rows: int, cols: int, seg_type: int = SEG_WEIGHTS_FP
                 dims=(rows, cols), original_size=rows * cols * 4, layer_index=layer_index)
 
 
-def raw_segment(name: str, array: np.ndarray, seg_type: int = SEG_LAYER_NORM, layer_index: int = 0) -> dict:
-    a = np.ascontiguousarray(array, dtype=np.float32)
-    return dict(name=name, payload=a.tobytes(), strategy_id=0, original_type=seg_type, dims=a.shape,
-                original_size=a.nbytes, layer_index=layer_index, layer_type="" if a.ndim < 2 else "LINEAR")
+def raw_segment(name: str, array: np.ndarray, seg_type: int = SEG_LAYER_NORM, layer_index: int = 0,
+                data_format: str = "f32", dims=None) -> dict:
+    """A stored-raw segment (strategy 0). With data_format other than "f32", `array` holds the
+    packed bytes of that source dtype (f16, bf16, q8_0, q4_k, ...) and `dims` the logical shape."""
+    if data_format == "f32":
+        a = np.ascontiguousarray(array, dtype=np.float32)
+        dims = a.shape
+    else:
+        a = np.ascontiguousarray(array).view(np.uint8).reshape(-1)
+    return dict(name=name, payload=a.tobytes(), strategy_id=0, original_type=seg_type, dims=tuple(dims),
+                original_size=a.nbytes, layer_index=layer_index, data_format=data_format,
+                layer_type="" if len(dims) < 2 else "LINEAR")
+
+
+def pack_source_dtype(w: np.ndarray, fmt: str) -> np.ndarray:
+    """fp32 values -> packed bytes of a source dtype the reference widens with
+    dequantizeSegmentToFP32: "f16", "bf16" (round to nearest even) or "q8_0" (blocks of 32:
+    fp16 scale d = max|x| / 127, then 32 int8 quants)."""
+    w = np.ascontiguousarray(w, np.float32).reshape(-1)
+    if fmt == "f16":
+        return w.astype(np.float16).view(np.uint8)
+    if fmt == "bf16":
+        u = w.view(np.uint32).astype(np.uint64)
+        u = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+        return u.astype(np.uint16).view(np.uint8)
+    if fmt == "q8_0":
+        b = w.reshape(-1, 32)
+        d = (np.abs(b).max(1) / 127.0).astype(np.float16)
+        q = np.where(d[:, None] > 0, np.rint(b / np.maximum(d.astype(np.float32), 1e-30)[:, None]), 0)
+        out = np.empty((b.shape[0], 34), np.uint8)
+        out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+        out[:, 2:] = np.clip(q, -127, 127).astype(np.int8).view(np.uint8)
+        return out.reshape(-1)
+    raise ValueError(f"no packer for source dtype {fmt!r}")
 
 
 def decoder_archive(path: str, *, n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab, seed=100,
-                    geometry="row", n_atoms=512, k=8, kv_atoms=None) -> None:
+                    geometry="row", n_atoms=512, k=8, kv_atoms=None, raw=None) -> None:
     """A decoder-shaped .sdr with the reference's GGUF-style tensor names
-    (api/cortex_sdk.cpp:456-524): every linear an HSDR segment, norm vectors stored raw."""
+    (api/cortex_sdk.cpp:456-524): every linear an HSDR segment, norm vectors stored raw.
+    `raw` maps tensor names to a source dtype ("f32", "f16", "bf16", "q8_0"): those linears are
+    stored uncompressed (strategy 0) in that dtype instead, as a converter leaves protected or
+    unsuitable tensors."""
     segs, sd = [], seed
     kw = dict(n_atoms=n_atoms, k=k)
+    raw = raw or {}
 
     def lin(name, r, c, t, li, atoms=None):
         nonlocal sd
         sd += 1
+        if name in raw:
+            w = np.random.default_rng(sd).normal(0, 0.02, (r, c)).astype(np.float32)
+            fmt = raw[name]
+            segs.append(raw_segment(name, w if fmt == "f32" else pack_source_dtype(w, fmt), t, li, data_format=fmt,
+                                    dims=(r, c)))
+            return
         a = dict(kw, n_atoms=atoms or n_atoms)
         if geometry != "row":
             a.update(tile_rows=geometry[0], tile_cols=geometry[1])

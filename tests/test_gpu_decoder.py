@@ -17,11 +17,28 @@ LOGIT_TOL = 2e-2
 CFG = dict(n_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=32, inter=256, vocab=300)
 
 
-def _build_model(tmp_path_factory, oracle, tag, **atoms):
+def _build_model(tmp_path_factory, oracle, tag, raw_formats=None, **atoms):
     path = str(tmp_path_factory.mktemp("dec") / f"{tag}.sdr")
-    synth.decoder_archive(path, **CFG, k=3, seed=7, **atoms)
+    raw_formats = raw_formats or {}
+    synth.decoder_archive(path, **CFG, k=3, seed=7, raw=raw_formats, **atoms)
     ld = cs.SDRModelLoader(path, index_only=True)
-    dense = lambda n: oracle.decompress(ld.loadCompressedBytesByName(n))
+    shapes = {"token_embd.weight": (CFG["vocab"], CFG["hidden"]), "output.weight": (CFG["vocab"], CFG["hidden"])}
+
+    def dense(n):
+        if n not in raw_formats:
+            return oracle.decompress(ld.loadCompressedBytesByName(n))
+        data = ld.loadSegmentByName(n)                       # stored raw: widen like the reference does
+        fmt = raw_formats[n]
+        w = data.view(np.float32) if fmt == "f32" else oracle.dequantize(fmt, data)
+        if n in shapes:
+            return w.reshape(shapes[n])
+        r, c = {"attn_q": (CFG["q_heads"] * CFG["head_dim"], CFG["hidden"]),
+                "attn_k": (CFG["kv_heads"] * CFG["head_dim"], CFG["hidden"]),
+                "attn_v": (CFG["kv_heads"] * CFG["head_dim"], CFG["hidden"]),
+                "attn_output": (CFG["hidden"], CFG["q_heads"] * CFG["head_dim"]),
+                "ffn_gate": (CFG["inter"], CFG["hidden"]), "ffn_up": (CFG["inter"], CFG["hidden"]),
+                "ffn_down": (CFG["hidden"], CFG["inter"])}[n.split(".")[2]]
+        return w.reshape(r, c)
     raw = lambda n: ld.loadSegmentByName(n).view(np.float32)
     blocks = []
     for i in range(CFG["n_layers"]):
@@ -48,6 +65,16 @@ def model_tc(tmp_path_factory, oracle):
     return _build_model(tmp_path_factory, oracle, "tc", n_atoms=128, kv_atoms=128)
 
 
+@pytest.fixture(scope="module")
+def model_raw(tmp_path_factory, oracle):
+    """Some tensors stored uncompressed in a source dtype, as a converter leaves protected ones:
+    the embedding as f16, the head as q8_0, one block's down projection as bf16, another's
+    query projection as plain f32."""
+    return _build_model(tmp_path_factory, oracle, "raw", n_atoms=32, kv_atoms=16,
+                        raw_formats={"token_embd.weight": "f16", "output.weight": "q8_0",
+                                     "blk.0.ffn_down.weight": "bf16", "blk.1.attn_q.weight": "f32"})
+
+
 def oracle_forward(oracle, weights, tokens, eps=1e-6, theta=1e6):
     cfg = dict(CFG, eps=eps, theta=theta)
     return oracle.decoder_forward(cfg, weights["tok"], weights["blocks"], weights["out_norm"], weights["head"], tokens)
@@ -67,6 +94,20 @@ def test_prefill_matches_oracle(ctx, oracle, model):
     assert np.abs(g_hid - hid).max() < 1e-3
     assert np.abs(g_logits - logits).max() < LOGIT_TOL
     assert int(g_logits.argmax()) == int(logits.argmax())
+
+
+def test_stored_raw_source_dtypes_are_widened_on_the_device(ctx, oracle, model_raw):
+    path, weights = model_raw
+    tokens = np.random.default_rng(5).integers(0, CFG["vocab"], 10)
+    hid, logits = oracle_forward(oracle, weights, tokens)
+    dec = make_decoder(path, ctx)
+    g_logits, g_hid = dec.forward(tokens, want_hidden=True)
+    assert np.abs(g_hid - hid).max() < 1e-3
+    assert np.abs(g_logits - logits).max() < LOGIT_TOL
+    assert int(g_logits.argmax()) == int(logits.argmax())
+    nxt, lg = dec.step([int(g_logits.argmax())], want_logits=True)
+    _, want = oracle_forward(oracle, weights, np.append(tokens, int(g_logits.argmax())))
+    assert np.abs(lg[0] - want).max() < LOGIT_TOL and int(nxt[0]) == int(want.argmax())
 
 
 def test_kv_cache_equals_recompute(ctx, oracle, model):
