@@ -642,6 +642,15 @@ class Decoder:
     def reset(self):
         _check(self.ctx._lib.csdr_decoder_reset(self._h))
 
+    def selection_policy(self, enable: bool = True, temperature: float = 1.0):
+        """The reference's select_best_from_logits for the steps (temperature scale, 1.5 off for
+        tokens the sequence has produced, first maximum) instead of plain argmax."""
+        _check(self.ctx._lib.csdr_decoder_selection_policy(self._h, 1 if enable else 0, temperature))
+
+    def note_generated(self, tokens, seq: int = 0):
+        t = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        _check(self.ctx._lib.csdr_decoder_note_generated(self._h, seq, t.ctypes.data_as(C.POINTER(C.c_int32)), t.size))
+
     def seek(self, seq: int, position: int):
         _check(self.ctx._lib.csdr_decoder_seek(self._h, seq, position))
 

@@ -114,6 +114,8 @@ SIGNATURES = {
     "csdr_decoder_create": (C.c_int, [_P, C.POINTER(DecoderConfig), C.POINTER(_P)]),
     "csdr_decoder_destroy": (C.c_int, [_P]),
     "csdr_decoder_reset": (C.c_int, [_P]),
+    "csdr_decoder_selection_policy": (C.c_int, [_P, C.c_int, C.c_float]),
+    "csdr_decoder_note_generated": (C.c_int, [_P, C.c_uint32, C.POINTER(C.c_int32), _SZ]),
     "csdr_decoder_exchange_export": (C.c_int, [_P, _P]),
     "csdr_decoder_exchange_import": (C.c_int, [_P, _P, _SZ]),
     "csdr_decoder_seek": (C.c_int, [_P, C.c_uint32, C.c_uint32]),

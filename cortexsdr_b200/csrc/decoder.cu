@@ -96,6 +96,12 @@ struct csdr_decoder {
     DevPtr kcache, vcache;  // [layer][seq][pos][kv head (local)][head_dim]
     size_t cache_layer_stride = 0;
     std::vector<int32_t> pos_host;
+    // token selection of the reference's generation loop (off: plain argmax): temperature and a
+    // bitmap of the tokens each sequence has produced, [max_batch][seen_words]
+    bool policy = false;
+    float temperature = 1.0f;
+    DevPtr seen;
+    uint32_t seen_words = 0;
     DevPtr pos_dev, tokens_dev, seq_of, pos_of, next_dev;
     DevPtr hidden, normed, q, k, v, att, proj, gate, up, staged, logits, logits_l;
     // projections of a group between its two launches, behind a block of per-token sums of
@@ -679,6 +685,34 @@ int csdr_decoder_reset(csdr_decoder* d) {
         need(d);
         std::fill(d->pos_host.begin(), d->pos_host.end(), 0);
         CSDR_CUDA(cudaMemsetAsync(d->pos_dev->ptr, 0, d->pos_dev->bytes, d->ctx->stream));
+        if (d->seen) CSDR_CUDA(cudaMemsetAsync(d->seen->ptr, 0, d->seen->bytes, d->ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
+    });
+}
+
+int csdr_decoder_selection_policy(csdr_decoder* d, int enable, float temperature) {
+    return guard([&] {
+        need(d);
+        d->policy = enable != 0;
+        d->temperature = temperature;
+        if (d->policy && !d->seen) {
+            d->seen_words = (d->cfg.vocab + 31u) / 32u;
+            d->seen = dev_alloc(d->ctx, static_cast<size_t>(d->cfg.max_batch) * d->seen_words * 4);
+            CSDR_CUDA(cudaMemsetAsync(d->seen->ptr, 0, d->seen->bytes, d->ctx->stream));
+            CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
+        }
+    });
+}
+
+int csdr_decoder_note_generated(csdr_decoder* d, uint32_t seq, const int32_t* tokens, size_t n_tokens) {
+    return guard([&] {
+        need(d);
+        if (!d->seen) throw Error(CSDR_ERR_INVALID_ARG, "turn the selection policy on first");
+        if (seq >= d->cfg.max_batch || (!tokens && n_tokens)) throw Error(CSDR_ERR_INVALID_ARG, "bad sequence or null tokens");
+        if (!n_tokens) return;
+        DevPtr t = upload(d->ctx, tokens, n_tokens * 4);
+        op_mark_seen(d->ctx, static_cast<uint32_t*>(d->seen->ptr) + static_cast<size_t>(seq) * d->seen_words,
+                     static_cast<const int32_t*>(t->ptr), static_cast<uint32_t>(n_tokens), d->cfg.vocab);
         CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
     });
 }
@@ -749,7 +783,11 @@ int csdr_decoder_step_device_async(csdr_decoder* d, const int32_t* tokens_dev, s
         embed(d, B);
         run_blocks(d, B);
         run_logits(d, B, 0, B);
-        op_argmax(ctx, F(d->logits), B, c.vocab, next_dev);
+        if (d->policy)
+            op_select(ctx, F(d->logits), B, c.vocab, next_dev, d->temperature, static_cast<uint32_t*>(d->seen->ptr),
+                      d->seen_words);
+        else
+            op_argmax(ctx, F(d->logits), B, c.vocab, next_dev);
         for (size_t b = 0; b < batch; ++b) ++d->pos_host[b];
     });
 }

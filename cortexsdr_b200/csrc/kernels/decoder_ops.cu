@@ -407,14 +407,24 @@ __global__ void gather_rows_kernel(const float* __restrict__ table, uint32_t n_r
 
 // One CTA per logits row; first maximum wins.
 __global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, uint32_t V, int32_t* __restrict__ out) {
+argmax_kernel(const float* __restrict__ logits, uint32_t V, int32_t* __restrict__ out, float temp_scale,
+              uint32_t* __restrict__ seen, uint32_t seen_words) {
+    // seen == nullptr: plain argmax. Else select_best_from_logits (api/cortex_sdk.cpp:1005-1030):
+    // score = logit * temp_scale, non-finite scores skipped, 1.5 off for tokens the sequence has
+    // produced (bitmap row blockIdx.x), first maximum wins; the pick is recorded in the bitmap.
     __shared__ float bv[32];
     __shared__ int32_t bi[32];
     const float* row = logits + static_cast<size_t>(blockIdx.x) * V;
+    uint32_t* mine = seen ? seen + static_cast<size_t>(blockIdx.x) * seen_words : nullptr;
     float best = -INFINITY;
     int32_t idx = 0x7FFFFFFF;
     for (uint32_t i = threadIdx.x; i < V; i += 1024) {
-        const float v = row[i];
+        float v = row[i];
+        if (mine) {
+            v *= temp_scale;
+            if (!isfinite(v)) continue;
+            if ((mine[i >> 5] >> (i & 31u)) & 1u) v -= 1.5f;
+        }
         if (v > best || (v == best && static_cast<int32_t>(i) < idx)) {
             best = v;
             idx = static_cast<int32_t>(i);
@@ -446,7 +456,20 @@ argmax_kernel(const float* __restrict__ logits, uint32_t V, int32_t* __restrict_
                 idx = oi;
             }
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7FFFFFFF ? 0 : idx;
+        if (threadIdx.x == 0) {
+            // nothing selectable: plain argmax answers token 0, the policy answers -1 like the reference
+            out[blockIdx.x] = idx == 0x7FFFFFFF ? (mine ? -1 : 0) : idx;
+            if (mine && idx != 0x7FFFFFFF) mine[idx >> 5] |= 1u << (idx & 31);
+        }
+    }
+}
+
+// Records tokens chosen outside a step (e.g. from the prefill's logits) for one sequence.
+__global__ void mark_seen_kernel(uint32_t* __restrict__ seen_row, const int32_t* __restrict__ tokens, uint32_t n,
+                                 uint32_t V) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int32_t t = tokens[i];
+        if (t >= 0 && static_cast<uint32_t>(t) < V) atomicOr(seen_row + (t >> 5), 1u << (t & 31));
     }
 }
 
@@ -580,9 +603,24 @@ void op_gather_rows(csdr_context* ctx, const float* table, uint32_t n_rows, uint
     ls.done("gather_rows_kernel");
 }
 
+void op_select(csdr_context* ctx, const float* logits, uint32_t rows, uint32_t V, int32_t* out, float temperature,
+               uint32_t* seen, uint32_t seen_words) {
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    argmax_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, V, out, temperature > 0.0f ? 1.0f / temperature : 1.0f, seen,
+                                                  seen_words);
+    ls.done("argmax_kernel");
+}
+
+void op_mark_seen(csdr_context* ctx, uint32_t* seen_row, const int32_t* tokens_dev, uint32_t n, uint32_t V) {
+    if (!n) return;
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    mark_seen_kernel<<<(n + 255u) / 256u, 256, 0, ctx->stream>>>(seen_row, tokens_dev, n, V);
+    ls.done("mark_seen_kernel");
+}
+
 void op_argmax(csdr_context* ctx, const float* logits, uint32_t rows, uint32_t V, int32_t* out) {
     LaunchScope ls(ctx, KC_DECODER_OP);
-    argmax_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, V, out);
+    argmax_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, V, out, 1.0f, nullptr, 0u);
     ls.done("argmax_kernel");
 }
 

@@ -39,6 +39,13 @@ void op_unshard(csdr_context* ctx, const float* staged, uint32_t P, uint32_t T, 
 void op_gather_rows(csdr_context* ctx, const float* table, uint32_t n_rows, uint32_t H, const int32_t* ids,
                     uint32_t T, float* out);
 void op_argmax(csdr_context* ctx, const float* logits, uint32_t rows, uint32_t V, int32_t* out);
+// The reference's token selection (select_best_from_logits, api/cortex_sdk.cpp:1005-1030) per
+// row: logit / temperature (<= 0: unscaled), non-finite scores skipped, 1.5 off for tokens whose
+// bit is set in the row's bitmap (seen: [rows][seen_words] words), first maximum wins, -1 when
+// nothing is selectable; the pick's bit is set.
+void op_select(csdr_context* ctx, const float* logits, uint32_t rows, uint32_t V, int32_t* out, float temperature,
+               uint32_t* seen, uint32_t seen_words);
+void op_mark_seen(csdr_context* ctx, uint32_t* seen_row, const int32_t* tokens_dev, uint32_t n, uint32_t V);
 void op_step_positions(csdr_context* ctx, int32_t* pos, uint32_t B, int32_t* seq_of, int32_t* pos_of);
 
 }  // namespace csdr

@@ -315,6 +315,16 @@ CSDR_API int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cf
                                  csdr_decoder** out);
 CSDR_API int csdr_decoder_destroy(csdr_decoder* d);
 CSDR_API int csdr_decoder_reset(csdr_decoder* d);
+/* Token selection of the reference's generation loop (select_best_from_logits,
+ * api/cortex_sdk.cpp:1005-1030) for the steps: score = logit / temperature (temperature <= 0:
+ * unscaled), non-finite scores skipped, 1.5 subtracted for tokens the sequence has produced
+ * already, first maximum wins, -1 when nothing is selectable. Off by default (plain argmax).
+ * While it is on every token a step selects is recorded for its sequence; note_generated records
+ * tokens chosen elsewhere (the one picked from the prefill's logits); csdr_decoder_reset forgets
+ * them all. */
+CSDR_API int csdr_decoder_selection_policy(csdr_decoder* d, int enable, float temperature);
+CSDR_API int csdr_decoder_note_generated(csdr_decoder* d, uint32_t seq, const int32_t* tokens,
+                                         size_t n_tokens);
 /* Tensor-parallel ranks (2 to 8, one process per GPU) can sum their partial projections through
  * peer memory instead of NCCL for steps of at most 16 tokens: every rank exports a 64-byte CUDA
  * IPC handle of its exchange region, the host program gathers the handles of all ranks

@@ -215,6 +215,17 @@ class Oracle:
                                C.c_size_t(k.shape[1]), C.c_size_t(hd), _ptr(out))
         return out
 
+    def select_best_from_logits(self, logits, generated, temperature):
+        """generated: iterable of token ids already produced."""
+        lg = np.ascontiguousarray(logits, np.float32)
+        flags = np.zeros(lg.size, np.uint8)
+        for t in generated:
+            if 0 <= int(t) < lg.size:
+                flags[int(t)] = 1
+        self.lib.orc_select_best_from_logits.restype = C.c_int
+        return int(self.lib.orc_select_best_from_logits(_ptr(lg), C.c_size_t(lg.size),
+                                                         flags.ctypes.data_as(C.c_void_p), C.c_float(temperature)))
+
     def decoder_forward(self, cfg: dict, tok_embd, blocks, out_norm, lm_head, tokens):
         """blocks: list of dicts with the nine dense fp32 arrays. Returns (hidden, logits)."""
         c = _DecoderCfg(cfg["n_layers"], cfg["hidden"], cfg["q_heads"], cfg["kv_heads"],

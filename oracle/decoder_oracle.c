@@ -158,3 +158,23 @@ int orc_decoder_forward(const orc_decoder_cfg* c, const float* tok_embd,
     free(hidden); free(normed); free(q); free(k); free(v); free(att); free(proj); free(gate); free(up);
     return 0;
 }
+
+/* select_best_from_logits, api/cortex_sdk.cpp:1005-1030 (token_is_repeated :946-948): score =
+ * logit * (temperature > 0 ? 1/temperature : 1); non-finite scores are skipped; 1.5 is taken off
+ * tokens already generated (generated[t] != 0); the first strictly greater score wins; -1 when no
+ * score is finite or the row is empty. */
+int orc_select_best_from_logits(const float* logits, size_t n, const unsigned char* generated, float temperature) {
+    const float temp_scale = temperature > 0.0f ? (1.0f / temperature) : 1.0f;
+    float best_score = -INFINITY;
+    int best_token = -1;
+    for (size_t t = 0; t < n; ++t) {
+        float score = logits[t] * temp_scale;
+        if (!isfinite(score)) continue;
+        if (generated && generated[t]) score -= 1.5f;
+        if (score > best_score) {
+            best_score = score;
+            best_token = (int)t;
+        }
+    }
+    return best_token;
+}

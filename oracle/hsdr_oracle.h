@@ -84,6 +84,7 @@ void orc_rms_norm(const float* in, const float* w, size_t tokens, size_t hidden,
 void orc_rope(float* t, size_t seq, size_t heads, size_t head_dim, float theta, size_t pos0);
 /* api/cortex_sdk.cpp:1245-1256 */
 void orc_silu_mul(const float* gate, const float* up, size_t n, float* out);
+int orc_select_best_from_logits(const float* logits, size_t n, const unsigned char* generated, float temperature);
 /* kernels/attention_kernels.cpp:26-113 + kernels/simd_kernels.cpp:198-217, causal, with
  * the kv heads shared by q_heads/kv_heads query heads (cortex_sdk.cpp:1453-1478).
  * q (seq, q_heads, hd); k, v (seq, kv_heads, hd); out (seq, q_heads*hd). */

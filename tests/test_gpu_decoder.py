@@ -175,6 +175,41 @@ def test_tensor_core_block_loop_matches_oracle(ctx, oracle, model_tc):
         assert int(nxt2[s_]) == int(want.argmax())
 
 
+def test_selection_policy_matches_the_reference_rule(ctx, oracle, model):
+    """Steps under select_best_from_logits: what the device picks equals the oracle's pick on the
+    same logits with the same history, for two sequences with different histories; turning the
+    policy off gives plain argmax again."""
+    path, _ = model
+    rng = np.random.default_rng(6)
+    dec = make_decoder(path, ctx, max_batch=2)
+    dec.selection_policy(True, temperature=0.7)
+    prompts = [rng.integers(0, CFG["vocab"], 6), rng.integers(0, CFG["vocab"], 4)]
+    history = [[], []]
+    cur = []
+    for s_, p_ in enumerate(prompts):
+        lg, _ = dec.forward(p_, seq=s_)
+        first = oracle.select_best_from_logits(lg, history[s_], 0.7)
+        history[s_].append(first)
+        dec.note_generated([first], seq=s_)
+        cur.append(first)
+    repeats = 0
+    for _ in range(12):
+        nxt, lg = dec.step(cur, want_logits=True)
+        for s_ in range(2):
+            want = oracle.select_best_from_logits(lg[s_], history[s_], 0.7)
+            assert int(nxt[s_]) == want
+            repeats += int(np.argmax(lg[s_])) != want          # the penalty changed the pick
+            history[s_].append(want)
+        cur = [int(t) for t in nxt]
+    assert repeats > 0                                          # a 300-token random model does repeat itself
+    dec.selection_policy(False)
+    nxt, lg = dec.step(cur, want_logits=True)
+    assert [int(t) for t in nxt] == [int(np.argmax(lg[0])), int(np.argmax(lg[1]))]
+    dec.reset()
+    with pytest.raises(ValueError):
+        dec.note_generated([1], seq=5)
+
+
 def test_decoder_limits_and_errors(ctx, model):
     path, _ = model
     dec = make_decoder(path, ctx)
