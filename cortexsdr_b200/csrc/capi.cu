@@ -226,9 +226,10 @@ int csdr_context_synchronize(csdr_context* ctx) {
             CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
             CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
             throw Error(CSDR_ERR_TIMEOUT,
-                        "a device-side wait ran out (fused GEMV hand-over): results of the calls since "
-                        "the last synchronize are invalid; set CSDR_FUSED_GEMV=0 if the GPU is shared "
-                        "with long-running kernels");
+                        "a device-side wait ran out (fused GEMV hand-over, a tensor-core kernel's barrier, or a "
+                        "tensor-parallel peer that never raised its flag): results of the calls since the last "
+                        "synchronize are invalid; set CSDR_FUSED_GEMV=0 if the GPU is shared with long-running "
+                        "kernels");
         }
     });
 }
