@@ -168,7 +168,7 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
     rng = np.random.default_rng(7)
     out = {"batch": B, "context": ctxlen, "steps": steps, "tp": world}
     if world > 1:
-        peer = not os.environ.get("CSDR_BENCH_NCCL_ONLY") and 2 < world <= 8
+        peer = not os.environ.get("CSDR_BENCH_NCCL_ONLY") and 2 <= world <= 8
         if os.environ.get("CSDR_TP_EXCHANGE") in ("peer", "nccl") and not os.environ.get("CSDR_BENCH_NCCL_ONLY") and world <= 8:
             peer = os.environ["CSDR_TP_EXCHANGE"] == "peer"
         out["partial_sums"] = "peer memory (in-kernel)" if peer else "ncclAllReduce"

@@ -308,19 +308,21 @@ bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
     for (uint32_t i = 0; i < n; ++i) total_atoms += segs[i]->g.n_atoms;
     if (partial && d->xch_use && T <= 16u && d->sum_pad + static_cast<size_t>(total_atoms) * 16u <= d->xch_blk) {
         // the projection kernel stores its finished rows into every rank's exchange slot and
-        // raises the flags; the gather sums the slots while staging
+        // raises the flags; a small launch waits for all ranks and sums the slots into the local
+        // block; the gather then runs as on one GPU
         const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, &d->xch, base, nullptr);
+        launch_exchange_reduce(d->ctx, d->xch, d->sum_pad, w.floats, w.base);
         if (act_hi) {
-            launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo, &d->xch, base);
+            launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo);
             return true;
         }
-        launch_wide_gather_exchanged(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts, d->xch, base);
+        launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts);
         return false;
     }
     const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
     if (partial) sum_over_ranks(d, w.base, w.floats);
     if (act_hi && w.tile_mt) {
-        launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo, nullptr, nullptr);
+        launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo);
         return true;
     }
     launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts);
@@ -660,10 +662,9 @@ int csdr_decoder_exchange_import(csdr_decoder* d, const void* handles, size_t n_
         x.status = d->ctx->status_word;
         x.ranks = d->P;
         d->xch = x;
-        // measured on B200s: at 2 ranks ncclAllReduce of a 32 KB block is ~4 us quicker than the
-        // fused exchange (4.40 vs 4.64 ms per step), at 8 ranks the fused exchange wins by a
-        // third; the environment overrides the default
-        d->xch_use = d->P > 2;
+        // measured on B200s: 3.92 vs 4.63 ms per step at 8 ranks, 4.53 vs 4.70 at 2 (same box) in
+        // favour of the peer exchange over ncclAllReduce; the environment overrides the default
+        d->xch_use = true;
         if (const char* e = std::getenv("CSDR_TP_EXCHANGE")) {
             if (std::string(e) == "peer") d->xch_use = true;
             else if (std::string(e) == "nccl") d->xch_use = false;

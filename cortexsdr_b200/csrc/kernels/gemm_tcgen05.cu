@@ -549,26 +549,16 @@ struct GatherMember {
     uint32_t cta_begin, rows_per_cta;
 };
 
-// What the gather needs of an exchange: this rank's own slots and flags.
-struct GatherExchange {
-    const float* slots;       // [2][ranks][blk_floats]
-    const uint32_t* flags;    // [2][ranks]
-    const uint32_t* seq;
-    uint32_t ranks, blk_floats;
-    uint32_t dx_off[kGatherGroupMax];   // offset of each member's Dx inside a block
-    int* status;
-};
-
 struct GatherGroupParams {
     GatherMember m[kGatherGroupMax];
     uint32_t n_seg, M, m_total, code_cap16;
     uint32_t region_bytes;    // shared memory of one member: codes | scales | Dx
     int y_layout;
     TokenScale ts;
-    GatherExchange xch;       // ranks <= 1: Dx is read from m[i].dx
     __nv_bfloat16* act_hi;    // SwiGLU pair: planes of silu(member 0) * member 1, laid out like y
     __nv_bfloat16* act_lo;
 };
+
 
 constexpr uint32_t kExchangeSpin = 2000000u;   // polls of a flag word before giving up (a few seconds)
 
@@ -576,6 +566,64 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+
+// Tensor-parallel exchange, receiving side: waits (bounded) until every rank's flag of the
+// current parity shows the sequence number the projection kernel before this launch published,
+// then adds the ranks' slots up in rank order into the local projection block. A launch of its
+// own, so that the slots cross L2 once: summing them in every gather CTA's staging loop read
+// ranks x 32 KB per CTA, 64 MB per exchange at 8 ranks.
+struct ReduceParams {
+    const float* slots;       // this rank's slot area, [2][ranks][blk_floats]
+    const uint32_t* flags;    // this rank's flag words, [2][ranks]
+    const uint32_t* seq;
+    uint32_t ranks, blk_floats, off_floats, count4;
+    float* dst;               // local block, at off_floats
+    int* status;
+};
+
+__global__ void __launch_bounds__(256) exchange_reduce_kernel(const __grid_constant__ ReduceParams p) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ int late_s;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(p.seq);   // set by the projection before this launch
+    const uint32_t par = seq & 1u;
+    if (tid == 0) late_s = 0;
+    __syncthreads();
+    if (tid < p.ranks) {
+        const uint32_t* f = p.flags + par * p.ranks + tid;
+        // once a wait has run out on this context nothing after it waits again: the step is lost
+        // anyway, and the host must get its error quickly
+        const bool already_failed = *reinterpret_cast<const volatile int*>(p.status) != 0;
+        uint32_t spins = 0;
+        while (ld_acquire_sys(f) != seq) {
+            if (already_failed || ++spins > kExchangeSpin) {
+                late_s = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && late_s && blockIdx.x == 0) atomicExch(p.status, 1);   // gave up: the host will see it
+    const float* slot0 = p.slots + static_cast<size_t>(par) * p.ranks * p.blk_floats + p.off_floats;
+    float4* dst = reinterpret_cast<float4*>(p.dst);
+    for (uint32_t i = blockIdx.x * blockDim.x + tid; i < p.count4; i += gridDim.x * blockDim.x) {
+        float4 v[kMaxExchangeRanks];               // all ranks' pieces in flight, then the adds
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)
+            if (r < p.ranks) v[r] = __ldcg(reinterpret_cast<const float4*>(slot0 + static_cast<size_t>(r) * p.blk_floats) + i);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)   // rank order: every rank gets the same sum
+            if (r < p.ranks) {
+                acc.x += v[r].x;
+                acc.y += v[r].y;
+                acc.z += v[r].z;
+                acc.w += v[r].w;
+            }
+        dst[i] = acc;
+    }
 }
 
 // PAIR: the group is (gate, up) of a SwiGLU block with equal row counts; a CTA gathers the same
@@ -622,77 +670,21 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float inv_rms_s[16];
-    __shared__ int late_s;
-    if (g.xch.ranks > 1u) {
-        // ---- partial projections of all ranks arrive through peer memory ----
-        const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(g.xch.seq);   // the projection before this kernel set it
-        const uint32_t par = seq & 1u;
-        if (tid == 0) late_s = 0;
-        __syncthreads();
-        if (tid < g.xch.ranks) {
-            const uint32_t* f = g.xch.flags + par * g.xch.ranks + tid;
-            // once a wait has run out on this context nothing after it waits again: the step is
-            // lost anyway, and the host must get its error quickly
-            const bool already_failed = *reinterpret_cast<const volatile int*>(g.xch.status) != 0;
-            uint32_t spins = 0;
-            while (ld_acquire_sys(f) != seq) {
-                if (already_failed || ++spins > kExchangeSpin) {   // gave up: the host will see it
-                    late_s = 1;
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-        const float* slot0 = g.xch.slots + static_cast<size_t>(par) * g.xch.ranks * g.xch.blk_floats;
-        if (active) {
+    if (active) {
 #pragma unroll
-            for (uint32_t q = 0; q < NM; ++q) {
-                const GatherMember& m = g.m[mi0 + q];
-                float* dxs = reinterpret_cast<float*>(ggsm + q * region + static_cast<size_t>(g.code_cap16) * 16u) + 64;
-                const uint32_t n4 = (m.K * MT) >> 2;
-                const float* mine = slot0 + g.xch.dx_off[mi0 + q];
-                for (uint32_t i = tid; i < n4; i += kGroupThreads) {
-                    float4 v[kMaxExchangeRanks];               // all ranks' pieces in flight, then the adds
-#pragma unroll
-                    for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)
-                        if (r < g.xch.ranks)
-                            v[r] = __ldcg(reinterpret_cast<const float4*>(mine + static_cast<size_t>(r) * g.xch.blk_floats) + i);
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                    for (uint32_t r = 0; r < kMaxExchangeRanks; ++r)   // rank order: every rank gets the same sum
-                        if (r < g.xch.ranks) {
-                            acc.x += v[r].x;
-                            acc.y += v[r].y;
-                            acc.z += v[r].z;
-                            acc.w += v[r].w;
-                        }
-                    reinterpret_cast<float4*>(dxs)[i] = acc;
-                }
-            }
+        for (uint32_t q = 0; q < NM; ++q) {
+            const GatherMember& m = g.m[mi0 + q];
+            float* dxs = reinterpret_cast<float*>(ggsm + q * region + static_cast<size_t>(g.code_cap16) * 16u) + 64;
+            const uint32_t n4 = (m.K * MT) >> 2;
+            for (uint32_t i = tid; i < n4; i += kGroupThreads)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                                 static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
+                             "l"(m.dx + static_cast<size_t>(i) * 4u)
+                             : "memory");
+            for (uint32_t i = (n4 << 2) + tid; i < m.K * MT; i += kGroupThreads) dxs[i] = m.dx[i];
         }
-        if (g.ts.sumsq && tid < MT) {
-            float t = 0.0f;
-            for (uint32_t r = 0; r < g.xch.ranks; ++r) t += __ldcg(slot0 + static_cast<size_t>(r) * g.xch.blk_floats + tid);
-            inv_rms_s[tid] = rsqrtf(t * g.ts.inv_width + g.ts.eps);
-        }
-        if (tid == 0 && late_s && blockIdx.x == 0) atomicExch(g.xch.status, 1);
-    } else {
-        if (active) {
-#pragma unroll
-            for (uint32_t q = 0; q < NM; ++q) {
-                const GatherMember& m = g.m[mi0 + q];
-                float* dxs = reinterpret_cast<float*>(ggsm + q * region + static_cast<size_t>(g.code_cap16) * 16u) + 64;
-                const uint32_t n4 = (m.K * MT) >> 2;
-                for (uint32_t i = tid; i < n4; i += kGroupThreads)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                                     static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
-                                 "l"(m.dx + static_cast<size_t>(i) * 4u)
-                                 : "memory");
-                for (uint32_t i = (n4 << 2) + tid; i < m.K * MT; i += kGroupThreads) dxs[i] = m.dx[i];
-            }
-        }
-        if (g.ts.sumsq && tid < MT) inv_rms_s[tid] = rsqrtf(g.ts.sumsq[tid < g.M ? tid : 0] * g.ts.inv_width + g.ts.eps);
     }
+    if (g.ts.sumsq && tid < MT) inv_rms_s[tid] = rsqrtf(g.ts.sumsq[tid < g.M ? tid : 0] * g.ts.inv_width + g.ts.eps);
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
@@ -841,8 +833,8 @@ WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, u
 
 namespace {
 void gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
-                       const WideOut* outs, int y_layout, const TokenScale& ts, const Exchange* x, const float* blk_base,
-                       __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr) {
+                       const WideOut* outs, int y_layout, const TokenScale& ts, __nv_bfloat16* act_hi = nullptr,
+                       __nv_bfloat16* act_lo = nullptr) {
     GatherGroupParams g{};
     if (act_hi) {
         if (n != 2 || segs[0]->g.rows != segs[1]->g.rows || !act_lo)
@@ -855,15 +847,6 @@ void gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint3
     g.m_total = M;
     g.y_layout = y_layout;
     g.ts = ts;
-    if (x && x->ranks > 1u) {
-        g.xch.slots = x->slots[x->rank];
-        g.xch.flags = x->flags[x->rank];
-        g.xch.seq = x->seq;
-        g.xch.ranks = x->ranks;
-        g.xch.blk_floats = x->blk_floats;
-        g.xch.status = x->status;
-        for (uint32_t i = 0; i < n; ++i) g.xch.dx_off[i] = static_cast<uint32_t>(w.dx[i] - blk_base);
-    }
     uint32_t total_rows = 0, max_k = 0, max_slots = 0;
     for (uint32_t i = 0; i < n; ++i) {
         const Geometry& sg = segs[i]->g;
@@ -886,7 +869,7 @@ void gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint3
 void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
                         const WideOut* outs, int y_layout, const TokenScale& ts) {
     if (w.tile_mt) {
-        gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts, nullptr, nullptr);
+        gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts);
         return;
     }
     for (uint32_t i = 0; i < n; ++i) {
@@ -895,19 +878,39 @@ void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint
     }
 }
 
-void launch_wide_gather_exchanged(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w,
-                                  uint32_t M, const WideOut* outs, int y_layout, const TokenScale& ts,
-                                  const Exchange& x, const float* blk_base) {
-    if (!w.tile_mt) throw Error(CSDR_ERR_LIMIT, "the peer-memory exchange carries single token tiles (at most 16 tokens)");
-    gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts, &x, blk_base);
+void launch_exchange_reduce(csdr_context* ctx, const Exchange& x, uint32_t off_floats, size_t floats, float* dst) {
+    if (x.ranks < 2u) return;
+    if ((off_floats & 3u) || (floats & 3u) || off_floats + floats > x.blk_floats)
+        throw Error(CSDR_ERR_INVALID_ARG, "exchange: block range must be whole float4s inside a slot");
+    ReduceParams p{};
+    p.slots = x.slots[x.rank];
+    p.flags = x.flags[x.rank];
+    p.seq = x.seq;
+    p.ranks = x.ranks;
+    p.blk_floats = x.blk_floats;
+    p.off_floats = off_floats;
+    p.count4 = static_cast<uint32_t>(floats / 4u);
+    p.dst = dst;
+    p.status = x.status;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(std::max(1u, std::min(64u, (p.count4 + 255u) / 256u)), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LaunchScope ls(ctx, KC_DECODER_OP);
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, exchange_reduce_kernel, p));
+    ls.done("exchange_reduce_kernel");
 }
 
 void launch_wide_gather_swiglu(csdr_context* ctx, const csdr_segment* const* gate_up, const WideDx& w, uint32_t M,
-                               const TokenScale& ts, __nv_bfloat16* act_hi, __nv_bfloat16* act_lo, const Exchange* x,
-                               const float* blk_base) {
+                               const TokenScale& ts, __nv_bfloat16* act_hi, __nv_bfloat16* act_lo) {
     if (!w.tile_mt) throw Error(CSDR_ERR_LIMIT, "the fused SwiGLU gather takes single token tiles (at most 16 tokens)");
     const WideOut none[2] = {WideOut{nullptr, nullptr, nullptr}, WideOut{nullptr, nullptr, nullptr}};
-    gather_tile_group(ctx, gate_up, 2, w, M, none, CSDR_LAYOUT_TOKEN_MAJOR, ts, x, blk_base, act_hi, act_lo);
+    gather_tile_group(ctx, gate_up, 2, w, M, none, CSDR_LAYOUT_TOKEN_MAJOR, ts, act_hi, act_lo);
 }
 
 void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,

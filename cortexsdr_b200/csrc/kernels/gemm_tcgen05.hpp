@@ -76,9 +76,8 @@ struct WideDx {
 // 2 (parity) x ranks slots of `blk_floats` floats plus 2 x ranks flag words. A rank's projection
 // kernel stores its finished rows into slot [parity][its rank] of EVERY rank's region (plain peer
 // stores), and its last CTA stores the exchange's sequence number into the matching flag word of
-// every region. The gather on each
-// rank waits (bounded) for all flags of the parity to show the number and sums the slots in rank
-// order while it stages Dx. Two parities: a rank can run at most one exchange ahead of a peer,
+// every region. A small launch on each rank waits (bounded) for all flags of the parity to show
+// the number and sums the slots in rank order into the local block the gather reads. Two parities: a rank can run at most one exchange ahead of a peer,
 // because its next gather needs that peer's next push. The sequence number lives in device
 // memory and is advanced by the projection kernel, so a captured CUDA graph replays correctly.
 constexpr uint32_t kMaxExchangeRanks = 8;
@@ -98,18 +97,14 @@ WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, u
                            const float* sums = nullptr);
 void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
                         const WideOut* outs, int y_layout, const TokenScale& ts);
-// Gather of a single token tile (M <= 16) whose projections (and sums of squares, when ts.sumsq
-// is set: then they sit at the start of the block) arrive through the exchange: `blk_base` is the
-// local address that corresponds to offset 0 of a block.
-void launch_wide_gather_exchanged(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w,
-                                  uint32_t M, const WideOut* outs, int y_layout, const TokenScale& ts,
-                                  const Exchange& x, const float* blk_base);
+// Receiving side of the exchange: one small launch waits for every rank's flag and adds the
+// ranks' slots up, in rank order, over block range [off_floats, off_floats + floats) into the
+// local block at dst; the gather behind it reads the sum like any local projection.
+void launch_exchange_reduce(csdr_context* ctx, const Exchange& x, uint32_t off_floats, size_t floats, float* dst);
 // (gate, up) of a SwiGLU block over at most 16 tokens: one gather launch that writes
-// silu(gate) * up, token-major, as bf16 planes for the down projection. `x` (with blk_base) when
-// the projections arrive through the tensor-parallel exchange, else null.
+// silu(gate) * up, token-major, as bf16 planes for the down projection.
 void launch_wide_gather_swiglu(csdr_context* ctx, const csdr_segment* const* gate_up, const WideDx& w, uint32_t M,
-                               const TokenScale& ts, __nv_bfloat16* act_hi, __nv_bfloat16* act_lo, const Exchange* x,
-                               const float* blk_base);
+                               const TokenScale& ts, __nv_bfloat16* act_hi, __nv_bfloat16* act_lo);
 bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, size_t batch);
 void launch_matmul_wide_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x,
                               uint32_t M, const WideOut* outs, int y_layout);
