@@ -144,7 +144,9 @@ FUSED_GEMV_DRAM_BYTES_NCU = 8996000   # per launch, cfg2 shape, batch 1 (8.996 M
 
 def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True):
     """Decode tokens/s of a decoder-shaped synthetic archive (every linear an HSDR row-tile segment
-    with its own dictionary, K=512 3x8; random-init stand-in for the config's weights)."""
+    with its own dictionary, K=512 3x8; random-init stand-in for the config's weights).
+    With more than one rank the decoder is tensor parallel; CSDR_BENCH_NCCL_ONLY=1 withholds the
+    ranks' IPC handles so that the partial sums go through ncclAllReduce (the comparison arm)."""
     from cortexsdr_b200 import synth
     spec = DECODERS[name]
     cfg = spec["cfg"]
