@@ -138,6 +138,18 @@ class Oracle:
             raise ValueError(f"orc_hsdr_decompress rc={rc}")
         return out
 
+    def code_tiles(self, tiles, atoms, gammas, k):
+        """Coding pass of the encoder over tiles (n_tiles, T) against atoms (K, T): packed u16
+        codes (n_tiles, S, k)."""
+        tiles, atoms, gammas = _f32(tiles), _f32(atoms), _f32(gammas)
+        n, T = tiles.shape
+        K, S = atoms.shape[0], gammas.size
+        assert atoms.shape[1] == T
+        out = np.empty((n, S, k), np.uint16)
+        self.lib.orc_hsdr_code_tiles(_ptr(tiles), C.c_size_t(n), C.c_size_t(T), _ptr(atoms), C.c_uint16(K),
+                                     C.c_uint8(S), C.c_uint8(k), _ptr(gammas), _ptr(out, C.c_uint16))
+        return out
+
     def _dict_args(self, d: SharedDict):
         return (_ptr(d.atoms), _ptr(d.scales), C.c_uint16(d.tile_rows), C.c_uint16(d.tile_cols),
                 C.c_uint16(d.n_atoms), C.c_uint8(d.n_stages), C.c_uint8(d.k))

@@ -59,6 +59,45 @@ void orc_unpack_codes(const uint16_t* packed, size_t n, int32_t* idx, int8_t* si
     }
 }
 
+/* hierarchicalBinaryCode :219-262 per tile + packIndexSign :76-80; see the header. */
+void orc_hsdr_code_tiles(const float* tiles, size_t n_tiles, size_t T, const float* D, uint16_t K,
+                         uint8_t S, uint8_t k, const float* gammas, uint16_t* packed) {
+    float* r = (float*)malloc(T * sizeof(float));
+    float* proj = (float*)malloc((size_t)K * sizeof(float));
+    uint8_t* used = (uint8_t*)malloc(K);
+    if (!r || !proj || !used) {
+        free(r); free(proj); free(used);
+        return;
+    }
+    for (size_t t = 0; t < n_tiles; ++t) {
+        memcpy(r, tiles + t * T, T * sizeof(float));
+        for (uint8_t l = 0; l < S; ++l) {
+            memset(used, 0, K);
+            for (uint8_t step = 0; step < k; ++step) {
+                for (uint16_t j = 0; j < K; ++j) {
+                    const float* atom = D + (size_t)j * T;
+                    float s = 0.0f;
+                    for (size_t c = 0; c < T; ++c) s += atom[c] * r[c];
+                    proj[j] = used[j] ? 0.0f : s;
+                }
+                uint16_t best = 0;
+                float best_abs = 0.0f;
+                for (uint16_t j = 0; j < K; ++j) {
+                    const float a = fabsf(proj[j]);
+                    if (a > best_abs) { best_abs = a; best = j; }
+                }
+                const int neg = !(proj[best] >= 0.0f);
+                packed[(t * S + l) * k + step] = (uint16_t)((best & 0x7FFFu) | (neg ? 0x8000u : 0u));
+                used[best] = 1;
+                const float scale = neg ? -gammas[l] : gammas[l];
+                const float* atom = D + (size_t)best * T;
+                for (size_t c = 0; c < T; ++c) r[c] -= scale * atom[c];
+            }
+        }
+    }
+    free(r); free(proj); free(used);
+}
+
 /* Shared body of matmulRowMajor (:1301-1337) and matmulWithExternalDictionary
  * (:1853-1882): Dx = D*x, then per-row signed gather scaled per stage. */
 static int fused_matmul(const float* D, const float* scales, const uint8_t* codes_bytes,

@@ -56,6 +56,15 @@ int orc_hsdc_matmul(const uint8_t* codes, size_t n, const float* atoms, const fl
  * strips :1412-1438). out holds rows*cols floats. */
 int orc_hsdr_decompress(const uint8_t* payload, size_t n, float* out);
 
+/* The encoder's coding pass: hierarchicalBinaryCode :219-262 over every tile (as encode_all,
+ * :552-566), packed with packIndexSign :76-80. tiles holds n_tiles x T floats in extractTiles
+ * order (:95-116); packed receives n_tiles*S*k codes, tile-major, then stage, then slot. Per
+ * step: project the residual on every atom (atoms already used in this stage count as 0), take
+ * the FIRST atom with the largest |projection| (sign + when the projection is >= 0), subtract
+ * gamma_l * sign * atom. The dictionary fit around it (:494-607) is not restated. */
+void orc_hsdr_code_tiles(const float* tiles, size_t n_tiles, size_t T, const float* D, uint16_t K,
+                         uint8_t S, uint8_t k, const float* gammas, uint16_t* packed);
+
 /* decompressWithExternalDictionary, :1804-1828. */
 int orc_hsdc_decompress(const uint8_t* codes, size_t n, const float* atoms, const float* scales,
                         uint16_t d_tile_rows, uint16_t d_tile_cols, uint16_t d_atoms,

@@ -155,10 +155,31 @@ def main():
     out["i8_out"] = ref.dequantize(Segment("i", i8.view(np.uint8), (2, 256), SEG_WEIGHTS_INT8, data_format="i8",
                                            scale=0.0123, zero_point=3.0), 512).copy()
     np.savez_compressed(os.path.join(OUT, "dequant.npz"), **out)
+    encoder_coding(ref)
     print("golden fixtures written to", OUT)
     for f in sorted(os.listdir(OUT)):
         print(f"  {f:24s} {os.path.getsize(os.path.join(OUT, f)):>9d} B")
 
 
+def encoder_coding(ref):
+    """The encoder's final coding pass: weights in, the payload the reference encoder made of
+    them out. Whatever the number of dictionary-update iterations, the codes of a payload are
+    hierarchicalBinaryCode (HierarchicalSDRStrategy.cpp:219-262) of the weights against the
+    payload's own dictionary (encode_all is the last thing fitHierarchicalKSVD runs, :552-571)."""
+    out = {}
+    for label, R, C, seed, cfg in (
+            ("row_fast", 64, 128, 0xE0C0, cfg_row1d(128, 32, 4, ksvd_iters=0)),
+            ("row_fit", 64, 128, 0xE0C1, cfg_row1d(128, 32, 4, ksvd_iters=3)),
+            ("tiles_2d", 128, 192, 0xE0C2, cfg_default(tile_rows=16, tile_cols=16, n_atoms=32, k=4, ksvd_iters=2))):
+        (w,) = ref.mt19937_normal(seed, [(R * C, 0, 0.05)])
+        pay = ref.compress(Segment("enc." + label, w.reshape(R, C), (R, C), SEG_ATTENTION), cfg, cfg)
+        out[label + "_w"] = w.reshape(R, C).copy()
+        out[label + "_payload"] = np.frombuffer(pay, np.uint8)
+    np.savez_compressed(os.path.join(OUT, "encoder_coding.npz"), **out)
+
+
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["encoder_coding"]:      # only this fixture, the others untouched
+        encoder_coding(Reference())
+    else:
+        main()
