@@ -98,6 +98,110 @@ void orc_hsdr_code_tiles(const float* tiles, size_t n_tiles, size_t T, const flo
     free(r); free(proj); free(used);
 }
 
+/* MT19937 (Matsumoto & Nishimura 1998) as std::mt19937 seeds and tempers it. */
+typedef struct { uint32_t mt[624]; int i; } orc_mt;
+static void mt_seed(orc_mt* g, uint32_t seed) {
+    g->mt[0] = seed;
+    for (int i = 1; i < 624; ++i) g->mt[i] = 1812433253u * (g->mt[i - 1] ^ (g->mt[i - 1] >> 30)) + (uint32_t)i;
+    g->i = 624;
+}
+static uint32_t mt_next(orc_mt* g) {
+    if (g->i >= 624) {
+        for (int i = 0; i < 624; ++i) {
+            const uint32_t y = (g->mt[i] & 0x80000000u) | (g->mt[(i + 1) % 624] & 0x7FFFFFFFu);
+            g->mt[i] = g->mt[(i + 397) % 624] ^ (y >> 1) ^ ((y & 1u) ? 0x9908B0DFu : 0u);
+        }
+        g->i = 0;
+    }
+    uint32_t y = g->mt[g->i++];
+    y ^= y >> 11;
+    y ^= (y << 7) & 0x9D2C5680u;
+    y ^= (y << 15) & 0xEFC60000u;
+    y ^= y >> 18;
+    return y;
+}
+/* uniform draw from [0, range) out of a 32-bit generator: Lemire's multiply-shift with
+ * rejection of the biased low products, the method libstdc++ (GCC 11 and later) uses. */
+static uint32_t mt_below(orc_mt* g, uint32_t range) {
+    uint64_t prod = (uint64_t)mt_next(g) * range;
+    uint32_t low = (uint32_t)prod;
+    if (low < range) {
+        const uint32_t threshold = (uint32_t)(0u - range) % range;
+        while (low < threshold) {
+            prod = (uint64_t)mt_next(g) * range;
+            low = (uint32_t)prod;
+        }
+    }
+    return (uint32_t)(prod >> 32);
+}
+
+static void wr32(uint8_t* p, uint32_t v) { memcpy(p, &v, 4); }
+static void wr16(uint8_t* p, uint16_t v) { memcpy(p, &v, 2); }
+
+/* compress :1068-1236 with ksvd_iters = 0; see the header. */
+long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
+                          uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t* out, size_t cap) {
+    const uint32_t R_full = (R / tile_rows) * tile_rows, C_full = (C / tile_cols) * tile_cols;
+    if (!R_full || !C_full) return -1;
+    const uint32_t n_rt = R_full / tile_rows, n_ct = C_full / tile_cols, n_tiles = n_rt * n_ct;
+    const size_t T = (size_t)tile_rows * tile_cols;
+    if (n_tiles < K) return -2;
+    const size_t n_codes = (size_t)n_tiles * S * k;
+    const size_t edge_floats = (size_t)R_full * (C - C_full) + (size_t)(R - R_full) * C;
+    const size_t total = HSDR_HDR + 4u * S + 4u * (size_t)K * T + 2u * n_codes + 4u * edge_floats;
+    if (total > cap) return -3;
+    float* tiles = (float*)malloc((size_t)n_tiles * T * sizeof(float));
+    if (!tiles) return -10;
+    /* extractTiles :95-116 over the aligned top-left block */
+    for (uint32_t br = 0; br < n_rt; ++br)
+        for (uint32_t bc = 0; bc < n_ct; ++bc)
+            for (uint32_t r = 0; r < tile_rows; ++r)
+                memcpy(tiles + ((size_t)br * n_ct + bc) * T + (size_t)r * tile_cols,
+                       W + (size_t)(br * tile_rows + r) * C + (size_t)bc * tile_cols, sizeof(float) * tile_cols);
+    memset(out, 0, HSDR_HDR);
+    memcpy(out, "HSDR", 4);
+    wr32(out + 4, 2u); wr32(out + 8, R); wr32(out + 12, C); wr32(out + 16, n_tiles);
+    wr16(out + 20, tile_rows); wr16(out + 22, tile_cols); wr16(out + 24, K);
+    out[26] = S; out[27] = k;
+    memcpy(out + 28, &decay, 4);
+    wr32(out + 32, (uint32_t)(4u * edge_floats));
+    float* gam = (float*)(out + HSDR_HDR);            /* 36 and 36+4S are multiples of 4 */
+    for (uint8_t l = 0; l < S; ++l) gam[l] = powf(decay, (float)l);          /* :507-509 */
+    float* D = (float*)(out + HSDR_HDR + 4u * S);
+    /* dictionary init :511-538 */
+    orc_mt g;
+    mt_seed(&g, 0xC0DEu);
+    for (uint16_t j = 0; j < K; ++j) {
+        const float* src = tiles + (size_t)mt_below(&g, n_tiles) * T;
+        float* atom = D + (size_t)j * T;
+        float sq = 0.0f;
+        for (size_t c = 0; c < T; ++c) sq += src[c] * src[c];
+        const float norm = sqrtf(sq > 1e-24f ? sq : 1e-24f);
+        for (size_t c = 0; c < T; ++c) atom[c] = src[c] / norm;
+    }
+    double norm_sum = 0.0;
+    for (uint32_t i = 0; i < n_tiles; ++i) {
+        double sq = 0.0;
+        for (size_t c = 0; c < T; ++c) sq += (double)tiles[i * T + c] * tiles[i * T + c];
+        norm_sum += sqrt(sq);
+    }
+    const float mean = (float)(norm_sum / (double)(n_tiles ? n_tiles : 1u));
+    const float root = sqrtf((float)((uint32_t)S * k));
+    const float init_scale = mean / (root > 1.0f ? root : 1.0f);
+    for (size_t i = 0; i < (size_t)K * T; ++i) D[i] *= init_scale;
+    /* encode_all :552-567; the code stream may sit on an odd 16-bit boundary only if 4S+4KT is
+     * odd, which it never is */
+    orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, (uint16_t*)(out + HSDR_HDR + 4u * S + 4u * (size_t)K * T));
+    free(tiles);
+    /* edge strips :1185-1197: top-right, then bottom */
+    uint8_t* e = out + total - 4u * edge_floats;
+    for (uint32_t r = 0; r < R_full; ++r, e += 4u * (C - C_full))
+        memcpy(e, W + (size_t)r * C + C_full, 4u * (size_t)(C - C_full));
+    for (uint32_t r = R_full; r < R; ++r, e += 4u * (size_t)C)
+        memcpy(e, W + (size_t)r * C, 4u * (size_t)C);
+    return (long)total;
+}
+
 /* Shared body of matmulRowMajor (:1301-1337) and matmulWithExternalDictionary
  * (:1853-1882): Dx = D*x, then per-row signed gather scaled per stage. */
 static int fused_matmul(const float* D, const float* scales, const uint8_t* codes_bytes,

@@ -65,6 +65,18 @@ int orc_hsdr_decompress(const uint8_t* payload, size_t n, float* out);
 void orc_hsdr_code_tiles(const float* tiles, size_t n_tiles, size_t T, const float* D, uint16_t K,
                          uint8_t S, uint8_t k, const float* gammas, uint16_t* packed);
 
+/* The encoder in its fast mode (ksvd_iters = 0): compress :1068-1236 with fitHierarchicalKSVD
+ * :494-571 reduced to its first encode. gamma_l = decay^l; atom j = tile number
+ * uniform_int_distribution(0, n_tiles-1)(mt19937(0xC0DE)) (libstdc++: Lemire's multiply-shift
+ * draw with rejection), normalised to unit length and scaled by mean tile norm / max(1,
+ * sqrt(S*k)); codes by the coding pass above; edge strips verbatim. Writes an HSDR v2 payload
+ * into out (capacity cap) and returns its size, or a negative number: -1 no full tile,
+ * -2 fewer tiles than atoms, -3 capacity, -10 memory. The reference build reorders the float
+ * sums of the normalisation (-ffast-math), so atoms agree with its payloads to rounding, not
+ * bit for bit. */
+long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
+                          uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t* out, size_t cap);
+
 /* decompressWithExternalDictionary, :1804-1828. */
 int orc_hsdc_decompress(const uint8_t* codes, size_t n, const float* atoms, const float* scales,
                         uint16_t d_tile_rows, uint16_t d_tile_cols, uint16_t d_atoms,

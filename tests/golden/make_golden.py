@@ -170,7 +170,8 @@ def encoder_coding(ref):
     for label, R, C, seed, cfg in (
             ("row_fast", 64, 128, 0xE0C0, cfg_row1d(128, 32, 4, ksvd_iters=0)),
             ("row_fit", 64, 128, 0xE0C1, cfg_row1d(128, 32, 4, ksvd_iters=3)),
-            ("tiles_2d", 128, 192, 0xE0C2, cfg_default(tile_rows=16, tile_cols=16, n_atoms=32, k=4, ksvd_iters=2))):
+            ("tiles_2d", 128, 192, 0xE0C2, cfg_default(tile_rows=16, tile_cols=16, n_atoms=32, k=4, ksvd_iters=2)),
+            ("edges_fast", 100, 150, 0xE0C3, cfg_default(tile_rows=16, tile_cols=16, n_atoms=32, k=4, ksvd_iters=0))):
         (w,) = ref.mt19937_normal(seed, [(R * C, 0, 0.05)])
         pay = ref.compress(Segment("enc." + label, w.reshape(R, C), (R, C), SEG_ATTENTION), cfg, cfg)
         out[label + "_w"] = w.reshape(R, C).copy()
