@@ -150,18 +150,20 @@ class Oracle:
                                      C.c_uint8(S), C.c_uint8(k), _ptr(gammas), _ptr(out, C.c_uint16))
         return out
 
-    def encode_fast(self, W, tile_rows, tile_cols, n_atoms, n_stages=3, k=8, decay=0.5):
-        """HSDR payload of W by the encoder's fast mode (no dictionary-update iterations)."""
+    def encode_fast(self, W, tile_rows, tile_cols, n_atoms, n_stages=3, k=8, decay=0.5, ksvd_iters=0):
+        """HSDR payload of W by the encoder; ksvd_iters = 0 is its fast mode (no dictionary-update
+        iterations)."""
         W = _f32(W)
         R, Cc = W.shape
         cap = 36 + 4 * n_stages + 4 * n_atoms * tile_rows * tile_cols + 2 * R * Cc * n_stages * k + 4 * R * Cc
         out = np.empty(cap, np.uint8)
-        self.lib.orc_hsdr_encode_fast.restype = C.c_long
-        n = self.lib.orc_hsdr_encode_fast(_ptr(W), C.c_uint32(R), C.c_uint32(Cc), C.c_uint16(tile_rows),
-                                          C.c_uint16(tile_cols), C.c_uint16(n_atoms), C.c_uint8(n_stages),
-                                          C.c_uint8(k), C.c_float(decay), _ptr(out, C.c_uint8), C.c_size_t(cap))
+        self.lib.orc_hsdr_encode.restype = C.c_long
+        n = self.lib.orc_hsdr_encode(_ptr(W), C.c_uint32(R), C.c_uint32(Cc), C.c_uint16(tile_rows),
+                                     C.c_uint16(tile_cols), C.c_uint16(n_atoms), C.c_uint8(n_stages),
+                                     C.c_uint8(k), C.c_float(decay), C.c_uint8(ksvd_iters),
+                                     _ptr(out, C.c_uint8), C.c_size_t(cap))
         if n < 0:
-            raise ValueError(f"orc_hsdr_encode_fast rc={n}")
+            raise ValueError(f"orc_hsdr_encode rc={n}")
         return out[:n].copy()
 
     def _dict_args(self, d: SharedDict):

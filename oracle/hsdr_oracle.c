@@ -138,9 +138,104 @@ static uint32_t mt_below(orc_mt* g, uint32_t range) {
 static void wr32(uint8_t* p, uint32_t v) { memcpy(p, &v, 4); }
 static void wr16(uint8_t* p, uint16_t v) { memcpy(p, &v, 2); }
 
-/* compress :1068-1236 with ksvd_iters = 0; see the header. */
+/* atomUpdateStep :281-489: every atom moves half a least-squares step toward the residuals of
+ * the tiles that use it (all atoms from the same residual, doubles for the sums), is rescaled
+ * to the target norm when it grows past 1.5 times it, and is replaced by a random tile when
+ * nothing uses it. One generator draw per call seeds the replacements. The user list packs
+ * (tile << 16 | slot), so the reference folds tile numbers above 65535; kept. */
+static int atom_update(const float* tiles, uint32_t n_tiles, size_t T, float* D, uint16_t K,
+                       const uint16_t* packed, uint8_t S, uint8_t k, const float* gam, orc_mt* g) {
+    const uint32_t slots = (uint32_t)S * k;
+    float* resid = (float*)malloc((size_t)n_tiles * T * sizeof(float));
+    double* corr = (double*)malloc(T * sizeof(double));
+    if (!resid || !corr) { free(resid); free(corr); return -10; }
+    double norm_sum = 0.0;
+    for (uint32_t i = 0; i < n_tiles; ++i) {
+        float* r = resid + (size_t)i * T;
+        for (size_t c = 0; c < T; ++c) r[c] = 0.0f;                 /* reconstruction first ... */
+        for (uint32_t s_ = 0; s_ < slots; ++s_) {
+            const uint16_t code = packed[(size_t)i * slots + s_];
+            const float scale = (code & 0x8000u) ? -gam[s_ / k] : gam[s_ / k];
+            const float* atom = D + (size_t)(code & 0x7FFFu) * T;
+            for (size_t c = 0; c < T; ++c) r[c] += scale * atom[c];
+        }
+        double sq = 0.0;
+        for (size_t c = 0; c < T; ++c) {
+            const float t = tiles[(size_t)i * T + c];
+            r[c] = t - r[c];                                          /* ... then the residual */
+            sq += (double)t * t;
+        }
+        norm_sum += sqrt(sq);
+    }
+    const double mean = norm_sum / (double)(n_tiles ? n_tiles : 1u);
+    double target = mean / sqrt((double)slots);
+    if (target < 1e-6) target = 1e-6;
+    const double cap = 1.5 * target;
+    const uint64_t base_seed = (uint64_t)mt_next(g) ^ 0xA0B1C2D3u;
+    for (uint32_t j = 0; j < K; ++j) {
+        float* atom = D + (size_t)j * T;
+        for (size_t c = 0; c < T; ++c) corr[c] = 0.0;
+        double wsum = 0.0;
+        int users = 0;
+        for (uint32_t i = 0; i < n_tiles; ++i)
+            for (uint32_t s_ = 0; s_ < slots; ++s_) {
+                const uint16_t code = packed[(size_t)i * slots + s_];
+                if ((uint32_t)(code & 0x7FFFu) != j) continue;
+                ++users;
+                const uint32_t it = (uint32_t)(i << 16) >> 16;       /* the packed user entry */
+                const uint16_t own = packed[(size_t)it * slots + s_];
+                const double gamma = (double)gam[s_ / k];
+                const double sg = ((own & 0x8000u) ? -1.0 : 1.0) * gamma;
+                const float* r = resid + (size_t)it * T;
+                for (size_t c = 0; c < T; ++c) corr[c] += sg * (double)r[c];
+                wsum += gamma * gamma;
+            }
+        int reseed = 0;
+        uint32_t salt = 0x9E3779B1u;
+        if (!users) reseed = 1;
+        else if (wsum <= 1e-12) continue;
+        else {
+            const double inv_w = 0.5 / wsum;
+            double new_sq = 0.0;
+            for (size_t c = 0; c < T; ++c) {
+                const double v = (double)atom[c] + corr[c] * inv_w;
+                const float vf = (float)v;
+                if (!isfinite(v) || !isfinite(vf)) { reseed = 1; break; }
+                atom[c] = vf;
+                new_sq += (double)vf * (double)vf;
+            }
+            if (!reseed && !isfinite(new_sq)) reseed = 1;
+            if (reseed) salt = 0xB7E15163u;
+            else {
+                const double nn = sqrt(new_sq);
+                if (nn > cap) {
+                    const double sc = target / nn;
+                    for (size_t c = 0; c < T; ++c) atom[c] = (float)((double)atom[c] * sc);
+                }
+            }
+        }
+        if (reseed) {
+            orc_mt local;
+            mt_seed(&local, (uint32_t)(base_seed ^ (uint64_t)(uint32_t)(j * salt)));
+            const float* src = tiles + (size_t)mt_below(&local, n_tiles) * T;
+            double sq = 0.0;
+            for (size_t c = 0; c < T; ++c) sq += (double)src[c] * src[c];
+            const double sc = target / sqrt(sq > 1e-30 ? sq : 1e-30);
+            for (size_t c = 0; c < T; ++c) atom[c] = (float)(src[c] * sc);
+        }
+    }
+    free(resid); free(corr);
+    return 0;
+}
+
 long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
                           uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t* out, size_t cap) {
+    return orc_hsdr_encode(W, R, C, tile_rows, tile_cols, K, S, k, decay, 0, out, cap);
+}
+
+/* compress :1068-1236 around fitHierarchicalKSVD :494-607; see the header. */
+long orc_hsdr_encode(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
+                     uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t ksvd_iters, uint8_t* out, size_t cap) {
     const uint32_t R_full = (R / tile_rows) * tile_rows, C_full = (C / tile_cols) * tile_cols;
     if (!R_full || !C_full) return -1;
     const uint32_t n_rt = R_full / tile_rows, n_ct = C_full / tile_cols, n_tiles = n_rt * n_ct;
@@ -191,7 +286,14 @@ long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_
     for (size_t i = 0; i < (size_t)K * T; ++i) D[i] *= init_scale;
     /* encode_all :552-567; the code stream may sit on an odd 16-bit boundary only if 4S+4KT is
      * odd, which it never is */
-    orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, (uint16_t*)(out + HSDR_HDR + 4u * S + 4u * (size_t)K * T));
+    uint16_t* codes = (uint16_t*)(out + HSDR_HDR + 4u * S + 4u * (size_t)K * T);
+    orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, codes);
+    for (uint8_t it = 0; it < ksvd_iters; ++it) {                          /* :573-577 */
+        if (atom_update(tiles, n_tiles, T, D, K, codes, S, k, gam, &g)) { free(tiles); return -10; }
+        orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, codes);
+    }
+    for (size_t i = 0; i < (size_t)K * T; ++i)                              /* :598-604 */
+        if (!isfinite(D[i])) D[i] = 0.0f;
     free(tiles);
     /* edge strips :1185-1197: top-right, then bottom */
     uint8_t* e = out + total - 4u * edge_floats;

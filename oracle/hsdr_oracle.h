@@ -77,6 +77,13 @@ void orc_hsdr_code_tiles(const float* tiles, size_t n_tiles, size_t T, const flo
 long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
                           uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t* out, size_t cap);
 
+/* The same with ksvd_iters rounds of (atomUpdateStep :281-489, encode again) between the first
+ * encode and the serialisation, and the final sweep that zeroes non-finite atoms (:598-604).
+ * Sums that the reference takes across OpenMP threads or reorders under -ffast-math are taken
+ * in index order here. */
+long orc_hsdr_encode(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
+                     uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t ksvd_iters, uint8_t* out, size_t cap);
+
 /* decompressWithExternalDictionary, :1804-1828. */
 int orc_hsdc_decompress(const uint8_t* codes, size_t n, const float* atoms, const float* scales,
                         uint16_t d_tile_rows, uint16_t d_tile_cols, uint16_t d_atoms,
