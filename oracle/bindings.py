@@ -392,6 +392,22 @@ class Reference:
             o += int(c)
         return res
 
+    def attention(self, q, k, v):
+        """Causal multi-head attention by the reference's kernel. q (seq, q_heads, hd); k, v
+        (seq, kv_heads, hd), repeated here to q_heads as the reference's decoder driver does
+        (repeat_kv_heads, api/cortex_sdk.cpp:1453-1478). Returns (seq, q_heads*hd)."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        seq, qh, hd = q.shape
+        rep = qh // k.shape[1]
+        k, v = _f32(np.repeat(k, rep, axis=1)), _f32(np.repeat(v, rep, axis=1))
+        out = np.empty((seq, qh * hd), np.float32)
+        self.lib.ref_multi_head_attention.restype = C.c_long
+        n = self.lib.ref_multi_head_attention(_ptr(q), _ptr(k), _ptr(v), _ptr(out), C.c_uint64(1), C.c_uint64(seq),
+                                              C.c_uint64(qh * hd), C.c_uint64(qh), C.c_int(1))
+        if n < 0:
+            raise self._err("multi_head_attention")
+        return out
+
     def compress(self, seg: Segment, attn_cfg=None, mlp_cfg=None) -> bytes:
         keep = []
         d = self._seg(seg, keep)

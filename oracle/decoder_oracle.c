@@ -2,7 +2,9 @@
  * arithmetic of the reference's run_transformer_decode (api/cortex_sdk.cpp:1543-1696)
  * primitive by primitive. The reference reaches this code only when a flag that is
  * never set is false, and none of its tests covers it: parity for this file is
- * UNPINNED (there is nothing to pin against except the primitives' definitions).
+ * UNPINNED, except orc_attention, which is checked against the reference's own attention
+ * kernel (kernels/attention_kernels.cpp, compiled into oracle/_ref): the other primitives sit
+ * in an anonymous namespace of a file that does not link without the ONNX parser.
  * Two parameters the reference hard-codes or guesses are explicit here: eps (its
  * default is 1e-5, cortex_sdk.cpp:1212) and head_dim (it guesses from
  * {128,64,256,32,16}, cortex_sdk.cpp:1335). */

@@ -10,7 +10,8 @@
  * and (c), where the reference tree is present, the reference library live.
  * Exception: the decoder-layer functions (decoder_oracle.c) restate code the
  * reference never executes with default settings and no reference test covers:
- * for those parity is UNPINNED beyond primitive-level checks.
+ * for those parity is UNPINNED beyond primitive-level checks (attention is pinned
+ * against the reference's attention kernel).
  *
  * All citations are paths inside the reference tree.
  */

@@ -22,6 +22,7 @@
 #include "ai_compression/core/AIDecompressor.hpp"
 #include "ai_compression/core/AIModelParser.hpp"
 #include "ai_compression/core/ModelSegment.hpp"
+#include "ai_compression/kernels/attention_kernels.hpp"
 #include "ai_compression/kernels/blas_kernels.hpp"
 
 #include <algorithm>
@@ -144,6 +145,18 @@ void ref_mt19937_normal(uint32_t seed, uint32_t n_arrays, const uint64_t* counts
 }
 
 void ref_free(void* p) { std::free(p); }
+
+// The attention kernel the reference's decoder driver calls (kernels/attention_kernels.cpp:
+// multi_head_attention, softmax from kernels/simd_kernels.cpp). q, k, v, out are
+// (batch, seq, hidden) with hidden = heads * head_dim; kv heads already repeated by the caller
+// as the driver does before the call.
+long ref_multi_head_attention(const float* q, const float* k, const float* v, float* out, uint64_t batch,
+                              uint64_t seq, uint64_t hidden, uint64_t heads, int causal) {
+    return guarded([&]() -> long {
+        CortexAICompression::Kernels::multi_head_attention(q, k, v, out, batch, seq, hidden, heads, causal != 0);
+        return 0;
+    });
+}
 
 // compress(): returns payload size, *out malloc'ed (free with ref_free). attn/mlp
 // configs seed the strategy exactly as `HierarchicalSDRStrategy(attn, mlp)` does.

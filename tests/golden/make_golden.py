@@ -156,6 +156,7 @@ def main():
                                            scale=0.0123, zero_point=3.0), 512).copy()
     np.savez_compressed(os.path.join(OUT, "dequant.npz"), **out)
     encoder_coding(ref)
+    attention_cases(ref)
     print("golden fixtures written to", OUT)
     for f in sorted(os.listdir(OUT)):
         print(f"  {f:24s} {os.path.getsize(os.path.join(OUT, f)):>9d} B")
@@ -179,8 +180,22 @@ def encoder_coding(ref):
     np.savez_compressed(os.path.join(OUT, "encoder_coding.npz"), **out)
 
 
+def attention_cases(ref):
+    """Causal attention of the decoder driver by the reference's own kernel
+    (kernels/attention_kernels.cpp multi_head_attention + kernels/simd_kernels.cpp softmax),
+    kv heads repeated as api/cortex_sdk.cpp:1453-1478 does: one head per kv head, and grouped
+    query heads in the 0.5B-shaped ratio (14 : 2, head size 64)."""
+    rng = np.random.default_rng(77)
+    out = {}
+    for label, seq, qh, kvh, hd in (("mha", 9, 4, 4, 16), ("gqa", 21, 14, 2, 64)):
+        q, k, v = (rng.normal(0, 1, (seq, h, hd)).astype(np.float32) for h in (qh, kvh, kvh))
+        out.update({label + "_q": q, label + "_k": k, label + "_v": v, label + "_out": ref.attention(q, k, v)})
+    np.savez_compressed(os.path.join(OUT, "attention.npz"), **out)
+
+
 if __name__ == "__main__":
-    if sys.argv[1:] == ["encoder_coding"]:      # only this fixture, the others untouched
-        encoder_coding(Reference())
+    only = {"encoder_coding": encoder_coding, "attention": attention_cases}
+    if len(sys.argv) == 2 and sys.argv[1] in only:      # only this fixture, the others untouched
+        only[sys.argv[1]](Reference())
     else:
         main()
