@@ -36,9 +36,10 @@ def _rank(rank, world, port, path, q):
         out = {}
         tokens = np.random.default_rng(0).integers(0, CFG["vocab"], 12)
         long_tokens = np.random.default_rng(1).integers(0, CFG["vocab"], 21)
-        # "nccl": partial projections summed by ncclAllReduce; "peer": pushed into peer memory and
-        # summed by the gather (steps of at most 16 tokens; the 21-token pass still takes NCCL)
-        os.environ["CSDR_TP_EXCHANGE"] = "peer"      # at two ranks the default would stay with NCCL
+        # "nccl": no IPC handles given, partial projections summed by ncclAllReduce; "peer": pushed
+        # into peer memory by the projection and summed by the reduce launch (steps of at most 16
+        # tokens; the 21-token pass still takes NCCL)
+        os.environ["CSDR_TP_EXCHANGE"] = "peer"      # explicit, whatever the default
         for tag, kw in (("nccl", {}), ("peer", dict(all_gather=all_gather))):
             dec = cs.Decoder(ld, **CFG, max_seq=64, max_batch=2, rms_eps=1e-6, comm=comm, **kw)
             logits, hidden = dec.forward(tokens, want_hidden=True)
