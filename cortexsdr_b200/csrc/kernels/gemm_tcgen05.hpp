@@ -77,8 +77,9 @@ struct WideDx {
 // kernel stores its finished rows into slot [parity][its rank] of EVERY rank's region (plain peer
 // stores), and its last CTA stores the exchange's sequence number into the matching flag word of
 // every region. A small launch on each rank waits (bounded) for all flags of the parity to show
-// the number and sums the slots in rank order into the local block the gather reads. Two parities: a rank can run at most one exchange ahead of a peer,
-// because its next gather needs that peer's next push. The sequence number lives in device
+// the number and sums the slots in rank order into the local block the gather reads. Two
+// parities: a rank can run at most one exchange ahead of a peer, because its next reduce launch
+// needs that peer's next push. The sequence number lives in device
 // memory and is advanced by the projection kernel, so a captured CUDA graph replays correctly.
 constexpr uint32_t kMaxExchangeRanks = 8;
 struct Exchange {
