@@ -124,3 +124,28 @@ def test_routing_errors_before_any_compute():
         ld.matmulHSDR("missing", np.zeros((512, 1), np.float32), 1)
     with pytest.raises(RuntimeError, match=r"is not HSDR-encoded \(strategy_id=0\)"):
         ld.matmulHSDR("layer.raw.weight", np.zeros((256, 1), np.float32), 1)
+
+
+def test_payload_reader_agrees_with_an_independent_writer(oracle):
+    # payloads framed by the oracle's restatement of the reference encoder (a writer that shares no
+    # code with the library's reader): every geometry is accepted and every field agrees,
+    # including the edge-strip offsets; a truncated or over-long index in any of them is rejected
+    rng = np.random.default_rng(21)
+    for R, Cc, tr, tc, K, S, k in ((40, 64, 1, 64, 16, 3, 2), (70, 52, 16, 16, 8, 2, 3), (33, 48, 8, 24, 4, 1, 1),
+                                   (64, 64, 32, 32, 4, 3, 4), (19, 130, 1, 128, 16, 4, 2)):
+        W = rng.normal(0, 0.05, (R, Cc)).astype(np.float32)
+        pay = oracle.encode_fast(W, tr, tc, K, S, k, 0.5)
+        i = cs.inspect_payload(pay)
+        n_tiles = (R // tr) * (Cc // tc)
+        edge = 4 * ((R // tr) * tr * (Cc - (Cc // tc) * tc) + (R - (R // tr) * tr) * Cc)
+        assert (i.kind, i.rows, i.cols, i.n_tiles, i.tile_rows, i.tile_cols) == (0, R, Cc, n_tiles, tr, tc)
+        assert (i.n_atoms, i.n_stages, i.k_per_stage, i.stage_decay, i.edge_bytes) == (K, S, k, 0.5, edge)
+        assert i.off_scales == 36 and i.off_dict == 36 + 4 * S
+        assert i.off_codes == i.off_dict + 4 * K * tr * tc and i.off_edges == i.off_codes + 2 * n_tiles * S * k
+        assert i.payload_bytes == pay.size == i.off_edges + edge
+        with pytest.raises(cs.CompressionError):
+            cs.inspect_payload(pay[:-1])
+        bad = pay.copy()
+        bad[i.off_codes:i.off_codes + 2] = np.array([K], np.uint16).view(np.uint8)     # first index past the table
+        with pytest.raises(cs.CompressionError, match="atom index"):
+            cs.inspect_payload(bad)
