@@ -74,7 +74,8 @@ void orc_hsdr_code_tiles(const float* tiles, size_t n_tiles, size_t T, const flo
  * into out (capacity cap) and returns its size, or a negative number: -1 no full tile,
  * -2 fewer tiles than atoms, -3 capacity, -10 memory. The reference build reorders the float
  * sums of the normalisation (-ffast-math), so atoms agree with its payloads to rounding, not
- * bit for bit. */
+ * bit for bit. The caller passes the tile shape configFor (:1024-1065) would choose: a row
+ * tile (tile_rows == 1) always spans the whole row. */
 long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
                           uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t* out, size_t cap);
 
