@@ -54,7 +54,7 @@ def workload_payload():
         pay = Reference().compress(Segment("blk.0.ffn_gate.weight", W, (R, C), SEG_FEED_FORWARD), cfg, cfg)
         src = "reference encoder (forRow1D, ksvd_iters=0)"
     else:
-        from cortexsdr_b200 import synth
+        from tests import synth
         pay = synth.hsdr_payload(R, C, n_atoms=K, n_stages=S, k=KPS, seed=2)
         src = "synthetic payload (reference encoder not built here)"
     with open(path + ".tmp", "wb") as f:
@@ -147,7 +147,7 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
     with its own dictionary, K=512 3x8; random-init stand-in for the config's weights).
     With more than one rank the decoder is tensor parallel; CSDR_BENCH_NCCL_ONLY=1 withholds the
     ranks' IPC handles so that the partial sums go through ncclAllReduce (the comparison arm)."""
-    from cortexsdr_b200 import synth
+    from tests import synth
     spec = DECODERS[name]
     cfg = spec["cfg"]
     os.makedirs(CACHE, exist_ok=True)

@@ -22,7 +22,7 @@
 //
 // Every mbarrier wait is a bounded try_wait loop; a wait that runs out sets the context's status
 // word, the roles stop issuing work, and the CTA still meets its cluster barriers and frees its
-// tensor memory. No load here uses cluster multicast.
+// tensor memory.
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_bf16.h>

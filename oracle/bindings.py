@@ -29,12 +29,23 @@ SEG_EMBEDDING = 13
 SEG_LAYER_NORM = 14
 
 
+def reference_tree():
+    """Where the reference sources lie: $CORTEXSDR_REF, else a checkout named ``reference``
+    beside this repository. None when neither holds a ``src`` folder."""
+    cands = [os.environ.get("CORTEXSDR_REF"),
+             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "src")):
+            return os.path.abspath(c)
+    return None
+
+
 def build(ref: bool = True) -> None:
     """Compile the C oracle and, when the reference tree is present, oracle/_ref."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
-    if ref and os.path.isdir(os.environ.get("CORTEXSDR_REF", "/root/reference") + "/src"):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref",
-                               "REF=" + os.environ.get("CORTEXSDR_REF", "/root/reference")])
+    tree = reference_tree() if ref else None
+    if tree:
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + tree])
 
 
 def _f32(a):

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 import cortexsdr_b200 as cs
-from cortexsdr_b200 import synth
+from tests import synth
 
 pytestmark = pytest.mark.gpu
 LOGIT_TOL = 2e-2

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 import cortexsdr_b200 as cs
-from cortexsdr_b200 import synth
+from tests import synth
 from conftest import rel_err
 
 pytestmark = pytest.mark.gpu

@@ -230,7 +230,7 @@ def test_row_shards_concatenate_to_whole(ctx, oracle, golden):
 def test_column_shards_add_up_to_the_whole_product(ctx, oracle):
     """Input-column shards (tensor parallelism): each shard times its slice of x is that slice's
     share of W x; shares add up to the oracle's product, on the GEMV path and the tensor-core path."""
-    from cortexsdr_b200 import synth
+    from tests import synth
     pay = synth.hsdr_payload(200, 512, n_atoms=128, k=4, seed=71)
     seg = cs.Segment.from_payload(pay, ctx)
     shards = [seg.shard_cols(b, e) for b, e in ((0, 128), (128, 320), (320, 512))]
@@ -253,7 +253,7 @@ def test_column_shards_add_up_to_the_whole_product(ctx, oracle):
 
 def test_grouped_matmul_matches_single_calls(ctx, oracle, golden):
     import torch
-    from cortexsdr_b200 import synth
+    from tests import synth
     pays = [synth.hsdr_payload(r, 512, n_atoms=k, k=4, seed=40 + i) for i, (r, k) in enumerate(((256, 64), (96, 32), (130, 64)))]
     segs = [cs.Segment.from_payload(p, ctx) for p in pays]
     rng = np.random.default_rng(9)
@@ -274,7 +274,7 @@ def test_grouped_tensor_core_projection_matches_oracle(ctx, oracle):
     """Members with different atom counts and row counts over one activation matrix: one
     projection launch for the group (bf16 planes built once), one gather launch up to 16 tokens."""
     import torch
-    from cortexsdr_b200 import synth
+    from tests import synth
     shapes = ((264, 128), (96, 256), (130, 128))
     # 472 columns: seven 64-column blocks and a ragged eighth
     pays = [synth.hsdr_payload(r, 472, n_atoms=k, k=4, seed=60 + i) for i, (r, k) in enumerate(shapes)]
@@ -321,7 +321,7 @@ def test_fused_and_two_kernel_paths_agree(lib, oracle, golden, monkeypatch):
 def test_chained_launches_are_ordered(ctx, oracle, golden):
     # y of one launch feeds the next as x: the dependent launch must see the finished result
     import torch
-    from cortexsdr_b200 import synth
+    from tests import synth
     p1 = synth.hsdr_payload(512, 512, n_atoms=64, k=4, seed=70)
     p2 = synth.hsdr_payload(512, 512, n_atoms=64, k=4, seed=71)
     s1, s2 = cs.Segment.from_payload(p1, ctx), cs.Segment.from_payload(p2, ctx)

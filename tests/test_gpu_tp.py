@@ -68,7 +68,7 @@ def test_two_rank_decoder_matches_single_gpu(tmp_path):
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    from cortexsdr_b200 import synth
+    from tests import synth
     path = str(tmp_path / "tp.sdr")
     synth.decoder_archive(path, **CFG, n_atoms=128, k=3, kv_atoms=128, seed=7)
     ctx = mp.get_context("spawn")

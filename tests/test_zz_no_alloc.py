@@ -9,7 +9,8 @@ import numpy as np
 import pytest
 
 import cortexsdr_b200 as cs
-from cortexsdr_b200 import _lib, synth
+from cortexsdr_b200 import _lib
+from tests import synth
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3  # the matmul tolerance used throughout these tests (relative, fp32 accumulate)
