@@ -104,6 +104,14 @@ class Context:
     def launch_count(self) -> int:
         return int(self._lib.csdr_context_launch_count(self._h))
 
+    def set_wait_limits(self, gemv_polls: int = 0, barrier_rounds: int = 0, exchange_polls: int = 0):
+        """Iteration limits of the bounded device-side waits; 0 restores a default."""
+        _check(self._lib.csdr_context_set_wait_limits(self._h, gemv_polls, barrier_rounds, exchange_polls))
+
+    def wait_selftest(self) -> int:
+        """Status of a wait on a flag nothing raises (ERR_TIMEOUT once the exchange limit is spent)."""
+        return int(self._lib.csdr_context_wait_selftest(self._h))
+
     def profile(self, enable: bool):
         """Bracket every kernel launch with CUDA events (benchmarks only)."""
         _check(self._lib.csdr_context_profile(self._h, 1 if enable else 0))

@@ -67,6 +67,8 @@ SIGNATURES = {
     "csdr_context_synchronize": (C.c_int, [_P]),
     "csdr_context_stream": (_P, [_P]),
     "csdr_context_launch_count": (C.c_uint64, [_P]),
+    "csdr_context_set_wait_limits": (C.c_int, [_P, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "csdr_context_wait_selftest": (C.c_int, [_P]),
     "csdr_context_profile": (C.c_int, [_P, C.c_int]),
     "csdr_context_profile_read": (C.c_int, [_P, C.c_int, C.POINTER(C.c_uint64),
                                             C.POINTER(C.c_double)]),
@@ -89,6 +91,7 @@ SIGNATURES = {
                                                  C.POINTER(_P), C.c_int]),
     "csdr_matmul_rowtiles_noalloc": (C.c_int, [_P, _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                                C.c_uint32, _P, C.c_int, C.c_int, _SZ, _P, C.c_int, _P]),
+    "csdr_matmul_rowtiles_noalloc_status": (C.c_int, [_P, C.POINTER(C.c_int)]),
     "csdr_decompress": (C.c_int, [_P, _P, _F, _SZ]),
     "csdr_decompress_device_async": (C.c_int, [_P, _P, _P]),
     "csdr_dequantize": (C.c_int, [_P, C.c_char_p, _P, _SZ, C.c_float, C.c_float, _F, _SZ,

@@ -95,6 +95,12 @@ void require_ctx(csdr_context* ctx) {
 
 using namespace csdr;
 
+namespace {
+void rethrow(int rc) {
+    if (rc != CSDR_OK) throw Error(rc, csdr_last_error());
+}
+}  // namespace
+
 void* csdr_context::scratch_get(int slot, size_t bytes) {
     if (!scratch[slot] || scratch[slot]->bytes < bytes) {
         // Work queued on the stream may still use the old buffer.
@@ -193,6 +199,8 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         }
         CSDR_CUDA(cudaMalloc(&ctx->status_word, sizeof(int)));
         CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
+        CSDR_CUDA(cudaMalloc(&ctx->gemv_seq, 2 * sizeof(uint32_t)));
+        CSDR_CUDA(cudaMemsetAsync(ctx->gemv_seq, 0, 2 * sizeof(uint32_t), ctx->stream));
         if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TENSOR_CORES")) ctx->tensor_cores = e[0] != '0';
@@ -210,6 +218,7 @@ int csdr_context_destroy(csdr_context* ctx) {
         cudaStreamSynchronize(ctx->stream);
         for (auto& s : ctx->scratch) s.reset();
         if (ctx->status_word) cudaFree(ctx->status_word);
+        if (ctx->gemv_seq) cudaFree(ctx->gemv_seq);
         if (ctx->pinned) cudaFreeHost(ctx->pinned);
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
@@ -225,12 +234,52 @@ int csdr_context_synchronize(csdr_context* ctx) {
         if (status != 0) {
             CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
             CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+            if (status == 2)
+                throw Error(CSDR_ERR_CODE_RANGE, "a gather met a packed code naming an atom >= n_atoms (it contributed "
+                                                 "nothing to its row): results since the last synchronize are invalid");
             throw Error(CSDR_ERR_TIMEOUT,
                         "a device-side wait ran out (fused GEMV hand-over, a tensor-core kernel's barrier, or a "
                         "tensor-parallel peer that never raised its flag): results of the calls since the last "
                         "synchronize are invalid; set CSDR_FUSED_GEMV=0 if the GPU is shared with long-running "
                         "kernels");
         }
+    });
+}
+
+int csdr_context_set_wait_limits(csdr_context* ctx, uint32_t gemv_polls, uint32_t barrier_rounds,
+                                 uint32_t exchange_polls) {
+    return guard([&] {
+        require_ctx(ctx);
+        const csdr_context fresh{};
+        ctx->spin_limit_gemv = gemv_polls ? gemv_polls : fresh.spin_limit_gemv;
+        ctx->spin_limit_barrier = barrier_rounds ? barrier_rounds : fresh.spin_limit_barrier;
+        ctx->spin_limit_exchange = exchange_polls ? exchange_polls : fresh.spin_limit_exchange;
+    });
+}
+
+int csdr_context_wait_selftest(csdr_context* ctx) {
+    return guard([&] {
+        require_ctx(ctx);
+        // A two-rank exchange laid out in local scratch: [2][2] slots of 64 floats, then the flag
+        // words, then the sequence counter. Rank 0's flag of parity 1 is raised, rank 1's never is.
+        constexpr uint32_t blk = 64;
+        float* region = static_cast<float*>(ctx->scratch_get(5, 4096));
+        CSDR_CUDA(cudaMemsetAsync(region, 0, 4096, ctx->stream));
+        uint32_t* flags = reinterpret_cast<uint32_t*>(region + 4 * blk);
+        uint32_t* seq = flags + 16;
+        const uint32_t one = 1;
+        CSDR_CUDA(cudaMemcpyAsync(seq, &one, 4, cudaMemcpyHostToDevice, ctx->stream));
+        CSDR_CUDA(cudaMemcpyAsync(flags + 2, &one, 4, cudaMemcpyHostToDevice, ctx->stream));
+        Exchange x{};
+        x.ranks = 2;
+        x.rank = 0;
+        x.blk_floats = blk;
+        x.slots[0] = x.slots[1] = region;
+        x.flags[0] = x.flags[1] = flags;
+        x.seq = seq;
+        x.status = ctx->status_word;
+        launch_exchange_reduce(ctx, x, 0, blk, region + 8 * blk);
+        rethrow(csdr_context_synchronize(ctx));
     });
 }
 

@@ -97,7 +97,7 @@ struct csdr_context {
     size_t smem_optin = 0;
     uint64_t launches = 0;
     // Grow-only scratch (Dx partials, factored 2-D products, host staging).
-    csdr::DevPtr scratch[6];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials
+    csdr::DevPtr scratch[6];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials, 5 wait self-test
     void* scratch_get(int slot, size_t bytes);
     int* status_word = nullptr;  // device int: kernels record bounded-wait timeouts here
     // Page-locked, device-mapped host staging for the host-buffer entry points (grow-only).
@@ -105,8 +105,13 @@ struct csdr_context {
     size_t pinned_bytes = 0;
     void* pinned_get(size_t bytes);
     uint32_t notify_seq = 0;     // value of the last completion word written into `pinned`
-    // Fused GEMV: every launch tags its partial results with a fresh non-zero epoch.
-    uint32_t gemv_epoch = 0;
+    // Fused GEMV: every launch tags its partial results with a fresh non-zero epoch, taken from a
+    // device counter ([0] launches completed, [1] finished CTAs) that the launch itself advances.
+    uint32_t* gemv_seq = nullptr;
+    // Iteration limits of the bounded device-side waits (csdr_context_set_wait_limits).
+    uint32_t spin_limit_gemv = 1000000u;      // fused GEMV hand-over polls (an L2 round trip each)
+    uint32_t spin_limit_barrier = 4000000u;   // mbarrier try_wait rounds of the tensor-core kernels
+    uint32_t spin_limit_exchange = 2000000u;  // polls of a peer's flag in the tensor-parallel exchange
     csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch

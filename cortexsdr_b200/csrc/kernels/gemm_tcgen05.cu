@@ -123,6 +123,7 @@ struct TcParams {
     uint32_t n_split;
     float* out;           // [n_split][K][M] (n_split == 1: Dx itself)
     int* status;
+    uint32_t spin;        // mbarrier try_wait rounds before a wait gives up
     int x_has_lo;         // 0 when the activations are bf16 already
 };
 
@@ -143,7 +144,7 @@ hsdr_dx_tcgen05_kernel(const __grid_constant__ TcParams p) {
     const uint32_t tok0 = blockIdx.y * N;
     const uint32_t kb_begin = blockIdx.z * p.kb_per_split;
     const uint32_t kb_end = min(p.n_kb, kb_begin + p.kb_per_split);
-    constexpr uint32_t kSpin = 4000000u;   // a fraction of a second of polling, then give up
+    const uint32_t kSpin = p.spin;   // a fraction of a second of polling by default, then give up
 
     if (tid == 0) {
         for (int i = 0; i < 3; ++i)
@@ -560,7 +561,6 @@ struct GatherGroupParams {
 };
 
 
-constexpr uint32_t kExchangeSpin = 2000000u;   // polls of a flag word before giving up (a few seconds)
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -580,6 +580,7 @@ struct ReduceParams {
     uint32_t ranks, blk_floats, off_floats, count4;
     float* dst;               // local block, at off_floats
     int* status;
+    uint32_t spin;            // polls of a flag word before giving up (a few seconds by default)
 };
 
 __global__ void __launch_bounds__(256) exchange_reduce_kernel(const __grid_constant__ ReduceParams p) {
@@ -598,7 +599,7 @@ __global__ void __launch_bounds__(256) exchange_reduce_kernel(const __grid_const
         const bool already_failed = *reinterpret_cast<const volatile int*>(p.status) != 0;
         uint32_t spins = 0;
         while (ld_acquire_sys(f) != seq) {
-            if (already_failed || ++spins > kExchangeSpin) {
+            if (already_failed || ++spins > p.spin) {
                 late_s = 1;
                 break;
             }
@@ -892,6 +893,7 @@ void launch_exchange_reduce(csdr_context* ctx, const Exchange& x, uint32_t off_f
     p.count4 = static_cast<uint32_t>(floats / 4u);
     p.dst = dst;
     p.status = x.status;
+    p.spin = ctx->spin_limit_exchange;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(std::max(1u, std::min(64u, (p.count4 + 255u) / 256u)), 1, 1);
     cfg.blockDim = dim3(256, 1, 1);
@@ -969,6 +971,7 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
     p.n_kb = n_kb;
     p.n_split = n_split;
     p.status = ctx->status_word;
+    p.spin = ctx->spin_limit_barrier;
     p.x_has_lo = a.x_dtype == CSDR_DTYPE_F32 ? 1 : 0;
     float* part = (n_split > 1 && !use_tma) ? static_cast<float*>(ctx->scratch_get(1, dx_floats * n_split * 4u)) : dx;
     p.out = part;

@@ -44,7 +44,6 @@ constexpr uint32_t kBlockK = 64;         // bf16 per tile row = 128 bytes = one 
 constexpr uint32_t kTileM = 128;         // atoms per CTA = MMA M
 constexpr uint32_t kATile = kTileM * 128u;
 constexpr uint32_t kMaxStages = 4;
-constexpr uint32_t kSpin = 4000000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -78,8 +77,8 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint6
         : "memory");
 }
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpin; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n"
@@ -135,6 +134,7 @@ struct Params {
     uint32_t* xch_done;
     const float* xch_sums;
     int* status;
+    uint32_t spin;               // mbarrier try_wait rounds before a wait gives up
     unsigned long long* trace;   // optional: 16 global-timer stamps per CTA (phase boundaries)
     uint32_t trace_ctas;
 };
@@ -232,7 +232,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
             }
             for (uint32_t it = pre; it < n_it; ++it) {
                 const uint32_t s = it % p.stages, use = it / p.stages;
-                if (!mbar_wait(smem_u32(&empty_bar[s]), (use - 1u) & 1u)) {
+                if (!mbar_wait(smem_u32(&empty_bar[s]), (use - 1u) & 1u, p.spin)) {
                     failed_s = 1;
                     break;
                 }
@@ -254,7 +254,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
             const uint32_t idesc = make_idesc(N);
             for (uint32_t it = 0; it < n_it; ++it) {
                 const uint32_t s = it % p.stages, use = it / p.stages;
-                if (!mbar_wait(smem_u32(&full_bar[s]), use & 1u)) {
+                if (!mbar_wait(smem_u32(&full_bar[s]), use & 1u, p.spin)) {
                     failed_s = 1;
                     break;
                 }
@@ -293,7 +293,7 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
     float* ptile = reinterpret_cast<float*>(smem);
     bool done = true;
     if (warp >= 2) {
-        done = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&accum_bar), 0u));   // warp-uniform
+        done = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&accum_bar), 0u, p.spin));   // warp-uniform
         if (!done) failed_s = 1;
         if (tid == 64) stamp(p, 4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -669,6 +669,7 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
                                                          1, static_cast<size_t>(tiles) * ranks * kTileM * N * 4u))
                                                    : nullptr;
     p.status = ctx->status_word;
+    p.spin = ctx->spin_limit_barrier;
     p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
     p.trace_ctas = static_cast<uint32_t>(ctx->sm_count) * 2u;
     if (xch && xch->ranks > 1u) {

@@ -10,13 +10,17 @@
 //              programmatic-dependent-launch wait: in a chain of matmuls the weight traffic
 //              of launch n+1 overlaps the tail of launch n.
 //   phase A    after the wait: x slab to shared memory, FMAs, warp-shuffle reduction. Each
-//              column-split partial leaves as ONE 64-bit word {value, launch epoch}.
+//              column-split partial leaves as ONE 64-bit word {value, launch epoch}. The
+//              epoch is read from a counter in device memory that the launch's last CTA
+//              advances, so a captured CUDA graph tags every replay afresh.
 //   hand-over  no barrier, no atomics, no fence (a device-wide fence behind an 8 MB read
 //              burst was measured at up to 7 us): phase B polls the partial words
 //              themselves, sixteen independent loads per thread per round, until every word
-//              carries this launch's epoch. An aligned 64-bit store is single-copy atomic,
-//              so a matching tag proves the value beside it. The poll is bounded and records
-//              a status word instead of spinning forever.
+//              carries this launch's epoch. Words are written with st.relaxed.gpu.b64 and
+//              polled with ld.relaxed.gpu.b64 (single-copy atomic by the memory model), so a
+//              matching tag proves the value beside it. The poll is bounded: the first wait
+//              that runs out records a status word and every later poll of the launch gives
+//              up after one look, so a launch waits at most one limit in all.
 //   phase B    Dx = sum of the partials in split order (results do not depend on
 //              scheduling), signed gather in the reference's order, y out. With wide token
 //              tiles a gather CTA owns a group of four tokens, so it polls only that slice.
@@ -50,8 +54,9 @@ struct FusedParams {
     uint32_t n_seg, n_tasks, C, slab, nsplit;
     uint32_t gather_ctas;   // CTAs that take part in phase B = row chunks * token groups
     XView x;
-    uint2* part;            // {float bits, epoch} per partial
-    uint32_t epoch;         // this launch's tag; never 0 (fresh scratch is zero)
+    unsigned long long* part;  // {float bits (low half), epoch (high half)} per partial
+    uint32_t* seq;          // device: [0] launches completed (the epoch is this + 1, never 0: fresh
+                            // scratch is zero), [1] CTAs of the running launch that have finished
     int* status;
     uint32_t spin_limit;
     unsigned long long* trace;  // optional: 16 global-timer stamps per CTA (phase boundaries)
@@ -65,10 +70,25 @@ __device__ __forceinline__ void stamp(const FusedParams& p, int slot) {
     }
 }
 
-__device__ __forceinline__ uint2 ld_poll(const uint2* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_poll(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
+}
+__device__ __forceinline__ void st_tagged(unsigned long long* p, float value, uint32_t epoch) {
+    const unsigned long long w = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+// The launch is over for this CTA: the last one to say so advances the launch counter (skipping
+// the value whose successor would be the tag 0) and clears the count for the next launch.
+__device__ __forceinline__ void cta_finished(const FusedParams& p) {
+    if (threadIdx.x == 0) {
+        if (atomicAdd(p.seq + 1, 1u) == gridDim.x - 1u) {
+            const uint32_t next = p.seq[0] + 1u;
+            p.seq[0] = next == 0xFFFFFFFFu ? 0u : next;
+            p.seq[1] = 0u;
+        }
+    }
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -208,6 +228,7 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
     stamp(p, 1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(p, 2);
+    const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(p.seq) + 1u;
 
     // ---- phase A ----
     float* xs = reinterpret_cast<float*>(smem_raw);
@@ -268,32 +289,38 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
                     if (lane == b) mine = v;
                 }
                 if (lane < MT && atom0 + a < sg.K)
-                    p.part[sg.part_off + (static_cast<size_t>(cur.split) * sg.K + atom0 + a) * MT + lane] =
-                        make_uint2(__float_as_uint(mine), p.epoch);
+                    st_tagged(p.part + sg.part_off + (static_cast<size_t>(cur.split) * sg.K + atom0 + a) * MT + lane,
+                              mine, epoch);
             }
             stamp(p, 8);
         }
         advance(cur);
     }
     stamp(p, 4);
-    if (!gathers) return;
+    if (!gathers) {
+        cta_finished(p);
+        return;
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // ---- phase B ----
     float* dxs = reinterpret_cast<float*>(smem_raw + plan.dxs_off);
     bool late = false;
+    // a wait that ran out earlier on this context (or in this launch) is not repeated
+    uint32_t limit = *reinterpret_cast<const volatile int*>(p.status) != 0 ? 0u : p.spin_limit;
+    const unsigned long long want_tag = static_cast<unsigned long long>(epoch) << 32;
     for (uint32_t si = 0; si < p.n_seg; ++si) {
         const FusedSeg& sg = p.seg[si];
         const uint32_t row0 = rchunk * sg.rows_per_cta;
         if (row0 < sg.R) {
             // -- hand-over: poll this token group's partial words, 16 loads in flight --
-            const uint2* part = p.part + sg.part_off;
+            const unsigned long long* part = p.part + sg.part_off;
             const uint32_t n_el = sg.K * MTG;                       // dxs elements
             const uint32_t mine_el = tid < n_el ? (n_el - tid + kThreads - 1u) / kThreads : 0u;
             const uint32_t n_w = mine_el * p.nsplit;               // words this thread owns
             uint32_t j0 = 0, sp0 = 0;                              // (element ordinal, split) of word w0
             for (uint32_t w0 = 0; w0 < n_w; w0 += 16u) {
-                uint2 e[16];
+                unsigned long long e[16];
                 for (uint32_t spins = 0;; ++spins) {
                     uint32_t j = j0, sp = sp0;
                     bool ok = true;
@@ -308,14 +335,15 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
                                 ++j;
                             }
                         } else {
-                            e[q] = make_uint2(0u, p.epoch);
+                            e[q] = want_tag;
                         }
                     }
 #pragma unroll
-                    for (int q = 0; q < 16; ++q) ok = ok && e[q].y == p.epoch;
+                    for (int q = 0; q < 16; ++q) ok = ok && static_cast<uint32_t>(e[q] >> 32) == epoch;
                     if (ok) break;
-                    if (spins > p.spin_limit) {  // gave up: the host will see it
+                    if (spins >= limit) {  // gave up: the host will see it; nothing after this waits
                         late = true;
+                        limit = 0u;
                         break;
                     }
                 }
@@ -324,7 +352,7 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
                     if (w0 + q < n_w) {
                         const uint32_t el = tid + j0 * kThreads;
                         const float prev = sp0 ? dxs[el] : 0.0f;  // split order, whatever the batch boundaries
-                        dxs[el] = prev + __uint_as_float(e[q].x);
+                        dxs[el] = prev + __uint_as_float(static_cast<uint32_t>(e[q]));
                         if (++sp0 == p.nsplit) {
                             sp0 = 0;
                             ++j0;
@@ -375,6 +403,7 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
     }
     if (late) atomicExch(p.status, 1);
     stamp(p, 7);
+    cta_finished(p);
 }
 
 template <int MT, int A, int U>
@@ -417,8 +446,6 @@ void launch_t(csdr_context* ctx, FusedParams& p, uint32_t max_k, bool pdl) {
     const uint32_t grid = static_cast<uint32_t>(ctx->sm_count) * static_cast<uint32_t>(std::min(occ_cached, 2));
     p.gather_ctas = std::max(token_groups, std::min(want_gather, grid) / token_groups * token_groups);
     plan_for(p.gather_ctas);  // never larger than the size computed above
-    if (++ctx->gemv_epoch == 0) ++ctx->gemv_epoch;  // 0 is what a fresh scratch buffer holds
-    p.epoch = ctx->gemv_epoch;
     // whole-x residency only pays when a CTA walks several column slabs
     if (plan.xcols == p.C && p.n_tasks <= grid && p.slab < p.C) {
         plan.xcols = p.slab;
@@ -487,10 +514,12 @@ void launch_gemv_fused(csdr_context* ctx, const csdr_segment* const* segs, uint3
         max_k = std::max(max_k, g.n_atoms);
     }
     p.n_tasks = task;
-    p.part = static_cast<uint2*>(ctx->scratch_get(4, std::max<size_t>(static_cast<size_t>(part_off) * 8u, 2u << 20)));
+    p.part = static_cast<unsigned long long*>(
+        ctx->scratch_get(4, std::max<size_t>(static_cast<size_t>(part_off) * 8u, 2u << 20)));
+    p.seq = ctx->gemv_seq;
     p.status = ctx->status_word;
     p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
-    p.spin_limit = 1000000u;  // each poll is an L2 round trip: about a second in all
+    p.spin_limit = ctx->spin_limit_gemv;  // each poll is an L2 round trip: about a second by default
     // Phase B: as many (row chunk, token group) jobs as there is work for; launch_t caps it at the grid.
     p.gather_ctas = std::max<uint32_t>(1u, static_cast<uint32_t>(static_cast<size_t>(max_rows) * mt / 32u));
     const bool pdl = ctx->pdl;

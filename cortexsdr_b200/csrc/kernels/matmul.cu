@@ -182,7 +182,7 @@ template <int MT>
 __global__ void __launch_bounds__(kGatherThreads)
 hsdr_gather_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, uint32_t k,
                    const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
-                   uint32_t rows_per_cta, int dx_in_smem, YView yv) {
+                   uint32_t rows_per_cta, int dx_in_smem, YView yv, int* status) {
     extern __shared__ __align__(16) unsigned char gsm[];
     const uint32_t slots = S * k;
     const uint32_t tid = threadIdx.x;
@@ -216,6 +216,7 @@ hsdr_gather_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, u
 
     const uint32_t b = tid % MT;
     constexpr uint32_t RP = kGatherThreads / MT;
+    bool bad = false;
     for (uint32_t rl = tid / MT; rl < rows_here; rl += RP) {
         const uint16_t* rc = cs + rl * slots;
         float acc = 0.0f;
@@ -223,8 +224,14 @@ hsdr_gather_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, u
             const float gamma = sc[l];
             for (uint32_t kk = 0; kk < k; ++kk) {
                 const uint32_t code = rc[l * k + kk];
+                const uint32_t atom = code & 0x7FFFu;
                 const float scale = (code & 0x8000u) ? -gamma : gamma;
-                acc = __fadd_rn(acc, __fmul_rn(scale, dxp[(code & 0x7FFFu) * MT + b]));
+                // a code naming an atom the dictionary does not have contributes nothing and is
+                // reported: images made by this library are checked on the host, raw device
+                // streams handed to the allocation-free entry point are not
+                const float v = atom < K ? dxp[atom * MT + b] : 0.0f;
+                bad |= atom >= K;
+                acc = __fadd_rn(acc, __fmul_rn(scale, v));
             }
         }
         if (b < yv.M) {
@@ -233,6 +240,7 @@ hsdr_gather_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t S, u
             yv.y[y_index(yv, r, b)] = acc;
         }
     }
+    if (bad && status) atomicExch(status, 2);
 }
 
 // ---------------------------------------------------------------------------
@@ -502,7 +510,7 @@ void launch_gather_t(csdr_context* ctx, const csdr_segment* seg, const float* dx
     LaunchScope ls(ctx, KC_GATHER);
     kern<<<grid, kGatherThreads, smem, ctx->stream>>>(
         seg->codes_ptr(), g.rows, g.n_stages, g.k, static_cast<const float*>(seg->scales->ptr), dx,
-        g.n_atoms, rows_per_cta, dx_in_smem, yv);
+        g.n_atoms, rows_per_cta, dx_in_smem, yv, ctx->status_word);
     ls.done("hsdr_gather_kernel");
 }
 
@@ -687,19 +695,30 @@ constexpr int kNoAllocMaxDevices = 64;
 // Held by every GPU that loads the library, until the process exits. Host code may name
 // this array only to ask for its address: the symbol itself is not a device pointer.
 static __device__ __align__(256) float g_noalloc_dx[kNoAllocMaxAtoms * kNoAllocTokens];
+// Set to 2 by the gather when a code named an atom >= n_atoms (the code contributed nothing);
+// read and cleared by csdr_matmul_rowtiles_noalloc_status.
+static __device__ int g_noalloc_status;
 
-// Device address of the array on `device`, which must be current. Looked up once per device.
-float* noalloc_scratch(int device) {
-    static float* addr[kNoAllocMaxDevices] = {};
+struct NoAllocScratch {
+    float* dx = nullptr;
+    int* status = nullptr;
+};
+
+// Device addresses of the two symbols on `device`, which must be current. Looked up once per device.
+NoAllocScratch noalloc_scratch(int device) {
+    static NoAllocScratch addr[kNoAllocMaxDevices] = {};
     static std::mutex mu;
     if (device < 0 || device >= kNoAllocMaxDevices) throw Error(CSDR_ERR_LIMIT, "device index beyond 63");
     std::lock_guard<std::mutex> lk(mu);
-    if (!addr[device]) {
+    if (!addr[device].dx) {
         float* p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dx);
-        if (e != cudaSuccess || !p)
+        int* q = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dx);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&q), g_noalloc_status);
+        if (e != cudaSuccess || !p || !q)
             throw Error(CSDR_ERR_CUDA, std::string("cudaGetSymbolAddress(scratch): ") + cudaGetErrorString(e));
-        addr[device] = p;
+        addr[device].status = q;
+        addr[device].dx = p;
     }
     return addr[device];
 }
@@ -721,7 +740,7 @@ void noalloc_check(const char* what) {
 template <int MT, int A, int U>
 void noalloc_chunk(const float* D, const uint16_t* codes, const float* scales, uint32_t R, uint32_t C,
                    uint32_t K, uint32_t S, uint32_t k, const XView& xv, const YView& yv, float* dx,
-                   int sm_count, cudaStream_t stream) {
+                   int* status, int sm_count, cudaStream_t stream) {
     uint32_t nsplit = std::min<uint32_t>(8u, std::max<uint32_t>(1u, (C + 1023u) / 1024u));
     const uint32_t slab = ((C + nsplit - 1u) / nsplit + 3u) & ~3u;
     nsplit = (C + slab - 1u) / slab;
@@ -757,7 +776,7 @@ void noalloc_chunk(const float* D, const uint16_t* codes, const float* scales, u
         auto kern = hsdr_gather_kernel<MT>;
         noalloc_smem(kern, smem);
         kern<<<(R + rows_per_cta - 1u) / rows_per_cta, kGatherThreads, smem, stream>>>(
-            codes, R, S, k, scales, dx, K, rows_per_cta, dx_in_smem, yv);
+            codes, R, S, k, scales, dx, K, rows_per_cta, dx_in_smem, yv, status);
         noalloc_check("hsdr_gather_kernel");
     }
 }
@@ -793,7 +812,7 @@ extern "C" int csdr_matmul_rowtiles_noalloc(const float* dict_dev, const uint16_
         int device = 0, sm_count = 0;
         CSDR_CUDA(cudaGetDevice(&device));
         CSDR_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
-        float* dx = noalloc_scratch(device);  // first call on a device looks the address up
+        const NoAllocScratch sc = noalloc_scratch(device);  // first call on a device looks the addresses up
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         // token tile: the widest power of two <= 16 whose x slab fits in 200 KiB of shared memory
         uint32_t nsplit = std::min<uint32_t>(8u, std::max<uint32_t>(1u, (cols + 1023u) / 1024u));
@@ -805,13 +824,32 @@ extern "C" int csdr_matmul_rowtiles_noalloc(const float* dict_dev, const uint16_
             XView xv{x_dev, x_dtype, x_layout, cols, static_cast<uint32_t>(batch), static_cast<uint32_t>(b0), m};
             YView yv{y_dev, y_layout, rows, static_cast<uint32_t>(batch), static_cast<uint32_t>(b0), m, nullptr};
             switch (pick_mt(m)) {
-                case 1: noalloc_chunk<1, 1, 8>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
-                case 2: noalloc_chunk<2, 1, 8>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
-                case 4: noalloc_chunk<4, 2, 4>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
-                case 8: noalloc_chunk<8, 4, 2>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
-                default: noalloc_chunk<16, 4, 2>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, dx, sm_count, st); break;
+                case 1: noalloc_chunk<1, 1, 8>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, sc.dx, sc.status, sm_count, st); break;
+                case 2: noalloc_chunk<2, 1, 8>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, sc.dx, sc.status, sm_count, st); break;
+                case 4: noalloc_chunk<4, 2, 4>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, sc.dx, sc.status, sm_count, st); break;
+                case 8: noalloc_chunk<8, 4, 2>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, sc.dx, sc.status, sm_count, st); break;
+                default: noalloc_chunk<16, 4, 2>(dict_dev, codes_dev, scales_dev, rows, cols, n_atoms, n_stages, k_per_stage, xv, yv, sc.dx, sc.status, sm_count, st); break;
             }
         }
     });
 }
 
+
+extern "C" int csdr_matmul_rowtiles_noalloc_status(void* stream, int* bad_codes) {
+    using namespace csdr;
+    return guard([&] {
+        if (!bad_codes) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        int device = 0;
+        CSDR_CUDA(cudaGetDevice(&device));
+        const NoAllocScratch sc = noalloc_scratch(device);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        int word = 0;
+        CSDR_CUDA(cudaMemcpyAsync(&word, sc.status, sizeof(int), cudaMemcpyDeviceToHost, st));
+        CSDR_CUDA(cudaMemsetAsync(sc.status, 0, sizeof(int), st));
+        CSDR_CUDA(cudaStreamSynchronize(st));
+        *bad_codes = word != 0;
+        if (word != 0)
+            throw Error(CSDR_ERR_CODE_RANGE, "csdr_matmul_rowtiles_noalloc: a packed code named an atom >= n_atoms "
+                                             "(it contributed nothing to its row)");
+    });
+}

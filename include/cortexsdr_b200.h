@@ -91,6 +91,20 @@ CSDR_API void* csdr_context_stream(csdr_context* ctx);
 /* Number of kernels this library has launched on the context since creation. */
 CSDR_API uint64_t csdr_context_launch_count(const csdr_context* ctx);
 
+/* Iteration limits of the device-side waits (no counterpart in the reference, which has no
+ * device). Every wait inside a kernel is a bounded poll: the fused decode GEMV's hand-over of
+ * partial results, the mbarrier waits of the tensor-core kernels, and a tensor-parallel rank's
+ * wait for its peers' flags. A wait that runs out records a status word, the kernel returns, and
+ * the next csdr_context_synchronize answers CSDR_ERR_TIMEOUT; the context stays usable. 0 keeps
+ * or restores a default (1e6 polls, 4e6 rounds, 2e6 polls: of the order of a second each). */
+CSDR_API int csdr_context_set_wait_limits(csdr_context* ctx, uint32_t gemv_polls,
+                                          uint32_t barrier_rounds, uint32_t exchange_polls);
+/* Diagnostic: runs the receiving side of a two-rank exchange on a scratch region whose second
+ * flag nothing ever raises, then synchronizes. Answers CSDR_ERR_TIMEOUT once the exchange
+ * limit is spent (set a small one first) - the proof that a lost peer surfaces as an error code
+ * rather than as a hung device. */
+CSDR_API int csdr_context_wait_selftest(csdr_context* ctx);
+
 /* Per-kernel device timing for benchmarks. While enabled, every kernel this library
  * launches on the context is bracketed by two CUDA events on the context's stream;
  * csdr_context_profile_read then gives, for one kernel class (0 <= cls < the count
@@ -186,14 +200,22 @@ CSDR_API int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segmen
  * reference: it exists for hosts that cannot call cudaMalloc while they run - a process
  * whose device memory map is frozen after start-up (real-time or certified systems), a
  * plug-in that lives inside another runtime's memory pool and owns no allocator of its own,
- * or a service that has handed all device memory to its own arena. This call allocates nothing, on the host or the device: no
- * cudaMalloc, no cudaFree, no library routine that allocates. Every buffer is the caller's,
+ * or a service that has handed all device memory to its own arena. This call makes no device
+ * allocation: no cudaMalloc, no cudaFree, no library routine that allocates device memory (on
+ * the host the success path allocates nothing either; an error builds its message string).
+ * What the CUDA driver does on its own account still happens once: with lazy module loading the
+ * first launch of each kernel variant - one per token-tile width 1, 2, 4, 8, 16, chosen from the
+ * batch - and the first address look-up load code onto the device. So warm up, before the memory
+ * map freezes and before any stream capture, with one call per tile width the caller will use
+ * (batches 1, 2, 4, 8 and 16 cover them all). Every buffer is the caller's,
  * as raw device pointers taken straight from a payload's streams:
  *   dict_dev    n_atoms x cols fp32 (the "HSDR" dictionary stream), 16-byte aligned
  *   codes_dev   rows x n_stages x k_per_stage packed u16 codes, 16-byte aligned, in an
  *               allocation whose length is rounded up to 16 bytes (kernels read it in
- *               128-bit units); every code must name an atom < n_atoms (csdr_payload_inspect
- *               checks that on the host)
+ *               128-bit units); every code should name an atom < n_atoms (csdr_payload_inspect
+ *               checks that on the host). A code that does not is skipped - it adds nothing to
+ *               its row, nothing is read out of bounds - and is reported by
+ *               csdr_matmul_rowtiles_noalloc_status
  *   scales_dev  n_stages fp32
  *   x_dev/y_dev activations and fp32 output, dtype and layouts as for csdr_matmul_device_async
  * The one piece of scratch the two-kernel path needs (Dx, n_atoms x 16 floats) sits in a
@@ -210,6 +232,10 @@ CSDR_API int csdr_matmul_rowtiles_noalloc(const float* dict_dev, const uint16_t*
                                           uint32_t n_atoms, uint32_t n_stages, uint32_t k_per_stage,
                                           const void* x_dev, int x_dtype, int x_layout, size_t batch,
                                           float* y_dev, int y_layout, void* stream);
+/* Waits for `stream`, then tells whether any allocation-free call on this device since the last
+ * query met a code naming an atom >= n_atoms: *bad_codes = 1 and CSDR_ERR_CODE_RANGE if so
+ * (the flag is cleared), else 0 and CSDR_OK. Allocates nothing. No counterpart in the reference. */
+CSDR_API int csdr_matmul_rowtiles_noalloc_status(void* stream, int* bad_codes);
 
 /* ---- materialise the weight ----
  * HierarchicalSDRStrategy::decompress (:1340) / ::decompressWithExternalDictionary

@@ -338,3 +338,54 @@ def test_chained_launches_are_ordered(ctx, oracle, golden):
         v = oracle.matmul(p2, oracle.matmul(p1, v, 1), 1)
     e = rel_err(a.cpu().numpy().T, v)
     assert e[0] < 1e-3, e
+
+
+def test_graph_replay_sees_new_activations(ctx, oracle):
+    # One fused GEMV captured in a CUDA graph, replayed with x changed in place between the
+    # replays: the hand-over tag is advanced on the device, so no replay may accept the
+    # partial results an earlier replay left in the scratch words.
+    import torch
+    from tests import synth
+    pay = synth.hsdr_payload(768, 2048, n_atoms=256, k=6, seed=90)
+    stream = torch.cuda.Stream()
+    c = cs.Context(0, stream.cuda_stream)
+    seg = cs.Segment.from_payload(pay, c)
+    x = torch.zeros((1, 2048), device="cuda")
+    y = torch.zeros((1, 768), device="cuda")
+    rng = np.random.default_rng(12)
+    with torch.cuda.stream(stream):
+        seg.matmul_device(x.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 1, y.data_ptr(), cs.TOKEN_MAJOR)
+        c.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            seg.matmul_device(x.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 1, y.data_ptr(), cs.TOKEN_MAJOR)
+        for i in range(6):
+            xh = rng.normal(0, 1 + i, (1, 2048)).astype(np.float32)
+            x.copy_(torch.from_numpy(xh), non_blocking=False)
+            g.replay()
+            c.synchronize()
+            want = oracle.matmul(pay, np.ascontiguousarray(xh.T), 1).T
+            e = rel_err(y.cpu().numpy(), want)
+            assert e[0] < TOL and e[1] < TOL, (i, e)
+    seg.close()
+    c.close()
+
+
+def test_a_wait_that_runs_out_is_an_error_code_not_a_hang(lib, oracle, golden):
+    # The receiving side of a tensor-parallel exchange waits on a flag that nothing raises; with
+    # a limit of a thousand polls it gives up within microseconds, the next synchronize says
+    # TIMEOUT, and the same context computes correctly afterwards.
+    from cortexsdr_b200 import _lib
+    c = cs.Context(0)
+    c.set_wait_limits(exchange_polls=1000)
+    assert c.wait_selftest() == _lib.ERR_TIMEOUT
+    assert b"wait ran out" in lib.csdr_last_error()
+    c.set_wait_limits()            # defaults again
+    c.synchronize()                # the status word was cleared with the report
+    g = golden("fused_rowtile.npz")
+    seg = cs.Segment.from_payload(g["payload"], c)
+    x = np.random.default_rng(5).normal(0, 1, (512, 3)).astype(np.float32)
+    e = rel_err(seg.matmul(x, 3), oracle.matmul(g["payload"], x, 3))
+    assert e[0] < TOL and e[1] < TOL
+    seg.close()
+    c.close()
