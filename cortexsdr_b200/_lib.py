@@ -104,6 +104,8 @@ SIGNATURES = {
     "csdr_archive_read_payload": (C.c_int, [_P, C.c_char_p, _P, _SZ, C.POINTER(_SZ)]),
     "csdr_archive_load_segment": (C.c_int, [_P, C.c_char_p, _P, _SZ, C.POINTER(_SZ)]),
     "csdr_archive_segment": (C.c_int, [_P, C.c_char_p, C.POINTER(_P)]),
+    "csdr_archive_release": (C.c_int, [_P, C.c_char_p]),
+    "csdr_archive_resident_bytes": (C.c_int, [_P, C.POINTER(_SZ)]),
     "csdr_archive_matmul_hsdr": (C.c_int, [_P, C.c_char_p, _F, _SZ, _F, _SZ, C.POINTER(_SZ)]),
     "csdr_archive_matmul_for_layer": (C.c_int, [_P, C.c_char_p, _F, _SZ, _F, _SZ, C.POINTER(_SZ)]),
     "csdr_archive_apply_linear": (C.c_int, [_P, C.c_char_p, _F, _SZ, _F, _F, _SZ, C.POINTER(_SZ)]),

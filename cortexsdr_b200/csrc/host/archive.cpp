@@ -179,6 +179,37 @@ int csdr_archive_segment(csdr_archive* ar, const char* name, const csdr_segment*
     });
 }
 
+int csdr_archive_release(csdr_archive* ar, const char* name) {
+    return guard([&] {
+        if (!ar) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (!name) {
+            for (auto& kv : ar->images) csdr_segment_destroy(kv.second);
+            ar->images.clear();
+            ar->raw.clear();
+            return;
+        }
+        auto it = ar->images.find(name);
+        if (it != ar->images.end()) {
+            csdr_segment_destroy(it->second);
+            ar->images.erase(it);
+        }
+        ar->raw.erase(name);
+    });
+}
+
+int csdr_archive_resident_bytes(const csdr_archive* ar, size_t* bytes) {
+    return guard([&] {
+        if (!ar || !bytes) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        size_t n = 0;
+        for (const auto& kv : ar->images) {
+            const csdr_segment* sg = kv.second;
+            n += sg->atoms->bytes + sg->codes->bytes + sg->scales->bytes + (sg->edges ? sg->edges->bytes : 0);
+        }
+        for (const auto& kv : ar->raw) n += kv.second->bytes;
+        *bytes = n;
+    });
+}
+
 int csdr_archive_load_segment(csdr_archive* ar, const char* name, void* buf, size_t capacity,
                               size_t* n) {
     return guard([&] {

@@ -15,9 +15,14 @@
  *   - error messages are owned by the library (thread-local; valid until the next call on
  *     the same thread) — never free them;
  *   - strings handed to the caller (stats JSON) are malloc'ed; release with cortex_free_string;
- *   - only LINEAR layers backed by HSDR segments (strategy id 5) run; whole-graph `run` and
- *     text generation (tokenizer, sampling policy) are outside this library and answer
- *     CORTEX_B200_ERROR_UNSUPPORTED_FORMAT.
+ *   - layers are LINEAR layers backed by HSDR segments (strategy id 5) or raw fp32 2-D
+ *     weights; `run` applies the archive's 2-D weights in index order, each feeding the next
+ *     (the reference's interpreter over a LINEAR-only graph);
+ *   - this library has no tokenizer: `generate_text` takes the prompt as decimal token ids
+ *     separated by blanks and returns the generated ids the same way. The loop, the decoder
+ *     shape discovery and the token selection (temperature 0.8, 1.5 off tokens already
+ *     generated, first maximum) follow api/cortex_sdk.cpp:1951-2054, :1335-1349, :1005-1030,
+ *     on the transformer path with a KV cache.
  */
 #ifndef CORTEX_SDK_B200_H
 #define CORTEX_SDK_B200_H
@@ -59,7 +64,10 @@ typedef struct CortexInferenceEngine* CortexInferenceEngineHandle;
 /* cortex_sdk.h:110 — opens the .sdr index; segments go to the device on first use. */
 CORTEXSDR_API CortexError cortex_inference_engine_create(const char* compressed_model_path,
                                                          CortexInferenceEngineHandle* handle);
-/* cortex_sdk.h:118-169 — engine settings; accepted and recorded. */
+/* cortex_sdk.h:118-169 — engine settings. batch size: what `run` expects (0 = from the input);
+ * mode/dropout: recorded, `run` refuses training with dropout; memory pool: MiB budget for
+ * cached device images; aggressive memory: a layer's image is dropped once it has run;
+ * layer prefetch: every HSDR segment is uploaded now. */
 CORTEXSDR_API CortexError cortex_inference_engine_set_batch_size(CortexInferenceEngineHandle handle, size_t batch_size);
 CORTEXSDR_API CortexError cortex_inference_engine_enable_dropout(CortexInferenceEngineHandle handle, int enable);
 CORTEXSDR_API CortexError cortex_inference_engine_set_mode(CortexInferenceEngineHandle handle, int training_mode);
@@ -68,10 +76,10 @@ CORTEXSDR_API CortexError cortex_inference_engine_enable_aggressive_memory(Corte
 /* cortex_sdk.h:158 — bytes of device memory held by uploaded segments. */
 CORTEXSDR_API CortexError cortex_inference_engine_get_memory_usage(CortexInferenceEngineHandle handle, size_t* bytes);
 CORTEXSDR_API CortexError cortex_inference_engine_enable_layer_prefetch(CortexInferenceEngineHandle handle, int enable);
-/* cortex_sdk.h:174 — {"layers":[{"name","exec_ms","used_compressed"}...]} of the last call. */
+/* cortex_sdk.h:174 — {"total_ms", "layers":[{"name","load_ms","exec_ms","output_size","used_compressed"}...]}. */
 CORTEXSDR_API CortexError cortex_inference_engine_get_last_run_stats_json(CortexInferenceEngineHandle handle, char** out_json);
 CORTEXSDR_API void cortex_free_string(char* s);
-/* cortex_sdk.h:192 — whole-graph interpreter: not on this path. */
+/* cortex_sdk.h:192 — the archive's 2-D weights in index order, token-major (batch x width). */
 CORTEXSDR_API CortexError cortex_inference_engine_run(CortexInferenceEngineHandle handle, const float* input_data,
                                                       size_t input_size, float* output_data, size_t output_size,
                                                       size_t* actual_output_size);
@@ -81,7 +89,7 @@ CORTEXSDR_API CortexError cortex_inference_engine_run_layer(CortexInferenceEngin
                                                             const float* input_data, size_t input_size,
                                                             float* output_data, size_t output_size,
                                                             size_t* actual_output_size);
-/* cortex_sdk.h:220 — needs the tokenizer and sampling policy: not on this path. */
+/* cortex_sdk.h:220 — token ids in, token ids out (see above); release with cortex_free_string. */
 CORTEXSDR_API CortexError cortex_inference_engine_generate_text(CortexInferenceEngineHandle handle, const char* prompt,
                                                                 int max_new_tokens, char** out_text);
 CORTEXSDR_API CortexError cortex_inference_engine_free(CortexInferenceEngineHandle handle);

@@ -284,6 +284,14 @@ CSDR_API int csdr_archive_load_segment(csdr_archive* ar, const char* name, void*
 /* Device image of a named HSDR segment, uploaded on first use and cached — the step the
  * reference repeats per call (file open + payload read + two copies). Owned by the archive. */
 CSDR_API int csdr_archive_segment(csdr_archive* ar, const char* name, const csdr_segment** seg);
+/* Drops the cached device image of `name` (NULL: of every segment); the next use uploads it
+ * again. The reference's counterpart is its layer cache's eviction
+ * (aggressive memory management, SparseInferenceEngine.hpp:414, :455).
+ * Images handed out by csdr_archive_segment are dangling after this. */
+CSDR_API int csdr_archive_release(csdr_archive* ar, const char* name);
+/* Device bytes held by the archive's cached images (dictionaries, codes, scales, edge strips,
+ * raw matrices) - SDRInferenceEngine::getCurrentMemoryUsage (SparseInferenceEngine.hpp:415). */
+CSDR_API int csdr_archive_resident_bytes(const csdr_archive* ar, size_t* bytes);
 /* SDRModelLoader::matmulHSDR (:1074): errors mirror the reference's
  * ("segment not found" -> CSDR_ERR_NOT_FOUND, "is not HSDR-encoded" -> CSDR_ERR_STRATEGY,
  * 2-D tiles -> CSDR_ERR_GEOMETRY). y_capacity in floats; *n_out = R*batch. */
