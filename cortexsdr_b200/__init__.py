@@ -394,6 +394,22 @@ class HierarchicalSDRStrategy:
         return out[:n.value].copy()
 
 
+def dequantize_inference(data, data_format: str, n_elements: int | None = None, ctx: Context | None = None) -> np.ndarray:
+    """A stored-raw tensor in a GGUF block format, widened the way the reference's inference side
+    does it (decodeSupportedGGUFQuantized, SparseInferenceEngine.cpp:276-469)."""
+    ctx = ctx or default_context()
+    p = _bytes(data)
+    bb, be = {"q4_0": (18, 32), "q8_0": (34, 32), "q4_k": (144, 256), "q5_k": (176, 256),
+              "q6_k": (210, 256)}.get(data_format.lower(), (1, 0))
+    cap = p.size // bb * be
+    out = np.empty(max(cap, 1), np.float32)
+    n = C.c_size_t()
+    _check(ctx._lib.csdr_dequantize_inference(ctx._h, data_format.lower().encode(), p.ctypes.data_as(C.c_void_p), p.size,
+                                              cap if n_elements is None else n_elements, _fp(out), out.size,
+                                              C.byref(n)))
+    return out[:n.value].copy()
+
+
 @dataclass
 class CompressedSegmentHeader:
     """core/AICompressor.hpp:51-65"""

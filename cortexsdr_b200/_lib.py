@@ -96,6 +96,7 @@ SIGNATURES = {
     "csdr_decompress_device_async": (C.c_int, [_P, _P, _P]),
     "csdr_dequantize": (C.c_int, [_P, C.c_char_p, _P, _SZ, C.c_float, C.c_float, _F, _SZ,
                                   C.POINTER(_SZ)]),
+    "csdr_dequantize_inference": (C.c_int, [_P, C.c_char_p, _P, _SZ, _SZ, _F, _SZ, C.POINTER(_SZ)]),
     "csdr_archive_open": (C.c_int, [_P, C.c_char_p, C.POINTER(_P)]),
     "csdr_archive_close": (C.c_int, [_P]),
     "csdr_archive_num_segments": (C.c_int, [_P, C.POINTER(_SZ)]),

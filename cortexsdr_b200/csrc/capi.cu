@@ -758,4 +758,30 @@ int csdr_dequantize(csdr_context* ctx, const char* fmt, const void* data, size_t
     });
 }
 
+int csdr_dequantize_inference(csdr_context* ctx, const char* fmt, const void* data, size_t nbytes,
+                              size_t n_elements, float* out_host, size_t capacity_floats, size_t* n_out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!data || !out_host) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        const int id = dequant_format_id(fmt);
+        if (id < 4)   // q4_0, q8_0, q4_k, q5_k, q6_k
+            throw Error(CSDR_ERR_UNSUPPORTED, std::string("unsupported block format '") + (fmt ? fmt : "") +
+                                                  "'; supported: q4_0, q8_0, q4_k, q5_k, q6_k");
+        static const size_t unit[] = {18, 34, 144, 176, 210};
+        const size_t bb = unit[id - 4], be = id < 6 ? 32 : 256;
+        if (nbytes < bb) throw Error(CSDR_ERR_FORMAT, "fewer bytes than one block");
+        // whole blocks only, trailing bytes ignored, count clipped to n_elements (:297-306)
+        const size_t whole = nbytes / bb * bb;
+        const size_t n = std::min(n_elements, whole / bb * be);
+        if (n_out) *n_out = n;
+        if (capacity_floats < n) throw Error(CSDR_ERR_BUFFER, "dequantize output buffer too small");
+        const size_t in_off = (whole / bb * be * 4 + 255) & ~static_cast<size_t>(255);
+        unsigned char* buf = static_cast<unsigned char*>(ctx->scratch_get(2, in_off + whole + 16));
+        CSDR_CUDA(cudaMemcpyAsync(buf + in_off, data, whole, cudaMemcpyHostToDevice, ctx->stream));
+        launch_dequantize_inference(ctx, id, buf + in_off, whole, n, reinterpret_cast<float*>(buf));
+        CSDR_CUDA(cudaMemcpyAsync(out_host, buf, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
 }  // extern "C"

@@ -197,8 +197,10 @@ Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint
             throw Error(CSDR_ERR_UNSUPPORTED, "decoder: tensor-parallel decoding needs HSDR-encoded linears ('" + name +
                                                   "' is stored raw)");
         // stored as it came from the model file: fp32, or a source dtype (f16, bf16, q4_0, q8_0,
-        // q4_k, q5_k, q6_k) that is widened to fp32 on the device once, with the kernels of
-        // dequantizeSegmentToFP32 (strategies/HierarchicalSDRStrategy.cpp:713-989)
+        // q4_k, q5_k, q6_k) that is widened to fp32 on the device once, in the element order of
+        // the reference's inference side (decodeSupportedGGUFQuantized,
+        // SparseInferenceEngine.cpp:276-469) - ggml's order for the k-quants, which differs from
+        // the order the encoder's dequantizeSegmentToFP32 assumes
         std::string fmt = h.data_format ? h.data_format : "";
         for (char& ch : fmt) ch = static_cast<char>(std::tolower(static_cast<unsigned char>(ch)));
         const size_t want = static_cast<size_t>(rows) * cols;
@@ -221,8 +223,8 @@ Linear load_linear(csdr_decoder* d, const std::string& name, uint32_t rows, uint
                 throw Error(CSDR_ERR_GEOMETRY, "tensor '" + name + "' is smaller than the decoder config needs");
             DevPtr packed = upload(d->ctx, bytes.data(), nbytes);
             l.raw = dev_alloc(d->ctx, dequant_output_count(id, nbytes) * 4);
-            launch_dequantize(d->ctx, id, static_cast<const uint8_t*>(packed->ptr), nbytes, dequant_output_count(id, nbytes),
-                              1.0f, 0.0f, F(l.raw));
+            launch_dequantize_inference(d->ctx, id, static_cast<const uint8_t*>(packed->ptr), nbytes,
+                                        dequant_output_count(id, nbytes), F(l.raw));
         }
         CSDR_CUDA(cudaStreamSynchronize(d->ctx->stream));
     } else {

@@ -190,6 +190,10 @@ void launch_decode_rows(csdr_context* ctx, const csdr_segment* seg, const int32_
 
 void launch_dequantize(csdr_context* ctx, int fmt_id, const uint8_t* data_dev, size_t nbytes,
                        size_t n_out, float scale, float zero_point, float* out_dev);
+// The same source dtypes as the reference's inference side widens a stored-raw tensor
+// (SparseInferenceEngine.cpp:276-469): ggml's element order for q4_k / q5_k / q6_k.
+void launch_dequantize_inference(csdr_context* ctx, int fmt_id, const uint8_t* data_dev, size_t nbytes, size_t n_out,
+                                 float* out_dev);
 int dequant_format_id(const char* fmt);               // -1 when unknown
 size_t dequant_output_count(int fmt_id, size_t nbytes);  // throws on bad size
 

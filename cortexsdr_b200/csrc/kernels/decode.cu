@@ -174,6 +174,63 @@ dequant_kquant_kernel(int fmt, const uint8_t* __restrict__ data, size_t n_blocks
     }
 }
 
+// Stored-raw k-quant tensors as the reference's INFERENCE side widens them
+// (decodeSupportedGGUFQuantized, SparseInferenceEngine.cpp:276-469): ggml's element order, not
+// the encoder's. One thread per output element, 256 elements per super-block.
+//   q4_k (:362-383)  64-element groups: 32 low nibbles under scale 2g, then 32 high nibbles
+//                    under scale 2g+1; (d*sc)*q - dmin*mn
+//   q6_k (:329-360)  128-element halves, four runs of 32: low nibbles of ql[0..31], of ql[32..63],
+//                    then the high nibbles; two bits of qh[l] each; d * float(sc[2r] * (q - 32))
+//   q5_k (:437-463)  the generic fall-back: 5-bit fields packed from byte 16, (q - 16) * d, with
+//                    d replaced by 1 when it is not finite or below 1e-12
+__global__ void __launch_bounds__(256)
+dequant_inference_kquant_kernel(int fmt, const uint8_t* __restrict__ data, size_t n_out, float* __restrict__ out) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n_out; i += stride) {
+        const size_t blk = i >> 8;
+        const uint32_t e = static_cast<uint32_t>(i & 255u);
+        float v;
+        if (fmt == Q4_K) {
+            const uint8_t* p = data + blk * 144;
+            const float d = ld_half(p), dmin = ld_half(p + 2);
+            const uint8_t* s12 = p + 4;
+            const uint32_t g = e >> 6, hi = (e >> 5) & 1u, l = e & 31u, j = 2u * g + hi;
+            uint32_t sc, mn;
+            if (j < 4) {
+                sc = s12[j] & 0x3Fu;
+                mn = s12[j + 4] & 0x3Fu;
+            } else {
+                sc = (s12[j + 4] & 0x0Fu) | ((s12[j - 4] >> 6) << 4);
+                mn = (s12[j + 4] >> 4) | ((s12[j] >> 6) << 4);
+            }
+            const uint8_t byte = p[16 + g * 32 + l];
+            const uint32_t q = hi ? (byte >> 4) : (byte & 0x0Fu);
+            v = __fsub_rn(__fmul_rn(__fmul_rn(d, static_cast<float>(sc)), static_cast<float>(q)),
+                          __fmul_rn(dmin, static_cast<float>(mn)));
+        } else if (fmt == Q6_K) {
+            const uint8_t* p = data + blk * 210;
+            const float d = ld_half(p + 208);
+            const uint32_t half = e >> 7, r = (e >> 5) & 3u, l = e & 31u;
+            const uint8_t lb = p[half * 64 + l + (r & 1u) * 32u];
+            const uint32_t lo = r >= 2 ? (lb >> 4) : (lb & 0x0Fu);
+            const uint32_t hi2 = (p[128 + half * 32 + l] >> (2u * r)) & 3u;
+            const int q = static_cast<int>(lo | (hi2 << 4)) - 32;
+            const int sc = static_cast<int8_t>(p[192 + half * 8 + 2u * r]);
+            v = __fmul_rn(d, static_cast<float>(sc * q));
+        } else {  // Q5_K
+            const uint8_t* p = data + blk * 176;
+            float d = ld_half(p);
+            if (!isfinite(d) || fabsf(d) < 1e-12f) d = 1.0f;
+            const uint32_t bit = e * 5u;
+            const uint8_t* f = p + 16 + (bit >> 3);
+            const uint32_t two = static_cast<uint32_t>(f[0]) | (static_cast<uint32_t>((bit >> 3) + 1u < 160u ? f[1] : 0u) << 8);
+            const int q = static_cast<int>((two >> (bit & 7u)) & 31u) - 16;
+            v = __fmul_rn(static_cast<float>(q), d);
+        }
+        out[i] = v;
+    }
+}
+
 }  // namespace
 
 void launch_decode_rows(csdr_context* ctx, const csdr_segment* seg, const int32_t* rows_dev,
@@ -217,6 +274,20 @@ size_t dequant_output_count(int fmt, size_t nbytes) {
                                  "Q6_K byte size not a multiple of 210"};
     if (nbytes % unit[fmt]) throw Error(CSDR_ERR_FORMAT, std::string("HSDR dequant: ") + what[fmt]);
     return nbytes / unit[fmt] * per[fmt];
+}
+
+void launch_dequantize_inference(csdr_context* ctx, int fmt, const uint8_t* data_dev, size_t nbytes, size_t n_out,
+                                 float* out_dev) {
+    if (n_out == 0) return;
+    if (fmt < Q4_K) {   // sequential formats: both sides of the reference agree on them
+        launch_dequantize(ctx, fmt, data_dev, nbytes, n_out, 1.0f, 0.0f, out_dev);
+        return;
+    }
+    LaunchScope ls(ctx, KC_DEQUANT);
+    const unsigned grid = static_cast<unsigned>(
+        std::min<size_t>((n_out + 255) / 256, static_cast<size_t>(ctx->sm_count) * 16));
+    dequant_inference_kquant_kernel<<<grid, 256, 0, ctx->stream>>>(fmt, data_dev, n_out, out_dev);
+    ls.done("dequant_inference_kquant_kernel");
 }
 
 void launch_dequantize(csdr_context* ctx, int fmt, const uint8_t* data_dev, size_t nbytes,

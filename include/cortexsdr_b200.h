@@ -253,6 +253,17 @@ CSDR_API int csdr_dequantize(csdr_context* ctx, const char* fmt, const void* dat
                              size_t nbytes, float scale, float zero_point, float* out_host,
                              size_t capacity_floats, size_t* n_out);
 
+/* The same block formats as the reference's INFERENCE side widens a stored-raw tensor
+ * (decodeSupportedGGUFQuantized, SparseInferenceEngine.cpp:276-469): ggml's element order -
+ * q4_k: 32 low nibbles then 32 high nibbles per 64-element group; q6_k: four runs of 32 per
+ * 128-element half; q5_k: that function's generic 5-bit fall-back; q4_0, q8_0 sequential.
+ * fmt: "q4_0","q8_0","q4_k","q5_k","q6_k". Whole blocks only; at most n_elements values.
+ * This is what the decoder applies to strategy-0 tensors; csdr_dequantize above is what the
+ * ENCODER applies to its inputs, and the two orders differ for the k-quants. */
+CSDR_API int csdr_dequantize_inference(csdr_context* ctx, const char* fmt, const void* data,
+                                       size_t nbytes, size_t n_elements, float* out_host,
+                                       size_t capacity_floats, size_t* n_out);
+
 /* ---- .sdr archive: SDRModelLoader / SDRInferenceEngine routing ---- */
 typedef struct {
     const char* name;           /* owned by the archive */

@@ -18,6 +18,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "liboracle_hsdr.so")
 REF_SO = os.path.join(_HERE, "_ref", "libcortexsdr_ref.so")
+REF_ENGINE_SO = os.path.join(_HERE, "_ref", "libcortexsdr_ref_engine.so")
 
 # SegmentType values, core/ModelSegment.hpp:36-55 of the reference.
 SEG_WEIGHTS_FP32 = 1
@@ -45,7 +46,7 @@ def build(ref: bool = True) -> None:
     subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
     tree = reference_tree() if ref else None
     if tree:
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + tree])
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "ref_engine", "REF=" + tree])
 
 
 def _f32(a):
@@ -222,6 +223,20 @@ class Oracle:
                                     C.c_size_t(cap))
         if n < 0:
             raise ValueError(f"orc_dequantize rc={n}")
+        return out[:n].copy()
+
+    def dequantize_inference(self, fmt, data, n_elements=None):
+        """Stored-raw tensor in a GGUF block format as the reference's inference side widens it."""
+        p = self._bytes(data)
+        bb, be = {"q4_0": (18, 32), "q8_0": (34, 32), "q4_k": (144, 256), "q5_k": (176, 256), "q6_k": (210, 256)}[fmt]
+        cap = p.size // bb * be
+        n_elements = cap if n_elements is None else n_elements
+        out = np.empty(max(cap, 1), np.float32)
+        self.lib.orc_dequantize_inference.restype = C.c_long
+        n = self.lib.orc_dequantize_inference(fmt.encode(), _ptr(p, C.c_uint8), C.c_size_t(p.size),
+                                              C.c_size_t(n_elements), _ptr(out), C.c_size_t(cap))
+        if n < 0:
+            raise ValueError(f"orc_dequantize_inference rc={n}")
         return out[:n].copy()
 
     def rms_norm(self, x, w, eps):
@@ -541,3 +556,25 @@ class Reference:
         if n < 0:
             raise self._err("matmulHSDR")
         return y
+
+
+class ReferenceEngine:
+    """The reference's inference engine (SDRModelLoader) behind ref_engine_shim.cpp, where built."""
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_ENGINE_SO)
+
+    def __init__(self):
+        self.lib = C.CDLL(REF_ENGINE_SO)
+        self.lib.ref_engine_last_error.restype = C.c_char_p
+
+    def layer_weights(self, path: str, name: str) -> np.ndarray:
+        """fp32 weights of a layer as SDRModelLoader::loadLayerByName decodes them."""
+        n = C.c_size_t()
+        if self.lib.ref_engine_layer_weights(path.encode(), name.encode(), None, C.c_size_t(0), C.byref(n)):
+            raise RuntimeError(self.lib.ref_engine_last_error().decode())
+        out = np.empty(n.value, np.float32)
+        if self.lib.ref_engine_layer_weights(path.encode(), name.encode(), _ptr(out), C.c_size_t(out.size), C.byref(n)):
+            raise RuntimeError(self.lib.ref_engine_last_error().decode())
+        return out

@@ -623,3 +623,105 @@ long orc_dequantize(const char* fmt, const uint8_t* p, size_t nbytes, float scal
     }
     return -3;
 }
+
+/* ---- SparseInferenceEngine.cpp:252-469: stored-raw GGUF block formats as the inference side
+ * decodes them ---- */
+static void gguf_scale_min_q4k(const uint8_t* scales, size_t j, uint8_t* sc, uint8_t* mn) {   /* :262-273 */
+    if (j < 4) {
+        *sc = (uint8_t)(scales[j] & 0x3F);
+        *mn = (uint8_t)(scales[j + 4] & 0x3F);
+    } else {
+        *sc = (uint8_t)((scales[j + 4] & 0x0F) | ((scales[j - 4] >> 6) << 4));
+        *mn = (uint8_t)((scales[j + 4] >> 4) | ((scales[j] >> 6) << 4));
+    }
+}
+
+static uint32_t read_bits_lsb(const uint8_t* bytes, size_t bit_offset, size_t bit_count) {     /* :250-260 */
+    uint32_t v = 0;
+    for (size_t b = 0; b < bit_count; ++b) {
+        const size_t a = bit_offset + b;
+        v |= (uint32_t)((bytes[a / 8] >> (a % 8)) & 1u) << b;
+    }
+    return v;
+}
+
+long orc_dequantize_inference(const char* fmt, const uint8_t* data, size_t nbytes, size_t n_elements,
+                              float* out, size_t cap) {
+    size_t bb = 0, be = 0;
+    if (!strcmp(fmt, "q4_0")) { bb = 18; be = 32; }
+    else if (!strcmp(fmt, "q8_0")) { bb = 34; be = 32; }
+    else if (!strcmp(fmt, "q4_k")) { bb = 144; be = 256; }
+    else if (!strcmp(fmt, "q5_k")) { bb = 176; be = 256; }
+    else if (!strcmp(fmt, "q6_k")) { bb = 210; be = 256; }
+    else return -3;
+    if (nbytes < bb) return -1;                                   /* :289-291 */
+    const size_t blocks = nbytes / bb;
+    size_t count = blocks * be;
+    if (n_elements < count) count = n_elements;                   /* :305 */
+    if (count > cap) return -2;
+    size_t o = 0;
+    for (size_t bi = 0; bi < blocks && o < count; ++bi) {
+        const uint8_t* blk = data + bi * bb;
+        if (bb == 34) {                                           /* q8_0 :311-318 */
+            const float d = orc_fp16_to_fp32(rd16(blk));
+            for (size_t i = 0; i < 32 && o < count; ++i) out[o++] = (float)(int8_t)blk[2 + i] * d;
+        } else if (bb == 210) {                                   /* q6_k :329-360 */
+            const uint8_t* ql = blk;
+            const uint8_t* qh = blk + 128;
+            const int8_t* scales = (const int8_t*)(blk + 192);
+            const float d = orc_fp16_to_fp32(rd16(blk + 208));
+            for (size_t half = 0; half < 2 && o < count; ++half) {
+                const uint8_t* qlh = ql + half * 64;
+                const uint8_t* qhh = qh + half * 32;
+                const int8_t* sch = scales + half * 8;
+                for (size_t l = 0; l < 32 && o < count; ++l) {
+                    const int q = (int)((qlh[l] & 0x0F) | (((qhh[l] >> 0) & 3) << 4)) - 32;
+                    out[o++] = d * (float)(sch[0] * q);
+                }
+                for (size_t l = 0; l < 32 && o < count; ++l) {
+                    const int q = (int)((qlh[l + 32] & 0x0F) | (((qhh[l] >> 2) & 3) << 4)) - 32;
+                    out[o++] = d * (float)(sch[2] * q);
+                }
+                for (size_t l = 0; l < 32 && o < count; ++l) {
+                    const int q = (int)(((qlh[l] >> 4) & 0x0F) | (((qhh[l] >> 4) & 3) << 4)) - 32;
+                    out[o++] = d * (float)(sch[4] * q);
+                }
+                for (size_t l = 0; l < 32 && o < count; ++l) {
+                    const int q = (int)(((qlh[l + 32] >> 4) & 0x0F) | (((qhh[l] >> 6) & 3) << 4)) - 32;
+                    out[o++] = d * (float)(sch[6] * q);
+                }
+            }
+        } else if (bb == 144) {                                   /* q4_k :362-383 */
+            const float d = orc_fp16_to_fp32(rd16(blk));
+            const float dmin = orc_fp16_to_fp32(rd16(blk + 2));
+            const uint8_t* scales = blk + 4;
+            const uint8_t* qs = blk + 16;
+            for (size_t g = 0; g < 4 && o < count; ++g) {
+                uint8_t s0, m0, s1, m1;
+                gguf_scale_min_q4k(scales, g * 2, &s0, &m0);
+                gguf_scale_min_q4k(scales, g * 2 + 1, &s1, &m1);
+                const float d0 = d * (float)s0, mm0 = dmin * (float)m0;
+                const float d1 = d * (float)s1, mm1 = dmin * (float)m1;
+                const uint8_t* qg = qs + g * 32;
+                for (size_t i = 0; i < 32 && o < count; ++i) out[o++] = d0 * (float)(qg[i] & 0x0F) - mm0;
+                for (size_t i = 0; i < 32 && o < count; ++i) out[o++] = d1 * (float)(qg[i] >> 4) - mm1;
+            }
+        } else if (bb == 18) {                                    /* q4_0 :397-405 */
+            const float d = orc_fp16_to_fp32(rd16(blk));
+            for (size_t i = 0; i < 32 && o < count; ++i) {
+                const uint8_t nib = (i & 1) == 0 ? (blk[2 + i / 2] & 0x0F) : (blk[2 + i / 2] >> 4);
+                out[o++] = ((float)nib - 8.0f) * d;
+            }
+        } else {                                                  /* q5_k: generic fallback :437-463 */
+            const size_t bits = 5, packed_bytes = (be * bits + 7) / 8;
+            const uint8_t* packed = blk + (bb - packed_bytes);
+            float d = orc_fp16_to_fp32(rd16(blk));
+            if (!isfinite(d) || fabsf(d) < 1e-12f) d = 1.0f;
+            for (size_t i = 0; i < be && o < count; ++i) {
+                const int32_t q = (int32_t)read_bits_lsb(packed, i * bits, bits) - 16;
+                out[o++] = (float)q * d;
+            }
+        }
+    }
+    return (long)o;
+}

@@ -103,6 +103,16 @@ int orc_dense_matmul(const float* W, size_t R, size_t C, const float* x, size_t 
 long orc_dequantize(const char* fmt, const uint8_t* data, size_t nbytes, float scale,
                     float zero_point, float* out, size_t out_cap);
 
+/* SparseInferenceEngine.cpp:276-469 (decodeSupportedGGUFQuantized): how the INFERENCE side
+ * widens a stored-raw tensor in a GGUF block format - ggml's element order, not the encoder's:
+ * q4_k 32 low nibbles then 32 high nibbles per 64-element group (:362-383); q6_k four runs of
+ * 32 per 128-element half, d * (float)(scale * q) with scales [0],[2],[4],[6] of the half
+ * (:329-360); q5_k through the generic bit-field fallback (:437-463: 5-bit fields from byte 16,
+ * (q - 16) * d); q4_0 and q8_0 sequential. fmt: "q4_0","q8_0","q4_k","q5_k","q6_k".
+ * Returns number of floats written (min(n_elements, what the blocks hold)), negative on errors. */
+long orc_dequantize_inference(const char* fmt, const uint8_t* data, size_t nbytes, size_t n_elements,
+                              float* out, size_t out_cap);
+
 float orc_fp16_to_fp32(uint16_t h); /* utils/fp16_convert.hpp:26-60 */
 
 /* ---- decoder-layer arithmetic (decoder_oracle.c) ---- */

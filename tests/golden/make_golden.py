@@ -157,6 +157,7 @@ def main():
     np.savez_compressed(os.path.join(OUT, "dequant.npz"), **out)
     encoder_coding(ref)
     attention_cases(ref)
+    raw_tensor_cases()
     print("golden fixtures written to", OUT)
     for f in sorted(os.listdir(OUT)):
         print(f"  {f:24s} {os.path.getsize(os.path.join(OUT, f)):>9d} B")
@@ -193,9 +194,40 @@ def attention_cases(ref):
     np.savez_compressed(os.path.join(OUT, "attention.npz"), **out)
 
 
+def raw_tensor_cases(_ref=None):
+    """Stored-raw tensors in GGUF block formats as the reference's INFERENCE side widens them
+    (SDRModelLoader::loadLayerByName -> decodeSupportedGGUFQuantized,
+    SparseInferenceEngine.cpp:276-469): random blocks with modest fp16 super-scales, written into
+    a .sdr as strategy-0 segments and read back through the reference's loader."""
+    import tempfile
+    from oracle.bindings import ReferenceEngine
+    from tests import synth
+    eng = ReferenceEngine()
+    rng = np.random.default_rng(4321)
+    out = {}
+    with tempfile.TemporaryDirectory() as d:
+        for fmt, unit, per, nblk in (("q4_k", 144, 256, 16), ("q5_k", 176, 256, 16), ("q6_k", 210, 256, 16),
+                                     ("q4_0", 18, 32, 64), ("q8_0", 34, 32, 64)):
+            raw = rng.integers(0, 256, size=unit * nblk, dtype=np.uint8)
+            blk = raw.reshape(nblk, unit)
+            halves = rng.normal(0, 0.05, size=(nblk, 2)).astype(np.float16).view(np.uint8).reshape(nblk, 4)
+            if fmt == "q6_k":
+                blk[:, 208:210] = halves[:, 0:2]
+            else:
+                blk[:, 0:4 if fmt in ("q4_k", "q5_k") else 2] = halves[:, 0:4 if fmt in ("q4_k", "q5_k") else 2]
+            n = per * nblk
+            path = os.path.join(d, fmt + ".sdr")
+            synth.write_sdr(path, [synth.raw_segment("blk.0.ffn_down.weight", raw, synth.SEG_FEED_FORWARD,
+                                                     data_format=fmt, dims=(n // 256, 256))])
+            out[fmt + "_in"] = raw
+            out[fmt + "_out"] = eng.layer_weights(path, "blk.0.ffn_down.weight")
+            assert out[fmt + "_out"].size == n
+    np.savez_compressed(os.path.join(OUT, "raw_tensors.npz"), **out)
+
+
 if __name__ == "__main__":
-    only = {"encoder_coding": encoder_coding, "attention": attention_cases}
+    only = {"encoder_coding": encoder_coding, "attention": attention_cases, "raw_tensors": raw_tensor_cases}
     if len(sys.argv) == 2 and sys.argv[1] in only:      # only this fixture, the others untouched
-        only[sys.argv[1]](Reference())
+        only[sys.argv[1]](Reference() if sys.argv[1] != "raw_tensors" else None)
     else:
         main()

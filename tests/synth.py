@@ -89,9 +89,9 @@ def raw_segment(name: str, array: np.ndarray, seg_type: int = SEG_LAYER_NORM, la
 
 
 def pack_source_dtype(w: np.ndarray, fmt: str) -> np.ndarray:
-    """fp32 values -> packed bytes of a source dtype the reference widens with
-    dequantizeSegmentToFP32: "f16", "bf16" (round to nearest even) or "q8_0" (blocks of 32:
-    fp16 scale d = max|x| / 127, then 32 int8 quants)."""
+    """fp32 values -> packed bytes of a source dtype the reference widens at load: "f16", "bf16"
+    (round to nearest even), "q8_0" (blocks of 32: fp16 scale d = max|x| / 127, then 32 int8
+    quants), or the k-quants "q4_k", "q5_k", "q6_k" in the block layouts its inference side reads."""
     w = np.ascontiguousarray(w, np.float32).reshape(-1)
     if fmt == "f16":
         return w.astype(np.float16).view(np.uint8)
@@ -107,7 +107,72 @@ def pack_source_dtype(w: np.ndarray, fmt: str) -> np.ndarray:
         out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
         out[:, 2:] = np.clip(q, -127, 127).astype(np.int8).view(np.uint8)
         return out.reshape(-1)
+    if fmt == "q4_k":
+        return _pack_q4_k(w)
+    if fmt == "q6_k":
+        return _pack_q6_k(w)
+    if fmt == "q5_k":
+        # the reference's inference side reads q5_k blocks through a generic 5-bit fall-back
+        # (fp16 scale at byte 0, 256 five-bit fields from byte 16, value (q - 16) * d): pack for that
+        b = w.reshape(-1, 256)
+        d = (np.abs(b).max(1) / 15.0).astype(np.float16)
+        q = np.clip(np.rint(b / np.maximum(d.astype(np.float32), 1e-30)[:, None]) + 16, 0, 31).astype(np.uint64)
+        out = np.zeros((b.shape[0], 176), np.uint8)
+        out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+        bits = ((q[:, :, None] >> np.arange(5, dtype=np.uint64)) & 1).astype(np.uint8).reshape(b.shape[0], 1280)
+        out[:, 16:] = np.packbits(bits, axis=1, bitorder="little")
+        return out.reshape(-1)
     raise ValueError(f"no packer for source dtype {fmt!r}")
+
+
+def _pack_q4_k(w: np.ndarray) -> np.ndarray:
+    """A plain min/max quantiser writing ggml's q4_K block layout (144 bytes per 256 values:
+    fp16 d, fp16 dmin, 12 bytes of 6-bit scales and mins, 128 bytes of nibbles; 64-value groups
+    hold 32 low nibbles then 32 high nibbles). Harness code: it only has to produce valid blocks."""
+    b = w.reshape(-1, 8, 32).astype(np.float32)
+    lo = np.minimum(b.min(2), 0.0)
+    scale = (b.max(2) - lo) / 15.0
+    d = (scale.max(1) / 63.0).astype(np.float16)
+    dmin = ((-lo).max(1) / 63.0).astype(np.float16)
+    df, dmf = np.maximum(d.astype(np.float32), 1e-30), np.maximum(dmin.astype(np.float32), 1e-30)
+    sc = np.clip(np.rint(scale / df[:, None]), 0, 63).astype(np.uint8)
+    mn = np.clip(np.rint(-lo / dmf[:, None]), 0, 63).astype(np.uint8)
+    eff = np.maximum(df[:, None] * sc, 1e-30)
+    q = np.clip(np.rint((b + (dmf[:, None] * mn)[:, :, None]) / eff[:, :, None]), 0, 15).astype(np.uint8)
+    out = np.zeros((b.shape[0], 144), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(-1, 2)
+    for j in range(4):
+        out[:, 4 + j] = (sc[:, j] & 63) | ((sc[:, j + 4] >> 4) << 6)
+        out[:, 8 + j] = (mn[:, j] & 63) | ((mn[:, j + 4] >> 4) << 6)
+        out[:, 12 + j] = (sc[:, j + 4] & 15) | ((mn[:, j + 4] & 15) << 4)
+    for g in range(4):
+        out[:, 16 + 32 * g:48 + 32 * g] = q[:, 2 * g] | (q[:, 2 * g + 1] << 4)
+    return out.reshape(-1)
+
+
+def _pack_q6_k(w: np.ndarray) -> np.ndarray:
+    """ggml's q6_K block layout (210 bytes per 256 values: 128 bytes of low nibbles, 64 bytes of
+    high bit pairs, 16 int8 scales, fp16 d), one scale per run of 32 written to both scale slots
+    of the run. Harness code."""
+    b = w.reshape(-1, 2, 4, 32).astype(np.float32)           # block, half, run, element
+    s = np.abs(b).max(3) / 31.0
+    d = (s.max((1, 2)) / 127.0).astype(np.float16)
+    df = np.maximum(d.astype(np.float32), 1e-30)
+    sc = np.clip(np.rint(s / df[:, None, None]), 1, 127).astype(np.int8)
+    q = np.clip(np.rint(b / (df[:, None, None] * sc)[..., None]) + 32, 0, 63).astype(np.uint8)
+    out = np.zeros((b.shape[0], 210), np.uint8)
+    for h in range(2):
+        ql = out[:, h * 64:h * 64 + 64]
+        ql[:, 0:32] = (q[:, h, 0] & 15) | ((q[:, h, 2] & 15) << 4)
+        ql[:, 32:64] = (q[:, h, 1] & 15) | ((q[:, h, 3] & 15) << 4)
+        out[:, 128 + h * 32:160 + h * 32] = ((q[:, h, 0] >> 4) | ((q[:, h, 1] >> 4) << 2) | ((q[:, h, 2] >> 4) << 4)
+                                             | ((q[:, h, 3] >> 4) << 6))
+        for r in range(4):
+            out[:, 192 + h * 8 + 2 * r] = sc[:, h, r].view(np.uint8)
+            out[:, 192 + h * 8 + 2 * r + 1] = sc[:, h, r].view(np.uint8)
+    out[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
 
 
 def decoder_archive(path: str, *, n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab, seed=100,

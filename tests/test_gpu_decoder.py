@@ -17,10 +17,10 @@ LOGIT_TOL = 2e-2
 CFG = dict(n_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=32, inter=256, vocab=300)
 
 
-def _build_model(tmp_path_factory, oracle, tag, raw_formats=None, **atoms):
+def _build_model(tmp_path_factory, oracle, tag, raw_formats=None, CFG=CFG, k=3, **atoms):
     path = str(tmp_path_factory.mktemp("dec") / f"{tag}.sdr")
     raw_formats = raw_formats or {}
-    synth.decoder_archive(path, **CFG, k=3, seed=7, raw=raw_formats, **atoms)
+    synth.decoder_archive(path, **CFG, k=k, seed=7, raw=raw_formats, **atoms)
     ld = cs.SDRModelLoader(path, index_only=True)
     shapes = {"token_embd.weight": (CFG["vocab"], CFG["hidden"]), "output.weight": (CFG["vocab"], CFG["hidden"])}
 
@@ -29,7 +29,9 @@ def _build_model(tmp_path_factory, oracle, tag, raw_formats=None, **atoms):
             return oracle.decompress(ld.loadCompressedBytesByName(n))
         data = ld.loadSegmentByName(n)                       # stored raw: widen like the reference does
         fmt = raw_formats[n]
-        w = data.view(np.float32) if fmt == "f32" else oracle.dequantize(fmt, data)
+        # widened as the reference's inference side does it: ggml's element order for block formats
+        w = (data.view(np.float32) if fmt == "f32" else
+             oracle.dequantize_inference(fmt, data) if fmt.startswith("q") else oracle.dequantize(fmt, data))
         if n in shapes:
             return w.reshape(shapes[n])
         r, c = {"attn_q": (CFG["q_heads"] * CFG["head_dim"], CFG["hidden"]),
@@ -69,20 +71,23 @@ def model_tc(tmp_path_factory, oracle):
 def model_raw(tmp_path_factory, oracle):
     """Some tensors stored uncompressed in a source dtype, as a converter leaves protected ones:
     the embedding as f16, the head as q8_0, one block's down projection as bf16, another's
-    query projection as plain f32."""
+    query projection as plain f32, and three k-quant tensors (q4_k, q5_k, q6_k), which the
+    reference's inference side reads in ggml's element order."""
     return _build_model(tmp_path_factory, oracle, "raw", n_atoms=32, kv_atoms=16,
                         raw_formats={"token_embd.weight": "f16", "output.weight": "q8_0",
-                                     "blk.0.ffn_down.weight": "bf16", "blk.1.attn_q.weight": "f32"})
+                                     "blk.0.ffn_down.weight": "bf16", "blk.1.attn_q.weight": "f32",
+                                     "blk.1.ffn_up.weight": "q4_k", "blk.0.attn_output.weight": "q6_k",
+                                     "blk.1.ffn_gate.weight": "q5_k"})
 
 
-def oracle_forward(oracle, weights, tokens, eps=1e-6, theta=1e6):
+def oracle_forward(oracle, weights, tokens, eps=1e-6, theta=1e6, CFG=CFG):
     cfg = dict(CFG, eps=eps, theta=theta)
     return oracle.decoder_forward(cfg, weights["tok"], weights["blocks"], weights["out_norm"], weights["head"], tokens)
 
 
-def make_decoder(path, ctx, **kw):
+def make_decoder(path, ctx, CFG=CFG, max_seq=64, **kw):
     ld = cs.SDRModelLoader(path, ctx)
-    return cs.Decoder(ld, **CFG, max_seq=64, rms_eps=1e-6, rope_theta=1e6, **kw)
+    return cs.Decoder(ld, **CFG, max_seq=max_seq, rms_eps=1e-6, rope_theta=1e6, **kw)
 
 
 def test_prefill_matches_oracle(ctx, oracle, model):
@@ -236,3 +241,71 @@ def test_exchange_needs_tensor_parallel_ranks(ctx, model):
     assert lib.csdr_decoder_exchange_import(dec._h, buf.raw, 1) == cs._lib.ERR_UNSUPPORTED
     assert lib.csdr_decoder_exchange_import(dec._h, buf.raw, 2) == cs._lib.ERR_INVALID_ARG
     assert b"exchange" in lib.csdr_last_error() or b"handle" in lib.csdr_last_error()
+
+
+# ---- the two decoder configurations at their real WIDTHS (depth reduced) ----
+# Width selects the kernel variants: the 14 : 2 grouped heads of 64 and the 151 936-row head of
+# the 0.5B shape; the 32 heads of 128, the 11 008-wide MLP and the 16-token step of the 7B shape.
+QWEN_W = dict(n_layers=2, hidden=896, q_heads=14, kv_heads=2, head_dim=64, inter=4864, vocab=151936)
+LLAMA_W = dict(n_layers=1, hidden=4096, q_heads=32, kv_heads=32, head_dim=128, inter=11008, vocab=32000)
+
+
+@pytest.fixture(scope="module")
+def model_qwen_width(tmp_path_factory, oracle):
+    return _build_model(tmp_path_factory, oracle, "qwenw", CFG=QWEN_W, k=8, n_atoms=512, kv_atoms=128)
+
+
+@pytest.fixture(scope="module")
+def model_llama_width(tmp_path_factory, oracle):
+    return _build_model(tmp_path_factory, oracle, "llamaw", CFG=LLAMA_W, k=8, n_atoms=512)
+
+
+def test_qwen_width_prefill_and_greedy_steps(ctx, oracle, model_qwen_width):
+    """Hidden 896, 14 query / 2 kv heads of 64, SwiGLU 4864, vocabulary 151 936, eps 1e-6, k/v
+    dictionaries of 128 atoms; two blocks. A 64-token prompt (tensor-core block loop), then
+    three greedy steps at batch 1 (fused GEMV path), each against the oracle's whole-sequence
+    recompute."""
+    path, weights = model_qwen_width
+    tokens = np.random.default_rng(7).integers(0, QWEN_W["vocab"], 64)
+    _, logits = oracle_forward(oracle, weights, tokens, CFG=QWEN_W)
+    dec = make_decoder(path, ctx, CFG=QWEN_W, max_seq=80)
+    g_logits, _ = dec.forward(tokens)
+    assert np.isfinite(g_logits).all()
+    assert np.abs(g_logits - logits).max() < LOGIT_TOL
+    assert int(g_logits.argmax()) == int(logits.argmax())
+    seq, nxt = list(tokens), int(g_logits.argmax())
+    for _ in range(3):
+        seq.append(nxt)
+        _, want = oracle_forward(oracle, weights, np.array(seq), CFG=QWEN_W)
+        got_next, got = dec.step([nxt], want_logits=True)
+        assert np.abs(got[0] - want).max() < LOGIT_TOL
+        assert int(got_next[0]) == int(want.argmax())
+        nxt = int(got_next[0])
+    dec.close()
+
+
+def test_llama_width_batch16_step(ctx, oracle, model_llama_width):
+    """Hidden 4096, 32 heads of 128, SwiGLU 11 008, vocabulary 32 000; one block. Sixteen
+    sequences with real, different, prefilled contexts step together (the 16-token tile of the
+    tensor-core projection, the grouped gathers, the batch-16 attention), then step again over
+    the cache rows the first step filed."""
+    path, weights = model_llama_width
+    rng = np.random.default_rng(8)
+    lens = [3, 9, 5, 12, 1, 7, 4, 10, 2, 8, 6, 11, 3, 5, 9, 7]
+    prompts = [rng.integers(0, LLAMA_W["vocab"], n) for n in lens]
+    dec = make_decoder(path, ctx, CFG=LLAMA_W, max_seq=32, max_batch=16)
+    for s_, p_ in enumerate(prompts):
+        dec.forward(p_, seq=s_, want_logits=False)
+    new = rng.integers(0, LLAMA_W["vocab"], 16)
+    nxt, lg = dec.step(new, want_logits=True)
+    assert np.isfinite(lg).all()
+    for s_, p_ in enumerate(prompts):
+        _, want = oracle_forward(oracle, weights, np.append(p_, new[s_]), CFG=LLAMA_W)
+        assert np.abs(lg[s_] - want).max() < LOGIT_TOL, s_
+        assert int(nxt[s_]) == int(want.argmax()), s_
+    nxt2, lg2 = dec.step(nxt, want_logits=True)
+    for s_ in (0, 3, 15):
+        _, want = oracle_forward(oracle, weights, np.concatenate([prompts[s_], [new[s_]], [nxt[s_]]]), CFG=LLAMA_W)
+        assert np.abs(lg2[s_] - want).max() < LOGIT_TOL, s_
+        assert int(nxt2[s_]) == int(want.argmax()), s_
+    dec.close()

@@ -117,6 +117,23 @@ def test_dequant_kquant_known_answers(ctx):
     assert out[0] == 34.0 and out[1] == -60.0
 
 
+def test_stored_raw_block_formats_in_the_inference_side_order(ctx, oracle, golden):
+    # what SDRModelLoader::loadLayerByName made of the same bytes (fixture written through the
+    # reference's loader): bit for bit, and unlike the encoder-side order for the k-quants
+    g = golden("raw_tensors.npz")
+    for fmt in ("q4_k", "q5_k", "q6_k", "q4_0", "q8_0"):
+        got = cs.dequantize_inference(g[fmt + "_in"], fmt, ctx=ctx)
+        assert np.array_equal(got.view(np.uint32), g[fmt + "_out"].view(np.uint32)), fmt
+        assert np.array_equal(got.view(np.uint32), oracle.dequantize_inference(fmt, g[fmt + "_in"]).view(np.uint32))
+    # clipped to the element count asked for, trailing partial block ignored
+    part = cs.dequantize_inference(np.append(g["q4_k_in"], np.zeros(7, np.uint8)), "q4_k", n_elements=300, ctx=ctx)
+    assert np.array_equal(part, g["q4_k_out"][:300])
+    enc = cs.HierarchicalSDRStrategy(ctx).dequantizeToFP32(g["q4_k_in"], "q4_k")
+    assert not np.array_equal(enc, g["q4_k_out"])
+    with pytest.raises(cs.CompressionError):
+        cs.dequantize_inference(g["q4_k_in"], "f16", ctx=ctx)
+
+
 def test_archive_e2e(ctx, golden):
     # src/test_hsdr_archive_e2e.cpp: .sdr written by the reference's AICompressor
     g = golden("archive_e2e.npz")
