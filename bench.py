@@ -6,10 +6,12 @@
 
 Workload (N=1): the MLP-projection case — W 11008x4096, HSDR 1-D row tiles (K=512, 3x8),
 decode GEMV at batch 1. One step = one pass over SEGS distinct device-resident copies of
-the compressed weight (SEGS * payload > 2 * L2, so every launch reads HBM, not L2).
+the compressed weight (SEGS * payload > 2 * L2, so every pass reads HBM, not L2), issued as ONE
+list of independent products (csdr_matmul_queue_device_async: one persistent launch).
 `value` = algorithmic compressed bytes processed per second with inputs resident in HBM;
-`e2e` = the same metric through the host-buffer C-ABI call (H2D of x and D2H of y inside
-the timed region). The M sweep {1, 8, 64, 512} is reported beside it.
+`e2e` = the same list through the host-buffer C-ABI call (csdr_matmul_queue: H2D of x and D2H of y
+inside the timed region). The same pass as a chain of single dependent launches, the grouped
+launches and the M sweep {1, 8, 64, 512} are reported beside it.
 """
 from __future__ import annotations
 
@@ -135,11 +137,12 @@ DECODERS = {
                               vocab=151936), kv_atoms=128, batch=1, context=512, steps=128, eps=1e-6, prefill=True),
     # config 4: Llama-7B shape, batch 16 at context 1024
     "llama7b": dict(cfg=dict(n_layers=32, hidden=4096, q_heads=32, kv_heads=32, head_dim=128, inter=11008,
-                             vocab=32000), kv_atoms=None, batch=16, context=1024, steps=32, eps=1e-5, prefill=False),
+                             vocab=32000), kv_atoms=None, batch=16, context=1024, steps=32, eps=1e-5, prefill=True),
 }
 
 
 FUSED_GEMV_DRAM_BYTES_NCU = 8996000   # per launch, cfg2 shape, batch 1 (8.996 MB read, 0 written)
+QUEUE_DRAM_BYTES_PER_TASK_NCU = None   # per task of the queue kernel, cfg2 shape, batch 1 (set from the ncu capture)
 
 
 def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True):
@@ -176,17 +179,24 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
         out["partial_sums"] = "peer memory (in-kernel)" if peer else "ncclAllReduce"
     with torch.cuda.stream(stream):
         if spec["prefill"]:
-            prompt = rng.integers(0, cfg["vocab"], ctxlen)
-            dec.forward(prompt, seq=0, want_logits=False)   # first pass builds per-dictionary caches
+            prompts = rng.integers(0, cfg["vocab"], (B, ctxlen))
+            dec.forward(prompts[0], seq=0, want_logits=False)   # first pass builds per-dictionary caches
             dec.reset()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
-            logits, _ = dec.forward(prompt, seq=0)
+            logits, _ = dec.forward(prompts[0], seq=0)
             e1.record(stream)
             torch.cuda.synchronize()
             out["prefill_ms"] = e0.elapsed_time(e1)
             out["prefill_tokens_per_s"] = ctxlen / (out["prefill_ms"] / 1e3)
-            first = np.array([int(logits.argmax())], np.int32)
+            firsts = [int(logits.argmax())]
+            for b in range(1, B):        # every sequence gets a real, different context
+                lg, _ = dec.forward(prompts[b], seq=b)
+                firsts.append(int(lg.argmax()))
+            if not np.isfinite(logits).all():
+                raise RuntimeError("prefill produced non-finite logits")
+            first = np.array(firsts, np.int32)
+            out["first_tokens"] = firsts[:4]
         else:
             for b in range(B):          # context without prefill: the cache rows below hold zeros;
                 dec.seek(b, ctxlen)     # decode cost does not depend on their content
@@ -227,6 +237,13 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     out.update(launch=mode, ms_per_step=ms / n, tokens_per_s=B * n / (ms / 1e3))
+    # a sanity signal on the timed path: one more step through the host-buffer call, logits read back
+    with torch.cuda.stream(stream):
+        nxt, lg = dec.step(tok.cpu().numpy(), want_logits=True)
+    out["logits_finite"] = bool(np.isfinite(lg).all())
+    out["next_tokens"] = [int(t) for t in nxt[:4]]
+    if not out["logits_finite"]:
+        raise RuntimeError("decode step produced non-finite logits")
     dec.close()
     ld.close()
     return out
@@ -340,18 +357,22 @@ def main():
             ms = float(t.item())
         return ms
 
-    # ---- headline: GEMV, batch 1, fp32 activations resident in HBM ----
+    # ---- headline: GEMV, batch 1, fp32 activations resident in HBM, the pass as one list ----
     x1, y1 = make_io(1, torch.float32)
-    eager_ms = timed(lambda: step(x1, y1, 1, cs.DTYPE_F32), args.steps, max(3, args.warmup))
-    # The step is launch-bound from Python (one ctypes call per matmul): capture it once in a
-    # CUDA graph and time the replay; the eager figure is reported beside it.
-    run_step, launch_mode = (lambda: step(x1, y1, 1, cs.DTYPE_F32)), "eager (one C-ABI call per matmul)"
+    queue = cs.Segment.matmul_queue_device(
+        [(s, x1.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 1, y1[i].data_ptr(), cs.TOKEN_MAJOR) for i, s in enumerate(segs)])
+    ctx.synchronize()
+
+    def qstep():
+        cs.Segment.matmul_queue_device(None, queue)
+    eager_ms = timed(qstep, args.steps, max(3, args.warmup))
+    run_step, launch_mode = qstep, "eager (one C-ABI call per pass)"
     if not args.no_graph:
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                step(x1, y1, 1, cs.DTYPE_F32)
-            run_step, launch_mode = graph.replay, f"CUDA graph replay of the step ({nseg} matmuls)"
+                qstep()
+            run_step, launch_mode = graph.replay, f"CUDA graph replay of the pass ({nseg} products, one list)"
         except Exception as e:  # capture not possible: keep the eager loop
             launch_mode += f"; graph capture failed: {type(e).__name__}"
             torch.cuda.synchronize()
@@ -367,18 +388,54 @@ def main():
     value = bytes1 * nseg * args.steps * world / (ms / 1e3) / 1e9
     # launch count of exactly the timed region
     l0 = ctx.launch_count
-    step(x1, y1, 1, cs.DTYPE_F32)
+    qstep()
     ctx.synchronize()
-    launches = (ctx.launch_count - l0) * args.steps
+    launches_per_step = ctx.launch_count - l0
+    launches = launches_per_step * args.steps
+
+    # ---- the same pass as a chain of single launches (each waits for the one before it) ----
+    chain = {}
+    try:
+        cfn = lambda: step(x1, y1, 1, cs.DTYPE_F32)
+        cfn()
+        ctx.synchronize()
+        if not args.no_graph:
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg, stream=stream):
+                step(x1, y1, 1, cs.DTYPE_F32)
+            cfn = cg.replay
+        cms = timed(cfn, args.steps, 3)
+        cgb = bytes1 * nseg * args.steps / (cms / 1e3) / 1e9
+        chain = {"GBps_compressed": cgb, "frac_hbm": cgb / hbm_peak, "us_per_launch": cms / args.steps / nseg * 1e3,
+                 "note": "one csdr_matmul_device_async per product, programmatic dependent launches"}
+    except Exception as e:
+        chain = {"error": f"{type(e).__name__}: {e}"[:200]}
+        torch.cuda.synchronize()
 
     # ---- per-kernel durations over the same steps (events around every launch) ----
     ctx.profile(True)
     with torch.cuda.stream(stream):
         for _ in range(min(args.steps, 20)):
-            step(x1, y1, 1, cs.DTYPE_F32)
+            qstep()
     prof = ctx.profile_read()
     ctx.profile(False)
-    if "hsdr_gemv_fused" in prof:
+    if "hsdr_gemv_queue" in prof:
+        # one launch per pass: its duration between two events on the stream, averaged
+        n_q, ms_q = prof["hsdr_gemv_queue"]
+        us_launch = ms_q / max(n_q, 1) * 1e3
+        per_launch = bytes1 * nseg / launches_per_step
+        achieved = per_launch / (us_launch * 1e-6) / 1e9
+        roofline = {"bound": "hbm", "kernel": "hsdr_gemv_queue_kernel", "achieved": achieved, "peak": hbm_peak,
+                    "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, scaled from the ncu
+                    # capture summarised in profiles/gemv_queue_cfg2_m1.md (traffic grows with the tasks)
+                    "traffic": QUEUE_DRAM_BYTES_PER_TASK_NCU * nseg / launches_per_step
+                    if (R, C) == (11008, 4096) and QUEUE_DRAM_BYTES_PER_TASK_NCU else None,
+                    "alg_bytes_per_launch": per_launch, "us_per_launch": us_launch,
+                    "tasks_per_launch": nseg / launches_per_step,
+                    "whole_pass_frac": value / world / hbm_peak,
+                    "note": "achieved = algorithmic bytes of one launch / its event-bracketed duration"}
+    elif "hsdr_gemv_fused" in prof:
         # one kernel per matmul: its launches overlap (programmatic dependent launch), so the
         # per-launch duration is the timed region divided by the launches in it
         us_launch = ms / args.steps / nseg * 1e3
@@ -438,9 +495,12 @@ def main():
 
     yh = np.empty((R, 1), np.float32)
 
+    yhs = [np.empty((R, 1), np.float32) for _ in segs]
+    xhs = [xh.copy() for _ in segs]      # every product brings its own host activations
+    hq = cs.Segment.matmul_queue([(s, xhs[i], 1, yhs[i]) for i, s in enumerate(segs)])
+
     def e2e_step():
-        for s in segs:
-            s.matmul(xh, 1, out=yh)
+        cs.Segment.matmul_queue(None, hq)
     for _ in range(2):
         e2e_step()
     if world > 1:
@@ -456,7 +516,13 @@ def main():
         e2e_s = float(t.item())
     e2e = {"value": bytes1 * nseg * n_e2e * world / e2e_s / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": nseg * C * 4, "d2h_bytes_per_step": nseg * R * 4,
-           "api": "csdr_matmul (host x, host y), one call per segment"}
+           "api": "csdr_matmul_queue (host x, host y), one call per pass"}
+    # the same through one host-buffer call per product
+    t0 = time.perf_counter()
+    for _ in range(3):
+        for s in segs:
+            s.matmul(xh, 1, out=yh)
+    e2e["per_product_calls_GBps"] = bytes1 * nseg * 3 / (time.perf_counter() - t0) / 1e9
 
     # ---- M sweep of the same workload (bf16 activations, token-major) ----
     sweep = {}
@@ -514,8 +580,14 @@ def main():
                        "launch": launch_mode, "eager_ms_per_step": eager_ms / args.steps,
                        "parallelism": f"replicas x{world}"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
+            "chain_of_single_launches": chain,
             "kernel_ms": {k: {"launches": v[0], "us_each": v[1] / v[0] * 1e3} for k, v in prof.items()},
             "grouped_same_x": grouped, "sweep": sweep, "decode_tokens_per_s": decode}
+    if isinstance(decode.get("llama7b"), dict) and "tokens_per_s" in decode["llama7b"]:
+        d7 = decode["llama7b"]
+        line["tp_decode"] = {"model": "llama7b-shaped, batch 16, context 1024", "tp": d7["tp"],
+                             "tokens_per_s": d7["tokens_per_s"], "ms_per_step": d7["ms_per_step"],
+                             "exchange": d7.get("partial_sums", "none (one rank)")}
     if rank == 0:
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(pay)

@@ -296,6 +296,44 @@ class Segment:
         _check(ctx._lib.csdr_matmul_group_device_async(ctx._h, hs, n, C.c_void_p(x_ptr), x_dtype,
                                                        x_layout, batch, ys, y_layout))
 
+    @staticmethod
+    def matmul_queue_device(tasks, prepared=None):
+        """Independent products in as few launches as possible. tasks: iterable of
+        (segment, x_ptr, x_dtype, x_layout, batch, y_ptr, y_layout[, bias_ptr]). Returns the
+        ctypes array; pass it back as `prepared` to issue the same list again without rebuilding it."""
+        if prepared is None:
+            tasks = list(tasks)
+            prepared = (_lib.MatmulTask * len(tasks))()
+            for i, t in enumerate(tasks):
+                prepared[i].seg, prepared[i].x_dev, prepared[i].x_dtype, prepared[i].x_layout = t[0]._h, t[1], t[2], t[3]
+                prepared[i].batch, prepared[i].y_dev, prepared[i].y_layout = t[4], t[5], t[6]
+                prepared[i].bias_dev = t[7] if len(t) > 7 and t[7] else None
+            prepared._ctx = tasks[0][0].ctx
+        ctx = prepared._ctx
+        _check(ctx._lib.csdr_matmul_queue_device_async(ctx._h, prepared, len(prepared)))
+        return prepared
+
+    @staticmethod
+    def matmul_queue(tasks, prepared=None):
+        """Independent products on host arrays, reference layout: tasks is an iterable of
+        (segment, x (C, batch) fp32, batch, out (R, batch) fp32). One upload, one launch per 32
+        tasks, one download. Returns the ctypes array; pass it back as `prepared` to run the same
+        list again without rebuilding it (the arrays must stay alive and in place)."""
+        if prepared is None:
+            tasks = list(tasks)
+            prepared = (_lib.MatmulHostTask * len(tasks))()
+            for i, (seg, x, batch, out) in enumerate(tasks):
+                if not (x.dtype == np.float32 and x.flags.c_contiguous and x.size == seg.cols * batch):
+                    raise ValueError("x must be C-contiguous fp32 with cols*batch elements")
+                if not (out.dtype == np.float32 and out.flags.c_contiguous and out.size == seg.rows * batch):
+                    raise ValueError("out must be C-contiguous fp32 with rows*batch elements")
+                prepared[i].seg, prepared[i].batch = seg._h, batch
+                prepared[i].x, prepared[i].y = x.__array_interface__["data"][0], out.__array_interface__["data"][0]
+            prepared._ctx = tasks[0][0].ctx
+        ctx = prepared._ctx
+        _check(ctx._lib.csdr_matmul_queue(ctx._h, prepared, len(prepared)))
+        return prepared
+
     def decompress(self) -> np.ndarray:
         out = np.empty((self.rows, self.cols), np.float32)
         _check(self.ctx._lib.csdr_decompress(self.ctx._h, self._h, _fp(out), out.size))

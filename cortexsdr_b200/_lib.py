@@ -46,6 +46,15 @@ class SegmentHeader(C.Structure):
                 ("dims", C.c_uint32 * 8)]
 
 
+class MatmulTask(C.Structure):
+    _fields_ = [("seg", C.c_void_p), ("x_dev", C.c_void_p), ("x_dtype", C.c_int), ("x_layout", C.c_int),
+                ("batch", C.c_size_t), ("y_dev", C.c_void_p), ("y_layout", C.c_int), ("bias_dev", C.c_void_p)]
+
+
+class MatmulHostTask(C.Structure):
+    _fields_ = [("seg", C.c_void_p), ("x", C.c_void_p), ("batch", C.c_size_t), ("y", C.c_void_p)]
+
+
 class DecoderConfig(C.Structure):
     _fields_ = [("n_layers", C.c_uint32), ("hidden", C.c_uint32), ("q_heads", C.c_uint32),
                 ("kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("inter", C.c_uint32),
@@ -89,6 +98,8 @@ SIGNATURES = {
     "csdr_matmul_device_async": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _SZ, _P, C.c_int, _P]),
     "csdr_matmul_group_device_async": (C.c_int, [_P, C.POINTER(_P), _SZ, _P, C.c_int, C.c_int, _SZ,
                                                  C.POINTER(_P), C.c_int]),
+    "csdr_matmul_queue_device_async": (C.c_int, [_P, C.POINTER(MatmulTask), _SZ]),
+    "csdr_matmul_queue": (C.c_int, [_P, C.POINTER(MatmulHostTask), _SZ]),
     "csdr_matmul_rowtiles_noalloc": (C.c_int, [_P, _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                                C.c_uint32, _P, C.c_int, C.c_int, _SZ, _P, C.c_int, _P]),
     "csdr_matmul_rowtiles_noalloc_status": (C.c_int, [_P, C.POINTER(C.c_int)]),

@@ -14,6 +14,7 @@ SOURCES = [
     "kernels/matmul.cu",
     "kernels/decode.cu",
     "kernels/gemv_fused.cu",
+    "kernels/gemv_queue.cu",
     "kernels/decoder_ops.cu",
     "kernels/gemm_tcgen05.cu", "kernels/gemm_tma.cu",
     "decoder.cu",

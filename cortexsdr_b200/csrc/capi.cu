@@ -6,10 +6,12 @@
 #include <chrono>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "internal.hpp"
 #include "kernels/gemm_tcgen05.hpp"
 #include "kernels/gemv_fused.hpp"
+#include "kernels/gemv_queue.hpp"
 
 namespace csdr {
 
@@ -62,7 +64,8 @@ DevPtr upload(csdr_context* ctx, const void* src, size_t bytes) {
 const char* kernel_class_name(int cls) {
     static const char* names[KC_COUNT] = {"hsdr_unpack", "hsdr_dx", "hsdr_gather", "hsdr_tile_project",
                                           "hsdr_tile_gather", "hsdr_edge", "dense_rows", "hsdr_decode_rows",
-                                          "dequant", "hsdr_gemm_tcgen05", "decoder_op", "hsdr_gemv_fused", "attention"};
+                                          "dequant", "hsdr_gemm_tcgen05", "decoder_op", "hsdr_gemv_fused", "attention",
+                                          "hsdr_gemv_queue"};
     return (cls >= 0 && cls < KC_COUNT) ? names[cls] : "?";
 }
 
@@ -164,6 +167,9 @@ void* csdr_context::pinned_get(size_t bytes) {
         const size_t want = std::max<size_t>(bytes, 1u << 20);
         CSDR_CUDA(cudaHostAlloc(&pinned, want, cudaHostAllocMapped));
         pinned_bytes = want;
+        // the completion word at the head must not hold a sequence number left by an earlier
+        // owner of these pages (page-locked memory is recycled between contexts)
+        std::memset(pinned, 0, 256);
     }
     return pinned;
 }
@@ -202,6 +208,8 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         CSDR_CUDA(cudaMalloc(&ctx->gemv_seq, 2 * sizeof(uint32_t)));
         CSDR_CUDA(cudaMemsetAsync(ctx->gemv_seq, 0, 2 * sizeof(uint32_t), ctx->stream));
         if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_GEMV_QUEUE")) ctx->gemv_queue = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_GEMV_QUEUE_SINGLE")) ctx->gemv_queue_single = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TENSOR_CORES")) ctx->tensor_cores = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TMA")) ctx->tma = e[0] != '0';
@@ -604,6 +612,16 @@ int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const*
             }
             return;
         }
+        if (n_segs > 1 && batch <= 4) {
+            // any number of members in one persistent launch
+            std::vector<QueueItem> items(n_segs);
+            for (size_t i = 0; i < n_segs; ++i)
+                items[i] = QueueItem{segs[i], x_dev, x_dtype, x_layout, batch, ys_dev[i], y_layout, nullptr};
+            if (gemv_queue_supported(ctx, items.data(), static_cast<uint32_t>(n_segs))) {
+                launch_gemv_queue(ctx, items.data(), static_cast<uint32_t>(n_segs));
+                return;
+            }
+        }
         size_t done = 0;
         while (done < n_segs) {
             const uint32_t n = static_cast<uint32_t>(std::min<size_t>(kMaxFusedGroup, n_segs - done));
@@ -633,6 +651,106 @@ int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const*
                 }
             }
             done += n;
+        }
+    });
+}
+
+int csdr_matmul_queue_device_async(csdr_context* ctx, const csdr_matmul_task* tasks, size_t n_tasks) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!tasks || n_tasks == 0) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (n_tasks > 0xFFFFu) throw Error(CSDR_ERR_LIMIT, "more than 65535 tasks in one list");
+        std::vector<QueueItem> items(n_tasks);
+        for (size_t i = 0; i < n_tasks; ++i) {
+            const csdr_matmul_task& t = tasks[i];
+            if (!t.seg || !t.x_dev || !t.y_dev) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+            if ((t.x_dtype != CSDR_DTYPE_F32 && t.x_dtype != CSDR_DTYPE_BF16) ||
+                (t.x_layout != CSDR_LAYOUT_FEATURE_MAJOR && t.x_layout != CSDR_LAYOUT_TOKEN_MAJOR) ||
+                (t.y_layout != CSDR_LAYOUT_FEATURE_MAJOR && t.y_layout != CSDR_LAYOUT_TOKEN_MAJOR))
+                throw Error(CSDR_ERR_INVALID_ARG, "unknown dtype or layout");
+            if (t.batch > 0xFFFFFFFFull) throw Error(CSDR_ERR_LIMIT, "batch too large");
+            items[i] = QueueItem{t.seg, t.x_dev, t.x_dtype, t.x_layout, t.batch, t.y_dev, t.y_layout, t.bias_dev};
+        }
+        if (gemv_queue_supported(ctx, items.data(), static_cast<uint32_t>(n_tasks))) {
+            launch_gemv_queue(ctx, items.data(), static_cast<uint32_t>(n_tasks));
+            return;
+        }
+        for (const QueueItem& it : items) {   // anything else: one product at a time
+            MatmulArgs a;
+            a.x = it.x;
+            a.x_dtype = it.x_dtype;
+            a.x_layout = it.x_layout;
+            a.batch = it.batch;
+            a.y = it.y;
+            a.y_layout = it.y_layout;
+            a.bias = it.bias;
+            launch_matmul(ctx, it.seg, a);
+        }
+    });
+}
+
+int csdr_matmul_queue(csdr_context* ctx, const csdr_matmul_host_task* tasks, size_t n_tasks) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!tasks || n_tasks == 0) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (n_tasks > 0xFFFFu) throw Error(CSDR_ERR_LIMIT, "more than 65535 tasks in one list");
+        // one staging block: every task's activations, then every task's result, 256-byte slots
+        size_t x_bytes = 0, y_bytes = 0;
+        for (size_t i = 0; i < n_tasks; ++i) {
+            const csdr_matmul_host_task& t = tasks[i];
+            if (!t.seg || !t.x || !t.y) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+            if (t.batch == 0 || t.batch > 0xFFFFu) throw Error(CSDR_ERR_INVALID_ARG, "batch must be 1 to 65535");
+            const Geometry& g = t.seg->g;
+            if (!g.row_tiles())
+                throw Error(CSDR_ERR_GEOMETRY, "HSDR matmul: fused matmul requires tile_rows == 1; use decompress() + "
+                                               "dense matmul for 2D tile encodings");
+            x_bytes += (static_cast<size_t>(g.cols) * t.batch * 4 + 255) & ~static_cast<size_t>(255);
+            y_bytes += (static_cast<size_t>(g.rows) * t.batch * 4 + 255) & ~static_cast<size_t>(255);
+        }
+        unsigned char* hbuf = static_cast<unsigned char*>(ctx->pinned_get(256 + x_bytes + y_bytes)) + 256;
+        unsigned char* dbuf = static_cast<unsigned char*>(ctx->scratch_get(3, x_bytes + y_bytes));
+        std::vector<QueueItem> items(n_tasks);
+        size_t xo = 0, yo = x_bytes;
+        for (size_t i = 0; i < n_tasks; ++i) {
+            const csdr_matmul_host_task& t = tasks[i];
+            const Geometry& g = t.seg->g;
+            const size_t xb = static_cast<size_t>(g.cols) * t.batch * 4, yb = static_cast<size_t>(g.rows) * t.batch * 4;
+            // tasks that share one host x share one staged copy
+            size_t x_at = xo;
+            bool shared = false;
+            for (size_t j = i; j-- > 0 && i - j <= 4;)
+                if (tasks[j].x == t.x && tasks[j].batch == t.batch && tasks[j].seg->g.cols == g.cols) {
+                    x_at = static_cast<const unsigned char*>(items[j].x) - dbuf;
+                    shared = true;
+                    break;
+                }
+            if (!shared) {
+                std::memcpy(hbuf + xo, t.x, xb);
+                xo += (xb + 255) & ~static_cast<size_t>(255);
+            }
+            items[i] = QueueItem{t.seg, dbuf + x_at, CSDR_DTYPE_F32, CSDR_LAYOUT_FEATURE_MAJOR, t.batch,
+                                 reinterpret_cast<float*>(dbuf + yo), CSDR_LAYOUT_FEATURE_MAJOR, nullptr};
+            yo += (yb + 255) & ~static_cast<size_t>(255);
+        }
+        CSDR_CUDA(cudaMemcpyAsync(dbuf, hbuf, xo, cudaMemcpyHostToDevice, ctx->stream));
+        if (gemv_queue_supported(ctx, items.data(), static_cast<uint32_t>(n_tasks))) {
+            launch_gemv_queue(ctx, items.data(), static_cast<uint32_t>(n_tasks));
+        } else {
+            for (const QueueItem& it : items) {
+                MatmulArgs a;
+                a.x = it.x;
+                a.batch = it.batch;
+                a.y = it.y;
+                launch_matmul(ctx, it.seg, a);
+            }
+        }
+        CSDR_CUDA(cudaMemcpyAsync(hbuf + x_bytes, dbuf + x_bytes, yo - x_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        yo = x_bytes;
+        for (size_t i = 0; i < n_tasks; ++i) {
+            const size_t yb = static_cast<size_t>(tasks[i].seg->g.rows) * tasks[i].batch * 4;
+            std::memcpy(tasks[i].y, hbuf + yo, yb);
+            yo += (yb + 255) & ~static_cast<size_t>(255);
         }
     });
 }

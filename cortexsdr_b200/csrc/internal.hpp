@@ -80,7 +80,7 @@ namespace csdr {
 // Kernel classes for launch counting and optional per-class device timing.
 enum KernelClass {
     KC_UNPACK = 0, KC_DX, KC_GATHER, KC_TILE_PROJECT, KC_TILE_GATHER, KC_EDGE, KC_DENSE,
-    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_GEMV_FUSED, KC_ATTENTION, KC_COUNT
+    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_GEMV_FUSED, KC_ATTENTION, KC_GEMV_QUEUE, KC_COUNT
 };
 const char* kernel_class_name(int cls);
 struct TimedLaunch {
@@ -114,6 +114,8 @@ struct csdr_context {
     uint32_t spin_limit_exchange = 2000000u;  // polls of a peer's flag in the tensor-parallel exchange
     csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
+    bool gemv_queue = true;  // CSDR_GEMV_QUEUE=0 keeps lists of products on single and grouped launches
+    bool gemv_queue_single = false;  // CSDR_GEMV_QUEUE_SINGLE=1 sends single products of at most 4 tokens there too
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
     bool tensor_cores = true;   // CSDR_TENSOR_CORES=0 keeps wide batches on the CUDA-core kernels
     bool tma = true;            // CSDR_TMA=0 keeps the register-fed tensor-core kernel

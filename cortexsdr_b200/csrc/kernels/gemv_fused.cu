@@ -56,7 +56,7 @@ struct FusedParams {
     XView x;
     unsigned long long* part;  // {float bits (low half), epoch (high half)} per partial
     uint32_t* seq;          // device: [0] launches completed (the epoch is this + 1, never 0: fresh
-                            // scratch is zero), [1] CTAs of the running launch that have finished
+                            // scratch is zero), [1] CTAs of the running launch that have read [0]
     int* status;
     uint32_t spin_limit;
     unsigned long long* trace;  // optional: 16 global-timer stamps per CTA (phase boundaries)
@@ -79,16 +79,21 @@ __device__ __forceinline__ void st_tagged(unsigned long long* p, float value, ui
     const unsigned long long w = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
     asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-// The launch is over for this CTA: the last one to say so advances the launch counter (skipping
-// the value whose successor would be the tag 0) and clears the count for the next launch.
-__device__ __forceinline__ void cta_finished(const FusedParams& p) {
-    if (threadIdx.x == 0) {
-        if (atomicAdd(p.seq + 1, 1u) == gridDim.x - 1u) {
-            const uint32_t next = p.seq[0] + 1u;
-            p.seq[0] = next == 0xFFFFFFFFu ? 0u : next;
-            p.seq[1] = 0u;
-        }
+// Every launch tags its words with (launches completed + 1). One thread per CTA reads the
+// counter and then checks in; the CTA that checks in last knows that every CTA of the launch has
+// read the counter and advances it for the next launch (skipping the value whose successor
+// would be the tag 0). The check-in is an acq_rel atomic, so the read is ordered before it; its
+// latency hides under the activation staging.
+__device__ __forceinline__ uint32_t take_epoch(uint32_t* seq) {
+    uint32_t done, prev;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(seq) : "memory");
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(seq + 1) : "memory");
+    if (prev == gridDim.x - 1u) {
+        seq[1] = 0u;
+        const uint32_t next = done + 1u;
+        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(seq), "r"(next == 0xFFFFFFFFu ? 0u : next) : "memory");
     }
+    return done + 1u;
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -228,7 +233,10 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
     stamp(p, 1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(p, 2);
-    const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(p.seq) + 1u;
+    __shared__ uint32_t epoch_s;
+    if (tid == 0) epoch_s = take_epoch(p.seq);
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
 
     // ---- phase A ----
     float* xs = reinterpret_cast<float*>(smem_raw);
@@ -297,10 +305,7 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
         advance(cur);
     }
     stamp(p, 4);
-    if (!gathers) {
-        cta_finished(p);
-        return;
-    }
+    if (!gathers) return;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // ---- phase B ----
@@ -403,7 +408,6 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
     }
     if (late) atomicExch(p.status, 1);
     stamp(p, 7);
-    cta_finished(p);
 }
 
 template <int MT, int A, int U>

@@ -19,6 +19,7 @@
 #include "../internal.hpp"
 #include "gemm_tcgen05.hpp"
 #include "gemv_fused.hpp"
+#include "gemv_queue.hpp"
 #include "views.cuh"
 
 namespace cg = cooperative_groups;
@@ -629,6 +630,14 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
     if (tcgen05_supported(ctx, seg, a.batch)) {
         launch_matmul_tcgen05(ctx, seg, a);
         return;
+    }
+    if (ctx->gemv_queue_single) {
+        // a list of one: the persistent kernel's streaming loader without the column split
+        const QueueItem item{seg, a.x, a.x_dtype, a.x_layout, a.batch, a.y, a.y_layout, a.bias};
+        if (gemv_queue_supported(ctx, &item, 1)) {
+            launch_gemv_queue(ctx, &item, 1);
+            return;
+        }
     }
     const size_t budget = std::min<size_t>(ctx->smem_optin, 200u * 1024u);
     const bool fast_rows = g.row_tiles() && (g.cols % 4u == 0);

@@ -196,6 +196,37 @@ CSDR_API int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segmen
                                             int x_layout, size_t batch, float* const* ys_dev,
                                             int y_layout);
 
+/* A list of INDEPENDENT products in as few launches as possible: the heads of a batch of
+ * requests, q|k|v and gate|up of a block, the experts of a routed layer. Lists whose members
+ * are all 1-D row-tile segments with one common batch of 1 to 4 tokens run as one persistent
+ * kernel per 32 tasks, in which the weight stream of task n+1 flows under the hand-over and
+ * gather of task n (tasks may differ in shape, activations and outputs); any other list is
+ * issued task by task. No task may read what another task of the same list writes. The
+ * reference issues one matmulHSDR call per product (SparseInferenceEngine.cpp:1074-1091). */
+typedef struct {
+    const csdr_segment* seg;
+    const void* x_dev;      /* activations, dtype/layout as the enums above */
+    int x_dtype, x_layout;
+    size_t batch;
+    float* y_dev;           /* fp32 */
+    int y_layout;
+    const float* bias_dev;  /* R floats or NULL */
+} csdr_matmul_task;
+CSDR_API int csdr_matmul_queue_device_async(csdr_context* ctx, const csdr_matmul_task* tasks,
+                                            size_t n_tasks);
+
+/* The same list with HOST buffers, reference layout (x: C x batch, y: R x batch, fp32): every
+ * task's activations cross to the device in one copy, the list runs as above, every result
+ * comes back in one copy, one synchronisation in all. Tasks that name the same host x share one
+ * staged copy. 1-D row tiles only, as matmulRowMajor (CSDR_ERR_GEOMETRY otherwise). */
+typedef struct {
+    const csdr_segment* seg;
+    const float* x;
+    size_t batch;
+    float* y;
+} csdr_matmul_host_task;
+CSDR_API int csdr_matmul_queue(csdr_context* ctx, const csdr_matmul_host_task* tasks, size_t n_tasks);
+
 /* The same row-tile product for callers that must not allocate. No counterpart in the
  * reference: it exists for hosts that cannot call cudaMalloc while they run - a process
  * whose device memory map is frozen after start-up (real-time or certified systems), a

@@ -406,3 +406,136 @@ def test_a_wait_that_runs_out_is_an_error_code_not_a_hang(lib, oracle, golden):
     assert e[0] < TOL and e[1] < TOL
     seg.close()
     c.close()
+
+
+def _queue_case(ctx, oracle, specs, batch, dtype="f32", layout="token", with_bias=False, replays=0):
+    """specs: (rows, cols, atoms, k) per task; every task gets its own activations."""
+    import torch
+    from tests import synth
+    rng = np.random.default_rng(len(specs) * 100 + batch)
+    segs, pays, xs, ys, xhs, biases, tasks = [], [], [], [], [], [], []
+    for i, (r, c, a, k) in enumerate(specs):
+        pay = synth.hsdr_payload(r, c, n_atoms=a, k=k, seed=500 + i)
+        seg = cs.Segment.from_payload(pay, ctx)
+        xh = rng.normal(0, 1, (batch, c)).astype(np.float32)
+        xt = torch.from_numpy(xh).cuda()
+        if dtype == "bf16":
+            xt = xt.to(torch.bfloat16)
+            xh = xt.float().cpu().numpy()
+        lay = cs.TOKEN_MAJOR
+        if layout == "feature":
+            xt, lay = xt.t().contiguous(), cs.FEATURE_MAJOR
+        y = torch.full((r, batch) if layout == "feature" else (batch, r), float("nan"), device="cuda")
+        b = torch.from_numpy(rng.normal(0, 1, r).astype(np.float32)).cuda() if with_bias else None
+        segs.append(seg); pays.append(pay); xs.append(xt); ys.append(y); xhs.append(xh); biases.append(b)
+        tasks.append((seg, xt.data_ptr(), cs.DTYPE_BF16 if dtype == "bf16" else cs.DTYPE_F32, lay, batch,
+                      y.data_ptr(), lay, b.data_ptr() if with_bias else 0))
+    torch.cuda.synchronize()
+    for _ in range(1 + replays):
+        cs.Segment.matmul_queue_device(tasks)
+    ctx.synchronize()
+    for i, pay in enumerate(pays):
+        want = oracle.matmul(pay, np.ascontiguousarray(xhs[i].T), batch)          # (R, batch)
+        if with_bias:
+            want = want + biases[i].cpu().numpy()[:, None]
+        got = ys[i].cpu().numpy()
+        got = got if layout == "feature" else got.T
+        e = rel_err(got, want)
+        assert e[0] < TOL and e[1] < TOL, (i, specs[i], batch, dtype, layout, e)
+    for s_ in segs:
+        s_.close()
+
+
+@pytest.mark.parametrize("batch", [1, 2, 3, 4])
+def test_queue_of_products_mixed_shapes(ctx, oracle, batch):
+    # different rows, widths (not multiples of the 1024-column slab), dictionary sizes (not
+    # multiples of the 8 atoms of a work unit) and code counts in one list
+    specs = [(384, 1024, 128, 6), (200, 4096, 512, 8), (77, 1540, 100, 5), (1000, 256, 64, 4), (16, 2052, 9, 3)]
+    _queue_case(ctx, oracle, specs, batch)
+
+
+def test_queue_longer_than_one_launch_with_bias_and_replays(ctx, oracle):
+    # 70 tasks = three launches of at most 32; bias added; run three times back to back (the
+    # second and third pass find the previous pass's tagged words in the scratch buffer)
+    specs = [(96 + 8 * (i % 5), 512 + 256 * (i % 3), 64, 4) for i in range(70)]
+    _queue_case(ctx, oracle, specs, 1, with_bias=True, replays=2)
+
+
+@pytest.mark.parametrize("dtype,layout", [("bf16", "token"), ("f32", "feature"), ("bf16", "feature")])
+def test_queue_activation_formats(ctx, oracle, dtype, layout):
+    _queue_case(ctx, oracle, [(264, 1536, 192, 5), (128, 1536, 64, 8), (512, 640, 128, 6)], 3, dtype=dtype, layout=layout)
+
+
+def test_queue_falls_back_for_wide_batches_and_2d_tiles(ctx, oracle):
+    import torch
+    from tests import synth
+    _queue_case(ctx, oracle, [(264, 1536, 192, 5), (128, 512, 64, 8)], 9)      # nine tokens: issued one by one
+    pay = synth.hsdr_payload(128, 192, tile_rows=32, tile_cols=32, n_atoms=32, k=4, seed=3)
+    seg = cs.Segment.from_payload(pay, ctx)
+    xh = np.random.default_rng(1).normal(0, 1, (2, 192)).astype(np.float32)
+    x, y = torch.from_numpy(xh).cuda(), torch.zeros((2, 128), device="cuda")
+    cs.Segment.matmul_queue_device([(seg, x.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 2, y.data_ptr(), cs.TOKEN_MAJOR)])
+    ctx.synchronize()
+    want = oracle.dense_matmul(oracle.decompress(pay), np.ascontiguousarray(xh.T), 2).T
+    e = rel_err(y.cpu().numpy(), want)
+    assert e[0] < TOL and e[1] < TOL
+
+
+def test_queue_graph_replay_with_changed_activations(ctx, oracle):
+    import torch
+    from tests import synth
+    stream = torch.cuda.Stream()
+    c = cs.Context(0, stream.cuda_stream)
+    pays = [synth.hsdr_payload(300 + 20 * i, 2048, n_atoms=256, k=6, seed=40 + i) for i in range(5)]
+    segs = [cs.Segment.from_payload(p, c) for p in pays]
+    x = torch.zeros((1, 2048), device="cuda")
+    ys = [torch.zeros((1, s.rows), device="cuda") for s in segs]
+    tasks = [(s, x.data_ptr(), cs.DTYPE_F32, cs.TOKEN_MAJOR, 1, y.data_ptr(), cs.TOKEN_MAJOR) for s, y in zip(segs, ys)]
+    rng = np.random.default_rng(3)
+    with torch.cuda.stream(stream):
+        cs.Segment.matmul_queue_device(tasks)
+        c.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            cs.Segment.matmul_queue_device(tasks)
+        for i in range(4):
+            xh = rng.normal(0, 1 + i, (1, 2048)).astype(np.float32)
+            x.copy_(torch.from_numpy(xh))
+            g.replay()
+            c.synchronize()
+            for p, y in zip(pays, ys):
+                e = rel_err(y.cpu().numpy(), oracle.matmul(p, np.ascontiguousarray(xh.T), 1).T)
+                assert e[0] < TOL and e[1] < TOL, (i, e)
+    for s_ in segs:
+        s_.close()
+    c.close()
+
+
+def test_queue_on_host_buffers(ctx, oracle):
+    # the same list through the host-buffer call: one upload, one download; two tasks share
+    # their activations (one staged copy), one has a batch of its own kind
+    from tests import synth
+    rng = np.random.default_rng(21)
+    pays = [synth.hsdr_payload(r, c, n_atoms=a, k=k, seed=60 + i)
+            for i, (r, c, a, k) in enumerate([(300, 1024, 128, 6), (520, 1024, 256, 8), (77, 1540, 100, 5)])]
+    segs = [cs.Segment.from_payload(p, ctx) for p in pays]
+    x01 = rng.normal(0, 1, (1024, 2)).astype(np.float32)
+    x2 = rng.normal(0, 1, (1540, 2)).astype(np.float32)
+    outs = [np.full((s.rows, 2), np.nan, np.float32) for s in segs]
+    prepared = cs.Segment.matmul_queue([(segs[0], x01, 2, outs[0]), (segs[1], x01, 2, outs[1]), (segs[2], x2, 2, outs[2])])
+    for p, x, out in zip(pays, (x01, x01, x2), outs):
+        e = rel_err(out, oracle.matmul(p, x, 2))
+        assert e[0] < TOL and e[1] < TOL
+    x01 *= 2.0                                               # same arrays, new values, prepared list reused
+    cs.Segment.matmul_queue(None, prepared)
+    e = rel_err(outs[1], oracle.matmul(pays[1], x01, 2))
+    assert e[0] < TOL and e[1] < TOL
+    # mixed batches are issued one by one, 2-D tiles are refused as the reference's fused call refuses them
+    y9 = np.zeros((300, 9), np.float32)
+    x9 = rng.normal(0, 1, (1024, 9)).astype(np.float32)
+    cs.Segment.matmul_queue([(segs[0], x9, 9, y9), (segs[1], x01, 2, outs[1])])
+    e = rel_err(y9, oracle.matmul(pays[0], x9, 9))
+    assert e[0] < TOL and e[1] < TOL
+    seg2d = cs.Segment.from_payload(synth.hsdr_payload(64, 64, tile_rows=32, tile_cols=32, n_atoms=16, k=2, seed=1), ctx)
+    with pytest.raises(cs.CompressionError, match="tile_rows == 1"):
+        cs.Segment.matmul_queue([(seg2d, np.zeros((64, 1), np.float32), 1, np.zeros((64, 1), np.float32))])
