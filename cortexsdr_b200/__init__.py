@@ -299,8 +299,9 @@ class Segment:
     @staticmethod
     def matmul_queue_device(tasks, prepared=None):
         """Independent products in as few launches as possible. tasks: iterable of
-        (segment, x_ptr, x_dtype, x_layout, batch, y_ptr, y_layout[, bias_ptr]). Returns the
-        ctypes array; pass it back as `prepared` to issue the same list again without rebuilding it."""
+        (segment, x_ptr, x_dtype, x_layout, batch, y_ptr, y_layout[, bias_ptr[, after_task]]); after_task
+        is the index of the earlier task whose output this task reads (-1: none). Returns the ctypes
+        array; pass it back as `prepared` to issue the same list again without rebuilding it."""
         if prepared is None:
             tasks = list(tasks)
             prepared = (_lib.MatmulTask * len(tasks))()
@@ -308,6 +309,7 @@ class Segment:
                 prepared[i].seg, prepared[i].x_dev, prepared[i].x_dtype, prepared[i].x_layout = t[0]._h, t[1], t[2], t[3]
                 prepared[i].batch, prepared[i].y_dev, prepared[i].y_layout = t[4], t[5], t[6]
                 prepared[i].bias_dev = t[7] if len(t) > 7 and t[7] else None
+                prepared[i].after_task = t[8] if len(t) > 8 else -1
             prepared._ctx = tasks[0][0].ctx
         ctx = prepared._ctx
         _check(ctx._lib.csdr_matmul_queue_device_async(ctx._h, prepared, len(prepared)))

@@ -48,7 +48,8 @@ class SegmentHeader(C.Structure):
 
 class MatmulTask(C.Structure):
     _fields_ = [("seg", C.c_void_p), ("x_dev", C.c_void_p), ("x_dtype", C.c_int), ("x_layout", C.c_int),
-                ("batch", C.c_size_t), ("y_dev", C.c_void_p), ("y_layout", C.c_int), ("bias_dev", C.c_void_p)]
+                ("batch", C.c_size_t), ("y_dev", C.c_void_p), ("y_layout", C.c_int), ("bias_dev", C.c_void_p),
+                ("after_task", C.c_int)]
 
 
 class MatmulHostTask(C.Structure):

@@ -209,6 +209,7 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         CSDR_CUDA(cudaMemsetAsync(ctx->gemv_seq, 0, 2 * sizeof(uint32_t), ctx->stream));
         if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE")) ctx->gemv_queue = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_DECODER_QUEUE")) ctx->decoder_queue = e[0] != '0';
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE_SINGLE")) ctx->gemv_queue_single = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TENSOR_CORES")) ctx->tensor_cores = e[0] != '0';
@@ -227,6 +228,7 @@ int csdr_context_destroy(csdr_context* ctx) {
         for (auto& s : ctx->scratch) s.reset();
         if (ctx->status_word) cudaFree(ctx->status_word);
         if (ctx->gemv_seq) cudaFree(ctx->gemv_seq);
+        if (ctx->queue_sync) cudaFree(ctx->queue_sync);
         if (ctx->pinned) cudaFreeHost(ctx->pinned);
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
@@ -669,7 +671,10 @@ int csdr_matmul_queue_device_async(csdr_context* ctx, const csdr_matmul_task* ta
                 (t.y_layout != CSDR_LAYOUT_FEATURE_MAJOR && t.y_layout != CSDR_LAYOUT_TOKEN_MAJOR))
                 throw Error(CSDR_ERR_INVALID_ARG, "unknown dtype or layout");
             if (t.batch > 0xFFFFFFFFull) throw Error(CSDR_ERR_LIMIT, "batch too large");
+            if (t.after_task >= static_cast<int>(i) || t.after_task < -1)
+                throw Error(CSDR_ERR_INVALID_ARG, "after_task must name an earlier task of the list, or be -1");
             items[i] = QueueItem{t.seg, t.x_dev, t.x_dtype, t.x_layout, t.batch, t.y_dev, t.y_layout, t.bias_dev};
+            items[i].dep = t.after_task;
         }
         if (gemv_queue_supported(ctx, items.data(), static_cast<uint32_t>(n_tasks))) {
             launch_gemv_queue(ctx, items.data(), static_cast<uint32_t>(n_tasks));

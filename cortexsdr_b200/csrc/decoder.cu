@@ -18,6 +18,7 @@
 #include "internal.hpp"
 #include "kernels/decoder_ops.hpp"
 #include "kernels/gemm_tcgen05.hpp"
+#include "kernels/gemv_queue.hpp"
 
 using namespace csdr;
 
@@ -119,6 +120,7 @@ struct csdr_decoder {
     // attention output, SwiGLU product) for steps that run on the tensor cores
     DevPtr xp_h, xp_att, xp_act;
     bool planes_capable = false;
+    bool queue_capable = false;    // every block linear an HSDR row-tile image the GEMV queue takes
     ~csdr_decoder() {
         for (void* m : xch_maps)
             if (m) cudaIpcCloseMemHandle(m);
@@ -374,6 +376,82 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
     }
 }
 
+// Steps of at most four tokens on one GPU: a block is three launches. The output projection,
+// gate, up and down of block n and q, k, v of block n + 1 run as ONE list on the persistent GEMV
+// kernel, with the residual additions, SwiGLU and both halves of the two RMS normalisations as
+// epilogues of its gather role (the rows leave as h and as h * w with per-CTA sums of squares;
+// the products that consume h * w are scaled by 1 / rms); rotary embedding with the cache write,
+// and attention, stay kernels of their own between two lists.
+bool use_queue(const csdr_decoder* d, uint32_t T) {
+    return d->queue_capable && d->P == 1 && T <= 4u && d->ctx->gemv_queue && d->ctx->decoder_queue;
+}
+
+void run_blocks_queue(csdr_decoder* d, uint32_t T) {
+    const csdr_decoder_config& c = d->cfg;
+    csdr_context* ctx = d->ctx;
+    const uint32_t H = c.hidden, HD = c.head_dim;
+    auto item = [&](const Linear& l, const float* x, float* y) {
+        return QueueItem{l.use(), x, CSDR_DTYPE_F32, CSDR_LAYOUT_TOKEN_MAJOR, T, y, CSDR_LAYOUT_TOKEN_MAJOR, nullptr};
+    };
+    float* hw = F(d->normed);   // h * w of the norm ahead; the first one is normalised outright
+    op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, hw);
+    {
+        const Layer& L = d->layers[0];
+        const QueueItem first[3] = {item(L.q, hw, F(d->q)), item(L.k, hw, F(d->k)), item(L.v, hw, F(d->v))};
+        launch_gemv_queue(ctx, first, 3);
+    }
+    for (uint32_t li = 0; li < c.n_layers; ++li) {
+        const Layer& L = d->layers[li];
+        float* kc = F(d->kcache) + li * d->cache_layer_stride;
+        float* vc = F(d->vcache) + li * d->cache_layer_stride;
+        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
+                      c.max_seq, c.rope_theta);
+        op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        QueueItem list[7];
+        uint32_t n = 0;
+        list[n] = item(L.o, F(d->att), F(d->hidden));            // 0: h += Wo att; h * w_ffn beside it
+        list[n].residual = F(d->hidden);
+        list[n].prep_weight = F(L.ffn_norm);
+        list[n].prep_out = hw;
+        ++n;
+        list[n] = item(L.gate, hw, F(d->gate));                  // 1: gate = Wg norm(h)
+        list[n].dep = 0;
+        list[n].scale_from = 0;
+        ++n;
+        list[n] = item(L.up, hw, F(d->up));                      // 2: act = silu(gate) * (Wu norm(h))
+        list[n].dep = 0;
+        list[n].scale_from = 0;
+        list[n].swiglu_gate = F(d->gate);
+        ++n;
+        list[n] = item(L.down, F(d->up), F(d->hidden));          // 3: h += Wd act
+        list[n].dep = 2;
+        list[n].residual = F(d->hidden);
+        const bool last = li + 1 == c.n_layers;
+        if (!last) {
+            const Layer& N = d->layers[li + 1];
+            list[n].prep_weight = F(N.attn_norm);
+            list[n].prep_out = hw;
+            ++n;
+            const Linear* qkv[3] = {&N.q, &N.k, &N.v};
+            float* outs[3] = {F(d->q), F(d->k), F(d->v)};
+            for (int j = 0; j < 3; ++j) {                        // 4..6: q, k, v of the next block
+                list[n] = item(*qkv[j], hw, outs[j]);
+                list[n].dep = 3;
+                list[n].scale_from = 3;
+                ++n;
+            }
+        } else {
+            ++n;
+        }
+        for (uint32_t i = 0; i < n; ++i) {
+            list[i].scale_eps = c.rms_eps;
+            list[i].scale_width = H;
+        }
+        launch_gemv_queue(ctx, list, n);
+    }
+    op_rmsnorm(ctx, F(d->hidden), F(d->out_norm), T, H, c.rms_eps, F(d->normed));
+}
+
 bool use_planes(const csdr_decoder* d, uint32_t T) {
     if (d->P > 1) return true;
     const csdr_context* ctx = d->ctx;
@@ -389,6 +467,10 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
     const uint32_t H = c.hidden, HD = c.head_dim;
     if (use_planes(d, T)) {
         run_blocks_planes(d, T);
+        return;
+    }
+    if (use_queue(d, T)) {
+        run_blocks_queue(d, T);
         return;
     }
     op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, F(d->normed));
@@ -586,6 +668,23 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
                 widest = std::max(widest, atoms(d->lm_head));
             }
             d->planes_capable = ok;
+            {
+                bool q_ok = true;
+                for (const Layer& L : d->layers) {
+                    const Linear* all[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
+                    for (const Linear* l : all) {
+                        if (l->raw || !l->use()) {
+                            q_ok = false;
+                            continue;
+                        }
+                        const QueueItem probe{l->use(), nullptr, CSDR_DTYPE_F32, CSDR_LAYOUT_TOKEN_MAJOR, 4, nullptr,
+                                              CSDR_LAYOUT_TOKEN_MAJOR, nullptr};
+                        q_ok = q_ok && gemv_queue_supported(ctx, &probe, 1);
+                    }
+                    q_ok = q_ok && !L.gate.raw && !L.up.raw && L.gate.rows_local == L.up.rows_local;
+                }
+                d->queue_capable = q_ok;
+            }
             if (d->P > 1 && !ok)
                 throw Error(CSDR_ERR_UNSUPPORTED,
                             "decoder: tensor parallelism needs every linear as HSDR row tiles with a multiple of 128 "

@@ -97,7 +97,7 @@ struct csdr_context {
     size_t smem_optin = 0;
     uint64_t launches = 0;
     // Grow-only scratch (Dx partials, factored 2-D products, host staging).
-    csdr::DevPtr scratch[6];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials, 5 wait self-test
+    csdr::DevPtr scratch[7];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials, 5 wait self-test, 6 GEMV queue
     void* scratch_get(int slot, size_t bytes);
     int* status_word = nullptr;  // device int: kernels record bounded-wait timeouts here
     // Page-locked, device-mapped host staging for the host-buffer entry points (grow-only).
@@ -108,6 +108,7 @@ struct csdr_context {
     // Fused GEMV: every launch tags its partial results with a fresh non-zero epoch, taken from a
     // device counter ([0] launches completed, [1] finished CTAs) that the launch itself advances.
     uint32_t* gemv_seq = nullptr;
+    uint32_t* queue_sync = nullptr;   // GEMV queue: launch counter pair, then two sets of task counters
     // Iteration limits of the bounded device-side waits (csdr_context_set_wait_limits).
     uint32_t spin_limit_gemv = 1000000u;      // fused GEMV hand-over polls (an L2 round trip each)
     uint32_t spin_limit_barrier = 4000000u;   // mbarrier try_wait rounds of the tensor-core kernels
@@ -115,6 +116,7 @@ struct csdr_context {
     csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool gemv_queue = true;  // CSDR_GEMV_QUEUE=0 keeps lists of products on single and grouped launches
+    bool decoder_queue = true;       // CSDR_DECODER_QUEUE=0 keeps small decoder steps on one launch per operation
     bool gemv_queue_single = false;  // CSDR_GEMV_QUEUE_SINGLE=1 sends single products of at most 4 tokens there too
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
     bool tensor_cores = true;   // CSDR_TENSOR_CORES=0 keeps wide batches on the CUDA-core kernels

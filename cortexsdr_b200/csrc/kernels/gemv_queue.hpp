@@ -1,5 +1,5 @@
-// A list of independent decode GEMVs (1-D row-tile segments, at most 4 tokens each) in one
-// persistent launch: see gemv_queue.cu.
+// A list of decode GEMVs (1-D row-tile segments, at most 4 tokens each) in one persistent launch,
+// with the decoder's glue folded into the gather as per-task epilogues: see gemv_queue.cu.
 #pragma once
 
 #include <cstddef>
@@ -20,9 +20,19 @@ struct QueueItem {
     float* y;               // device, fp32
     int y_layout;
     const float* bias;      // device, R floats, or null
+    // ---- optional glue (token-major fp32 buffers of [batch][rows]) ----
+    const float* residual = nullptr;     // y = W x + residual (may be y itself)
+    const float* swiglu_gate = nullptr;  // y = silu(gate) * (W x); gate = y of the task just before, same rows
+    const float* prep_weight = nullptr;  // also leave y * w in prep_out and the sums of squares of y for scale_from users
+    float* prep_out = nullptr;
+    int dep = -1;                        // index of an earlier task whose rows must be complete before x is read
+    int scale_from = -1;                 // index of an earlier task with prep_weight: y = (W x) / rms of that task's y
+    float scale_eps = 0.0f;
+    uint32_t scale_width = 0;            // rows of that task (the width the mean runs over)
 };
 
-// Every item a 1-D row-tile image with cols a multiple of 4, one common batch of 1 to 4 tokens.
+// Every item a 1-D row-tile image with cols a multiple of 4, one common batch of 1 to 4 tokens;
+// dep and scale_from point backwards within the same group of kMaxQueueTasks.
 bool gemv_queue_supported(const csdr_context* ctx, const QueueItem* items, uint32_t n);
 void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n);
 

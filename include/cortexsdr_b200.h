@@ -196,12 +196,14 @@ CSDR_API int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segmen
                                             int x_layout, size_t batch, float* const* ys_dev,
                                             int y_layout);
 
-/* A list of INDEPENDENT products in as few launches as possible: the heads of a batch of
- * requests, q|k|v and gate|up of a block, the experts of a routed layer. Lists whose members
+/* A list of products in as few launches as possible: the heads of a batch of requests, q|k|v
+ * and gate|up of a block, the experts of a routed layer, a chain of layers. Lists whose members
  * are all 1-D row-tile segments with one common batch of 1 to 4 tokens run as one persistent
  * kernel per 32 tasks, in which the weight stream of task n+1 flows under the hand-over and
  * gather of task n (tasks may differ in shape, activations and outputs); any other list is
- * issued task by task. No task may read what another task of the same list writes. The
+ * issued task by task, in order. A task whose activations are another task's output names that
+ * task in after_task (an index below its own, in the same group of 32; -1: none): its weights
+ * still stream ahead, its activations are read once that task's rows are complete. The
  * reference issues one matmulHSDR call per product (SparseInferenceEngine.cpp:1074-1091). */
 typedef struct {
     const csdr_segment* seg;
@@ -211,6 +213,7 @@ typedef struct {
     float* y_dev;           /* fp32 */
     int y_layout;
     const float* bias_dev;  /* R floats or NULL */
+    int after_task;         /* -1, or the index of the task whose y this task's x_dev is (or depends on) */
 } csdr_matmul_task;
 CSDR_API int csdr_matmul_queue_device_async(csdr_context* ctx, const csdr_matmul_task* tasks,
                                             size_t n_tasks);

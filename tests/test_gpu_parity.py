@@ -539,3 +539,36 @@ def test_queue_on_host_buffers(ctx, oracle):
     seg2d = cs.Segment.from_payload(synth.hsdr_payload(64, 64, tile_rows=32, tile_cols=32, n_atoms=16, k=2, seed=1), ctx)
     with pytest.raises(cs.CompressionError, match="tile_rows == 1"):
         cs.Segment.matmul_queue([(seg2d, np.zeros((64, 1), np.float32), 1, np.zeros((64, 1), np.float32))])
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_queue_chain_of_dependent_products(ctx, oracle, batch):
+    # y1 = W1 x, y2 = W2 y1, y3 = W3 y2 and, beside the chain, y4 = W4 x: one list, one launch; the
+    # later tasks name the task whose rows they read
+    import torch
+    from tests import synth
+    dims = [(640, 1024), (384, 640), (200, 384), (96, 1024)]
+    pays = [synth.hsdr_payload(r, c, n_atoms=128, k=5, seed=80 + i, weight_std=0.05) for i, (r, c) in enumerate(dims)]
+    segs = [cs.Segment.from_payload(p, ctx) for p in pays]
+    xh = np.random.default_rng(batch).normal(0, 1, (batch, 1024)).astype(np.float32)
+    x = torch.from_numpy(xh).cuda()
+    ys = [torch.full((batch, r), float("nan"), device="cuda") for r, _ in dims]
+    F, T = cs.DTYPE_F32, cs.TOKEN_MAJOR
+    tasks = [(segs[0], x.data_ptr(), F, T, batch, ys[0].data_ptr(), T, 0, -1),
+             (segs[3], x.data_ptr(), F, T, batch, ys[3].data_ptr(), T, 0, -1),
+             (segs[1], ys[0].data_ptr(), F, T, batch, ys[1].data_ptr(), T, 0, 0),
+             (segs[2], ys[1].data_ptr(), F, T, batch, ys[2].data_ptr(), T, 0, 2)]
+    torch.cuda.synchronize()
+    for _ in range(3):                       # back to back: alternate counter sets, cleared by the launch before
+        prepared = cs.Segment.matmul_queue_device(tasks)
+    ctx.synchronize()
+    w1 = oracle.matmul(pays[0], np.ascontiguousarray(xh.T), batch)
+    w2 = oracle.matmul(pays[1], w1, batch)
+    w3 = oracle.matmul(pays[2], w2, batch)
+    w4 = oracle.matmul(pays[3], np.ascontiguousarray(xh.T), batch)
+    for got, want in zip(ys, (w1, w2, w3, w4)):
+        e = rel_err(got.cpu().numpy().T, want)
+        assert e[0] < TOL and e[1] < TOL, e
+    with pytest.raises(Exception):           # a task may only point backwards
+        cs.Segment.matmul_queue_device([(segs[0], x.data_ptr(), F, T, batch, ys[0].data_ptr(), T, 0, 0)])
+    del prepared

@@ -160,7 +160,9 @@ def test_generate_text_on_token_ids(sdk, ctx, oracle, tmp_path):
     select_best_from_logits at temperature 0.8 over the tokens generated so far."""
     import cortexsdr_b200 as cs
     from tests import synth
-    cfg = dict(n_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=32, inter=256, vocab=300)
+    # a head size the reference's discovery finds: it tries 128, 64, 256, 32, 16 in that order on
+    # the q/k/v widths (api/cortex_sdk.cpp:1335-1349), so 128-wide q and 64-wide k/v mean heads of 64
+    cfg = dict(n_layers=2, hidden=128, q_heads=2, kv_heads=1, head_dim=64, inter=256, vocab=300)
     path = str(tmp_path / "gen.sdr")
     synth.decoder_archive(path, **cfg, k=3, seed=11, n_atoms=32, kv_atoms=16)
     prompt = [5, 17, 250, 3, 99]
