@@ -116,7 +116,7 @@ struct csdr_context {
     csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool gemv_queue = true;  // CSDR_GEMV_QUEUE=0 keeps lists of products on single and grouped launches
-    bool decoder_queue = true;       // CSDR_DECODER_QUEUE=0 keeps small decoder steps on one launch per operation
+    bool decoder_queue = false;      // CSDR_DECODER_QUEUE=1: decoder steps of up to four tokens run a block as three launches
     bool gemv_queue_single = false;  // CSDR_GEMV_QUEUE_SINGLE=1 sends single products of at most 4 tokens there too
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
     bool tensor_cores = true;   // CSDR_TENSOR_CORES=0 keeps wide batches on the CUDA-core kernels
