@@ -9,34 +9,40 @@
 //
 //   loader    (1 warp)  walks the flat list of work units (task, group of 8 atoms) this CTA owns
 //                       and keeps a ring of shared-memory stages full: per stage 8 dictionary rows
-//                       x 1024 columns and the matching slab of the activations, all as
-//                       cp.async.bulk copies that signal the stage's mbarrier (activations that
-//                       are not fp32 token-major are converted by the warp itself). The dictionary
-//                       is static, so the first ring-full of weight copies is issued BEFORE the
-//                       programmatic-dependent-launch wait, and across a dependency between two
-//                       tasks of the list the weights of the later task are already in flight
-//                       while its activations are still being produced.
+//                       x 1024 columns and, for activations that were there before the launch, the
+//                       matching slab of them, all as cp.async.bulk copies that signal the stage's
+//                       mbarrier. The dictionary is static, so the first ring-full of weight
+//                       copies is issued BEFORE the programmatic-dependent-launch wait, and the
+//                       weights of a task whose activations another task of the list is still
+//                       producing are in flight while it waits.
 //   products  (8 warps) one atom per warp: dot products of the staged row slab with the staged
 //                       activations, accumulated over the row's slabs in registers, reduced with
-//                       warp shuffles, stored as the finished Dx (no column-split partials); the
-//                       warp then checks in on the task's counter (release).
-//   gather    (4 warps) trails behind, task by task: prefetches its rows of the next task's code
-//                       stream (cp.async), waits for the current task's counter (acquire), copies
-//                       Dx to shared memory, then the signed gather in the reference's order and
-//                       the task's epilogue, and checks in on the task's row counter.
+//                       warp shuffles, and published as ONE 64-bit word {value, launch tag} per
+//                       (atom, token): the finished Dx, no column-split partials. Activations that
+//                       an earlier task of the list produces arrive as such tagged words too: the
+//                       eight warps poll their slices of the slab until every word carries the
+//                       launch's tag.
+//   gather    (4 warps) each warp on its own, no barrier between them: prefetches its rows of its
+//                       next task's code stream (cp.async), polls the task's Dx words until they
+//                       carry the launch's tag, then the signed gather in the reference's order
+//                       and the task's epilogue. Lists of plain, independent products give every
+//                       fourth task to a warp; lists with dependencies split each task's rows
+//                       over the four warps instead (shortest path through a chain).
+//
+// A matching tag proves the value beside it (64-bit relaxed gpu-scope accesses are single-copy
+// atomic), so no hand-over needs a fence, a counter or an atomic, and the data itself is what is
+// polled. The tag is the count of queue launches completed, plus one, read from device memory
+// (the last CTA to have read it advances it), so a captured CUDA graph tags every replay afresh.
 //
 // Epilogues fold the decoder glue of api/cortex_sdk.cpp:1569-1679 into the gather so that a block
-// of the decoder is one list: bias; residual add (add_vectors, :1234-1243); SwiGLU against an
-// earlier task's rows (silu_mul, :1245-1256); and the two halves of RMS normalisation (rms_norm,
-// :1208-1232): a task may leave y * w beside y together with per-CTA sums of squares of y, and a
-// later task that consumes y * w multiplies its own product by 1 / sqrt(mean + eps).
-// A task may name an earlier task of the list whose rows must all be written before its
-// activations are read.
+// of the decoder is one list: bias; residual add (add_vectors, :1234-1243); SwiGLU against the
+// task before (silu_mul, :1245-1256); and the two halves of RMS normalisation (rms_norm,
+// :1208-1232): a task may leave y * w beside y together with sums of squares of y, and a later
+// task that consumes y * w multiplies its own product by 1 / sqrt(mean + eps).
 //
-// Every wait is bounded (mbarrier phases, counters): one that runs out sets the status word, all
-// roles of the CTA stop waiting, and the kernel returns. Counters live in two sets used by
-// alternate launches; a launch clears the set of the launch after it. All CTAs must be resident
-// (grid = SM count, one per SM).
+// Every wait is bounded (mbarrier phases, polls): one that runs out sets the status word, all
+// roles of the CTA stop waiting, and the kernel returns. All CTAs must be resident (grid = SM
+// count, one per SM).
 #include <algorithm>
 
 #include "../internal.hpp"
@@ -49,33 +55,37 @@ namespace {
 
 constexpr uint32_t kLoaderWarps = 1, kProductWarps = 8, kGatherWarps = 4;
 constexpr uint32_t kThreads = 32u * (kLoaderWarps + kProductWarps + kGatherWarps);
-constexpr uint32_t kGatherThreads = 32u * kGatherWarps;
+constexpr uint32_t kProductThreads = 32u * kProductWarps;
 constexpr uint32_t kAtomsPerUnit = 8;          // one per product warp
 constexpr uint32_t kSlab = 1024;               // columns per stage
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kMaxTokens = 4;
 
 enum : uint32_t { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+enum : uint32_t { X_PLAIN = 0, X_TAGGED = 1 };
+
+typedef unsigned long long u64;
 
 struct QTask {
     const float* D;
     const uint16_t* codes;
     const float* scales;
-    const void* x;
-    float* y;
+    const void* x;            // X_PLAIN: activations (dtype, layout); X_TAGGED: u64 words [M][C]
+    float* y;                 // fp32 result, or null when only the tagged copy is wanted
+    u64* y_tag;               // tagged copy [M][R] for a later task of the list, or null
     const float* bias;
     const float* residual;    // [M][R] token-major, may alias y
     const float* gate;        // EPI_SWIGLU: the gate projection's rows, [M][R]
-    const float* prep_w;      // leave y * w in prep_out and this CTA's sums of squares of y in the task's slot
+    const float* prep_w;      // leave y * w (prep_out and/or prep_tag) and sums of squares of y
     float* prep_out;
+    u64* prep_tag;
     uint32_t K, R, C, S, k;
     uint32_t unit0;           // first flat unit of this task
     uint32_t n_units;
-    uint32_t dx_off;          // float offset of its Dx slot: [K][MT]
+    uint32_t dx_off;          // word offset of its Dx slot: [K][MT]
     uint32_t rows_per_cta;
-    uint32_t x_dtype, x_layout, y_layout;
+    uint32_t x_kind, x_dtype, x_layout, y_layout;
     uint32_t M;
-    int32_t dep;              // earlier task whose rows must be complete before x is read, or -1
     int32_t scale_from;       // earlier task whose sums of squares normalise this product, or -1
     float scale_eps, scale_inv_width;
     uint32_t epilogue;
@@ -86,11 +96,13 @@ struct QParams {
     uint32_t n_tasks, n_units;
     uint32_t n_stages;          // ring depth
     uint32_t stage_bytes;       // D slab + x slab
-    uint32_t codes_bytes;       // one code buffer of the gather role
-    float* dx;                  // Dx slots
-    float* sumsq;               // [task][grid][kMaxTokens] per-CTA sums of squares
+    uint32_t gw_bytes;          // shared memory of one gather warp: Dx copy + two code buffers + scales
+    uint32_t dxs_bytes;         // the Dx copy inside it
+    uint32_t codes_bytes;       // one code buffer inside it
+    uint32_t split_rows;        // 1: a task's rows are split over the gather warps; 0: tasks are dealt out to them
+    u64* dx;                    // tagged Dx words
+    u64* sumsq;                 // tagged sums of squares: [task][grid * kGatherWarps][kMaxTokens]
     uint32_t* seq;              // [0] queue launches completed, [1] CTAs that have read [0]
-    uint32_t* counters;         // [2 sets][kMaxQueueTasks][2]: products checked in, CTAs whose rows are written
     int* status;
     uint32_t spin_poll, spin_barrier;
 };
@@ -118,47 +130,72 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     return false;
 }
 
-// Bounded wait until a counter reaches its target (acquire): one look, then at most `limit` more.
-__device__ __forceinline__ bool count_wait(const uint32_t* c, uint32_t target, uint32_t limit, const volatile int* failed) {
-    for (uint32_t i = 0;; ++i) {
-        uint32_t v;
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(c) : "memory");
-        if (v >= target) return true;
-        if (i >= limit || *failed) return false;
-    }
+__device__ __forceinline__ u64 ld_tagged(const u64* p) {
+    u64 v;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_tagged(u64* p, float value, uint32_t tag) {
+    const u64 w = (static_cast<u64>(tag) << 32) | __float_as_uint(value);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 
-__device__ __forceinline__ void count_arrive(uint32_t* c) {
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c) : "memory");
-}
-
-// Queue launches completed so far; its parity names this launch's counter set. The thread that
-// calls this checks in (acq_rel) after reading; the CTA that checks in last knows every CTA has
-// read the count and advances it for the next launch.
-__device__ __forceinline__ uint32_t take_launch_index(uint32_t* seq) {
+// The launch's tag: queue launches completed + 1. The thread that calls this checks in with an
+// acq_rel atomic after reading the counter; the CTA that checks in last knows every CTA has read
+// it and advances it for the next launch (never to the value whose successor would be the tag 0).
+__device__ __forceinline__ uint32_t take_tag(uint32_t* seq) {
     uint32_t done, prev;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(seq) : "memory");
     asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(seq + 1) : "memory");
     if (prev == gridDim.x - 1u) {
         seq[1] = 0u;
-        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(seq), "r"(done + 1u) : "memory");
+        const uint32_t next = done + 1u;
+        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(seq), "r"(next == 0xFFFFFFFFu ? 0u : next) : "memory");
     }
-    return done;
+    return done + 1u;
 }
 
 __device__ __forceinline__ XView x_view(const QTask& t) {
     return XView{t.x, static_cast<int>(t.x_dtype), static_cast<int>(t.x_layout), t.C, t.M, 0u, t.M};
 }
 
-// Shared memory: [n_stages][stage_bytes] | dxs [max K][MT] | codes [2][codes_bytes] | scales [2][16]
+// Polls `n` tagged words (word i of this lane at src[i * stride]) in batches of B loads in
+// flight until every one carries `tag`; stores the values through `put(i, value)`. Bounded:
+// returns false when a batch did not complete within `limit` rounds (or another role gave up).
+template <int B, typename Put>
+__device__ __forceinline__ bool poll_words(const u64* src, uint32_t n, uint32_t stride, uint32_t tag, uint32_t& limit,
+                                           const volatile int* failed, bool backoff, Put&& put) {
+    bool ok = true;
+    for (uint32_t i0 = 0; i0 < n; i0 += B) {
+        u64 e[B];
+        for (uint32_t spins = 0;; ++spins) {
+            bool all = true;
+#pragma unroll
+            for (int q = 0; q < B; ++q) e[q] = i0 + q < n ? ld_tagged(src + static_cast<size_t>(i0 + q) * stride) : (static_cast<u64>(tag) << 32);
+#pragma unroll
+            for (int q = 0; q < B; ++q) all = all && static_cast<uint32_t>(e[q] >> 32) == tag;
+            if (all) break;
+            if (spins >= limit || *failed) {
+                ok = false;
+                limit = 0u;   // nothing after a wait that ran out waits again
+                break;
+            }
+            if (backoff) __nanosleep(128);   // a warp that trails the products on purpose polls gently
+        }
+#pragma unroll
+        for (int q = 0; q < B; ++q)
+            if (i0 + q < n) put(i0 + q, __uint_as_float(static_cast<uint32_t>(e[q])));
+    }
+    return ok;
+}
+
+// Shared memory: [n_stages][stage_bytes] | per gather warp: Dx copy, codes [2][codes_bytes], scales [2][16]
 template <int MT>
 __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __grid_constant__ QParams p) {
     extern __shared__ __align__(128) unsigned char qsm[];
-    __shared__ __align__(8) unsigned long long full_bar[kMaxStages], empty_bar[kMaxStages];
+    __shared__ __align__(8) u64 full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ int failed_s;
-    __shared__ uint32_t set_s;
-    __shared__ float red_s[kGatherThreads];
-    __shared__ float inv_s[kMaxTokens];
+    __shared__ uint32_t tag_s;
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t NS = p.n_stages;
@@ -184,9 +221,6 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
         uint32_t it_issue = 0, it_fill = 0;                 // stage counters over this CTA's whole walk
         uint32_t ui = blockIdx.x, us = 0, uti = 0;           // weight cursor: unit, slab within it, task
         uint32_t fi = blockIdx.x, fs = 0, fti = 0;           // activation cursor
-        uint32_t dep_seen = 0xFFFFFFFFu;                     // task whose dependency has been awaited
-        const uint32_t* cnt = nullptr;                       // this launch's counter set (known after the wait)
-        uint32_t limit = p.spin_poll;
         bool ok = true;
         auto issue = [&]() {   // dictionary rows of (ui, us) into slot it_issue % NS
             task_of(ui, uti);
@@ -215,49 +249,42 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 ui += gridDim.x;
             }
         };
-        auto fill = [&]() -> bool {   // activations of (fi, fs) into slot it_fill % NS; then the stage is armed
+        auto fill = [&]() {   // activations of (fi, fs) into slot it_fill % NS; then the stage is armed
             task_of(fi, fti);
             const QTask& t = p.task[fti];
-            if (t.dep >= 0 && dep_seen != fti) {
-                // the rows this task reads are written by another task of the list
-                int seen = 1;
-                if (lane == 0) seen = count_wait(cnt + 2 * t.dep + 1, gridDim.x, limit, failed) ? 1 : 0;
-                seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
-                if (!seen) return false;
-                asm volatile("fence.proxy.async;" ::: "memory");   // the bulk copies below read those rows
-                dep_seen = fti;
-            }
             const uint32_t slot = it_fill % NS;
             const uint32_t c0 = fs * kSlab;
             const uint32_t cw = min(kSlab, t.C - c0);
             float* xs = reinterpret_cast<float*>(qsm + static_cast<size_t>(slot) * p.stage_bytes + kAtomsPerUnit * kSlab * 4u);
             const uint32_t bar = smem_u32(&full_bar[slot]);
-            const XView xv = x_view(t);
-            const bool rows_contig = xv.layout == CSDR_LAYOUT_TOKEN_MAJOR || xv.Mtotal == 1;
-            if (xv.dtype == CSDR_DTYPE_F32 && rows_contig &&
-                ((reinterpret_cast<uintptr_t>(xv.x) | (static_cast<uintptr_t>(xv.C) * 4u)) & 15u) == 0) {
-                // one bulk copy per token, completing on the stage's barrier like the weights
-                if (lane == 0)
-                    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(xv.M * cw * 4u)
-                                 : "memory");
-                __syncwarp();
-                if (lane < xv.M) {
-                    const float* src = static_cast<const float*>(xv.x) + static_cast<size_t>(lane) * xv.C + c0;
-                    asm volatile(
-                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                            smem_u32(xs + lane * kSlab)),
-                        "l"(src), "r"(cw * 4u), "r"(bar)
-                        : "memory");
+            if (t.x_kind == X_PLAIN) {
+                const XView xv = x_view(t);
+                const bool rows_contig = xv.layout == CSDR_LAYOUT_TOKEN_MAJOR || xv.Mtotal == 1;
+                if (xv.dtype == CSDR_DTYPE_F32 && rows_contig &&
+                    ((reinterpret_cast<uintptr_t>(xv.x) | (static_cast<uintptr_t>(xv.C) * 4u)) & 15u) == 0) {
+                    // one bulk copy per token, completing on the stage's barrier like the weights
+                    if (lane == 0)
+                        asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(xv.M * cw * 4u)
+                                     : "memory");
+                    __syncwarp();
+                    if (lane < xv.M) {
+                        const float* src = static_cast<const float*>(xv.x) + static_cast<size_t>(lane) * xv.C + c0;
+                        asm volatile(
+                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                smem_u32(xs + lane * kSlab)),
+                            "l"(src), "r"(cw * 4u), "r"(bar)
+                            : "memory");
+                    }
+                } else {
+                    for (uint32_t i = lane; i < MT * kSlab; i += 32u) {
+                        const uint32_t b = i / kSlab, c = i - b * kSlab;
+                        if (c < cw && b < xv.M) xs[i] = load_x(xv, c0 + c, b);
+                    }
                 }
-            } else {
-                for (uint32_t i = lane; i < MT * kSlab; i += 32u) {
-                    const uint32_t b = i / kSlab, c = i - b * kSlab;
-                    if (c < cw && b < xv.M) xs[i] = load_x(xv, c0 + c, b);
-                }
-            }
+            }   // X_TAGGED: the product warps fetch the slab themselves when they reach the stage
             __syncwarp();
             if (lane == 0) {
-                unsigned long long st;
+                u64 st;
                 asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 %0, [%1];" : "=l"(st) : "r"(bar) : "memory");
                 (void)st;
             }
@@ -266,26 +293,15 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 fs = 0;
                 fi += gridDim.x;
             }
-            return true;
         };
         // the first ring-full of weight copies does not depend on anything before this launch
         while (ui < p.n_units && it_issue < NS) issue();
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (lane == 0) {
-            const uint32_t done = take_launch_index(p.seq);
-            set_s = done & 1u;
-            // the other set belongs to the launch after this one: clear it (its last user has finished)
-            if (blockIdx.x == 0) {
-                uint32_t* other = p.counters + ((done + 1u) & 1u) * (2u * kMaxQueueTasks);
-                for (uint32_t i = 0; i < 2u * kMaxQueueTasks; ++i) other[i] = 0u;
-            }
-        }
+        if (lane == 0) tag_s = take_tag(p.seq);
         asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
-        cnt = p.counters + set_s * (2u * kMaxQueueTasks);
-        if (*reinterpret_cast<const volatile int*>(p.status) != 0) limit = 0u;
         while (ok && (it_fill < it_issue || ui < p.n_units)) {
-            while (ok && it_fill < it_issue) ok = fill();
-            if (ok && ui < p.n_units) {
+            while (it_fill < it_issue) fill();
+            if (ui < p.n_units) {
                 // slot of the next stage: free once the products have drained its previous use
                 const uint32_t slot = it_issue % NS, use = it_issue / NS;
                 if (!mbar_wait(smem_u32(&empty_bar[slot]), (use - 1u) & 1u, p.spin_barrier, failed)) {
@@ -304,7 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
             // were armed with bytes but never received their arrival, then wait for the bytes
             for (uint32_t itx = it_fill; itx < it_issue; ++itx) {
                 if (lane == 0) {
-                    unsigned long long st;
+                    u64 st;
                     asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 %0, [%1];"
                                  : "=l"(st)
                                  : "r"(smem_u32(&full_bar[itx % NS]))
@@ -323,11 +339,12 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
         // ================= products =================
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
-        uint32_t* cnt = p.counters + set_s * (2u * kMaxQueueTasks);
+        const uint32_t tag = tag_s;
         const uint32_t w = warp - 1u;                         // atom within the unit
+        uint32_t limit = *reinterpret_cast<const volatile int*>(p.status) != 0 ? 0u : p.spin_poll;
         uint32_t it = 0, ti = 0;
         bool ok = true;
-        for (uint32_t u = blockIdx.x; ok && u < p.n_units; u += gridDim.x) {
+        for (uint32_t u = blockIdx.x; u < p.n_units; u += gridDim.x) {
             task_of(u, ti);
             const QTask& t = p.task[ti];
             const uint32_t atom = (u - t.unit0) * kAtomsPerUnit + w;
@@ -337,15 +354,51 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
             for (int b = 0; b < MT; ++b) acc[b] = 0.0f;
             for (uint32_t s = 0; s < n_st; ++s, ++it) {
                 const uint32_t slot = it % NS;
-                if (!mbar_wait(smem_u32(&full_bar[slot]), (it / NS) & 1u, p.spin_barrier, failed)) {
-                    ok = false;
-                    break;
+                unsigned char* st = qsm + static_cast<size_t>(slot) * p.stage_bytes;
+                const uint32_t cw = min(kSlab, t.C - s * kSlab);
+                if (t.x_kind == X_TAGGED) {
+                    // this warp's eighth of the slab, token by token: 128 columns, four per lane
+                    float* xs = reinterpret_cast<float*>(st + kAtomsPerUnit * kSlab * 4u);
+                    const uint32_t c_lane = w * 128u + lane * 4u;
+                    if (c_lane < cw) {
+                        const u64* src = static_cast<const u64*>(t.x) + s * kSlab + c_lane;
+                        // word i of this lane: token i / 4, column c_lane + i % 4
+                        u64 e[4 * MT];
+                        for (uint32_t spins = 0;; ++spins) {
+                            bool all = true;
+#pragma unroll
+                            for (int q = 0; q < 4 * MT; ++q) {
+                                const uint32_t b = q >> 2;
+                                e[q] = b < t.M ? ld_tagged(src + static_cast<size_t>(b) * t.C + (q & 3)) : (static_cast<u64>(tag) << 32);
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4 * MT; ++q) all = all && static_cast<uint32_t>(e[q] >> 32) == tag;
+                            if (all) break;
+                            if (spins >= limit || *failed) {   // gave up: every role of the CTA stops waiting
+                                ok = false;
+                                limit = 0u;
+                                failed_s = 1;
+                                break;
+                            }
+                        }
+#pragma unroll
+                        for (int b = 0; b < MT; ++b)
+                            *reinterpret_cast<float4*>(xs + b * kSlab + c_lane) =
+                                make_float4(__uint_as_float(static_cast<uint32_t>(e[4 * b])), __uint_as_float(static_cast<uint32_t>(e[4 * b + 1])),
+                                            __uint_as_float(static_cast<uint32_t>(e[4 * b + 2])), __uint_as_float(static_cast<uint32_t>(e[4 * b + 3])));
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(kProductThreads) : "memory");   // the whole slab is staged
                 }
-                if (atom < t.K) {
-                    const unsigned char* st = qsm + static_cast<size_t>(slot) * p.stage_bytes;
+                // after a wait has run out the warp keeps walking its stages (the named barrier above
+                // needs all eight warps) but no longer waits or computes
+                if (!mbar_wait(smem_u32(&full_bar[slot]), (it / NS) & 1u, ok ? p.spin_barrier : 1u, failed)) {
+                    ok = false;
+                    failed_s = 1;
+                }
+                if (ok && atom < t.K) {
                     const float4* d4 = reinterpret_cast<const float4*>(st + w * (kSlab * 4u));
                     const float4* x4 = reinterpret_cast<const float4*>(st + kAtomsPerUnit * kSlab * 4u);
-                    const uint32_t cw4 = min(kSlab, t.C - s * kSlab) >> 2;
+                    const uint32_t cw4 = cw >> 2;
 #pragma unroll
                     for (uint32_t j = 0; j < kSlab / 128u; ++j) {
                         const uint32_t c4 = j * 32u + lane;
@@ -366,12 +419,11 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 }
                 __syncwarp();
                 if (lane == 0) {
-                    unsigned long long stt;
+                    u64 stt;
                     asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 %0, [%1];" : "=l"(stt) : "r"(smem_u32(&empty_bar[slot])) : "memory");
                     (void)stt;
                 }
             }
-            if (!ok) break;
             float mine = 0.0f;
 #pragma unroll
             for (int b = 0; b < MT; ++b) {
@@ -380,94 +432,95 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
                 if (lane == static_cast<uint32_t>(b)) mine = v;
             }
-            if (lane < MT && atom < t.K) p.dx[t.dx_off + static_cast<size_t>(atom) * MT + lane] = mine;
-            __syncwarp();
-            if (lane == 0) count_arrive(cnt + 2 * ti);          // this warp's share of the task's Dx is written
+            if (ok && lane < MT && atom < t.K) st_tagged(p.dx + t.dx_off + static_cast<size_t>(atom) * MT + lane, mine, tag);
         }
-        if (!ok && lane == 0) {
-            failed_s = 1;
-            atomicExch(p.status, 1);
-        }
+        if (!ok && lane == 0) atomicExch(p.status, 1);
     } else {
-        // ================= gather =================
-        const uint32_t gt = tid - 32u * (kLoaderWarps + kProductWarps);
-        unsigned char* tail = qsm + static_cast<size_t>(NS) * p.stage_bytes;
-        uint32_t max_k = 0;
-        for (uint32_t i = 0; i < p.n_tasks; ++i) max_k = max(max_k, p.task[i].K);
-        float* dxs = reinterpret_cast<float*>(tail);
-        unsigned char* codes_buf = tail + ((static_cast<size_t>(max_k) * MT * 4u + 127u) & ~static_cast<size_t>(127));
+        // ================= gather: four warps, each on its own =================
+        const uint32_t g = warp - (kLoaderWarps + kProductWarps);
+        unsigned char* mine = qsm + static_cast<size_t>(NS) * p.stage_bytes + static_cast<size_t>(g) * p.gw_bytes;
+        float* dxs = reinterpret_cast<float*>(mine);
+        unsigned char* codes_buf = mine + p.dxs_bytes;
         float* scales_buf = reinterpret_cast<float*>(codes_buf + 2u * static_cast<size_t>(p.codes_bytes));
-        auto fetch_codes = [&](uint32_t ti) {   // this CTA's rows of task ti's code stream, non-blocking
-            const QTask& t = p.task[ti];
-            const uint32_t row0 = blockIdx.x * t.rows_per_cta;
-            if (row0 < t.R) {
-                const uint32_t rows_here = min(t.rows_per_cta, t.R - row0);
-                const uint32_t slots = t.S * t.k;
-                const size_t byte0 = static_cast<size_t>(row0) * slots * 2u;
-                const size_t aligned0 = byte0 & ~static_cast<size_t>(15);
-                const uint32_t n16 = (static_cast<uint32_t>(byte0 - aligned0) + rows_here * slots * 2u + 15u) >> 4;
-                unsigned char* dst = codes_buf + (ti & 1u) * static_cast<size_t>(p.codes_bytes);
-                const unsigned char* src = reinterpret_cast<const unsigned char*>(t.codes) + aligned0;
-                for (uint32_t i = gt; i < n16; i += kGatherThreads)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + i * 16u)), "l"(src + i * 16u)
-                                 : "memory");
-                float* sc = scales_buf + (ti & 1u) * 16u;
-                for (uint32_t i = gt; i < t.S && i < 16u; i += kGatherThreads)
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(sc + i)), "l"(t.scales + i) : "memory");
+        const uint32_t t_first = p.split_rows ? 0u : g, t_step = p.split_rows ? 1u : kGatherWarps;
+        // rows of task t this warp gathers
+        auto my_rows = [&](const QTask& t, uint32_t& row0, uint32_t& rows_here) {
+            uint32_t r0 = blockIdx.x * t.rows_per_cta, n = r0 < t.R ? min(t.rows_per_cta, t.R - r0) : 0u;
+            if (p.split_rows) {
+                const uint32_t per = t.rows_per_cta / kGatherWarps;   // rows_per_cta is a multiple of 8
+                const uint32_t lo = min(n, g * per), hi = min(n, (g + 1u) * per);
+                r0 += lo;
+                n = hi - lo;
+            }
+            row0 = r0;
+            rows_here = n;
+        };
+        auto fetch_codes = [&](uint32_t ti, uint32_t buf) {   // non-blocking; one commit group per call
+            if (ti < p.n_tasks) {
+                const QTask& t = p.task[ti];
+                uint32_t row0, rows_here;
+                my_rows(t, row0, rows_here);
+                if (rows_here) {
+                    const uint32_t slots = t.S * t.k;
+                    const size_t byte0 = static_cast<size_t>(row0) * slots * 2u;
+                    const size_t aligned0 = byte0 & ~static_cast<size_t>(15);
+                    const uint32_t n16 = (static_cast<uint32_t>(byte0 - aligned0) + rows_here * slots * 2u + 15u) >> 4;
+                    unsigned char* dst = codes_buf + buf * static_cast<size_t>(p.codes_bytes);
+                    const unsigned char* src = reinterpret_cast<const unsigned char*>(t.codes) + aligned0;
+                    for (uint32_t i = lane; i < n16; i += 32u)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + i * 16u)), "l"(src + i * 16u)
+                                     : "memory");
+                    float* sc = scales_buf + buf * 16u;
+                    if (lane < t.S && lane < 16u)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(sc + lane)), "l"(t.scales + lane) : "memory");
+                }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        fetch_codes(0);                                      // static weights: before the dependency wait
+        fetch_codes(t_first, 0);                             // static weights: before the dependency wait
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
-        uint32_t* cnt = p.counters + set_s * (2u * kMaxQueueTasks);
+        const uint32_t tag = tag_s;
         uint32_t limit = *reinterpret_cast<const volatile int*>(p.status) != 0 ? 0u : p.spin_poll;
         bool late = false;
-        for (uint32_t ti = 0; ti < p.n_tasks; ++ti) {
+        uint32_t buf = 0;
+        const uint32_t n_parts = gridDim.x * kGatherWarps;
+        for (uint32_t ti = t_first; ti < p.n_tasks; ti += t_step, buf ^= 1u) {
             const QTask& t = p.task[ti];
-            if (ti + 1u < p.n_tasks) fetch_codes(ti + 1u);
-            else asm volatile("cp.async.commit_group;" ::: "memory");
-            const uint32_t row0 = blockIdx.x * t.rows_per_cta;
-            const bool active = row0 < t.R;
-            // hand-over: every product warp of every unit of this task has checked in
-            if (gt == 0) {
-                bool seen = count_wait(cnt + 2 * ti, t.n_units * kProductWarps, limit, failed);
-                if (seen && t.scale_from >= 0) seen = count_wait(cnt + 2 * t.scale_from + 1, gridDim.x, limit, failed);
-                if (!seen) {
+            fetch_codes(ti + t_step, buf ^ 1u);
+            uint32_t row0, rows_here;
+            my_rows(t, row0, rows_here);
+            // hand-over: this task's Dx words, sixteen loads in flight per lane
+            if (rows_here) {
+                const uint32_t n_w = t.K * MT;
+                const uint32_t n_mine = lane < n_w ? (n_w - lane + 31u) / 32u : 0u;
+                if (!poll_words<16>(p.dx + t.dx_off + lane, n_mine, 32u, tag, limit, failed, !p.split_rows,
+                                    [&](uint32_t i, float v) { dxs[lane + i * 32u] = v; }))
                     late = true;
-                    failed_s = 1;
-                }
             }
-            asm volatile("bar.sync 2, %0;" ::"n"(kGatherThreads) : "memory");
-            if (*failed) limit = 0u;
-            if (active) {
-                const float* src = p.dx + t.dx_off;
-                const uint32_t n4 = (t.K * MT) >> 2;
-                for (uint32_t i = gt; i < n4; i += kGatherThreads)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dxs + i * 4u)), "l"(src + i * 4u) : "memory");
-                for (uint32_t i = (n4 << 2) + gt; i < t.K * MT; i += kGatherThreads) dxs[i] = __ldcg(src + i);
-            }
-            if (t.scale_from >= 0 && gt < t.M) {
-                // 1 / rms of the rows this task's activations came from: the per-CTA sums in CTA order
-                const float* ps = p.sumsq + static_cast<size_t>(t.scale_from) * gridDim.x * kMaxTokens + gt;
+            float inv = 1.0f;
+            if (t.scale_from >= 0) {
+                // 1 / rms of the rows this task's activations came from: the partial sums of every
+                // gather warp of every CTA, added in slot order (lane b takes token b)
                 float ss = 0.0f;
-                for (uint32_t c = 0; c < gridDim.x; ++c) ss += __ldcg(ps + static_cast<size_t>(c) * kMaxTokens);
-                inv_s[gt] = 1.0f / sqrtf(ss * t.scale_inv_width + t.scale_eps);
+                if (lane < t.M) {
+                    const u64* ps = p.sumsq + static_cast<size_t>(t.scale_from) * n_parts * kMaxTokens + lane;
+                    if (!poll_words<16>(ps, n_parts, kMaxTokens, tag, limit, failed, false, [&](uint32_t, float v) { ss += v; })) late = true;
+                }
+                const float mine_inv = 1.0f / sqrtf(ss * t.scale_inv_width + t.scale_eps);
+                inv = __shfl_sync(0xFFFFFFFFu, mine_inv, lane % MT);
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 0;" ::: "memory");      // this task's codes and Dx (the next task's codes flew during the wait above)
-            asm volatile("bar.sync 2, %0;" ::"n"(kGatherThreads) : "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");      // this task's codes (the next task's may still fly)
+            __syncwarp();
             float ss_mine = 0.0f;
-            const uint32_t b = gt % MT;
-            if (active) {
-                const uint32_t rows_here = min(t.rows_per_cta, t.R - row0);
+            const uint32_t b = lane % MT;
+            if (rows_here) {
                 const uint32_t slots = t.S * t.k;
                 const uint32_t skip = static_cast<uint32_t>((static_cast<size_t>(row0) * slots * 2u) & 15u) >> 1;
-                const uint16_t* cs = reinterpret_cast<const uint16_t*>(codes_buf + (ti & 1u) * static_cast<size_t>(p.codes_bytes)) + skip;
-                const float* sc = scales_buf + (ti & 1u) * 16u;
-                constexpr uint32_t RP = kGatherThreads / MT;
-                const float inv = t.scale_from >= 0 && b < t.M ? inv_s[b] : 1.0f;
-                for (uint32_t rl = gt / MT; rl < rows_here; rl += RP) {
+                const uint16_t* cs = reinterpret_cast<const uint16_t*>(codes_buf + buf * static_cast<size_t>(p.codes_bytes)) + skip;
+                const float* sc = scales_buf + buf * 16u;
+                constexpr uint32_t RP = 32u / MT;
+                for (uint32_t rl = lane / MT; rl < rows_here; rl += RP) {
                     const uint16_t* rc = cs + rl * slots;
                     float accr = 0.0f;
                     for (uint32_t l = 0; l < t.S; ++l) {
@@ -493,46 +546,67 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                         if (t.bias) accr += t.bias[r];
                         const size_t tm = static_cast<size_t>(b) * t.R + r;
                         if (t.epilogue == EPI_SWIGLU) {
-                            const float g = t.gate[tm];
-                            accr = (g * (1.0f / (1.0f + expf(-g)))) * accr;
+                            const float gv = t.gate[tm];
+                            accr = (gv * (1.0f / (1.0f + expf(-gv)))) * accr;
                         }
                         if (t.residual) accr += t.residual[tm];
-                        const size_t yi = t.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * t.M + b : tm;
-                        t.y[yi] = accr;
+                        if (t.y) t.y[t.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * t.M + b : tm] = accr;
+                        if (t.y_tag) st_tagged(t.y_tag + tm, accr, tag);
                         if (t.prep_w) {
-                            t.prep_out[tm] = accr * t.prep_w[r];
+                            const float hw = accr * t.prep_w[r];
+                            if (t.prep_out) t.prep_out[tm] = hw;
+                            if (t.prep_tag) st_tagged(t.prep_tag + tm, hw, tag);
                             ss_mine = fmaf(accr, accr, ss_mine);
                         }
                     }
                 }
             }
             if (t.prep_w) {
-                // this CTA's sums of squares per token, added up in thread order
-                red_s[gt] = ss_mine;
-                asm volatile("bar.sync 2, %0;" ::"n"(kGatherThreads) : "memory");
-                if (gt < kMaxTokens) {
-                    float ss = 0.0f;
-                    if (gt < MT)
-                        for (uint32_t j = gt; j < kGatherThreads; j += MT) ss += red_s[j];
-                    p.sumsq[(static_cast<size_t>(ti) * gridDim.x + blockIdx.x) * kMaxTokens + gt] = ss;
+                // this warp's sums of squares per token: lanes with the same token, in lane order
+                float ss = 0.0f;
+                for (uint32_t j = b; j < 32u; j += MT) ss += __shfl_sync(0xFFFFFFFFu, ss_mine, j);
+                if (lane < MT && lane < kMaxTokens) {
+                    // with the tasks dealt out, the other three slots of the CTA hold nothing
+                    const size_t base = (static_cast<size_t>(ti) * n_parts + static_cast<size_t>(blockIdx.x) * kGatherWarps) * kMaxTokens;
+                    if (p.split_rows) {
+                        st_tagged(p.sumsq + base + g * kMaxTokens + lane, lane < t.M ? ss : 0.0f, tag);
+                    } else {
+                        for (uint32_t q = 0; q < kGatherWarps; ++q)
+                            st_tagged(p.sumsq + base + q * kMaxTokens + lane, q == 0 && lane < t.M ? ss : 0.0f, tag);
+                    }
                 }
             }
-            asm volatile("bar.sync 2, %0;" ::"n"(kGatherThreads) : "memory");   // rows written; dxs and the code buffer are free
-            if (gt == 0) count_arrive(cnt + 2 * ti + 1);
+            __syncwarp();   // dxs and the code buffer are free for the warp's next task
         }
-        if (late && gt == 0) atomicExch(p.status, 1);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (late && lane == 0) {
+            failed_s = 1;
+            atomicExch(p.status, 1);
+        }
     }
 }
 
 uint32_t stage_bytes_for(int mt) { return kAtomsPerUnit * kSlab * 4u + static_cast<uint32_t>(mt) * kSlab * 4u; }
 uint32_t codes_bytes_for(uint32_t max_code_bytes) { return (max_code_bytes + 31u + 127u) & ~127u; }
+uint32_t dxs_bytes_for(uint32_t max_k, int mt) { return (max_k * static_cast<uint32_t>(mt) * 4u + 127u) & ~127u; }
 size_t tail_bytes_for(uint32_t max_k, int mt, uint32_t max_code_bytes) {
-    return ((static_cast<size_t>(max_k) * mt * 4u + 127u) & ~static_cast<size_t>(127)) + 2u * codes_bytes_for(max_code_bytes) + 128u;
+    return static_cast<size_t>(kGatherWarps) * (dxs_bytes_for(max_k, mt) + 2u * codes_bytes_for(max_code_bytes) + 128u);
 }
 size_t smem_budget(const csdr_context* ctx) { return std::min<size_t>(ctx->smem_optin, 216u * 1024u); }
 uint32_t rows_per_cta_for(const csdr_context* ctx, uint32_t rows) {
     const uint32_t G = static_cast<uint32_t>(ctx->sm_count);
     return ((rows + G - 1u) / G + 7u) & ~7u;
+}
+bool needs_split(const QueueItem* items, uint32_t n) {
+    for (uint32_t i = 0; i < n; ++i)
+        if (items[i].dep >= 0 || items[i].scale_from >= 0 || items[i].swiglu_gate || items[i].prep_weight || items[i].residual)
+            return true;
+    return n < 2u * kGatherWarps;   // short lists: the shortest path through each task
+}
+// bytes of code stream one gather warp stages per task
+uint32_t code_bytes_per_warp(const csdr_context* ctx, const Geometry& g, bool split) {
+    const uint32_t rpc = rows_per_cta_for(ctx, g.rows);
+    return (split ? rpc / kGatherWarps : rpc) * g.slots() * 2u;
 }
 
 template <int MT>
@@ -540,6 +614,8 @@ void launch_t(csdr_context* ctx, QParams& p, uint32_t max_k, uint32_t max_code_b
     auto kern = hsdr_gemv_queue_kernel<MT>;
     p.stage_bytes = stage_bytes_for(MT);
     p.codes_bytes = codes_bytes_for(max_code_bytes);
+    p.dxs_bytes = dxs_bytes_for(max_k, MT);
+    p.gw_bytes = p.dxs_bytes + 2u * p.codes_bytes + 128u;
     const size_t tail = tail_bytes_for(max_k, MT, max_code_bytes);
     const size_t budget = smem_budget(ctx);
     if (tail + 3u * p.stage_bytes > budget) throw Error(CSDR_ERR_LIMIT, "GEMV queue: shared memory need exceeds the device limit");
@@ -568,27 +644,38 @@ bool gemv_queue_supported(const csdr_context* ctx, const QueueItem* items, uint3
     const size_t batch = items[0].batch;
     if (batch == 0 || batch > kMaxTokens) return false;
     const int mt = batch <= 1 ? 1 : batch <= 2 ? 2 : 4;
-    uint32_t max_k = 0, max_code_bytes = 0;
-    for (uint32_t i = 0; i < n; ++i) {
-        const QueueItem& it = items[i];
-        const Geometry& g = it.seg->g;
-        if (!g.row_tiles() || g.cols % 4u || it.batch != batch) return false;
-        if (g.n_atoms > 4096u || g.n_stages > 16u) return false;
-        const bool glue = it.residual || it.swiglu_gate || it.prep_weight || it.scale_from >= 0;
-        if (glue && it.y_layout != CSDR_LAYOUT_TOKEN_MAJOR && batch > 1) return false;
-        // dependencies point backwards, inside one launch's worth of tasks
-        const int first = static_cast<int>(i / kMaxQueueTasks * kMaxQueueTasks);
-        if (it.dep >= static_cast<int>(i) || it.scale_from >= static_cast<int>(i)) return false;
-        if ((it.dep >= 0 && it.dep < first) || (it.scale_from >= 0 && it.scale_from < first)) return false;
-        if (it.prep_weight && !it.prep_out) return false;
-        // the SwiGLU epilogue reads the gate rows this CTA's own threads wrote: same row count, earlier task
-        if (it.swiglu_gate && (i == static_cast<uint32_t>(first) || items[i - 1].seg->g.rows != g.rows || items[i - 1].y != it.swiglu_gate))
-            return false;
-        max_k = std::max(max_k, g.n_atoms);
-        max_code_bytes = std::max(max_code_bytes, rows_per_cta_for(ctx, g.rows) * g.slots() * 2u);
+    for (uint32_t i0 = 0; i0 < n; i0 += kMaxQueueTasks) {
+        const uint32_t cnt = std::min(kMaxQueueTasks, n - i0);
+        const bool split = needs_split(items + i0, cnt);
+        uint32_t max_k = 0, max_code_bytes = 0;
+        for (uint32_t i = i0; i < i0 + cnt; ++i) {
+            const QueueItem& it = items[i];
+            const Geometry& g = it.seg->g;
+            if (!g.row_tiles() || g.cols % 4u || it.batch != batch) return false;
+            if (g.n_atoms > 4096u || g.n_stages > 16u) return false;
+            const bool glue = it.residual || it.swiglu_gate || it.prep_weight || it.scale_from >= 0 || it.dep >= 0;
+            if (glue && it.y_layout != CSDR_LAYOUT_TOKEN_MAJOR && batch > 1) return false;
+            // dependencies point backwards, inside one launch's worth of tasks, at the very buffer read
+            if (it.dep >= static_cast<int>(i) || it.scale_from >= static_cast<int>(i)) return false;
+            if ((it.dep >= 0 && it.dep < static_cast<int>(i0)) || (it.scale_from >= 0 && it.scale_from < static_cast<int>(i0)))
+                return false;
+            if (it.dep >= 0) {
+                const QueueItem& src = items[it.dep];
+                if (it.x_dtype != CSDR_DTYPE_F32 || it.seg->g.cols != src.seg->g.rows) return false;
+                if (it.x != src.y && !(src.prep_weight && it.x == src.prep_out)) return false;
+                if (it.x == src.y && src.y_layout != CSDR_LAYOUT_TOKEN_MAJOR && batch > 1) return false;
+            }
+            if (it.scale_from >= 0 && !items[it.scale_from].prep_weight) return false;
+            if (it.prep_weight && !it.prep_out) return false;
+            // the SwiGLU epilogue reads the gate rows this warp's own lanes wrote: the task before, same rows
+            if (it.swiglu_gate && (i == i0 || items[i - 1].seg->g.rows != g.rows || items[i - 1].y != it.swiglu_gate)) return false;
+            max_k = std::max(max_k, g.n_atoms);
+            max_code_bytes = std::max(max_code_bytes, code_bytes_per_warp(ctx, g, split));
+        }
+        // the ring needs three stages beside the gather warps' buffers
+        if (tail_bytes_for(max_k, mt, max_code_bytes) + 3u * stage_bytes_for(mt) > smem_budget(ctx)) return false;
     }
-    // the ring needs three stages beside the gather role's buffers
-    return tail_bytes_for(max_k, mt, max_code_bytes) + 3u * stage_bytes_for(mt) <= smem_budget(ctx);
+    return true;
 }
 
 void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
@@ -596,15 +683,37 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
     const int mt = batch <= 1 ? 1 : batch <= 2 ? 2 : 4;
     const uint32_t G = static_cast<uint32_t>(ctx->sm_count);
     if (!ctx->queue_sync) {
-        // [0..1] launch counter pair, then two counter sets; zeroed once, the launches keep them so
-        const size_t words = 2u + 2u * 2u * kMaxQueueTasks;
-        CSDR_CUDA(cudaMalloc(&ctx->queue_sync, words * sizeof(uint32_t)));
-        CSDR_CUDA(cudaMemsetAsync(ctx->queue_sync, 0, words * sizeof(uint32_t), ctx->stream));
+        CSDR_CUDA(cudaMalloc(&ctx->queue_sync, 2 * sizeof(uint32_t)));   // the launch counter pair
+        CSDR_CUDA(cudaMemsetAsync(ctx->queue_sync, 0, 2 * sizeof(uint32_t), ctx->stream));
     }
     for (uint32_t i0 = 0; i0 < n; i0 += kMaxQueueTasks) {
         const uint32_t cnt = std::min(kMaxQueueTasks, n - i0);
+        const bool split = needs_split(items + i0, cnt);
         QParams p{};
-        uint32_t unit = 0, dx_off = 0, max_k = 0, max_code_bytes = 0;
+        // scratch words: Dx slots, sums of squares, then a tagged copy of every output a later task reads
+        const size_t sumsq_words = static_cast<size_t>(kMaxQueueTasks) * G * kGatherWarps * kMaxTokens;
+        size_t words = sumsq_words;
+        uint32_t unit = 0, max_k = 0, max_code_bytes = 0;
+        size_t tag_off[kMaxQueueTasks][2] = {};   // [task][0: y, 1: prep_out]; 0 = no tagged copy
+        for (uint32_t i = 0; i < cnt; ++i) {
+            const QueueItem& it = items[i0 + i];
+            const Geometry& g = it.seg->g;
+            QTask& t = p.task[i];
+            t.dx_off = static_cast<uint32_t>(words - sumsq_words);
+            words += (static_cast<size_t>(g.n_atoms) * mt + 3u) & ~static_cast<size_t>(3);
+            if (it.dep >= 0) {
+                const uint32_t d = static_cast<uint32_t>(it.dep) - i0;
+                const QueueItem& src = items[it.dep];
+                const int which = it.x == src.y ? 0 : 1;
+                if (!tag_off[d][which]) {
+                    tag_off[d][which] = words;
+                    words += static_cast<size_t>(batch) * src.seg->g.rows;
+                }
+            }
+        }
+        u64* scratch = static_cast<u64*>(ctx->scratch_get(6, std::max<size_t>(words * 8u, 4u << 20)));
+        p.sumsq = scratch;
+        p.dx = scratch + sumsq_words;
         for (uint32_t i = 0; i < cnt; ++i) {
             const QueueItem& it = items[i0 + i];
             const Geometry& g = it.seg->g;
@@ -613,12 +722,20 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
             t.codes = it.seg->codes_ptr();
             t.scales = static_cast<const float*>(it.seg->scales->ptr);
             t.x = it.x;
+            t.x_kind = X_PLAIN;
+            if (it.dep >= 0) {
+                const uint32_t d = static_cast<uint32_t>(it.dep) - i0;
+                t.x = scratch + tag_off[d][it.x == items[it.dep].y ? 0 : 1];
+                t.x_kind = X_TAGGED;
+            }
             t.y = it.y;
+            t.y_tag = tag_off[i][0] ? scratch + tag_off[i][0] : nullptr;
             t.bias = it.bias;
             t.residual = it.residual;
             t.gate = it.swiglu_gate;
             t.prep_w = it.prep_weight;
             t.prep_out = it.prep_out;
+            t.prep_tag = tag_off[i][1] ? scratch + tag_off[i][1] : nullptr;
             t.K = g.n_atoms;
             t.R = g.rows;
             t.C = g.cols;
@@ -626,31 +743,23 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
             t.k = g.k;
             t.unit0 = unit;
             t.n_units = (g.n_atoms + kAtomsPerUnit - 1u) / kAtomsPerUnit;
-            t.dx_off = dx_off;
             t.rows_per_cta = rows_per_cta_for(ctx, g.rows);
             t.x_dtype = static_cast<uint32_t>(it.x_dtype);
             t.x_layout = static_cast<uint32_t>(it.x_layout);
             t.y_layout = static_cast<uint32_t>(it.y_layout);
             t.M = batch;
-            t.dep = it.dep >= 0 ? it.dep - static_cast<int>(i0) : -1;
             t.scale_from = it.scale_from >= 0 ? it.scale_from - static_cast<int>(i0) : -1;
             t.scale_eps = it.scale_eps;
             t.scale_inv_width = it.scale_width ? 1.0f / static_cast<float>(it.scale_width) : 0.0f;
             t.epilogue = it.swiglu_gate ? EPI_SWIGLU : EPI_PLAIN;
             unit += t.n_units;
-            dx_off += (g.n_atoms * static_cast<uint32_t>(mt) + 3u) & ~3u;
             max_k = std::max(max_k, g.n_atoms);
-            max_code_bytes = std::max(max_code_bytes, t.rows_per_cta * g.slots() * 2u);
+            max_code_bytes = std::max(max_code_bytes, code_bytes_per_warp(ctx, g, split));
         }
         p.n_tasks = cnt;
         p.n_units = unit;
-        const size_t sumsq_floats = static_cast<size_t>(kMaxQueueTasks) * G * kMaxTokens;
-        float* scratch = static_cast<float*>(
-            ctx->scratch_get(6, std::max<size_t>((static_cast<size_t>(dx_off) + sumsq_floats) * 4u, 2u << 20)));
-        p.sumsq = scratch;
-        p.dx = scratch + sumsq_floats;
+        p.split_rows = split ? 1u : 0u;
         p.seq = ctx->queue_sync;
-        p.counters = ctx->queue_sync + 2;
         p.status = ctx->status_word;
         p.spin_poll = ctx->spin_limit_gemv;
         p.spin_barrier = ctx->spin_limit_barrier;

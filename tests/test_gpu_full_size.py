@@ -112,7 +112,7 @@ def test_config2_default_2d_tiles_mlp(ctx, oracle):
     seg = cs.Segment.from_payload(pay, ctx)
     Wo = oracle.decompress(pay)
     assert np.array_equal(seg.decompress(), Wo)
-    for M in (1, 4):
+    for M in (1, 4, 64, 512):
         x = np.random.default_rng(M).normal(0, 1, (4096, M)).astype(np.float32)
         e = rel_err(seg.matmul(x, M, allow_2d=True), oracle.dense_matmul(Wo, x, M))
         assert e[0] < TOL and e[1] < TOL, (M, e)
@@ -123,7 +123,7 @@ def test_config5_kquant_source_shared_dictionary(ctx, oracle, tmp_path):
     bit for bit like the oracle, then - as the reference does for quantised GGUF tensors, whose
     blocks are source dtypes, not coefficient packing - HSDR-encoded from the fp32 values by the
     reference encoder into an .hsda whose FEED_FORWARD role shares one 128x128-tile dictionary.
-    The sparsity setting of the config is inert for HSDR, so one archive stands for all three."""
+    Default density here (8 atoms per stage); the sparsity sweep is test_config5_sparsity_sweep."""
     import torch
     from oracle.bindings import SEG_FEED_FORWARD, Reference, Segment, cfg_default, cfg_mlp
     if not Reference.available():
@@ -163,4 +163,39 @@ def test_config5_kquant_source_shared_dictionary(ctx, oracle, tmp_path):
             want = (Wd.double() @ xb.cuda().double()).float().cpu().numpy()  # dense product of the decoded weights
             e = rel_err(y, want)
             assert e[0] < TOL and e[1] < TOL, (name, M, e)
+        del Wd
+
+
+@pytest.mark.parametrize("sparsity,k", [(0.01, 2), (0.02, 3), (0.05, 9)])
+def test_config5_sparsity_sweep(ctx, oracle, tmp_path, sparsity, k):
+    """The sparsity settings of the k-quant configuration. HSDR ignores the archive-level sparsity
+    option, so the sweep is mapped onto the codec's own density: active atoms per stage
+    k = max(1, round(sparsity * n_atoms / n_stages)) = 2, 3, 9 for 512 atoms in 3 stages (this
+    mapping is this repository's, not the reference's). Both tensors share one dictionary of
+    128x128 tiles; products at M = 1 and 128 against the dense product of the weights the
+    reference decodes from the same archive."""
+    import torch
+    from oracle.bindings import SEG_FEED_FORWARD, Reference, Segment, cfg_default, cfg_mlp
+    if not Reference.available():
+        pytest.skip("needs the compiled reference (oracle/_ref) to write the shared-dictionary archive")
+    assert k == max(1, round(sparsity * 512 / 3))
+    ref = Reference()
+    shapes = ((14336, 4096), (4096, 14336))
+    segs = [Segment(f"blk.{i}.ffn.weight", np.random.default_rng(10 + i).normal(0, 0.02, s).astype(np.float32), s,
+                    SEG_FEED_FORWARD, layer_index=i) for i, s in enumerate(shapes)]
+    path = str(tmp_path / f"cfg5_k{k}.hsda")
+    assert ref.hsda_write(segs, path, cfg_default(ksvd_iters=0), cfg_mlp(ksvd_iters=0, k=k)) == 1
+    del segs
+    r = cs.HSDAReader.fromFile(path, ctx)
+    for i, (R, C) in enumerate(shapes):
+        name = f"blk.{i}.ffn.weight"
+        W = r.decompress(name)
+        assert zlib.crc32(W.tobytes()) == zlib.crc32(ref.hsda_decompress(path, name, R, C).tobytes())
+        Wd = torch.from_numpy(W).cuda()
+        for M in (1, 128):
+            xb = torch.randn((C, M), generator=torch.Generator().manual_seed(M + i)).to(torch.bfloat16).float()
+            y = r.matmul(name, np.ascontiguousarray(xb.numpy()), M, allow_2d=True)
+            want = (Wd.double() @ xb.cuda().double()).float().cpu().numpy()
+            e = rel_err(y, want)
+            assert e[0] < TOL and e[1] < TOL, (name, k, M, e)
         del Wd
