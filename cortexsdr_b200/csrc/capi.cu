@@ -27,6 +27,11 @@ DeviceBuffer::DeviceBuffer(size_t n, int dev) : bytes(n), device(dev) {
 DeviceBuffer::~DeviceBuffer() {
     if (ptr) cudaFree(ptr);
 }
+void DeviceBuffer::release_data() {
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    bytes = 0;
+}
 
 Geometry make_geometry(const csdr_payload_info& v) {
     Geometry g;
@@ -209,6 +214,7 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         CSDR_CUDA(cudaMemsetAsync(ctx->gemv_seq, 0, 2 * sizeof(uint32_t), ctx->stream));
         if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE")) ctx->gemv_queue = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_CACHE_2D")) ctx->cache_2d = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_QUEUE")) ctx->decoder_queue = e[0] != '0';
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE_SINGLE")) ctx->gemv_queue_single = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
@@ -614,8 +620,9 @@ int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const*
             }
             return;
         }
-        if (n_segs > 1 && batch <= 4) {
-            // any number of members in one persistent launch
+        if (n_segs >= 8 && batch <= 4) {
+            // long lists: any number of members in one persistent launch (short ones are quicker as
+            // grouped launches of up to four)
             std::vector<QueueItem> items(n_segs);
             for (size_t i = 0; i < n_segs; ++i)
                 items[i] = QueueItem{segs[i], x_dev, x_dtype, x_layout, batch, ys_dev[i], y_layout, nullptr};

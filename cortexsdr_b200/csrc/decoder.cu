@@ -378,10 +378,9 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
 
 // Steps of at most four tokens on one GPU: a block is three launches. The output projection,
 // gate, up and down of block n and q, k, v of block n + 1 run as ONE list on the persistent GEMV
-// kernel, with the residual additions, SwiGLU and both halves of the two RMS normalisations as
-// epilogues of its gather role (the rows leave as h and as h * w with per-CTA sums of squares;
-// the products that consume h * w are scaled by 1 / rms); rotary embedding with the cache write,
-// and attention, stay kernels of their own between two lists.
+// kernel, with the residual additions and SwiGLU as epilogues of its gather role and the two RMS
+// normalisations folded into the products that consume them; rotary embedding with the cache
+// write, and attention, stay kernels of their own between two lists.
 bool use_queue(const csdr_decoder* d, uint32_t T) {
     return d->queue_capable && d->P == 1 && T <= 4u && d->ctx->gemv_queue && d->ctx->decoder_queue;
 }
@@ -393,11 +392,11 @@ void run_blocks_queue(csdr_decoder* d, uint32_t T) {
     auto item = [&](const Linear& l, const float* x, float* y) {
         return QueueItem{l.use(), x, CSDR_DTYPE_F32, CSDR_LAYOUT_TOKEN_MAJOR, T, y, CSDR_LAYOUT_TOKEN_MAJOR, nullptr};
     };
-    float* hw = F(d->normed);   // h * w of the norm ahead; the first one is normalised outright
-    op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, hw);
+    float* xn = F(d->normed);   // the first norm is a kernel of its own; the others ride on the lists
+    op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, xn);
     {
         const Layer& L = d->layers[0];
-        const QueueItem first[3] = {item(L.q, hw, F(d->q)), item(L.k, hw, F(d->k)), item(L.v, hw, F(d->v))};
+        const QueueItem first[3] = {item(L.q, xn, F(d->q)), item(L.k, xn, F(d->k)), item(L.v, xn, F(d->v))};
         launch_gemv_queue(ctx, first, 3);
     }
     for (uint32_t li = 0; li < c.n_layers; ++li) {
@@ -409,44 +408,34 @@ void run_blocks_queue(csdr_decoder* d, uint32_t T) {
         op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
         QueueItem list[7];
         uint32_t n = 0;
-        list[n] = item(L.o, F(d->att), F(d->hidden));            // 0: h += Wo att; h * w_ffn beside it
+        list[n] = item(L.o, F(d->att), F(d->hidden));            // 0: h += Wo att
         list[n].residual = F(d->hidden);
-        list[n].prep_weight = F(L.ffn_norm);
-        list[n].prep_out = hw;
         ++n;
-        list[n] = item(L.gate, hw, F(d->gate));                  // 1: gate = Wg norm(h)
+        list[n] = item(L.gate, F(d->hidden), F(d->gate));        // 1: gate = Wg norm(h)
         list[n].dep = 0;
-        list[n].scale_from = 0;
+        list[n].norm_weight = F(L.ffn_norm);
         ++n;
-        list[n] = item(L.up, hw, F(d->up));                      // 2: act = silu(gate) * (Wu norm(h))
+        list[n] = item(L.up, F(d->hidden), F(d->up));            // 2: act = silu(gate) * (Wu norm(h))
         list[n].dep = 0;
-        list[n].scale_from = 0;
+        list[n].norm_weight = F(L.ffn_norm);
         list[n].swiglu_gate = F(d->gate);
         ++n;
         list[n] = item(L.down, F(d->up), F(d->hidden));          // 3: h += Wd act
         list[n].dep = 2;
         list[n].residual = F(d->hidden);
-        const bool last = li + 1 == c.n_layers;
-        if (!last) {
+        ++n;
+        if (li + 1 < c.n_layers) {
             const Layer& N = d->layers[li + 1];
-            list[n].prep_weight = F(N.attn_norm);
-            list[n].prep_out = hw;
-            ++n;
             const Linear* qkv[3] = {&N.q, &N.k, &N.v};
             float* outs[3] = {F(d->q), F(d->k), F(d->v)};
             for (int j = 0; j < 3; ++j) {                        // 4..6: q, k, v of the next block
-                list[n] = item(*qkv[j], hw, outs[j]);
+                list[n] = item(*qkv[j], F(d->hidden), outs[j]);
                 list[n].dep = 3;
-                list[n].scale_from = 3;
+                list[n].norm_weight = F(N.attn_norm);
                 ++n;
             }
-        } else {
-            ++n;
         }
-        for (uint32_t i = 0; i < n; ++i) {
-            list[i].scale_eps = c.rms_eps;
-            list[i].scale_width = H;
-        }
+        for (uint32_t i = 0; i < n; ++i) list[i].norm_eps = c.rms_eps;
         launch_gemv_queue(ctx, list, n);
     }
     op_rmsnorm(ctx, F(d->hidden), F(d->out_norm), T, H, c.rms_eps, F(d->normed));

@@ -57,6 +57,7 @@ struct DeviceBuffer {
     std::shared_ptr<void> aux;
     DeviceBuffer(size_t n, int dev);
     ~DeviceBuffer();
+    void release_data();   // frees the memory now; what hangs on `aux` stays
     DeviceBuffer(const DeviceBuffer&) = delete;
     DeviceBuffer& operator=(const DeviceBuffer&) = delete;
 };
@@ -116,6 +117,7 @@ struct csdr_context {
     csdr::DevPtr gemv_trace;  // when set: 8 global-timer stamps per CTA of the last fused GEMV
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool gemv_queue = true;  // CSDR_GEMV_QUEUE=0 keeps lists of products on single and grouped launches
+    bool cache_2d = true;            // CSDR_CACHE_2D=0: wide batches on 2-D tiles stay on the factored CUDA-core kernels
     bool decoder_queue = false;      // CSDR_DECODER_QUEUE=1: decoder steps of up to four tokens run a block as three launches
     bool gemv_queue_single = false;  // CSDR_GEMV_QUEUE_SINGLE=1 sends single products of at most 4 tokens there too
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
@@ -153,6 +155,10 @@ struct csdr_segment {
     size_t codes_offset = 0;    // element offset of this image's first code within `codes`
     csdr::DevPtr edges;         // fp32: top-right strip then bottom strip; may be null
     std::vector<float> scales_host;
+    // 2-D tile images only: the weight rebuilt once as a dense row-tile "dictionary" (one atom per
+    // output row) whose cached bf16 planes feed the tensor-core kernel at wide batches - what the
+    // reference's layer cache holds as fp32 after decompress(). Built on the first wide product.
+    mutable std::shared_ptr<csdr_segment> dense;
     const uint16_t* codes_ptr() const {
         return static_cast<const uint16_t*>(codes->ptr) + codes_offset;
     }

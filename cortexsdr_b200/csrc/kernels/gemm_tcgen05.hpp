@@ -25,6 +25,9 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
 // dictionary.
 bool dx_tma_supported(const csdr_context* ctx, const csdr_segment* seg, size_t batch);
 void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride);
+// Builds and caches the bf16 planes of the segment's dictionary now (they are otherwise built
+// on the first projection); afterwards the fp32 atoms are no longer read by the TMA kernel.
+void dx_tma_prepare(csdr_context* ctx, const csdr_segment* seg);
 
 
 // Activations as token-major bf16 planes [tokens][cols]: hi = bf16(x), lo = bf16(x - hi); lo is

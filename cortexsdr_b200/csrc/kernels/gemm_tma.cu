@@ -696,6 +696,8 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     ls.done("hsdr_dx_tma_kernel");
 }
 
+void dx_tma_prepare(csdr_context* ctx, const csdr_segment* seg) { (void)tma_detail::planes_for(ctx, seg); }
+
 void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride) {
     const uint32_t M = static_cast<uint32_t>(a.batch);
     const XPlanesView x = make_x_planes(ctx, a.x, a.x_dtype, a.x_layout, M, seg->g.cols);

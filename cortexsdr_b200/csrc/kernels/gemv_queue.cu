@@ -34,11 +34,13 @@
 // polled. The tag is the count of queue launches completed, plus one, read from device memory
 // (the last CTA to have read it advances it), so a captured CUDA graph tags every replay afresh.
 //
-// Epilogues fold the decoder glue of api/cortex_sdk.cpp:1569-1679 into the gather so that a block
-// of the decoder is one list: bias; residual add (add_vectors, :1234-1243); SwiGLU against the
-// task before (silu_mul, :1245-1256); and the two halves of RMS normalisation (rms_norm,
-// :1208-1232): a task may leave y * w beside y together with sums of squares of y, and a later
-// task that consumes y * w multiplies its own product by 1 / sqrt(mean + eps).
+// The decoder glue of api/cortex_sdk.cpp:1569-1679 is folded in so that a block of the decoder
+// is one list: bias, residual add (add_vectors, :1234-1243) and SwiGLU against the task before
+// (silu_mul, :1245-1256) are epilogues of the gather; RMS normalisation (rms_norm, :1208-1232)
+// of activations that come from an earlier task is split in two: the product warps multiply
+// the slab by the norm weights as they stage it and sum the squares of what they staged (every
+// unit sees the whole activation row), the task's first unit publishes that sum as one more
+// tagged word per token, and the gather scales its rows by 1 / sqrt(mean + eps).
 //
 // Every wait is bounded (mbarrier phases, polls): one that runs out sets the status word, all
 // roles of the CTA stop waiting, and the kernel returns. All CTAs must be resident (grid = SM
@@ -76,9 +78,7 @@ struct QTask {
     const float* bias;
     const float* residual;    // [M][R] token-major, may alias y
     const float* gate;        // EPI_SWIGLU: the gate projection's rows, [M][R]
-    const float* prep_w;      // leave y * w (prep_out and/or prep_tag) and sums of squares of y
-    float* prep_out;
-    u64* prep_tag;
+    const float* norm_w;      // X_TAGGED only: y = W rmsnorm(x; norm_w, norm_eps)
     uint32_t K, R, C, S, k;
     uint32_t unit0;           // first flat unit of this task
     uint32_t n_units;
@@ -86,8 +86,7 @@ struct QTask {
     uint32_t rows_per_cta;
     uint32_t x_kind, x_dtype, x_layout, y_layout;
     uint32_t M;
-    int32_t scale_from;       // earlier task whose sums of squares normalise this product, or -1
-    float scale_eps, scale_inv_width;
+    float norm_eps;
     uint32_t epilogue;
 };
 
@@ -101,7 +100,7 @@ struct QParams {
     uint32_t codes_bytes;       // one code buffer inside it
     uint32_t split_rows;        // 1: a task's rows are split over the gather warps; 0: tasks are dealt out to them
     u64* dx;                    // tagged Dx words
-    u64* sumsq;                 // tagged sums of squares: [task][grid * kGatherWarps][kMaxTokens]
+    u64* sumsq;                 // tagged sums of squares of a task's activations: [task][kMaxTokens]
     uint32_t* seq;              // [0] queue launches completed, [1] CTAs that have read [0]
     int* status;
     uint32_t spin_poll, spin_barrier;
@@ -196,6 +195,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
     __shared__ __align__(8) u64 full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ int failed_s;
     __shared__ uint32_t tag_s;
+    __shared__ float ssq_s[kProductWarps][kMaxTokens];
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t NS = p.n_stages;
@@ -349,9 +349,9 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
             const QTask& t = p.task[ti];
             const uint32_t atom = (u - t.unit0) * kAtomsPerUnit + w;
             const uint32_t n_st = stages_of(t);
-            float acc[MT];
+            float acc[MT], ssq[MT];
 #pragma unroll
-            for (int b = 0; b < MT; ++b) acc[b] = 0.0f;
+            for (int b = 0; b < MT; ++b) acc[b] = ssq[b] = 0.0f;
             for (uint32_t s = 0; s < n_st; ++s, ++it) {
                 const uint32_t slot = it % NS;
                 unsigned char* st = qsm + static_cast<size_t>(slot) * p.stage_bytes;
@@ -381,11 +381,16 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                                 break;
                             }
                         }
+                        float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
+                        if (t.norm_w) wv = __ldg(reinterpret_cast<const float4*>(t.norm_w + s * kSlab + c_lane));
 #pragma unroll
-                        for (int b = 0; b < MT; ++b)
-                            *reinterpret_cast<float4*>(xs + b * kSlab + c_lane) =
-                                make_float4(__uint_as_float(static_cast<uint32_t>(e[4 * b])), __uint_as_float(static_cast<uint32_t>(e[4 * b + 1])),
-                                            __uint_as_float(static_cast<uint32_t>(e[4 * b + 2])), __uint_as_float(static_cast<uint32_t>(e[4 * b + 3])));
+                        for (int b = 0; b < MT; ++b) {
+                            const float4 h = make_float4(__uint_as_float(static_cast<uint32_t>(e[4 * b])), __uint_as_float(static_cast<uint32_t>(e[4 * b + 1])),
+                                                         __uint_as_float(static_cast<uint32_t>(e[4 * b + 2])), __uint_as_float(static_cast<uint32_t>(e[4 * b + 3])));
+                            // the squares of the raw values, for the 1 / rms the gather applies behind the product
+                            ssq[b] = fmaf(h.x, h.x, fmaf(h.y, h.y, fmaf(h.z, h.z, fmaf(h.w, h.w, ssq[b]))));
+                            *reinterpret_cast<float4*>(xs + b * kSlab + c_lane) = make_float4(h.x * wv.x, h.y * wv.y, h.z * wv.z, h.w * wv.w);
+                        }
                     }
                     asm volatile("bar.sync 1, %0;" ::"n"(kProductThreads) : "memory");   // the whole slab is staged
                 }
@@ -433,6 +438,24 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 if (lane == static_cast<uint32_t>(b)) mine = v;
             }
             if (ok && lane < MT && atom < t.K) st_tagged(p.dx + t.dx_off + static_cast<size_t>(atom) * MT + lane, mine, tag);
+            if (t.norm_w) {
+                // every unit has staged the whole activation row; the task's first unit publishes the sum
+                // of squares per token: lanes, then warps, in order
+#pragma unroll
+                for (int b = 0; b < MT; ++b) {
+                    float v = ssq[b];
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+                    if (lane == 0) ssq_s[w][b] = v;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kProductThreads) : "memory");
+                if (u == t.unit0 && w == 0 && lane < t.M && ok) {
+                    float v = 0.0f;
+                    for (uint32_t q = 0; q < kProductWarps; ++q) v += ssq_s[q][lane];
+                    st_tagged(p.sumsq + static_cast<size_t>(ti) * kMaxTokens + lane, v, tag);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kProductThreads) : "memory");
+            }
         }
         if (!ok && lane == 0) atomicExch(p.status, 1);
     } else {
@@ -484,14 +507,28 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
         uint32_t limit = *reinterpret_cast<const volatile int*>(p.status) != 0 ? 0u : p.spin_poll;
         bool late = false;
         uint32_t buf = 0;
-        const uint32_t n_parts = gridDim.x * kGatherWarps;
         for (uint32_t ti = t_first; ti < p.n_tasks; ti += t_step, buf ^= 1u) {
             const QTask& t = p.task[ti];
             fetch_codes(ti + t_step, buf ^ 1u);
             uint32_t row0, rows_here;
             my_rows(t, row0, rows_here);
-            // hand-over: this task's Dx words, sixteen loads in flight per lane
+            // hand-over. First a light watch on one word per unit (its last atom, first token), so that
+            // a warp that is early does not sweep the whole slot again and again; then this task's Dx
+            // words, sixteen loads in flight per lane (stragglers are polled where they are).
             if (rows_here) {
+                const uint32_t n_u = t.n_units;
+                const uint32_t n_watch = lane < n_u ? (n_u - lane + 31u) / 32u : 0u;
+                for (uint32_t spins = 0;; ++spins) {
+                    bool all = true;
+                    for (uint32_t q = 0; q < n_watch; ++q) {
+                        const uint32_t unit = lane + q * 32u;
+                        const uint32_t atom = min(unit * kAtomsPerUnit + kAtomsPerUnit - 1u, t.K - 1u);
+                        all = all && static_cast<uint32_t>(ld_tagged(p.dx + t.dx_off + static_cast<size_t>(atom) * MT) >> 32) == tag;
+                    }
+                    if (__all_sync(0xFFFFFFFFu, all)) break;
+                    if (__any_sync(0xFFFFFFFFu, spins >= limit || *failed)) break;   // the sweep below records the failure
+                    if (!p.split_rows) __nanosleep(256);
+                }
                 const uint32_t n_w = t.K * MT;
                 const uint32_t n_mine = lane < n_w ? (n_w - lane + 31u) / 32u : 0u;
                 if (!poll_words<16>(p.dx + t.dx_off + lane, n_mine, 32u, tag, limit, failed, !p.split_rows,
@@ -499,20 +536,18 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                     late = true;
             }
             float inv = 1.0f;
-            if (t.scale_from >= 0) {
-                // 1 / rms of the rows this task's activations came from: the partial sums of every
-                // gather warp of every CTA, added in slot order (lane b takes token b)
+            if (t.norm_w) {
+                // 1 / rms of this task's activations: the sum of squares its first unit published
                 float ss = 0.0f;
-                if (lane < t.M) {
-                    const u64* ps = p.sumsq + static_cast<size_t>(t.scale_from) * n_parts * kMaxTokens + lane;
-                    if (!poll_words<16>(ps, n_parts, kMaxTokens, tag, limit, failed, false, [&](uint32_t, float v) { ss += v; })) late = true;
-                }
-                const float mine_inv = 1.0f / sqrtf(ss * t.scale_inv_width + t.scale_eps);
+                if (lane < t.M &&
+                    !poll_words<1>(p.sumsq + static_cast<size_t>(ti) * kMaxTokens + lane, 1u, 1u, tag, limit, failed, false,
+                                   [&](uint32_t, float v) { ss = v; }))
+                    late = true;
+                const float mine_inv = 1.0f / sqrtf(ss / static_cast<float>(t.C) + t.norm_eps);
                 inv = __shfl_sync(0xFFFFFFFFu, mine_inv, lane % MT);
             }
             asm volatile("cp.async.wait_group 1;" ::: "memory");      // this task's codes (the next task's may still fly)
             __syncwarp();
-            float ss_mine = 0.0f;
             const uint32_t b = lane % MT;
             if (rows_here) {
                 const uint32_t slots = t.S * t.k;
@@ -542,7 +577,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                     }
                     if (b < t.M) {
                         const uint32_t r = row0 + rl;
-                        if (t.scale_from >= 0) accr *= inv;
+                        if (t.norm_w) accr *= inv;
                         if (t.bias) accr += t.bias[r];
                         const size_t tm = static_cast<size_t>(b) * t.R + r;
                         if (t.epilogue == EPI_SWIGLU) {
@@ -552,27 +587,6 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                         if (t.residual) accr += t.residual[tm];
                         if (t.y) t.y[t.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * t.M + b : tm] = accr;
                         if (t.y_tag) st_tagged(t.y_tag + tm, accr, tag);
-                        if (t.prep_w) {
-                            const float hw = accr * t.prep_w[r];
-                            if (t.prep_out) t.prep_out[tm] = hw;
-                            if (t.prep_tag) st_tagged(t.prep_tag + tm, hw, tag);
-                            ss_mine = fmaf(accr, accr, ss_mine);
-                        }
-                    }
-                }
-            }
-            if (t.prep_w) {
-                // this warp's sums of squares per token: lanes with the same token, in lane order
-                float ss = 0.0f;
-                for (uint32_t j = b; j < 32u; j += MT) ss += __shfl_sync(0xFFFFFFFFu, ss_mine, j);
-                if (lane < MT && lane < kMaxTokens) {
-                    // with the tasks dealt out, the other three slots of the CTA hold nothing
-                    const size_t base = (static_cast<size_t>(ti) * n_parts + static_cast<size_t>(blockIdx.x) * kGatherWarps) * kMaxTokens;
-                    if (p.split_rows) {
-                        st_tagged(p.sumsq + base + g * kMaxTokens + lane, lane < t.M ? ss : 0.0f, tag);
-                    } else {
-                        for (uint32_t q = 0; q < kGatherWarps; ++q)
-                            st_tagged(p.sumsq + base + q * kMaxTokens + lane, q == 0 && lane < t.M ? ss : 0.0f, tag);
                     }
                 }
             }
@@ -599,7 +613,7 @@ uint32_t rows_per_cta_for(const csdr_context* ctx, uint32_t rows) {
 }
 bool needs_split(const QueueItem* items, uint32_t n) {
     for (uint32_t i = 0; i < n; ++i)
-        if (items[i].dep >= 0 || items[i].scale_from >= 0 || items[i].swiglu_gate || items[i].prep_weight || items[i].residual)
+        if (items[i].dep >= 0 || items[i].swiglu_gate || items[i].norm_weight || items[i].residual)
             return true;
     return n < 2u * kGatherWarps;   // short lists: the shortest path through each task
 }
@@ -653,20 +667,17 @@ bool gemv_queue_supported(const csdr_context* ctx, const QueueItem* items, uint3
             const Geometry& g = it.seg->g;
             if (!g.row_tiles() || g.cols % 4u || it.batch != batch) return false;
             if (g.n_atoms > 4096u || g.n_stages > 16u) return false;
-            const bool glue = it.residual || it.swiglu_gate || it.prep_weight || it.scale_from >= 0 || it.dep >= 0;
+            const bool glue = it.residual || it.swiglu_gate || it.norm_weight || it.dep >= 0;
             if (glue && it.y_layout != CSDR_LAYOUT_TOKEN_MAJOR && batch > 1) return false;
             // dependencies point backwards, inside one launch's worth of tasks, at the very buffer read
-            if (it.dep >= static_cast<int>(i) || it.scale_from >= static_cast<int>(i)) return false;
-            if ((it.dep >= 0 && it.dep < static_cast<int>(i0)) || (it.scale_from >= 0 && it.scale_from < static_cast<int>(i0)))
-                return false;
+            if (it.dep >= static_cast<int>(i)) return false;
+            if (it.dep >= 0 && it.dep < static_cast<int>(i0)) return false;
             if (it.dep >= 0) {
                 const QueueItem& src = items[it.dep];
-                if (it.x_dtype != CSDR_DTYPE_F32 || it.seg->g.cols != src.seg->g.rows) return false;
-                if (it.x != src.y && !(src.prep_weight && it.x == src.prep_out)) return false;
-                if (it.x == src.y && src.y_layout != CSDR_LAYOUT_TOKEN_MAJOR && batch > 1) return false;
+                if (it.x_dtype != CSDR_DTYPE_F32 || it.seg->g.cols != src.seg->g.rows || it.x != src.y) return false;
+                if (src.y_layout != CSDR_LAYOUT_TOKEN_MAJOR && batch > 1) return false;
             }
-            if (it.scale_from >= 0 && !items[it.scale_from].prep_weight) return false;
-            if (it.prep_weight && !it.prep_out) return false;
+            if (it.norm_weight && it.dep < 0) return false;   // the norm rides on activations staged by the product warps
             // the SwiGLU epilogue reads the gate rows this warp's own lanes wrote: the task before, same rows
             if (it.swiglu_gate && (i == i0 || items[i - 1].seg->g.rows != g.rows || items[i - 1].y != it.swiglu_gate)) return false;
             max_k = std::max(max_k, g.n_atoms);
@@ -681,7 +692,6 @@ bool gemv_queue_supported(const csdr_context* ctx, const QueueItem* items, uint3
 void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
     const uint32_t batch = static_cast<uint32_t>(items[0].batch);
     const int mt = batch <= 1 ? 1 : batch <= 2 ? 2 : 4;
-    const uint32_t G = static_cast<uint32_t>(ctx->sm_count);
     if (!ctx->queue_sync) {
         CSDR_CUDA(cudaMalloc(&ctx->queue_sync, 2 * sizeof(uint32_t)));   // the launch counter pair
         CSDR_CUDA(cudaMemsetAsync(ctx->queue_sync, 0, 2 * sizeof(uint32_t), ctx->stream));
@@ -690,11 +700,11 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
         const uint32_t cnt = std::min(kMaxQueueTasks, n - i0);
         const bool split = needs_split(items + i0, cnt);
         QParams p{};
-        // scratch words: Dx slots, sums of squares, then a tagged copy of every output a later task reads
-        const size_t sumsq_words = static_cast<size_t>(kMaxQueueTasks) * G * kGatherWarps * kMaxTokens;
+        // scratch words: sums of squares, Dx slots, then a tagged copy of every output a later task reads
+        const size_t sumsq_words = static_cast<size_t>(kMaxQueueTasks) * kMaxTokens;
         size_t words = sumsq_words;
         uint32_t unit = 0, max_k = 0, max_code_bytes = 0;
-        size_t tag_off[kMaxQueueTasks][2] = {};   // [task][0: y, 1: prep_out]; 0 = no tagged copy
+        size_t tag_off[kMaxQueueTasks] = {};      // 0 = no tagged copy of this task's y
         for (uint32_t i = 0; i < cnt; ++i) {
             const QueueItem& it = items[i0 + i];
             const Geometry& g = it.seg->g;
@@ -703,11 +713,9 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
             words += (static_cast<size_t>(g.n_atoms) * mt + 3u) & ~static_cast<size_t>(3);
             if (it.dep >= 0) {
                 const uint32_t d = static_cast<uint32_t>(it.dep) - i0;
-                const QueueItem& src = items[it.dep];
-                const int which = it.x == src.y ? 0 : 1;
-                if (!tag_off[d][which]) {
-                    tag_off[d][which] = words;
-                    words += static_cast<size_t>(batch) * src.seg->g.rows;
+                if (!tag_off[d]) {
+                    tag_off[d] = words;
+                    words += static_cast<size_t>(batch) * items[it.dep].seg->g.rows;
                 }
             }
         }
@@ -725,17 +733,16 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
             t.x_kind = X_PLAIN;
             if (it.dep >= 0) {
                 const uint32_t d = static_cast<uint32_t>(it.dep) - i0;
-                t.x = scratch + tag_off[d][it.x == items[it.dep].y ? 0 : 1];
+                t.x = scratch + tag_off[d];
                 t.x_kind = X_TAGGED;
             }
             t.y = it.y;
-            t.y_tag = tag_off[i][0] ? scratch + tag_off[i][0] : nullptr;
+            t.y_tag = tag_off[i] ? scratch + tag_off[i] : nullptr;
             t.bias = it.bias;
             t.residual = it.residual;
             t.gate = it.swiglu_gate;
-            t.prep_w = it.prep_weight;
-            t.prep_out = it.prep_out;
-            t.prep_tag = tag_off[i][1] ? scratch + tag_off[i][1] : nullptr;
+            t.norm_w = it.norm_weight;
+            t.norm_eps = it.norm_eps;
             t.K = g.n_atoms;
             t.R = g.rows;
             t.C = g.cols;
@@ -748,9 +755,6 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
             t.x_layout = static_cast<uint32_t>(it.x_layout);
             t.y_layout = static_cast<uint32_t>(it.y_layout);
             t.M = batch;
-            t.scale_from = it.scale_from >= 0 ? it.scale_from - static_cast<int>(i0) : -1;
-            t.scale_eps = it.scale_eps;
-            t.scale_inv_width = it.scale_width ? 1.0f / static_cast<float>(it.scale_width) : 0.0f;
             t.epilogue = it.swiglu_gate ? EPI_SWIGLU : EPI_PLAIN;
             unit += t.n_units;
             max_k = std::max(max_k, g.n_atoms);

@@ -23,16 +23,13 @@ struct QueueItem {
     // ---- optional glue (token-major fp32 buffers of [batch][rows]) ----
     const float* residual = nullptr;     // y = W x + residual (may be y itself)
     const float* swiglu_gate = nullptr;  // y = silu(gate) * (W x); gate = y of the task just before, same rows
-    const float* prep_weight = nullptr;  // also leave y * w in prep_out and the sums of squares of y for scale_from users
-    float* prep_out = nullptr;
-    int dep = -1;                        // index of an earlier task whose rows must be complete before x is read
-    int scale_from = -1;                 // index of an earlier task with prep_weight: y = (W x) / rms of that task's y
-    float scale_eps = 0.0f;
-    uint32_t scale_width = 0;            // rows of that task (the width the mean runs over)
+    int dep = -1;                        // index of the earlier task whose y is this task's x (x == that y)
+    const float* norm_weight = nullptr;  // with dep: y = W rmsnorm(x; norm_weight, norm_eps)
+    float norm_eps = 0.0f;
 };
 
 // Every item a 1-D row-tile image with cols a multiple of 4, one common batch of 1 to 4 tokens;
-// dep and scale_from point backwards within the same group of kMaxQueueTasks.
+// dep points backwards within the same group of kMaxQueueTasks.
 bool gemv_queue_supported(const csdr_context* ctx, const QueueItem* items, uint32_t n);
 void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n);
 

@@ -453,6 +453,23 @@ dense_rows_kernel(const float* __restrict__ W, uint32_t R, uint32_t C, XView xv,
     }
 }
 
+// y (token-major or feature-major, + bias) from a feature-major product t[r][stride].
+__global__ void __launch_bounds__(256)
+retile_bias_kernel(const float* __restrict__ t, uint32_t R, uint32_t M, uint32_t stride, YView yv) {
+    __shared__ float tile[32][33];
+    const uint32_t r0 = blockIdx.x * 32u, b0 = blockIdx.y * 32u;
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+    for (uint32_t j = ty; j < 32u; j += 8u) {
+        const uint32_t r = r0 + j, b = b0 + tx;
+        tile[j][tx] = (r < R && b < M) ? t[static_cast<size_t>(r) * stride + b] : 0.0f;
+    }
+    __syncthreads();
+    for (uint32_t j = ty; j < 32u; j += 8u) {
+        const uint32_t b = b0 + j, r = r0 + tx;
+        if (r < R && b < M) yv.y[y_index(yv, r, b)] = tile[tx][j] + (yv.bias ? yv.bias[r] : 0.0f);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host-side dispatch
 // ---------------------------------------------------------------------------
@@ -638,6 +655,45 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
             launch_gemv_queue(ctx, &item, 1);
             return;
         }
+    }
+    if (!g.row_tiles() && ctx->cache_2d && ctx->tensor_cores && a.batch >= 16 && g.rows % 128u == 0 && g.cols % 8u == 0 &&
+        g.rows <= 0x7FFFu * 128u) {
+        // 2-D tiles at a wide batch: what the reference does (decompress once, keep the layer, dense
+        // product - SparseInferenceEngine.cpp:1301-1310 behind its layer cache), on the tensor cores:
+        // the weight is rebuilt once by the bit-exact decode kernel, split into bf16 hi/lo planes that
+        // stay with the segment (4 bytes per element, as the reference's cached fp32 layer), and every
+        // wide product is the TMA-fed tcgen05 kernel over those planes with one "atom" per output row.
+        // Rebuilding tiles in shared memory per product instead would re-read S*k atoms of 64 KB per
+        // tile from L2 - 4 to 5 GB per product at the 7B shapes, whatever the batch.
+        if (!seg->dense) {
+            auto dn = std::make_shared<csdr_segment>();
+            dn->ctx = ctx;
+            dn->g.rows = dn->g.n_tiles = dn->g.rows_full = g.rows;   // not used by the projection
+            dn->g.cols = dn->g.cols_full = dn->g.tile_cols = g.cols;
+            dn->g.tile_rows = 1;
+            dn->g.n_col_tiles = 1;
+            dn->g.n_atoms = g.rows;
+            dn->g.n_stages = dn->g.k = 1;
+            dn->atoms = std::make_shared<DeviceBuffer>(static_cast<size_t>(g.rows) * g.cols * 4u, ctx->device);
+            launch_decode_rows(ctx, seg, nullptr, g.rows, static_cast<float*>(dn->atoms->ptr));
+            if (!dx_tma_supported(ctx, dn.get(), a.batch)) throw Error(CSDR_ERR_UNSUPPORTED, "tensor maps unavailable");
+            dx_tma_prepare(ctx, dn.get());
+            CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+            dn->atoms->release_data();                               // the planes hang on the buffer object
+            seg->dense = dn;
+        }
+        const uint32_t M = static_cast<uint32_t>(a.batch);
+        const bool direct = a.y_layout == CSDR_LAYOUT_FEATURE_MAJOR && !a.bias;
+        float* out = direct ? a.y
+                            : static_cast<float*>(ctx->scratch_get(1, static_cast<size_t>(g.rows) * M * sizeof(float)));
+        launch_dx_tma(ctx, seg->dense.get(), a, out, M);
+        if (!direct) {
+            YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
+            LaunchScope ls(ctx, KC_DECODER_OP);
+            retile_bias_kernel<<<dim3((g.rows + 31u) / 32u, (M + 31u) / 32u), 256, 0, ctx->stream>>>(out, g.rows, M, M, yv);
+            ls.done("retile_bias_kernel");
+        }
+        return;
     }
     const size_t budget = std::min<size_t>(ctx->smem_optin, 200u * 1024u);
     const bool fast_rows = g.row_tiles() && (g.cols % 4u == 0);

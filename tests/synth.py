@@ -35,6 +35,31 @@ def hsdr_payload(rows: int, cols: int, *, tile_rows: int = 1, tile_cols: int | N
     return b"".join((hdr, scales.tobytes(), atoms.tobytes(), codes.tobytes(), edges.tobytes()))
 
 
+def shared_dictionary(tile_rows: int, tile_cols: int, *, n_atoms: int = 512, n_stages: int = 3, k: int = 8,
+                      decay: float = 0.5, seed: int = 0, weight_std: float = 0.02):
+    """(atoms fp32 [n_atoms][tile_rows*tile_cols], stage scales) of a dictionary several tensors share
+    (SharedDictionary, strategies/HierarchicalSDRStrategy.hpp:194-198)."""
+    rng = np.random.default_rng(seed)
+    scales = np.array([decay ** l for l in range(n_stages)], np.float32)
+    atom_std = weight_std / np.sqrt(k * float((scales.astype(np.float64) ** 2).sum()))
+    atoms = rng.standard_normal((n_atoms, tile_rows * tile_cols), dtype=np.float32) * np.float32(atom_std)
+    return atoms, scales
+
+
+def hsdc_payload(rows: int, cols: int, *, tile_rows: int, tile_cols: int, n_atoms: int = 512, n_stages: int = 3,
+                 k: int = 8, decay: float = 0.5, seed: int = 0) -> bytes:
+    """A codes-only "HSDC" stream (HSDRCodesHeader, strategies/HierarchicalSDRStrategy.cpp:675-692) with
+    uniformly random (atom, sign) codes; the shape must divide by the tile."""
+    assert rows % tile_rows == 0 and cols % tile_cols == 0
+    rng = np.random.default_rng(seed)
+    n_tiles = (rows // tile_rows) * (cols // tile_cols)
+    n_codes = n_tiles * n_stages * k
+    codes = (rng.integers(0, n_atoms, n_codes, dtype=np.uint16)
+             | (rng.integers(0, 2, n_codes, dtype=np.uint16) << 15)).astype(np.uint16)
+    hdr = struct.pack("<4sIIIIHHHBBf", b"HSDC", 1, rows, cols, n_tiles, tile_rows, tile_cols, n_atoms, n_stages, k, decay)
+    return hdr + codes.tobytes()
+
+
 def _s(x: str) -> bytes:
     b = x.encode()
     return struct.pack("<I", len(b)) + b
