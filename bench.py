@@ -126,9 +126,28 @@ def cpu_baseline(pay: bytes, iters: int = 7):
             orc.matmul(pay, x, 1)
             ts.append(time.perf_counter() - t0)
         sec, kind = statistics.median(ts), "port"
-    return {"value": alg_bytes(len(pay), 1) / sec / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
-            "sample": f"1 of {SEGS} segments, batch 1, median of {iters} calls after 2 warm-ups",
-            "ms_per_matmul": sec * 1e3}
+    out = {"value": alg_bytes(len(pay), 1) / sec / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+           "sample": f"1 of {SEGS} segments, batch 1, median of {iters} calls after 2 warm-ups",
+           "ms_per_matmul": sec * 1e3}
+    if Reference.available():
+        # the reference's other route: decompress() then the dense product (linear_forward: one
+        # std::thread per hardware thread at batch 1, no BLAS in this build)
+        try:
+            sec2, _ = Reference().decompress_dense_timed(pay, R, C, np.ascontiguousarray(x.T), 1, iters=3)
+            model = ""
+            try:
+                for line in open("/proc/cpuinfo"):
+                    if line.startswith("model name"):
+                        model = line.split(":", 1)[1].strip()
+                        break
+            except OSError:
+                pass
+            out["decompress_plus_dense"] = {"value": alg_bytes(len(pay), 1) / sec2 / 1e9, "unit": "GB/s",
+                                            "ms_per_matmul": sec2 * 1e3, "threads": os.cpu_count(), "cpu": model,
+                                            "note": "decompress single-threaded, dense product over all hardware threads"}
+        except Exception as e:
+            out["decompress_plus_dense"] = {"error": f"{type(e).__name__}: {e}"[:160]}
+    return out
 
 
 DECODERS = {
@@ -246,6 +265,67 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
         raise RuntimeError("decode step produced non-finite logits")
     dec.close()
     ld.close()
+    return out
+
+
+def other_configs(cs, torch, ctx, stream, timed, hbm_peak, tf_peak, args):
+    """Configurations 1, 2 (2-D tiles) and 5 beside the headline: microseconds per product with the
+    operands resident, every pass over more distinct weight copies than L2 holds unless noted.
+    Payloads are synthetic stand-ins of the configurations' shapes (timing does not depend on
+    which atoms the codes name). frac_hbm counts the compressed bytes a product has to read."""
+    from tests import synth
+    out = {}
+    gen = torch.Generator(device="cuda").manual_seed(5)
+
+    def run(label, make_seg, n_copies, rows, cols, payload_bytes, batches, shared_bytes=0, dtype=torch.bfloat16):
+        ent = {}
+        try:
+            copies = [make_seg(i) for i in range(n_copies)]
+            for m in batches:
+                x = torch.randn((m, cols), generator=gen, device="cuda").to(dtype)
+                y = torch.empty((n_copies, m, rows), device="cuda")
+                dt = cs.DTYPE_BF16 if dtype == torch.bfloat16 else cs.DTYPE_F32
+
+                def step():
+                    for i, sg in enumerate(copies):
+                        sg.matmul_device(x.data_ptr(), dt, cs.TOKEN_MAJOR, m, y[i].data_ptr(), cs.TOKEN_MAJOR)
+                step()
+                ctx.synchronize()
+                st = max(3, args.steps // (4 if m >= 64 else 2))
+                ms = timed(step, st, 3)
+                per = ms / st / n_copies * 1e-3
+                alg = payload_bytes + shared_bytes / n_copies + cols * m * x.element_size() + rows * m * 4
+                e = {"us_per_matmul": per * 1e6, "GBps_compressed": alg / per / 1e9, "frac_hbm": alg / per / 1e9 / hbm_peak,
+                     "TFLOPs_dense_equiv": 2.0 * rows * cols * m / per / 1e12}
+                e["frac_bf16_peak"] = e["TFLOPs_dense_equiv"] / tf_peak
+                ent[f"M{m}"] = e
+                del x, y
+            for sg in copies:
+                sg.close()
+        except Exception as ex:
+            ent["error"] = f"{type(ex).__name__}: {ex}"[:200]
+            torch.cuda.synchronize()
+        out[label] = ent
+        torch.cuda.empty_cache()
+
+    # config 1: 4096 x 4096, batch 1 - row tiles, and the reference's default 128 x 128 tiles
+    p1 = synth.hsdr_payload(4096, 4096, seed=0)
+    run("cfg1_row_tiles", lambda i: cs.Segment.from_payload(p1, ctx), 32, 4096, 4096, len(p1), (1,), dtype=torch.float32)
+    p1t = synth.hsdr_payload(4096, 4096, tile_rows=128, tile_cols=128, n_atoms=256, k=5, seed=0)
+    run("cfg1_tiles_128x128", lambda i: cs.Segment.from_payload(p1t, ctx), 16, 4096, 4096, len(p1t), (1,), dtype=torch.float32)
+    # config 2 in 2-D tiles (forMLP: 512 atoms, 8 per stage): decode batches on the factored kernels,
+    # wide batches on the tensor cores over planes rebuilt once per segment
+    p2t = synth.hsdr_payload(R, C, tile_rows=128, tile_cols=128, n_atoms=512, k=8, seed=2)
+    run("cfg2_tiles_128x128", lambda i: cs.Segment.from_payload(p2t, ctx), 8, R, C, len(p2t), (1, 64, 512))
+    # config 5: two tensors behind ONE shared dictionary of 128 x 128 tiles (33.5 MB: L2-resident)
+    atoms, scales = synth.shared_dictionary(128, 128, seed=5)
+    dic = cs.Dictionary(ctx, 128, 128, 512, 3, 8, atoms, scales)
+    for label, (r5, c5) in (("cfg5_14336x4096_shared", (14336, 4096)), ("cfg5_4096x14336_shared", (4096, 14336))):
+        codes = synth.hsdc_payload(r5, c5, tile_rows=128, tile_cols=128, seed=r5)
+        run(label, lambda i: cs.Segment.from_payload(codes, ctx, dic), 2, r5, c5, len(codes), (1, 128), shared_bytes=atoms.nbytes)
+        if "error" not in out[label]:
+            out[label]["note"] = "the shared dictionary stays in L2 between products: not an HBM figure"
+    dic.close()
     return out
 
 
@@ -551,6 +631,15 @@ def main():
             sweep[f"M{m}"] = ent
             del xm, ym
 
+    # ---- the other matmul configurations (device-resident, synthetic payloads of their shapes) ----
+    other = {}
+    if not args.no_sweep and world == 1:
+        for s_ in segs:
+            s_.close()
+        segs.clear()
+        torch.cuda.empty_cache()
+        other = other_configs(cs, torch, ctx, stream, timed, hbm_peak, tf_peak, args)
+
     # ---- decoder-shaped decode tokens/s (tensor-parallel over the ranks when world > 1) ----
     decode = {}
     for s_ in segs:
@@ -585,7 +674,7 @@ def main():
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
             "chain_of_single_launches": chain,
             "kernel_ms": {k: {"launches": v[0], "us_each": v[1] / v[0] * 1e3} for k, v in prof.items()},
-            "grouped_same_x": grouped, "sweep": sweep, "decode_tokens_per_s": decode}
+            "grouped_same_x": grouped, "sweep": sweep, "other_configs": other, "decode_tokens_per_s": decode}
     if isinstance(decode.get("llama7b"), dict) and "tokens_per_s" in decode["llama7b"]:
         d7 = decode["llama7b"]
         line["tp_decode"] = {"model": "llama7b-shaped, batch 16, context 1024", "tp": d7["tp"],

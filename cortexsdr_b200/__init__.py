@@ -369,11 +369,37 @@ class SharedDictionary:
 
 
 class HierarchicalSDRStrategy:
-    """Decode side of the strategy plug-in (id 5). compress() is not part of this library:
-    archives are produced by the reference encoder."""
+    """The strategy plug-in (id 5): the decode side, and the encoder's fast mode (ksvd_iters = 0);
+    dictionary-update iterations stay with the reference encoder."""
 
     def __init__(self, ctx: Context | None = None):
         self.ctx = ctx or default_context()
+
+    def compress(self, W, *, tile_rows: int = 128, tile_cols: int = 128, n_atoms: int = 256, n_stages: int = 3,
+                 k: int = 5, decay: float = 0.5, ksvd_iters: int = 0) -> bytes:
+        """HSDR payload of the fp32 matrix W (compress, strategies/HierarchicalSDRStrategy.cpp:1068-1236),
+        encoded on the device. Defaults are the reference's HierarchicalSDRConfig{} geometry."""
+        W = _f32(W)
+        if W.ndim != 2:
+            raise CompressionError("HSDR: expected a 2-D tensor")
+        n = C.c_size_t()
+        lib, h = self.ctx._lib, self.ctx._h
+        args = (h, _fp(W), W.shape[0], W.shape[1], tile_rows, tile_cols, n_atoms, n_stages, k, decay, ksvd_iters)
+        rc = lib.csdr_hsdr_encode(*args, None, 0, C.byref(n))
+        if rc != _lib.ERR_BUFFER:
+            _check(rc)
+        out = np.empty(n.value, np.uint8)
+        _check(lib.csdr_hsdr_encode(*args, out.ctypes.data_as(C.c_void_p), out.size, C.byref(n)))
+        return out.tobytes()
+
+    def encode_codes(self, tiles, atoms, stage_scales, k: int) -> np.ndarray:
+        """The coding pass alone: packed u16 codes (n_tiles, n_stages, k)."""
+        tiles, atoms, stage_scales = _f32(tiles), _f32(atoms), _f32(stage_scales)
+        n, T = tiles.shape
+        out = np.empty((n, stage_scales.size, k), np.uint16)
+        _check(self.ctx._lib.csdr_encode_codes(self.ctx._h, _fp(tiles), n, T, _fp(atoms), atoms.shape[0], stage_scales.size, k,
+                                               _fp(stage_scales), out.ctypes.data_as(C.POINTER(C.c_uint16)), out.size))
+        return out
 
     def decompress(self, compressedData, originalType=None, originalSize: int = 0) -> np.ndarray:
         info = inspect_payload(compressedData)

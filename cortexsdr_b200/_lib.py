@@ -108,6 +108,10 @@ SIGNATURES = {
     "csdr_decompress_device_async": (C.c_int, [_P, _P, _P]),
     "csdr_dequantize": (C.c_int, [_P, C.c_char_p, _P, _SZ, C.c_float, C.c_float, _F, _SZ,
                                   C.POINTER(_SZ)]),
+    "csdr_hsdr_encode": (C.c_int, [_P, _F, C.c_uint32, C.c_uint32, C.c_uint16, C.c_uint16, C.c_uint16, C.c_uint8,
+                                   C.c_uint8, C.c_float, C.c_uint8, _P, _SZ, C.POINTER(_SZ)]),
+    "csdr_encode_codes": (C.c_int, [_P, _F, _SZ, _SZ, _F, C.c_uint16, C.c_uint8, C.c_uint8, _F,
+                                    C.POINTER(C.c_uint16), _SZ]),
     "csdr_dequantize_inference": (C.c_int, [_P, C.c_char_p, _P, _SZ, _SZ, _F, _SZ, C.POINTER(_SZ)]),
     "csdr_archive_open": (C.c_int, [_P, C.c_char_p, C.POINTER(_P)]),
     "csdr_archive_close": (C.c_int, [_P]),

@@ -18,6 +18,8 @@ SOURCES = [
     "kernels/decoder_ops.cu",
     "kernels/gemm_tcgen05.cu", "kernels/gemm_tma.cu",
     "decoder.cu",
+    "kernels/encode.cu",
+    "encoder.cu",
     "host/format.cpp",
     "host/archive.cpp",
     "host/sdk_capi.cpp",

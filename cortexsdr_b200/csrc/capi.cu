@@ -70,7 +70,7 @@ const char* kernel_class_name(int cls) {
     static const char* names[KC_COUNT] = {"hsdr_unpack", "hsdr_dx", "hsdr_gather", "hsdr_tile_project",
                                           "hsdr_tile_gather", "hsdr_edge", "dense_rows", "hsdr_decode_rows",
                                           "dequant", "hsdr_gemm_tcgen05", "decoder_op", "hsdr_gemv_fused", "attention",
-                                          "hsdr_gemv_queue"};
+                                          "hsdr_gemv_queue", "hsdr_encode"};
     return (cls >= 0 && cls < KC_COUNT) ? names[cls] : "?";
 }
 
@@ -337,7 +337,7 @@ int csdr_context_gemv_trace(csdr_context* ctx, int enable, uint64_t* out, size_t
     return guard([&] {
         require_ctx(ctx);
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
-        const size_t words = static_cast<size_t>(ctx->sm_count) * 2u * 16u;
+        const size_t words = static_cast<size_t>(ctx->sm_count) * 64u;   // fused GEMV: 2 CTAs x 16 per SM; queue: 8 tasks x 8
         if (out && ctx->gemv_trace) {
             const size_t n = std::min(capacity, words);
             CSDR_CUDA(cudaMemcpy(out, ctx->gemv_trace->ptr, n * 8u, cudaMemcpyDeviceToHost));

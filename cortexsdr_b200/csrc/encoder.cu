@@ -1,0 +1,173 @@
+// extern "C" face of the HSDR encoder (fast mode) and of its coding pass alone.
+//
+// HierarchicalSDRStrategy::compress (strategies/HierarchicalSDRStrategy.cpp:1068-1236) around
+// fitHierarchicalKSVD (:494-607) with ksvd_iters = 0: tiles of the aligned top-left block, a
+// dictionary of K tiles picked by std::mt19937(0xC0DE), normalised and scaled by the mean tile norm
+// over sqrt(S * k), one coding pass, and the payload "HSDR" v2 with the raw edge strips behind it.
+// The tile picks and the byte layout are host work; everything that touches the tensor runs on
+// the device (kernels/encode.cu).
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "internal.hpp"
+#include "kernels/encode.hpp"
+
+using namespace csdr;
+
+namespace {
+
+// std::mt19937 as the standard defines it (Matsumoto and Nishimura 1998; seeding by Knuth's
+// 1812433253 recurrence).
+struct Mt19937 {
+    uint32_t mt[624];
+    int i = 624;
+    explicit Mt19937(uint32_t seed) {
+        mt[0] = seed;
+        for (int j = 1; j < 624; ++j) mt[j] = 1812433253u * (mt[j - 1] ^ (mt[j - 1] >> 30)) + static_cast<uint32_t>(j);
+    }
+    uint32_t next() {
+        if (i >= 624) {
+            for (int j = 0; j < 624; ++j) {
+                const uint32_t y = (mt[j] & 0x80000000u) | (mt[(j + 1) % 624] & 0x7FFFFFFFu);
+                mt[j] = mt[(j + 397) % 624] ^ (y >> 1) ^ ((y & 1u) ? 0x9908B0DFu : 0u);
+            }
+            i = 0;
+        }
+        uint32_t y = mt[i++];
+        y ^= y >> 11;
+        y ^= (y << 7) & 0x9D2C5680u;
+        y ^= (y << 15) & 0xEFC60000u;
+        y ^= y >> 18;
+        return y;
+    }
+    // uniform in [0, range): the multiply-shift draw with rejection (Lemire 2019) that GCC's
+    // uniform_int_distribution performs for a 32-bit generator, which the reference was built with
+    uint32_t below(uint32_t range) {
+        uint64_t prod = static_cast<uint64_t>(next()) * range;
+        uint32_t low = static_cast<uint32_t>(prod);
+        if (low < range) {
+            const uint32_t threshold = (0u - range) % range;
+            while (low < threshold) {
+                prod = static_cast<uint64_t>(next()) * range;
+                low = static_cast<uint32_t>(prod);
+            }
+        }
+        return static_cast<uint32_t>(prod >> 32);
+    }
+};
+
+void put32(uint8_t* p, uint32_t v) { std::memcpy(p, &v, 4); }
+void put16(uint8_t* p, uint16_t v) { std::memcpy(p, &v, 2); }
+
+}  // namespace
+
+extern "C" {
+
+int csdr_encode_codes(csdr_context* ctx, const float* tiles, size_t n_tiles, size_t tile_dim, const float* atoms,
+                      uint16_t n_atoms, uint8_t n_stages, uint8_t k_per_stage, const float* stage_scales,
+                      uint16_t* codes_out, size_t capacity) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!tiles || !atoms || !stage_scales || !codes_out) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (!n_tiles || !tile_dim || !n_atoms || !n_stages || !k_per_stage || n_atoms > 0x7FFF)
+            throw Error(CSDR_ERR_INVALID_ARG, "zero or out-of-range size");
+        if (n_tiles > 0xFFFFFFFFull || tile_dim > 0xFFFFFFFFull) throw Error(CSDR_ERR_LIMIT, "too many tiles");
+        const size_t n_codes = n_tiles * n_stages * k_per_stage;
+        if (capacity < n_codes) throw Error(CSDR_ERR_BUFFER, "code buffer too small");
+        DevPtr t = upload(ctx, tiles, n_tiles * tile_dim * 4);
+        DevPtr d = upload(ctx, atoms, static_cast<size_t>(n_atoms) * tile_dim * 4);
+        DevPtr g = upload(ctx, stage_scales, 4u * n_stages);
+        DevPtr c = std::make_shared<DeviceBuffer>(n_codes * 2, ctx->device);
+        launch_code_tiles(ctx, static_cast<const float*>(t->ptr), static_cast<uint32_t>(n_tiles), static_cast<uint32_t>(tile_dim), d,
+                          n_atoms, n_stages, k_per_stage, static_cast<const float*>(g->ptr), static_cast<uint16_t*>(c->ptr));
+        CSDR_CUDA(cudaMemcpyAsync(codes_out, c->ptr, n_codes * 2, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+int csdr_hsdr_encode(csdr_context* ctx, const float* W, uint32_t rows, uint32_t cols, uint16_t tile_rows,
+                     uint16_t tile_cols, uint16_t n_atoms, uint8_t n_stages, uint8_t k_per_stage, float stage_decay,
+                     uint8_t ksvd_iters, void* payload_out, size_t capacity, size_t* n_out) {
+    return guard([&] {
+        require_ctx(ctx);
+        if (!W || !n_out) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
+        if (!rows || !cols || !tile_rows || !tile_cols || !n_atoms || !n_stages || !k_per_stage || n_atoms > 0x7FFF)
+            throw Error(CSDR_ERR_INVALID_ARG, "HSDR: zero or out-of-range config field");
+        if (ksvd_iters != 0)
+            throw Error(CSDR_ERR_UNSUPPORTED, "HSDR encode: only the fast mode (ksvd_iters = 0) runs on the device; "
+                                              "dictionary-update iterations stay with the reference encoder");
+        const uint32_t R_full = rows / tile_rows * tile_rows, C_full = cols / tile_cols * tile_cols;
+        if (!R_full || !C_full) throw Error(CSDR_ERR_GEOMETRY, "HSDR: tensor smaller than one tile");
+        const uint32_t n_rt = R_full / tile_rows, n_ct = C_full / tile_cols;
+        const uint64_t n_tiles64 = static_cast<uint64_t>(n_rt) * n_ct;
+        if (n_tiles64 < n_atoms) throw Error(CSDR_ERR_GEOMETRY, "HSDR: not enough tiles to fit dictionary");   // :1143-1145
+        const uint32_t n_tiles = static_cast<uint32_t>(n_tiles64);
+        const size_t T = static_cast<size_t>(tile_rows) * tile_cols;
+        const size_t n_codes = static_cast<size_t>(n_tiles) * n_stages * k_per_stage;
+        const size_t edge_floats = static_cast<size_t>(R_full) * (cols - C_full) + static_cast<size_t>(rows - R_full) * cols;
+        const size_t hdr = 36, total = hdr + 4u * n_stages + 4u * static_cast<size_t>(n_atoms) * T + 2u * n_codes + 4u * edge_floats;
+        *n_out = total;
+        if (!payload_out || capacity < total) throw Error(CSDR_ERR_BUFFER, "payload buffer too small");
+        uint8_t* out = static_cast<uint8_t*>(payload_out);
+
+        DevPtr Wd = upload(ctx, W, static_cast<size_t>(rows) * cols * 4);
+        DevPtr tiles = std::make_shared<DeviceBuffer>(static_cast<size_t>(n_tiles) * T * 4, ctx->device);
+        launch_extract_tiles(ctx, static_cast<const float*>(Wd->ptr), cols, tile_rows, tile_cols, n_rt, n_ct,
+                             static_cast<float*>(tiles->ptr));
+        // mean tile norm, summed in tile order on the host from per-tile doubles (:527-533)
+        DevPtr norms = std::make_shared<DeviceBuffer>(static_cast<size_t>(n_tiles) * 8, ctx->device);
+        launch_tile_norms(ctx, static_cast<const float*>(tiles->ptr), n_tiles, static_cast<uint32_t>(T), static_cast<double*>(norms->ptr));
+        std::vector<double> nh(n_tiles);
+        CSDR_CUDA(cudaMemcpyAsync(nh.data(), norms->ptr, nh.size() * 8, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        double norm_sum = 0.0;
+        for (double v : nh) norm_sum += v;
+        const float mean = static_cast<float>(norm_sum / static_cast<double>(n_tiles));
+        const float root = std::sqrt(static_cast<float>(static_cast<uint32_t>(n_stages) * k_per_stage));
+        const float init_scale = mean / (root > 1.0f ? root : 1.0f);
+        // tile picks (:513-517)
+        Mt19937 gen(0xC0DEu);
+        std::vector<uint32_t> picks(n_atoms);
+        for (uint32_t j = 0; j < n_atoms; ++j) picks[j] = gen.below(n_tiles);
+        DevPtr picks_d = upload(ctx, picks.data(), picks.size() * 4);
+        DevPtr D = std::make_shared<DeviceBuffer>(static_cast<size_t>(n_atoms) * T * 4, ctx->device);
+        launch_init_atoms(ctx, static_cast<const float*>(tiles->ptr), static_cast<const uint32_t*>(picks_d->ptr), n_atoms,
+                          static_cast<uint32_t>(T), init_scale, static_cast<float*>(D->ptr));
+        std::vector<float> gam(n_stages);
+        for (uint8_t l = 0; l < n_stages; ++l) gam[l] = std::pow(stage_decay, static_cast<float>(l));   // :507-509
+        DevPtr gam_d = upload(ctx, gam.data(), gam.size() * 4);
+        DevPtr codes = std::make_shared<DeviceBuffer>(n_codes * 2, ctx->device);
+        launch_code_tiles(ctx, static_cast<const float*>(tiles->ptr), n_tiles, static_cast<uint32_t>(T), D, n_atoms, n_stages,
+                          k_per_stage, static_cast<const float*>(gam_d->ptr), static_cast<uint16_t*>(codes->ptr));
+
+        // the payload (serialize, :1198-1235): header | stage scales | dictionary | codes | edge strips
+        std::memset(out, 0, hdr);
+        std::memcpy(out, "HSDR", 4);
+        put32(out + 4, 2u);
+        put32(out + 8, rows);
+        put32(out + 12, cols);
+        put32(out + 16, n_tiles);
+        put16(out + 20, tile_rows);
+        put16(out + 22, tile_cols);
+        put16(out + 24, n_atoms);
+        out[26] = n_stages;
+        out[27] = k_per_stage;
+        std::memcpy(out + 28, &stage_decay, 4);
+        put32(out + 32, static_cast<uint32_t>(4u * edge_floats));
+        std::memcpy(out + hdr, gam.data(), 4u * n_stages);
+        uint8_t* dict_at = out + hdr + 4u * n_stages;
+        uint8_t* codes_at = dict_at + 4u * static_cast<size_t>(n_atoms) * T;
+        CSDR_CUDA(cudaMemcpyAsync(dict_at, D->ptr, 4u * static_cast<size_t>(n_atoms) * T, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaMemcpyAsync(codes_at, codes->ptr, n_codes * 2, cudaMemcpyDeviceToHost, ctx->stream));
+        CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
+        // raw strips: top-right, then bottom (:1185-1197)
+        uint8_t* e = codes_at + 2u * n_codes;
+        const size_t wr = static_cast<size_t>(cols - C_full) * 4;
+        for (uint32_t r = 0; r < R_full && wr; ++r, e += wr) std::memcpy(e, W + static_cast<size_t>(r) * cols + C_full, wr);
+        for (uint32_t r = R_full; r < rows; ++r, e += static_cast<size_t>(cols) * 4)
+            std::memcpy(e, W + static_cast<size_t>(r) * cols, static_cast<size_t>(cols) * 4);
+    });
+}
+
+}  // extern "C"

@@ -81,7 +81,7 @@ namespace csdr {
 // Kernel classes for launch counting and optional per-class device timing.
 enum KernelClass {
     KC_UNPACK = 0, KC_DX, KC_GATHER, KC_TILE_PROJECT, KC_TILE_GATHER, KC_EDGE, KC_DENSE,
-    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_GEMV_FUSED, KC_ATTENTION, KC_GEMV_QUEUE, KC_COUNT
+    KC_DECODE_ROWS, KC_DEQUANT, KC_GEMM, KC_DECODER_OP, KC_GEMV_FUSED, KC_ATTENTION, KC_GEMV_QUEUE, KC_ENCODE, KC_COUNT
 };
 const char* kernel_class_name(int cls);
 struct TimedLaunch {

@@ -1,0 +1,22 @@
+// Device side of the HSDR encoder's fast mode: see encode.cu.
+#pragma once
+
+#include <cstdint>
+
+#include "../internal.hpp"
+
+namespace csdr {
+
+// W (row-major, C columns) -> tiles [n_rt * n_ct][tr * tc] of its aligned top-left block.
+void launch_extract_tiles(csdr_context* ctx, const float* W, uint32_t C, uint32_t tr, uint32_t tc, uint32_t n_rt,
+                          uint32_t n_ct, float* tiles);
+// norms[t] = Euclidean norm of tile t, as a double.
+void launch_tile_norms(csdr_context* ctx, const float* tiles, uint32_t n_tiles, uint32_t T, double* norms);
+// D[j] = tiles[picks[j]] / |tiles[picks[j]]| * init_scale.
+void launch_init_atoms(csdr_context* ctx, const float* tiles, const uint32_t* picks_dev, uint32_t K, uint32_t T, float init_scale,
+                       float* D);
+// The coding pass: packed codes [n_tiles][S][k] of the tiles against dictionary D (K x T).
+void launch_code_tiles(csdr_context* ctx, const float* tiles, uint32_t n_tiles, uint32_t T, const DevPtr& D, uint32_t K,
+                       uint32_t S, uint32_t k, const float* gammas_dev, uint16_t* codes_dev);
+
+}  // namespace csdr

@@ -104,7 +104,18 @@ struct QParams {
     uint32_t* seq;              // [0] queue launches completed, [1] CTAs that have read [0]
     int* status;
     uint32_t spin_poll, spin_barrier;
+    unsigned long long* trace;  // optional: global-timer stamps, [cta][8 tasks][8 slots] (tuning)
 };
+
+// slots: 0 first activations staged, 1 Dx of the CTA's first unit of the task published,
+// 2 gather warp 0 saw the watch words, 3 swept Dx, 4 rows written; 5 kernel entry, 6 tag taken
+__device__ __forceinline__ void stamp(const QParams& p, uint32_t task, uint32_t slot) {
+    if (p.trace && task < 8u) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[(static_cast<size_t>(blockIdx.x) * 8u + task) * 8u + slot] = t;
+    }
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -200,6 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t NS = p.n_stages;
     if (tid == 0) {
+        stamp(p, 0, 5);
         for (uint32_t s = 0; s < NS; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[s])));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&empty_bar[s])), "r"(kProductWarps));
@@ -297,7 +309,10 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
         // the first ring-full of weight copies does not depend on anything before this launch
         while (ui < p.n_units && it_issue < NS) issue();
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (lane == 0) tag_s = take_tag(p.seq);
+        if (lane == 0) {
+            tag_s = take_tag(p.seq);
+            stamp(p, 0, 6);
+        }
         asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
         while (ok && (it_fill < it_issue || ui < p.n_units)) {
             while (it_fill < it_issue) fill();
@@ -393,6 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                         }
                     }
                     asm volatile("bar.sync 1, %0;" ::"n"(kProductThreads) : "memory");   // the whole slab is staged
+                    if (s == 0 && tid == 32u) stamp(p, ti, 0);
                 }
                 // after a wait has run out the warp keeps walking its stages (the named barrier above
                 // needs all eight warps) but no longer waits or computes
@@ -438,6 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 if (lane == static_cast<uint32_t>(b)) mine = v;
             }
             if (ok && lane < MT && atom < t.K) st_tagged(p.dx + t.dx_off + static_cast<size_t>(atom) * MT + lane, mine, tag);
+            if (tid == 32u) stamp(p, ti, 1);
             if (t.norm_w) {
                 // every unit has staged the whole activation row; the task's first unit publishes the sum
                 // of squares per token: lanes, then warps, in order
@@ -529,6 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                     if (__any_sync(0xFFFFFFFFu, spins >= limit || *failed)) break;   // the sweep below records the failure
                     if (!p.split_rows) __nanosleep(256);
                 }
+                if (g == 0 && lane == 0) stamp(p, ti, 2);
                 const uint32_t n_w = t.K * MT;
                 const uint32_t n_mine = lane < n_w ? (n_w - lane + 31u) / 32u : 0u;
                 if (!poll_words<16>(p.dx + t.dx_off + lane, n_mine, 32u, tag, limit, failed, !p.split_rows,
@@ -546,6 +564,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 const float mine_inv = 1.0f / sqrtf(ss / static_cast<float>(t.C) + t.norm_eps);
                 inv = __shfl_sync(0xFFFFFFFFu, mine_inv, lane % MT);
             }
+            if (g == 0 && lane == 0) stamp(p, ti, 3);
             asm volatile("cp.async.wait_group 1;" ::: "memory");      // this task's codes (the next task's may still fly)
             __syncwarp();
             const uint32_t b = lane % MT;
@@ -591,6 +610,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 }
             }
             __syncwarp();   // dxs and the code buffer are free for the warp's next task
+            if (g == 0 && lane == 0) stamp(p, ti, 4);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (late && lane == 0) {
@@ -767,6 +787,7 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
         p.status = ctx->status_word;
         p.spin_poll = ctx->spin_limit_gemv;
         p.spin_barrier = ctx->spin_limit_barrier;
+        p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
         switch (mt) {
             case 1: launch_t<1>(ctx, p, max_k, max_code_bytes); break;
             case 2: launch_t<2>(ctx, p, max_k, max_code_bytes); break;

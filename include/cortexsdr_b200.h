@@ -287,6 +287,28 @@ CSDR_API int csdr_dequantize(csdr_context* ctx, const char* fmt, const void* dat
                              size_t nbytes, float scale, float zero_point, float* out_host,
                              size_t capacity_floats, size_t* n_out);
 
+/* ---- encoder, fast mode ----
+ * HierarchicalSDRStrategy::compress (strategies/HierarchicalSDRStrategy.cpp:1068-1236) with
+ * ksvd_iters = 0 (fitHierarchicalKSVD :494-571: a dictionary of n_atoms tiles picked by
+ * std::mt19937(0xC0DE), normalised and scaled, then one coding pass), on the device: W is
+ * rows x cols fp32 row-major on the host, the result an "HSDR" v2 payload. *n_out receives the
+ * payload size (also when the buffer is too small: CSDR_ERR_BUFFER). Header, stage scales, tile
+ * picks and edge strips equal the reference encoder's; atoms agree to rounding; a code may differ
+ * where a round's two best atoms tie within fp32 rounding (the coding pass works on projections
+ * computed once and updated through the Gram matrix instead of re-projecting a residual).
+ * ksvd_iters != 0 (dictionary-update iterations): CSDR_ERR_UNSUPPORTED. */
+CSDR_API int csdr_hsdr_encode(csdr_context* ctx, const float* W, uint32_t rows, uint32_t cols,
+                              uint16_t tile_rows, uint16_t tile_cols, uint16_t n_atoms,
+                              uint8_t n_stages, uint8_t k_per_stage, float stage_decay,
+                              uint8_t ksvd_iters, void* payload_out, size_t capacity, size_t* n_out);
+/* The coding pass alone (hierarchicalBinaryCode, :219-262, over every tile): tiles is
+ * (n_tiles x tile_dim) fp32, atoms (n_atoms x tile_dim), both on the host; codes_out receives
+ * n_tiles * n_stages * k_per_stage packed codes (packIndexSign, :76-80). */
+CSDR_API int csdr_encode_codes(csdr_context* ctx, const float* tiles, size_t n_tiles, size_t tile_dim,
+                               const float* atoms, uint16_t n_atoms, uint8_t n_stages,
+                               uint8_t k_per_stage, const float* stage_scales, uint16_t* codes_out,
+                               size_t capacity);
+
 /* The same block formats as the reference's INFERENCE side widens a stored-raw tensor
  * (decodeSupportedGGUFQuantized, SparseInferenceEngine.cpp:276-469): ggml's element order -
  * q4_k: 32 low nibbles then 32 high nibbles per 64-element group; q6_k: four runs of 32 per

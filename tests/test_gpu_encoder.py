@@ -1,0 +1,99 @@
+"""The encoder's fast mode on the GPU against the oracle's restatement of the reference encoder
+(pinned to the reference's own payloads in test_oracle_golden.py) and against the payloads the
+reference encoder wrote (tests/golden/encoder_coding.npz).
+
+The device codes the tiles from projections computed once and updated through the Gram matrix;
+the reference re-projects a residual every round. The two are equal in exact arithmetic, so the
+bar is: header, stage scales, tile picks and edge strips identical; atoms within 2e-6 of the
+largest atom value; codes identical except where a round's best candidates tie within rounding
+(at least 99.5 % identical here), and a reconstruction error within 1e-4 (relative) of the
+reference's."""
+import numpy as np
+import pytest
+
+import cortexsdr_b200 as cs
+
+pytestmark = pytest.mark.gpu
+
+
+def _tiles_of(W, tile_rows, tile_cols):
+    # extractTiles order (strategies/HierarchicalSDRStrategy.cpp:95-116)
+    nr, nc = W.shape[0] // tile_rows, W.shape[1] // tile_cols
+    return np.stack([W[a * tile_rows:(a + 1) * tile_rows, b * tile_cols:(b + 1) * tile_cols].reshape(-1)
+                     for a in range(nr) for b in range(nc)])
+
+
+def _rebuild(tiles_shape, D, scales, codes):
+    # decodeAllTiles (:612-634) on the host, in double
+    n, T = tiles_shape
+    out = np.zeros((n, T))
+    idx, sgn = (codes & 0x7FFF).astype(np.int64), np.where(codes & 0x8000, -1.0, 1.0)
+    for l in range(codes.shape[1]):
+        for s in range(codes.shape[2]):
+            out += (scales[l] * sgn[:, l, s])[:, None] * D[idx[:, l, s]].astype(np.float64)
+    return out
+
+
+def _compare_codes(tiles, D, scales, mine, ref):
+    same = float((mine == ref).mean())
+    assert same >= 0.995, same
+    err_m = np.linalg.norm(tiles - _rebuild(tiles.shape, D, scales, mine)) / np.linalg.norm(tiles)
+    err_r = np.linalg.norm(tiles - _rebuild(tiles.shape, D, scales, ref)) / np.linalg.norm(tiles)
+    assert abs(err_m - err_r) <= 1e-4 * max(err_r, 1e-12), (err_m, err_r)
+    # an atom is used at most once per stage (used_this_stage, :229-241)
+    per_stage = (mine & 0x7FFF).reshape(-1, mine.shape[2])
+    assert all(len(set(r)) == mine.shape[2] for r in per_stage.tolist())
+    return same
+
+
+@pytest.mark.parametrize("label", ["row_fast", "row_fit", "tiles_2d"])
+def test_coding_pass_against_reference_payloads(ctx, oracle, golden, label):
+    g = golden("encoder_coding.npz")
+    W, pay = g[label + "_w"], g[label + "_payload"]
+    v = oracle.parse(pay)
+    T = v.tile_rows * v.tile_cols
+    D = pay[v.off_dict:v.off_dict + 4 * v.n_atoms * T].view(np.float32).reshape(v.n_atoms, T)
+    packed, _, _, scales = oracle.codes(pay)
+    tiles = _tiles_of(W, v.tile_rows, v.tile_cols)
+    mine = cs.HierarchicalSDRStrategy(ctx).encode_codes(tiles, D, scales, v.k)
+    _compare_codes(tiles, D, scales, mine, packed.reshape(mine.shape))
+
+
+@pytest.mark.parametrize("shape,tile,atoms,k", [((96, 128), (1, 128), 32, 4), ((100, 150), (16, 16), 32, 4),
+                                                 ((512, 1024), (1, 1024), 128, 6), ((640, 512), (32, 64), 128, 5)])
+def test_fast_mode_payload_against_the_oracle(ctx, oracle, shape, tile, atoms, k):
+    # the last two shapes have 128 atoms and tile widths that are multiples of 8: projections and
+    # Gram matrix on the tensor cores; the first two run on the CUDA cores
+    W = np.random.default_rng(shape[0]).normal(0, 0.05, shape).astype(np.float32)
+    st = cs.HierarchicalSDRStrategy(ctx)
+    mine = np.frombuffer(st.compress(W, tile_rows=tile[0], tile_cols=tile[1], n_atoms=atoms, k=k), np.uint8)
+    want = oracle.encode_fast(W, tile[0], tile[1], atoms, 3, k, 0.5, 0)
+    v = oracle.parse(want)
+    assert mine.size == want.size
+    assert np.array_equal(mine[:v.off_dict], want[:v.off_dict])                      # header + stage scales
+    T = tile[0] * tile[1]
+    Dw = want[v.off_dict:v.off_codes].view(np.float32).reshape(atoms, T)
+    Dm = mine[v.off_dict:v.off_codes].view(np.float32).reshape(atoms, T)
+    assert np.abs(Dw - Dm).max() <= 2e-6 * np.abs(Dw).max()                          # same tiles picked, same scale
+    assert np.array_equal(mine[v.off_edges:], want[v.off_edges:])                    # edge strips
+    n = v.n_tiles * v.n_stages * v.k
+    cm = mine[v.off_codes:v.off_codes + 2 * n].view(np.uint16).reshape(v.n_tiles, v.n_stages, v.k)
+    cw = want[v.off_codes:v.off_codes + 2 * n].view(np.uint16).reshape(v.n_tiles, v.n_stages, v.k)
+    scales = want[v.off_scales:v.off_scales + 4 * v.n_stages].view(np.float32)
+    tiles = _tiles_of(W, *tile)
+    _compare_codes(tiles, Dw, scales, cm, cw)
+    # what this library encoded, it and the oracle decode alike
+    seg = cs.Segment.from_payload(mine.tobytes(), ctx)
+    assert np.array_equal(seg.decompress(), oracle.decompress(mine))
+    seg.close()
+
+
+def test_encoder_refusals(ctx):
+    st = cs.HierarchicalSDRStrategy(ctx)
+    W = np.zeros((8, 64), np.float32)
+    with pytest.raises(cs.CompressionError, match="smaller than one tile"):
+        st.compress(W, tile_rows=16, tile_cols=16, n_atoms=4)
+    with pytest.raises(cs.CompressionError, match="not enough tiles"):
+        st.compress(W, tile_rows=1, tile_cols=64, n_atoms=16)
+    with pytest.raises(cs.CompressionError, match="fast mode"):
+        st.compress(np.ones((64, 64), np.float32), tile_rows=1, tile_cols=64, n_atoms=8, ksvd_iters=3)
