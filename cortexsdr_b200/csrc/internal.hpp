@@ -98,7 +98,7 @@ struct csdr_context {
     size_t smem_optin = 0;
     uint64_t launches = 0;
     // Grow-only scratch (Dx partials, factored 2-D products, host staging).
-    csdr::DevPtr scratch[7];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials, 5 wait self-test, 6 GEMV queue
+    csdr::DevPtr scratch[8];  // 0 Dx, 1 tile products, 2 materialised W, 3 host staging, 4 fused-GEMV partials, 5 activation planes / wait self-test, 6 GEMV queue, 7 dense product before re-tiling
     void* scratch_get(int slot, size_t bytes);
     int* status_word = nullptr;  // device int: kernels record bounded-wait timeouts here
     // Page-locked, device-mapped host staging for the host-buffer entry points (grow-only).

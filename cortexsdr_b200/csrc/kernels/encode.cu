@@ -220,7 +220,9 @@ void launch_code_tiles(csdr_context* ctx, const float* tiles, uint32_t n_tiles, 
     if (K == 0 || K > 1024u) throw Error(CSDR_ERR_LIMIT, "encoder: dictionaries of 1 to 1024 atoms");
     // projections atom-major, Pt[K][n_tiles], then the Gram matrix G[K][K]
     const size_t pt_floats = static_cast<size_t>(K) * n_tiles, g_floats = static_cast<size_t>(K) * K;
-    float* Pt = static_cast<float*>(ctx->scratch_get(1, (pt_floats + g_floats) * sizeof(float)));
+    // buffers of their own: the projection kernel below uses (and may regrow) the context's scratch
+    DeviceBuffer work((pt_floats + g_floats) * sizeof(float), ctx->device);
+    float* Pt = static_cast<float*>(work.ptr);
     float* G = Pt + pt_floats;
     // the dictionary in the role of a row-tile segment's atoms, the tiles in the role of the tokens
     csdr_segment dict{};
@@ -259,6 +261,7 @@ void launch_code_tiles(csdr_context* ctx, const float* tiles, uint32_t n_tiles, 
     else if (K <= 512) greedy_kernel<16><<<grid, 128, 0, ctx->stream>>>(Pt, n_tiles, G, gammas_dev, codes_dev, n_tiles, K, S, k);
     else greedy_kernel<32><<<grid, 128, 0, ctx->stream>>>(Pt, n_tiles, G, gammas_dev, codes_dev, n_tiles, K, S, k);
     ls.done("greedy_kernel");
+    CSDR_CUDA(cudaStreamSynchronize(ctx->stream));   // `work` goes away with this scope
 }
 
 }  // namespace csdr

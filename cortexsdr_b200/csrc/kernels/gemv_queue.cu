@@ -207,6 +207,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
     __shared__ int failed_s;
     __shared__ uint32_t tag_s;
     __shared__ float ssq_s[kProductWarps][kMaxTokens];
+    __shared__ float inv_s[kMaxTokens];
     asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t NS = p.n_stages;
@@ -476,10 +477,11 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
         }
         if (!ok && lane == 0) atomicExch(p.status, 1);
     } else {
-        // ================= gather: four warps, each on its own =================
+        // ================= gather: four warps =================
         const uint32_t g = warp - (kLoaderWarps + kProductWarps);
         unsigned char* mine = qsm + static_cast<size_t>(NS) * p.stage_bytes + static_cast<size_t>(g) * p.gw_bytes;
         float* dxs = reinterpret_cast<float*>(mine);
+        float* dxs0 = reinterpret_cast<float*>(qsm + static_cast<size_t>(NS) * p.stage_bytes);   // warp 0's copy, shared when rows are split
         unsigned char* codes_buf = mine + p.dxs_bytes;
         float* scales_buf = reinterpret_cast<float*>(codes_buf + 2u * static_cast<size_t>(p.codes_bytes));
         const uint32_t t_first = p.split_rows ? 0u : g, t_step = p.split_rows ? 1u : kGatherWarps;
@@ -530,39 +532,57 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
             uint32_t row0, rows_here;
             my_rows(t, row0, rows_here);
             // hand-over. First a light watch on one word per unit (its last atom, first token), so that
-            // a warp that is early does not sweep the whole slot again and again; then this task's Dx
-            // words, sixteen loads in flight per lane (stragglers are polled where they are).
-            if (rows_here) {
-                const uint32_t n_u = t.n_units;
-                const uint32_t n_watch = lane < n_u ? (n_u - lane + 31u) / 32u : 0u;
-                for (uint32_t spins = 0;; ++spins) {
-                    bool all = true;
-                    for (uint32_t q = 0; q < n_watch; ++q) {
-                        const uint32_t unit = lane + q * 32u;
-                        const uint32_t atom = min(unit * kAtomsPerUnit + kAtomsPerUnit - 1u, t.K - 1u);
-                        all = all && static_cast<uint32_t>(ld_tagged(p.dx + t.dx_off + static_cast<size_t>(atom) * MT) >> 32) == tag;
-                    }
-                    if (__all_sync(0xFFFFFFFFu, all)) break;
-                    if (__any_sync(0xFFFFFFFFu, spins >= limit || *failed)) break;   // the sweep below records the failure
-                    if (!p.split_rows) __nanosleep(256);
-                }
-                if (g == 0 && lane == 0) stamp(p, ti, 2);
-                const uint32_t n_w = t.K * MT;
-                const uint32_t n_mine = lane < n_w ? (n_w - lane + 31u) / 32u : 0u;
-                if (!poll_words<16>(p.dx + t.dx_off + lane, n_mine, 32u, tag, limit, failed, !p.split_rows,
-                                    [&](uint32_t i, float v) { dxs[lane + i * 32u] = v; }))
-                    late = true;
-            }
+            // nobody sweeps the whole slot again and again while the products are still at work; then
+            // this task's Dx words, sixteen loads in flight per lane (stragglers are polled where they
+            // are). With a task's rows split over the warps, the four warps share ONE copy of Dx: warp 0
+            // watches, all 128 threads sweep - every poller less is load off the few L2 lines all CTAs
+            // are asking for.
+            const bool coop = p.split_rows != 0u;
+            const bool cta_rows = blockIdx.x * t.rows_per_cta < t.R;
+            float* dx_use = coop ? dxs0 : dxs;
             float inv = 1.0f;
-            if (t.norm_w) {
-                // 1 / rms of this task's activations: the sum of squares its first unit published
-                float ss = 0.0f;
-                if (lane < t.M &&
-                    !poll_words<1>(p.sumsq + static_cast<size_t>(ti) * kMaxTokens + lane, 1u, 1u, tag, limit, failed, false,
-                                   [&](uint32_t, float v) { ss = v; }))
+            if (coop ? cta_rows : rows_here != 0u) {
+                if (!coop || g == 0) {
+                    const uint32_t n_u = t.n_units;
+                    const uint32_t n_watch = lane < n_u ? (n_u - lane + 31u) / 32u : 0u;
+                    for (uint32_t spins = 0;; ++spins) {
+                        bool all = true;
+                        for (uint32_t q = 0; q < n_watch; ++q) {
+                            const uint32_t unit = lane + q * 32u;
+                            const uint32_t atom = min(unit * kAtomsPerUnit + kAtomsPerUnit - 1u, t.K - 1u);
+                            all = all && static_cast<uint32_t>(ld_tagged(p.dx + t.dx_off + static_cast<size_t>(atom) * MT) >> 32) == tag;
+                        }
+                        if (__all_sync(0xFFFFFFFFu, all)) break;
+                        if (__any_sync(0xFFFFFFFFu, spins >= limit || *failed)) break;   // the sweep below records the failure
+                        if (!coop) __nanosleep(256);
+                    }
+                    if (g == 0 && lane == 0) stamp(p, ti, 2);
+                }
+                if (coop) asm volatile("bar.sync 2, %0;" ::"n"(32u * kGatherWarps) : "memory");
+                const uint32_t n_w = t.K * MT;
+                const uint32_t me = coop ? g * 32u + lane : lane, step = coop ? 32u * kGatherWarps : 32u;
+                const uint32_t n_mine = me < n_w ? (n_w - me + step - 1u) / step : 0u;
+                if (!poll_words<16>(p.dx + t.dx_off + me, n_mine, step, tag, limit, failed, !coop,
+                                    [&](uint32_t i, float v) { dx_use[me + i * step] = v; }))
                     late = true;
-                const float mine_inv = 1.0f / sqrtf(ss / static_cast<float>(t.C) + t.norm_eps);
-                inv = __shfl_sync(0xFFFFFFFFu, mine_inv, lane % MT);
+                if (t.norm_w) {
+                    // 1 / rms of this task's activations: the sum of squares its first unit published
+                    float ss = 0.0f;
+                    const bool owns = coop ? (g == 0 && lane < t.M) : lane < t.M;
+                    if (owns && !poll_words<1>(p.sumsq + static_cast<size_t>(ti) * kMaxTokens + lane, 1u, 1u, tag, limit, failed, false,
+                                               [&](uint32_t, float v) { ss = v; }))
+                        late = true;
+                    const float mine_inv = 1.0f / sqrtf(ss / static_cast<float>(t.C) + t.norm_eps);
+                    if (coop) {
+                        if (owns) inv_s[lane] = mine_inv;
+                    } else {
+                        inv = __shfl_sync(0xFFFFFFFFu, mine_inv, lane % MT);
+                    }
+                }
+                if (coop) {
+                    asm volatile("bar.sync 2, %0;" ::"n"(32u * kGatherWarps) : "memory");
+                    if (t.norm_w) inv = inv_s[lane % MT];
+                }
             }
             if (g == 0 && lane == 0) stamp(p, ti, 3);
             asm volatile("cp.async.wait_group 1;" ::: "memory");      // this task's codes (the next task's may still fly)
@@ -586,7 +606,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                             for (int q = 0; q < 8; ++q) {
                                 const uint32_t code = k0 + q < t.k ? lc[k0 + q] : 0u;
                                 const uint32_t a = code & 0x7FFFu;
-                                const float dv = a < t.K ? dxs[a * MT + b] : 0.0f;
+                                const float dv = a < t.K ? dx_use[a * MT + b] : 0.0f;
                                 v[q] = __fmul_rn((code & 0x8000u) ? -gamma : gamma, dv);
                             }
 #pragma unroll
@@ -609,7 +629,8 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                     }
                 }
             }
-            __syncwarp();   // dxs and the code buffer are free for the warp's next task
+            __syncwarp();   // the warp's code buffer is free for its next task
+            if (coop && cta_rows) asm volatile("bar.sync 2, %0;" ::"n"(32u * kGatherWarps) : "memory");   // so is the shared Dx copy
             if (g == 0 && lane == 0) stamp(p, ti, 4);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");

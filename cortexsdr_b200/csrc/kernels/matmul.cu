@@ -685,7 +685,7 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
         const uint32_t M = static_cast<uint32_t>(a.batch);
         const bool direct = a.y_layout == CSDR_LAYOUT_FEATURE_MAJOR && !a.bias;
         float* out = direct ? a.y
-                            : static_cast<float*>(ctx->scratch_get(1, static_cast<size_t>(g.rows) * M * sizeof(float)));
+                            : static_cast<float*>(ctx->scratch_get(7, static_cast<size_t>(g.rows) * M * sizeof(float)));
         launch_dx_tma(ctx, seg->dense.get(), a, out, M);
         if (!direct) {
             YView yv{a.y, a.y_layout, g.rows, M, 0u, M, a.bias};
