@@ -164,7 +164,8 @@ FUSED_GEMV_DRAM_BYTES_NCU = 8996000   # per launch, cfg2 shape, batch 1 (8.996 M
 QUEUE_DRAM_BYTES_PER_TASK_NCU = None   # per task of the queue kernel, cfg2 shape, batch 1 (set from the ncu capture)
 
 
-def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True):
+def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True, kv_dtype="f32",
+                  shared_dicts=False):
     """Decode tokens/s of a decoder-shaped synthetic archive (every linear an HSDR row-tile segment
     with its own dictionary, K=512 3x8; random-init stand-in for the config's weights).
     With more than one rank the decoder is tensor parallel; CSDR_BENCH_NCCL_ONLY=1 withholds the
@@ -173,9 +174,12 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
     spec = DECODERS[name]
     cfg = spec["cfg"]
     os.makedirs(CACHE, exist_ok=True)
-    path = os.path.join(CACHE, f"{name}.sdr")
+    # shared_dicts: a different archive of the same shapes - every block role (attn_q ... ffn_down)
+    # shares ONE dictionary over all blocks (resource segments inside the .sdr), so a step reads
+    # seven dictionaries and the codes instead of a dictionary per tensor
+    path = os.path.join(CACHE, f"{name}{'_shared' if shared_dicts else ''}.sdr")
     if rank == 0 and not os.path.exists(path):
-        synth.decoder_archive(path + ".tmp", **cfg, kv_atoms=spec["kv_atoms"], seed=100)
+        synth.decoder_archive(path + ".tmp", **cfg, kv_atoms=spec["kv_atoms"], seed=100, shared_dicts=shared_dicts)
         os.replace(path + ".tmp", path)
     if world > 1:
         dist.barrier()
@@ -188,9 +192,10 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
             dist.all_gather_object(got, b)
             return got
     dec = cs.Decoder(ld, **cfg, max_seq=ctxlen + steps + 8, max_batch=B, rms_eps=spec["eps"], comm=comm,
-                     all_gather=None if os.environ.get("CSDR_BENCH_NCCL_ONLY") else ag)
+                     all_gather=None if os.environ.get("CSDR_BENCH_NCCL_ONLY") else ag, kv_dtype=kv_dtype)
     rng = np.random.default_rng(7)
-    out = {"batch": B, "context": ctxlen, "steps": steps, "tp": world}
+    out = {"batch": B, "context": ctxlen, "steps": steps, "tp": world, "kv_cache": kv_dtype,
+           "dictionaries": "one per block role, shared by all blocks" if shared_dicts else "one per tensor"}
     if world > 1:
         peer = not os.environ.get("CSDR_BENCH_NCCL_ONLY") and 2 <= world <= 8
         if os.environ.get("CSDR_TP_EXCHANGE") in ("peer", "nccl") and not os.environ.get("CSDR_BENCH_NCCL_ONLY") and world <= 8:
@@ -613,15 +618,28 @@ def main():
         for m in (1, 8, 64, 512):
             xm, ym = make_io(m, torch.bfloat16)
             st = max(3, args.steps // (4 if m >= 64 else 1))
-            msm = timed(lambda: step(xm, ym, m, cs.DTYPE_BF16), st, 3)
+            sfn, how = (lambda: step(xm, ym, m, cs.DTYPE_BF16)), "eager"
+            if not args.no_graph:
+                try:
+                    with torch.cuda.stream(stream):
+                        sfn()                    # builds per-dictionary caches outside the capture
+                    ctx.synchronize()
+                    sg = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(sg, stream=stream):
+                        step(xm, ym, m, cs.DTYPE_BF16)
+                    sfn, how = sg.replay, "cuda graph"
+                except Exception as e:
+                    how = f"eager (graph capture failed: {type(e).__name__})"
+                    torch.cuda.synchronize()
+            msm = timed(sfn, st, 3)
             per = msm / st / nseg * 1e-3
-            ent = {"us_per_matmul": per * 1e6}
+            ent = {"us_per_matmul": per * 1e6, "launch": how}
             if m <= 16:
                 ent["GBps_compressed"] = alg_bytes(len(pay), m, 2) / per / 1e9
                 ent["frac_hbm"] = ent["GBps_compressed"] / hbm_peak
             ent["TFLOPs_dense_equiv"] = 2.0 * R * C * m / per / 1e12
             ent["frac_bf16_peak"] = ent["TFLOPs_dense_equiv"] / tf_peak
-            if m >= 64:
+            if m >= 8:
                 # events around every launch: where the time of one wide matmul goes
                 ctx.profile(True)
                 with torch.cuda.stream(stream):
@@ -661,6 +679,22 @@ def main():
         except Exception as e:
             decode[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
             torch.cuda.synchronize()
+            continue
+        try:
+            # the cache OPTION as its own line (rows rounded to bf16, sums fp32); the figures above
+            # stay on the fp32 cache, the reference's arithmetic
+            decode[name + "_bf16_kv"] = decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm,
+                                                      not args.no_graph, kv_dtype="bf16")
+        except Exception as e:
+            decode[name + "_bf16_kv"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            torch.cuda.synchronize()
+        if world == 1:
+            try:
+                decode[name + "_shared_dicts"] = decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm,
+                                                               not args.no_graph, shared_dicts=True)
+            except Exception as e:
+                decode[name + "_shared_dicts"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                torch.cuda.synchronize()
 
     line = {"metric": "compressed_weight_matmul_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,

@@ -61,7 +61,7 @@ class DecoderConfig(C.Structure):
                 ("kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("inter", C.c_uint32),
                 ("vocab", C.c_uint32), ("max_seq", C.c_uint32), ("max_batch", C.c_uint32),
                 ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("tp_rank", C.c_uint32),
-                ("tp_size", C.c_uint32), ("nccl_comm", C.c_void_p)]
+                ("tp_size", C.c_uint32), ("nccl_comm", C.c_void_p), ("kv_dtype", C.c_uint32)]
 
 
 _P = C.c_void_p

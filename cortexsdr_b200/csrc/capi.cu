@@ -5,6 +5,8 @@
 #include <cstdlib>
 #include <chrono>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -154,9 +156,15 @@ bool wait_host_word(const volatile uint32_t* word, uint32_t seq) {
 }  // namespace csdr_hostio
 using namespace csdr_hostio;
 
+// The attribute belongs to the function on the device, not to a context: the record of what has
+// been opted into is shared by all contexts of the process (a context that set a smaller value
+// behind another's back would otherwise lower it).
 void csdr_context::opt_in_smem(const void* kernel, size_t bytes) {
     if (bytes <= 48u * 1024u) return;
-    size_t& have = smem_optins[kernel];
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, size_t> optins;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& have = optins[{device, kernel}];
     if (bytes > have) {
         CSDR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
         have = bytes;
@@ -216,6 +224,7 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE")) ctx->gemv_queue = e[0] != '0';
         if (const char* e = std::getenv("CSDR_CACHE_2D")) ctx->cache_2d = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_QUEUE")) ctx->decoder_queue = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_DECODER_FOLD")) ctx->decoder_fold = e[0] != '0';
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE_SINGLE")) ctx->gemv_queue_single = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TENSOR_CORES")) ctx->tensor_cores = e[0] != '0';

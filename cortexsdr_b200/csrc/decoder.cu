@@ -18,6 +18,7 @@
 #include "internal.hpp"
 #include "kernels/decoder_ops.hpp"
 #include "kernels/gemm_tcgen05.hpp"
+#include "kernels/gemv_fused.hpp"
 #include "kernels/gemv_queue.hpp"
 
 using namespace csdr;
@@ -95,7 +96,9 @@ struct csdr_decoder {
     DevPtr out_norm;
     std::vector<Layer> layers;
     DevPtr kcache, vcache;  // [layer][seq][pos][kv head (local)][head_dim]
-    size_t cache_layer_stride = 0;
+    size_t cache_layer_stride = 0;   // elements
+    int kv_dtype = CSDR_DTYPE_F32;   // fp32 as the reference computes, or bf16 (half the cache traffic; sums stay fp32)
+    size_t kv_es = 4;
     std::vector<int32_t> pos_host;
     // token selection of the reference's generation loop (off: plain argmax): temperature and a
     // bitmap of the tokens each sequence has produced, [max_batch][seen_words]
@@ -121,6 +124,7 @@ struct csdr_decoder {
     DevPtr xp_h, xp_att, xp_act;
     bool planes_capable = false;
     bool queue_capable = false;    // every block linear an HSDR row-tile image the GEMV queue takes
+    uint32_t fold_max_mt = 0;      // widest token tile at which the one-launch GEMVs take the blocks' glue (0: never)
     ~csdr_decoder() {
         for (void* m : xch_maps)
             if (m) cudaIpcCloseMemHandle(m);
@@ -359,11 +363,11 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
         Layer& L = d->layers[li];
         wide(d, {&L.q, &L.k, &L.v}, h_hi, h_n, T, true, false, sums,
              {WideOut{F(d->q), nullptr, nullptr}, WideOut{F(d->k), nullptr, nullptr}, WideOut{F(d->v), nullptr, nullptr}});
-        float* kc = F(d->kcache) + li * d->cache_layer_stride;
-        float* vc = F(d->vcache) + li * d->cache_layer_stride;
-        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
+        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
                       c.max_seq, c.rope_theta);
-        op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, nullptr,
+        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, nullptr,
                      a_hi, a_hi + a_n);
         wide(d, {&L.o}, a_hi, a_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
         op_scale_sumsq_planes(ctx, F(d->hidden), F(L.ffn_norm), T, Hl, h_hi, h_hi + h_n, sums);
@@ -401,11 +405,11 @@ void run_blocks_queue(csdr_decoder* d, uint32_t T) {
     }
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         const Layer& L = d->layers[li];
-        float* kc = F(d->kcache) + li * d->cache_layer_stride;
-        float* vc = F(d->vcache) + li * d->cache_layer_stride;
-        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
+        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
                       c.max_seq, c.rope_theta);
-        op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
         QueueItem list[7];
         uint32_t n = 0;
         list[n] = item(L.o, F(d->att), F(d->hidden));            // 0: h += Wo att
@@ -441,6 +445,56 @@ void run_blocks_queue(csdr_decoder* d, uint32_t T) {
     op_rmsnorm(ctx, F(d->hidden), F(d->out_norm), T, H, c.rms_eps, F(d->normed));
 }
 
+// A short step with the glue of api/cortex_sdk.cpp:1569-1679 folded into the one-launch GEMVs: the
+// two RMS normalisations ride on the products that consume them (q|k|v, gate|up), the residual
+// additions on the output and down projections, SwiGLU on the (gate, up) pair. Six launches per
+// block (q|k|v, rotary + cache, attention, output, gate|up, down) instead of nine.
+uint32_t token_tile(uint32_t T) { return T <= 1 ? 1u : T <= 2 ? 2u : T <= 4 ? 4u : T <= 8 ? 8u : 16u; }
+bool use_folded(const csdr_decoder* d, uint32_t T) {
+    return d->P == 1 && T <= 16u && d->ctx->decoder_fold && token_tile(T) <= d->fold_max_mt;
+}
+void fused_with_glue(csdr_decoder* d, std::initializer_list<const Linear*> ls, const float* x, uint32_t T,
+                     std::initializer_list<float*> ys, const FusedGlue& glue) {
+    const csdr_segment* segs[kMaxFusedGroup];
+    float* outs[kMaxFusedGroup];
+    uint32_t n = 0;
+    auto y = ys.begin();
+    for (const Linear* l : ls) {
+        segs[n] = l->use();
+        outs[n++] = *y++;
+    }
+    launch_gemv_fused(d->ctx, segs, n, x, CSDR_DTYPE_F32, CSDR_LAYOUT_TOKEN_MAJOR, T, 0, T, outs, CSDR_LAYOUT_TOKEN_MAJOR,
+                      nullptr, static_cast<int>(token_tile(T)), &glue);
+}
+void run_blocks_folded(csdr_decoder* d, uint32_t T) {
+    const csdr_decoder_config& c = d->cfg;
+    csdr_context* ctx = d->ctx;
+    const uint32_t H = c.hidden, HD = c.head_dim;
+    float* h = F(d->hidden);
+    for (uint32_t li = 0; li < c.n_layers; ++li) {
+        const Layer& L = d->layers[li];
+        FusedGlue g_attn;
+        g_attn.norm_w = F(L.attn_norm);
+        g_attn.norm_eps = c.rms_eps;
+        fused_with_glue(d, {&L.q, &L.k, &L.v}, h, T, {F(d->q), F(d->k), F(d->v)}, g_attn);
+        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
+                      c.max_seq, c.rope_theta);
+        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        FusedGlue g_res;
+        g_res.residual[0] = h;
+        fused_with_glue(d, {&L.o}, F(d->att), T, {h}, g_res);                       // h += Wo att
+        FusedGlue g_mlp;
+        g_mlp.norm_w = F(L.ffn_norm);
+        g_mlp.norm_eps = c.rms_eps;
+        g_mlp.swiglu = true;
+        fused_with_glue(d, {&L.gate, &L.up}, h, T, {F(d->gate), F(d->up)}, g_mlp);  // up = silu(gate) * up
+        fused_with_glue(d, {&L.down}, F(d->up), T, {h}, g_res);                     // h += Wd act
+    }
+    op_rmsnorm(ctx, h, F(d->out_norm), T, H, c.rms_eps, F(d->normed));
+}
+
 bool use_planes(const csdr_decoder* d, uint32_t T) {
     if (d->P > 1) return true;
     const csdr_context* ctx = d->ctx;
@@ -462,15 +516,19 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
         run_blocks_queue(d, T);
         return;
     }
+    if (use_folded(d, T)) {
+        run_blocks_folded(d, T);
+        return;
+    }
     op_rmsnorm(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, H, c.rms_eps, F(d->normed));
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         Layer& L = d->layers[li];
         linear_group(d, {&L.q, &L.k, &L.v}, F(d->normed), T, {F(d->q), F(d->k), F(d->v)});
-        float* kc = F(d->kcache) + li * d->cache_layer_stride;
-        float* vc = F(d->vcache) + li * d->cache_layer_stride;
-        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
+        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
                       c.max_seq, c.rope_theta);
-        op_attention(ctx, F(d->q), kc, vc, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
         linear(d, L.o, F(d->att), T, F(d->proj));
         op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
         linear_group(d, {&L.gate, &L.up}, F(d->normed), T, {F(d->gate), F(d->up)});
@@ -614,8 +672,12 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         d->T_max = std::max(c.max_seq, c.max_batch);
         const size_t T = d->T_max;
         d->cache_layer_stride = static_cast<size_t>(c.max_batch) * c.max_seq * d->KVD_l;
-        d->kcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * 4);
-        d->vcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * 4);
+        if (c.kv_dtype != CSDR_DTYPE_F32 && c.kv_dtype != CSDR_DTYPE_BF16)
+            throw Error(CSDR_ERR_INVALID_ARG, "decoder: kv_dtype must be CSDR_DTYPE_F32 or CSDR_DTYPE_BF16");
+        d->kv_dtype = static_cast<int>(c.kv_dtype);
+        d->kv_es = d->kv_dtype == CSDR_DTYPE_BF16 ? 2 : 4;
+        d->kcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * d->kv_es);
+        d->vcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * d->kv_es);
         d->pos_host.assign(c.max_batch, 0);
         d->pos_dev = dev_alloc(ctx, c.max_batch * 4);
         d->tokens_dev = dev_alloc(ctx, T * 4);
@@ -673,6 +735,30 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
                     q_ok = q_ok && !L.gate.raw && !L.up.raw && L.gate.rows_local == L.up.rows_local;
                 }
                 d->queue_capable = q_ok;
+            }
+            if (d->P == 1) {
+                // widest token tile at which every group of every block takes the folded glue
+                for (uint32_t mt : {16u, 8u, 4u, 2u, 1u}) {
+                    bool f_ok = true;
+                    for (const Layer& L : d->layers) {
+                        const Linear* all[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
+                        for (const Linear* l : all) f_ok = f_ok && !l->raw && l->use();
+                        if (!f_ok) break;
+                        FusedGlue norm, mlp, none;
+                        norm.norm_w = mlp.norm_w = F(L.attn_norm);
+                        mlp.swiglu = true;
+                        const csdr_segment* qkv[3] = {L.q.use(), L.k.use(), L.v.use()};
+                        const csdr_segment* gu[2] = {L.gate.use(), L.up.use()};
+                        const csdr_segment* o = L.o.use();
+                        const csdr_segment* dn = L.down.use();
+                        f_ok = gemv_fused_glue_supported(ctx, qkv, 3, mt, norm) && gemv_fused_glue_supported(ctx, gu, 2, mt, mlp) &&
+                               gemv_fused_glue_supported(ctx, &o, 1, mt, none) && gemv_fused_glue_supported(ctx, &dn, 1, mt, none);
+                    }
+                    if (f_ok) {
+                        d->fold_max_mt = mt;
+                        break;
+                    }
+                }
             }
             if (d->P > 1 && !ok)
                 throw Error(CSDR_ERR_UNSUPPORTED,

@@ -20,8 +20,10 @@ struct csdr_archive {
     ArchiveIndex index;
     std::unordered_map<std::string, csdr_segment*> images;  // HSDR device images
     std::unordered_map<std::string, DevPtr> raw;            // stored-raw fp32 matrices
+    std::unordered_map<std::string, csdr_dictionary*> dicts;  // shared-dictionary resource segments, by name
     ~csdr_archive() {
         for (auto& kv : images) csdr_segment_destroy(kv.second);
+        for (auto& kv : dicts) csdr_dictionary_destroy(kv.second);
     }
 };
 
@@ -54,12 +56,39 @@ const SegmentHeader& need_header(const csdr_archive* ar, const char* name, const
     return *h;
 }
 
+// Device image of a shared-dictionary resource segment (kSharedDictFormat), uploaded once and
+// shared by every tensor coded against it.
+const csdr_dictionary* dictionary_of(csdr_archive* ar, const std::string& name, const std::string& user) {
+    auto it = ar->dicts.find(name);
+    if (it != ar->dicts.end()) return it->second;
+    const SegmentHeader* dh = ar->index.find(name);
+    if (!dh) throw Error(CSDR_ERR_NOT_FOUND, "shared dictionary '" + name + "' named by segment '" + user + "' is not in the archive");
+    if (dh->strategy_id != 0 || dh->data_format != kSharedDictFormat)
+        throw Error(CSDR_ERR_FORMAT, "segment '" + name + "' is not a shared-dictionary resource (stored raw, data_format hsdr_dict)");
+    const std::vector<uint8_t> bytes = ar->index.read_payload(*dh);
+    const HsdaDictionary d = parse_dictionary_record(bytes.data(), bytes.size(), "shared dictionary");
+    csdr_dictionary* dict = nullptr;
+    rethrow_last(csdr_dictionary_create(ar->ctx, d.tile_rows, d.tile_cols, d.n_atoms, d.n_stages, d.k_per_stage, d.atoms.data(),
+                                        d.scales.data(), &dict));
+    ar->dicts.emplace(name, dict);
+    return dict;
+}
+
 const csdr_segment* image_of(csdr_archive* ar, const SegmentHeader& h) {
     auto it = ar->images.find(h.name);
     if (it != ar->images.end()) return it->second;
     const std::vector<uint8_t> bytes = ar->index.read_payload(h);
     csdr_segment* seg = nullptr;
-    rethrow_last(csdr_segment_create(ar->ctx, bytes.data(), bytes.size(), &seg));
+    if (bytes.size() >= 4 && std::memcmp(bytes.data(), "HSDC", 4) == 0) {
+        // codes only: the dictionary is a resource segment of this archive, named behind "hsdc@"
+        const size_t plen = std::strlen(kSharedCodesPrefix);
+        if (h.data_format.compare(0, plen, kSharedCodesPrefix) != 0 || h.data_format.size() == plen)
+            throw Error(CSDR_ERR_FORMAT, "segment '" + h.name + "' holds codes only but names no shared dictionary (data_format hsdc@<segment>)");
+        const csdr_dictionary* dict = dictionary_of(ar, h.data_format.substr(plen), h.name);
+        rethrow_last(csdr_segment_create_shared(ar->ctx, bytes.data(), bytes.size(), dict, &seg));
+    } else {
+        rethrow_last(csdr_segment_create(ar->ctx, bytes.data(), bytes.size(), &seg));
+    }
     ar->images.emplace(h.name, seg);
     return seg;
 }
@@ -185,6 +214,8 @@ int csdr_archive_release(csdr_archive* ar, const char* name) {
         if (!name) {
             for (auto& kv : ar->images) csdr_segment_destroy(kv.second);
             ar->images.clear();
+            for (auto& kv : ar->dicts) csdr_dictionary_destroy(kv.second);
+            ar->dicts.clear();
             ar->raw.clear();
             return;
         }
@@ -201,10 +232,14 @@ int csdr_archive_resident_bytes(const csdr_archive* ar, size_t* bytes) {
     return guard([&] {
         if (!ar || !bytes) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
         size_t n = 0;
+        std::unordered_map<const void*, size_t> dictionaries;   // a shared dictionary counts once
         for (const auto& kv : ar->images) {
             const csdr_segment* sg = kv.second;
-            n += sg->atoms->bytes + sg->codes->bytes + sg->scales->bytes + (sg->edges ? sg->edges->bytes : 0);
+            dictionaries[sg->atoms->ptr] = sg->atoms->bytes;
+            n += sg->codes->bytes + sg->scales->bytes + (sg->edges ? sg->edges->bytes : 0);
         }
+        for (const auto& kv : ar->dicts) dictionaries[kv.second->atoms->ptr] = kv.second->atoms->bytes;
+        for (const auto& kv : dictionaries) n += kv.second;
         for (const auto& kv : ar->raw) n += kv.second->bytes;
         *bytes = n;
     });

@@ -195,6 +195,42 @@ std::vector<uint8_t> ArchiveIndex::read_payload(const SegmentHeader& h) const {
     return bytes;
 }
 
+HsdaDictionary parse_dictionary_record(const uint8_t* p, size_t n, const char* what) {
+    const std::string w(what);
+    size_t off = 0;
+    auto need = [&](size_t bytes) {
+        if (bytes > n - off) throw Error(CSDR_ERR_FORMAT, w + ": unexpected end of dictionary record");
+    };
+    HsdaDictionary d;
+    need(20);
+    d.tile_rows = rd<uint16_t>(p + 0);
+    d.tile_cols = rd<uint16_t>(p + 2);
+    d.n_atoms = rd<uint16_t>(p + 4);
+    d.n_stages = p[6];
+    d.k_per_stage = p[7];
+    d.ksvd_iters = p[8];
+    d.stage_decay = rd<float>(p + 12);
+    d.max_tiles_for_fit = rd<uint32_t>(p + 16);
+    off = 20;
+    need(4);
+    const uint32_t n_scales = rd<uint32_t>(p + off);
+    off += 4;
+    if (n_scales != d.n_stages) throw Error(CSDR_ERR_FORMAT, w + ": dictionary arrays do not match its config");
+    need(4ull * n_scales);
+    d.scales.resize(n_scales);
+    std::memcpy(d.scales.data(), p + off, 4ull * n_scales);
+    off += 4ull * n_scales;
+    need(4);
+    const uint32_t n_atom_floats = rd<uint32_t>(p + off);
+    off += 4;
+    if (static_cast<uint64_t>(n_atom_floats) != static_cast<uint64_t>(d.n_atoms) * d.tile_rows * d.tile_cols)
+        throw Error(CSDR_ERR_FORMAT, w + ": dictionary arrays do not match its config");
+    need(4ull * n_atom_floats);
+    d.atoms.resize(n_atom_floats);
+    std::memcpy(d.atoms.data(), p + off, 4ull * n_atom_floats);
+    return d;
+}
+
 HsdaFile HsdaFile::open(const std::string& path) {
     std::ifstream in(path, std::ios::binary);
     if (!in) throw Error(CSDR_ERR_IO, "HSDA readFromFile: cannot open " + path);

@@ -66,6 +66,23 @@ struct HsdaDictionary {
     uint32_t max_tiles_for_fit = 0;
     std::vector<float> scales, atoms;
 };
+// One dictionary record as a .hsda holds it (raw config, u32 count + stage scales, u32 count +
+// atoms), from memory; `what` prefixes the error text. Also the payload of a shared-dictionary
+// resource segment inside a .sdr (see kSharedDictFormat).
+HsdaDictionary parse_dictionary_record(const uint8_t* p, size_t n, const char* what);
+
+// Shared dictionaries inside a .sdr. The reference keeps them in a container of their own
+// (.hsda) because its archive has no "shared resources" section
+// (ai_compression_cli.cpp:727-733, strategies/HierarchicalSDRStrategy.hpp:303-308). The
+// convention read here needs no new section, only index fields the archive already has:
+//   * a dictionary is an ordinary segment stored raw (strategy 0) whose data_format is
+//     "hsdr_dict" and whose payload is one .hsda dictionary record;
+//   * a tensor coded against it is an HSDR segment (strategy 5) whose payload is a codes-only
+//     "HSDC" stream and whose data_format is "hsdc@" + the dictionary segment's name.
+// The reference's index reader opens such an archive unchanged (it cannot run those tensors).
+constexpr const char* kSharedDictFormat = "hsdr_dict";
+constexpr const char* kSharedCodesPrefix = "hsdc@";
+
 struct HsdaSegment {
     std::string name;
     uint32_t dict_index = 0;

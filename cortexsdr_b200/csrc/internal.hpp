@@ -118,6 +118,7 @@ struct csdr_context {
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool gemv_queue = true;  // CSDR_GEMV_QUEUE=0 keeps lists of products on single and grouped launches
     bool cache_2d = true;            // CSDR_CACHE_2D=0: wide batches on 2-D tiles stay on the factored CUDA-core kernels
+    bool decoder_fold = true;        // CSDR_DECODER_FOLD=0: norms, residuals and SwiGLU of a short decoder step as kernels of their own
     bool decoder_queue = false;      // CSDR_DECODER_QUEUE=1: decoder steps of up to four tokens run a block as three launches
     bool gemv_queue_single = false;  // CSDR_GEMV_QUEUE_SINGLE=1 sends single products of at most 4 tokens there too
     bool pdl = true;         // CSDR_PDL=0 launches without programmatic dependent launch
@@ -126,7 +127,6 @@ struct csdr_context {
     size_t tc_min_batch = 8;    // CSDR_TC_MIN_BATCH: smallest batch sent to the tcgen05 path
     // Per-device launch facts, remembered per context (function attributes and occupancy belong
     // to a device; a process may hold contexts on several).
-    std::unordered_map<const void*, size_t> smem_optins;              // kernel -> dynamic smem opted into
     void opt_in_smem(const void* kernel, size_t bytes);               // raises the opt-in when bytes needs it
     std::unordered_map<const void*, std::pair<size_t, int>> occupancy; // kernel -> (smem asked, CTAs per SM)
     bool tma_attrs_set = false;

@@ -180,9 +180,17 @@ add_rmsnorm_kernel(float* __restrict__ hidden, const float* __restrict__ delta,
 
 // grid (tokens); rotates q in place, writes rotated k and plain v into the cache slot
 // (seq_of[t], pos_of[t]). q (T, QH, HD); k, v (T, KVH, HD); caches (B, max_seq, KVH, HD).
+template <typename KV>
+__device__ __forceinline__ KV to_kv(float v);
+template <>
+__device__ __forceinline__ float to_kv<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_kv<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename KV>
 __global__ void __launch_bounds__(256)
 rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                  float* __restrict__ kc, float* __restrict__ vc, const int32_t* __restrict__ seq_of,
+                  KV* __restrict__ kc, KV* __restrict__ vc, const int32_t* __restrict__ seq_of,
                   const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t HD,
                   uint32_t max_seq, float theta) {
     pdl_enter();
@@ -210,8 +218,8 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
             const uint32_t kh = head - QH;
             const float* b = kt + kh * HD + i;
             const float x0 = b[0], x1 = b[1];
-            kc[slot + kh * HD + i] = x0 * c - x1 * s;
-            kc[slot + kh * HD + i + 1] = x0 * s + x1 * c;
+            kc[slot + kh * HD + i] = to_kv<KV>(x0 * c - x1 * s);
+            kc[slot + kh * HD + i + 1] = to_kv<KV>(x0 * s + x1 * c);
         }
     };
     auto angle_of = [&](uint32_t i, float& c, float& s) {
@@ -239,8 +247,8 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
         const uint32_t kv0 = h0 > QH ? h0 - QH : 0u, kv1 = h1 > QH ? h1 - QH : 0u;
         if (HD & 1u)
             for (uint32_t kh = kv0 + threadIdx.x; kh < kv1; kh += 256)
-                kc[slot + kh * HD + HD - 1] = kt[kh * HD + HD - 1];
-        for (uint32_t e = kv0 * HD + threadIdx.x; e < kv1 * HD; e += 256) vc[slot + e] = vt[e];
+                kc[slot + kh * HD + HD - 1] = to_kv<KV>(kt[kh * HD + HD - 1]);
+        for (uint32_t e = kv0 * HD + threadIdx.x; e < kv1 * HD; e += 256) vc[slot + e] = to_kv<KV>(vt[e]);
     }
 }
 
@@ -273,17 +281,59 @@ __device__ __forceinline__ void load_row(const float* p, float (&v)[VPL]) {
     }
 }
 
+// A lane's share of one cache row. fp32 cache: the values. bf16 cache (an option; sums stay fp32):
+// the packed words, widened where they are used (a bf16 is the upper half of its fp32), and twice
+// the keys per step so that a warp keeps as many bytes in flight.
+template <typename KV, int VPL>
+struct CacheRow;
+template <int VPL>
+struct CacheRow<float, VPL> {
+    float v[VPL];
+    __device__ __forceinline__ void load(const float* p) { load_row<VPL>(p, v); }
+    __device__ __forceinline__ float get(int e) const { return v[e]; }
+};
+template <int VPL>
+struct CacheRow<__nv_bfloat16, VPL> {
+    uint32_t w[(VPL + 1) / 2];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+        if constexpr (VPL == 1) {
+            w[0] = __ldg(reinterpret_cast<const unsigned short*>(p));
+        } else if constexpr (VPL == 2) {
+            w[0] = __ldg(reinterpret_cast<const uint32_t*>(p));
+        } else if constexpr (VPL == 4) {
+            const uint2 t = __ldg(reinterpret_cast<const uint2*>(p));
+            w[0] = t.x;
+            w[1] = t.y;
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPL / 8; ++i) {
+                const uint4 t = __ldg(reinterpret_cast<const uint4*>(p) + i);
+                w[4 * i] = t.x;
+                w[4 * i + 1] = t.y;
+                w[4 * i + 2] = t.z;
+                w[4 * i + 3] = t.w;
+            }
+        }
+    }
+    __device__ __forceinline__ float get(int e) const {
+        const uint32_t x = w[e >> 1];
+        if constexpr (VPL == 1) return __uint_as_float(x << 16);
+        return __uint_as_float((e & 1) ? (x & 0xFFFF0000u) : (x << 16));
+    }
+};
+
 // WARPS warps split the keys of one (token, head); few (token, head) pairs (batched decode
 // against a long context) take more warps each so that enough K/V rows are in flight per SM.
-template <int VPL, int kAttnWarps>
+template <typename KV, int VPL, int kAttnWarps>
 __global__ void __launch_bounds__(kAttnWarps * 32)
-attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
-                 const float* __restrict__ vc, const int32_t* __restrict__ seq_of,
+attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
+                 const KV* __restrict__ vc, const int32_t* __restrict__ seq_of,
                  const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t max_seq,
                  float scale, float* __restrict__ out, __nv_bfloat16* __restrict__ hi,
                  __nv_bfloat16* __restrict__ lo) {
     pdl_enter();
     constexpr uint32_t HD = VPL * 32u;
+    constexpr int kKeys = kAttnKeys * static_cast<int>(sizeof(float) / sizeof(KV));
     __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps];
     __shared__ float sm_acc[kAttnWarps][HD];
     const uint32_t t = blockIdx.x, h = blockIdx.y;
@@ -297,28 +347,28 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
 #pragma unroll
     for (int e = 0; e < VPL; ++e) acc[e] = 0.0f;
     float m = -INFINITY, l = 0.0f;
-    for (int32_t j0 = warp * kAttnKeys; j0 < n_keys; j0 += kAttnWarps * kAttnKeys) {
-        float kv[kAttnKeys][VPL], vv[kAttnKeys][VPL];
+    for (int32_t j0 = warp * kKeys; j0 < n_keys; j0 += kAttnWarps * kKeys) {
+        CacheRow<KV, VPL> kv[kKeys], vv[kKeys];
 #pragma unroll
-        for (int u = 0; u < kAttnKeys; ++u) {
+        for (int u = 0; u < kKeys; ++u) {
             const int32_t j = min(j0 + u, n_keys - 1);   // clamp: the tail re-reads the last row, unused
-            load_row<VPL>(kc + base + static_cast<size_t>(j) * row, kv[u]);
-            load_row<VPL>(vc + base + static_cast<size_t>(j) * row, vv[u]);
+            kv[u].load(kc + base + static_cast<size_t>(j) * row);
+            vv[u].load(vc + base + static_cast<size_t>(j) * row);
         }
-        float s[kAttnKeys];
+        float s[kKeys];
 #pragma unroll
-        for (int u = 0; u < kAttnKeys; ++u) {
+        for (int u = 0; u < kKeys; ++u) {
             float d = 0.0f;
 #pragma unroll
-            for (int e = 0; e < VPL; ++e) d = fmaf(qv[e], kv[u][e], d);
+            for (int e = 0; e < VPL; ++e) d = fmaf(qv[e], kv[u].get(e), d);
             s[u] = d;
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1)
 #pragma unroll
-            for (int u = 0; u < kAttnKeys; ++u) s[u] += __shfl_xor_sync(0xFFFFFFFFu, s[u], off);
+            for (int u = 0; u < kKeys; ++u) s[u] += __shfl_xor_sync(0xFFFFFFFFu, s[u], off);
 #pragma unroll
-        for (int u = 0; u < kAttnKeys; ++u) {
+        for (int u = 0; u < kKeys; ++u) {
             if (j0 + u < n_keys) {
                 const float sc = s[u] * scale;
                 const float m_new = fmaxf(m, sc);
@@ -326,7 +376,7 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ kc,
                 const float p = expf(sc - m_new);
                 l = l * corr + p;
 #pragma unroll
-                for (int e = 0; e < VPL; ++e) acc[e] = fmaf(p, vv[u][e], acc[e] * corr);
+                for (int e = 0; e < VPL; ++e) acc[e] = fmaf(p, vv[u].get(e), acc[e] * corr);
                 m = m_new;
             }
         }
@@ -528,18 +578,22 @@ void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const 
     ls.done("add_rmsnorm_kernel");
 }
 
-void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, float* kc, float* vc,
+void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, void* kc, void* vc, int kv_dtype,
                    const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
                    uint32_t HD, uint32_t max_seq, float theta) {
     LaunchScope ls(ctx, KC_DECODER_OP);
     // slices of the heads per token: enough CTAs for a decode step, one for a long prefill
     const uint32_t slices = T >= 256u ? 1u : std::min<uint32_t>(QH + KVH, std::max(1u, 256u / std::max(T, 1u)));
-    launch_pdl(ctx, rope_cache_kernel, dim3(T, std::min(slices, 16u)), dim3(256), q, k, v, kc, vc, seq_of, pos_of, QH, KVH, HD,
-               max_seq, theta);
+    if (kv_dtype == CSDR_DTYPE_BF16)
+        launch_pdl(ctx, rope_cache_kernel<__nv_bfloat16>, dim3(T, std::min(slices, 16u)), dim3(256), q, k, v,
+                   static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), seq_of, pos_of, QH, KVH, HD, max_seq, theta);
+    else
+        launch_pdl(ctx, rope_cache_kernel<float>, dim3(T, std::min(slices, 16u)), dim3(256), q, k, v, static_cast<float*>(kc),
+                   static_cast<float*>(vc), seq_of, pos_of, QH, KVH, HD, max_seq, theta);
     ls.done("rope_cache_kernel");
 }
 
-void op_attention(csdr_context* ctx, const float* q, const float* kc, const float* vc,
+void op_attention(csdr_context* ctx, const float* q, const void* kc, const void* vc, int kv_dtype,
                   const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
                   uint32_t HD, uint32_t max_seq, float* out, __nv_bfloat16* hi, __nv_bfloat16* lo) {
     if (HD % 32u || HD > 256u || HD == 96u || HD == 160u || HD == 192u || HD == 224u)
@@ -550,9 +604,16 @@ void op_attention(csdr_context* ctx, const float* q, const float* kc, const floa
     const uint32_t pairs = T * QH;
     const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
     const int warps = pairs >= sms * 8u ? 4 : pairs >= sms * 4u ? 8 : 16;
-#define CSDR_ATTN(V, W)                                                                                         \
-    launch_pdl(ctx, attention_kernel<V, W>, grid, dim3(W * 32), q, kc, vc, seq_of, pos_of, QH, KVH, max_seq, scale, \
-               out, hi, lo)
+#define CSDR_ATTN(V, W)                                                                                              \
+    do {                                                                                                             \
+        if (kv_dtype == CSDR_DTYPE_BF16)                                                                             \
+            launch_pdl(ctx, attention_kernel<__nv_bfloat16, V, W>, grid, dim3(W * 32), q,                            \
+                       static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), seq_of, pos_of, \
+                       QH, KVH, max_seq, scale, out, hi, lo);                                                        \
+        else                                                                                                         \
+            launch_pdl(ctx, attention_kernel<float, V, W>, grid, dim3(W * 32), q, static_cast<const float*>(kc),     \
+                       static_cast<const float*>(vc), seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo);         \
+    } while (0)
 #define CSDR_ATTN_W(V)                     \
     do {                                   \
         if (warps == 4) CSDR_ATTN(V, 4);   \

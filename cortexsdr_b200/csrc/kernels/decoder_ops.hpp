@@ -25,10 +25,11 @@ void op_norm_from_sumsq(csdr_context* ctx, const float* x, const float* w, const
                         uint32_t H, uint32_t full_width, float eps, float* out);
 void op_add_rmsnorm(csdr_context* ctx, float* hidden, const float* delta, const float* w, uint32_t T,
                     uint32_t H, float eps, float* out);
-void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, float* kc, float* vc,
+// kc, vc: the layer's cache, fp32 or bf16 as kv_dtype (CSDR_DTYPE_*) says.
+void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, void* kc, void* vc, int kv_dtype,
                    const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
                    uint32_t HD, uint32_t max_seq, float theta);
-void op_attention(csdr_context* ctx, const float* q, const float* kc, const float* vc, const int32_t* seq_of,
+void op_attention(csdr_context* ctx, const float* q, const void* kc, const void* vc, int kv_dtype, const int32_t* seq_of,
                   const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH, uint32_t HD, uint32_t max_seq,
                   float* out, __nv_bfloat16* hi = nullptr, __nv_bfloat16* lo = nullptr);
 void op_silu_mul(csdr_context* ctx, const float* gate, const float* up, size_t n, float* out);

@@ -60,6 +60,9 @@ struct FusedParams {
     int* status;
     uint32_t spin_limit;
     unsigned long long* trace;  // optional: 16 global-timer stamps per CTA (phase boundaries)
+    const float* norm_w;    // y = W rmsnorm(x; norm_w, norm_eps); needs the whole x per CTA
+    float norm_eps;
+    uint32_t swiglu;        // segment 1's rows leave as silu(segment 0's row) * row
 };
 
 __device__ __forceinline__ void stamp(const FusedParams& p, int slot) {
@@ -241,9 +244,38 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
     // ---- phase A ----
     float* xs = reinterpret_cast<float*>(smem_raw);
     const float4* xs4 = reinterpret_cast<const float4*>(xs);
-    if (whole_x && blockIdx.x < p.n_tasks) {
+    __shared__ float ssq_s[kThreads / 32][MT];
+    __shared__ float inv_s[MT];
+    if (whole_x && (blockIdx.x < p.n_tasks || (p.norm_w && gathers))) {
         stage_x<MT>(p.x, 0, p.C, p.C, xs);
         __syncthreads();
+        if (p.norm_w) {
+            // rms_norm (api/cortex_sdk.cpp:1208-1232) split in two: the weights go onto the staged row
+            // here, 1 / rms onto the gathered rows; every CTA sums the squares of the whole row
+            float4* xw = reinterpret_cast<float4*>(xs);
+            const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+#pragma unroll
+            for (int b = 0; b < MT; ++b) {
+                float ss = 0.0f;
+                for (uint32_t c4 = tid; c4 < xcols4; c4 += kThreads) {
+                    const float4 v = xw[b * xcols4 + c4];
+                    const float4 w = __ldg(w4 + c4);
+                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+                    xw[b * xcols4 + c4] = make_float4(v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+                if (lane == 0) ssq_s[warp][b] = ss;
+            }
+            __syncthreads();
+            if (tid < MT) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kThreads / 32; ++w) ss += ssq_s[w][tid];
+                inv_s[tid] = 1.0f / sqrtf(ss / static_cast<float>(p.C) + p.norm_eps);
+            }
+            __syncthreads();
+        }
     }
     stamp(p, 3);
     float acc[A][MT];
@@ -399,8 +431,16 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
                 const uint32_t tok = tg * MTG + b;
                 if (tok < sg.y.M) {
                     const uint32_t r = row0 + rl;
+                    if (p.norm_w) accr *= inv_s[tok];
                     if (sg.y.bias) accr += sg.y.bias[r];
-                    sg.y.y[y_index(sg.y, r, tok)] = accr;
+                    const size_t yi = y_index(sg.y, r, tok);
+                    if (p.swiglu && si == 1u) {
+                        // silu_mul (api/cortex_sdk.cpp:1245-1256); this thread wrote the gate row itself
+                        const float gv = p.seg[0].y.y[yi];
+                        accr = (gv * (1.0f / (1.0f + expf(-gv)))) * accr;
+                    }
+                    if (sg.y.residual) accr += sg.y.residual[yi];
+                    sg.y.y[yi] = accr;
                 }
             }
         }
@@ -445,13 +485,16 @@ void launch_t(csdr_context* ctx, FusedParams& p, uint32_t max_k, bool pdl) {
         occ.first = smem;
     }
     const int occ_cached = occ.second;
-    if (occ_cached < 1) throw Error(CSDR_ERR_LIMIT, "fused GEMV does not fit on an SM");
+    if (occ_cached < 1)
+        throw Error(CSDR_ERR_LIMIT, "fused GEMV does not fit on an SM (token tile " + std::to_string(MT) + ", " +
+                                        std::to_string(smem) + " bytes of shared memory, " + std::to_string(p.n_seg) + " segments)");
     // Every CTA must be resident for the barrier: at most what one otherwise idle GPU holds.
     const uint32_t grid = static_cast<uint32_t>(ctx->sm_count) * static_cast<uint32_t>(std::min(occ_cached, 2));
     p.gather_ctas = std::max(token_groups, std::min(want_gather, grid) / token_groups * token_groups);
     plan_for(p.gather_ctas);  // never larger than the size computed above
-    // whole-x residency only pays when a CTA walks several column slabs
-    if (plan.xcols == p.C && p.n_tasks <= grid && p.slab < p.C) {
+    // whole-x residency only pays when a CTA walks several column slabs (the folded normalisation
+    // needs it regardless: every CTA sums the squares of the whole row)
+    if (!p.norm_w && plan.xcols == p.C && p.n_tasks <= grid && p.slab < p.C) {
         plan.xcols = p.slab;
     }
     cudaLaunchConfig_t cfg{};
@@ -482,10 +525,27 @@ bool gemv_fused_supported(const csdr_context* ctx, const csdr_segment* const* se
     return true;
 }
 
+bool gemv_fused_glue_supported(const csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, uint32_t mt,
+                               const FusedGlue& glue) {
+    if (!gemv_fused_supported(ctx, segs, n, mt)) return false;
+    if (glue.norm_w && static_cast<size_t>(mt) * segs[0]->g.cols * 4u > 64u * 1024u) return false;
+    if (glue.swiglu && (n != 2u || segs[0]->g.rows != segs[1]->g.rows)) return false;
+    return true;
+}
+
 void launch_gemv_fused(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const void* x,
                        int x_dtype, int x_layout, uint32_t m_total, uint32_t b0, uint32_t m,
-                       float* const* ys, int y_layout, const float* const* biases, int mt) {
+                       float* const* ys, int y_layout, const float* const* biases, int mt, const FusedGlue* glue) {
     FusedParams p{};
+    if (glue) {
+        if (!gemv_fused_glue_supported(ctx, segs, n, static_cast<uint32_t>(mt), *glue))
+            throw Error(CSDR_ERR_UNSUPPORTED, "fused GEMV: the folded glue does not fit this launch");
+        if ((glue->norm_w && reinterpret_cast<uintptr_t>(glue->norm_w) % 16u) || (glue->norm_w && x_dtype != CSDR_DTYPE_F32))
+            throw Error(CSDR_ERR_INVALID_ARG, "fused GEMV: folded normalisation wants fp32 activations and 16-byte aligned weights");
+        p.norm_w = glue->norm_w;
+        p.norm_eps = glue->norm_eps;
+        p.swiglu = glue->swiglu ? 1u : 0u;
+    }
     const Geometry& g0 = segs[0]->g;
     const uint32_t C = g0.cols;
     // Column slabs of about 1024 floats, each a multiple of 4 (128-bit loads).
@@ -511,7 +571,7 @@ void launch_gemv_fused(csdr_context* ctx, const csdr_segment* const* segs, uint3
         s.k = g.k;
         s.task0 = task;
         s.part_off = part_off;
-        s.y = YView{ys[i], y_layout, g.rows, m_total, b0, m, biases ? biases[i] : nullptr};
+        s.y = YView{ys[i], y_layout, g.rows, m_total, b0, m, biases ? biases[i] : nullptr, glue ? glue->residual[i] : nullptr};
         task += ((g.n_atoms + 8u * A - 1u) / (8u * A)) * nsplit;
         part_off += nsplit * g.n_atoms * mt;
         max_rows = std::max(max_rows, g.rows);

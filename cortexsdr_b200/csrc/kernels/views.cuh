@@ -45,6 +45,7 @@ struct YView {
     uint32_t b0;
     uint32_t M;
     const float* bias;
+    const float* residual = nullptr;   // added behind the product, indexed like y (may be y itself)
 };
 
 __device__ __forceinline__ size_t y_index(const YView& v, uint32_t r, uint32_t b) {

@@ -410,6 +410,10 @@ typedef struct {
      * tp_size == 1 means no sharding. comm is an ncclComm_t (void*) or NULL. */
     uint32_t tp_rank, tp_size;
     void* nccl_comm;
+    /* KV cache element type: CSDR_DTYPE_F32 (0, default: the reference's arithmetic) or
+     * CSDR_DTYPE_BF16 (keys and values rounded to bf16 when they enter the cache, scores and
+     * sums in fp32; half the cache bytes per step). No counterpart in the reference. */
+    uint32_t kv_dtype;
 } csdr_decoder_config;
 
 CSDR_API int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg,

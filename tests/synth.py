@@ -12,7 +12,7 @@ import struct
 
 import numpy as np
 
-SEG_WEIGHTS_FP32, SEG_ATTENTION, SEG_FEED_FORWARD, SEG_EMBEDDING, SEG_LAYER_NORM = 1, 11, 12, 13, 14
+SEG_WEIGHTS_FP32, SEG_CONFIG, SEG_ATTENTION, SEG_FEED_FORWARD, SEG_EMBEDDING, SEG_LAYER_NORM = 1, 10, 11, 12, 13, 14
 
 
 def hsdr_payload(rows: int, cols: int, *, tile_rows: int = 1, tile_cols: int | None = None,
@@ -200,20 +200,64 @@ def _pack_q6_k(w: np.ndarray) -> np.ndarray:
     return out.reshape(-1)
 
 
+def dictionary_record(atoms: np.ndarray, scales: np.ndarray, *, tile_rows: int, tile_cols: int, k: int,
+                      decay: float = 0.5) -> bytes:
+    """One dictionary as a .hsda holds it (SharedDictArchive::writeToStream,
+    strategies/HierarchicalSDRStrategy.cpp:1972-2002): the 20-byte raw HierarchicalSDRConfig, then
+    counted stage scales and atoms. Also the payload of a shared-dictionary resource segment."""
+    n_atoms, n_stages = atoms.shape[0], len(scales)
+    cfg = struct.pack("<HHHBBBxxxfI", tile_rows, tile_cols, n_atoms, n_stages, k, 0, decay, 0)
+    assert len(cfg) == 20
+    return (cfg + struct.pack("<I", n_stages) + np.asarray(scales, np.float32).tobytes()
+            + struct.pack("<I", atoms.size) + np.ascontiguousarray(atoms, np.float32).tobytes())
+
+
+def read_dictionary_record(b: bytes):
+    """Inverse of dictionary_record: (tile_rows, tile_cols, n_atoms, n_stages, k, atoms, scales)."""
+    b = bytes(b)
+    tile_rows, tile_cols, n_atoms, n_stages, k = struct.unpack_from("<HHHBB", b, 0)
+    (n_scales,) = struct.unpack_from("<I", b, 20)
+    scales = np.frombuffer(b, np.float32, n_scales, 24).copy()
+    (n_floats,) = struct.unpack_from("<I", b, 24 + 4 * n_scales)
+    atoms = np.frombuffer(b, np.float32, n_floats, 28 + 4 * n_scales).reshape(n_atoms, tile_rows * tile_cols).copy()
+    return tile_rows, tile_cols, n_atoms, n_stages, k, atoms, scales
+
+
+SHARED_DICT_FORMAT = "hsdr_dict"
+
+
 def decoder_archive(path: str, *, n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab, seed=100,
-                    geometry="row", n_atoms=512, k=8, kv_atoms=None, raw=None) -> None:
+                    geometry="row", n_atoms=512, k=8, kv_atoms=None, raw=None, shared_dicts=False) -> None:
     """A decoder-shaped .sdr with the reference's GGUF-style tensor names
     (api/cortex_sdk.cpp:456-524): every linear an HSDR segment, norm vectors stored raw.
     `raw` maps tensor names to a source dtype ("f32", "f16", "bf16", "q8_0"): those linears are
     stored uncompressed (strategy 0) in that dtype instead, as a converter leaves protected or
-    unsuitable tensors."""
+    unsuitable tensors. `shared_dicts`: the seven block roles (attn_q ... ffn_down) each share ONE
+    dictionary over all blocks - a resource segment "hsdr.shared_dict/<role>" (stored raw,
+    data_format "hsdr_dict", one .hsda dictionary record) and per block a codes-only "HSDC"
+    payload whose data_format names it ("hsdc@hsdr.shared_dict/<role>")."""
     segs, sd = [], seed
     kw = dict(n_atoms=n_atoms, k=k)
     raw = raw or {}
+    role_dicts = {}
 
     def lin(name, r, c, t, li, atoms=None):
         nonlocal sd
         sd += 1
+        role = name.split(".")[2] if name.startswith("blk.") else None
+        if shared_dicts and role and name not in raw and geometry == "row":
+            K = atoms or n_atoms
+            dname = f"hsdr.shared_dict/{role}"
+            if role not in role_dicts:
+                d_atoms, d_scales = shared_dictionary(1, c, n_atoms=K, k=k, seed=seed + 7919 * (len(role_dicts) + 1))
+                role_dicts[role] = dname
+                segs.append(dict(name=dname, payload=dictionary_record(d_atoms, d_scales, tile_rows=1, tile_cols=c, k=k),
+                                 strategy_id=0, original_type=SEG_CONFIG, dims=(K, c), original_size=d_atoms.nbytes,
+                                 data_format=SHARED_DICT_FORMAT, layer_type="", layer_index=0))
+            pay = hsdc_payload(r, c, tile_rows=1, tile_cols=c, n_atoms=K, k=k, seed=sd)
+            segs.append(dict(name=name, payload=pay, strategy_id=5, original_type=t, dims=(r, c), original_size=r * c * 4,
+                             data_format="hsdc@" + dname, layer_index=li))
+            return
         if name in raw:
             w = np.random.default_rng(sd).normal(0, 0.02, (r, c)).astype(np.float32)
             fmt = raw[name]

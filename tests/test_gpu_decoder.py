@@ -17,16 +17,25 @@ LOGIT_TOL = 2e-2
 CFG = dict(n_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=32, inter=256, vocab=300)
 
 
-def _build_model(tmp_path_factory, oracle, tag, raw_formats=None, CFG=CFG, k=3, **atoms):
+def _build_model(tmp_path_factory, oracle, tag, raw_formats=None, CFG=CFG, k=3, shared_dicts=False, **atoms):
     path = str(tmp_path_factory.mktemp("dec") / f"{tag}.sdr")
     raw_formats = raw_formats or {}
-    synth.decoder_archive(path, **CFG, k=k, seed=7, raw=raw_formats, **atoms)
+    synth.decoder_archive(path, **CFG, k=k, seed=7, raw=raw_formats, shared_dicts=shared_dicts, **atoms)
     ld = cs.SDRModelLoader(path, index_only=True)
     shapes = {"token_embd.weight": (CFG["vocab"], CFG["hidden"]), "output.weight": (CFG["vocab"], CFG["hidden"])}
+    dictionaries = {}
 
     def dense(n):
         if n not in raw_formats:
-            return oracle.decompress(ld.loadCompressedBytesByName(n))
+            payload = ld.loadCompressedBytesByName(n)
+            if bytes(payload[:4]) == b"HSDC":
+                # codes only: the dictionary is the resource segment the header's data_format names
+                dname = ld.findSegmentHeader(n).data_format.split("@", 1)[1]
+                if dname not in dictionaries:
+                    from oracle.bindings import SharedDict
+                    dictionaries[dname] = SharedDict(*synth.read_dictionary_record(ld.loadSegmentByName(dname)))
+                return oracle.hsdc_decompress(payload, dictionaries[dname])
+            return oracle.decompress(payload)
         data = ld.loadSegmentByName(n)                       # stored raw: widen like the reference does
         fmt = raw_formats[n]
         # widened as the reference's inference side does it: ggml's element order for block formats
@@ -58,6 +67,11 @@ def _build_model(tmp_path_factory, oracle, tag, raw_formats=None, CFG=CFG, k=3, 
 @pytest.fixture(scope="module")
 def model(tmp_path_factory, oracle):
     return _build_model(tmp_path_factory, oracle, "tiny", n_atoms=32, kv_atoms=16)
+
+
+@pytest.fixture(scope="module")
+def model_shared(tmp_path_factory, oracle):
+    return _build_model(tmp_path_factory, oracle, "shared", shared_dicts=True, n_atoms=32, kv_atoms=16)
 
 
 @pytest.fixture(scope="module")
@@ -115,6 +129,48 @@ def test_stored_raw_source_dtypes_are_widened_on_the_device(ctx, oracle, model_r
     assert np.abs(lg[0] - want).max() < LOGIT_TOL and int(nxt[0]) == int(want.argmax())
 
 
+def test_shared_dictionaries_inside_the_archive(ctx, oracle, model_shared):
+    """An .sdr whose seven block roles each share one dictionary over all blocks: the dictionary a
+    resource segment (stored raw, data_format "hsdr_dict", one .hsda dictionary record), every
+    block's tensor a codes-only "HSDC" payload whose data_format names it. The reference has this
+    only as a separate container (.hsda; ai_compression_cli.cpp:727-733 names the missing archive
+    section). Prefill, steps and a product by name against the oracle's external-dictionary
+    decode (decompressWithExternalDictionary, HierarchicalSDRStrategy.cpp:1804-1828)."""
+    path, weights = model_shared
+    ld = cs.SDRModelLoader(path, ctx)
+    hdr = ld.findSegmentHeader("blk.1.ffn_up.weight")
+    assert hdr.data_format == "hsdc@hsdr.shared_dict/ffn_up" and hdr.compression_strategy_id == 5
+    assert ld.findSegmentHeader("hsdr.shared_dict/ffn_up").data_format == "hsdr_dict"
+    # a product by name goes through the shared dictionary
+    x = np.random.default_rng(3).normal(0, 1, (CFG["hidden"], 2)).astype(np.float32)
+    y = ld.matmulHSDR("blk.1.ffn_up.weight", x, 2)
+    want = weights["blocks"][1]["w_up"].astype(np.float64) @ x
+    assert np.abs(y - want).max() / np.abs(want).max() < 1e-4
+    tokens = np.random.default_rng(4).integers(0, CFG["vocab"], 11)
+    _, logits = oracle_forward(oracle, weights, tokens)
+    dec = cs.Decoder(ld, **CFG, max_seq=64, rms_eps=1e-6, rope_theta=1e6)
+    got, _ = dec.forward(tokens)
+    assert np.abs(got - logits).max() < LOGIT_TOL and int(got.argmax()) == int(logits.argmax())
+    seq, nxt = list(tokens), int(got.argmax())
+    for _ in range(2):
+        seq.append(nxt)
+        _, want_l = oracle_forward(oracle, weights, np.array(seq))
+        got_next, got_l = dec.step([nxt], want_logits=True)
+        assert np.abs(got_l[0] - want_l).max() < LOGIT_TOL and int(got_next[0]) == int(want_l.argmax())
+        nxt = int(got_next[0])
+    # the blocks hold two images per role and ONE dictionary: resident bytes count it once
+    per_role = {"attn_q": CFG["hidden"], "attn_k": CFG["hidden"], "attn_v": CFG["hidden"],
+                "attn_output": CFG["q_heads"] * CFG["head_dim"], "ffn_gate": CFG["hidden"], "ffn_up": CFG["hidden"],
+                "ffn_down": CFG["inter"]}
+    atoms = {r: (16 if r in ("attn_k", "attn_v") else 32) for r in per_role}
+    dict_bytes = sum(atoms[r] * c * 4 for r, c in per_role.items())
+    own = 2 * 32 * CFG["hidden"] * 4                      # embedding and head keep dictionaries of their own
+    resident = ld.resident_bytes()
+    assert dict_bytes + own < resident < 2 * dict_bytes + own
+    dec.close()
+    ld.close()
+
+
 def test_kv_cache_equals_recompute(ctx, oracle, model):
     path, weights = model
     tokens = np.random.default_rng(1).integers(0, CFG["vocab"], 12)
@@ -134,6 +190,42 @@ def test_kv_cache_equals_recompute(ctx, oracle, model):
         assert np.abs(got[0] - want).max() < LOGIT_TOL
         assert int(got_next[0]) == int(want.argmax())
         nxt = int(got_next[0])
+
+
+def test_folded_glue_equals_separate_kernels(oracle, model, monkeypatch):
+    """A short step runs its normalisations, residual additions and SwiGLU inside the one-launch
+    GEMVs (six launches per block); CSDR_DECODER_FOLD=0 keeps them as kernels of their own (nine).
+    Both against the oracle, and against each other, for one, three and five tokens per pass."""
+    path, weights = model
+    rng = np.random.default_rng(21)
+    prompt = rng.integers(0, CFG["vocab"], 7)
+    results = {}
+    for fold in ("1", "0"):
+        monkeypatch.setenv("CSDR_DECODER_FOLD", fold)
+        c = cs.Context(0)
+        dec = make_decoder(path, c, max_batch=3)
+        launches0 = c.launch_count
+        lg5, _ = dec.forward(prompt[:5])                     # five tokens: token tile of 8
+        n5 = c.launch_count - launches0
+        lg1, _ = dec.forward(prompt[5:6])                    # one token
+        lg3 = []
+        dec.forward(prompt[:3], seq=1, want_logits=False)    # three tokens: token tile of 4
+        dec.forward(prompt[:2], seq=2, want_logits=False)
+        nxt, step = dec.step([int(prompt[6]), 11, 12], want_logits=True)
+        results[fold] = (lg5, lg1, step, n5)
+        dec.close()
+        c.close()
+    _, want5 = oracle_forward(oracle, weights, prompt[:5])
+    _, want6 = oracle_forward(oracle, weights, prompt[:6])
+    _, want7 = oracle_forward(oracle, weights, prompt[:7])
+    for fold in ("1", "0"):
+        lg5, lg1, step, _ = results[fold]
+        assert np.abs(lg5 - want5).max() < LOGIT_TOL, fold
+        assert np.abs(lg1 - want6).max() < LOGIT_TOL, fold
+        assert np.abs(step[0] - want7).max() < LOGIT_TOL, fold
+    assert np.abs(results["1"][2] - results["0"][2]).max() < 1e-4
+    # per block: 9 launches apart, 6 folded
+    assert results["0"][3] - results["1"][3] == 3 * CFG["n_layers"]
 
 
 def test_batched_step_sequences_are_independent(ctx, oracle, model):
@@ -260,31 +352,61 @@ def model_llama_width(tmp_path_factory, oracle):
     return _build_model(tmp_path_factory, oracle, "llamaw", CFG=LLAMA_W, k=8, n_atoms=512)
 
 
-def test_qwen_width_prefill_and_greedy_steps(ctx, oracle, model_qwen_width):
+_ORACLE_MEMO = {}
+
+
+def oracle_forward_memo(oracle, weights, tokens, CFG):
+    """The oracle's logits for a token sequence, kept so that the fp32- and bf16-cache runs of a
+    test share one CPU recompute."""
+    key = (id(weights), np.asarray(tokens, np.int64).tobytes())
+    if key not in _ORACLE_MEMO:
+        _ORACLE_MEMO[key] = oracle_forward(oracle, weights, tokens, CFG=CFG)
+    return _ORACLE_MEMO[key]
+
+
+# "bf16": the KV cache OPTION (rows rounded to bf16 on entry, scores and sums fp32). It does not meet
+# the fp32 cache's bar of 2e-2 at the 7B widths (observed 2.4e-2), which is why it is not the
+# default; its own bar is 5e-2.
+KV_TOL = {"f32": LOGIT_TOL, "bf16": 5e-2}
+
+
+def same_pick(got, want, tol):
+    """Equal argmax; at the bf16 cache's wider bar, unless the oracle's two best logits are closer
+    than that bar allows to tell."""
+    if int(got.argmax()) == int(want.argmax()):
+        return True
+    top2 = np.partition(want, -2)[-2:]
+    return tol > LOGIT_TOL and float(top2[1] - top2[0]) < 2 * tol
+
+
+@pytest.mark.parametrize("kv_dtype", ["f32", "bf16"])
+def test_qwen_width_prefill_and_greedy_steps(ctx, oracle, model_qwen_width, kv_dtype):
     """Hidden 896, 14 query / 2 kv heads of 64, SwiGLU 4864, vocabulary 151 936, eps 1e-6, k/v
     dictionaries of 128 atoms; two blocks. A 64-token prompt (tensor-core block loop), then
     three greedy steps at batch 1 (fused GEMV path), each against the oracle's whole-sequence
     recompute."""
     path, weights = model_qwen_width
     tokens = np.random.default_rng(7).integers(0, QWEN_W["vocab"], 64)
-    _, logits = oracle_forward(oracle, weights, tokens, CFG=QWEN_W)
-    dec = make_decoder(path, ctx, CFG=QWEN_W, max_seq=80)
+    _, logits = oracle_forward_memo(oracle, weights, tokens, CFG=QWEN_W)
+    dec = make_decoder(path, ctx, CFG=QWEN_W, max_seq=80, kv_dtype=kv_dtype)
     g_logits, _ = dec.forward(tokens)
     assert np.isfinite(g_logits).all()
-    assert np.abs(g_logits - logits).max() < LOGIT_TOL
-    assert int(g_logits.argmax()) == int(logits.argmax())
-    seq, nxt = list(tokens), int(g_logits.argmax())
+    tol = KV_TOL[kv_dtype]
+    assert np.abs(g_logits - logits).max() < tol
+    assert same_pick(g_logits, logits, tol)
+    seq, nxt = list(tokens), int(logits.argmax())
     for _ in range(3):
         seq.append(nxt)
-        _, want = oracle_forward(oracle, weights, np.array(seq), CFG=QWEN_W)
+        _, want = oracle_forward_memo(oracle, weights, np.array(seq), CFG=QWEN_W)
         got_next, got = dec.step([nxt], want_logits=True)
-        assert np.abs(got[0] - want).max() < LOGIT_TOL
-        assert int(got_next[0]) == int(want.argmax())
-        nxt = int(got_next[0])
+        assert np.abs(got[0] - want).max() < tol
+        assert same_pick(got[0], want, tol) and int(got_next[0]) == int(got[0].argmax())
+        nxt = int(want.argmax())
     dec.close()
 
 
-def test_llama_width_batch16_step(ctx, oracle, model_llama_width):
+@pytest.mark.parametrize("kv_dtype", ["f32", "bf16"])
+def test_llama_width_batch16_step(ctx, oracle, model_llama_width, kv_dtype):
     """Hidden 4096, 32 heads of 128, SwiGLU 11 008, vocabulary 32 000; one block. Sixteen
     sequences with real, different, prefilled contexts step together (the 16-token tile of the
     tensor-core projection, the grouped gathers, the batch-16 attention), then step again over
@@ -293,19 +415,20 @@ def test_llama_width_batch16_step(ctx, oracle, model_llama_width):
     rng = np.random.default_rng(8)
     lens = [3, 9, 5, 12, 1, 7, 4, 10, 2, 8, 6, 11, 3, 5, 9, 7]
     prompts = [rng.integers(0, LLAMA_W["vocab"], n) for n in lens]
-    dec = make_decoder(path, ctx, CFG=LLAMA_W, max_seq=32, max_batch=16)
+    dec = make_decoder(path, ctx, CFG=LLAMA_W, max_seq=32, max_batch=16, kv_dtype=kv_dtype)
     for s_, p_ in enumerate(prompts):
         dec.forward(p_, seq=s_, want_logits=False)
     new = rng.integers(0, LLAMA_W["vocab"], 16)
     nxt, lg = dec.step(new, want_logits=True)
     assert np.isfinite(lg).all()
+    tol = KV_TOL[kv_dtype]
     for s_, p_ in enumerate(prompts):
-        _, want = oracle_forward(oracle, weights, np.append(p_, new[s_]), CFG=LLAMA_W)
-        assert np.abs(lg[s_] - want).max() < LOGIT_TOL, s_
-        assert int(nxt[s_]) == int(want.argmax()), s_
+        _, want = oracle_forward_memo(oracle, weights, np.append(p_, new[s_]), CFG=LLAMA_W)
+        assert np.abs(lg[s_] - want).max() < tol, s_
+        assert same_pick(lg[s_], want, tol) and int(nxt[s_]) == int(lg[s_].argmax()), s_
     nxt2, lg2 = dec.step(nxt, want_logits=True)
     for s_ in (0, 3, 15):
-        _, want = oracle_forward(oracle, weights, np.concatenate([prompts[s_], [new[s_]], [nxt[s_]]]), CFG=LLAMA_W)
-        assert np.abs(lg2[s_] - want).max() < LOGIT_TOL, s_
-        assert int(nxt2[s_]) == int(want.argmax()), s_
+        _, want = oracle_forward_memo(oracle, weights, np.concatenate([prompts[s_], [new[s_]], [nxt[s_]]]), CFG=LLAMA_W)
+        assert np.abs(lg2[s_] - want).max() < tol, s_
+        assert same_pick(lg2[s_], want, tol) and int(nxt2[s_]) == int(lg2[s_].argmax()), s_
     dec.close()

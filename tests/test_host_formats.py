@@ -118,6 +118,31 @@ def test_compute_fails_loudly_without_device():
         ld.matmulHSDR("layer.hsdr.weight", np.zeros((512, 1), np.float32), 1)
 
 
+def test_shared_dictionary_resources_in_the_index(tmp_path, oracle):
+    """An .sdr with shared-dictionary resource segments is an ordinary archive to the index reader:
+    the dictionary is a stored-raw segment whose payload is one .hsda dictionary record, a tensor
+    coded against it carries a codes-only payload and names the dictionary in its data_format."""
+    from tests import synth
+    from oracle.bindings import SharedDict
+    cfg = dict(n_layers=2, hidden=64, q_heads=2, kv_heads=1, head_dim=32, inter=128, vocab=50)
+    path = str(tmp_path / "shared.sdr")
+    synth.decoder_archive(path, **cfg, k=3, n_atoms=16, kv_atoms=8, shared_dicts=True)
+    ld = cs.SDRModelLoader(path, index_only=True)
+    names = [h.name for h in ld.getSegmentHeaders()]
+    assert sum(n.startswith("hsdr.shared_dict/") for n in names) == 7          # one per block role, not per block
+    d = ld.findSegmentHeader("hsdr.shared_dict/ffn_down")
+    assert (d.data_format, d.compression_strategy_id) == ("hsdr_dict", 0)
+    tr, tc, K, S, k, atoms, scales = synth.read_dictionary_record(ld.loadSegmentByName(d.name))
+    assert (tr, tc, K, S, k) == (1, cfg["inter"], 16, 3, 3) and atoms.shape == (16, cfg["inter"])
+    for blk in (0, 1):
+        h = ld.findSegmentHeader(f"blk.{blk}.ffn_down.weight")
+        assert (h.data_format, h.compression_strategy_id) == ("hsdc@hsdr.shared_dict/ffn_down", 5)
+        pay = ld.loadCompressedBytesByName(h.name)
+        assert bytes(pay[:4]) == b"HSDC" and cs.inspect_payload(pay).kind == 1   # CSDR_KIND_HSDC
+        w = oracle.hsdc_decompress(pay, SharedDict(tr, tc, K, S, k, atoms, scales))
+        assert w.shape == (cfg["hidden"], cfg["inter"]) and np.isfinite(w).all()
+
+
 def test_routing_errors_before_any_compute():
     ld = cs.SDRModelLoader(os.path.join(GOLDEN, "routing.sdr"), index_only=True)
     with pytest.raises(RuntimeError, match="matmulHSDR: segment not found"):
