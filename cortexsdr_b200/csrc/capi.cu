@@ -160,7 +160,7 @@ using namespace csdr_hostio;
 // been opted into is shared by all contexts of the process (a context that set a smaller value
 // behind another's back would otherwise lower it).
 void csdr_context::opt_in_smem(const void* kernel, size_t bytes) {
-    if (bytes <= 48u * 1024u) return;
+    if (bytes <= 40u * 1024u) return;   // static shared memory counts toward the 48 KB a kernel has without opting in
     static std::mutex mu;
     static std::map<std::pair<int, const void*>, size_t> optins;
     std::lock_guard<std::mutex> lock(mu);

@@ -189,6 +189,180 @@ greedy_kernel(const float* __restrict__ Pt, size_t stride, const float* __restri
     }
 }
 
+
+// ---- dictionary update (atomUpdateStep, :281-489) ----
+// residual[i] = tile[i] - sum over its codes of (+-gamma_l) * atom, codes in stream order.
+__global__ void __launch_bounds__(256)
+residual_kernel(const float* __restrict__ tiles, const float* __restrict__ D, const uint16_t* __restrict__ codes,
+                const float* __restrict__ gammas, uint32_t n_tiles, uint32_t T, uint32_t S, uint32_t k,
+                float* __restrict__ resid) {
+    const uint32_t slots = S * k;
+    for (uint32_t i = blockIdx.x; i < n_tiles; i += gridDim.x) {
+        const uint16_t* cs = codes + static_cast<size_t>(i) * slots;
+        for (uint32_t c = threadIdx.x; c < T; c += 256u) {
+            float r = 0.0f;
+            for (uint32_t s = 0; s < slots; ++s) {
+                const uint32_t code = cs[s];
+                const float g = gammas[s / k];
+                r = __fadd_rn(r, __fmul_rn((code & 0x8000u) ? -g : g, D[static_cast<size_t>(code & 0x7FFFu) * T + c]));
+            }
+            resid[static_cast<size_t>(i) * T + c] = tiles[static_cast<size_t>(i) * T + c] - r;
+        }
+    }
+}
+
+constexpr uint32_t kUpdCols = 2048;   // columns of an atom one CTA corrects: eight doubles per thread
+
+struct AtomPartial {
+    double new_sq;       // sum of squares of the candidate over this CTA's columns
+    double wsum;         // sum of gamma^2 over the atom's users (the same in every column block)
+    uint32_t users;
+    uint32_t nonfinite;
+};
+
+// grid (atom, column block). The CTA walks the whole code stream in order, 256 codes at a time;
+// the codes that name its atom are compacted in stream order (tile-major, slot-minor: the order
+// of the reference's user list) and their residual rows are added up, signed and scaled, in
+// double. The reference packs a user as (tile << 16 | slot) in 32 bits, so a tile number above
+// 65535 folds onto its low 16 bits, for the residual row and for the sign alike; kept.
+// Then the candidate atom + corr / (2 * wsum), as a float, into cand, with this block's share of
+// its squared norm.
+__global__ void __launch_bounds__(256)
+atom_correct_kernel(const float* __restrict__ resid, const float* __restrict__ D, const uint16_t* __restrict__ codes,
+                    const float* __restrict__ gammas, uint32_t n_tiles, uint32_t T, uint32_t S, uint32_t k,
+                    float* __restrict__ cand, AtomPartial* __restrict__ partial) {
+    constexpr uint32_t PER = kUpdCols / 256u;
+    __shared__ uint32_t list_s[256];          // (flat code position) of this chunk's users, in order
+    __shared__ uint32_t warp_count[8];
+    __shared__ double red_s[8];
+    __shared__ uint32_t flag_s;
+    const uint32_t j = blockIdx.x, cb = blockIdx.y;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t slots = S * k;
+    const size_t n_codes = static_cast<size_t>(n_tiles) * slots;
+    const uint32_t c0 = cb * kUpdCols;
+    double corr[PER];
+#pragma unroll
+    for (uint32_t q = 0; q < PER; ++q) corr[q] = 0.0;
+    double wsum = 0.0;
+    uint32_t users = 0;
+    if (tid == 0) flag_s = 0;
+    for (size_t base = 0; base < n_codes; base += 256u) {
+        const size_t pos = base + tid;
+        const bool hit = pos < n_codes && (codes[pos] & 0x7FFFu) == j;
+        const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, hit);
+        if (lane == 0) warp_count[warp] = __popc(ballot);
+        __syncthreads();
+        uint32_t before = 0, total = 0;
+#pragma unroll
+        for (uint32_t w = 0; w < 8u; ++w) {
+            const uint32_t n = warp_count[w];
+            before += w < warp ? n : 0u;
+            total += n;
+        }
+        if (hit) list_s[before + __popc(ballot & ((1u << lane) - 1u))] = static_cast<uint32_t>(pos - base);
+        __syncthreads();
+        for (uint32_t u = 0; u < total; ++u) {
+            const size_t p = base + list_s[u];
+            const uint32_t i = static_cast<uint32_t>(p / slots), s_ = static_cast<uint32_t>(p - static_cast<size_t>(i) * slots);
+            const uint32_t it = i & 0xFFFFu;
+            const uint32_t own = codes[static_cast<size_t>(it) * slots + s_];
+            const double gamma = static_cast<double>(gammas[s_ / k]);
+            const double sg = (own & 0x8000u) ? -gamma : gamma;
+            const float* r = resid + static_cast<size_t>(it) * T + c0;
+#pragma unroll
+            for (uint32_t q = 0; q < PER; ++q) {
+                const uint32_t c = tid + q * 256u;
+                if (c0 + c < T) corr[q] += sg * static_cast<double>(r[c]);
+            }
+            wsum += gamma * gamma;
+        }
+        users += total;
+        // list_s is rewritten only behind the next chunk's first barrier
+    }
+    double sq = 0.0;
+    bool bad = false;
+    if (users && wsum > 1e-12) {
+        const double inv_w = 0.5 / wsum;
+#pragma unroll
+        for (uint32_t q = 0; q < PER; ++q) {
+            const uint32_t c = c0 + tid + q * 256u;
+            if (c < T) {
+                const double v = static_cast<double>(D[static_cast<size_t>(j) * T + c]) + corr[q] * inv_w;
+                const float vf = static_cast<float>(v);
+                if (!isfinite(v) || !isfinite(vf)) bad = true;
+                cand[static_cast<size_t>(j) * T + c] = vf;
+                sq += static_cast<double>(vf) * static_cast<double>(vf);
+            }
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, off);
+    if (lane == 0) red_s[warp] = sq;
+    if (bad) atomicOr(&flag_s, 1u);
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (uint32_t w = 0; w < 8u; ++w) t += red_s[w];
+        partial[static_cast<size_t>(j) * gridDim.y + cb] = AtomPartial{t, wsum, users, flag_s};
+    }
+}
+
+// One CTA per atom: the decision of :404-487 from the column blocks' partials. No user: the atom
+// becomes a random tile scaled to the target norm; weights that vanish: it stays; a non-finite
+// candidate: random tile again (another salt); else the candidate, pulled back to the target norm
+// when it has grown past 1.5 times it.
+__global__ void __launch_bounds__(256)
+atom_commit_kernel(const float* __restrict__ tiles, const float* __restrict__ cand, const AtomPartial* __restrict__ partial,
+                   uint32_t n_blocks, const uint32_t* __restrict__ pick_unused, const uint32_t* __restrict__ pick_nonfinite,
+                   uint32_t T, double target, float* __restrict__ D) {
+    __shared__ double red_s[8];
+    const uint32_t j = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    double new_sq = 0.0;
+    uint32_t nonfinite = 0;
+    for (uint32_t b = 0; b < n_blocks; ++b) {
+        const AtomPartial& p = partial[static_cast<size_t>(j) * n_blocks + b];
+        new_sq += p.new_sq;
+        nonfinite |= p.nonfinite;
+    }
+    const AtomPartial& p0 = partial[static_cast<size_t>(j) * n_blocks];
+    float* atom = D + static_cast<size_t>(j) * T;
+    const float* src = nullptr;
+    if (p0.users == 0u) {
+        src = tiles + static_cast<size_t>(pick_unused[j]) * T;
+    } else if (p0.wsum <= 1e-12) {
+        return;
+    } else if (nonfinite || !isfinite(new_sq)) {
+        src = tiles + static_cast<size_t>(pick_nonfinite[j]) * T;
+    }
+    if (!src) {
+        const double nn = sqrt(new_sq);
+        const bool shrink = nn > 1.5 * target;
+        const double sc = shrink ? target / nn : 1.0;
+        for (uint32_t c = tid; c < T; c += 256u) {
+            const float v = cand[static_cast<size_t>(j) * T + c];
+            atom[c] = shrink ? static_cast<float>(static_cast<double>(v) * sc) : v;
+        }
+        return;
+    }
+    double sq = 0.0;
+    for (uint32_t c = tid; c < T; c += 256u) sq += static_cast<double>(src[c]) * static_cast<double>(src[c]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, off);
+    if (lane == 0) red_s[warp] = sq;
+    __syncthreads();
+    double total = 0.0;
+    for (uint32_t w = 0; w < 8u; ++w) total += red_s[w];
+    const double sc = target / sqrt(total > 1e-30 ? total : 1e-30);
+    for (uint32_t c = tid; c < T; c += 256u) atom[c] = static_cast<float>(static_cast<double>(src[c]) * sc);
+}
+
+// The sweep behind the last round (:598-604): values that are not finite become 0.
+__global__ void __launch_bounds__(256) finite_sweep_kernel(float* __restrict__ D, size_t n) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        if (!isfinite(D[i])) D[i] = 0.0f;
+}
+
 }  // namespace
 
 void launch_extract_tiles(csdr_context* ctx, const float* W, uint32_t C, uint32_t tr, uint32_t tc, uint32_t n_rt,
@@ -262,6 +436,38 @@ void launch_code_tiles(csdr_context* ctx, const float* tiles, uint32_t n_tiles, 
     else greedy_kernel<32><<<grid, 128, 0, ctx->stream>>>(Pt, n_tiles, G, gammas_dev, codes_dev, n_tiles, K, S, k);
     ls.done("greedy_kernel");
     CSDR_CUDA(cudaStreamSynchronize(ctx->stream));   // `work` goes away with this scope
+}
+
+}  // namespace csdr
+
+namespace csdr {
+
+void launch_atom_update(csdr_context* ctx, const float* tiles, uint32_t n_tiles, uint32_t T, float* D, uint32_t K,
+                        uint32_t S, uint32_t k, const float* gammas_dev, const uint16_t* codes_dev, double target,
+                        const uint32_t* pick_unused_dev, const uint32_t* pick_nonfinite_dev) {
+    const uint32_t n_blocks = (T + kUpdCols - 1u) / kUpdCols;
+    DeviceBuffer resid(static_cast<size_t>(n_tiles) * T * sizeof(float), ctx->device);
+    DeviceBuffer cand(static_cast<size_t>(K) * T * sizeof(float), ctx->device);
+    DeviceBuffer partial(static_cast<size_t>(K) * n_blocks * sizeof(AtomPartial), ctx->device);
+    LaunchScope ls(ctx, KC_ENCODE);
+    residual_kernel<<<std::min<uint32_t>(n_tiles, static_cast<uint32_t>(ctx->sm_count) * 8u), 256, 0, ctx->stream>>>(
+        tiles, D, codes_dev, gammas_dev, n_tiles, T, S, k, static_cast<float*>(resid.ptr));
+    atom_correct_kernel<<<dim3(K, n_blocks), 256, 0, ctx->stream>>>(static_cast<const float*>(resid.ptr), D, codes_dev, gammas_dev,
+                                                                    n_tiles, T, S, k, static_cast<float*>(cand.ptr),
+                                                                    static_cast<AtomPartial*>(partial.ptr));
+    atom_commit_kernel<<<K, 256, 0, ctx->stream>>>(tiles, static_cast<const float*>(cand.ptr),
+                                                   static_cast<const AtomPartial*>(partial.ptr), n_blocks, pick_unused_dev,
+                                                   pick_nonfinite_dev, T, target, D);
+    ls.done("atom update kernels");
+    CSDR_CUDA(cudaStreamSynchronize(ctx->stream));   // the work buffers go away with this scope
+}
+
+void launch_finite_sweep(csdr_context* ctx, float* D, size_t n) {
+    if (!n) return;
+    LaunchScope ls(ctx, KC_ENCODE);
+    finite_sweep_kernel<<<static_cast<unsigned>(std::min<size_t>((n + 255) / 256, static_cast<size_t>(ctx->sm_count) * 16)), 256, 0,
+                          ctx->stream>>>(D, n);
+    ls.done("finite_sweep_kernel");
 }
 
 }  // namespace csdr

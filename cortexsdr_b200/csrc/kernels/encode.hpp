@@ -19,4 +19,15 @@ void launch_init_atoms(csdr_context* ctx, const float* tiles, const uint32_t* pi
 void launch_code_tiles(csdr_context* ctx, const float* tiles, uint32_t n_tiles, uint32_t T, const DevPtr& D, uint32_t K,
                        uint32_t S, uint32_t k, const float* gammas_dev, uint16_t* codes_dev);
 
+// One dictionary-update round (atomUpdateStep, strategies/HierarchicalSDRStrategy.cpp:281-489): every
+// atom moves half a least-squares step toward the residuals of the tiles that use it. `target` is
+// the mean tile norm over sqrt(S * k); the pick arrays name, per atom, the tile that replaces it
+// when nothing uses it / when its candidate is not finite (drawn on the host as the reference
+// draws them).
+void launch_atom_update(csdr_context* ctx, const float* tiles, uint32_t n_tiles, uint32_t T, float* D, uint32_t K,
+                        uint32_t S, uint32_t k, const float* gammas_dev, const uint16_t* codes_dev, double target,
+                        const uint32_t* pick_unused_dev, const uint32_t* pick_nonfinite_dev);
+// Non-finite dictionary values become 0 (:598-604).
+void launch_finite_sweep(csdr_context* ctx, float* D, size_t n);
+
 }  // namespace csdr

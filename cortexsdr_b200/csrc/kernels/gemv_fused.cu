@@ -55,8 +55,7 @@ struct FusedParams {
     uint32_t gather_ctas;   // CTAs that take part in phase B = row chunks * token groups
     XView x;
     unsigned long long* part;  // {float bits (low half), epoch (high half)} per partial
-    uint32_t* seq;          // device: [0] launches completed (the epoch is this + 1, never 0: fresh
-                            // scratch is zero), [1] CTAs of the running launch that have read [0]
+    unsigned long long* seq;  // device: {launches completed, CTAs checked in} (take_launch_tag)
     int* status;
     uint32_t spin_limit;
     unsigned long long* trace;  // optional: 16 global-timer stamps per CTA (phase boundaries)
@@ -82,23 +81,6 @@ __device__ __forceinline__ void st_tagged(unsigned long long* p, float value, ui
     const unsigned long long w = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
     asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-// Every launch tags its words with (launches completed + 1). One thread per CTA reads the
-// counter and then checks in; the CTA that checks in last knows that every CTA of the launch has
-// read the counter and advances it for the next launch (skipping the value whose successor
-// would be the tag 0). The check-in is an acq_rel atomic, so the read is ordered before it; its
-// latency hides under the activation staging.
-__device__ __forceinline__ uint32_t take_epoch(uint32_t* seq) {
-    uint32_t done, prev;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(seq) : "memory");
-    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(seq + 1) : "memory");
-    if (prev == gridDim.x - 1u) {
-        seq[1] = 0u;
-        const uint32_t next = done + 1u;
-        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(seq), "r"(next == 0xFFFFFFFFu ? 0u : next) : "memory");
-    }
-    return done + 1u;
-}
-
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
                  "l"(gmem_src)
@@ -144,6 +126,7 @@ struct SmemPlan {
     uint32_t codes_off[kMaxFusedGroup];   // byte offsets
     uint32_t scales_off[kMaxFusedGroup];
     uint32_t dxs_off;
+    uint32_t normw_off;                   // the norm weights of the folded normalisation, [C]
 };
 
 // Register budget: two launches must be able to sit on an SM together (two CTAs each), or the
@@ -232,34 +215,42 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    if (p.norm_w) {
+        // the norm weights are static too: into shared memory before the wait
+        unsigned char* nw = smem_raw + plan.normw_off;
+        for (uint32_t i = tid; i < (p.C >> 2); i += kThreads) cp_async16(nw + i * 16u, p.norm_w + i * 4u);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     // x and the partial buffer belong to earlier work on the stream
     stamp(p, 1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(p, 2);
     __shared__ uint32_t epoch_s;
-    if (tid == 0) epoch_s = take_epoch(p.seq);
-    __syncthreads();
-    const uint32_t epoch = epoch_s;
+    // thread 0 checks in (one L2 round trip) while the others already stage the activations
+    if (tid == 0) epoch_s = take_launch_tag(p.seq);
 
     // ---- phase A ----
     float* xs = reinterpret_cast<float*>(smem_raw);
     const float4* xs4 = reinterpret_cast<const float4*>(xs);
     __shared__ float ssq_s[kThreads / 32][MT];
     __shared__ float inv_s[MT];
-    if (whole_x && (blockIdx.x < p.n_tasks || (p.norm_w && gathers))) {
-        stage_x<MT>(p.x, 0, p.C, p.C, xs);
-        __syncthreads();
+    const bool stage_whole = whole_x && (blockIdx.x < p.n_tasks || (p.norm_w && gathers));
+    if (stage_whole) stage_x<MT>(p.x, 0, p.C, p.C, xs);
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    if (stage_whole) {
         if (p.norm_w) {
             // rms_norm (api/cortex_sdk.cpp:1208-1232) split in two: the weights go onto the staged row
             // here, 1 / rms onto the gathered rows; every CTA sums the squares of the whole row
             float4* xw = reinterpret_cast<float4*>(xs);
-            const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+            const float4* w4 = reinterpret_cast<const float4*>(smem_raw + plan.normw_off);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's share of the weights is the share it reads
 #pragma unroll
             for (int b = 0; b < MT; ++b) {
                 float ss = 0.0f;
                 for (uint32_t c4 = tid; c4 < xcols4; c4 += kThreads) {
                     const float4 v = xw[b * xcols4 + c4];
-                    const float4 w = __ldg(w4 + c4);
+                    const float4 w = w4[c4];
                     ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
                     xw[b * xcols4 + c4] = make_float4(v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
                 }
@@ -473,7 +464,9 @@ void launch_t(csdr_context* ctx, FusedParams& p, uint32_t max_k, bool pdl) {
             off += ((p.seg[i].S + 3u) & ~3u) * 4u;
         }
         plan.dxs_off = static_cast<uint32_t>(off);
-        return off + static_cast<size_t>(max_k) * (MT < 4 ? MT : 4) * 4u;
+        off += static_cast<size_t>(max_k) * (MT < 4 ? MT : 4) * 4u;
+        plan.normw_off = static_cast<uint32_t>(off);
+        return off + (p.norm_w ? static_cast<size_t>(p.C) * 4u : 0u);
     };
     const uint32_t want_gather = p.gather_ctas;
     const size_t smem = plan_for(std::min<uint32_t>(want_gather, static_cast<uint32_t>(ctx->sm_count)));
@@ -580,7 +573,7 @@ void launch_gemv_fused(csdr_context* ctx, const csdr_segment* const* segs, uint3
     p.n_tasks = task;
     p.part = static_cast<unsigned long long*>(
         ctx->scratch_get(4, std::max<size_t>(static_cast<size_t>(part_off) * 8u, 2u << 20)));
-    p.seq = ctx->gemv_seq;
+    p.seq = reinterpret_cast<unsigned long long*>(ctx->gemv_seq);
     p.status = ctx->status_word;
     p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
     p.spin_limit = ctx->spin_limit_gemv;  // each poll is an L2 round trip: about a second by default

@@ -101,7 +101,7 @@ struct QParams {
     uint32_t split_rows;        // 1: a task's rows are split over the gather warps; 0: tasks are dealt out to them
     u64* dx;                    // tagged Dx words
     u64* sumsq;                 // tagged sums of squares of a task's activations: [task][kMaxTokens]
-    uint32_t* seq;              // [0] queue launches completed, [1] CTAs that have read [0]
+    unsigned long long* seq;    // {launches completed, CTAs checked in} (take_launch_tag)
     int* status;
     uint32_t spin_poll, spin_barrier;
     unsigned long long* trace;  // optional: global-timer stamps, [cta][8 tasks][8 slots] (tuning)
@@ -148,21 +148,6 @@ __device__ __forceinline__ u64 ld_tagged(const u64* p) {
 __device__ __forceinline__ void st_tagged(u64* p, float value, uint32_t tag) {
     const u64 w = (static_cast<u64>(tag) << 32) | __float_as_uint(value);
     asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
-}
-
-// The launch's tag: queue launches completed + 1. The thread that calls this checks in with an
-// acq_rel atomic after reading the counter; the CTA that checks in last knows every CTA has read
-// it and advances it for the next launch (never to the value whose successor would be the tag 0).
-__device__ __forceinline__ uint32_t take_tag(uint32_t* seq) {
-    uint32_t done, prev;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(seq) : "memory");
-    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(seq + 1) : "memory");
-    if (prev == gridDim.x - 1u) {
-        seq[1] = 0u;
-        const uint32_t next = done + 1u;
-        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(seq), "r"(next == 0xFFFFFFFFu ? 0u : next) : "memory");
-    }
-    return done + 1u;
 }
 
 __device__ __forceinline__ XView x_view(const QTask& t) {
@@ -311,7 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
         while (ui < p.n_units && it_issue < NS) issue();
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0) {
-            tag_s = take_tag(p.seq);
+            tag_s = take_launch_tag(p.seq);
             stamp(p, 0, 6);
         }
         asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
@@ -804,7 +789,7 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
         p.n_tasks = cnt;
         p.n_units = unit;
         p.split_rows = split ? 1u : 0u;
-        p.seq = ctx->queue_sync;
+        p.seq = reinterpret_cast<unsigned long long*>(ctx->queue_sync);
         p.status = ctx->status_word;
         p.spin_poll = ctx->spin_limit_gemv;
         p.spin_barrier = ctx->spin_limit_barrier;

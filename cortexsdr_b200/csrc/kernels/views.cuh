@@ -54,4 +54,22 @@ __device__ __forceinline__ size_t y_index(const YView& v, uint32_t r, uint32_t b
                : static_cast<size_t>(v.b0 + b) * v.R + r;
 }
 
+// The tag of a launch: (launches completed) mod (2^32 - 1), plus one - never 0, the value fresh
+// scratch holds. One 64-bit word in device memory keeps {launches completed (high half), CTAs of
+// the running launch that have checked in (low half)}; a CTA checks in with ONE atomic add, whose
+// return value also carries the count it needs, and the CTA that checks in last adds the rest of
+// 2^32 so that the high half moves on and the low half returns to zero. Every CTA of a launch
+// reads the same high half (it only moves after the last check-in), and the next launch checks
+// in behind its dependency wait, when this launch's stores are visible. Because the word lives
+// on the device, a captured CUDA graph tags every replay afresh.
+__device__ __forceinline__ uint32_t take_launch_tag(unsigned long long* seq) {
+    unsigned long long old;
+    asm volatile("atom.relaxed.gpu.global.add.u64 %0, [%1], 1;" : "=l"(old) : "l"(seq) : "memory");
+    if (static_cast<uint32_t>(old) == gridDim.x - 1u) {
+        const unsigned long long rest = (1ull << 32) - gridDim.x;
+        asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(seq), "l"(rest) : "memory");
+    }
+    return static_cast<uint32_t>((old >> 32) % 0xFFFFFFFFull) + 1u;
+}
+
 }  // namespace csdr
