@@ -161,7 +161,7 @@ DECODERS = {
 
 
 FUSED_GEMV_DRAM_BYTES_NCU = 8996000   # per launch, cfg2 shape, batch 1 (8.996 MB read, 0 written)
-QUEUE_DRAM_BYTES_PER_TASK_NCU = None   # per task of the queue kernel, cfg2 shape, batch 1 (set from the ncu capture)
+QUEUE_DRAM_BYTES_PER_TASK_NCU = 9171000   # per product of the list kernel, cfg2 shape, batch 1 (146.7 MB per 16-product launch)
 
 
 def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True, kv_dtype="f32",
@@ -331,6 +331,42 @@ def other_configs(cs, torch, ctx, stream, timed, hbm_peak, tf_peak, args):
         if "error" not in out[label]:
             out[label]["note"] = "the shared dictionary stays in L2 between products: not an HBM figure"
     dic.close()
+    return out
+
+
+def encoder_bench(cs, ctx, args):
+    """The encoder on config 1's shape (4096 x 4096, row tiles, 512 atoms, 3 x 8 codes): wall time of
+    csdr_hsdr_encode with host buffers (the 64 MB tensor crosses to the device inside the call, the
+    payload comes back), fast mode and with two dictionary-update rounds; beside it the reference
+    encoder on the host cores for the fast mode."""
+    out = {"shape": "4096x4096, row tiles, 512 atoms, 3x8 codes"}
+    W = np.random.default_rng(0).normal(0, 0.02, (4096, 4096)).astype(np.float32)
+    st = cs.HierarchicalSDRStrategy(ctx)
+    kw = dict(tile_rows=1, tile_cols=4096, n_atoms=512, n_stages=3, k=8)
+    try:
+        for label, iters in (("fast", 0), ("two_update_rounds", 2)):
+            st.compress(W, **kw, ksvd_iters=iters)              # warm-up: kernels loaded, scratch sized
+            best = None
+            for _ in range(2):
+                t0 = time.perf_counter()
+                pay = st.compress(W, **kw, ksvd_iters=iters)
+                dt = (time.perf_counter() - t0) * 1e3
+                best = dt if best is None else min(best, dt)
+            out[label + "_ms"] = best
+            out[label + "_payload_bytes"] = len(pay)
+    except Exception as e:
+        out["error"] = f"{type(e).__name__}: {e}"[:200]
+    if not args.no_cpu:
+        try:
+            from oracle.bindings import SEG_FEED_FORWARD, Reference, Segment, cfg_row1d
+            if Reference.available():
+                cfg = cfg_row1d(4096, 512, 8, ksvd_iters=0)
+                t0 = time.perf_counter()
+                Reference().compress(Segment("blk.0.ffn_gate.weight", W, (4096, 4096), SEG_FEED_FORWARD), cfg, cfg)
+                out["cpu_reference_fast_ms"] = (time.perf_counter() - t0) * 1e3
+                out["cpu_threads"] = os.cpu_count()
+        except Exception as e:
+            out["cpu_reference_error"] = f"{type(e).__name__}: {e}"[:160]
     return out
 
 
@@ -657,6 +693,7 @@ def main():
         segs.clear()
         torch.cuda.empty_cache()
         other = other_configs(cs, torch, ctx, stream, timed, hbm_peak, tf_peak, args)
+        other["encoder"] = encoder_bench(cs, ctx, args)
 
     # ---- decoder-shaped decode tokens/s (tensor-parallel over the ranks when world > 1) ----
     decode = {}

@@ -369,8 +369,8 @@ class SharedDictionary:
 
 
 class HierarchicalSDRStrategy:
-    """The strategy plug-in (id 5): the decode side, and the encoder's fast mode (ksvd_iters = 0);
-    dictionary-update iterations stay with the reference encoder."""
+    """The strategy plug-in (id 5): the decode side and the encoder (fast mode and dictionary-update
+    rounds)."""
 
     def __init__(self, ctx: Context | None = None):
         self.ctx = ctx or default_context()

@@ -225,6 +225,9 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         if (const char* e = std::getenv("CSDR_CACHE_2D")) ctx->cache_2d = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_QUEUE")) ctx->decoder_queue = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_FOLD")) ctx->decoder_fold = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_FUSED_POLL_SLEEP")) ctx->fused_poll_sleep_ns = static_cast<uint32_t>(std::max(0, std::atoi(e)));
+        if (const char* e = std::getenv("CSDR_QUEUE_POLL_SLEEP")) ctx->queue_poll_sleep_ns = static_cast<uint32_t>(std::max(0, std::atoi(e)));
+        if (const char* e = std::getenv("CSDR_QUEUE_MIN_GROUP")) ctx->queue_min_group = static_cast<uint32_t>(std::max(1, std::atoi(e)));
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE_SINGLE")) ctx->gemv_queue_single = e[0] != '0';
         if (const char* e = std::getenv("CSDR_PDL")) ctx->pdl = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TENSOR_CORES")) ctx->tensor_cores = e[0] != '0';
@@ -629,7 +632,7 @@ int csdr_matmul_group_device_async(csdr_context* ctx, const csdr_segment* const*
             }
             return;
         }
-        if (n_segs >= 8 && batch <= 4) {
+        if (n_segs >= ctx->queue_min_group && batch <= 4) {
             // long lists: any number of members in one persistent launch (short ones are quicker as
             // grouped launches of up to four)
             std::vector<QueueItem> items(n_segs);

@@ -1,11 +1,14 @@
-// extern "C" face of the HSDR encoder (fast mode) and of its coding pass alone.
+// extern "C" face of the HSDR encoder and of its coding pass alone.
 //
 // HierarchicalSDRStrategy::compress (strategies/HierarchicalSDRStrategy.cpp:1068-1236) around
-// fitHierarchicalKSVD (:494-607) with ksvd_iters = 0: tiles of the aligned top-left block, a
-// dictionary of K tiles picked by std::mt19937(0xC0DE), normalised and scaled by the mean tile norm
-// over sqrt(S * k), one coding pass, and the payload "HSDR" v2 with the raw edge strips behind it.
-// The tile picks and the byte layout are host work; everything that touches the tensor runs on
-// the device (kernels/encode.cu).
+// fitHierarchicalKSVD (:494-607): tiles of the aligned top-left block, a dictionary of K tiles
+// picked by std::mt19937(0xC0DE), normalised and scaled by the mean tile norm over sqrt(S * k),
+// one coding pass, then ksvd_iters rounds of (atomUpdateStep :281-489, coding pass), the sweep of
+// non-finite values, and the payload "HSDR" v2 with the raw edge strips behind it. The random
+// draws and the byte layout are host work; everything that touches the tensor runs on the device
+// (kernels/encode.cu). As in compress, the fit runs on all tiles (max_tiles_for_fit only bounds
+// the reference's streaming and grouped encoders).
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <vector>
@@ -94,9 +97,6 @@ int csdr_hsdr_encode(csdr_context* ctx, const float* W, uint32_t rows, uint32_t 
         if (!W || !n_out) throw Error(CSDR_ERR_INVALID_ARG, "null argument");
         if (!rows || !cols || !tile_rows || !tile_cols || !n_atoms || !n_stages || !k_per_stage || n_atoms > 0x7FFF)
             throw Error(CSDR_ERR_INVALID_ARG, "HSDR: zero or out-of-range config field");
-        if (ksvd_iters != 0)
-            throw Error(CSDR_ERR_UNSUPPORTED, "HSDR encode: only the fast mode (ksvd_iters = 0) runs on the device; "
-                                              "dictionary-update iterations stay with the reference encoder");
         const uint32_t R_full = rows / tile_rows * tile_rows, C_full = cols / tile_cols * tile_cols;
         if (!R_full || !C_full) throw Error(CSDR_ERR_GEOMETRY, "HSDR: tensor smaller than one tile");
         const uint32_t n_rt = R_full / tile_rows, n_ct = C_full / tile_cols;
@@ -123,7 +123,8 @@ int csdr_hsdr_encode(csdr_context* ctx, const float* W, uint32_t rows, uint32_t 
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
         double norm_sum = 0.0;
         for (double v : nh) norm_sum += v;
-        const float mean = static_cast<float>(norm_sum / static_cast<double>(n_tiles));
+        const double mean_d = norm_sum / static_cast<double>(n_tiles);
+        const float mean = static_cast<float>(mean_d);
         const float root = std::sqrt(static_cast<float>(static_cast<uint32_t>(n_stages) * k_per_stage));
         const float init_scale = mean / (root > 1.0f ? root : 1.0f);
         // tile picks (:513-517)
@@ -140,6 +141,34 @@ int csdr_hsdr_encode(csdr_context* ctx, const float* W, uint32_t rows, uint32_t 
         DevPtr codes = std::make_shared<DeviceBuffer>(n_codes * 2, ctx->device);
         launch_code_tiles(ctx, static_cast<const float*>(tiles->ptr), n_tiles, static_cast<uint32_t>(T), D, n_atoms, n_stages,
                           k_per_stage, static_cast<const float*>(gam_d->ptr), static_cast<uint16_t*>(codes->ptr));
+
+        if (ksvd_iters) {
+            // the update's target norm (:306-318) from the same tile norms, in double
+            const double target = std::max(mean_d / std::sqrt(static_cast<double>(static_cast<uint32_t>(n_stages) * k_per_stage)), 1e-6);
+            std::vector<uint32_t> pick_a(n_atoms), pick_b(n_atoms);
+            DevPtr pick_a_d = std::make_shared<DeviceBuffer>(static_cast<size_t>(n_atoms) * 4, ctx->device);
+            DevPtr pick_b_d = std::make_shared<DeviceBuffer>(static_cast<size_t>(n_atoms) * 4, ctx->device);
+            for (uint8_t it = 0; it < ksvd_iters; ++it) {
+                // one draw of the fit's generator per round seeds the replacements (:320); an atom's
+                // own generator is seeded with it and the atom's number times a salt (:395-400, :430-436)
+                const uint64_t base_seed = static_cast<uint64_t>(gen.next()) ^ 0xA0B1C2D3ull;
+                for (uint32_t j = 0; j < n_atoms; ++j) {
+                    Mt19937 unused(static_cast<uint32_t>(base_seed ^ static_cast<uint64_t>(static_cast<uint32_t>(j * 0x9E3779B1u))));
+                    pick_a[j] = unused.below(n_tiles);
+                    Mt19937 nonfinite(static_cast<uint32_t>(base_seed ^ static_cast<uint64_t>(static_cast<uint32_t>(j * 0xB7E15163u))));
+                    pick_b[j] = nonfinite.below(n_tiles);
+                }
+                CSDR_CUDA(cudaMemcpyAsync(pick_a_d->ptr, pick_a.data(), pick_a.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+                CSDR_CUDA(cudaMemcpyAsync(pick_b_d->ptr, pick_b.data(), pick_b.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+                launch_atom_update(ctx, static_cast<const float*>(tiles->ptr), n_tiles, static_cast<uint32_t>(T),
+                                   static_cast<float*>(D->ptr), n_atoms, n_stages, k_per_stage, static_cast<const float*>(gam_d->ptr),
+                                   static_cast<const uint16_t*>(codes->ptr), target, static_cast<const uint32_t*>(pick_a_d->ptr),
+                                   static_cast<const uint32_t*>(pick_b_d->ptr));
+                launch_code_tiles(ctx, static_cast<const float*>(tiles->ptr), n_tiles, static_cast<uint32_t>(T), D, n_atoms, n_stages,
+                                  k_per_stage, static_cast<const float*>(gam_d->ptr), static_cast<uint16_t*>(codes->ptr));
+            }
+        }
+        launch_finite_sweep(ctx, static_cast<float*>(D->ptr), static_cast<size_t>(n_atoms) * T);
 
         // the payload (serialize, :1198-1235): header | stage scales | dictionary | codes | edge strips
         std::memset(out, 0, hdr);

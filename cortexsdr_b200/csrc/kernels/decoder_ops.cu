@@ -9,10 +9,12 @@
 //   silu_mul_kernel       silu_mul, :1245-1256
 //   add_kernel            add_vectors, :1234-1243
 //   argmax_kernel         greedy pick over the logits row
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
 #include <algorithm>
 #include <cfloat>
+#include <type_traits>
 
 #include "../internal.hpp"
 #include "decoder_ops.hpp"
@@ -324,7 +326,18 @@ struct CacheRow<__nv_bfloat16, VPL> {
 
 // WARPS warps split the keys of one (token, head); few (token, head) pairs (batched decode
 // against a long context) take more warps each so that enough K/V rows are in flight per SM.
-template <typename KV, int VPL, int kAttnWarps>
+// The cache element type of an attention kernel, from its pointer type (host-side launch helper).
+template <typename KV, typename... Rest>
+const KV* kernel_kv(void (*)(const float*, const KV*, Rest...)) {
+    return nullptr;
+}
+
+// kSplit: the keys of one (token, head) are split over the CTAs of a thread-block cluster
+// (grid z = cluster size) and the CTAs' partial softmax states are merged by the cluster's first
+// CTA through distributed shared memory - for steps with fewer (token, head) pairs than SMs
+// (batch-1 decode), where one CTA per pair would walk the whole context alone, one load latency
+// after the other.
+template <typename KV, int VPL, int kAttnWarps, bool kSplit>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
                  const KV* __restrict__ vc, const int32_t* __restrict__ seq_of,
@@ -347,7 +360,8 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
 #pragma unroll
     for (int e = 0; e < VPL; ++e) acc[e] = 0.0f;
     float m = -INFINITY, l = 0.0f;
-    for (int32_t j0 = warp * kKeys; j0 < n_keys; j0 += kAttnWarps * kKeys) {
+    const uint32_t crank = kSplit ? blockIdx.z : 0u, csize = kSplit ? gridDim.z : 1u;
+    for (int32_t j0 = (crank * kAttnWarps + warp) * kKeys; j0 < n_keys; j0 += csize * kAttnWarps * kKeys) {
         CacheRow<KV, VPL> kv[kKeys], vv[kKeys];
 #pragma unroll
         for (int u = 0; u < kKeys; ++u) {
@@ -388,13 +402,12 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
 #pragma unroll
     for (int e = 0; e < VPL; ++e) sm_acc[warp][lane * VPL + e] = acc[e];
     __syncthreads();
+    float M = -INFINITY, L = 0.0f, o[VPL];
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) o[e] = 0.0f;
     if (warp == 0) {
-        float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w]);
-        float L = 0.0f, o[VPL];
-#pragma unroll
-        for (int e = 0; e < VPL; ++e) o[e] = 0.0f;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
             const float f = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
@@ -402,6 +415,43 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
 #pragma unroll
             for (int e = 0; e < VPL; ++e) o[e] = fmaf(sm_acc[w][lane * VPL + e], f, o[e]);
         }
+    }
+    if constexpr (kSplit) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        // this CTA's state where the first CTA can read it: row 0 of the buffers (a lane rewrites
+        // only the slots it has just read)
+        if (warp == 0) {
+            if (lane == 0) {
+                sm_m[0] = M;
+                sm_l[0] = L;
+            }
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) sm_acc[0][lane * VPL + e] = o[e];
+        }
+        cluster.sync();
+        if (crank == 0 && warp == 0) {
+            float Mc = -INFINITY;
+            for (uint32_t r = 0; r < csize; ++r) Mc = fmaxf(Mc, cluster.map_shared_rank(&sm_m[0], r)[0]);
+            float Lc = 0.0f, oc[VPL];
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) oc[e] = 0.0f;
+            for (uint32_t r = 0; r < csize; ++r) {                       // in rank order: the result does not depend on timing
+                const float mr = cluster.map_shared_rank(&sm_m[0], r)[0];
+                const float f = mr == -INFINITY ? 0.0f : expf(mr - Mc);
+                Lc = fmaf(cluster.map_shared_rank(&sm_l[0], r)[0], f, Lc);
+                const float* ar = cluster.map_shared_rank(&sm_acc[0][0], r);
+#pragma unroll
+                for (int e = 0; e < VPL; ++e) oc[e] = fmaf(ar[lane * VPL + e], f, oc[e]);
+            }
+            L = Lc;
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) o[e] = oc[e];
+        }
+        cluster.sync();   // the peers' shared memory must outlive the reads above
+        if (crank != 0) return;
+    }
+    if (warp == 0) {
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
         const size_t o0 = (static_cast<size_t>(t) * QH + h) * HD + lane * VPL;
 #pragma unroll
@@ -599,26 +649,50 @@ void op_attention(csdr_context* ctx, const float* q, const void* kc, const void*
     if (HD % 32u || HD > 256u || HD == 96u || HD == 160u || HD == 192u || HD == 224u)
         throw Error(CSDR_ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 128 or 256");
     const float scale = 1.0f / sqrtf(static_cast<float>(HD));
-    dim3 grid(T, QH);
     LaunchScope ls(ctx, KC_ATTENTION);
     const uint32_t pairs = T * QH;
     const uint32_t sms = static_cast<uint32_t>(ctx->sm_count);
+    // few pairs: a cluster of 2, 4 or 8 CTAs per pair shares the keys
+    uint32_t split = 1;
+    while (split < 8u && pairs * split * 2u <= sms) split *= 2u;
     const int warps = pairs >= sms * 8u ? 4 : pairs >= sms * 4u ? 8 : 16;
-#define CSDR_ATTN(V, W)                                                                                              \
-    do {                                                                                                             \
-        if (kv_dtype == CSDR_DTYPE_BF16)                                                                             \
-            launch_pdl(ctx, attention_kernel<__nv_bfloat16, V, W>, grid, dim3(W * 32), q,                            \
-                       static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), seq_of, pos_of, \
-                       QH, KVH, max_seq, scale, out, hi, lo);                                                        \
-        else                                                                                                         \
-            launch_pdl(ctx, attention_kernel<float, V, W>, grid, dim3(W * 32), q, static_cast<const float*>(kc),     \
-                       static_cast<const float*>(vc), seq_of, pos_of, QH, KVH, max_seq, scale, out, hi, lo);         \
+    auto launch = [&](auto kern, int w) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(T, QH, split);
+        cfg.blockDim = dim3(static_cast<unsigned>(w) * 32u);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = ctx->pdl ? 1 : 0;
+        cfg.numAttrs = 1;
+        if (split > 1) {
+            attr[1].id = cudaLaunchAttributeClusterDimension;
+            attr[1].val.clusterDim.x = 1;
+            attr[1].val.clusterDim.y = 1;
+            attr[1].val.clusterDim.z = split;
+            cfg.numAttrs = 2;
+        }
+        cfg.attrs = attr;
+        using KVp = std::remove_pointer_t<decltype(kernel_kv(kern))>;
+        CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, q, static_cast<const KVp*>(kc), static_cast<const KVp*>(vc), seq_of, pos_of, QH, KVH,
+                                     max_seq, scale, out, hi, lo));
+    };
+#define CSDR_ATTN(V, W)                                                                     \
+    do {                                                                                    \
+        if (kv_dtype == CSDR_DTYPE_BF16) {                                                  \
+            if (split > 1) launch(attention_kernel<__nv_bfloat16, V, W, true>, W);          \
+            else launch(attention_kernel<__nv_bfloat16, V, W, false>, W);                   \
+        } else {                                                                            \
+            if (split > 1) launch(attention_kernel<float, V, W, true>, W);                  \
+            else launch(attention_kernel<float, V, W, false>, W);                           \
+        }                                                                                   \
     } while (0)
-#define CSDR_ATTN_W(V)                     \
-    do {                                   \
-        if (warps == 4) CSDR_ATTN(V, 4);   \
+#define CSDR_ATTN_W(V)                        \
+    do {                                      \
+        if (split > 1) CSDR_ATTN(V, 16);      \
+        else if (warps == 4) CSDR_ATTN(V, 4); \
         else if (warps == 8) CSDR_ATTN(V, 8); \
-        else CSDR_ATTN(V, 16);             \
+        else CSDR_ATTN(V, 16);                \
     } while (0)
     switch (HD / 32u) {
         case 1: CSDR_ATTN_W(1); break;

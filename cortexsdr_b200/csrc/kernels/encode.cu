@@ -1,6 +1,7 @@
-// HSDR encoder on the device, the mode the reference calls fast (ksvd_iters = 0: the dictionary
-// is a scaled sample of the tiles and the tensor is coded once against it;
-// strategies/HierarchicalSDRStrategy.cpp:494-571 inside compress, :1068-1236).
+// HSDR encoder on the device (strategies/HierarchicalSDRStrategy.cpp:494-607 inside compress,
+// :1068-1236): the dictionary starts as a scaled sample of the tiles, the tensor is coded against
+// it, and every further round (ksvd_iters of them; 0 is the mode the reference calls fast) moves
+// the atoms toward the residuals of their users and codes again.
 //
 //   extractTiles (:95-116)              extract_tiles_kernel: W -> [n_tiles][T]
 //   dictionary init (:511-538)          the tile picks come from std::mt19937(0xC0DE) with
@@ -21,6 +22,12 @@
 //                                       registers. Equal in exact arithmetic; in fp32 the two differ
 //                                       in rounding, so a round whose two best candidates tie within
 //                                       rounding may pick the other atom.
+//   atomUpdateStep (:281-489)           residual_kernel, atom_correct_kernel (one CTA per atom and
+//                                       block of 2048 columns walks the code stream in order,
+//                                       compacts the atom's users and adds their signed residual
+//                                       rows up in double), atom_commit_kernel (the keep / rescale /
+//                                       replace decision per atom); the replacement tiles are drawn
+//                                       on the host with the reference's per-atom generators.
 #include <cuda_runtime.h>
 
 #include <algorithm>

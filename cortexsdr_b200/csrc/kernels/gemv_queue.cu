@@ -104,6 +104,7 @@ struct QParams {
     unsigned long long* seq;    // {launches completed, CTAs checked in} (take_launch_tag)
     int* status;
     uint32_t spin_poll, spin_barrier;
+    uint32_t poll_sleep_ns;     // pause between two looks at words another CTA has yet to write
     unsigned long long* trace;  // optional: global-timer stamps, [cta][8 tasks][8 slots] (tuning)
 };
 
@@ -381,6 +382,9 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                                 failed_s = 1;
                                 break;
                             }
+                            // every product warp of every CTA that owns a unit of this task is waiting here:
+                            // polling flat out, they fill the L2 queues the producers' stores have to pass
+                            __nanosleep(p.poll_sleep_ns);
                         }
                         float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
                         if (t.norm_w) wv = __ldg(reinterpret_cast<const float4*>(t.norm_w + s * kSlab + c_lane));
@@ -539,7 +543,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                         }
                         if (__all_sync(0xFFFFFFFFu, all)) break;
                         if (__any_sync(0xFFFFFFFFu, spins >= limit || *failed)) break;   // the sweep below records the failure
-                        if (!coop) __nanosleep(256);
+                        __nanosleep(coop ? p.poll_sleep_ns : 256u);
                     }
                     if (g == 0 && lane == 0) stamp(p, ti, 2);
                 }
@@ -790,6 +794,7 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
         p.n_units = unit;
         p.split_rows = split ? 1u : 0u;
         p.seq = reinterpret_cast<unsigned long long*>(ctx->queue_sync);
+        p.poll_sleep_ns = ctx->queue_poll_sleep_ns;
         p.status = ctx->status_word;
         p.spin_poll = ctx->spin_limit_gemv;
         p.spin_barrier = ctx->spin_limit_barrier;

@@ -287,16 +287,18 @@ CSDR_API int csdr_dequantize(csdr_context* ctx, const char* fmt, const void* dat
                              size_t nbytes, float scale, float zero_point, float* out_host,
                              size_t capacity_floats, size_t* n_out);
 
-/* ---- encoder, fast mode ----
- * HierarchicalSDRStrategy::compress (strategies/HierarchicalSDRStrategy.cpp:1068-1236) with
- * ksvd_iters = 0 (fitHierarchicalKSVD :494-571: a dictionary of n_atoms tiles picked by
- * std::mt19937(0xC0DE), normalised and scaled, then one coding pass), on the device: W is
+/* ---- encoder ----
+ * HierarchicalSDRStrategy::compress (strategies/HierarchicalSDRStrategy.cpp:1068-1236) on the
+ * device: fitHierarchicalKSVD (:494-607) - a dictionary of n_atoms tiles picked by
+ * std::mt19937(0xC0DE), normalised and scaled, one coding pass, then ksvd_iters rounds of
+ * atomUpdateStep (:281-489) + coding pass (0 rounds is the reference's fast mode). W is
  * rows x cols fp32 row-major on the host, the result an "HSDR" v2 payload. *n_out receives the
  * payload size (also when the buffer is too small: CSDR_ERR_BUFFER). Header, stage scales, tile
  * picks and edge strips equal the reference encoder's; atoms agree to rounding; a code may differ
  * where a round's two best atoms tie within fp32 rounding (the coding pass works on projections
- * computed once and updated through the Gram matrix instead of re-projecting a residual).
- * ksvd_iters != 0 (dictionary-update iterations): CSDR_ERR_UNSUPPORTED. */
+ * computed once and updated through the Gram matrix instead of re-projecting a residual), and
+ * behind such a code the update rounds move the atoms it touches differently: with rounds the
+ * two encoders agree in reconstruction error, not atom for atom. */
 CSDR_API int csdr_hsdr_encode(csdr_context* ctx, const float* W, uint32_t rows, uint32_t cols,
                               uint16_t tile_rows, uint16_t tile_cols, uint16_t n_atoms,
                               uint8_t n_stages, uint8_t k_per_stage, float stage_decay,
