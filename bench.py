@@ -264,6 +264,14 @@ def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_gra
     # a sanity signal on the timed path: one more step through the host-buffer call, logits read back
     with torch.cuda.stream(stream):
         nxt, lg = dec.step(tok.cpu().numpy(), want_logits=True)
+    # where a step's time goes: events around every launch of three eager steps (launches do not
+    # overlap in this mode, so the sum exceeds the step time above; shares are what it shows)
+    ctx.profile(True)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            one()
+    out["kernels_per_step"] = {k: {"launches": v[0] // 3, "us_each": round(v[1] / v[0] * 1e3, 2)} for k, v in ctx.profile_read().items()}
+    ctx.profile(False)
     out["logits_finite"] = bool(np.isfinite(lg).all())
     out["next_tokens"] = [int(t) for t in nxt[:4]]
     if not out["logits_finite"]:
@@ -303,6 +311,10 @@ def other_configs(cs, torch, ctx, stream, timed, hbm_peak, tf_peak, args):
                 e = {"us_per_matmul": per * 1e6, "GBps_compressed": alg / per / 1e9, "frac_hbm": alg / per / 1e9 / hbm_peak,
                      "TFLOPs_dense_equiv": 2.0 * rows * cols * m / per / 1e12}
                 e["frac_bf16_peak"] = e["TFLOPs_dense_equiv"] / tf_peak
+                ctx.profile(True)                       # one pass with events around every launch
+                step()
+                e["kernel_us"] = {k: round(v[1] / v[0] * 1e3, 2) for k, v in ctx.profile_read().items()}
+                ctx.profile(False)
                 ent[f"M{m}"] = e
                 del x, y
             for sg in copies:
@@ -496,7 +508,16 @@ def main():
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 qstep()
-            run_step, launch_mode = graph.replay, f"CUDA graph replay of the pass ({nseg} products, one list)"
+            # consecutive eager launches overlap through programmatic dependent launch (the next
+            # launch's CTAs move in as this one's leave), replays of a one-kernel graph do not: keep
+            # whichever form is faster on this box
+            graph.replay()
+            graph_ms = timed(graph.replay, args.steps, 3)
+            if graph_ms < eager_ms:
+                run_step, launch_mode = graph.replay, f"CUDA graph replay of the pass ({nseg} products, one list)"
+            else:
+                launch_mode = (f"one C-ABI call per pass ({nseg} products, one list), consecutive launches overlapping; "
+                               f"graph replay {graph_ms / args.steps:.4f} ms per step")
         except Exception as e:  # capture not possible: keep the eager loop
             launch_mode += f"; graph capture failed: {type(e).__name__}"
             torch.cuda.synchronize()
@@ -717,6 +738,8 @@ def main():
             decode[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
             torch.cuda.synchronize()
             continue
+        if world > 1:
+            continue        # the option lines are single-GPU figures
         try:
             # the cache OPTION as its own line (rows rounded to bf16, sums fp32); the figures above
             # stay on the fp32 cache, the reference's arithmetic

@@ -224,8 +224,8 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE")) ctx->gemv_queue = e[0] != '0';
         if (const char* e = std::getenv("CSDR_CACHE_2D")) ctx->cache_2d = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_QUEUE")) ctx->decoder_queue = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_TILE_TC")) ctx->tile_tc = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_FOLD")) ctx->decoder_fold = e[0] != '0';
-        if (const char* e = std::getenv("CSDR_FUSED_POLL_SLEEP")) ctx->fused_poll_sleep_ns = static_cast<uint32_t>(std::max(0, std::atoi(e)));
         if (const char* e = std::getenv("CSDR_QUEUE_POLL_SLEEP")) ctx->queue_poll_sleep_ns = static_cast<uint32_t>(std::max(0, std::atoi(e)));
         if (const char* e = std::getenv("CSDR_QUEUE_MIN_GROUP")) ctx->queue_min_group = static_cast<uint32_t>(std::max(1, std::atoi(e)));
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE_SINGLE")) ctx->gemv_queue_single = e[0] != '0';

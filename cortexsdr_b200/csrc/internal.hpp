@@ -118,9 +118,9 @@ struct csdr_context {
     bool fused_gemv = true;  // CSDR_FUSED_GEMV=0 selects the two-kernel path
     bool gemv_queue = true;  // CSDR_GEMV_QUEUE=0 keeps lists of products on single and grouped launches
     bool cache_2d = true;            // CSDR_CACHE_2D=0: wide batches on 2-D tiles stay on the factored CUDA-core kernels
-    uint32_t fused_poll_sleep_ns = 0;    // CSDR_FUSED_POLL_SLEEP: the same for the one-launch GEMV's partials
     uint32_t queue_poll_sleep_ns = 400;  // CSDR_QUEUE_POLL_SLEEP: pause between polls of the list kernel's dependent hand-overs
     uint32_t queue_min_group = 8;    // CSDR_QUEUE_MIN_GROUP: smallest same-x group the list kernel takes over grouped fused launches
+    bool tile_tc = true;             // CSDR_TILE_TC=0: 2-D tile products of a few tokens stay on the CUDA-core projection
     bool decoder_fold = true;        // CSDR_DECODER_FOLD=0: norms, residuals and SwiGLU of a short decoder step as kernels of their own
     bool decoder_queue = false;      // CSDR_DECODER_QUEUE=1: decoder steps of up to four tokens run a block as three launches
     bool gemv_queue_single = false;  // CSDR_GEMV_QUEUE_SINGLE=1 sends single products of at most 4 tokens there too
@@ -162,6 +162,9 @@ struct csdr_segment {
     // output row) whose cached bf16 planes feed the tensor-core kernel at wide batches - what the
     // reference's layer cache holds as fp32 after decompress(). Built on the first wide product.
     mutable std::shared_ptr<csdr_segment> dense;
+    // 2-D tile images only: the dictionary seen as n_atoms * tile_rows rows of tile_cols columns,
+    // the shape in which the tensor-core projection computes all tile products of a few tokens.
+    mutable std::shared_ptr<csdr_segment> tile_view;
     const uint16_t* codes_ptr() const {
         return static_cast<const uint16_t*>(codes->ptr) + codes_offset;
     }

@@ -44,10 +44,11 @@ struct Exchange;
 // With an exchange (tensor parallelism, at most 16 tokens) the finished rows go into every
 // rank's slot for this rank, at the offsets dx[i] - blk_base, `sums` (this rank's per-token sums
 // of squares, or null) ride along at offset 0, and the launch's last CTA raises the flags: the
-// projection and its share of the collective are one kernel.
+// projection and its share of the collective are one kernel. transposed (one dictionary, no
+// exchange): Dx leaves token-major, [token][atom] with dx_stride floats between token rows.
 void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
                          float* const* dx, uint32_t dx_stride, const Exchange* xch, const float* blk_base,
-                         const float* sums);
+                         const float* sums, bool transposed = false);
 
 // Up to four row-tile segments over the same activation planes: one projection launch and, for
 // a single token tile (M <= 16), one gather launch for the whole group. y = W x (+ bias)

@@ -114,7 +114,8 @@ struct Params {
     uint32_t tile_begin[kMaxGroup + 1];   // first atom tile (blockIdx.x) of each member
     float* dx_of[kMaxGroup];              // each member's Dx, [K_s][dx_stride]
     uint32_t M;             // tokens
-    uint32_t dx_stride;     // floats between Dx rows (>= M)
+    uint32_t dx_stride;     // floats between Dx rows (>= M); transposed: between token rows (>= atoms)
+    uint32_t transposed;    // Dx leaves token-major, [token][atom], instead of [atom][token]
     uint32_t n_tile;        // MMA N: 16, 32, 64 or 128
     uint32_t tmem_cols;     // power of two >= max(32, n_tile)
     uint32_t n_kb;          // C / 64
@@ -334,6 +335,14 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
     const size_t xslot = (static_cast<size_t>(xseq & 1u) * p.xch_ranks + p.xch_rank) * p.xch_blk;
     // a finished piece of Dx: four tokens of one atom, to the local buffer or to every rank
     auto emit = [&](uint32_t atom, uint32_t tok, const float4& v, bool vec) {
+        if (p.transposed) {   // local only: four tokens of one atom go to four token rows
+            float* dst = dx + static_cast<size_t>(tok) * p.dx_stride + atom;
+            dst[0] = v.x;
+            if (tok + 1u < p.M) dst[p.dx_stride] = v.y;
+            if (tok + 2u < p.M) dst[2u * static_cast<size_t>(p.dx_stride)] = v.z;
+            if (tok + 3u < p.M) dst[3u * static_cast<size_t>(p.dx_stride)] = v.w;
+            return;
+        }
         const size_t o = static_cast<size_t>(atom) * p.dx_stride + tok;
         if (p.xch_ranks > 1u) {
             const size_t xo = xslot + p.xch_off[seg] + o;
@@ -366,6 +375,19 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
         // one rank and an aligned token count: the tile is Dx itself; otherwise this rank's slab
         const bool direct = n_ranks == 1u && ((p.M | p.dx_stride) & 3u) == 0;
         const uint32_t n4 = N / 4u;
+        if (direct && p.transposed) {
+            // token-major out: four consecutive atoms of one token per store, so that a warp writes
+            // whole lines of a token's row
+            constexpr uint32_t r4n = kTileM / 4u;
+            for (uint32_t i = tid; i < N * r4n; i += kThreads) {
+                const uint32_t tc = i / r4n, r4 = i - tc * r4n;
+                if (tok0 + tc < p.M) {
+                    const float* src = ptile + static_cast<size_t>(r4 * 4u) * pstride + tc;
+                    const float4 v = make_float4(src[0], src[pstride], src[2u * pstride], src[3u * pstride]);
+                    *reinterpret_cast<float4*>(dx + static_cast<size_t>(tok0 + tc) * p.dx_stride + atom0 + r4 * 4u) = v;
+                }
+            }
+        } else
         for (uint32_t i = tid; i < kTileM * n4; i += kThreads) {
             const uint32_t row = i / n4, c4 = i - row * n4;
             const float4 v = *reinterpret_cast<const float4*>(ptile + static_cast<size_t>(row) * pstride + c4 * 4u);
@@ -571,8 +593,10 @@ XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_l
 
 void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
                          float* const* dx, uint32_t dx_stride, const Exchange* xch, const float* blk_base,
-                         const float* sums) {
+                         const float* sums, bool transposed) {
     using namespace tma_detail;
+    if (transposed && ((xch && xch->ranks > 1u) || n_seg != 1u))
+        throw Error(CSDR_ERR_INVALID_ARG, "a token-major projection is local and has one dictionary");
     if (n_seg == 0 || n_seg > kMaxGroup) throw Error(CSDR_ERR_LIMIT, "projection group holds 1 to 4 dictionaries");
     const uint32_t cols = segs[0]->g.cols;
     const bool has_lo = x.lo != nullptr;
@@ -659,6 +683,7 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
 
     p.M = M;
     p.dx_stride = dx_stride;
+    p.transposed = transposed ? 1u : 0u;
     p.n_tile = N;
     p.tmem_cols = std::max(32u, N);
     p.n_kb = n_kb;
@@ -701,7 +726,7 @@ void dx_tma_prepare(csdr_context* ctx, const csdr_segment* seg) { (void)tma_deta
 void launch_dx_tma(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs& a, float* dx, uint32_t dx_stride) {
     const uint32_t M = static_cast<uint32_t>(a.batch);
     const XPlanesView x = make_x_planes(ctx, a.x, a.x_dtype, a.x_layout, M, seg->g.cols);
-    launch_dx_tma_group(ctx, &seg, 1, x, M, &dx, dx_stride, nullptr, nullptr, nullptr);
+    launch_dx_tma_group(ctx, &seg, 1, x, M, &dx, dx_stride, nullptr, nullptr, nullptr, false);
 }
 
 }  // namespace csdr

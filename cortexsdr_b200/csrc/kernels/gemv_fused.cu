@@ -62,7 +62,6 @@ struct FusedParams {
     const float* norm_w;    // y = W rmsnorm(x; norm_w, norm_eps); needs the whole x per CTA
     float norm_eps;
     uint32_t swiglu;        // segment 1's rows leave as silu(segment 0's row) * row
-    uint32_t poll_sleep_ns; // pause between two looks at partials another CTA has yet to publish (0: none)
 };
 
 __device__ __forceinline__ void stamp(const FusedParams& p, int slot) {
@@ -375,7 +374,6 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
                         limit = 0u;
                         break;
                     }
-                    if (p.poll_sleep_ns) __nanosleep(p.poll_sleep_ns);   // leave the L2 queues to the CTAs still publishing
                 }
 #pragma unroll
                 for (int q = 0; q < 16; ++q) {
@@ -578,7 +576,6 @@ void launch_gemv_fused(csdr_context* ctx, const csdr_segment* const* segs, uint3
     p.seq = reinterpret_cast<unsigned long long*>(ctx->gemv_seq);
     p.status = ctx->status_word;
     p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
-    p.poll_sleep_ns = ctx->fused_poll_sleep_ns;
     p.spin_limit = ctx->spin_limit_gemv;  // each poll is an L2 round trip: about a second by default
     // Phase B: as many (row chunk, token group) jobs as there is work for; launch_t caps it at the grid.
     p.gather_ctas = std::max<uint32_t>(1u, static_cast<uint32_t>(static_cast<size_t>(max_rows) * mt / 32u));

@@ -324,11 +324,18 @@ hsdr_tile_project_kernel(const float* __restrict__ D, uint32_t VR /* K*Tr */, ui
 // CTA = (32 rows j) x (8 column-tile groups); group partials are summed through
 // shared memory in a fixed order.
 // ---------------------------------------------------------------------------
+// Where the tile products P[atom][column tile][row in tile][token] sit, in floats: the CUDA-core
+// projection writes them in that order; the tensor-core projection writes token-major rows
+// [token * n_ct + column tile][atom * Tr + row].
+struct TileProductStrides {
+    size_t atom, col_tile, row, token;
+};
+
 template <int MT>
 __global__ void __launch_bounds__(256)
 hsdr_tile_gather_kernel(const uint16_t* __restrict__ codes, uint32_t Tr, uint32_t n_ct,
                         uint32_t n_jchunks, uint32_t S, uint32_t k,
-                        const float* __restrict__ scales, const float* __restrict__ P, YView yv) {
+                        const float* __restrict__ scales, const float* __restrict__ P, TileProductStrides ps, YView yv) {
     extern __shared__ __align__(16) unsigned char tsm[];
     const uint32_t slots = S * k;
     const uint32_t tid = threadIdx.x;
@@ -357,15 +364,25 @@ hsdr_tile_gather_kernel(const uint16_t* __restrict__ codes, uint32_t Tr, uint32_
     if (j < Tr) {
         for (uint32_t bc = grp; bc < n_ct; bc += 8u) {
             const uint16_t* tc = cs + bc * slots;
-            for (uint32_t l = 0; l < S; ++l) {
-                const float gamma = sc[l];
-                for (uint32_t kk = 0; kk < k; ++kk) {
-                    const uint32_t code = tc[l * k + kk];
-                    const float scale = (code & 0x8000u) ? -gamma : gamma;
-                    const float* p = P + ((static_cast<size_t>(code & 0x7FFFu) * n_ct + bc) * Tr + j) * MT;
+            const float* pb = P + static_cast<size_t>(bc) * ps.col_tile + static_cast<size_t>(j) * ps.row;
+            // eight codes at a time: their products are L2 round trips and must be in flight
+            // together; the adds follow in slot order
+            for (uint32_t s0 = 0; s0 < slots; s0 += 8u) {
+                float v[8][MT], scale[8];
 #pragma unroll
-                    for (int b = 0; b < MT; ++b) acc[b] = fmaf(scale, p[b], acc[b]);
+                for (int q = 0; q < 8; ++q) {
+                    const uint32_t s_ = min(s0 + q, slots - 1u);
+                    const uint32_t code = tc[s_];
+                    const float gamma = sc[s_ / k];
+                    scale[q] = s0 + q < slots ? ((code & 0x8000u) ? -gamma : gamma) : 0.0f;
+                    const float* p = pb + static_cast<size_t>(code & 0x7FFFu) * ps.atom;
+#pragma unroll
+                    for (int b = 0; b < MT; ++b) v[q][b] = __ldg(p + static_cast<size_t>(b) * ps.token);
                 }
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+#pragma unroll
+                    for (int b = 0; b < MT; ++b) acc[b] = fmaf(scale[q], v[q][b], acc[b]);
             }
         }
     }
@@ -578,9 +595,39 @@ void matmul_tiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XView&
                             8u * 32u * MT * sizeof(float);
         ensure_smem(kern, smem);
         LaunchScope ls(ctx, KC_TILE_GATHER);
+        const TileProductStrides ps{static_cast<size_t>(g.n_col_tiles) * g.tile_rows * MT, static_cast<size_t>(g.tile_rows) * MT, MT, 1};
         kern<<<n_row_tiles * n_jchunks, 256, smem, ctx->stream>>>(
             seg->codes_ptr(), g.tile_rows, g.n_col_tiles, n_jchunks, g.n_stages, g.k,
-            static_cast<const float*>(seg->scales->ptr), P, yv);
+            static_cast<const float*>(seg->scales->ptr), P, ps, yv);
+        ls.done("hsdr_tile_gather_kernel");
+    }
+    if (seg->edges) {
+        LaunchScope ls(ctx, KC_EDGE);
+        hsdr_edge_kernel<MT><<<(g.rows + 7u) / 8u, 256, 0, ctx->stream>>>(
+            static_cast<const float*>(seg->edges->ptr), g.rows, g.cols, g.rows_full, g.cols_full, xv, yv);
+        ls.done("hsdr_edge_kernel");
+    }
+}
+
+// Tokens [b0, b0 + m) of a 2-D tile product whose tile products came from the tensor-core
+// projection: P_T[(token * n_ct + column tile)][atom * Tr + row].
+template <int MT>
+void tiles_gather_token_major(csdr_context* ctx, const csdr_segment* seg, const float* P_T, uint32_t b0, const XView& xv,
+                              const YView& yv) {
+    const Geometry& g = seg->g;
+    const size_t row_floats = static_cast<size_t>(g.n_atoms) * g.tile_rows;
+    auto kern = hsdr_tile_gather_kernel<MT>;
+    const uint32_t n_jchunks = (g.tile_rows + 31u) / 32u;
+    const uint32_t n_row_tiles = g.rows_full / g.tile_rows;
+    const size_t cap16 = (static_cast<size_t>(g.n_col_tiles) * g.slots() * 2u + 31u) >> 4;
+    const size_t smem = cap16 * 16u + ((g.n_stages + 3u) & ~3u) * sizeof(float) + 8u * 32u * MT * sizeof(float);
+    ensure_smem(kern, smem);
+    {
+        LaunchScope ls(ctx, KC_TILE_GATHER);
+        const TileProductStrides ps{g.tile_rows, row_floats, 1, static_cast<size_t>(g.n_col_tiles) * row_floats};
+        kern<<<n_row_tiles * n_jchunks, 256, smem, ctx->stream>>>(
+            seg->codes_ptr(), g.tile_rows, g.n_col_tiles, n_jchunks, g.n_stages, g.k, static_cast<const float*>(seg->scales->ptr),
+            P_T + static_cast<size_t>(b0) * g.n_col_tiles * row_floats, ps, yv);
         ls.done("hsdr_tile_gather_kernel");
     }
     if (seg->edges) {
@@ -698,6 +745,43 @@ void launch_matmul(csdr_context* ctx, const csdr_segment* seg, const MatmulArgs&
     const size_t budget = std::min<size_t>(ctx->smem_optin, 200u * 1024u);
     const bool fast_rows = g.row_tiles() && (g.cols % 4u == 0);
     const bool fast_tiles = !fast_rows && (g.tile_cols % 4u == 0);
+    if (!fast_rows && ctx->tile_tc && ctx->tensor_cores && ctx->tma && g.cols == g.cols_full && g.tile_cols % 8u == 0 &&
+        (static_cast<size_t>(g.n_atoms) * g.tile_rows) % 128u == 0 &&
+        a.batch * g.n_col_tiles >= ctx->tc_min_batch &&
+        a.batch * g.n_col_tiles * g.n_atoms * static_cast<size_t>(g.tile_rows) * 4u <= (1ull << 30)) {
+        // 2-D tiles, a few tokens: the tile products are ONE GEMM - the dictionary read as
+        // K * Tr rows of Tc columns against the activations read as batch * n_ct tokens of Tc
+        // columns (a token-major activation row IS its n_ct column tiles one after the other) -
+        // on the tensor cores, out in token-major rows the gather reads with unit stride.
+        if (!seg->tile_view) {
+            auto tv = std::make_shared<csdr_segment>();
+            tv->ctx = ctx;
+            tv->g.rows = tv->g.rows_full = tv->g.n_tiles = 1;
+            tv->g.cols = tv->g.cols_full = tv->g.tile_cols = g.tile_cols;
+            tv->g.tile_rows = tv->g.n_col_tiles = 1;
+            tv->g.n_atoms = g.n_atoms * g.tile_rows;
+            tv->g.n_stages = tv->g.k = 1;
+            tv->atoms = seg->atoms;
+            seg->tile_view = tv;
+        }
+        const csdr_segment* tv = seg->tile_view.get();
+        if (dx_tma_supported(ctx, tv, a.batch * g.n_col_tiles)) {
+            const uint32_t M = static_cast<uint32_t>(a.batch), n_tok = M * g.n_col_tiles;
+            const XPlanesView xp = make_x_planes(ctx, a.x, a.x_dtype, a.x_layout, M, g.cols);
+            float* P_T = static_cast<float*>(ctx->scratch_get(7, static_cast<size_t>(n_tok) * tv->g.n_atoms * sizeof(float)));
+            launch_dx_tma_group(ctx, &tv, 1, xp, n_tok, &P_T, tv->g.n_atoms, nullptr, nullptr, nullptr, true);
+            for (size_t b0 = 0; b0 < a.batch; b0 += 4) {
+                const uint32_t m = static_cast<uint32_t>(std::min<size_t>(4, a.batch - b0));
+                XView xv{a.x, a.x_dtype, a.x_layout, g.cols, M, static_cast<uint32_t>(b0), m};
+                YView yv{a.y, a.y_layout, g.rows, M, static_cast<uint32_t>(b0), m, a.bias};
+                dispatch_mt(pick_mt(m), [&](auto mt) {
+                    constexpr int MT = decltype(mt)::value;
+                    if constexpr (MT <= 4) tiles_gather_token_major<MT>(ctx, seg, P_T, static_cast<uint32_t>(b0), xv, yv);
+                });
+            }
+            return;
+        }
+    }
     int mt_cap = 0;
     if (fast_rows) {
         uint32_t nsplit = std::min<uint32_t>(8u, std::max<uint32_t>(1u, (g.cols + 1023u) / 1024u));
