@@ -635,7 +635,9 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     }
     const int max_cluster = ctx->tma_max_cluster;
     uint32_t stages = std::min<uint32_t>(kMaxStages, static_cast<uint32_t>((smem_max - 1024u) / stage_bytes));
-    stages = std::max(1u, stages);
+    // no more stages than column blocks: a short reduction (2-D tile products: two blocks) leaves
+    // room for a second CTA on the SM, whose set-up then overlaps this one's epilogue
+    stages = std::max(1u, std::min(stages, n_kb));
     const size_t smem = std::max<size_t>(static_cast<size_t>(stages) * stage_bytes,
                                          static_cast<size_t>(kTileM) * (N + 4u) * 4u) + 1024u;
 

@@ -46,6 +46,7 @@
 // roles of the CTA stop waiting, and the kernel returns. All CTAs must be resident (grid = SM
 // count, one per SM).
 #include <algorithm>
+#include <cstdlib>
 
 #include "../internal.hpp"
 #include "gemv_queue.hpp"
@@ -636,7 +637,12 @@ uint32_t dxs_bytes_for(uint32_t max_k, int mt) { return (max_k * static_cast<uin
 size_t tail_bytes_for(uint32_t max_k, int mt, uint32_t max_code_bytes) {
     return static_cast<size_t>(kGatherWarps) * (dxs_bytes_for(max_k, mt) + 2u * codes_bytes_for(max_code_bytes) + 128u);
 }
-size_t smem_budget(const csdr_context* ctx) { return std::min<size_t>(ctx->smem_optin, 216u * 1024u); }
+// All the shared memory a CTA can opt into, less the kernel's static part and the per-CTA reserve:
+// one CTA per SM anyway, and every stage more is 32 KB more of weights in flight.
+size_t smem_budget(const csdr_context* ctx) {
+    if (const char* e = std::getenv("CSDR_QUEUE_SMEM_KB")) return std::min<size_t>(ctx->smem_optin, static_cast<size_t>(std::atoi(e)) * 1024u);
+    return ctx->smem_optin > 4096u ? ctx->smem_optin - 4096u : ctx->smem_optin;
+}
 uint32_t rows_per_cta_for(const csdr_context* ctx, uint32_t rows) {
     const uint32_t G = static_cast<uint32_t>(ctx->sm_count);
     return ((rows + G - 1u) / G + 7u) & ~7u;

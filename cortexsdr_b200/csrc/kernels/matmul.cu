@@ -350,6 +350,10 @@ hsdr_tile_gather_kernel(const uint16_t* __restrict__ codes, uint32_t Tr, uint32_
     uint4* cs16 = reinterpret_cast<uint4*>(tsm);
     float* sc = reinterpret_cast<float*>(tsm + static_cast<size_t>(cap16) * 16u);
     float* red = sc + ((S + 3u) & ~3u);            // [8][32][MT]
+    float* mine = red + 8u * 32u * MT;             // [32][MT]: this CTA's sums, for the cluster's first CTA
+    // grid y = cluster size: the column tiles of a row tile are dealt to the CTAs of a cluster when
+    // there are too few row tiles to fill the GPU
+    const uint32_t crank = blockIdx.y, csize = gridDim.y;
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(codes) + aligned0);
     for (uint32_t i = tid; i < n16; i += 256) cs16[i] = src[i];
     for (uint32_t i = tid; i < S; i += 256) sc[i] = scales[i];
@@ -362,7 +366,7 @@ hsdr_tile_gather_kernel(const uint16_t* __restrict__ codes, uint32_t Tr, uint32_
 #pragma unroll
     for (int b = 0; b < MT; ++b) acc[b] = 0.0f;
     if (j < Tr) {
-        for (uint32_t bc = grp; bc < n_ct; bc += 8u) {
+        for (uint32_t bc = crank * 8u + grp; bc < n_ct; bc += 8u * csize) {
             const uint16_t* tc = cs + bc * slots;
             const float* pb = P + static_cast<size_t>(bc) * ps.col_tile + static_cast<size_t>(j) * ps.row;
             // eight codes at a time: their products are L2 round trips and must be in flight
@@ -394,14 +398,29 @@ hsdr_tile_gather_kernel(const uint16_t* __restrict__ codes, uint32_t Tr, uint32_
         float s = 0.0f;
 #pragma unroll
         for (int g = 0; g < 8; ++g) s += red[(g * 32u + jj) * MT + b];
-        const uint32_t jr = jc * 32u + jj;
-        if (jr < Tr && b < yv.M) {
-            const uint32_t r = br * Tr + jr;
-            if (yv.bias) s += yv.bias[r];
-            yv.y[y_index(yv, r, b)] = s;
+        mine[t] = s;
+    }
+    if (csize > 1u) cg::this_cluster().sync();
+    else __syncthreads();
+    if (crank == 0u) {
+        for (uint32_t t = tid; t < 32u * MT; t += 256) {
+            const uint32_t jj = t / MT, b = t - jj * MT;
+            float s = mine[t];
+            for (uint32_t r = 1; r < csize; ++r) s += cg::this_cluster().map_shared_rank(mine, r)[t];   // rank order
+            const uint32_t jr = jc * 32u + jj;
+            if (jr < Tr && b < yv.M) {
+                const uint32_t row = br * Tr + jr;
+                if (yv.bias) s += yv.bias[row];
+                yv.y[y_index(yv, row, b)] = s;
+            }
         }
     }
+    if (csize > 1u) cg::this_cluster().sync();   // the peers' shared memory must outlive the reads above
 }
+
+// One launch of the gather over tile products laid out as `ps` says.
+template <int MT>
+void launch_tile_gather(csdr_context* ctx, const csdr_segment* seg, const float* P, const TileProductStrides& ps, const YView& yv);
 
 // ---------------------------------------------------------------------------
 // Raw edge strips (stored fp32 verbatim): rows < R_full add their top-right strip's
@@ -569,6 +588,37 @@ void matmul_rowtiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XVi
 }
 
 template <int MT>
+void launch_tile_gather(csdr_context* ctx, const csdr_segment* seg, const float* P, const TileProductStrides& ps, const YView& yv) {
+    const Geometry& g = seg->g;
+    auto kern = hsdr_tile_gather_kernel<MT>;
+    const uint32_t n_jchunks = (g.tile_rows + 31u) / 32u;
+    const uint32_t n_row_tiles = g.rows_full / g.tile_rows;
+    const size_t cap16 = (static_cast<size_t>(g.n_col_tiles) * g.slots() * 2u + 31u) >> 4;
+    const size_t smem = cap16 * 16u + ((g.n_stages + 3u) & ~3u) * sizeof(float) + 9u * 32u * MT * sizeof(float);
+    ensure_smem(kern, smem);
+    const uint32_t ctas = n_row_tiles * n_jchunks, sms = static_cast<uint32_t>(ctx->sm_count);
+    uint32_t csplit = 1;
+    while (csplit < 8u && ctas * csplit < 2u * sms && g.n_col_tiles >= 16u * csplit) csplit *= 2u;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas, csplit, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = csplit;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = csplit > 1u ? 1 : 0;
+    LaunchScope ls(ctx, KC_TILE_GATHER);
+    CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, seg->codes_ptr(), static_cast<uint32_t>(g.tile_rows), static_cast<uint32_t>(g.n_col_tiles),
+                                 n_jchunks, static_cast<uint32_t>(g.n_stages), static_cast<uint32_t>(g.k),
+                                 static_cast<const float*>(seg->scales->ptr), P, ps, yv));
+    ls.done("hsdr_tile_gather_kernel");
+}
+
+template <int MT>
 void matmul_tiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XView& xv,
                         const YView& yv) {
     const Geometry& g = seg->g;
@@ -586,21 +636,9 @@ void matmul_tiles_chunk(csdr_context* ctx, const csdr_segment* seg, const XView&
             xv, P);
         ls.done("hsdr_tile_project_kernel");
     }
-    {
-        auto kern = hsdr_tile_gather_kernel<MT>;
-        const uint32_t n_jchunks = (g.tile_rows + 31u) / 32u;
-        const uint32_t n_row_tiles = g.rows_full / g.tile_rows;
-        const size_t cap16 = (static_cast<size_t>(g.n_col_tiles) * g.slots() * 2u + 31u) >> 4;
-        const size_t smem = cap16 * 16u + ((g.n_stages + 3u) & ~3u) * sizeof(float) +
-                            8u * 32u * MT * sizeof(float);
-        ensure_smem(kern, smem);
-        LaunchScope ls(ctx, KC_TILE_GATHER);
-        const TileProductStrides ps{static_cast<size_t>(g.n_col_tiles) * g.tile_rows * MT, static_cast<size_t>(g.tile_rows) * MT, MT, 1};
-        kern<<<n_row_tiles * n_jchunks, 256, smem, ctx->stream>>>(
-            seg->codes_ptr(), g.tile_rows, g.n_col_tiles, n_jchunks, g.n_stages, g.k,
-            static_cast<const float*>(seg->scales->ptr), P, ps, yv);
-        ls.done("hsdr_tile_gather_kernel");
-    }
+    launch_tile_gather<MT>(ctx, seg, P,
+                           TileProductStrides{static_cast<size_t>(g.n_col_tiles) * g.tile_rows * MT, static_cast<size_t>(g.tile_rows) * MT, MT, 1},
+                           yv);
     if (seg->edges) {
         LaunchScope ls(ctx, KC_EDGE);
         hsdr_edge_kernel<MT><<<(g.rows + 7u) / 8u, 256, 0, ctx->stream>>>(
@@ -616,20 +654,8 @@ void tiles_gather_token_major(csdr_context* ctx, const csdr_segment* seg, const 
                               const YView& yv) {
     const Geometry& g = seg->g;
     const size_t row_floats = static_cast<size_t>(g.n_atoms) * g.tile_rows;
-    auto kern = hsdr_tile_gather_kernel<MT>;
-    const uint32_t n_jchunks = (g.tile_rows + 31u) / 32u;
-    const uint32_t n_row_tiles = g.rows_full / g.tile_rows;
-    const size_t cap16 = (static_cast<size_t>(g.n_col_tiles) * g.slots() * 2u + 31u) >> 4;
-    const size_t smem = cap16 * 16u + ((g.n_stages + 3u) & ~3u) * sizeof(float) + 8u * 32u * MT * sizeof(float);
-    ensure_smem(kern, smem);
-    {
-        LaunchScope ls(ctx, KC_TILE_GATHER);
-        const TileProductStrides ps{g.tile_rows, row_floats, 1, static_cast<size_t>(g.n_col_tiles) * row_floats};
-        kern<<<n_row_tiles * n_jchunks, 256, smem, ctx->stream>>>(
-            seg->codes_ptr(), g.tile_rows, g.n_col_tiles, n_jchunks, g.n_stages, g.k, static_cast<const float*>(seg->scales->ptr),
-            P_T + static_cast<size_t>(b0) * g.n_col_tiles * row_floats, ps, yv);
-        ls.done("hsdr_tile_gather_kernel");
-    }
+    launch_tile_gather<MT>(ctx, seg, P_T + static_cast<size_t>(b0) * g.n_col_tiles * row_floats,
+                           TileProductStrides{g.tile_rows, row_floats, 1, static_cast<size_t>(g.n_col_tiles) * row_floats}, yv);
     if (seg->edges) {
         LaunchScope ls(ctx, KC_EDGE);
         hsdr_edge_kernel<MT><<<(g.rows + 7u) / 8u, 256, 0, ctx->stream>>>(

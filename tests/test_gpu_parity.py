@@ -572,3 +572,46 @@ def test_queue_chain_of_dependent_products(ctx, oracle, batch):
     with pytest.raises(Exception):           # a task may only point backwards
         cs.Segment.matmul_queue_device([(segs[0], x.data_ptr(), F, T, batch, ys[0].data_ptr(), T, 0, 0)])
     del prepared
+
+
+@pytest.mark.parametrize("batch", [1, 3, 7, 13])
+def test_2d_tile_products_on_the_tensor_cores(ctx, oracle, batch, monkeypatch):
+    """2-D tiles below 16 tokens, no column edge strip, tile width a multiple of 8 and
+    n_atoms * tile_rows a multiple of 128: every tile product comes from ONE tensor-core GEMM
+    (dictionary as n_atoms * tile_rows rows of tile_cols columns against batch * n_col_tiles
+    "tokens"), written token-major for the gather. Against decompress + dense of the oracle, and
+    against the CUDA-core projection (CSDR_TILE_TC=0) on the same payload; a row edge strip and
+    bf16 token-major activations on device pointers included."""
+    import torch
+    from tests import synth
+    pay = synth.hsdr_payload(200, 256, tile_rows=32, tile_cols=64, n_atoms=32, k=4, seed=21)   # 8 edge rows
+    W = oracle.decompress(pay)
+    x = np.random.default_rng(batch).normal(0, 1, (256, batch)).astype(np.float32)
+    want = oracle.dense_matmul(W, x, batch)
+    seg = cs.Segment.from_payload(pay, ctx)
+    l0 = ctx.launch_count
+    got = seg.matmul(x, batch, allow_2d=True)
+    launches_tc = ctx.launch_count - l0
+    e = rel_err(got, want)
+    assert e[0] < TOL and e[1] < TOL, e
+    # bf16 activations, token-major, on device pointers
+    xt = torch.from_numpy(np.ascontiguousarray(x.T)).cuda().to(torch.bfloat16)
+    yt = torch.empty((batch, 200), device="cuda", dtype=torch.float32)
+    seg.matmul_device(xt.data_ptr(), cs.DTYPE_BF16, cs.TOKEN_MAJOR, batch, yt.data_ptr(), cs.TOKEN_MAJOR)
+    ctx.synchronize()
+    want16 = oracle.dense_matmul(W, np.ascontiguousarray(xt.float().cpu().numpy().T), batch)
+    e = rel_err(yt.cpu().numpy().T, want16)
+    assert e[0] < TOL and e[1] < TOL, e
+    seg.close()
+    monkeypatch.setenv("CSDR_TILE_TC", "0")
+    plain = cs.Context(0)
+    seg2 = cs.Segment.from_payload(pay, plain)
+    l0 = plain.launch_count
+    got2 = seg2.matmul(x, batch, allow_2d=True)
+    launches_plain = plain.launch_count - l0
+    e = rel_err(got2, want)
+    assert e[0] < TOL and e[1] < TOL, e
+    assert np.abs(got - got2).max() <= 1e-4 * np.abs(want).max()
+    assert launches_tc != launches_plain or batch <= 4      # the two routes differ in their launches
+    seg2.close()
+    plain.close()
