@@ -566,8 +566,11 @@ def main():
     ctx.profile(False)
     if "hsdr_gemv_queue" in prof:
         # one launch per pass: its duration between two events on the stream, averaged
+        # the launch's duration: the timed region (CUDA events around it on the launching stream)
+        # divided by the launches in it; beside it one launch bracketed by events, nothing overlapping
         n_q, ms_q = prof["hsdr_gemv_queue"]
-        us_launch = ms_q / max(n_q, 1) * 1e3
+        us_isolated = ms_q / max(n_q, 1) * 1e3
+        us_launch = ms / args.steps / launches_per_step * 1e3
         per_launch = bytes1 * nseg / launches_per_step
         achieved = per_launch / (us_launch * 1e-6) / 1e9
         roofline = {"bound": "hbm", "kernel": "hsdr_gemv_queue_kernel", "achieved": achieved, "peak": hbm_peak,
@@ -577,9 +580,10 @@ def main():
                     "traffic": QUEUE_DRAM_BYTES_PER_TASK_NCU * nseg / launches_per_step
                     if (R, C) == (11008, 4096) and QUEUE_DRAM_BYTES_PER_TASK_NCU else None,
                     "alg_bytes_per_launch": per_launch, "us_per_launch": us_launch,
+                    "us_per_launch_isolated": us_isolated,
                     "tasks_per_launch": nseg / launches_per_step,
-                    "whole_pass_frac": value / world / hbm_peak,
-                    "note": "achieved = algorithmic bytes of one launch / its event-bracketed duration"}
+                    "note": "achieved = algorithmic bytes of one launch / (timed region / launches in it); "
+                            "isolated = one launch between two events, nothing overlapping it"}
     elif "hsdr_gemv_fused" in prof:
         # one kernel per matmul: its launches overlap (programmatic dependent launch), so the
         # per-launch duration is the timed region divided by the launches in it
@@ -740,14 +744,15 @@ def main():
             continue
         if world > 1:
             continue        # the option lines are single-GPU figures
-        try:
-            # the cache OPTION as its own line (rows rounded to bf16, sums fp32); the figures above
-            # stay on the fp32 cache, the reference's arithmetic
-            decode[name + "_bf16_kv"] = decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm,
-                                                      not args.no_graph, kv_dtype="bf16")
-        except Exception as e:
-            decode[name + "_bf16_kv"] = {"error": f"{type(e).__name__}: {e}"[:300]}
-            torch.cuda.synchronize()
+        for kvd in ("f16", "bf16"):
+            try:
+                # the 16-bit cache OPTIONS as lines of their own (rows rounded on entry, sums fp32); the
+                # figures above stay on the fp32 cache, the reference's arithmetic
+                decode[f"{name}_{kvd}_kv"] = decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm,
+                                                           not args.no_graph, kv_dtype=kvd)
+            except Exception as e:
+                decode[f"{name}_{kvd}_kv"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                torch.cuda.synchronize()
         if world == 1:
             try:
                 decode[name + "_shared_dicts"] = decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm,

@@ -714,7 +714,7 @@ class Decoder:
     def __init__(self, loader: SDRModelLoader, *, n_layers, hidden, q_heads, kv_heads, head_dim,
                  inter, vocab, max_seq, max_batch=1, rms_eps=1e-5, rope_theta=1e6, comm: "NcclComm | None" = None,
                  all_gather=None, kv_dtype="f32"):
-        """kv_dtype: "f32" (the reference's arithmetic) or "bf16" (cache rows rounded to bf16, sums fp32).
+        """kv_dtype: "f32" (the reference's arithmetic), "f16" or "bf16" (cache rows rounded to 16 bits, sums fp32).
         all_gather: a callable bytes -> list[bytes] (one entry per rank, rank order) supplied by
         the host program, e.g. built on torch.distributed.all_gather_object. When given with a
         communicator of 2 to 8 ranks, the ranks exchange CUDA IPC handles through it and sum their
@@ -723,7 +723,7 @@ class Decoder:
         self.cfg = DecoderConfig(n_layers, hidden, q_heads, kv_heads, head_dim, inter, vocab,
                                  max_seq, max_batch, rms_eps, rope_theta, comm.rank if comm else 0,
                                  comm.world if comm else 1, comm._h if comm else None,
-                                 {"f32": 0, "bf16": 1}[kv_dtype])
+                                 {"f32": 0, "bf16": 1, "f16": 2}[kv_dtype])
         h = C.c_void_p()
         _check(self.ctx._lib.csdr_decoder_create(loader._h, C.byref(self.cfg), C.byref(h)))
         self._h = h

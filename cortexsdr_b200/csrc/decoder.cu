@@ -97,7 +97,7 @@ struct csdr_decoder {
     std::vector<Layer> layers;
     DevPtr kcache, vcache;  // [layer][seq][pos][kv head (local)][head_dim]
     size_t cache_layer_stride = 0;   // elements
-    int kv_dtype = CSDR_DTYPE_F32;   // fp32 as the reference computes, or bf16 (half the cache traffic; sums stay fp32)
+    int kv_dtype = CSDR_DTYPE_F32;   // fp32 as the reference computes, or fp16 / bf16 (half the cache traffic; sums stay fp32)
     size_t kv_es = 4;
     std::vector<int32_t> pos_host;
     // token selection of the reference's generation loop (off: plain argmax): temperature and a
@@ -672,10 +672,10 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
         d->T_max = std::max(c.max_seq, c.max_batch);
         const size_t T = d->T_max;
         d->cache_layer_stride = static_cast<size_t>(c.max_batch) * c.max_seq * d->KVD_l;
-        if (c.kv_dtype != CSDR_DTYPE_F32 && c.kv_dtype != CSDR_DTYPE_BF16)
-            throw Error(CSDR_ERR_INVALID_ARG, "decoder: kv_dtype must be CSDR_DTYPE_F32 or CSDR_DTYPE_BF16");
+        if (c.kv_dtype != CSDR_DTYPE_F32 && c.kv_dtype != CSDR_DTYPE_BF16 && c.kv_dtype != CSDR_DTYPE_F16)
+            throw Error(CSDR_ERR_INVALID_ARG, "decoder: kv_dtype must be CSDR_DTYPE_F32, CSDR_DTYPE_F16 or CSDR_DTYPE_BF16");
         d->kv_dtype = static_cast<int>(c.kv_dtype);
-        d->kv_es = d->kv_dtype == CSDR_DTYPE_BF16 ? 2 : 4;
+        d->kv_es = d->kv_dtype == CSDR_DTYPE_F32 ? 4 : 2;
         d->kcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * d->kv_es);
         d->vcache = dev_alloc(ctx, d->cache_layer_stride * c.n_layers * d->kv_es);
         d->pos_host.assign(c.max_batch, 0);

@@ -11,6 +11,7 @@
 //   argmax_kernel         greedy pick over the logits row
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 #include <cfloat>
@@ -188,6 +189,8 @@ template <>
 __device__ __forceinline__ float to_kv<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 to_kv<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half to_kv<__half>(float v) { return __float2half_rn(v); }
 
 template <typename KV>
 __global__ void __launch_bounds__(256)
@@ -283,21 +286,23 @@ __device__ __forceinline__ void load_row(const float* p, float (&v)[VPL]) {
     }
 }
 
-// A lane's share of one cache row. fp32 cache: the values. bf16 cache (an option; sums stay fp32):
-// the packed words, widened where they are used (a bf16 is the upper half of its fp32), and twice
-// the keys per step so that a warp keeps as many bytes in flight.
+// A lane's share of one cache row. fp32 cache: the values. 16-bit caches (options: fp16, bf16; scores
+// and sums stay fp32): the packed words, widened where they are used, and twice the keys per step
+// so that a warp keeps as many bytes in flight.
+template <typename KV>
+__device__ __forceinline__ float widen16(uint32_t pair, int odd);
+template <>
+__device__ __forceinline__ float widen16<__nv_bfloat16>(uint32_t pair, int odd) {   // a bf16 is the upper half of its fp32
+    return __uint_as_float(odd ? (pair & 0xFFFF0000u) : (pair << 16));
+}
+template <>
+__device__ __forceinline__ float widen16<__half>(uint32_t pair, int odd) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(odd ? pair >> 16 : pair & 0xFFFFu)));
+}
 template <typename KV, int VPL>
-struct CacheRow;
-template <int VPL>
-struct CacheRow<float, VPL> {
-    float v[VPL];
-    __device__ __forceinline__ void load(const float* p) { load_row<VPL>(p, v); }
-    __device__ __forceinline__ float get(int e) const { return v[e]; }
-};
-template <int VPL>
-struct CacheRow<__nv_bfloat16, VPL> {
+struct CacheRow {
     uint32_t w[(VPL + 1) / 2];
-    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    __device__ __forceinline__ void load(const KV* p) {
         if constexpr (VPL == 1) {
             w[0] = __ldg(reinterpret_cast<const unsigned short*>(p));
         } else if constexpr (VPL == 2) {
@@ -317,12 +322,47 @@ struct CacheRow<__nv_bfloat16, VPL> {
             }
         }
     }
-    __device__ __forceinline__ float get(int e) const {
-        const uint32_t x = w[e >> 1];
-        if constexpr (VPL == 1) return __uint_as_float(x << 16);
-        return __uint_as_float((e & 1) ? (x & 0xFFFF0000u) : (x << 16));
-    }
+    __device__ __forceinline__ float get(int e) const { return widen16<KV>(w[e >> 1], e & 1); }
 };
+template <int VPL>
+struct CacheRow<float, VPL> {
+    float v[VPL];
+    __device__ __forceinline__ void load(const float* p) { load_row<VPL>(p, v); }
+    __device__ __forceinline__ float get(int e) const { return v[e]; }
+};
+
+// Sums over the warp of N values per lane (N = 4 or 8), all N sums back in every lane. The first
+// rounds halve the payload instead of carrying every value through every round: lanes whose bit
+// `off` is set keep the upper half of the values and hand the lower half over, and the other way
+// round; 9 + 8 shuffles for eight values instead of 40.
+template <int N>
+__device__ __forceinline__ void warp_sums(float (&s)[N], uint32_t lane) {
+    static_assert(N == 4 || N == 8, "four or eight values");
+    int n = N;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        if (n > 1) {
+            const int half = n / 2;
+            const bool upper = (lane & static_cast<uint32_t>(off)) != 0u;
+#pragma unroll
+            for (int i = 0; i < N / 2; ++i) {
+                if (i < half) {
+                    const float send = upper ? s[i] : s[i + half];
+                    const float keep = upper ? s[i + half] : s[i];
+                    s[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, off);
+                }
+            }
+            n = half;
+        } else {
+            s[0] += __shfl_xor_sync(0xFFFFFFFFu, s[0], off);
+        }
+    }
+    // lane l now holds the sum of value number (l >> shift) & (N - 1)
+    constexpr int shift = N == 8 ? 2 : 3;
+    const float mine = s[0];
+#pragma unroll
+    for (int u = 0; u < N; ++u) s[u] = __shfl_sync(0xFFFFFFFFu, mine, u << shift);
+}
 
 // WARPS warps split the keys of one (token, head); few (token, head) pairs (batched decode
 // against a long context) take more warps each so that enough K/V rows are in flight per SM.
@@ -377,23 +417,31 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
             for (int e = 0; e < VPL; ++e) d = fmaf(qv[e], kv[u].get(e), d);
             s[u] = d;
         }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-            for (int u = 0; u < kKeys; ++u) s[u] += __shfl_xor_sync(0xFFFFFFFFu, s[u], off);
+        warp_sums<kKeys>(s, lane);
+        // the keys of a step join the running softmax together: one new maximum, one correction of
+        // what has been summed so far, then every key's weight
+        float m_new = m;
 #pragma unroll
         for (int u = 0; u < kKeys; ++u) {
-            if (j0 + u < n_keys) {
-                const float sc = s[u] * scale;
-                const float m_new = fmaxf(m, sc);
-                const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first key
-                const float p = expf(sc - m_new);
-                l = l * corr + p;
-#pragma unroll
-                for (int e = 0; e < VPL; ++e) acc[e] = fmaf(p, vv[u].get(e), acc[e] * corr);
-                m = m_new;
-            }
+            s[u] = j0 + u < n_keys ? s[u] * scale : -INFINITY;
+            m_new = fmaxf(m_new, s[u]);
         }
+        const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first step; the step's first key is always valid
+        float psum = 0.0f;
+#pragma unroll
+        for (int u = 0; u < kKeys; ++u) {
+            s[u] = expf(s[u] - m_new);        // exp(-inf) = 0 for the keys past the end
+            psum += s[u];
+        }
+        l = fmaf(l, corr, psum);
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) {
+            float a = acc[e] * corr;
+#pragma unroll
+            for (int u = 0; u < kKeys; ++u) a = fmaf(s[u], vv[u].get(e), a);
+            acc[e] = a;
+        }
+        m = m_new;
     }
     if (lane == 0) {
         sm_m[warp] = m;
@@ -637,6 +685,9 @@ void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, 
     if (kv_dtype == CSDR_DTYPE_BF16)
         launch_pdl(ctx, rope_cache_kernel<__nv_bfloat16>, dim3(T, std::min(slices, 16u)), dim3(256), q, k, v,
                    static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), seq_of, pos_of, QH, KVH, HD, max_seq, theta);
+    else if (kv_dtype == CSDR_DTYPE_F16)
+        launch_pdl(ctx, rope_cache_kernel<__half>, dim3(T, std::min(slices, 16u)), dim3(256), q, k, v, static_cast<__half*>(kc),
+                   static_cast<__half*>(vc), seq_of, pos_of, QH, KVH, HD, max_seq, theta);
     else
         launch_pdl(ctx, rope_cache_kernel<float>, dim3(T, std::min(slices, 16u)), dim3(256), q, k, v, static_cast<float*>(kc),
                    static_cast<float*>(vc), seq_of, pos_of, QH, KVH, HD, max_seq, theta);
@@ -682,6 +733,9 @@ void op_attention(csdr_context* ctx, const float* q, const void* kc, const void*
         if (kv_dtype == CSDR_DTYPE_BF16) {                                                  \
             if (split > 1) launch(attention_kernel<__nv_bfloat16, V, W, true>, W);          \
             else launch(attention_kernel<__nv_bfloat16, V, W, false>, W);                   \
+        } else if (kv_dtype == CSDR_DTYPE_F16) {                                            \
+            if (split > 1) launch(attention_kernel<__half, V, W, true>, W);                 \
+            else launch(attention_kernel<__half, V, W, false>, W);                          \
         } else {                                                                            \
             if (split > 1) launch(attention_kernel<float, V, W, true>, W);                  \
             else launch(attention_kernel<float, V, W, false>, W);                           \

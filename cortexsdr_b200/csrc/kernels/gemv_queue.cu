@@ -639,10 +639,7 @@ size_t tail_bytes_for(uint32_t max_k, int mt, uint32_t max_code_bytes) {
 }
 // All the shared memory a CTA can opt into, less the kernel's static part and the per-CTA reserve:
 // one CTA per SM anyway, and every stage more is 32 KB more of weights in flight.
-size_t smem_budget(const csdr_context* ctx) {
-    if (const char* e = std::getenv("CSDR_QUEUE_SMEM_KB")) return std::min<size_t>(ctx->smem_optin, static_cast<size_t>(std::atoi(e)) * 1024u);
-    return ctx->smem_optin > 4096u ? ctx->smem_optin - 4096u : ctx->smem_optin;
-}
+size_t smem_budget(const csdr_context* ctx) { return ctx->smem_optin > 4096u ? ctx->smem_optin - 4096u : ctx->smem_optin; }
 uint32_t rows_per_cta_for(const csdr_context* ctx, uint32_t rows) {
     const uint32_t G = static_cast<uint32_t>(ctx->sm_count);
     return ((rows + G - 1u) / G + 7u) & ~7u;

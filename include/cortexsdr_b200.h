@@ -54,7 +54,8 @@ enum {
     CSDR_ERR_LIMIT = -12        /* size beyond a documented fixed maximum */
 };
 
-enum { CSDR_DTYPE_F32 = 0, CSDR_DTYPE_BF16 = 1 };
+enum { CSDR_DTYPE_F32 = 0, CSDR_DTYPE_BF16 = 1,
+       CSDR_DTYPE_F16 = 2 /* KV-cache element type only; activations are fp32 or bf16 */ };
 enum { CSDR_LAYOUT_FEATURE_MAJOR = 0, CSDR_LAYOUT_TOKEN_MAJOR = 1 };
 enum { CSDR_KIND_HSDR = 0, CSDR_KIND_HSDC = 1 };
 
@@ -412,9 +413,10 @@ typedef struct {
      * tp_size == 1 means no sharding. comm is an ncclComm_t (void*) or NULL. */
     uint32_t tp_rank, tp_size;
     void* nccl_comm;
-    /* KV cache element type: CSDR_DTYPE_F32 (0, default: the reference's arithmetic) or
-     * CSDR_DTYPE_BF16 (keys and values rounded to bf16 when they enter the cache, scores and
-     * sums in fp32; half the cache bytes per step). No counterpart in the reference. */
+    /* KV cache element type: CSDR_DTYPE_F32 (0, default: the reference's arithmetic),
+     * CSDR_DTYPE_F16 or CSDR_DTYPE_BF16 (keys and values rounded to 16 bits when they enter
+     * the cache, scores and sums in fp32; half the cache bytes per step; fp16 keeps three more
+     * mantissa bits and wants |k|, |v| < 65504). No counterpart in the reference. */
     uint32_t kv_dtype;
 } csdr_decoder_config;
 

@@ -364,10 +364,10 @@ def oracle_forward_memo(oracle, weights, tokens, CFG):
     return _ORACLE_MEMO[key]
 
 
-# "bf16": the KV cache OPTION (rows rounded to bf16 on entry, scores and sums fp32). It does not meet
-# the fp32 cache's bar of 2e-2 at the 7B widths (observed 2.4e-2), which is why it is not the
-# default; its own bar is 5e-2.
-KV_TOL = {"f32": LOGIT_TOL, "bf16": 5e-2}
+# The 16-bit KV cache OPTIONS (rows rounded on entry, scores and sums fp32). fp16 (10 mantissa bits)
+# meets the fp32 cache's bar of 2e-2; bf16 (7 bits) does not at the 7B widths (observed 2.4e-2) and
+# has a bar of its own, 5e-2. The default stays fp32, the reference's arithmetic.
+KV_TOL = {"f32": LOGIT_TOL, "f16": LOGIT_TOL, "bf16": 5e-2}
 
 
 def same_pick(got, want, tol):
@@ -379,7 +379,7 @@ def same_pick(got, want, tol):
     return tol > LOGIT_TOL and float(top2[1] - top2[0]) < 2 * tol
 
 
-@pytest.mark.parametrize("kv_dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("kv_dtype", ["f32", "f16", "bf16"])
 def test_qwen_width_prefill_and_greedy_steps(ctx, oracle, model_qwen_width, kv_dtype):
     """Hidden 896, 14 query / 2 kv heads of 64, SwiGLU 4864, vocabulary 151 936, eps 1e-6, k/v
     dictionaries of 128 atoms; two blocks. A 64-token prompt (tensor-core block loop), then
@@ -405,7 +405,7 @@ def test_qwen_width_prefill_and_greedy_steps(ctx, oracle, model_qwen_width, kv_d
     dec.close()
 
 
-@pytest.mark.parametrize("kv_dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("kv_dtype", ["f32", "f16", "bf16"])
 def test_llama_width_batch16_step(ctx, oracle, model_llama_width, kv_dtype):
     """Hidden 4096, 32 heads of 128, SwiGLU 11 008, vocabulary 32 000; one block. Sixteen
     sequences with real, different, prefilled contexts step together (the 16-token tile of the
