@@ -392,6 +392,34 @@ class HierarchicalSDRStrategy:
         _check(lib.csdr_hsdr_encode(*args, out.ctypes.data_as(C.c_void_p), out.size, C.byref(n)))
         return out.tobytes()
 
+    def compress_shared(self, tensors, *, tile_rows: int, tile_cols: int, n_atoms: int, n_stages: int = 3, k: int = 8,
+                        decay: float = 0.5, ksvd_iters: int = 0):
+        """Several fp32 matrices behind ONE dictionary (compressGroupedSegments,
+        strategies/HierarchicalSDRStrategy.cpp:2211-2500, fit on all pooled tiles), encoded on the
+        device. Returns (dictionary record bytes - the .hsda record, also the payload of a
+        shared-dictionary resource segment of a .sdr -, [codes-only "HSDC" payload per tensor])."""
+        Ws = [_f32(W) for W in tensors]
+        if any(W.ndim != 2 for W in Ws):
+            raise CompressionError("HSDR: expected 2-D tensors")
+        n = len(Ws)
+        ptrs = (C.POINTER(C.c_float) * n)(*[_fp(W) for W in Ws])
+        rows = (C.c_uint32 * n)(*[W.shape[0] for W in Ws])
+        cols = (C.c_uint32 * n)(*[W.shape[1] for W in Ws])
+        dict_n = C.c_size_t()
+        code_n = (C.c_size_t * n)()
+        lib, h = self.ctx._lib, self.ctx._h
+        head = (h, ptrs, rows, cols, n, tile_rows, tile_cols, n_atoms, n_stages, k, decay, ksvd_iters)
+        rc = lib.csdr_hsdr_encode_shared(*head, None, 0, C.byref(dict_n), None, None, code_n)
+        if rc != _lib.ERR_BUFFER:
+            _check(rc)
+        dict_out = np.empty(dict_n.value, np.uint8)
+        outs = [np.empty(code_n[i], np.uint8) for i in range(n)]
+        out_ptrs = (C.c_void_p * n)(*[o.ctypes.data for o in outs])
+        caps = (C.c_size_t * n)(*[o.size for o in outs])
+        _check(lib.csdr_hsdr_encode_shared(*head, dict_out.ctypes.data_as(C.c_void_p), dict_out.size, C.byref(dict_n), out_ptrs,
+                                           caps, code_n))
+        return dict_out.tobytes(), [o.tobytes() for o in outs]
+
     def encode_codes(self, tiles, atoms, stage_scales, k: int) -> np.ndarray:
         """The coding pass alone: packed u16 codes (n_tiles, n_stages, k)."""
         tiles, atoms, stage_scales = _f32(tiles), _f32(atoms), _f32(stage_scales)

@@ -112,6 +112,10 @@ SIGNATURES = {
                                    C.c_uint8, C.c_float, C.c_uint8, _P, _SZ, C.POINTER(_SZ)]),
     "csdr_encode_codes": (C.c_int, [_P, _F, _SZ, _SZ, _F, C.c_uint16, C.c_uint8, C.c_uint8, _F,
                                     C.POINTER(C.c_uint16), _SZ]),
+    "csdr_hsdr_encode_shared": (C.c_int, [_P, C.POINTER(_F), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), _SZ,
+                                          C.c_uint16, C.c_uint16, C.c_uint16, C.c_uint8, C.c_uint8, C.c_float,
+                                          C.c_uint8, _P, _SZ, C.POINTER(_SZ), C.POINTER(_P), C.POINTER(_SZ),
+                                          C.POINTER(_SZ)]),
     "csdr_dequantize_inference": (C.c_int, [_P, C.c_char_p, _P, _SZ, _SZ, _F, _SZ, C.POINTER(_SZ)]),
     "csdr_archive_open": (C.c_int, [_P, C.c_char_p, C.POINTER(_P)]),
     "csdr_archive_close": (C.c_int, [_P]),

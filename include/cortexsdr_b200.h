@@ -304,6 +304,23 @@ CSDR_API int csdr_hsdr_encode(csdr_context* ctx, const float* W, uint32_t rows, 
                               uint16_t tile_rows, uint16_t tile_cols, uint16_t n_atoms,
                               uint8_t n_stages, uint8_t k_per_stage, float stage_decay,
                               uint8_t ksvd_iters, void* payload_out, size_t capacity, size_t* n_out);
+/* Several tensors behind ONE dictionary: compressGroupedSegments (:2211-2500) for tensors of one
+ * configuration, with the fit on all pooled tiles (max_tiles_for_fit = 0) - the tensors' tiles
+ * pooled in order, one fit on the pool (fitSharedDictionary, :1446-1469), every tensor coded
+ * against the result (compressFP32WithExternalDictionary, :1691-1754). Every shape must divide
+ * by the tile (CSDR_ERR_GEOMETRY otherwise, as the reference throws). dict_out receives the
+ * dictionary as a .hsda holds it (20-byte config, counted stage scales, counted atoms:
+ * SharedDictArchive::writeToStream, :1972-2002) - also the payload of a shared-dictionary
+ * resource segment of a .sdr; codes_out[i] receives tensor i's codes-only "HSDC" stream.
+ * dict_bytes and codes_bytes[i] receive the sizes, also when a buffer is missing or too small
+ * (CSDR_ERR_BUFFER). The reservoir-sampled fit of the reference (a cap on the pool) is not built. */
+CSDR_API int csdr_hsdr_encode_shared(csdr_context* ctx, const float* const* tensors,
+                                     const uint32_t* rows, const uint32_t* cols, size_t n_tensors,
+                                     uint16_t tile_rows, uint16_t tile_cols, uint16_t n_atoms,
+                                     uint8_t n_stages, uint8_t k_per_stage, float stage_decay,
+                                     uint8_t ksvd_iters, void* dict_out, size_t dict_capacity,
+                                     size_t* dict_bytes, void* const* codes_out,
+                                     const size_t* codes_capacity, size_t* codes_bytes);
 /* The coding pass alone (hierarchicalBinaryCode, :219-262, over every tile): tiles is
  * (n_tiles x tile_dim) fp32, atoms (n_atoms x tile_dim), both on the host; codes_out receives
  * n_tiles * n_stages * k_per_stage packed codes (packIndexSign, :76-80). */

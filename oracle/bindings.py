@@ -178,6 +178,41 @@ class Oracle:
             raise ValueError(f"orc_hsdr_encode rc={n}")
         return out[:n].copy()
 
+    def encode_shared(self, Ws, tile_rows, tile_cols, n_atoms, n_stages=3, k=8, decay=0.5, ksvd_iters=0):
+        """compressGroupedSegments (strategies/HierarchicalSDRStrategy.cpp:2211-2500) for tensors of
+        one configuration with the fit on all tiles (max_tiles_for_fit = 0): the tensors' tiles
+        pooled in order, ONE fit on the pool (fitSharedDictionary, :1446-1469), every tensor coded
+        against the result (compressFP32WithExternalDictionary, :1691-1754). Shapes must divide by
+        the tile. Returns (SharedDict, [codes-only "HSDC" payload per tensor])."""
+        import struct
+        T = tile_rows * tile_cols
+        pools = []
+        for W in Ws:
+            W = _f32(W)
+            R, Cc = W.shape
+            if R % tile_rows or Cc % tile_cols:
+                raise ValueError("shape not divisible by tile size")
+            nr, nc = R // tile_rows, Cc // tile_cols                    # extractTiles order, :95-116
+            pools.append(np.ascontiguousarray(W.reshape(nr, tile_rows, nc, tile_cols).transpose(0, 2, 1, 3).reshape(nr * nc, T)))
+        pool = np.ascontiguousarray(np.concatenate(pools))
+        D = np.empty((n_atoms, T), np.float32)
+        gam = np.empty(n_stages, np.float32)
+        codes = np.empty((pool.shape[0], n_stages, k), np.uint16)
+        self.lib.orc_hsdr_fit_tiles.restype = C.c_int
+        rc = self.lib.orc_hsdr_fit_tiles(_ptr(pool), C.c_uint32(pool.shape[0]), C.c_size_t(T), C.c_uint16(n_atoms),
+                                         C.c_uint8(n_stages), C.c_uint8(k), C.c_float(decay), C.c_uint8(ksvd_iters),
+                                         _ptr(D), _ptr(gam), _ptr(codes, C.c_uint16))
+        if rc:
+            raise ValueError(f"orc_hsdr_fit_tiles rc={rc}")
+        d = SharedDict(tile_rows, tile_cols, n_atoms, n_stages, k, D, gam)
+        payloads = []
+        for W, tiles in zip(Ws, pools):
+            R, Cc = W.shape
+            packed = self.code_tiles(tiles, D, gam, k)
+            hdr = struct.pack("<4sIIIIHHHBBf", b"HSDC", 1, R, Cc, tiles.shape[0], tile_rows, tile_cols, n_atoms, n_stages, k, decay)
+            payloads.append(np.frombuffer(hdr + packed.tobytes(), np.uint8).copy())
+        return d, payloads
+
     def _dict_args(self, d: SharedDict):
         return (_ptr(d.atoms), _ptr(d.scales), C.c_uint16(d.tile_rows), C.c_uint16(d.tile_cols),
                 C.c_uint16(d.n_atoms), C.c_uint8(d.n_stages), C.c_uint8(d.k))

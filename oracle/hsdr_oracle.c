@@ -233,6 +233,45 @@ long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_
     return orc_hsdr_encode(W, R, C, tile_rows, tile_cols, K, S, k, decay, 0, out, cap);
 }
 
+/* fitHierarchicalKSVD :494-607 on a pool of tiles (one tensor's, or several tensors' pooled by
+ * fitSharedDictionary :1446-1469): stage scales :507-509, dictionary init :511-538 (tiles picked
+ * by mt19937(0xC0DE), normalised, scaled by the mean tile norm over sqrt(S * k)), a coding pass
+ * :552-567, ksvd_iters rounds of atom update + coding pass :573-577, the non-finite sweep
+ * :598-604. D (K x T), gam (S) and codes (n_tiles x S x k, the last pass's) are outputs. */
+int orc_hsdr_fit_tiles(const float* tiles, uint32_t n_tiles, size_t T, uint16_t K, uint8_t S, uint8_t k, float decay,
+                       uint8_t ksvd_iters, float* D, float* gam, uint16_t* codes) {
+    if (n_tiles < K) return -2;
+    for (uint8_t l = 0; l < S; ++l) gam[l] = powf(decay, (float)l);          /* :507-509 */
+    orc_mt g;
+    mt_seed(&g, 0xC0DEu);
+    for (uint16_t j = 0; j < K; ++j) {
+        const float* src = tiles + (size_t)mt_below(&g, n_tiles) * T;
+        float* atom = D + (size_t)j * T;
+        float sq = 0.0f;
+        for (size_t c = 0; c < T; ++c) sq += src[c] * src[c];
+        const float norm = sqrtf(sq > 1e-24f ? sq : 1e-24f);
+        for (size_t c = 0; c < T; ++c) atom[c] = src[c] / norm;
+    }
+    double norm_sum = 0.0;
+    for (uint32_t i = 0; i < n_tiles; ++i) {
+        double sq = 0.0;
+        for (size_t c = 0; c < T; ++c) sq += (double)tiles[i * T + c] * tiles[i * T + c];
+        norm_sum += sqrt(sq);
+    }
+    const float mean = (float)(norm_sum / (double)(n_tiles ? n_tiles : 1u));
+    const float root = sqrtf((float)((uint32_t)S * k));
+    const float init_scale = mean / (root > 1.0f ? root : 1.0f);
+    for (size_t i = 0; i < (size_t)K * T; ++i) D[i] *= init_scale;
+    orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, codes);          /* encode_all :552-567 */
+    for (uint8_t it = 0; it < ksvd_iters; ++it) {                          /* :573-577 */
+        if (atom_update(tiles, n_tiles, T, D, K, codes, S, k, gam, &g)) return -10;
+        orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, codes);
+    }
+    for (size_t i = 0; i < (size_t)K * T; ++i)                              /* :598-604 */
+        if (!isfinite(D[i])) D[i] = 0.0f;
+    return 0;
+}
+
 /* compress :1068-1236 around fitHierarchicalKSVD :494-607; see the header. */
 long orc_hsdr_encode(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
                      uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t ksvd_iters, uint8_t* out, size_t cap) {
@@ -261,39 +300,10 @@ long orc_hsdr_encode(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows,
     memcpy(out + 28, &decay, 4);
     wr32(out + 32, (uint32_t)(4u * edge_floats));
     float* gam = (float*)(out + HSDR_HDR);            /* 36 and 36+4S are multiples of 4 */
-    for (uint8_t l = 0; l < S; ++l) gam[l] = powf(decay, (float)l);          /* :507-509 */
     float* D = (float*)(out + HSDR_HDR + 4u * S);
-    /* dictionary init :511-538 */
-    orc_mt g;
-    mt_seed(&g, 0xC0DEu);
-    for (uint16_t j = 0; j < K; ++j) {
-        const float* src = tiles + (size_t)mt_below(&g, n_tiles) * T;
-        float* atom = D + (size_t)j * T;
-        float sq = 0.0f;
-        for (size_t c = 0; c < T; ++c) sq += src[c] * src[c];
-        const float norm = sqrtf(sq > 1e-24f ? sq : 1e-24f);
-        for (size_t c = 0; c < T; ++c) atom[c] = src[c] / norm;
-    }
-    double norm_sum = 0.0;
-    for (uint32_t i = 0; i < n_tiles; ++i) {
-        double sq = 0.0;
-        for (size_t c = 0; c < T; ++c) sq += (double)tiles[i * T + c] * tiles[i * T + c];
-        norm_sum += sqrt(sq);
-    }
-    const float mean = (float)(norm_sum / (double)(n_tiles ? n_tiles : 1u));
-    const float root = sqrtf((float)((uint32_t)S * k));
-    const float init_scale = mean / (root > 1.0f ? root : 1.0f);
-    for (size_t i = 0; i < (size_t)K * T; ++i) D[i] *= init_scale;
-    /* encode_all :552-567; the code stream may sit on an odd 16-bit boundary only if 4S+4KT is
-     * odd, which it never is */
+    /* the code stream may sit on an odd 16-bit boundary only if 4S+4KT is odd, which it never is */
     uint16_t* codes = (uint16_t*)(out + HSDR_HDR + 4u * S + 4u * (size_t)K * T);
-    orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, codes);
-    for (uint8_t it = 0; it < ksvd_iters; ++it) {                          /* :573-577 */
-        if (atom_update(tiles, n_tiles, T, D, K, codes, S, k, gam, &g)) { free(tiles); return -10; }
-        orc_hsdr_code_tiles(tiles, n_tiles, T, D, K, S, k, gam, codes);
-    }
-    for (size_t i = 0; i < (size_t)K * T; ++i)                              /* :598-604 */
-        if (!isfinite(D[i])) D[i] = 0.0f;
+    if (orc_hsdr_fit_tiles(tiles, n_tiles, T, K, S, k, decay, ksvd_iters, D, gam, codes)) { free(tiles); return -10; }
     free(tiles);
     /* edge strips :1185-1197: top-right, then bottom */
     uint8_t* e = out + total - 4u * edge_floats;

@@ -76,6 +76,11 @@ void orc_hsdr_code_tiles(const float* tiles, size_t n_tiles, size_t T, const flo
  * sums of the normalisation (-ffast-math), so atoms agree with its payloads to rounding, not
  * bit for bit. The caller passes the tile shape configFor (:1024-1065) would choose: a row
  * tile (tile_rows == 1) always spans the whole row. */
+/* The fit of the encoder on a pool of tiles (n_tiles x T): dictionary D (K x T), stage scales gam
+ * (S) and the pool's codes (n_tiles x S x k) out. fitHierarchicalKSVD, :494-607; what
+ * fitSharedDictionary (:1446-1469) runs on the pooled tiles of several tensors. */
+int orc_hsdr_fit_tiles(const float* tiles, uint32_t n_tiles, size_t T, uint16_t K, uint8_t S, uint8_t k, float decay,
+                       uint8_t ksvd_iters, float* D, float* gam, uint16_t* codes);
 long orc_hsdr_encode_fast(const float* W, uint32_t R, uint32_t C, uint16_t tile_rows, uint16_t tile_cols,
                           uint16_t K, uint8_t S, uint8_t k, float decay, uint8_t* out, size_t cap);
 

@@ -158,6 +158,7 @@ def main():
     encoder_coding(ref)
     attention_cases(ref)
     raw_tensor_cases()
+    grouped_encoder(ref)
     print("golden fixtures written to", OUT)
     for f in sorted(os.listdir(OUT)):
         print(f"  {f:24s} {os.path.getsize(os.path.join(OUT, f)):>9d} B")
@@ -179,6 +180,30 @@ def encoder_coding(ref):
         out[label + "_w"] = w.reshape(R, C).copy()
         out[label + "_payload"] = np.frombuffer(pay, np.uint8)
     np.savez_compressed(os.path.join(OUT, "encoder_coding.npz"), **out)
+
+
+def grouped_encoder(ref):
+    """compressGroupedSegments (HierarchicalSDRStrategy.cpp:2211-2500): weights in, the .hsda bytes the
+    reference made of them out - three row-tile tensors behind one dictionary after two update
+    rounds, and two tensors of 16 x 16 tiles behind another in fast mode. The fit runs on all pooled
+    tiles (max_tiles_for_fit = 0)."""
+    import tempfile
+    out = {}
+    cases = (("rows", [(48, 128)] * 3, cfg_row1d(128, 16, 3, ksvd_iters=2, max_tiles_for_fit=0)),
+             ("tiles", [(64, 96), (32, 64)], cfg_default(tile_rows=16, tile_cols=16, n_atoms=16, k=3, ksvd_iters=0,
+                                                          max_tiles_for_fit=0)))
+    for label, shapes, cfg in cases:
+        segs = []
+        for i, (R, C) in enumerate(shapes):
+            (w,) = ref.mt19937_normal(0xE100 + 16 * len(out) + i, [(R * C, 0, 0.05)])
+            segs.append(Segment(f"blk.{i}.attn_q.weight", w.reshape(R, C), (R, C), SEG_ATTENTION, layer_index=i))
+            out[f"{label}_w{i}"] = w.reshape(R, C)
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, "g.hsda")
+            assert ref.hsda_write(segs, path, cfg, cfg) == 1
+            out[label + "_hsda"] = np.frombuffer(open(path, "rb").read(), np.uint8)
+        out[label + "_n"] = len(shapes)
+    np.savez_compressed(os.path.join(OUT, "grouped_encoder.npz"), **out)
 
 
 def attention_cases(ref):
@@ -226,7 +251,8 @@ def raw_tensor_cases(_ref=None):
 
 
 if __name__ == "__main__":
-    only = {"encoder_coding": encoder_coding, "attention": attention_cases, "raw_tensors": raw_tensor_cases}
+    only = {"encoder_coding": encoder_coding, "attention": attention_cases, "raw_tensors": raw_tensor_cases,
+            "grouped_encoder": grouped_encoder}
     if len(sys.argv) == 2 and sys.argv[1] in only:      # only this fixture, the others untouched
         only[sys.argv[1]](Reference() if sys.argv[1] != "raw_tensors" else None)
     else:

@@ -160,3 +160,96 @@ def test_unused_atoms_are_replaced_as_the_reference_replaces_them(ctx, oracle):
     assert used_first < 64                                   # the case does leave atoms unused
     assert np.abs(Dw - Dm).max() <= 2e-6 * np.abs(Dw).max()
     assert np.array_equal(cm, cw)
+
+
+def _hsda_parts(raw):
+    import struct
+    raw = bytes(raw)
+    assert raw[:4] == b"HSDA"
+    _, nd, ns = struct.unpack_from("<III", raw, 4)
+    assert nd == 1
+    o = 16
+    record_at = o
+    tr, tc, K, S, k = struct.unpack_from("<HHHBB", raw, o)
+    o += 20
+    (n_sc,) = struct.unpack_from("<I", raw, o)
+    o += 4 + 4 * n_sc
+    (n_at,) = struct.unpack_from("<I", raw, o)
+    o += 4 + 4 * n_at
+    record = raw[record_at:o]
+    codes = []
+    for _ in range(ns):
+        (ln,) = struct.unpack_from("<I", raw, o)
+        o += 4 + ln
+        _, _, _, clen = struct.unpack_from("<IQBI", raw, o)
+        o += 17
+        codes.append(raw[o:o + clen])
+        o += clen
+    return (tr, tc, K, S, k), record, codes
+
+
+@pytest.mark.parametrize("label,iters", [("rows", 2), ("tiles", 0)])
+def test_grouped_encoder_against_the_reference_archive(ctx, oracle, golden, label, iters):
+    """Several tensors behind one dictionary (compressGroupedSegments, :2211-2500) on the device,
+    against the .hsda the reference wrote from the same weights: the dictionary record's config and
+    stage scales byte for byte (the reference's ksvd_iters and max_tiles_for_fit fields included),
+    atoms within 2e-6 of the largest, every tensor's codes-only payload with its header equal and
+    its codes equal except at rounding ties (>= 99.5 %), and the same reconstruction."""
+    from tests import synth
+    from oracle.bindings import SharedDict
+    g = golden("grouped_encoder.npz")
+    (tr, tc, K, S, k), record, ref_codes = _hsda_parts(g[label + "_hsda"])
+    Ws = [g[f"{label}_w{i}"] for i in range(int(g[label + "_n"]))]
+    rec, pays = cs.HierarchicalSDRStrategy(ctx).compress_shared(Ws, tile_rows=tr, tile_cols=tc, n_atoms=K, n_stages=S, k=k,
+                                                                ksvd_iters=iters)
+    assert len(rec) == len(record)
+    head = 24 + 4 * S + 4                                   # config, counted scales, atom count
+    assert rec[:head] == record[:head]
+    mine, want = synth.read_dictionary_record(rec), synth.read_dictionary_record(record)
+    assert np.abs(mine[5] - want[5]).max() <= 2e-6 * np.abs(want[5]).max()
+    d_ref = SharedDict(*want)
+    for W, pay, ref_pay in zip(Ws, pays, ref_codes):
+        assert pay[:32] == ref_pay[:32] and len(pay) == len(ref_pay)
+        a, b = np.frombuffer(pay, np.uint16, offset=32), np.frombuffer(ref_pay, np.uint16, offset=32)
+        assert float((a == b).mean()) >= 0.995
+        err_m = np.linalg.norm(W - oracle.hsdc_decompress(pay, SharedDict(*mine))) / np.linalg.norm(W)
+        err_r = np.linalg.norm(W - oracle.hsdc_decompress(ref_pay, d_ref)) / np.linalg.norm(W)
+        assert abs(err_m - err_r) <= 1e-4 * err_r, (err_m, err_r)
+
+
+def test_grouped_encoder_to_an_archive_with_shared_dictionaries(ctx, oracle, tmp_path):
+    """From weights to products through a shared dictionary, all on this library: three tensors
+    encoded behind one dictionary on the device, written as a .sdr whose dictionary is a resource
+    segment and whose tensors are codes-only segments naming it, opened and multiplied; against
+    the oracle's grouped encoder and its external-dictionary product."""
+    from tests import synth
+    from oracle.bindings import SharedDict
+    rng = np.random.default_rng(31)
+    Ws = [rng.normal(0, 0.05, (r, 256)).astype(np.float32) for r in (128, 64, 192)]
+    kw = dict(tile_rows=1, tile_cols=256, n_atoms=128, n_stages=3, k=4)
+    st = cs.HierarchicalSDRStrategy(ctx)
+    rec, pays = st.compress_shared(Ws, **kw, ksvd_iters=1)
+    d_want, pays_want = oracle.encode_shared(Ws, 1, 256, 128, 3, 4, 0.5, 1)
+    mine = synth.read_dictionary_record(rec)
+    assert np.array_equal(mine[6], d_want.scales)
+    segs = [dict(name="hsdr.shared_dict/ffn_up", payload=rec, strategy_id=0, original_type=synth.SEG_CONFIG, dims=(128, 256),
+                 original_size=128 * 256 * 4, data_format=synth.SHARED_DICT_FORMAT, layer_type="", layer_index=0)]
+    for i, (W, pay) in enumerate(zip(Ws, pays)):
+        segs.append(dict(name=f"blk.{i}.ffn_up.weight", payload=pay, strategy_id=5, original_type=synth.SEG_FEED_FORWARD,
+                         dims=W.shape, original_size=W.nbytes, data_format="hsdc@hsdr.shared_dict/ffn_up", layer_index=i))
+    path = str(tmp_path / "grouped.sdr")
+    synth.write_sdr(path, segs)
+    ld = cs.SDRModelLoader(path, ctx)
+    x = rng.normal(0, 1, (256, 3)).astype(np.float32)
+    d_mine = SharedDict(*mine)
+    for i, (W, pay) in enumerate(zip(Ws, pays)):
+        y = ld.matmulHSDR(f"blk.{i}.ffn_up.weight", x, 3)
+        want = oracle.hsdc_matmul(pay, d_mine, x, 3)                         # this archive, decoded by the oracle
+        assert np.abs(y - want).max() <= 1e-3 * np.abs(want).max()
+        # and the fit is as good as the oracle's own grouped fit of the same weights
+        err_m = np.linalg.norm(W - oracle.hsdc_decompress(pay, d_mine)) / np.linalg.norm(W)
+        err_w = np.linalg.norm(W - oracle.hsdc_decompress(pays_want[i], d_want)) / np.linalg.norm(W)
+        assert abs(err_m - err_w) <= 2e-3 * err_w, (err_m, err_w)
+    ld.close()
+    with pytest.raises(cs.CompressionError, match="not divisible"):
+        st.compress_shared([np.zeros((10, 100), np.float32)], tile_rows=4, tile_cols=32, n_atoms=2)
