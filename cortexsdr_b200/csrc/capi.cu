@@ -225,6 +225,7 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         if (const char* e = std::getenv("CSDR_CACHE_2D")) ctx->cache_2d = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_QUEUE")) ctx->decoder_queue = e[0] != '0';
         if (const char* e = std::getenv("CSDR_TILE_TC")) ctx->tile_tc = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_HOST_ZERO_COPY")) ctx->host_zero_copy = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_FOLD")) ctx->decoder_fold = e[0] != '0';
         if (const char* e = std::getenv("CSDR_QUEUE_POLL_SLEEP")) ctx->queue_poll_sleep_ns = static_cast<uint32_t>(std::max(0, std::atoi(e)));
         if (const char* e = std::getenv("CSDR_QUEUE_MIN_GROUP")) ctx->queue_min_group = static_cast<uint32_t>(std::max(1, std::atoi(e)));
@@ -731,7 +732,36 @@ int csdr_matmul_queue(csdr_context* ctx, const csdr_matmul_host_task* tasks, siz
             x_bytes += (static_cast<size_t>(g.cols) * t.batch * 4 + 255) & ~static_cast<size_t>(255);
             y_bytes += (static_cast<size_t>(g.rows) * t.batch * 4 + 255) & ~static_cast<size_t>(255);
         }
-        unsigned char* hbuf = static_cast<unsigned char*>(ctx->pinned_get(256 + x_bytes + y_bytes)) + 256;
+        // A caller whose activations (and results) sit one behind the other in PAGE-LOCKED memory, in
+        // task order and in 256-byte multiples, has laid them out as the staging block is: the
+        // copy engines then move them straight from (to) the caller's memory, one transfer each
+        // way, and the two passes through a staging buffer fall away.
+        unsigned char* y_mapped = nullptr;   // device view of the caller's page-locked results, when they have one
+        auto page_locked_run = [&](bool outputs) {
+            const unsigned char* expect = nullptr;
+            for (size_t i = 0; i < n_tasks; ++i) {
+                const csdr_matmul_host_task& t = tasks[i];
+                const size_t nb = static_cast<size_t>(outputs ? t.seg->g.rows : t.seg->g.cols) * t.batch * 4;
+                const unsigned char* p = reinterpret_cast<const unsigned char*>(outputs ? static_cast<const void*>(t.y) : t.x);
+                if ((nb & 255u) || (i && p != expect)) return false;
+                expect = p + nb;
+            }
+            const unsigned char* first = reinterpret_cast<const unsigned char*>(outputs ? static_cast<const void*>(tasks[0].y) : tasks[0].x);
+            for (const unsigned char* q : {first, expect - 1}) {
+                cudaPointerAttributes at{};
+                if (cudaPointerGetAttributes(&at, q) != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    return false;
+                }
+                if (at.type != cudaMemoryTypeHost) return false;
+                if (outputs && q == first) y_mapped = static_cast<unsigned char*>(at.devicePointer);
+            }
+            return true;
+        };
+        const bool x_direct = page_locked_run(false), y_direct = page_locked_run(true);
+        const bool y_zero_copy = y_direct && y_mapped != nullptr && ctx->host_zero_copy;
+        unsigned char* hbuf = (x_direct && y_direct) ? nullptr
+                                                     : static_cast<unsigned char*>(ctx->pinned_get(256 + x_bytes + y_bytes)) + 256;
         unsigned char* dbuf = static_cast<unsigned char*>(ctx->scratch_get(3, x_bytes + y_bytes));
         std::vector<QueueItem> items(n_tasks);
         size_t xo = 0, yo = x_bytes;
@@ -742,21 +772,25 @@ int csdr_matmul_queue(csdr_context* ctx, const csdr_matmul_host_task* tasks, siz
             // tasks that share one host x share one staged copy
             size_t x_at = xo;
             bool shared = false;
-            for (size_t j = i; j-- > 0 && i - j <= 4;)
-                if (tasks[j].x == t.x && tasks[j].batch == t.batch && tasks[j].seg->g.cols == g.cols) {
-                    x_at = static_cast<const unsigned char*>(items[j].x) - dbuf;
-                    shared = true;
-                    break;
-                }
+            if (!x_direct)
+                for (size_t j = i; j-- > 0 && i - j <= 4;)
+                    if (tasks[j].x == t.x && tasks[j].batch == t.batch && tasks[j].seg->g.cols == g.cols) {
+                        x_at = static_cast<const unsigned char*>(items[j].x) - dbuf;
+                        shared = true;
+                        break;
+                    }
             if (!shared) {
-                std::memcpy(hbuf + xo, t.x, xb);
+                if (!x_direct) std::memcpy(hbuf + xo, t.x, xb);
                 xo += (xb + 255) & ~static_cast<size_t>(255);
             }
-            items[i] = QueueItem{t.seg, dbuf + x_at, CSDR_DTYPE_F32, CSDR_LAYOUT_FEATURE_MAJOR, t.batch,
-                                 reinterpret_cast<float*>(dbuf + yo), CSDR_LAYOUT_FEATURE_MAJOR, nullptr};
+            // results of a page-locked run that the device can address go straight to the caller's
+            // memory, row by row as the gather finishes them: no copy behind the launch at all
+            float* y_at = y_zero_copy ? reinterpret_cast<float*>(y_mapped + (yo - x_bytes)) : reinterpret_cast<float*>(dbuf + yo);
+            items[i] = QueueItem{t.seg, dbuf + x_at, CSDR_DTYPE_F32, CSDR_LAYOUT_FEATURE_MAJOR, t.batch, y_at,
+                                 CSDR_LAYOUT_FEATURE_MAJOR, nullptr};
             yo += (yb + 255) & ~static_cast<size_t>(255);
         }
-        CSDR_CUDA(cudaMemcpyAsync(dbuf, hbuf, xo, cudaMemcpyHostToDevice, ctx->stream));
+        CSDR_CUDA(cudaMemcpyAsync(dbuf, x_direct ? tasks[0].x : static_cast<const void*>(hbuf), xo, cudaMemcpyHostToDevice, ctx->stream));
         if (gemv_queue_supported(ctx, items.data(), static_cast<uint32_t>(n_tasks))) {
             launch_gemv_queue(ctx, items.data(), static_cast<uint32_t>(n_tasks));
         } else {
@@ -768,13 +802,17 @@ int csdr_matmul_queue(csdr_context* ctx, const csdr_matmul_host_task* tasks, siz
                 launch_matmul(ctx, it.seg, a);
             }
         }
-        CSDR_CUDA(cudaMemcpyAsync(hbuf + x_bytes, dbuf + x_bytes, yo - x_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        if (!y_zero_copy)
+            CSDR_CUDA(cudaMemcpyAsync(y_direct ? static_cast<void*>(tasks[0].y) : static_cast<void*>(hbuf + x_bytes), dbuf + x_bytes,
+                                      yo - x_bytes, cudaMemcpyDeviceToHost, ctx->stream));
         CSDR_CUDA(cudaStreamSynchronize(ctx->stream));
-        yo = x_bytes;
-        for (size_t i = 0; i < n_tasks; ++i) {
-            const size_t yb = static_cast<size_t>(tasks[i].seg->g.rows) * tasks[i].batch * 4;
-            std::memcpy(tasks[i].y, hbuf + yo, yb);
-            yo += (yb + 255) & ~static_cast<size_t>(255);
+        if (!y_direct) {
+            yo = x_bytes;
+            for (size_t i = 0; i < n_tasks; ++i) {
+                const size_t yb = static_cast<size_t>(tasks[i].seg->g.rows) * tasks[i].batch * 4;
+                std::memcpy(tasks[i].y, hbuf + yo, yb);
+                yo += (yb + 255) & ~static_cast<size_t>(255);
+            }
         }
     });
 }

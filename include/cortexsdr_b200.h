@@ -222,7 +222,10 @@ CSDR_API int csdr_matmul_queue_device_async(csdr_context* ctx, const csdr_matmul
 /* The same list with HOST buffers, reference layout (x: C x batch, y: R x batch, fp32): every
  * task's activations cross to the device in one copy, the list runs as above, every result
  * comes back in one copy, one synchronisation in all. Tasks that name the same host x share one
- * staged copy. 1-D row tiles only, as matmulRowMajor (CSDR_ERR_GEOMETRY otherwise). */
+ * staged copy. When the tasks' activations (results) lie one behind the other, in task order
+ * and in multiples of 256 bytes, in page-locked host memory (cudaHostAlloc / cudaHostRegister),
+ * they are transferred straight from (to) the caller's memory instead of through a staging
+ * buffer. 1-D row tiles only, as matmulRowMajor (CSDR_ERR_GEOMETRY otherwise). */
 typedef struct {
     const csdr_segment* seg;
     const float* x;

@@ -541,6 +541,36 @@ def test_queue_on_host_buffers(ctx, oracle):
         cs.Segment.matmul_queue([(seg2d, np.zeros((64, 1), np.float32), 1, np.zeros((64, 1), np.float32))])
 
 
+def test_queue_on_page_locked_host_buffers(ctx, oracle):
+    """Activations and results one behind the other in page-locked memory, in task order and in
+    multiples of 256 bytes: moved straight from and to the caller's memory. Same results as
+    through the staging buffer (pageable arrays), and as the oracle's; a list whose results are
+    NOT contiguous takes the staged way for them."""
+    import torch
+    from tests import synth
+    rng = np.random.default_rng(23)
+    n, R, Cc = 6, 320, 1024                                    # 320 * 4 and 1024 * 4 are multiples of 256
+    pays = [synth.hsdr_payload(R, Cc, n_atoms=128, k=6, seed=80 + i) for i in range(n)]
+    segs = [cs.Segment.from_payload(p, ctx) for p in pays]
+    x_pin = torch.empty((n, Cc), dtype=torch.float32, pin_memory=True)
+    y_pin = torch.full((n, R), float("nan"), dtype=torch.float32, pin_memory=True)
+    xa, ya = x_pin.numpy(), y_pin.numpy()
+    xa[:] = rng.normal(0, 1, (n, Cc)).astype(np.float32)
+    cs.Segment.matmul_queue([(segs[i], xa[i].reshape(Cc, 1), 1, ya[i].reshape(R, 1)) for i in range(n)])
+    plain = [np.full((R, 1), np.nan, np.float32) for _ in range(n)]
+    cs.Segment.matmul_queue([(segs[i], xa[i].copy().reshape(Cc, 1), 1, plain[i]) for i in range(n)])
+    for i in range(n):
+        want = oracle.matmul(pays[i], xa[i].reshape(Cc, 1), 1)
+        e = rel_err(ya[i].reshape(R, 1), want)
+        assert e[0] < TOL and e[1] < TOL, i
+        assert np.array_equal(ya[i].reshape(R, 1), plain[i])
+    # results in reverse order: page-locked, not consecutive
+    y2 = torch.full((n, R), float("nan"), dtype=torch.float32, pin_memory=True).numpy()
+    cs.Segment.matmul_queue([(segs[i], xa[i].reshape(Cc, 1), 1, y2[n - 1 - i].reshape(R, 1)) for i in range(n)])
+    for i in range(n):
+        assert np.array_equal(y2[n - 1 - i].reshape(R, 1), plain[i])
+
+
 @pytest.mark.parametrize("batch", [1, 3])
 def test_queue_chain_of_dependent_products(ctx, oracle, batch):
     # y1 = W1 x, y2 = W2 y1, y3 = W3 y2 and, beside the chain, y4 = W4 x: one list, one launch; the
