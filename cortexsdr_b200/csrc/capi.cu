@@ -218,8 +218,8 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         }
         CSDR_CUDA(cudaMalloc(&ctx->status_word, sizeof(int)));
         CSDR_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
-        CSDR_CUDA(cudaMalloc(&ctx->gemv_seq, 2 * sizeof(uint32_t)));
-        CSDR_CUDA(cudaMemsetAsync(ctx->gemv_seq, 0, 2 * sizeof(uint32_t), ctx->stream));
+        CSDR_CUDA(cudaMalloc(&ctx->gemv_seq, 1024 * sizeof(uint32_t)));   // launch tag words: last tag, pad, one slot per CTA
+        CSDR_CUDA(cudaMemsetAsync(ctx->gemv_seq, 0, 1024 * sizeof(uint32_t), ctx->stream));
         if (const char* e = std::getenv("CSDR_FUSED_GEMV")) ctx->fused_gemv = e[0] != '0';
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE")) ctx->gemv_queue = e[0] != '0';
         if (const char* e = std::getenv("CSDR_CACHE_2D")) ctx->cache_2d = e[0] != '0';

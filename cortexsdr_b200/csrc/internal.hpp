@@ -119,7 +119,7 @@ struct csdr_context {
     bool gemv_queue = true;  // CSDR_GEMV_QUEUE=0 keeps lists of products on single and grouped launches
     bool cache_2d = true;            // CSDR_CACHE_2D=0: wide batches on 2-D tiles stay on the factored CUDA-core kernels
     uint32_t queue_poll_sleep_ns = 400;  // CSDR_QUEUE_POLL_SLEEP: pause between polls of the list kernel's dependent hand-overs
-    uint32_t queue_min_group = 8;    // CSDR_QUEUE_MIN_GROUP: smallest same-x group the list kernel takes over grouped fused launches
+    uint32_t queue_min_group = 4;    // CSDR_QUEUE_MIN_GROUP: smallest same-x group the list kernel takes over grouped fused launches
     bool host_zero_copy = true;      // CSDR_HOST_ZERO_COPY=0: results of a host list go back by a copy even when the caller's memory is device-addressable
     bool tile_tc = true;             // CSDR_TILE_TC=0: 2-D tile products of a few tokens stay on the CUDA-core projection
     bool decoder_fold = true;        // CSDR_DECODER_FOLD=0: norms, residuals and SwiGLU of a short decoder step as kernels of their own

@@ -55,7 +55,7 @@ struct FusedParams {
     uint32_t gather_ctas;   // CTAs that take part in phase B = row chunks * token groups
     XView x;
     unsigned long long* part;  // {float bits (low half), epoch (high half)} per partial
-    unsigned long long* seq;  // device: {launches completed, CTAs checked in} (take_launch_tag)
+    uint32_t* seq;          // device: launch tag words (read_launch_tag / retire_launch_tag)
     int* status;
     uint32_t spin_limit;
     unsigned long long* trace;  // optional: 16 global-timer stamps per CTA (phase boundaries)
@@ -226,8 +226,8 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
     asm volatile("griddepcontrol.wait;" ::: "memory");
     stamp(p, 2);
     __shared__ uint32_t epoch_s;
-    // thread 0 checks in (one L2 round trip) while the others already stage the activations
-    if (tid == 0) epoch_s = take_launch_tag(p.seq);
+    // thread 0 reads the launch's tag (one L2 round trip) while the others already stage the activations
+    if (tid == 0) epoch_s = read_launch_tag(p.seq);
 
     // ---- phase A ----
     float* xs = reinterpret_cast<float*>(smem_raw);
@@ -438,6 +438,9 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
         __syncthreads();  // dxs is rewritten for the next segment
     }
     if (late) atomicExch(p.status, 1);
+    // CTA 0 (always a gather CTA) retires the launch's tag: every CTA has read it long ago
+    if (blockIdx.x == 0 && warp == 0 && !retire_launch_tag(p.seq, epoch, lane, limit ? limit : 1u) && lane == 0)
+        atomicExch(p.status, 1);
     stamp(p, 7);
 }
 
@@ -573,7 +576,7 @@ void launch_gemv_fused(csdr_context* ctx, const csdr_segment* const* segs, uint3
     p.n_tasks = task;
     p.part = static_cast<unsigned long long*>(
         ctx->scratch_get(4, std::max<size_t>(static_cast<size_t>(part_off) * 8u, 2u << 20)));
-    p.seq = reinterpret_cast<unsigned long long*>(ctx->gemv_seq);
+    p.seq = ctx->gemv_seq;
     p.status = ctx->status_word;
     p.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
     p.spin_limit = ctx->spin_limit_gemv;  // each poll is an L2 round trip: about a second by default

@@ -60,7 +60,7 @@ constexpr uint32_t kLoaderWarps = 1, kProductWarps = 8, kGatherWarps = 4;
 constexpr uint32_t kThreads = 32u * (kLoaderWarps + kProductWarps + kGatherWarps);
 constexpr uint32_t kProductThreads = 32u * kProductWarps;
 constexpr uint32_t kAtomsPerUnit = 8;          // one per product warp
-constexpr uint32_t kSlab = 1024;               // columns per stage
+constexpr uint32_t kSlab = 1024;               // columns per stage (a multiple of 1024)
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kMaxTokens = 4;
 
@@ -102,7 +102,7 @@ struct QParams {
     uint32_t split_rows;        // 1: a task's rows are split over the gather warps; 0: tasks are dealt out to them
     u64* dx;                    // tagged Dx words
     u64* sumsq;                 // tagged sums of squares of a task's activations: [task][kMaxTokens]
-    unsigned long long* seq;    // {launches completed, CTAs checked in} (take_launch_tag)
+    uint32_t* seq;              // launch tag words (read_launch_tag / retire_launch_tag)
     int* status;
     uint32_t spin_poll, spin_barrier;
     uint32_t poll_sleep_ns;     // pause between two looks at words another CTA has yet to write
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
         while (ui < p.n_units && it_issue < NS) issue();
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0) {
-            tag_s = take_launch_tag(p.seq);
+            tag_s = read_launch_tag(p.seq);
             stamp(p, 0, 6);
         }
         asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
@@ -314,6 +314,8 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 issue();
             }
         }
+        // CTA 0's loader has nothing left to do: it retires the launch's tag for the next launch
+        if (blockIdx.x == 0 && !retire_launch_tag(p.seq, tag_s, lane, p.spin_poll)) ok = false;
         if (!ok) {
             if (lane == 0) {
                 failed_s = 1;
@@ -360,9 +362,11 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 unsigned char* st = qsm + static_cast<size_t>(slot) * p.stage_bytes;
                 const uint32_t cw = min(kSlab, t.C - s * kSlab);
                 if (t.x_kind == X_TAGGED) {
-                    // this warp's eighth of the slab, token by token: 128 columns, four per lane
+                    // this warp's eighth of the slab, token by token, 128 columns (four per lane) at a time
                     float* xs = reinterpret_cast<float*>(st + kAtomsPerUnit * kSlab * 4u);
-                    const uint32_t c_lane = w * 128u + lane * 4u;
+#pragma unroll 1
+                    for (uint32_t part = 0; part < kSlab / 1024u; ++part) {
+                    const uint32_t c_lane = w * (kSlab / 8u) + part * 128u + lane * 4u;
                     if (c_lane < cw) {
                         const u64* src = static_cast<const u64*>(t.x) + s * kSlab + c_lane;
                         // word i of this lane: token i / 4, column c_lane + i % 4
@@ -397,6 +401,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                             ssq[b] = fmaf(h.x, h.x, fmaf(h.y, h.y, fmaf(h.z, h.z, fmaf(h.w, h.w, ssq[b]))));
                             *reinterpret_cast<float4*>(xs + b * kSlab + c_lane) = make_float4(h.x * wv.x, h.y * wv.y, h.z * wv.z, h.w * wv.w);
                         }
+                    }
                     }
                     asm volatile("bar.sync 1, %0;" ::"n"(kProductThreads) : "memory");   // the whole slab is staged
                     if (s == 0 && tid == 32u) stamp(p, ti, 0);
@@ -648,7 +653,10 @@ bool needs_split(const QueueItem* items, uint32_t n) {
     for (uint32_t i = 0; i < n; ++i)
         if (items[i].dep >= 0 || items[i].swiglu_gate || items[i].norm_weight || items[i].residual)
             return true;
-    return n < 2u * kGatherWarps;   // short lists: the shortest path through each task
+    // independent products: a warp per task, the tasks' gathers side by side (with the rows split,
+    // one task's hand-over and gather follow the other's: 2.8 us each, measured); a single
+    // product has nothing to run beside
+    return n < 2u;
 }
 // bytes of code stream one gather warp stages per task
 uint32_t code_bytes_per_warp(const csdr_context* ctx, const Geometry& g, bool split) {
@@ -726,8 +734,8 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
     const uint32_t batch = static_cast<uint32_t>(items[0].batch);
     const int mt = batch <= 1 ? 1 : batch <= 2 ? 2 : 4;
     if (!ctx->queue_sync) {
-        CSDR_CUDA(cudaMalloc(&ctx->queue_sync, 2 * sizeof(uint32_t)));   // the launch counter pair
-        CSDR_CUDA(cudaMemsetAsync(ctx->queue_sync, 0, 2 * sizeof(uint32_t), ctx->stream));
+        CSDR_CUDA(cudaMalloc(&ctx->queue_sync, (2u + kMaxTagCtas) * sizeof(uint32_t)));   // the launch tag words
+        CSDR_CUDA(cudaMemsetAsync(ctx->queue_sync, 0, (2u + kMaxTagCtas) * sizeof(uint32_t), ctx->stream));
     }
     for (uint32_t i0 = 0; i0 < n; i0 += kMaxQueueTasks) {
         const uint32_t cnt = std::min(kMaxQueueTasks, n - i0);
@@ -796,7 +804,7 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
         p.n_tasks = cnt;
         p.n_units = unit;
         p.split_rows = split ? 1u : 0u;
-        p.seq = reinterpret_cast<unsigned long long*>(ctx->queue_sync);
+        p.seq = ctx->queue_sync;
         p.poll_sleep_ns = ctx->queue_poll_sleep_ns;
         p.status = ctx->status_word;
         p.spin_poll = ctx->spin_limit_gemv;

@@ -54,22 +54,40 @@ __device__ __forceinline__ size_t y_index(const YView& v, uint32_t r, uint32_t b
                : static_cast<size_t>(v.b0 + b) * v.R + r;
 }
 
-// The tag of a launch: (launches completed) mod (2^32 - 1), plus one - never 0, the value fresh
-// scratch holds. One 64-bit word in device memory keeps {launches completed (high half), CTAs of
-// the running launch that have checked in (low half)}; a CTA checks in with ONE atomic add, whose
-// return value also carries the count it needs, and the CTA that checks in last adds the rest of
-// 2^32 so that the high half moves on and the low half returns to zero. Every CTA of a launch
-// reads the same high half (it only moves after the last check-in), and the next launch checks
-// in behind its dependency wait, when this launch's stores are visible. Because the word lives
-// on the device, a captured CUDA graph tags every replay afresh.
-__device__ __forceinline__ uint32_t take_launch_tag(unsigned long long* seq) {
-    unsigned long long old;
-    asm volatile("atom.relaxed.gpu.global.add.u64 %0, [%1], 1;" : "=l"(old) : "l"(seq) : "memory");
-    if (static_cast<uint32_t>(old) == gridDim.x - 1u) {
-        const unsigned long long rest = (1ull << 32) - gridDim.x;
-        asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(seq), "l"(rest) : "memory");
+// The tag of a launch: one more than the tag of the launch before it on the context (never 0, the
+// value fresh scratch holds), kept in DEVICE memory so that a captured CUDA graph tags every replay
+// afresh. seq[0] is the last tag handed out; seq[2 + cta] is where a CTA leaves the tag it took.
+//   * Every CTA reads seq[0] with a plain load behind its dependency wait (the launch before has
+//     completed by then, its write of seq[0] is visible) and leaves tag = seq[0] + 1 in its own
+//     slot: no atomic, nothing to wait for. (All CTAs of a launch checking in with an atomic on
+//     one word took 4 us for 148 CTAs: same-address atomics serialise in L2.)
+//   * One warp of CTA 0 that has nothing else to do retires the tag: it waits (bounded) until
+//     every CTA's slot holds the tag - every CTA has read seq[0] - and only then writes
+//     seq[0] = tag for the next launch.
+constexpr uint32_t kMaxTagCtas = 1022;   // seq holds 2 + kMaxTagCtas words
+__device__ __forceinline__ uint32_t read_launch_tag(uint32_t* seq) {
+    uint32_t last;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(last) : "l"(seq) : "memory");
+    const uint32_t tag = last + 1u == 0u ? 1u : last + 1u;
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(seq + 2u + blockIdx.x), "r"(tag) : "memory");
+    return tag;
+}
+// Called by all 32 lanes of one warp of CTA 0. False when the wait ran out (the tag is retired all
+// the same, so that the context does not reuse it; the caller records the failure).
+__device__ __forceinline__ bool retire_launch_tag(uint32_t* seq, uint32_t tag, uint32_t lane, uint32_t limit) {
+    bool done = false;
+    for (uint32_t spins = 0; spins <= limit && !done; ++spins) {
+        bool ok = true;
+        for (uint32_t i = lane; i < gridDim.x; i += 32u) {
+            uint32_t v;
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(seq + 2u + i) : "memory");
+            ok = ok && v == tag;
+        }
+        done = __all_sync(0xFFFFFFFFu, ok);
+        if (!done) __nanosleep(200);
     }
-    return static_cast<uint32_t>((old >> 32) % 0xFFFFFFFFull) + 1u;
+    if (lane == 0) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(seq), "r"(tag) : "memory");
+    return done;
 }
 
 }  // namespace csdr
