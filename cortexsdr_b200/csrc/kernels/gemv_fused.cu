@@ -11,8 +11,8 @@
 //              of launch n+1 overlaps the tail of launch n.
 //   phase A    after the wait: x slab to shared memory, FMAs, warp-shuffle reduction. Each
 //              column-split partial leaves as ONE 64-bit word {value, launch epoch}. The
-//              epoch is read from a counter in device memory that the launch's last CTA
-//              advances, so a captured CUDA graph tags every replay afresh.
+//              epoch is read (a plain load) from a word in device memory that CTA 0 moves on
+//              once every CTA has read it, so a captured CUDA graph tags every replay afresh.
 //   hand-over  no barrier, no atomics, no fence (a device-wide fence behind an 8 MB read
 //              burst was measured at up to 7 us): phase B polls the partial words
 //              themselves, sixteen independent loads per thread per round, until every word

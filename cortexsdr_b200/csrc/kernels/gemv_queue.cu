@@ -31,8 +31,9 @@
 //
 // A matching tag proves the value beside it (64-bit relaxed gpu-scope accesses are single-copy
 // atomic), so no hand-over needs a fence, a counter or an atomic, and the data itself is what is
-// polled. The tag is the count of queue launches completed, plus one, read from device memory
-// (the last CTA to have read it advances it), so a captured CUDA graph tags every replay afresh.
+// polled. The tag is one more than the tag of the launch before, read from device memory with a
+// plain load (CTA 0's loader moves the word on once every CTA has left the tag it read in a slot
+// of its own), so a captured CUDA graph tags every replay afresh.
 //
 // The decoder glue of api/cortex_sdk.cpp:1569-1679 is folded in so that a block of the decoder
 // is one list: bias, residual add (add_vectors, :1234-1243) and SwiGLU against the task before
