@@ -59,8 +59,7 @@ __device__ __forceinline__ size_t y_index(const YView& v, uint32_t r, uint32_t b
 // afresh. seq[0] is the last tag handed out; seq[2 + cta] is where a CTA leaves the tag it took.
 //   * Every CTA reads seq[0] with a plain load behind its dependency wait (the launch before has
 //     completed by then, its write of seq[0] is visible) and leaves tag = seq[0] + 1 in its own
-//     slot: no atomic, nothing to wait for. (All CTAs of a launch checking in with an atomic on
-//     one word took 4 us for 148 CTAs: same-address atomics serialise in L2.)
+//     slot: no atomic, nothing to wait for.
 //   * One warp of CTA 0 that has nothing else to do retires the tag: it waits (bounded) until
 //     every CTA's slot holds the tag - every CTA has read seq[0] - and only then writes
 //     seq[0] = tag for the next launch.
