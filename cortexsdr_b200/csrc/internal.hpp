@@ -55,6 +55,8 @@ struct DeviceBuffer {
     int device = 0;
     // Derived data cached beside the buffer and freed with it (a dictionary's bf16 planes).
     std::shared_ptr<void> aux;
+    // A dictionary's atoms re-laid in the blocks the list kernel's loader fetches (gemv_queue.cu).
+    std::shared_ptr<DeviceBuffer> stage_blocks;
     DeviceBuffer(size_t n, int dev);
     ~DeviceBuffer();
     void release_data();   // frees the memory now; what hangs on `aux` stays

@@ -9,12 +9,14 @@
 //
 //   loader    (1 warp)  walks the flat list of work units (task, group of 8 atoms) this CTA owns
 //                       and keeps a ring of shared-memory stages full: per stage 8 dictionary rows
-//                       x 1024 columns and, for activations that were there before the launch, the
-//                       matching slab of them, all as cp.async.bulk copies that signal the stage's
-//                       mbarrier. The dictionary is static, so the first ring-full of weight
-//                       copies is issued BEFORE the programmatic-dependent-launch wait, and the
-//                       weights of a task whose activations another task of the list is still
-//                       producing are in flight while it waits.
+//                       x 1024 columns - ONE cp.async.bulk copy, from a copy of the dictionary
+//                       re-laid in exactly these blocks when the list kernel first meets it - and,
+//                       for activations that were there before the launch, the matching slab of
+//                       them, all signalling the stage's mbarrier. The dictionary is static, so
+//                       the first ring-full of weight copies is issued BEFORE the
+//                       programmatic-dependent-launch wait, and the weights of a task whose
+//                       activations another task of the list is still producing are in flight
+//                       while it waits.
 //   products  (8 warps) one atom per warp: dot products of the staged row slab with the staged
 //                       activations, accumulated over the row's slabs in registers, reduced with
 //                       warp shuffles, and published as ONE 64-bit word {value, launch tag} per
@@ -71,7 +73,7 @@ enum : uint32_t { X_PLAIN = 0, X_TAGGED = 1 };
 typedef unsigned long long u64;
 
 struct QTask {
-    const float* D;
+    const float* D;           // the dictionary in stage blocks (stage_blocks_kernel), not row-major
     const uint16_t* codes;
     const float* scales;
     const void* x;            // X_PLAIN: activations (dtype, layout); X_TAGGED: u64 words [M][C]
@@ -236,12 +238,14 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(n_atoms * cw * 4u)
                              : "memory");
             __syncwarp();
-            if (lane < n_atoms) {
-                const float* src = t.D + static_cast<size_t>(atom0 + lane) * t.C + c0;
-                const uint32_t dst = smem_u32(qsm + static_cast<size_t>(slot) * p.stage_bytes + lane * (kSlab * 4u));
+            if (lane == 0) {
+                // the stage's rows are ONE block of the re-laid dictionary (stage_blocks_kernel): one copy
+                // (eight copies of one row slab each kept the loader busy issuing: 10 % of the pass)
+                const float* src = t.D + static_cast<size_t>(atom0) * t.C + static_cast<size_t>(n_atoms) * c0;
+                const uint32_t dst = smem_u32(qsm + static_cast<size_t>(slot) * p.stage_bytes);
                 asm volatile(
                     "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                    "l"(src), "r"(cw * 4u), "r"(bar)
+                    "l"(src), "r"(n_atoms * cw * 4u), "r"(bar)
                     : "memory");
             }
             ++it_issue;
@@ -414,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                     failed_s = 1;
                 }
                 if (ok && atom < t.K) {
-                    const float4* d4 = reinterpret_cast<const float4*>(st + w * (kSlab * 4u));
+                    const float4* d4 = reinterpret_cast<const float4*>(st + static_cast<size_t>(w) * cw * 4u);   // rows packed at the slab's width
                     const float4* x4 = reinterpret_cast<const float4*>(st + kAtomsPerUnit * kSlab * 4u);
                     const uint32_t cw4 = cw >> 2;
 #pragma unroll
@@ -665,6 +669,39 @@ uint32_t code_bytes_per_warp(const csdr_context* ctx, const Geometry& g, bool sp
     return (split ? rpc / kGatherWarps : rpc) * g.slots() * 2u;
 }
 
+// The dictionary re-laid for the loader: atoms in groups of eight (a unit), a unit's columns in
+// slabs of kSlab, and the rows of one (unit, slab) one behind the other - the bytes of one stage,
+// contiguous. Block (u, s) starts at float u * 8 * C + n_u * s * kSlab (n_u = atoms of unit u:
+// 8, fewer in the last unit) and holds n_u rows of cw_s = min(kSlab, C - s * kSlab) floats.
+__global__ void __launch_bounds__(256)
+stage_blocks_kernel(const float* __restrict__ D, uint32_t K, uint32_t C, float* __restrict__ out) {
+    const size_t n = static_cast<size_t>(K) * C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint32_t a = static_cast<uint32_t>(i / C), c = static_cast<uint32_t>(i - static_cast<size_t>(a) * C);
+        const uint32_t u = a / kAtomsPerUnit, r = a - u * kAtomsPerUnit;
+        const uint32_t s = c / kSlab, cc = c - s * kSlab;
+        const uint32_t n_u = min(kAtomsPerUnit, K - u * kAtomsPerUnit), cw = min(kSlab, C - s * kSlab);
+        out[static_cast<size_t>(u) * kAtomsPerUnit * C + static_cast<size_t>(n_u) * s * kSlab + static_cast<size_t>(r) * cw + cc] = D[i];
+    }
+}
+
+// Built on a dictionary's first use by the list kernel and kept with it (as many bytes again as the
+// atoms): not inside a stream capture, like every first use that allocates.
+const DeviceBuffer* stage_blocks_of(csdr_context* ctx, const csdr_segment* seg) {
+    DeviceBuffer* atoms = seg->atoms.get();
+    if (!atoms->stage_blocks) {
+        const Geometry& g = seg->g;
+        auto blocks = std::make_shared<DeviceBuffer>(static_cast<size_t>(g.n_atoms) * g.cols * sizeof(float), ctx->device);
+        const size_t n = static_cast<size_t>(g.n_atoms) * g.cols;
+        LaunchScope ls(ctx, KC_GEMV_QUEUE);
+        stage_blocks_kernel<<<static_cast<unsigned>(std::min<size_t>((n + 255) / 256, static_cast<size_t>(ctx->sm_count) * 16)), 256, 0, ctx->stream>>>(
+            static_cast<const float*>(atoms->ptr), g.n_atoms, g.cols, static_cast<float*>(blocks->ptr));
+        ls.done("stage_blocks_kernel");
+        atoms->stage_blocks = blocks;
+    }
+    return atoms->stage_blocks.get();
+}
+
 template <int MT>
 void launch_t(csdr_context* ctx, QParams& p, uint32_t max_k, uint32_t max_code_bytes) {
     auto kern = hsdr_gemv_queue_kernel<MT>;
@@ -676,6 +713,7 @@ void launch_t(csdr_context* ctx, QParams& p, uint32_t max_k, uint32_t max_code_b
     const size_t budget = smem_budget(ctx);
     if (tail + 3u * p.stage_bytes > budget) throw Error(CSDR_ERR_LIMIT, "GEMV queue: shared memory need exceeds the device limit");
     p.n_stages = static_cast<uint32_t>(std::min<size_t>(kMaxStages, (budget - tail) / p.stage_bytes));
+    if (const char* e = std::getenv("CSDR_QUEUE_STAGES")) p.n_stages = std::max(2u, std::min<uint32_t>(p.n_stages, static_cast<uint32_t>(std::atoi(e))));
     const size_t smem = tail + static_cast<size_t>(p.n_stages) * p.stage_bytes;
     ctx->opt_in_smem(reinterpret_cast<const void*>(kern), smem);
     cudaLaunchConfig_t cfg{};
@@ -768,7 +806,7 @@ void launch_gemv_queue(csdr_context* ctx, const QueueItem* items, uint32_t n) {
             const QueueItem& it = items[i0 + i];
             const Geometry& g = it.seg->g;
             QTask& t = p.task[i];
-            t.D = static_cast<const float*>(it.seg->atoms->ptr);
+            t.D = static_cast<const float*>(stage_blocks_of(ctx, it.seg)->ptr);
             t.codes = it.seg->codes_ptr();
             t.scales = static_cast<const float*>(it.seg->scales->ptr);
             t.x = it.x;
