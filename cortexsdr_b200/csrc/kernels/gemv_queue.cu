@@ -713,7 +713,6 @@ void launch_t(csdr_context* ctx, QParams& p, uint32_t max_k, uint32_t max_code_b
     const size_t budget = smem_budget(ctx);
     if (tail + 3u * p.stage_bytes > budget) throw Error(CSDR_ERR_LIMIT, "GEMV queue: shared memory need exceeds the device limit");
     p.n_stages = static_cast<uint32_t>(std::min<size_t>(kMaxStages, (budget - tail) / p.stage_bytes));
-    if (const char* e = std::getenv("CSDR_QUEUE_STAGES")) p.n_stages = std::max(2u, std::min<uint32_t>(p.n_stages, static_cast<uint32_t>(std::atoi(e))));
     const size_t smem = tail + static_cast<size_t>(p.n_stages) * p.stage_bytes;
     ctx->opt_in_smem(reinterpret_cast<const void*>(kern), smem);
     cudaLaunchConfig_t cfg{};
