@@ -161,7 +161,7 @@ DECODERS = {
 
 
 FUSED_GEMV_DRAM_BYTES_NCU = 8996000   # per launch, cfg2 shape, batch 1 (8.996 MB read, 0 written)
-QUEUE_DRAM_BYTES_PER_TASK_NCU = 9171000   # per product of the list kernel, cfg2 shape, batch 1 (146.7 MB per 16-product launch)
+QUEUE_DRAM_BYTES_PER_TASK_NCU = 9207000   # per product of the list kernel, cfg2 shape, batch 1 (147.3 MB per 16-product launch)
 
 
 def decoder_bench(name, cs, torch, dist, ctx, stream, rank, world, comm, use_graph=True, kv_dtype="f32",
