@@ -299,9 +299,16 @@ __global__ void __launch_bounds__(kThreads, 1) hsdr_gemv_queue_kernel(const __gr
                 fi += gridDim.x;
             }
         };
-        // the first ring-full of weight copies does not depend on anything before this launch
-        while (ui < p.n_units && it_issue < NS) issue();
+        // The first weight copies do not depend on anything before this launch: two stages go out
+        // ahead of the dependency wait. Not the whole ring: the launch tag and the first activation
+        // slabs are small loads that would queue up behind 160 KB of weight traffic per SM (the tag
+        // came back 2 us late with five stages ahead of it); the loop below fills the rest of the
+        // ring, activations first.
+        if (lane == 0) stamp(p, 1, 7);
+        while (ui < p.n_units && it_issue < min(NS, 2u)) issue();
+        if (lane == 0) stamp(p, 3, 7);
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (lane == 0) stamp(p, 4, 7);
         if (lane == 0) {
             tag_s = read_launch_tag(p.seq);
             stamp(p, 0, 6);
