@@ -113,7 +113,8 @@ struct QParams {
 };
 
 // slots: 0 first activations staged, 1 Dx of the CTA's first unit of the task published,
-// 2 gather warp 0 saw the watch words, 3 swept Dx, 4 rows written; 5 kernel entry, 6 tag taken
+// 2 gather warp 0 saw the watch words, 3 swept Dx, 4 rows written; 5 kernel entry, 6 tag taken;
+// slot 7 of tasks 1, 3, 4: the loader starts, has issued its first copies, is past the dependency wait
 __device__ __forceinline__ void stamp(const QParams& p, uint32_t task, uint32_t slot) {
     if (p.trace && task < 8u) {
         unsigned long long t;
