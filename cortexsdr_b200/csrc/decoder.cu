@@ -112,6 +112,11 @@ struct csdr_decoder {
     // squares: [sum_pad floats][Dx of every member]; tensor-parallel ranks add theirs up in place
     DevPtr dxbuf;
     uint32_t sum_pad = 0;
+    // the RMS-norm half that rides on the output and down gathers of a decode step:
+    // [kNextNormCtas][16] shares of the sums of squares, and how many CTAs of the last such
+    // gather left shares for the projection launch behind it to add up (0: none pending)
+    DevPtr norm_scratch;
+    uint32_t norm_pending = 0;
     // peer-memory exchange of partial projections between tensor-parallel ranks (steps of at
     // most 16 tokens); until the host program has passed the peers' handles in, NCCL sums them
     DevPtr xch_region;
@@ -297,9 +302,13 @@ void sum_over_ranks(csdr_decoder* d, float* from, size_t floats) {
 // silu(gate) * up into these planes and returns true; else the caller applies SiLU itself.
 // `partial`: every rank holds a column slice of the dictionaries, so the projections must be
 // summed over the ranks before the gather.
+// `next_w` (one linear): the first half of the next RMS normalisation of the output - planes of
+// next_w * y into the hidden planes, sums of y^2 into the sums block - rides on the gather when
+// the step is a single token tile (the gather leaves shares of the sums, the next call's
+// projection launch adds them up), and is a launch of its own behind the gather otherwise.
 bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_bfloat16* planes, size_t plane_elems,
           uint32_t T, bool normed, bool partial, const float* sums, std::initializer_list<WideOut> outs,
-          __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr) {
+          __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr, const float* next_w = nullptr) {
     const csdr_segment* segs[4];
     WideOut o[4];
     uint32_t n = 0;
@@ -312,28 +321,41 @@ bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
     float* base = F(d->dxbuf);
     TokenScale ts{};
     if (normed) ts = TokenScale{sums, 1.0f / static_cast<float>(d->cfg.hidden), d->cfg.rms_eps};
+    NextNorm nn{};
+    if (next_w) {
+        __nv_bfloat16* h_hi = BF(d->xp_h);
+        nn = NextNorm{next_w, h_hi, h_hi + static_cast<size_t>(T) * d->H_l, F(d->norm_scratch)};
+    }
+    // shares left by the previous call's gather: this call's projection adds them up
+    const NormShares shares{F(d->norm_scratch), d->norm_pending, F(d->dxbuf)};
+    d->norm_pending = 0;
+    auto gather = [&](const WideDx& w) {
+        const uint32_t rode = launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts, next_w ? &nn : nullptr);
+        if (next_w && !rode) op_scale_sumsq_planes(d->ctx, o[0].y, next_w, T, d->H_l, nn.hi, nn.lo, F(d->dxbuf));
+        d->norm_pending = rode;
+    };
     uint32_t total_atoms = 0;
     for (uint32_t i = 0; i < n; ++i) total_atoms += segs[i]->g.n_atoms;
     if (partial && d->xch_use && T <= 16u && d->sum_pad + static_cast<size_t>(total_atoms) * 16u <= d->xch_blk) {
         // the projection kernel stores its finished rows into every rank's exchange slot and
         // raises the flags; a small launch waits for all ranks and sums the slots into the local
         // block; the gather then runs as on one GPU
-        const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, &d->xch, base, nullptr);
+        const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, &d->xch, base, nullptr, &shares);
         launch_exchange_reduce(d->ctx, d->xch, d->sum_pad, w.floats, w.base);
         if (act_hi) {
             launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo);
             return true;
         }
-        launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts);
+        gather(w);
         return false;
     }
-    const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad);
+    const WideDx w = launch_wide_project(d->ctx, segs, n, xp, T, base + d->sum_pad, nullptr, nullptr, nullptr, &shares);
     if (partial) sum_over_ranks(d, w.base, w.floats);
     if (act_hi && w.tile_mt) {
         launch_wide_gather_swiglu(d->ctx, segs, w, T, ts, act_hi, act_lo);
         return true;
     }
-    launch_wide_gather(d->ctx, segs, n, w, T, o, CSDR_LAYOUT_TOKEN_MAJOR, ts);
+    gather(w);
     return false;
 }
 
@@ -341,8 +363,9 @@ bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_b
 // every step under tensor parallelism). Every glue kernel hands its result to the next
 // projection as bf16 planes; q|k|v and gate|up share a projection launch and a gather launch;
 // the residual additions ride on the gathers of the output and down projections; RMS
-// normalisation is split into "planes of w*h + sums of squares" before the projection and
-// "times 1/rms" in the gather; SwiGLU is folded into the gate|up gather for single token tiles.
+// normalisation is split into "planes of w*h + sums of squares" before the projection (for single
+// token tiles part of the gather that produced h, else a launch of its own) and "times 1/rms" in
+// the gather; SwiGLU is folded into the gate|up gather for single token tiles.
 // With P ranks the hidden state is replicated; heads, KV cache and intermediate width are sliced
 // P ways, q|k|v|gate|up by code rows, and the output and down projections by dictionary columns,
 // so that the only exchanges are the sums of those two projections' partial results (K x T
@@ -359,6 +382,7 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
     __nv_bfloat16* i_hi = BF(d->xp_act);
     const size_t h_n = static_cast<size_t>(T) * Hl, a_n = static_cast<size_t>(T) * d->QD_l, i_n = static_cast<size_t>(T) * d->I_l;
     op_scale_sumsq_planes(ctx, F(d->hidden), F(d->layers[0].attn_norm), T, Hl, h_hi, h_hi + h_n, sums);
+    d->norm_pending = 0;    // a step that ended in an error may have left shares behind
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         Layer& L = d->layers[li];
         wide(d, {&L.q, &L.k, &L.v}, h_hi, h_n, T, true, false, sums,
@@ -369,14 +393,16 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
                       c.max_seq, c.rope_theta);
         op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, nullptr,
                      a_hi, a_hi + a_n);
-        wide(d, {&L.o}, a_hi, a_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
-        op_scale_sumsq_planes(ctx, F(d->hidden), F(L.ffn_norm), T, Hl, h_hi, h_hi + h_n, sums);
+        wide(d, {&L.o}, a_hi, a_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}}, nullptr, nullptr,
+             F(L.ffn_norm));
         if (!wide(d, {&L.gate, &L.up}, h_hi, h_n, T, true, false, sums,
                   {WideOut{F(d->gate), nullptr, nullptr}, WideOut{F(d->up), nullptr, nullptr}}, i_hi, i_hi + i_n))
             op_silu_mul_planes(ctx, F(d->gate), F(d->up), i_n, i_hi, i_hi + i_n);
-        wide(d, {&L.down}, i_hi, i_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}});
-        const float* next_norm = li + 1 < c.n_layers ? F(d->layers[li + 1].attn_norm) : F(d->out_norm);
-        op_scale_sumsq_planes(ctx, F(d->hidden), next_norm, T, Hl, h_hi, h_hi + h_n, sums);
+        // the last block's sums have no projection launch behind them to add shares up
+        const bool last = li + 1 == c.n_layers;
+        wide(d, {&L.down}, i_hi, i_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}}, nullptr, nullptr,
+             last ? nullptr : F(d->layers[li + 1].attn_norm));
+        if (last) op_scale_sumsq_planes(ctx, F(d->hidden), F(d->out_norm), T, Hl, h_hi, h_hi + h_n, sums);
     }
 }
 
@@ -771,6 +797,8 @@ int csdr_decoder_create(csdr_archive* ar, const csdr_decoder_config* cfg, csdr_d
                 d->sum_pad = static_cast<uint32_t>((T + 63) / 64 * 64);
                 d->dxbuf = dev_alloc(ctx, (d->sum_pad + static_cast<size_t>(widest) * std::max<size_t>(T, 16)) * 4);
                 CSDR_CUDA(cudaMemsetAsync(d->dxbuf->ptr, 0, d->dxbuf->bytes, ctx->stream));
+                d->norm_scratch = dev_alloc(ctx, static_cast<size_t>(kNextNormCtas) * 16u * 4u);
+                CSDR_CUDA(cudaMemsetAsync(d->norm_scratch->ptr, 0, d->norm_scratch->bytes, ctx->stream));
             }
         }
         if (d->P > 1 && d->P <= kMaxExchangeRanks) {

@@ -364,6 +364,13 @@ __device__ __forceinline__ void warp_sums(float (&s)[N], uint32_t lane) {
     for (int u = 0; u < N; ++u) s[u] = __shfl_sync(0xFFFFFFFFu, mine, u << shift);
 }
 
+// 2^x in one instruction (ex2.approx: relative error 2^-22; 2^-inf = 0).
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // WARPS warps split the keys of one (token, head); few (token, head) pairs (batched decode
 // against a long context) take more warps each so that enough K/V rows are in flight per SM.
 // The cache element type of an attention kernel, from its pointer type (host-side launch helper).
@@ -397,17 +404,34 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
     const size_t base = static_cast<size_t>(seq_of[t]) * max_seq * row + kvh * HD + lane * VPL;
     float qv[VPL], acc[VPL];
     load_row<VPL>(q + (static_cast<size_t>(t) * QH + h) * HD + lane * VPL, qv);
+    // scores are kept as log2 of the softmax weights (the query carries scale * log2 e), so that a
+    // weight is one ex2 instruction; maxima and running sums are in the same units throughout
+    const float qscale = scale * 1.4426950408889634f;
 #pragma unroll
-    for (int e = 0; e < VPL; ++e) acc[e] = 0.0f;
+    for (int e = 0; e < VPL; ++e) {
+        qv[e] *= qscale;
+        acc[e] = 0.0f;
+    }
     float m = -INFINITY, l = 0.0f;
     const uint32_t crank = kSplit ? blockIdx.z : 0u, csize = kSplit ? gridDim.z : 1u;
     for (int32_t j0 = (crank * kAttnWarps + warp) * kKeys; j0 < n_keys; j0 += csize * kAttnWarps * kKeys) {
         CacheRow<KV, VPL> kv[kKeys], vv[kKeys];
+        const bool whole = j0 + kKeys <= n_keys;   // warp-uniform: every step but a warp's last
+        if (whole) {
+            const KV* k0 = kc + base + static_cast<size_t>(j0) * row;
+            const KV* v0 = vc + base + static_cast<size_t>(j0) * row;
 #pragma unroll
-        for (int u = 0; u < kKeys; ++u) {
-            const int32_t j = min(j0 + u, n_keys - 1);   // clamp: the tail re-reads the last row, unused
-            kv[u].load(kc + base + static_cast<size_t>(j) * row);
-            vv[u].load(vc + base + static_cast<size_t>(j) * row);
+            for (int u = 0; u < kKeys; ++u) {
+                kv[u].load(k0 + static_cast<size_t>(u) * row);
+                vv[u].load(v0 + static_cast<size_t>(u) * row);
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < kKeys; ++u) {
+                const int32_t j = min(j0 + u, n_keys - 1);   // clamp: the tail re-reads the last row, unused
+                kv[u].load(kc + base + static_cast<size_t>(j) * row);
+                vv[u].load(vc + base + static_cast<size_t>(j) * row);
+            }
         }
         float s[kKeys];
 #pragma unroll
@@ -421,16 +445,18 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
         // the keys of a step join the running softmax together: one new maximum, one correction of
         // what has been summed so far, then every key's weight
         float m_new = m;
+        if (!whole) {
 #pragma unroll
-        for (int u = 0; u < kKeys; ++u) {
-            s[u] = j0 + u < n_keys ? s[u] * scale : -INFINITY;
-            m_new = fmaxf(m_new, s[u]);
+            for (int u = 0; u < kKeys; ++u)
+                if (j0 + u >= n_keys) s[u] = -INFINITY;
         }
-        const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first step; the step's first key is always valid
+#pragma unroll
+        for (int u = 0; u < kKeys; ++u) m_new = fmaxf(m_new, s[u]);
+        const float corr = exp2_fast(m - m_new);   // 2^-inf = 0 on the first step; the step's first key is always valid
         float psum = 0.0f;
 #pragma unroll
         for (int u = 0; u < kKeys; ++u) {
-            s[u] = expf(s[u] - m_new);        // exp(-inf) = 0 for the keys past the end
+            s[u] = exp2_fast(s[u] - m_new);        // 2^-inf = 0 for the keys past the end
             psum += s[u];
         }
         l = fmaf(l, corr, psum);
@@ -458,7 +484,7 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
         for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm_m[w]);
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
-            const float f = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
+            const float f = sm_m[w] == -INFINITY ? 0.0f : exp2_fast(sm_m[w] - M);
             L = fmaf(sm_l[w], f, L);
 #pragma unroll
             for (int e = 0; e < VPL; ++e) o[e] = fmaf(sm_acc[w][lane * VPL + e], f, o[e]);
@@ -486,7 +512,7 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
             for (int e = 0; e < VPL; ++e) oc[e] = 0.0f;
             for (uint32_t r = 0; r < csize; ++r) {                       // in rank order: the result does not depend on timing
                 const float mr = cluster.map_shared_rank(&sm_m[0], r)[0];
-                const float f = mr == -INFINITY ? 0.0f : expf(mr - Mc);
+                const float f = mr == -INFINITY ? 0.0f : exp2_fast(mr - Mc);
                 Lc = fmaf(cluster.map_shared_rank(&sm_l[0], r)[0], f, Lc);
                 const float* ar = cluster.map_shared_rank(&sm_acc[0][0], r);
 #pragma unroll

@@ -558,6 +558,7 @@ struct GatherGroupParams {
     TokenScale ts;
     __nv_bfloat16* act_hi;    // SwiGLU pair: planes of silu(member 0) * member 1, laid out like y
     __nv_bfloat16* act_lo;
+    NextNorm next;            // NORM instances only
 };
 
 
@@ -630,9 +631,12 @@ __global__ void __launch_bounds__(256) exchange_reduce_kernel(const __grid_const
 // PAIR: the group is (gate, up) of a SwiGLU block with equal row counts; a CTA gathers the same
 // rows of both and writes silu(gate) * up as bf16 planes (silu_mul, api/cortex_sdk.cpp:1245-1256,
 // folded in), so the two fp32 intermediates never exist.
-template <int MT, bool PAIR>
+// NORM (one member, token-major y): the first half of the next RMS normalisation rides along,
+// see NextNorm.
+template <int MT, bool PAIR, bool NORM>
 __global__ void __launch_bounds__(kGroupThreads)
 hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
+    static_assert(!(PAIR && NORM), "the SwiGLU pair has no next norm");
     extern __shared__ __align__(16) unsigned char ggsm[];
     asm volatile("griddepcontrol.launch_dependents;");
     constexpr uint32_t NM = PAIR ? 2u : 1u;      // members this CTA works on
@@ -689,9 +693,10 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    if (!active) return;
+    if (!NORM && !active) return;
     const uint32_t b = tid % MT;
     constexpr uint32_t RP = kGroupThreads / MT;
+    float ss = 0.0f;    // NORM: this thread's share of its token's sum of squares
     for (uint32_t rl = tid / MT; rl < rows_here; rl += RP) {
         float res[NM];
 #pragma unroll
@@ -731,16 +736,35 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
                 float acc = res[0];
                 if (m0.residual) acc += m0.residual[o];
                 m0.y[o] = acc;
+                if (NORM) {
+                    ss = fmaf(acc, acc, ss);
+                    const float p = acc * g.next.w[r];
+                    const __nv_bfloat16 h = __float2bfloat16_rn(p);
+                    g.next.hi[o] = h;
+                    g.next.lo[o] = __float2bfloat16_rn(p - __bfloat162float(h));
+                }
             }
+        }
+    }
+    if (NORM) {
+        __shared__ float red_s[kGroupThreads];
+        red_s[tid] = ss;                       // index = row lane * MT + token
+        __syncthreads();
+        if (tid < 16u) {
+            float t = 0.0f;
+            if (tid < MT)
+                for (uint32_t j = 0; j < RP; ++j) t += red_s[j * MT + tid];
+            g.next.partial[blockIdx.x * 16u + tid] = t;
         }
     }
 }
 
 template <int MT>
-void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t total_rows, uint32_t max_k, uint32_t max_slots) {
-    const bool pair = g.act_hi != nullptr;
+uint32_t launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t total_rows, uint32_t max_k, uint32_t max_slots) {
+    const bool pair = g.act_hi != nullptr, norm = g.next.w != nullptr;
     // about three CTAs per SM over the whole group (a pair walks the rows of one member)
-    const uint32_t want = 3u * static_cast<uint32_t>(ctx->sm_count);   // measured best of 1..4 on the 7B-shaped decode
+    uint32_t want = 3u * static_cast<uint32_t>(ctx->sm_count);   // measured best of 1..4 on the 7B-shaped decode
+    if (norm) want = std::min(want, kNextNormCtas);
     const uint32_t rows_all = pair ? g.m[0].R : total_rows;
     const uint32_t rows_per_cta = std::max(kGroupThreads / MT, (rows_all + want - 1u) / want);
     uint32_t ctas = 0;
@@ -752,7 +776,8 @@ void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t tot
     g.code_cap16 = (rows_per_cta * max_slots * 2u + 15u + 16u) >> 4;
     g.region_bytes = static_cast<uint32_t>(static_cast<size_t>(g.code_cap16) * 16u + 64u * 4u + static_cast<size_t>(max_k) * MT * 4u);
     const size_t smem = static_cast<size_t>(g.region_bytes) * (pair ? 2u : 1u);
-    auto kern = pair ? hsdr_gather_group_kernel<MT, true> : hsdr_gather_group_kernel<MT, false>;
+    auto kern = pair ? hsdr_gather_group_kernel<MT, true, false>
+                     : norm ? hsdr_gather_group_kernel<MT, false, true> : hsdr_gather_group_kernel<MT, false, false>;
     ctx->opt_in_smem(reinterpret_cast<const void*>(kern), smem);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(ctas, 1, 1);
@@ -767,6 +792,7 @@ void launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t tot
     LaunchScope ls(ctx, KC_GATHER);
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, g));
     ls.done("hsdr_gather_group_kernel");
+    return ctas;
 }
 
 void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float* dx, uint32_t M, const YView& yv,
@@ -810,7 +836,8 @@ bool wide_group_supported(const csdr_context* ctx, const csdr_segment* const* se
 }
 
 WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x, uint32_t M,
-                           float* dx_base, const Exchange* xch, const float* blk_base, const float* sums) {
+                           float* dx_base, const Exchange* xch, const float* blk_base, const float* sums,
+                           const NormShares* shares) {
     if (n == 0 || n > kGatherGroupMax) throw Error(CSDR_ERR_LIMIT, "matmul group holds 1 to 4 segments");
     WideDx w{};
     if (M <= 16u) {
@@ -828,15 +855,16 @@ WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, u
         w.dx[i] = w.base + off;
         off += static_cast<size_t>(segs[i]->g.n_atoms) * w.stride;
     }
-    launch_dx_tma_group(ctx, segs, n, x, M, w.dx, w.stride, xch, blk_base, sums);
+    launch_dx_tma_group(ctx, segs, n, x, M, w.dx, w.stride, xch, blk_base, sums, false, shares);
     return w;
 }
 
 namespace {
-void gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
+uint32_t gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
                        const WideOut* outs, int y_layout, const TokenScale& ts, __nv_bfloat16* act_hi = nullptr,
-                       __nv_bfloat16* act_lo = nullptr) {
+                       __nv_bfloat16* act_lo = nullptr, const NextNorm* next = nullptr) {
     GatherGroupParams g{};
+    if (next) g.next = *next;
     if (act_hi) {
         if (n != 2 || segs[0]->g.rows != segs[1]->g.rows || !act_lo)
             throw Error(CSDR_ERR_INVALID_ARG, "a SwiGLU pair is two segments with the same number of rows");
@@ -858,25 +886,27 @@ void gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, uint3
         max_slots = std::max(max_slots, sg.slots());
     }
     switch (w.tile_mt) {
-        case 1: launch_gather_group_t<1>(ctx, g, total_rows, max_k, max_slots); break;
-        case 2: launch_gather_group_t<2>(ctx, g, total_rows, max_k, max_slots); break;
-        case 4: launch_gather_group_t<4>(ctx, g, total_rows, max_k, max_slots); break;
-        case 8: launch_gather_group_t<8>(ctx, g, total_rows, max_k, max_slots); break;
-        default: launch_gather_group_t<16>(ctx, g, total_rows, max_k, max_slots); break;
+        case 1: return launch_gather_group_t<1>(ctx, g, total_rows, max_k, max_slots);
+        case 2: return launch_gather_group_t<2>(ctx, g, total_rows, max_k, max_slots);
+        case 4: return launch_gather_group_t<4>(ctx, g, total_rows, max_k, max_slots);
+        case 8: return launch_gather_group_t<8>(ctx, g, total_rows, max_k, max_slots);
+        default: return launch_gather_group_t<16>(ctx, g, total_rows, max_k, max_slots);
     }
 }
 }  // namespace
 
-void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
-                        const WideOut* outs, int y_layout, const TokenScale& ts) {
+uint32_t launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
+                            const WideOut* outs, int y_layout, const TokenScale& ts, const NextNorm* next) {
     if (w.tile_mt) {
-        gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts);
-        return;
+        const bool ride = next && next->w && n == 1u && y_layout == CSDR_LAYOUT_TOKEN_MAJOR;
+        const uint32_t ctas = gather_tile_group(ctx, segs, n, w, M, outs, y_layout, ts, nullptr, nullptr, ride ? next : nullptr);
+        return ride ? ctas : 0u;
     }
     for (uint32_t i = 0; i < n; ++i) {
         YView yv{outs[i].y, y_layout, segs[i]->g.rows, M, 0u, M, outs[i].bias};
         launch_gather_wide(ctx, segs[i], w.dx[i], M, yv, outs[i].residual, ts);
     }
+    return 0u;
 }
 
 void launch_exchange_reduce(csdr_context* ctx, const Exchange& x, uint32_t off_floats, size_t floats, float* dst) {

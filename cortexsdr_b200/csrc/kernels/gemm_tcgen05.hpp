@@ -40,15 +40,17 @@ struct XPlanesView {
 // 16-byte aligned, else a conversion into context scratch (valid until the next conversion).
 XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_layout, uint32_t M, uint32_t cols);
 struct Exchange;
+struct NormShares;
 // One projection launch for up to four dictionaries over the same activations (q|k|v, gate|up).
 // With an exchange (tensor parallelism, at most 16 tokens) the finished rows go into every
 // rank's slot for this rank, at the offsets dx[i] - blk_base, `sums` (this rank's per-token sums
 // of squares, or null) ride along at offset 0, and the launch's last CTA raises the flags: the
 // projection and its share of the collective are one kernel. transposed (one dictionary, no
 // exchange): Dx leaves token-major, [token][atom] with dx_stride floats between token rows.
+// shares: see NextNorm.
 void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
                          float* const* dx, uint32_t dx_stride, const Exchange* xch, const float* blk_base,
-                         const float* sums, bool transposed = false);
+                         const float* sums, bool transposed = false, const NormShares* shares = nullptr);
 
 // Up to four row-tile segments over the same activation planes: one projection launch and, for
 // a single token tile (M <= 16), one gather launch for the whole group. y = W x (+ bias)
@@ -65,6 +67,24 @@ struct TokenScale {
     const float* sumsq = nullptr;
     float inv_width = 0.0f;
     float eps = 0.0f;
+};
+// The first half of the NEXT RMS normalisation, riding on a one-member gather over a single token
+// tile: beside y the gather writes the bf16 planes of w * y (what the next projection reads) and
+// every CTA leaves its share of the per-token sums of y^2 in `partial`. The projection launch
+// behind the gather gets the shares as NormShares and one of its CTAs adds them up, in CTA order
+// (so the sums do not depend on any order of arrival), into `sumsq`, where the gather behind that
+// projection finds them and turns them into 1 / rms.
+constexpr uint32_t kNextNormCtas = 1024;
+struct NextNorm {
+    const float* w = nullptr;       // the next norm's weights, one per row of y
+    __nv_bfloat16* hi = nullptr;    // planes of w * y, laid out like y (token-major)
+    __nv_bfloat16* lo = nullptr;
+    float* partial = nullptr;       // [kNextNormCtas][16] shares, one row per CTA of the gather
+};
+struct NormShares {
+    const float* partial = nullptr;
+    uint32_t ctas = 0;              // CTAs of the gather that left shares
+    float* sumsq = nullptr;         // [tokens]
 };
 // Where a group's projections live between the two launches: member i at dx[i], rows `stride`
 // floats apart, `floats` in all from `base` (one contiguous block, so that tensor-parallel
@@ -99,9 +119,11 @@ struct Exchange {
 // The two halves of launch_matmul_wide_group. dx_base == nullptr: context scratch.
 WideDx launch_wide_project(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, XPlanesView x, uint32_t M,
                            float* dx_base, const Exchange* xch = nullptr, const float* blk_base = nullptr,
-                           const float* sums = nullptr);
-void launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
-                        const WideOut* outs, int y_layout, const TokenScale& ts);
+                           const float* sums = nullptr, const NormShares* shares = nullptr);
+// Returns the number of CTAs that left shares when `next` was given and rode on the gather (one
+// member, single token tile, token-major y); 0 leaves the next norm's first half to the caller.
+uint32_t launch_wide_gather(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n, const WideDx& w, uint32_t M,
+                        const WideOut* outs, int y_layout, const TokenScale& ts, const NextNorm* next = nullptr);
 // Receiving side of the exchange: one small launch waits for every rank's flag and adds the
 // ranks' slots up, in rank order, over block range [off_floats, off_floats + floats) into the
 // local block at dst; the gather behind it reads the sum like any local projection.

@@ -134,6 +134,11 @@ struct Params {
     uint32_t* xch_seq;
     uint32_t* xch_done;
     const float* xch_sums;
+    // Shares of per-token sums of squares left by the gather before this launch (NextNorm): one
+    // CTA adds them up for the gather behind this launch. Null: none.
+    const float* norm_partial;
+    uint32_t norm_ctas;
+    float* norm_sumsq;
     int* status;
     uint32_t spin;               // mbarrier try_wait rounds before a wait gives up
     unsigned long long* trace;   // optional: 16 global-timer stamps per CTA (phase boundaries)
@@ -293,6 +298,30 @@ hsdr_dx_tma_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant
     const uint32_t pstride = N + 4u;
     float* ptile = reinterpret_cast<float*>(smem);
     bool done = true;
+    if (p.norm_partial && warp >= 2 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        // the four epilogue warps of one CTA have nothing to do until the accumulator is
+        // complete: they add up the shares, 32 partial sums of every token in a fixed order of
+        // CTAs, then those in order
+        __shared__ float share_s[32][16];
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const uint32_t t = tid - 64u, q = t & 3u, j = t >> 2;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (uint32_t c = j; c < p.norm_ctas; c += 32u) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(p.norm_partial + static_cast<size_t>(c) * 16u) + q);
+            a.x += v.x;
+            a.y += v.y;
+            a.z += v.z;
+            a.w += v.w;
+        }
+        *reinterpret_cast<float4*>(&share_s[j][q * 4u]) = a;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (t < 16u && t < p.M) {
+            float s = 0.0f;
+            for (uint32_t i = 0; i < 32u; ++i) s += share_s[i][t];
+            p.norm_sumsq[t] = s;
+        }
+    }
     if (warp >= 2) {
         done = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&accum_bar), 0u, p.spin));   // warp-uniform
         if (!done) failed_s = 1;
@@ -593,7 +622,7 @@ XPlanesView make_x_planes(csdr_context* ctx, const void* x, int x_dtype, int x_l
 
 void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uint32_t n_seg, XPlanesView x, uint32_t M,
                          float* const* dx, uint32_t dx_stride, const Exchange* xch, const float* blk_base,
-                         const float* sums, bool transposed) {
+                         const float* sums, bool transposed, const NormShares* shares) {
     using namespace tma_detail;
     if (transposed && ((xch && xch->ranks > 1u) || n_seg != 1u))
         throw Error(CSDR_ERR_INVALID_ARG, "a token-major projection is local and has one dictionary");
@@ -624,7 +653,7 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
     const uint32_t n_kb = (cols + kBlockK - 1u) / kBlockK;
     const uint32_t stage_bytes = 2u * kATile + (has_lo ? 2u : 1u) * N * 128u;
 
-    const size_t smem_max = ctx->smem_optin - 2048u;   // static barriers and alignment slack
+    const size_t smem_max = ctx->smem_optin - 4096u;   // static barriers, the shares block and alignment slack
     if (!ctx->tma_attrs_set) {
         ctx->opt_in_smem(reinterpret_cast<const void*>(hsdr_dx_tma_kernel), smem_max);
         if (cudaFuncSetAttribute(hsdr_dx_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess)
@@ -718,6 +747,13 @@ void launch_dx_tma_group(csdr_context* ctx, const csdr_segment* const* segs, uin
         p.xch_sums = sums;
     }
 
+    if (shares && shares->ctas) {
+        if (M > 16u || shares->ctas > kNextNormCtas)
+            throw Error(CSDR_ERR_INVALID_ARG, "shares of sums of squares come from a gather over a single token tile");
+        p.norm_partial = shares->partial;
+        p.norm_ctas = shares->ctas;
+        p.norm_sumsq = shares->sumsq;
+    }
     LaunchScope ls(ctx, KC_GEMM);
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_dx_tma_kernel, maps, map_xhi, map_xlo, p));
     ls.done("hsdr_dx_tma_kernel");
