@@ -157,6 +157,11 @@ DECODERS = {
     # config 4: Llama-7B shape, batch 16 at context 1024
     "llama7b": dict(cfg=dict(n_layers=32, hidden=4096, q_heads=32, kv_heads=32, head_dim=128, inter=11008,
                              vocab=32000), kv_atoms=None, batch=16, context=1024, steps=32, eps=1e-5, prefill=True),
+    # two blocks of config 4 (every launch of a block at its full size, a few hundred MB on the
+    # device): the case for kernel profilers, not a reported figure
+    "llama7b_2blocks": dict(cfg=dict(n_layers=2, hidden=4096, q_heads=32, kv_heads=32, head_dim=128, inter=11008,
+                                     vocab=32000), kv_atoms=None, batch=16, context=1024, steps=12, eps=1e-5,
+                            prefill=False),
 }
 
 
