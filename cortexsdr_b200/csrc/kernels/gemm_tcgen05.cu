@@ -559,7 +559,17 @@ struct GatherGroupParams {
     __nv_bfloat16* act_hi;    // SwiGLU pair: planes of silu(member 0) * member 1, laid out like y
     __nv_bfloat16* act_lo;
     NextNorm next;            // NORM instances only
+    unsigned long long* trace;   // optional: global-timer stamps in slots 8..11 of a CTA's 16
+    uint32_t trace_ctas;
 };
+
+__device__ __forceinline__ void gather_stamp(const GatherGroupParams& g, int slot) {
+    if (g.trace && blockIdx.x < g.trace_ctas) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g.trace[blockIdx.x * 16u + slot] = t;
+    }
+}
 
 
 
@@ -648,6 +658,7 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     }
     const GatherMember& m0 = g.m[mi0];
     const uint32_t tid = threadIdx.x;
+    if (tid == 0) gather_stamp(g, 8);
     const uint32_t row0 = (blockIdx.x - m0.cta_begin) * m0.rows_per_cta;
     const bool active = row0 < m0.R;
     const uint32_t rows_here = active ? min(m0.rows_per_cta, m0.R - row0) : 0u;
@@ -674,6 +685,7 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
         for (uint32_t i = tid; i < m.S; i += kGroupThreads) sc[i] = m.scales[i];
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) gather_stamp(g, 9);
     __shared__ float inv_rms_s[16];
     if (active) {
 #pragma unroll
@@ -693,12 +705,20 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+    if (tid == 0) gather_stamp(g, 10);
     if (!NORM && !active) return;
-    const uint32_t b = tid % MT;
-    constexpr uint32_t RP = kGroupThreads / MT;
-    float ss = 0.0f;    // NORM: this thread's share of its token's sum of squares
-    for (uint32_t rl = tid / MT; rl < rows_here; rl += RP) {
-        float res[NM];
+    // A thread gathers one row for TV tokens (four from a 4-token tile up: one 128-bit read of
+    // Dx serves four sums, and a row's codes, read eight to a 128-bit word where the row starts
+    // on a 16-byte boundary, are shared by fewer threads); TQ threads side by side cover a row.
+    constexpr uint32_t TV = MT >= 4 ? 4u : static_cast<uint32_t>(MT);
+    constexpr uint32_t TQ = MT / TV;
+    constexpr uint32_t RP = kGroupThreads / TQ;
+    const uint32_t b0 = (tid % TQ) * TV;
+    float ss[TV];       // NORM: this thread's shares of its tokens' sums of squares
+#pragma unroll
+    for (uint32_t j = 0; j < TV; ++j) ss[j] = 0.0f;
+    for (uint32_t rl = tid / TQ; rl < rows_here; rl += RP) {
+        float res[NM][TV];
 #pragma unroll
         for (uint32_t q = 0; q < NM; ++q) {
             const GatherMember& m = g.m[mi0 + q];
@@ -707,37 +727,72 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
             const float* sc = reinterpret_cast<const float*>(base + static_cast<size_t>(g.code_cap16) * 16u);
             const float* dxs = sc + 64;
             const uint16_t* rc = cs + rl * (m.S * m.k);
-            float acc = 0.0f;
-            for (uint32_t l = 0; l < m.S; ++l) {
-                const float gamma = sc[l];
+            float acc[TV];
+#pragma unroll
+            for (uint32_t j = 0; j < TV; ++j) acc[j] = 0.0f;
+            auto add = [&](uint32_t code, float gamma) {
+                const float scale = (code & 0x8000u) ? -gamma : gamma;
+                const float* dp = dxs + (code & 0x7FFFu) * MT + b0;
+                if constexpr (TV == 4u) {
+                    const float4 d = *reinterpret_cast<const float4*>(dp);
+                    acc[0] = __fadd_rn(acc[0], __fmul_rn(scale, d.x));
+                    acc[1] = __fadd_rn(acc[1], __fmul_rn(scale, d.y));
+                    acc[2] = __fadd_rn(acc[2], __fmul_rn(scale, d.z));
+                    acc[3] = __fadd_rn(acc[3], __fmul_rn(scale, d.w));
+                } else {
+#pragma unroll
+                    for (uint32_t j = 0; j < TV; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(scale, dp[j]));
+                }
+            };
+            if (((m.k & 7u) | skip[q]) == 0u) {      // rows of whole 16-byte words, the first one aligned
+                for (uint32_t l = 0; l < m.S; ++l) {
+                    const float gamma = sc[l];
+                    for (uint32_t k8 = 0; k8 < m.k; k8 += 8u) {
+                        const uint4 c = *reinterpret_cast<const uint4*>(rc + l * m.k + k8);
+                        add(c.x & 0xFFFFu, gamma);
+                        add(c.x >> 16, gamma);
+                        add(c.y & 0xFFFFu, gamma);
+                        add(c.y >> 16, gamma);
+                        add(c.z & 0xFFFFu, gamma);
+                        add(c.z >> 16, gamma);
+                        add(c.w & 0xFFFFu, gamma);
+                        add(c.w >> 16, gamma);
+                    }
+                }
+            } else {
+                for (uint32_t l = 0; l < m.S; ++l) {
+                    const float gamma = sc[l];
 #pragma unroll 4
-                for (uint32_t kk = 0; kk < m.k; ++kk) {
-                    const uint32_t code = rc[l * m.k + kk];
-                    const float scale = (code & 0x8000u) ? -gamma : gamma;
-                    acc = __fadd_rn(acc, __fmul_rn(scale, dxs[(code & 0x7FFFu) * MT + b]));
+                    for (uint32_t kk = 0; kk < m.k; ++kk) add(rc[l * m.k + kk], gamma);
                 }
             }
-            if (g.ts.sumsq) acc *= inv_rms_s[b];
-            if (m.bias) acc += m.bias[row0 + rl];
-            res[q] = acc;
+#pragma unroll
+            for (uint32_t j = 0; j < TV; ++j) {
+                if (g.ts.sumsq) acc[j] *= inv_rms_s[b0 + j];
+                if (m.bias) acc[j] += m.bias[row0 + rl];
+                res[q][j] = acc[j];
+            }
         }
-        if (b < g.M) {
-            const uint32_t r = row0 + rl;
+        const uint32_t r = row0 + rl;
+#pragma unroll
+        for (uint32_t j = 0; j < TV; ++j) {
+            const uint32_t b = b0 + j;
+            if (b >= g.M) continue;
             const size_t o = g.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * g.m_total + b
                                                                       : static_cast<size_t>(b) * m0.R + r;
             if (PAIR) {
-                const float x = res[0];
+                const float x = res[0][j];
                 const float sig = 1.0f / (1.0f + expf(-x));
-                const float v = (x * sig) * res[NM - 1];
+                const float v = (x * sig) * res[NM - 1][j];
                 const __nv_bfloat16 h = __float2bfloat16_rn(v);
                 g.act_hi[o] = h;
                 g.act_lo[o] = __float2bfloat16_rn(v - __bfloat162float(h));
             } else {
-                float acc = res[0];
+                float acc = res[0][j];
                 if (m0.residual) acc += m0.residual[o];
                 m0.y[o] = acc;
                 if (NORM) {
-                    ss = fmaf(acc, acc, ss);
+                    ss[j] = fmaf(acc, acc, ss[j]);
                     const float p = acc * g.next.w[r];
                     const __nv_bfloat16 h = __float2bfloat16_rn(p);
                     g.next.hi[o] = h;
@@ -746,9 +801,11 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
             }
         }
     }
+    if (tid == 0) gather_stamp(g, 11);
     if (NORM) {
-        __shared__ float red_s[kGroupThreads];
-        red_s[tid] = ss;                       // index = row lane * MT + token
+        __shared__ float red_s[RP * MT];       // index = row lane * MT + token
+#pragma unroll
+        for (uint32_t j = 0; j < TV; ++j) red_s[(tid / TQ) * MT + b0 + j] = ss[j];
         __syncthreads();
         if (tid < 16u) {
             float t = 0.0f;
@@ -763,7 +820,7 @@ template <int MT>
 uint32_t launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t total_rows, uint32_t max_k, uint32_t max_slots) {
     const bool pair = g.act_hi != nullptr, norm = g.next.w != nullptr;
     // about three CTAs per SM over the whole group (a pair walks the rows of one member)
-    uint32_t want = 3u * static_cast<uint32_t>(ctx->sm_count);   // measured best of 1..4 on the 7B-shaped decode
+    uint32_t want = 3u * static_cast<uint32_t>(ctx->sm_count);   // 1, 2 and 3 per SM measured within 1 % of each other on the 7B-shaped decode
     if (norm) want = std::min(want, kNextNormCtas);
     const uint32_t rows_all = pair ? g.m[0].R : total_rows;
     const uint32_t rows_per_cta = std::max(kGroupThreads / MT, (rows_all + want - 1u) / want);
@@ -865,6 +922,8 @@ uint32_t gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, u
                        __nv_bfloat16* act_lo = nullptr, const NextNorm* next = nullptr) {
     GatherGroupParams g{};
     if (next) g.next = *next;
+    g.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
+    g.trace_ctas = static_cast<uint32_t>(ctx->sm_count) * 2u;
     if (act_hi) {
         if (n != 2 || segs[0]->g.rows != segs[1]->g.rows || !act_lo)
             throw Error(CSDR_ERR_INVALID_ARG, "a SwiGLU pair is two segments with the same number of rows");

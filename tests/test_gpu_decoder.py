@@ -405,6 +405,27 @@ def test_qwen_width_prefill_and_greedy_steps(ctx, oracle, model_qwen_width, kv_d
     dec.close()
 
 
+def test_llama_width_batch11_step(ctx, oracle, model_llama_width):
+    """Eleven sequences step together: a 16-token tile with five empty columns through the
+    tensor-core projection, the gathers (the next norm's first half riding on the output and
+    down gathers, its sums added up by the projection behind them) and attention."""
+    path, weights = model_llama_width
+    rng = np.random.default_rng(18)
+    lens = [4, 1, 9, 6, 2, 11, 3, 7, 5, 8, 10]
+    prompts = [rng.integers(0, LLAMA_W["vocab"], n) for n in lens]
+    dec = make_decoder(path, ctx, CFG=LLAMA_W, max_seq=32, max_batch=16)
+    for s_, p_ in enumerate(prompts):
+        dec.forward(p_, seq=s_, want_logits=False)
+    new = rng.integers(0, LLAMA_W["vocab"], len(lens))
+    nxt, lg = dec.step(new, want_logits=True)
+    assert lg.shape[0] == len(lens) and np.isfinite(lg).all()
+    for s_ in (0, 1, 5, 10):
+        _, want = oracle_forward_memo(oracle, weights, np.append(prompts[s_], new[s_]), CFG=LLAMA_W)
+        assert np.abs(lg[s_] - want).max() < 2e-2, s_
+        assert same_pick(lg[s_], want, 2e-2) and int(nxt[s_]) == int(lg[s_].argmax()), s_
+    dec.close()
+
+
 @pytest.mark.parametrize("kv_dtype", ["f32", "f16", "bf16"])
 def test_llama_width_batch16_step(ctx, oracle, model_llama_width, kv_dtype):
     """Hidden 4096, 32 heads of 128, SwiGLU 11 008, vocabulary 32 000; one block. Sixteen
