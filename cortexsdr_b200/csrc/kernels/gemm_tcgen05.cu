@@ -719,6 +719,19 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     for (uint32_t j = 0; j < TV; ++j) ss[j] = 0.0f;
     for (uint32_t rl = tid / TQ; rl < rows_here; rl += RP) {
         float res[NM][TV];
+        // what the epilogue adds and multiplies comes from global memory and does not depend on
+        // the sums: requested here, it arrives while the codes are walked
+        float resid[TV], wnext = 0.0f;
+        if (!PAIR) {
+#pragma unroll
+            for (uint32_t j = 0; j < TV; ++j) {
+                const uint32_t b = b0 + j, r = row0 + rl;
+                const size_t o = g.y_layout == CSDR_LAYOUT_FEATURE_MAJOR ? static_cast<size_t>(r) * g.m_total + b
+                                                                          : static_cast<size_t>(b) * m0.R + r;
+                resid[j] = (m0.residual && b < g.M) ? m0.residual[o] : 0.0f;
+            }
+            if (NORM) wnext = g.next.w[row0 + rl];
+        }
 #pragma unroll
         for (uint32_t q = 0; q < NM; ++q) {
             const GatherMember& m = g.m[mi0 + q];
@@ -789,11 +802,11 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
                 g.act_lo[o] = __float2bfloat16_rn(v - __bfloat162float(h));
             } else {
                 float acc = res[0][j];
-                if (m0.residual) acc += m0.residual[o];
+                if (m0.residual) acc += resid[j];
                 m0.y[o] = acc;
                 if (NORM) {
                     ss[j] = fmaf(acc, acc, ss[j]);
-                    const float p = acc * g.next.w[r];
+                    const float p = acc * wnext;
                     const __nv_bfloat16 h = __float2bfloat16_rn(p);
                     g.next.hi[o] = h;
                     g.next.lo[o] = __float2bfloat16_rn(p - __bfloat162float(h));
