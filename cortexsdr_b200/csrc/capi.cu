@@ -227,6 +227,7 @@ int csdr_context_create(int device, void* stream, csdr_context** out) {
         if (const char* e = std::getenv("CSDR_TILE_TC")) ctx->tile_tc = e[0] != '0';
         if (const char* e = std::getenv("CSDR_HOST_ZERO_COPY")) ctx->host_zero_copy = e[0] != '0';
         if (const char* e = std::getenv("CSDR_DECODER_FOLD")) ctx->decoder_fold = e[0] != '0';
+        if (const char* e = std::getenv("CSDR_ATTENTION_ROPE_FOLD")) ctx->attention_rope_fold = e[0] != '0';
         if (const char* e = std::getenv("CSDR_QUEUE_POLL_SLEEP")) ctx->queue_poll_sleep_ns = static_cast<uint32_t>(std::max(0, std::atoi(e)));
         if (const char* e = std::getenv("CSDR_QUEUE_MIN_GROUP")) ctx->queue_min_group = static_cast<uint32_t>(std::max(1, std::atoi(e)));
         if (const char* e = std::getenv("CSDR_GEMV_QUEUE_SINGLE")) ctx->gemv_queue_single = e[0] != '0';

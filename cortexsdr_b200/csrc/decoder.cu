@@ -117,6 +117,9 @@ struct csdr_decoder {
     // gather left shares for the projection launch behind it to add up (0: none pending)
     DevPtr norm_scratch;
     uint32_t norm_pending = 0;
+    // every token of the pass being run belongs to a different sequence (a decode step, or a
+    // one-token forward): set by the entry points before the block loop
+    bool distinct_seqs = false;
     // peer-memory exchange of partial projections between tensor-parallel ranks (steps of at
     // most 16 tokens); until the host program has passed the peers' handles in, NCCL sums them
     DevPtr xch_region;
@@ -306,6 +309,25 @@ void sum_over_ranks(csdr_decoder* d, float* from, size_t floats) {
 // next_w * y into the hidden planes, sums of y^2 into the sums block - rides on the gather when
 // the step is a single token tile (the gather leaves shares of the sums, the next call's
 // projection launch adds them up), and is a launch of its own behind the gather otherwise.
+// Rotary embedding of q and k, the cache write and attention of block li over d->q, d->k, d->v:
+// one launch when every token of the step belongs to a different sequence (a decode step), else
+// the rotary kernel first (tokens of one sequence attend to each other's cache rows).
+void attend(csdr_decoder* d, uint32_t li, uint32_t T, float* out, __nv_bfloat16* hi = nullptr, __nv_bfloat16* lo = nullptr) {
+    const csdr_decoder_config& c = d->cfg;
+    csdr_context* ctx = d->ctx;
+    void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+    void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
+    if (d->distinct_seqs && ctx->attention_rope_fold && attention_step_supported(c.head_dim)) {
+        op_attention_step(ctx, F(d->q), F(d->k), F(d->v), c.rope_theta, kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T,
+                          d->QH_l, d->KVH_l, c.head_dim, c.max_seq, out, hi, lo);
+        return;
+    }
+    op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l,
+                  c.head_dim, c.max_seq, c.rope_theta);
+    op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, c.head_dim, c.max_seq, out,
+                 hi, lo);
+}
+
 bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_bfloat16* planes, size_t plane_elems,
           uint32_t T, bool normed, bool partial, const float* sums, std::initializer_list<WideOut> outs,
           __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr, const float* next_w = nullptr) {
@@ -387,12 +409,7 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
         Layer& L = d->layers[li];
         wide(d, {&L.q, &L.k, &L.v}, h_hi, h_n, T, true, false, sums,
              {WideOut{F(d->q), nullptr, nullptr}, WideOut{F(d->k), nullptr, nullptr}, WideOut{F(d->v), nullptr, nullptr}});
-        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
-                      c.max_seq, c.rope_theta);
-        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, nullptr,
-                     a_hi, a_hi + a_n);
+        attend(d, li, T, nullptr, a_hi, a_hi + a_n);
         wide(d, {&L.o}, a_hi, a_n, T, false, true, nullptr, {WideOut{F(d->hidden), nullptr, F(d->hidden)}}, nullptr, nullptr,
              F(L.ffn_norm));
         if (!wide(d, {&L.gate, &L.up}, h_hi, h_n, T, true, false, sums,
@@ -431,11 +448,7 @@ void run_blocks_queue(csdr_decoder* d, uint32_t T) {
     }
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         const Layer& L = d->layers[li];
-        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
-                      c.max_seq, c.rope_theta);
-        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        attend(d, li, T, F(d->att));
         QueueItem list[7];
         uint32_t n = 0;
         list[n] = item(L.o, F(d->att), F(d->hidden));            // 0: h += Wo att
@@ -503,11 +516,7 @@ void run_blocks_folded(csdr_decoder* d, uint32_t T) {
         g_attn.norm_w = F(L.attn_norm);
         g_attn.norm_eps = c.rms_eps;
         fused_with_glue(d, {&L.q, &L.k, &L.v}, h, T, {F(d->q), F(d->k), F(d->v)}, g_attn);
-        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
-                      c.max_seq, c.rope_theta);
-        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        attend(d, li, T, F(d->att));
         FusedGlue g_res;
         g_res.residual[0] = h;
         fused_with_glue(d, {&L.o}, F(d->att), T, {h}, g_res);                       // h += Wo att
@@ -550,11 +559,7 @@ void run_blocks(csdr_decoder* d, uint32_t T) {
     for (uint32_t li = 0; li < c.n_layers; ++li) {
         Layer& L = d->layers[li];
         linear_group(d, {&L.q, &L.k, &L.v}, F(d->normed), T, {F(d->q), F(d->k), F(d->v)});
-        void* kc = static_cast<char*>(d->kcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        void* vc = static_cast<char*>(d->vcache->ptr) + li * d->cache_layer_stride * d->kv_es;
-        op_rope_cache(ctx, F(d->q), F(d->k), F(d->v), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD,
-                      c.max_seq, c.rope_theta);
-        op_attention(ctx, F(d->q), kc, vc, d->kv_dtype, I32(d->seq_of), I32(d->pos_of), T, d->QH_l, d->KVH_l, HD, c.max_seq, F(d->att));
+        attend(d, li, T, F(d->att));
         linear(d, L.o, F(d->att), T, F(d->proj));
         op_add_rmsnorm(ctx, F(d->hidden), F(d->proj), F(L.ffn_norm), T, H, c.rms_eps, F(d->normed));
         linear_group(d, {&L.gate, &L.up}, F(d->normed), T, {F(d->gate), F(d->up)});
@@ -954,6 +959,7 @@ int csdr_decoder_forward(csdr_decoder* d, uint32_t seq, const int32_t* tokens, s
         CSDR_CUDA(cudaMemcpyAsync(d->seq_of->ptr, so.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
         CSDR_CUDA(cudaMemcpyAsync(d->pos_of->ptr, po.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream));
         embed(d, T);
+        d->distinct_seqs = T == 1u;
         run_blocks(d, T);
         if (hidden_out) {
             materialise_normed(d, T);
@@ -986,6 +992,7 @@ int csdr_decoder_step_device_async(csdr_decoder* d, const int32_t* tokens_dev, s
             CSDR_CUDA(cudaMemcpyAsync(d->tokens_dev->ptr, tokens_dev, B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
         op_step_positions(ctx, I32(d->pos_dev), B, I32(d->seq_of), I32(d->pos_of));
         embed(d, B);
+        d->distinct_seqs = true;
         run_blocks(d, B);
         run_logits(d, B, 0, B);
         if (d->policy)

@@ -124,6 +124,7 @@ struct csdr_context {
     uint32_t queue_min_group = 4;    // CSDR_QUEUE_MIN_GROUP: smallest same-x group the list kernel takes over grouped fused launches
     bool host_zero_copy = true;      // CSDR_HOST_ZERO_COPY=0: results of a host list go back by a copy even when the caller's memory is device-addressable
     bool tile_tc = true;             // CSDR_TILE_TC=0: 2-D tile products of a few tokens stay on the CUDA-core projection
+    bool attention_rope_fold = true; // CSDR_ATTENTION_ROPE_FOLD=0: rotary embedding and cache write of a decode step as a kernel of their own
     bool decoder_fold = true;        // CSDR_DECODER_FOLD=0: norms, residuals and SwiGLU of a short decoder step as kernels of their own
     bool decoder_queue = false;      // CSDR_DECODER_QUEUE=1: decoder steps of up to four tokens run a block as three launches
     bool gemv_queue_single = false;  // CSDR_GEMV_QUEUE_SINGLE=1 sends single products of at most 4 tokens there too

@@ -323,13 +323,48 @@ struct CacheRow {
         }
     }
     __device__ __forceinline__ float get(int e) const { return widen16<KV>(w[e >> 1], e & 1); }
+    // the row as the cache would hold it: every value rounded to the cache type
+    __device__ __forceinline__ void set(const float (&f)[VPL]) {
+#pragma unroll
+        for (int i = 0; i < (VPL + 1) / 2; ++i) {
+            const KV lo = to_kv<KV>(f[2 * i]);
+            const KV hi = to_kv<KV>(2 * i + 1 < VPL ? f[2 * i + 1] : 0.0f);
+            w[i] = static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(&lo)) |
+                   (static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(&hi)) << 16);
+        }
+    }
 };
 template <int VPL>
 struct CacheRow<float, VPL> {
     float v[VPL];
     __device__ __forceinline__ void load(const float* p) { load_row<VPL>(p, v); }
     __device__ __forceinline__ float get(int e) const { return v[e]; }
+    __device__ __forceinline__ void set(const float (&f)[VPL]) {
+#pragma unroll
+        for (int e = 0; e < VPL; ++e) v[e] = f[e];
+    }
 };
+
+// Rotary embedding and cache write of a decode step folded into the attention kernel (every
+// token of the step belongs to a different sequence, so no token attends to another token of
+// the launch): the kernel rotates its query row in registers, takes the newest key and value of
+// its sequence from the projection outputs (rotated and rounded as the cache would hold them)
+// instead of the cache, and one CTA per (token, kv head) files them in the cache for later steps.
+struct StepRope {
+    const float* k = nullptr;   // (T, KVH, HD) fresh keys, not yet rotated; null: q and the cache are ready
+    const float* v = nullptr;   // (T, KVH, HD) fresh values
+    float theta = 0.0f;
+};
+
+// cos and sin of the rotary angle of pair (i, i + 1) at a position (apply_rope_inplace,
+// api/cortex_sdk.cpp:1363-1423: freq = theta^(-i / head_dim)).
+__device__ __forceinline__ void rope_angle(uint32_t i, uint32_t HD, int32_t pos, float theta, float& c, float& s) {
+    const float exponent = static_cast<float>(i) / static_cast<float>(HD);
+    const float freq = powf(theta, -exponent);
+    const float angle = static_cast<float>(pos) * freq;
+    c = cosf(angle);
+    s = sinf(angle);
+}
 
 // Sums over the warp of N values per lane (N = 4 or 8), all N sums back in every lane. The first
 // rounds halve the payload instead of carrying every value through every round: lanes whose bit
@@ -375,7 +410,7 @@ __device__ __forceinline__ float exp2_fast(float x) {
 // against a long context) take more warps each so that enough K/V rows are in flight per SM.
 // The cache element type of an attention kernel, from its pointer type (host-side launch helper).
 template <typename KV, typename... Rest>
-const KV* kernel_kv(void (*)(const float*, const KV*, Rest...)) {
+KV* kernel_kv(void (*)(const float*, KV*, Rest...)) {
     return nullptr;
 }
 
@@ -386,11 +421,11 @@ const KV* kernel_kv(void (*)(const float*, const KV*, Rest...)) {
 // after the other.
 template <typename KV, int VPL, int kAttnWarps, bool kSplit>
 __global__ void __launch_bounds__(kAttnWarps * 32)
-attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
-                 const KV* __restrict__ vc, const int32_t* __restrict__ seq_of,
+attention_kernel(const float* __restrict__ q, KV* __restrict__ kc,
+                 KV* __restrict__ vc, const int32_t* __restrict__ seq_of,
                  const int32_t* __restrict__ pos_of, uint32_t QH, uint32_t KVH, uint32_t max_seq,
                  float scale, float* __restrict__ out, __nv_bfloat16* __restrict__ hi,
-                 __nv_bfloat16* __restrict__ lo) {
+                 __nv_bfloat16* __restrict__ lo, const StepRope rope) {
     pdl_enter();
     constexpr uint32_t HD = VPL * 32u;
     constexpr int kKeys = kAttnKeys * static_cast<int>(sizeof(float) / sizeof(KV));
@@ -399,11 +434,49 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
     const uint32_t t = blockIdx.x, h = blockIdx.y;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t kvh = h / (QH / KVH);
-    const int32_t n_keys = min(pos_of[t] + 1, static_cast<int32_t>(max_seq));
+    const int32_t n_keys = min(pos_of[t] + 1, static_cast<int32_t>(max_seq));   // the newest key is the last one
     const size_t row = static_cast<size_t>(KVH) * HD;
     const size_t base = static_cast<size_t>(seq_of[t]) * max_seq * row + kvh * HD + lane * VPL;
     float qv[VPL], acc[VPL];
     load_row<VPL>(q + (static_cast<size_t>(t) * QH + h) * HD + lane * VPL, qv);
+    // step with the rotary embedding folded in (VPL >= 2: a lane holds whole pairs): rotate the
+    // query, build the newest key and value rows, file them in the cache once per (token, kv head)
+    const int32_t pos = pos_of[t];
+    const bool fresh = VPL >= 2 && rope.k != nullptr && pos >= 0 && pos < static_cast<int32_t>(max_seq);
+    CacheRow<KV, VPL> knew, vnew;
+    if (VPL >= 2 && rope.k != nullptr) {
+        float kf[VPL], vf[VPL];
+        if (fresh) {
+            load_row<VPL>(rope.k + (static_cast<size_t>(t) * KVH + kvh) * HD + lane * VPL, kf);
+            load_row<VPL>(rope.v + (static_cast<size_t>(t) * KVH + kvh) * HD + lane * VPL, vf);
+        }
+#pragma unroll
+        for (int e = 0; e + 1 < VPL; e += 2) {
+            float c, sn;
+            rope_angle(lane * VPL + e, HD, pos, rope.theta, c, sn);
+            const float q0 = qv[e], q1 = qv[e + 1];
+            qv[e] = q0 * c - q1 * sn;
+            qv[e + 1] = q0 * sn + q1 * c;
+            if (fresh) {
+                const float k0 = kf[e], k1 = kf[e + 1];
+                kf[e] = k0 * c - k1 * sn;
+                kf[e + 1] = k0 * sn + k1 * c;
+            }
+        }
+        if (fresh) {
+            knew.set(kf);
+            vnew.set(vf);
+            if (warp == 0 && h == kvh * (QH / KVH) && (!kSplit || blockIdx.z == 0)) {
+                const size_t slot = static_cast<size_t>(seq_of[t]) * max_seq * (static_cast<size_t>(KVH) * HD) +
+                                    static_cast<size_t>(pos) * (static_cast<size_t>(KVH) * HD) + kvh * HD + lane * VPL;
+#pragma unroll
+                for (int e = 0; e < VPL; ++e) {
+                    kc[slot + e] = to_kv<KV>(kf[e]);
+                    vc[slot + e] = to_kv<KV>(vf[e]);
+                }
+            }
+        }
+    }
     // scores are kept as log2 of the softmax weights (the query carries scale * log2 e), so that a
     // weight is one ex2 instruction; maxima and running sums are in the same units throughout
     const float qscale = scale * 1.4426950408889634f;
@@ -432,6 +505,14 @@ attention_kernel(const float* __restrict__ q, const KV* __restrict__ kc,
                 kv[u].load(kc + base + static_cast<size_t>(j) * row);
                 vv[u].load(vc + base + static_cast<size_t>(j) * row);
             }
+        }
+        if (fresh && j0 + kKeys > pos) {      // this step holds the newest key: not from the cache
+#pragma unroll
+            for (int u = 0; u < kKeys; ++u)
+                if (j0 + u == pos) {
+                    kv[u] = knew;
+                    vv[u] = vnew;
+                }
         }
         float s[kKeys];
 #pragma unroll
@@ -720,11 +801,23 @@ void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, 
     ls.done("rope_cache_kernel");
 }
 
+bool attention_step_supported(uint32_t HD) { return HD == 64u || HD == 128u || HD == 256u; }
+
 void op_attention(csdr_context* ctx, const float* q, const void* kc, const void* vc, int kv_dtype,
                   const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH,
                   uint32_t HD, uint32_t max_seq, float* out, __nv_bfloat16* hi, __nv_bfloat16* lo) {
+    op_attention_step(ctx, q, nullptr, nullptr, 0.0f, const_cast<void*>(kc), const_cast<void*>(vc), kv_dtype, seq_of, pos_of, T,
+                      QH, KVH, HD, max_seq, out, hi, lo);
+}
+
+void op_attention_step(csdr_context* ctx, const float* q, const float* k_new, const float* v_new, float theta, void* kc,
+                       void* vc, int kv_dtype, const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH,
+                       uint32_t KVH, uint32_t HD, uint32_t max_seq, float* out, __nv_bfloat16* hi, __nv_bfloat16* lo) {
     if (HD % 32u || HD > 256u || HD == 96u || HD == 160u || HD == 192u || HD == 224u)
         throw Error(CSDR_ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 128 or 256");
+    if (k_new && !attention_step_supported(HD))
+        throw Error(CSDR_ERR_UNSUPPORTED, "attention with the rotary embedding folded in: head_dim must be 64, 128 or 256");
+    const StepRope rope{k_new, v_new, theta};
     const float scale = 1.0f / sqrtf(static_cast<float>(HD));
     LaunchScope ls(ctx, KC_ATTENTION);
     const uint32_t pairs = T * QH;
@@ -751,8 +844,8 @@ void op_attention(csdr_context* ctx, const float* q, const void* kc, const void*
         }
         cfg.attrs = attr;
         using KVp = std::remove_pointer_t<decltype(kernel_kv(kern))>;
-        CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, q, static_cast<const KVp*>(kc), static_cast<const KVp*>(vc), seq_of, pos_of, QH, KVH,
-                                     max_seq, scale, out, hi, lo));
+        CSDR_CUDA(cudaLaunchKernelEx(&cfg, kern, q, static_cast<KVp*>(kc), static_cast<KVp*>(vc), seq_of, pos_of, QH, KVH,
+                                     max_seq, scale, out, hi, lo, rope));
     };
 #define CSDR_ATTN(V, W)                                                                     \
     do {                                                                                    \

@@ -32,6 +32,16 @@ void op_rope_cache(csdr_context* ctx, float* q, const float* k, const float* v, 
 void op_attention(csdr_context* ctx, const float* q, const void* kc, const void* vc, int kv_dtype, const int32_t* seq_of,
                   const int32_t* pos_of, uint32_t T, uint32_t QH, uint32_t KVH, uint32_t HD, uint32_t max_seq,
                   float* out, __nv_bfloat16* hi = nullptr, __nv_bfloat16* lo = nullptr);
+// A decode step (every token of a different sequence): rotary embedding of q and of the new
+// keys, the cache write of the new keys and values, and attention in ONE launch. q, k_new, v_new
+// are the projection outputs as they stand (not rotated); the kernel takes a sequence's newest
+// key and value from them, rounded as the cache holds them, and files them in the cache.
+// head_dim 64, 128 or 256 (attention_step_supported).
+bool attention_step_supported(uint32_t HD);
+void op_attention_step(csdr_context* ctx, const float* q, const float* k_new, const float* v_new, float theta, void* kc,
+                       void* vc, int kv_dtype, const int32_t* seq_of, const int32_t* pos_of, uint32_t T, uint32_t QH,
+                       uint32_t KVH, uint32_t HD, uint32_t max_seq, float* out, __nv_bfloat16* hi = nullptr,
+                       __nv_bfloat16* lo = nullptr);
 void op_silu_mul(csdr_context* ctx, const float* gate, const float* up, size_t n, float* out);
 void op_silu_mul_planes(csdr_context* ctx, const float* gate, const float* up, size_t n, __nv_bfloat16* hi,
                         __nv_bfloat16* lo);

@@ -401,6 +401,14 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
             constexpr uint32_t RP = kThreads / MTG;
             for (uint32_t rl = tid / MTG; rl < rows_here; rl += RP) {
                 const uint16_t* rc = cs + rl * slots;
+                // what the epilogue adds comes from global memory and does not depend on the sum:
+                // requested here, it arrives while the codes are walked
+                const uint32_t tok = tg * MTG + b;
+                const uint32_t r = row0 + rl;
+                const bool live = tok < sg.y.M;
+                const size_t yi = live ? y_index(sg.y, r, tok) : 0;
+                const float bias_v = live && sg.y.bias ? sg.y.bias[r] : 0.0f;
+                const float resid_v = live && sg.y.residual ? sg.y.residual[yi] : 0.0f;
                 float accr = 0.0f;
                 for (uint32_t l = 0; l < sg.S; ++l) {
                     const float gamma = sc[l];
@@ -419,18 +427,15 @@ hsdr_gemv_fused_kernel(const __grid_constant__ FusedParams p, const __grid_const
                             if (k0 + q < sg.k) accr = __fadd_rn(accr, t[q]);
                     }
                 }
-                const uint32_t tok = tg * MTG + b;
-                if (tok < sg.y.M) {
-                    const uint32_t r = row0 + rl;
+                if (live) {
                     if (p.norm_w) accr *= inv_s[tok];
-                    if (sg.y.bias) accr += sg.y.bias[r];
-                    const size_t yi = y_index(sg.y, r, tok);
+                    if (sg.y.bias) accr += bias_v;
                     if (p.swiglu && si == 1u) {
                         // silu_mul (api/cortex_sdk.cpp:1245-1256); this thread wrote the gate row itself
                         const float gv = p.seg[0].y.y[yi];
                         accr = (gv * (1.0f / (1.0f + expf(-gv)))) * accr;
                     }
-                    if (sg.y.residual) accr += sg.y.residual[yi];
+                    if (sg.y.residual) accr += resid_v;
                     sg.y.y[yi] = accr;
                 }
             }
