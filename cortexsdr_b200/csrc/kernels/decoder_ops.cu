@@ -192,6 +192,13 @@ __device__ __forceinline__ __nv_bfloat16 to_kv<__nv_bfloat16>(float v) { return 
 template <>
 __device__ __forceinline__ __half to_kv<__half>(float v) { return __float2half_rn(v); }
 
+// One rotary pair. Products and sums are rounded one by one (no fused multiply-add), so that
+// every kernel that rotates a row gets the same bits.
+__device__ __forceinline__ void rope_rotate(float x0, float x1, float c, float s, float& y0, float& y1) {
+    y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+}
+
 template <typename KV>
 __global__ void __launch_bounds__(256)
 rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
@@ -216,15 +223,14 @@ rope_cache_kernel(float* __restrict__ q, const float* __restrict__ k, const floa
     auto rotate = [&](uint32_t head, uint32_t i, float c, float s) {
         if (head < QH) {
             float* b = qt + head * HD + i;
-            const float x0 = b[0], x1 = b[1];
-            b[0] = x0 * c - x1 * s;
-            b[1] = x0 * s + x1 * c;
+            rope_rotate(b[0], b[1], c, s, b[0], b[1]);
         } else if (in_cache) {
             const uint32_t kh = head - QH;
             const float* b = kt + kh * HD + i;
-            const float x0 = b[0], x1 = b[1];
-            kc[slot + kh * HD + i] = to_kv<KV>(x0 * c - x1 * s);
-            kc[slot + kh * HD + i + 1] = to_kv<KV>(x0 * s + x1 * c);
+            float y0, y1;
+            rope_rotate(b[0], b[1], c, s, y0, y1);
+            kc[slot + kh * HD + i] = to_kv<KV>(y0);
+            kc[slot + kh * HD + i + 1] = to_kv<KV>(y1);
         }
     };
     auto angle_of = [&](uint32_t i, float& c, float& s) {
@@ -454,14 +460,8 @@ attention_kernel(const float* __restrict__ q, KV* __restrict__ kc,
         for (int e = 0; e + 1 < VPL; e += 2) {
             float c, sn;
             rope_angle(lane * VPL + e, HD, pos, rope.theta, c, sn);
-            const float q0 = qv[e], q1 = qv[e + 1];
-            qv[e] = q0 * c - q1 * sn;
-            qv[e + 1] = q0 * sn + q1 * c;
-            if (fresh) {
-                const float k0 = kf[e], k1 = kf[e + 1];
-                kf[e] = k0 * c - k1 * sn;
-                kf[e + 1] = k0 * sn + k1 * c;
-            }
+            rope_rotate(qv[e], qv[e + 1], c, sn, qv[e], qv[e + 1]);
+            if (fresh) rope_rotate(kf[e], kf[e + 1], c, sn, kf[e], kf[e + 1]);
         }
         if (fresh) {
             knew.set(kf);

@@ -426,6 +426,34 @@ def test_llama_width_batch11_step(ctx, oracle, model_llama_width):
     dec.close()
 
 
+@pytest.mark.parametrize("which", ["qwen", "llama"])
+def test_step_rotary_fold_matches_separate_kernel(which, model_qwen_width, model_llama_width, monkeypatch):
+    """A decode step with the rotary embedding and the cache write inside the attention launch
+    gives the logits of the step that runs them as a kernel of their own, now and one step later
+    (the later step reads the cache rows the earlier one filed): same arithmetic, same bits."""
+    path, CFGW = (model_qwen_width[0], QWEN_W) if which == "qwen" else (model_llama_width[0], LLAMA_W)
+    rng = np.random.default_rng(21)
+    n_seq = 1 if which == "qwen" else 9
+    prompts = [rng.integers(0, CFGW["vocab"], 3 + 2 * s_) for s_ in range(n_seq)]
+    new = rng.integers(0, CFGW["vocab"], n_seq)
+    got = {}
+    for fold in ("1", "0"):
+        monkeypatch.setenv("CSDR_ATTENTION_ROPE_FOLD", fold)
+        c = cs.Context(0)
+        dec = make_decoder(path, c, CFG=CFGW, max_seq=32, max_batch=16)
+        for s_, p_ in enumerate(prompts):
+            dec.forward(p_, seq=s_, want_logits=False)
+        nxt, lg = dec.step(new, want_logits=True)
+        nxt2, lg2 = dec.step(nxt, want_logits=True)
+        got[fold] = (np.array(lg), np.array(lg2), np.array(nxt2))
+        dec.close()
+        c.close()
+    assert np.isfinite(got["1"][0]).all()
+    assert np.array_equal(got["1"][0], got["0"][0])
+    assert np.array_equal(got["1"][1], got["0"][1])
+    assert np.array_equal(got["1"][2], got["0"][2])
+
+
 @pytest.mark.parametrize("kv_dtype", ["f32", "f16", "bf16"])
 def test_llama_width_batch16_step(ctx, oracle, model_llama_width, kv_dtype):
     """Hidden 4096, 32 heads of 128, SwiGLU 11 008, vocabulary 32 000; one block. Sixteen
