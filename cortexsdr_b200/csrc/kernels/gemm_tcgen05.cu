@@ -1094,7 +1094,19 @@ void launch_matmul_tcgen05(csdr_context* ctx, const csdr_segment* seg, const Mat
         ls.done("dx_reduce_kernel");
     }
     if (tile_mt) {
-        // one token tile: Dx is exactly the [n_atoms][mt] block the compact gather expects
+        // one token tile: Dx is exactly the [n_atoms][mt] block the compact gathers expect; the
+        // group gather (a row for four tokens per thread) as a group of one where its scale block fits
+        if (g.n_stages <= 64u) {
+            WideDx w{};
+            w.base = dx;
+            w.dx[0] = dx;
+            w.floats = static_cast<size_t>(g.n_atoms) * tile_mt;
+            w.stride = tile_mt;
+            w.tile_mt = tile_mt;
+            const WideOut out{a.y, a.bias, nullptr};
+            gather_tile_group(ctx, &seg, 1, w, M, &out, a.y_layout, TokenScale{});
+            return;
+        }
         launch_gather_tile(ctx, seg, dx, static_cast<int>(tile_mt), a.y, a.y_layout, M, 0u, M, a.bias);
         return;
     }
