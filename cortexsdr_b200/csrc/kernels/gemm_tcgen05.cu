@@ -561,6 +561,8 @@ struct GatherGroupParams {
     NextNorm next;            // NORM instances only
     unsigned long long* trace;   // optional: global-timer stamps in slots 8..11 of a CTA's 16
     uint32_t trace_ctas;
+    int* status;                 // context status word: a wait that ran out is recorded here
+    uint32_t spin;               // mbarrier try_wait rounds before the wait for Dx gives up
 };
 
 __device__ __forceinline__ void gather_stamp(const GatherGroupParams& g, int slot) {
@@ -649,6 +651,11 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     static_assert(!(PAIR && NORM), "the SwiGLU pair has no next norm");
     extern __shared__ __align__(16) unsigned char ggsm[];
     asm volatile("griddepcontrol.launch_dependents;");
+    __shared__ __align__(8) unsigned long long dx_bar;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&dx_bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     constexpr uint32_t NM = PAIR ? 2u : 1u;      // members this CTA works on
     uint32_t mi0 = 0;
     if (!PAIR) {
@@ -687,7 +694,32 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) gather_stamp(g, 9);
     __shared__ float inv_rms_s[16];
-    if (active) {
+    // Dx of the member(s): one bulk copy each, completing on the barrier, where the block is whole
+    // 16-byte units on a 16-byte boundary (always, for dictionaries of the tensor-core path);
+    // 16-byte asynchronous copies by every thread otherwise
+    bool bulk = active;
+#pragma unroll
+    for (uint32_t q = 0; q < NM; ++q) {
+        const GatherMember& m = g.m[mi0 + q];
+        bulk = bulk && ((m.K * MT) & 3u) == 0u && (reinterpret_cast<uintptr_t>(m.dx) & 15u) == 0u;
+    }
+    if (active && bulk) {
+        if (tid == 0) {
+            uint32_t total = 0;
+#pragma unroll
+            for (uint32_t q = 0; q < NM; ++q) total += g.m[mi0 + q].K * MT * 4u;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&dx_bar)), "r"(total) : "memory");
+#pragma unroll
+            for (uint32_t q = 0; q < NM; ++q) {
+                const GatherMember& m = g.m[mi0 + q];
+                float* dxs = reinterpret_cast<float*>(ggsm + q * region + static_cast<size_t>(g.code_cap16) * 16u) + 64;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(dxs)),
+                             "l"(m.dx), "r"(m.K * MT * 4u), "r"(smem_u32(&dx_bar))
+                             : "memory");
+            }
+        }
+    } else if (active) {
 #pragma unroll
         for (uint32_t q = 0; q < NM; ++q) {
             const GatherMember& m = g.m[mi0 + q];
@@ -705,6 +737,15 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+    {
+        // the whole CTA goes on or gives up together (a wait that ran out: the host reads the
+        // status word, nothing is gathered)
+        const bool landed = !(active && bulk) || mbar_wait(smem_u32(&dx_bar), 0u, g.spin);
+        if (!__syncthreads_and(landed)) {
+            if (tid == 0) atomicExch(g.status, 1);
+            return;
+        }
+    }
     if (tid == 0) gather_stamp(g, 10);
     if (!NORM && !active) return;
     // A thread gathers one row for TV tokens (four from a 4-token tile up: one 128-bit read of
@@ -940,6 +981,8 @@ uint32_t gather_tile_group(csdr_context* ctx, const csdr_segment* const* segs, u
     if (next) g.next = *next;
     g.trace = ctx->gemv_trace ? static_cast<unsigned long long*>(ctx->gemv_trace->ptr) : nullptr;
     g.trace_ctas = static_cast<uint32_t>(ctx->sm_count) * 2u;
+    g.status = ctx->status_word;
+    g.spin = ctx->spin_limit_barrier;
     if (act_hi) {
         if (n != 2 || segs[0]->g.rows != segs[1]->g.rows || !act_lo)
             throw Error(CSDR_ERR_INVALID_ARG, "a SwiGLU pair is two segments with the same number of rows");
