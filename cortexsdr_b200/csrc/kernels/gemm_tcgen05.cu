@@ -342,9 +342,14 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
                         const float* __restrict__ scales, const float* __restrict__ dx, uint32_t K,
                         uint32_t M /* tokens in dx rows */, uint32_t rows_per_cta, YView yv,
                         const float* residual /* laid out like y, added on the way out; may be y itself */,
-                        TokenScale ts) {
+                        TokenScale ts, int* status, uint32_t spin) {
     extern __shared__ __align__(16) float wsm[];
     asm volatile("griddepcontrol.launch_dependents;");
+    __shared__ __align__(8) unsigned long long dx_bar;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&dx_bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     float* dxs = wsm;                                           // [K][64]
     float* gs = wsm + static_cast<size_t>(K) * kWideTokens;     // stage scales, [<= 64]
     uint32_t* csm = reinterpret_cast<uint32_t*>(gs + kWideMaxSlots);   // [half-warp][kWideCodeWords]
@@ -381,18 +386,32 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // stage the Dx slice (zero beyond the last token): asynchronous 16-byte copies, all of a
     // thread's requests in flight at once
-    if ((M & 3u) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15u) == 0) {
-        for (uint32_t i = tid; i < K * (kWideTokens / 4u); i += kWideThreads) {
-            const uint32_t a = i / (kWideTokens / 4u), q = i - a * (kWideTokens / 4u);
-            const float* src = dx + static_cast<size_t>(a) * M + t0 + q * 4u;
-            const uint32_t valid = q * 4u < tw ? min(16u, (tw - q * 4u) * 4u) : 0u;   // bytes; the rest reads as zero
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                             static_cast<uint32_t>(__cvta_generic_to_shared(dxs + i * 4u))),
-                         "l"(valid ? src : dx), "r"(valid)
+    const bool bulk = (M & 3u) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15u) == 0;
+    if (bulk) {
+        // bulk copies completing on the barrier: the whole slice at once when it is the whole of Dx
+        // (64 tokens in all), else one copy per atom row; tokens past the end are zeroed by hand
+        if (tid == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&dx_bar)), "r"(K * tw * 4u)
                          : "memory");
+        if (M == kWideTokens) {
+            if (tid == 0)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(dxs)),
+                             "l"(dx), "r"(K * kWideTokens * 4u), "r"(smem_u32(&dx_bar))
+                             : "memory");
+        } else {
+            for (uint32_t a = tid; a < K; a += kWideThreads) {
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(dxs + static_cast<size_t>(a) * kWideTokens)),
+                             "l"(dx + static_cast<size_t>(a) * M + t0), "r"(tw * 4u), "r"(smem_u32(&dx_bar))
+                             : "memory");
+            }
+            if (tw < kWideTokens)
+                for (uint32_t i = tid; i < K * (kWideTokens - tw); i += kWideThreads) {
+                    const uint32_t a = i / (kWideTokens - tw), t = tw + i - a * (kWideTokens - tw);
+                    dxs[static_cast<size_t>(a) * kWideTokens + t] = 0.0f;
+                }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
         for (uint32_t i = tid; i < K * kWideTokens; i += kWideThreads) {
             const uint32_t a = i / kWideTokens, t = i - a * kWideTokens;
@@ -400,6 +419,15 @@ hsdr_gather_wide_kernel(const uint16_t* __restrict__ codes, uint32_t R, uint32_t
         }
     }
     __syncthreads();
+    {
+        // the whole CTA goes on or gives up together (a wait that ran out: the host reads the
+        // status word, nothing is gathered)
+        const bool landed = !bulk || mbar_wait(smem_u32(&dx_bar), 0u, spin);
+        if (!__syncthreads_and(landed)) {
+            if (tid == 0) atomicExch(status, 1);
+            return;
+        }
+    }
 
     const float4* dxs4 = reinterpret_cast<const float4*>(dxs) + l16;
     uint32_t* my_csm = csm + hw * kWideCodeWords;
@@ -934,7 +962,7 @@ void launch_gather_wide(csdr_context* ctx, const csdr_segment* seg, const float*
     cfg.numAttrs = 1;
     CSDR_CUDA(cudaLaunchKernelEx(&cfg, hsdr_gather_wide_kernel, seg->codes_ptr(), g.rows, g.n_stages, g.k,
                                  static_cast<const float*>(seg->scales->ptr), dx, g.n_atoms, M, rows_per_cta, yv,
-                                 residual, ts));
+                                 residual, ts, ctx->status_word, ctx->spin_limit_barrier));
     ls.done("hsdr_gather_wide_kernel");
 }
 
