@@ -901,8 +901,8 @@ hsdr_gather_group_kernel(const __grid_constant__ GatherGroupParams g) {
 template <int MT>
 uint32_t launch_gather_group_t(csdr_context* ctx, GatherGroupParams& g, uint32_t total_rows, uint32_t max_k, uint32_t max_slots) {
     const bool pair = g.act_hi != nullptr, norm = g.next.w != nullptr;
-    // about three CTAs per SM over the whole group (a pair walks the rows of one member)
-    // two per SM: the rows of a CTA still fit one pass of its threads at 16 tokens, and an SM takes
+    // CTAs over the whole group (a pair walks the rows of one member), two per SM: the rows of a
+    // CTA still fit one pass of its threads at 16 tokens, and an SM takes
     // in two copies of Dx instead of three (1, 2 and 3 per SM measured within 1.5 % of each other on
     // the 7B-shaped decode, 2 ahead)
     uint32_t want = 2u * static_cast<uint32_t>(ctx->sm_count);
