@@ -299,16 +299,6 @@ void sum_over_ranks(csdr_decoder* d, float* from, size_t floats) {
     nccl_check(nccl().AllReduce(from, from, floats, ncclFloat, ncclSum, d->comm, d->ctx->stream), "ncclAllReduce");
 }
 
-// One group of linears over activation planes: projection launch, rank sum, gather launch.
-// `normed`: the planes hold w*h and the gather applies 1/rms from the sums of squares.
-// `act_hi`: the group is (gate, up) and, when the step is a single token tile, the gather writes
-// silu(gate) * up into these planes and returns true; else the caller applies SiLU itself.
-// `partial`: every rank holds a column slice of the dictionaries, so the projections must be
-// summed over the ranks before the gather.
-// `next_w` (one linear): the first half of the next RMS normalisation of the output - planes of
-// next_w * y into the hidden planes, sums of y^2 into the sums block - rides on the gather when
-// the step is a single token tile (the gather leaves shares of the sums, the next call's
-// projection launch adds them up), and is a launch of its own behind the gather otherwise.
 // Rotary embedding of q and k, the cache write and attention of block li over d->q, d->k, d->v:
 // one launch when every token of the step belongs to a different sequence (a decode step), else
 // the rotary kernel first (tokens of one sequence attend to each other's cache rows).
@@ -328,6 +318,16 @@ void attend(csdr_decoder* d, uint32_t li, uint32_t T, float* out, __nv_bfloat16*
                  hi, lo);
 }
 
+// One group of linears over activation planes: projection launch, rank sum, gather launch.
+// `normed`: the planes hold w*h and the gather applies 1/rms from the sums of squares.
+// `act_hi`: the group is (gate, up) and, when the step is a single token tile, the gather writes
+// silu(gate) * up into these planes and returns true; else the caller applies SiLU itself.
+// `partial`: every rank holds a column slice of the dictionaries, so the projections must be
+// summed over the ranks before the gather.
+// `next_w` (one linear): the first half of the next RMS normalisation of the output - planes of
+// next_w * y into the hidden planes, sums of y^2 into the sums block - rides on the gather when
+// the step is a single token tile (the gather leaves shares of the sums, the next call's
+// projection launch adds them up), and is a launch of its own behind the gather otherwise.
 bool wide(csdr_decoder* d, std::initializer_list<const Linear*> ls, const __nv_bfloat16* planes, size_t plane_elems,
           uint32_t T, bool normed, bool partial, const float* sums, std::initializer_list<WideOut> outs,
           __nv_bfloat16* act_hi = nullptr, __nv_bfloat16* act_lo = nullptr, const float* next_w = nullptr) {
@@ -423,11 +423,12 @@ void run_blocks_planes(csdr_decoder* d, uint32_t T) {
     }
 }
 
-// Steps of at most four tokens on one GPU: a block is three launches. The output projection,
+// Steps of at most four tokens on one GPU: a block is two or three launches. The output projection,
 // gate, up and down of block n and q, k, v of block n + 1 run as ONE list on the persistent GEMV
 // kernel, with the residual additions and SwiGLU as epilogues of its gather role and the two RMS
-// normalisations folded into the products that consume them; rotary embedding with the cache
-// write, and attention, stay kernels of their own between two lists.
+// normalisations folded into the products that consume them; attention (with the rotary
+// embedding and the cache write inside it on a decode step) stays a kernel of its own between
+// two lists.
 bool use_queue(const csdr_decoder* d, uint32_t T) {
     return d->queue_capable && d->P == 1 && T <= 4u && d->ctx->gemv_queue && d->ctx->decoder_queue;
 }
@@ -486,8 +487,9 @@ void run_blocks_queue(csdr_decoder* d, uint32_t T) {
 
 // A short step with the glue of api/cortex_sdk.cpp:1569-1679 folded into the one-launch GEMVs: the
 // two RMS normalisations ride on the products that consume them (q|k|v, gate|up), the residual
-// additions on the output and down projections, SwiGLU on the (gate, up) pair. Six launches per
-// block (q|k|v, rotary + cache, attention, output, gate|up, down) instead of nine.
+// additions on the output and down projections, SwiGLU on the (gate, up) pair. Five launches per
+// block on a decode step (q|k|v, attention with the rotary embedding and the cache write inside,
+// output, gate|up, down; six when the rotary kernel runs on its own) instead of nine.
 uint32_t token_tile(uint32_t T) { return T <= 1 ? 1u : T <= 2 ? 2u : T <= 4 ? 4u : T <= 8 ? 8u : 16u; }
 bool use_folded(const csdr_decoder* d, uint32_t T) {
     return d->P == 1 && T <= 16u && d->ctx->decoder_fold && token_tile(T) <= d->fold_max_mt;
